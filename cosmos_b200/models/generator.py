@@ -1,0 +1,164 @@
+"""Generator engine: prompt prefill on the AR tower, flow-matching denoise loop on the DM tower
+with classifier-free guidance, and tokenizer decode.
+
+The hot loop mirrors the reference's call stack (reference cookbooks/cosmos3/generator/
+audiovisual/README.md:43-48 for the recipe; README.md:74 for the attention semantics):
+for each step, run the DM tower on the cond and uncond branches (as one batch of 2, or one
+branch per CFG-parallel rank), combine the velocities and advance the latent. The prompt's
+AR-tower K/V are computed once and reused by all steps.
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass, field
+from typing import Dict, List, Optional, Sequence, Tuple
+
+import torch
+
+from .. import ops
+from ..config import MoTConfig, SamplingConfig
+from . import rope, sampler as samplers
+from .mot import KV, LOCAL_ATTN, AttnContext, MoTModel, WorkspaceAttn, patchify, unpatchify
+
+
+@dataclass
+class GenState:
+    """Everything the denoise loop needs for one sample."""
+    grid: Tuple[int, int, int]                 # latent (T, H, W)
+    pos: torch.Tensor                          # [3, S_dm] positions of all DM tokens
+    cos_sin: Tuple[torch.Tensor, torch.Tensor]
+    ar_kv_cond: List[KV]
+    ar_kv_uncond: Optional[List[KV]]
+    n_video: int
+    n_sound: int = 0
+    n_action: int = 0
+    domain: int = 0
+    action_dim: Optional[int] = None
+    fps: Optional[int] = None
+    cond_mask: Optional[torch.Tensor] = None   # [S_dm] True = clean conditioning token (never updated)
+    clean_tokens: Optional[torch.Tensor] = None  # [1, S_dm, F] values for the cond_mask positions
+    control_tokens: Optional[torch.Tensor] = None
+
+
+class GeneratorEngine:
+    def __init__(self, model: MoTModel, ctx: Optional[AttnContext] = None, cfg_group=None):
+        """`ctx` is the attention/parallel context of the DM tower; `cfg_group` (optional) is a
+        `parallel.cfgp.CFGParallel` that runs one guidance branch per rank group."""
+        self.model = model
+        self.cfg: MoTConfig = model.cfg
+        dev = next(model.parameters()).device
+        self.ctx = ctx if ctx is not None else (WorkspaceAttn() if dev.type == "cuda" else LOCAL_ATTN)
+        self.cfg_group = cfg_group
+
+    # ------------------------------------------------------------------ prompt
+    @torch.no_grad()
+    def encode_prompt(self, ids: torch.Tensor) -> List[KV]:
+        """ids [B, n] (already padded/truncated to the conditioning length) -> per-layer (K, V)."""
+        pos = rope.text_positions(ids.shape[1], 0, ids.device)
+        _, kvs = self.model.ar_forward(self.model.embed_tokens(ids), pos)
+        return kvs
+
+    # ------------------------------------------------------------------ one DM evaluation
+    @torch.no_grad()
+    def velocity(self, tokens: torch.Tensor, sigma: torch.Tensor, st: GenState, ar_kv: List[KV]
+                 ) -> torch.Tensor:
+        """tokens [B, S_dm, F] (noisy video/sound/action features, padded to a common width)
+        -> velocity prediction of the same shape, bf16/fp32 as the model computes."""
+        m = self.model
+        nv, ns, na = st.n_video, st.n_sound, st.n_action
+        pd = self.cfg.patch_dim
+        dt = m.patch_in.dtype
+        video = tokens[:, :nv, :pd]
+        sound = tokens[:, nv:nv + ns, :self.cfg.sound_latent_dim] if ns else None
+        action = tokens[:, nv + ns:nv + ns + na, :st.action_dim] if na else None
+        cm = None if st.cond_mask is None else st.cond_mask[None].expand(tokens.shape[0], -1)
+        x = m.dm_embed(video.to(dt), sound, action, st.domain, st.fps, cm)
+        h = m.dm_forward(x, sigma, st.pos, ar_kv, self.ctx, cos_sin=st.cos_sin)
+        heads = m.dm_heads(h, nv, ns, na, st.domain, st.action_dim)
+        out = torch.zeros(tokens.shape, dtype=heads["video"].dtype, device=tokens.device) \
+            if (ns or na) else None
+        if out is None:
+            return heads["video"]
+        out[:, :nv, :pd] = heads["video"]
+        if ns:
+            out[:, nv:nv + ns, :self.cfg.sound_latent_dim] = heads["sound"]
+        if na:
+            out[:, nv + ns:, :st.action_dim] = heads["action"]
+        return out
+
+    @torch.no_grad()
+    def denoise_step(self, x: torch.Tensor, sigma: float, sigma_next: float, st: GenState,
+                     sc: SamplingConfig, smp=None) -> torch.Tensor:
+        """One guided step on the fp32 latent tokens x [1, S_dm, F]; returns the updated tokens."""
+        dev = x.device
+        use_cfg = (st.ar_kv_uncond is not None and sc.guidance != 1.0
+                   and samplers.guidance_active(sigma, sc.guidance_interval))
+        xin = x
+        if st.cond_mask is not None and st.clean_tokens is not None:
+            xin = torch.where(st.cond_mask[None, :, None], st.clean_tokens.to(x.dtype), x)
+        mdt = self.model.patch_in.dtype
+        if self.cfg_group is not None and use_cfg:
+            vc, vu = self.cfg_group.branch_velocities(self, xin, sigma, st)
+        elif use_cfg:
+            kv2 = [(torch.cat([kc, ku]), torch.cat([vc_, vu_]))
+                   for (kc, vc_), (ku, vu_) in zip(st.ar_kv_cond, st.ar_kv_uncond)] \
+                if not hasattr(st, "_kv2") else st._kv2
+            st._kv2 = kv2
+            sig = torch.full((2,), float(sigma), device=dev)
+            v2 = self.velocity(xin.to(mdt).expand(2, -1, -1), sig, st, kv2)
+            vc, vu = v2[:1], v2[1:]
+        else:
+            sig = torch.full((1,), float(sigma), device=dev)
+            vc, vu = self.velocity(xin.to(mdt), sig, st, st.ar_kv_cond), None
+        if smp is None or isinstance(smp, samplers.EulerSampler):
+            dt = float(sigma_next - sigma)
+            if smp is not None:
+                smp.i += 1
+            s, f = x.shape[1], x.shape[2]
+            x2 = x.reshape(s, f)
+            if x2.is_cuda and vc.dtype == torch.bfloat16:
+                x_new = ops.cfg_euler_step(x2.contiguous(), vc.reshape(s, f), None if vu is None else vu.reshape(s, f),
+                                           sc.guidance, dt, sc.normalize_cfg).reshape(x.shape)
+            else:
+                x_new = ops.ref.cfg_euler_step(x2, vc.reshape(s, f), None if vu is None else vu.reshape(s, f),
+                                               sc.guidance, dt, sc.normalize_cfg).reshape(x.shape).to(x.dtype)
+        else:
+            v = samplers.cfg_velocity(vc, vu, sc.guidance, sc.normalize_cfg)
+            x_new = smp.step(x, v.to(x.dtype))
+        if st.cond_mask is not None and st.clean_tokens is not None:
+            x_new = torch.where(st.cond_mask[None, :, None], st.clean_tokens.to(x_new.dtype), x_new)
+        return x_new
+
+    # ------------------------------------------------------------------ full loop
+    @torch.no_grad()
+    def sample(self, st: GenState, sc: SamplingConfig, noise: Optional[torch.Tensor] = None,
+               feat_dim: Optional[int] = None, callback=None) -> torch.Tensor:
+        """Runs the whole denoise loop and returns the final fp32 tokens [1, S_dm, F]."""
+        dev = st.pos.device
+        s_dm = st.pos.shape[1]
+        f = feat_dim or self.cfg.patch_dim
+        if noise is None:
+            g = torch.Generator(device=dev)
+            g.manual_seed(sc.seed)
+            noise = torch.randn(1, s_dm, f, generator=g, device=dev, dtype=torch.float32)
+        sig = samplers.shifted_sigmas(sc.num_steps, sc.shift, sc.sigma_max, device="cpu")
+        smp = samplers.make_sampler(sc.scheduler, sig)
+        x = noise.float() * float(sig[0]) if sc.sigma_max is not None else noise.float()
+        for i in range(sc.num_steps):
+            x = self.denoise_step(x, float(sig[i]), float(sig[i + 1]), st, sc, smp)
+            if callback is not None:
+                callback(i, x)
+        return x
+
+    def make_state(self, ids_cond: torch.Tensor, ids_uncond: Optional[torch.Tensor],
+                   grid: Tuple[int, int, int], n_sound: int = 0, n_action: int = 0, **kw) -> GenState:
+        cfg = self.cfg
+        dev = ids_cond.device
+        tgrid = (grid[0] // cfg.patch_t, grid[1] // cfg.patch_hw, grid[2] // cfg.patch_hw)
+        pp = rope.generator_positions(ids_cond.shape[1], tgrid, n_sound, n_action, dev)
+        parts = [pp["video"]] + ([pp["sound"]] if n_sound else []) + ([pp["action"]] if n_action else [])
+        pos = torch.cat(parts, dim=1)
+        cos_sin = rope.rope_tables(pos, cfg.head_dim, cfg.rope_theta, cfg.mrope_section)
+        kv_c = self.encode_prompt(ids_cond)
+        kv_u = self.encode_prompt(ids_uncond) if ids_uncond is not None else None
+        return GenState(grid=grid, pos=pos, cos_sin=cos_sin, ar_kv_cond=kv_c, ar_kv_uncond=kv_u,
+                        n_video=pp["video"].shape[1], n_sound=n_sound, n_action=n_action, **kw)

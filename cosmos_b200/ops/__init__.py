@@ -1,0 +1,177 @@
+"""Fused ops of the framework.
+
+Every function takes torch tensors. CUDA bf16 tensors run the hand-written sm_100a kernels
+of ``cosmos_b200/_C.so`` (``torch.ops.cosmos_b200.*``); CPU tensors (and fp32 CUDA tensors
+in tests of the oracle itself) run the plain-PyTorch definitions in ``reference.py``.
+There is no silent fallback on a GPU: if the extension cannot be loaded, calling an op with
+a CUDA bf16 tensor raises.
+"""
+from __future__ import annotations
+
+import math
+import os
+from pathlib import Path
+from typing import Optional, Tuple
+
+import torch
+
+from . import reference as ref
+from .reference import (EPI_GATED_RESID, EPI_PLAIN, EPI_QKV_ROPE, EPI_SWIGLU, MASK_CAUSAL, MASK_FULL,
+                        MASK_MOT)
+
+_SO = Path(__file__).resolve().parents[1] / "_C.so"
+_loaded = False
+_load_error: Optional[str] = None
+
+
+def load_extension(build_if_missing: bool = True) -> bool:
+    """Loads (building in-tree first if needed) the kernel library. Returns True on success."""
+    global _loaded, _load_error
+    if _loaded:
+        return True
+    try:
+        if not _SO.exists() and build_if_missing and os.environ.get("COSMOS_B200_NO_BUILD") != "1":
+            from ._build import build
+            build()
+        torch.ops.load_library(str(_SO))
+        _loaded = True
+    except Exception as e:  # noqa: BLE001 - reported to the caller on first GPU use
+        _load_error = f"{type(e).__name__}: {e}"
+    return _loaded
+
+
+def extension_loaded() -> bool:
+    return _loaded
+
+
+def _use_cuda(t: torch.Tensor) -> bool:
+    if not (t.is_cuda and t.dtype == torch.bfloat16):
+        return False
+    if not load_extension():
+        raise RuntimeError(
+            "cosmos_b200 kernel library is not available on this GPU host "
+            f"({_load_error}); run `python -m cosmos_b200.ops._build`")
+    return True
+
+
+def _k():
+    return torch.ops.cosmos_b200
+
+
+STATUS_MESSAGES = {
+    0: "ok",
+    1: "timeout: TMA producer waiting for a free stage",
+    2: "timeout: MMA issuer waiting for data",
+    3: "timeout: epilogue waiting for accumulators",
+    4: "timeout: softmax waiting for scores",
+    5: "timeout: waiting for a peer signal",
+    6: "bad argument",
+}
+
+
+def check_status(reset: bool = True) -> None:
+    """Synchronises and raises if any kernel recorded a failure (bounded wait expired)."""
+    if not _loaded or not torch.cuda.is_available():
+        return
+    w = _k().status_word()
+    code = int(w.item())
+    if code != 0:
+        if reset:
+            w.zero_()
+        raise RuntimeError(f"cosmos_b200 kernel reported status {code}: {STATUS_MESSAGES.get(code, '?')}")
+
+
+# --------------------------------------------------------------------------- ops
+def gemm(a, w, bias=None, epi: int = EPI_PLAIN, resid=None, gate=None, rows_per_batch: int = 0, out=None):
+    """a [.., K] @ w[N, K]^T with a fused epilogue (see csrc/gemm_tcgen05.cu)."""
+    if _use_cuda(a):
+        return _k().gemm(a, w, bias, epi, resid, gate, rows_per_batch, out)
+    r = ref.gemm(a, w, bias, epi, resid, gate, rows_per_batch)
+    if out is not None:
+        out.copy_(r.reshape(out.shape))
+        return out
+    return r
+
+
+def linear(x, w, bias=None):
+    return gemm(x, w, bias)
+
+
+def gemm_qkv_rope(a, w, bias, cos, sin, gamma_q, gamma_k, n_q_heads: int, n_k_heads: int,
+                  eps: float = 1e-6, route_ptr=None, route_ld=None, out=None):
+    if _use_cuda(a):
+        return _k().gemm_qkv_rope(a, w, bias, cos, sin, gamma_q, gamma_k, n_q_heads, n_k_heads, eps,
+                                  route_ptr, route_ld, out)
+    assert route_ptr is None, "routed epilogue is CUDA-only"
+    r = ref.gemm_qkv_rope(a, w, bias, cos, sin, gamma_q, gamma_k, n_q_heads, n_k_heads, eps)
+    if out is not None:
+        out.copy_(r.reshape(out.shape))
+        return out
+    return r
+
+
+def attention(q, k, v, scale: Optional[float] = None, mask: int = MASK_FULL, n_ar: int = 0,
+              return_lse: bool = False, dest_ptr=None, rows_per_dest: int = 0, out=None
+              ) -> Tuple[torch.Tensor, Optional[torch.Tensor]]:
+    """Flash attention, q [B, Sq, Hq, D], k/v [B, Skv, Hkv, D] -> (o [B, Sq, Hq, D], lse|None)."""
+    scale = scale if scale is not None else 1.0 / math.sqrt(q.shape[-1])
+    if _use_cuda(q) and q.shape[-1] == 128:
+        o, lse = _k().attn_fwd(q, k, v, scale, mask, n_ar, return_lse, dest_ptr, rows_per_dest, out)
+        return o, (lse if return_lse else None)
+    assert dest_ptr is None, "routed epilogue is CUDA-only"
+    o, lse = ref.attention(q, k, v, scale, mask, n_ar, return_lse)
+    if out is not None:
+        out.copy_(o)
+        o = out
+    return o, lse
+
+
+def rmsnorm(x, gamma=None, eps: float = 1e-6, residual=None):
+    """Returns (y, x + residual | None)."""
+    if _use_cuda(x):
+        y, r = _k().rmsnorm(x.contiguous(), gamma, eps, None if residual is None else residual.contiguous())
+        return y, (r if residual is not None else None)
+    return ref.rmsnorm(x, gamma, eps, residual)
+
+
+def adaln_rmsnorm(x, gamma, shift, scale, rows_per_batch: int, eps: float = 1e-6):
+    if _use_cuda(x):
+        return _k().adaln_rmsnorm(x.contiguous(), gamma, shift, scale, rows_per_batch, eps)
+    return ref.adaln_rmsnorm(x, gamma, shift, scale, rows_per_batch, eps)
+
+
+def mrope(x, cos=None, sin=None, gamma=None, eps: float = 1e-6):
+    """Per-head RMSNorm + rotary embedding on x [.., rows, H, 128]; returns a new tensor on CPU,
+    works in place on CUDA (and returns x)."""
+    if _use_cuda(x) and x.shape[-1] == 128:
+        _k().mrope_(x, cos, sin, gamma, eps)
+        return x
+    return ref.mrope(x, cos, sin, gamma, eps)
+
+
+def gated_residual(x, f, gate=None, rows_per_batch: int = 1):
+    if _use_cuda(x):
+        return _k().gated_residual(x.contiguous(), f.contiguous(), gate, rows_per_batch)
+    return ref.gated_residual(x, f, gate, rows_per_batch)
+
+
+def swiglu(gate_up):
+    if _use_cuda(gate_up):
+        return _k().swiglu(gate_up.contiguous())
+    return ref.swiglu(gate_up)
+
+
+def cfg_euler_step(x, vc, vu, guidance: float, dt: float, normalize: bool = False):
+    """x fp32 latent [rows, d]; CUDA path updates x in place and returns it."""
+    if x.is_cuda and vc.dtype == torch.bfloat16 and load_extension() and x.shape[-1] % 8 == 0 and x.shape[-1] <= 1024:
+        _k().cfg_euler_step_(x, vc.contiguous(), None if vu is None else vu.contiguous(), guidance, dt, normalize)
+        return x
+    return ref.cfg_euler_step(x, vc, vu, guidance, dt, normalize)
+
+
+def l2_flush(buf: torch.Tensor) -> None:
+    """Overwrites `buf` (larger than L2) so that the next kernel starts with a cold cache."""
+    if buf.is_cuda and load_extension():
+        _k().l2_flush_(buf)
+    else:
+        buf.zero_()

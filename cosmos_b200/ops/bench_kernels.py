@@ -1,0 +1,106 @@
+"""Micro-benchmarks of the hot kernels: CUDA-event timing after warm-up, L2 flushed between
+iterations, achieved TFLOP/s (or GB/s) and fraction of the measured peaks.
+
+    python -m cosmos_b200.ops.bench_kernels [--what gemm,attn,norm] [--iters 5] [--small]
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import math
+from pathlib import Path
+
+import torch
+
+from cosmos_b200 import ops
+
+
+def _peaks():
+    p = Path(__file__).resolve().parents[2] / "MEASURED_PEAKS.json"
+    if p.exists():
+        d = json.loads(p.read_text())
+        return d["bf16_tflops"], d["hbm_gbs"], "measured"
+    return 1590.0, 6650.0, "fallback"
+
+
+def timeit(fn, iters, flush):
+    for _ in range(3):
+        fn()
+    torch.cuda.synchronize()
+    times = []
+    for _ in range(iters):
+        ops.l2_flush(flush)
+        s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        s.record()
+        fn()
+        e.record()
+        torch.cuda.synchronize()
+        times.append(s.elapsed_time(e))
+    times.sort()
+    return times[len(times) // 2]
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--what", default="gemm,attn,norm")
+    ap.add_argument("--iters", type=int, default=5)
+    ap.add_argument("--small", action="store_true", help="sizes for a profiler capture")
+    ap.add_argument("--cublas", action="store_true", help="also time torch.matmul / SDPA for comparison")
+    args = ap.parse_args()
+    ops.load_extension()
+    tf_peak, bw_peak, src = _peaks()
+    dev = "cuda"
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
+    out = []
+    what = args.what.split(",")
+    if "gemm" in what:
+        shapes = [(8192, 4096, 4096)] if args.small else [
+            (16384, 4096, 4096), (16384, 6144, 4096), (16384, 24576, 4096), (16384, 4096, 12288)]
+        for m, n, k in shapes:
+            a = torch.randn(m, k, device=dev).bfloat16()
+            w = torch.randn(n, k, device=dev).bfloat16()
+            epi = ops.EPI_SWIGLU if n == 24576 else ops.EPI_PLAIN
+            ms = timeit(lambda: ops.gemm(a, w, epi=epi), args.iters, flush)
+            tf = 2.0 * m * n * k / ms / 1e9
+            rec = {"kernel": "gemm_bf16_tcgen05", "shape": [m, n, k], "epi": epi, "ms": round(ms, 4),
+                   "tflops": round(tf, 1), f"frac_of_{src}_bf16": round(tf / tf_peak, 3)}
+            if args.cublas:
+                ms2 = timeit(lambda: torch.matmul(a, w.t()), args.iters, flush)
+                rec["cublas_ms"] = round(ms2, 4)
+            out.append(rec)
+            print(json.dumps(rec), flush=True)
+    if "attn" in what:
+        cfgs = [(4096, 4096, 8, 2)] if args.small else [(16384, 16384, 8, 2), (32768, 32768, 8, 2)]
+        for sq, skv, hq, hkv in cfgs:
+            q = torch.randn(1, sq, hq, 128, device=dev).bfloat16()
+            k = torch.randn(1, skv, hkv, 128, device=dev).bfloat16()
+            v = torch.randn(1, skv, hkv, 128, device=dev).bfloat16()
+            ms = timeit(lambda: ops.attention(q, k, v), args.iters, flush)
+            tf = 4.0 * sq * skv * hq * 128 / ms / 1e9
+            rec = {"kernel": "flash_attn_fwd_tcgen05", "shape": [sq, skv, hq, hkv], "ms": round(ms, 4),
+                   "tflops": round(tf, 1), f"frac_of_{src}_bf16": round(tf / tf_peak, 3)}
+            if args.cublas:
+                qt, kt, vt = (t.permute(0, 2, 1, 3) for t in (q, k, v))
+                ms2 = timeit(lambda: torch.nn.functional.scaled_dot_product_attention(qt, kt, vt, enable_gqa=True),
+                             args.iters, flush)
+                rec["sdpa_ms"] = round(ms2, 4)
+            out.append(rec)
+            print(json.dumps(rec), flush=True)
+    if "norm" in what:
+        rows, d = (16384, 4096) if args.small else (111600, 4096)
+        x = torch.randn(rows, d, device=dev).bfloat16()
+        g = torch.ones(d, device=dev).bfloat16()
+        mod = torch.randn(1, 2 * d, device=dev).bfloat16()
+        ms = timeit(lambda: ops.adaln_rmsnorm(x, g, mod[:, :d], mod[:, d:], rows), args.iters, flush)
+        gbs = 2.0 * rows * d * 2 / ms / 1e6
+        rec = {"kernel": "adaln_rmsnorm", "shape": [rows, d], "ms": round(ms, 4), "gbs": round(gbs, 1),
+               f"frac_of_{src}_hbm": round(gbs / bw_peak, 3)}
+        out.append(rec)
+        print(json.dumps(rec), flush=True)
+    torch.cuda.synchronize()
+    ops.check_status()
+    return out
+
+
+if __name__ == "__main__":
+    main()

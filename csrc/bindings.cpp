@@ -1,0 +1,341 @@
+// torch glue for the sm_100a kernel library: registers torch.ops.cosmos_b200.* and validates
+// shapes/dtypes/strides before handing raw pointers to the launchers in kernels.h.
+#include <ATen/ATen.h>
+#include <ATen/cuda/CUDAContext.h>
+#include <c10/cuda/CUDAGuard.h>
+#include <torch/library.h>
+
+#include <map>
+#include <mutex>
+#include <optional>
+
+#include "kernels.h"
+#include "runtime.h"
+
+namespace {
+
+using at::Tensor;
+using OptT = std::optional<Tensor>;
+
+cudaStream_t cur_stream() { return at::cuda::getCurrentCUDAStream().stream(); }
+
+void check_bf16_cuda(const Tensor& t, const char* name) {
+  TORCH_CHECK(t.is_cuda(), name, " must be a CUDA tensor");
+  TORCH_CHECK(t.scalar_type() == at::kBFloat16, name, " must be bfloat16");
+}
+const void* opt_ptr(const OptT& t) { return t.has_value() && t->defined() ? t->data_ptr() : nullptr; }
+
+// One int32 status word per device; kernels CAS their first failure code into it.
+Tensor status_tensor(int device) {
+  static std::mutex mu;
+  static std::map<int, Tensor> words;
+  std::lock_guard<std::mutex> g(mu);
+  auto it = words.find(device);
+  if (it == words.end()) {
+    Tensor t = at::zeros({1}, at::TensorOptions().dtype(at::kInt).device(at::kCUDA, device));
+    it = words.emplace(device, t).first;
+  }
+  return it->second;
+}
+
+Tensor status_word() {
+  int dev = 0;
+  cudaGetDevice(&dev);
+  return status_tensor(dev);
+}
+
+Tensor as_2d(const Tensor& x) { return x.dim() == 2 ? x : x.reshape({-1, x.size(-1)}); }
+
+// C = A @ W^T with fused epilogue. A [.., K]; W [N, K]; returns [.., N] (or [.., N/2] for SwiGLU).
+Tensor gemm(const Tensor& A_, const Tensor& W, const OptT& bias, int64_t epi, const OptT& resid,
+            const OptT& gate, int64_t rows_per_batch, const OptT& out) {
+  check_bf16_cuda(A_, "A");
+  check_bf16_cuda(W, "W");
+  c10::cuda::CUDAGuard guard(A_.device());
+  Tensor A = as_2d(A_);
+  TORCH_CHECK(A.stride(1) == 1 && W.dim() == 2 && W.stride(1) == 1, "A and W must be row-major");
+  TORCH_CHECK(A.size(1) == W.size(1), "K mismatch: A ", A.sizes(), " W ", W.sizes());
+  const int64_t M = A.size(0), N = W.size(0), K = A.size(1);
+  const int64_t n_out = (epi == EPI_SWIGLU) ? N / 2 : N;
+  Tensor C;
+  if (out.has_value() && out->defined()) {
+    C = as_2d(*out);
+    check_bf16_cuda(C, "out");
+    TORCH_CHECK(C.size(0) == M && C.size(1) == n_out && C.stride(1) == 1, "bad out shape");
+  } else {
+    C = at::empty({M, n_out}, A.options());
+  }
+  cosmos::GemmArgs g;
+  g.A = A.data_ptr(); g.B = W.data_ptr(); g.C = C.data_ptr();
+  g.M = (int)M; g.N = (int)N; g.K = (int)K;
+  g.lda = A.stride(0); g.ldb = W.stride(0); g.ldc = C.stride(0);
+  g.epi = (int)epi;
+  if (bias.has_value() && bias->defined()) {
+    check_bf16_cuda(*bias, "bias");
+    TORCH_CHECK(bias->numel() == N && bias->is_contiguous(), "bias must be [N]");
+    TORCH_CHECK(epi != EPI_SWIGLU, "bias is not supported with the SwiGLU epilogue");
+    g.bias = bias->data_ptr();
+  }
+  Tensor R;
+  if (epi == EPI_GATED_RESID) {
+    TORCH_CHECK(resid.has_value() && resid->defined(), "gated-residual epilogue needs a residual");
+    R = as_2d(*resid);
+    check_bf16_cuda(R, "resid");
+    TORCH_CHECK(R.size(0) == M && R.size(1) == N && R.stride(1) == 1 && R.stride(0) % 8 == 0,
+                "bad residual shape");
+    g.R = R.data_ptr(); g.ldr = R.stride(0);
+    if (gate.has_value() && gate->defined()) {
+      check_bf16_cuda(*gate, "gate");
+      TORCH_CHECK(gate->is_contiguous() && gate->size(-1) == N && N % 8 == 0, "gate must be [B, N]");
+      TORCH_CHECK(rows_per_batch > 0 && gate->numel() / N * rows_per_batch >= M,
+                  "gate rows do not cover M");
+      g.gate = gate->data_ptr();
+    }
+    g.rows_per_batch = (int)rows_per_batch;
+  }
+  g.status = status_tensor(A.get_device()).data_ptr<int>();
+  cosmos::gemm_bf16(g, cur_stream());
+  auto shape = A_.sizes().vec();
+  shape.back() = n_out;
+  return C.reshape(shape);
+}
+
+// QKV projection with per-head RMSNorm + rotary embedding in the epilogue and optional
+// routing of each 128-column head chunk (route_ptr / route_ld are int64 device tensors).
+Tensor gemm_qkv_rope(const Tensor& A_, const Tensor& W, const OptT& bias, const OptT& cos_t,
+                     const OptT& sin_t, const OptT& gamma_q, const OptT& gamma_k, int64_t n_q_heads,
+                     int64_t n_k_heads, double eps, const OptT& route_ptr, const OptT& route_ld,
+                     const OptT& out) {
+  check_bf16_cuda(A_, "A");
+  check_bf16_cuda(W, "W");
+  c10::cuda::CUDAGuard guard(A_.device());
+  Tensor A = as_2d(A_);
+  TORCH_CHECK(A.stride(1) == 1 && W.stride(1) == 1 && A.size(1) == W.size(1), "bad A/W");
+  const int64_t M = A.size(0), N = W.size(0), K = A.size(1);
+  TORCH_CHECK(N % 128 == 0, "N must be a multiple of the head size 128");
+  cosmos::GemmArgs g;
+  Tensor C;
+  const bool routed = route_ptr.has_value() && route_ptr->defined();
+  if (routed) {
+    TORCH_CHECK(route_ld.has_value() && route_ptr->scalar_type() == at::kLong &&
+                    route_ld->scalar_type() == at::kLong && route_ptr->is_cuda() &&
+                    route_ptr->numel() == N / 128 && route_ld->numel() == N / 128,
+                "route tables must be int64 CUDA tensors with one entry per head");
+    g.route_ptr = reinterpret_cast<const long long*>(route_ptr->data_ptr<int64_t>());
+    g.route_ld = reinterpret_cast<const long long*>(route_ld->data_ptr<int64_t>());
+    C = out.has_value() && out->defined() ? *out : at::empty({0}, A.options());
+  } else {
+    if (out.has_value() && out->defined()) {
+      C = as_2d(*out);
+      TORCH_CHECK(C.size(0) == M && C.size(1) == N && C.stride(1) == 1 && C.stride(0) % 8 == 0);
+    } else {
+      C = at::empty({M, N}, A.options());
+    }
+    g.C = C.data_ptr(); g.ldc = C.stride(0);
+  }
+  g.A = A.data_ptr(); g.B = W.data_ptr();
+  g.M = (int)M; g.N = (int)N; g.K = (int)K;
+  g.lda = A.stride(0); g.ldb = W.stride(0);
+  g.epi = EPI_QKV_ROPE;
+  if (bias.has_value() && bias->defined()) {
+    check_bf16_cuda(*bias, "bias");
+    g.bias = bias->data_ptr();
+  }
+  if (cos_t.has_value() && cos_t->defined()) {
+    TORCH_CHECK(sin_t.has_value() && cos_t->scalar_type() == at::kFloat && cos_t->is_contiguous() &&
+                    sin_t->is_contiguous() && cos_t->size(-1) == 64 && sin_t->sizes() == cos_t->sizes(),
+                "cos/sin tables must be contiguous fp32 [rows, 64]");
+    g.cos_tab = cos_t->data_ptr<float>(); g.sin_tab = sin_t->data_ptr<float>();
+    g.rope_rows = (int)(cos_t->numel() / 64);
+  }
+  if (gamma_q.has_value() && gamma_q->defined()) { check_bf16_cuda(*gamma_q, "gamma_q"); g.gamma_q = gamma_q->data_ptr(); }
+  if (gamma_k.has_value() && gamma_k->defined()) { check_bf16_cuda(*gamma_k, "gamma_k"); g.gamma_k = gamma_k->data_ptr(); }
+  g.n_q_heads = (int)n_q_heads; g.n_k_heads = (int)n_k_heads; g.eps = (float)eps;
+  g.status = status_tensor(A.get_device()).data_ptr<int>();
+  cosmos::gemm_bf16(g, cur_stream());
+  if (routed) return C;
+  auto shape = A_.sizes().vec();
+  shape.back() = N;
+  return C.reshape(shape);
+}
+
+// q [B, Sq, Hq, 128], k/v [B, Skv, Hkv, 128] (any strides with unit inner stride) -> (o, lse)
+std::tuple<Tensor, Tensor> attn_fwd(const Tensor& q, const Tensor& k, const Tensor& v, double scale,
+                                    int64_t mask, int64_t n_ar, bool return_lse, const OptT& dest_ptr,
+                                    int64_t rows_per_dest, const OptT& out) {
+  check_bf16_cuda(q, "q"); check_bf16_cuda(k, "k"); check_bf16_cuda(v, "v");
+  c10::cuda::CUDAGuard guard(q.device());
+  TORCH_CHECK(q.dim() == 4 && k.dim() == 4 && v.dim() == 4, "q/k/v must be [B, S, H, 128]");
+  TORCH_CHECK(q.size(3) == 128 && k.size(3) == 128 && v.size(3) == 128, "head_dim must be 128");
+  TORCH_CHECK(q.stride(3) == 1 && k.stride(3) == 1 && v.stride(3) == 1, "inner stride must be 1");
+  TORCH_CHECK(k.sizes() == v.sizes() && q.size(0) == k.size(0), "shape mismatch");
+  for (const Tensor* t : {&q, &k, &v})
+    for (int d = 0; d < 3; ++d) TORCH_CHECK(t->stride(d) % 8 == 0, "strides must be multiples of 8");
+  const int64_t B = q.size(0), Sq = q.size(1), Hq = q.size(2), Skv = k.size(1), Hkv = k.size(2);
+  Tensor o;
+  const bool routed = dest_ptr.has_value() && dest_ptr->defined();
+  if (out.has_value() && out->defined()) {
+    o = *out;
+    check_bf16_cuda(o, "out");
+    TORCH_CHECK(o.dim() == 4 && o.stride(3) == 1 && o.size(2) == Hq && o.size(3) == 128, "bad out");
+  } else {
+    TORCH_CHECK(!routed, "routed output needs an explicit `out` describing the destination strides");
+    o = at::empty({B, Sq, Hq, 128}, q.options());
+  }
+  Tensor lse;
+  cosmos::AttnArgs a;
+  if (return_lse) {
+    lse = at::empty({B, Hq, Sq}, q.options().dtype(at::kFloat));
+    a.lse = lse.data_ptr<float>();
+  } else {
+    lse = at::empty({0}, q.options().dtype(at::kFloat));
+  }
+  a.Q = q.data_ptr(); a.K = k.data_ptr(); a.V = v.data_ptr(); a.O = o.data_ptr();
+  a.B = (int)B; a.Sq = (int)Sq; a.Skv = (int)Skv; a.Hq = (int)Hq; a.Hkv = (int)Hkv;
+  a.q_stride_b = q.stride(0); a.q_stride_s = q.stride(1); a.q_stride_h = q.stride(2);
+  a.k_stride_b = k.stride(0); a.k_stride_s = k.stride(1); a.k_stride_h = k.stride(2);
+  a.v_stride_b = v.stride(0); a.v_stride_s = v.stride(1); a.v_stride_h = v.stride(2);
+  a.o_stride_b = o.stride(0); a.o_stride_s = o.stride(1); a.o_stride_h = o.stride(2);
+  a.scale = (float)scale; a.mask = (int)mask; a.n_ar = (int)n_ar;
+  if (routed) {
+    TORCH_CHECK(dest_ptr->scalar_type() == at::kLong && dest_ptr->is_cuda() && rows_per_dest > 0 &&
+                    dest_ptr->numel() * rows_per_dest >= Sq,
+                "dest_ptr must be an int64 CUDA tensor covering all query rows");
+    a.dest_ptr = reinterpret_cast<const long long*>(dest_ptr->data_ptr<int64_t>());
+    a.rows_per_dest = (int)rows_per_dest;
+  }
+  a.status = status_tensor(q.get_device()).data_ptr<int>();
+  cosmos::flash_attn_fwd(a, cur_stream());
+  return {o, lse};
+}
+
+std::tuple<Tensor, Tensor> rmsnorm(const Tensor& x, const OptT& gamma, double eps, const OptT& residual) {
+  check_bf16_cuda(x, "x");
+  c10::cuda::CUDAGuard guard(x.device());
+  TORCH_CHECK(x.is_contiguous(), "x must be contiguous");
+  const int64_t d = x.size(-1), rows = x.numel() / d;
+  Tensor y = at::empty_like(x);
+  Tensor res_out;
+  const void* rin = nullptr;
+  void* rout = nullptr;
+  if (residual.has_value() && residual->defined()) {
+    TORCH_CHECK(residual->is_contiguous() && residual->sizes() == x.sizes(), "bad residual");
+    res_out = at::empty_like(x);
+    rin = residual->data_ptr();
+    rout = res_out.data_ptr();
+  } else {
+    res_out = at::empty({0}, x.options());
+  }
+  if (gamma.has_value() && gamma->defined()) TORCH_CHECK(gamma->numel() == d && gamma->is_contiguous());
+  cosmos::rmsnorm(x.data_ptr(), opt_ptr(gamma), y.data_ptr(), rows, (int)d, (float)eps, rin, rout,
+                  cur_stream());
+  return {y, res_out};
+}
+
+Tensor adaln_rmsnorm(const Tensor& x, const OptT& gamma, const Tensor& shift, const Tensor& scale,
+                     int64_t rows_per_batch, double eps) {
+  check_bf16_cuda(x, "x"); check_bf16_cuda(shift, "shift"); check_bf16_cuda(scale, "scale");
+  c10::cuda::CUDAGuard guard(x.device());
+  TORCH_CHECK(x.is_contiguous(), "x must be contiguous");
+  const int64_t d = x.size(-1), rows = x.numel() / d;
+  TORCH_CHECK(shift.size(-1) == d && scale.size(-1) == d && shift.stride(-1) == 1 && scale.stride(-1) == 1);
+  Tensor sh = shift.dim() == 1 ? shift.unsqueeze(0) : shift.reshape({-1, d});
+  Tensor sc = scale.dim() == 1 ? scale.unsqueeze(0) : scale.reshape({-1, d});
+  TORCH_CHECK(sh.stride(0) == sc.stride(0) || sh.size(0) == 1, "shift/scale need equal row strides");
+  TORCH_CHECK(sh.size(0) * rows_per_batch >= rows, "modulation rows do not cover x");
+  Tensor y = at::empty_like(x);
+  cosmos::adaln_rmsnorm(x.data_ptr(), opt_ptr(gamma), sh.data_ptr(), sc.data_ptr(), y.data_ptr(), rows,
+                        (int)d, (int)rows_per_batch, sh.size(0) == 1 ? 0 : sh.stride(0), (float)eps,
+                        cur_stream());
+  return y;
+}
+
+// In place on x [rows.., heads, 128]
+void mrope_(Tensor x, const OptT& cos_t, const OptT& sin_t, const OptT& gamma, double eps) {
+  check_bf16_cuda(x, "x");
+  c10::cuda::CUDAGuard guard(x.device());
+  TORCH_CHECK(x.dim() >= 3 && x.size(-1) == 128 && x.stride(-1) == 1 && x.stride(-2) == 128,
+              "x must be [..., heads, 128] with packed heads");
+  const int64_t heads = x.size(-2);
+  const int64_t row_stride = x.stride(-3);
+  const int64_t rows = x.numel() / (heads * 128);
+  if (x.dim() > 3)
+    for (int d = 0; d < x.dim() - 3; ++d)
+      TORCH_CHECK(x.stride(d) == x.stride(d + 1) * x.size(d + 1), "leading dims must be collapsible");
+  const float* c = nullptr;
+  const float* s = nullptr;
+  int rr = 0;
+  if (cos_t.has_value() && cos_t->defined()) {
+    TORCH_CHECK(cos_t->scalar_type() == at::kFloat && cos_t->is_contiguous() && sin_t.has_value() &&
+                sin_t->is_contiguous() && cos_t->size(-1) == 64);
+    c = cos_t->data_ptr<float>(); s = sin_t->data_ptr<float>(); rr = (int)(cos_t->numel() / 64);
+  }
+  cosmos::mrope_apply(x.data_ptr(), rows, (int)heads, row_stride, c, s, rr, opt_ptr(gamma), (float)eps,
+                      cur_stream());
+}
+
+Tensor gated_residual(const Tensor& x, const Tensor& f, const OptT& gate, int64_t rows_per_batch) {
+  check_bf16_cuda(x, "x"); check_bf16_cuda(f, "f");
+  c10::cuda::CUDAGuard guard(x.device());
+  TORCH_CHECK(x.is_contiguous() && f.is_contiguous() && x.sizes() == f.sizes());
+  const int64_t d = x.size(-1), rows = x.numel() / d;
+  Tensor y = at::empty_like(x);
+  long long gs = 0;
+  if (gate.has_value() && gate->defined()) {
+    check_bf16_cuda(*gate, "gate");
+    TORCH_CHECK(gate->size(-1) == d && gate->stride(-1) == 1);
+    Tensor g2 = gate->dim() == 1 ? gate->unsqueeze(0) : gate->reshape({-1, d});
+    gs = g2.size(0) == 1 ? 0 : g2.stride(0);
+    TORCH_CHECK(gs % 8 == 0 && g2.size(0) * rows_per_batch >= rows);
+  }
+  cosmos::gated_residual(x.data_ptr(), f.data_ptr(), opt_ptr(gate), y.data_ptr(), rows, (int)d,
+                         (int)rows_per_batch, gs, cur_stream());
+  return y;
+}
+
+Tensor swiglu(const Tensor& gate_up) {
+  check_bf16_cuda(gate_up, "gate_up");
+  c10::cuda::CUDAGuard guard(gate_up.device());
+  TORCH_CHECK(gate_up.is_contiguous() && gate_up.size(-1) % 16 == 0);
+  const int64_t dff = gate_up.size(-1) / 2, rows = gate_up.numel() / (2 * dff);
+  auto shape = gate_up.sizes().vec();
+  shape.back() = dff;
+  Tensor y = at::empty(shape, gate_up.options());
+  cosmos::swiglu(gate_up.data_ptr(), y.data_ptr(), rows, (int)dff, cur_stream());
+  return y;
+}
+
+// x fp32 [rows, d] updated in place: x += dt * cfg(vc, vu)
+void cfg_euler_step_(Tensor x, const Tensor& vc, const OptT& vu, double guidance, double dt, bool normalize) {
+  c10::cuda::CUDAGuard guard(x.device());
+  TORCH_CHECK(x.is_cuda() && x.scalar_type() == at::kFloat && x.is_contiguous(), "x must be fp32 contiguous");
+  check_bf16_cuda(vc, "vc");
+  TORCH_CHECK(vc.is_contiguous() && vc.numel() == x.numel());
+  if (vu.has_value() && vu->defined()) { check_bf16_cuda(*vu, "vu"); TORCH_CHECK(vu->is_contiguous() && vu->numel() == x.numel()); }
+  const int64_t d = x.size(-1), rows = x.numel() / d;
+  cosmos::cfg_euler_step(x.data_ptr<float>(), vc.data_ptr(), opt_ptr(vu), (float)guidance, (float)dt,
+                         normalize ? 1 : 0, rows, (int)d, cur_stream());
+}
+
+void l2_flush_(Tensor buf) {
+  c10::cuda::CUDAGuard guard(buf.device());
+  TORCH_CHECK(buf.is_cuda() && buf.is_contiguous());
+  cosmos::l2_flush(buf.data_ptr(), buf.nbytes(), cur_stream());
+}
+
+}  // namespace
+
+TORCH_LIBRARY(cosmos_b200, m) {
+  m.def("status_word", &status_word);
+  m.def("gemm", &gemm);
+  m.def("gemm_qkv_rope", &gemm_qkv_rope);
+  m.def("attn_fwd", &attn_fwd);
+  m.def("rmsnorm", &rmsnorm);
+  m.def("adaln_rmsnorm", &adaln_rmsnorm);
+  m.def("mrope_", &mrope_);
+  m.def("gated_residual", &gated_residual);
+  m.def("swiglu", &swiglu);
+  m.def("cfg_euler_step_", &cfg_euler_step_);
+  m.def("l2_flush_", &l2_flush_);
+  cosmos::register_runtime_ops(m);
+}

@@ -1,0 +1,517 @@
+// K1: persistent bf16 GEMM  C[M,N] = A[M,K] * B[N,K]^T  on tcgen05 tensor cores.
+//
+// Layout of one CTA (192 threads):
+//   warp 0      TMA producer  (A 128x64 and B 256x64 tiles, 128-byte swizzle, 4-stage ring)
+//   warp 1      MMA issuer    (tcgen05.mma M=128 N=256 K=16, fp32 accumulators in TMEM,
+//                              two 256-column accumulator buffers so the epilogue of tile i
+//                              overlaps the main loop of tile i+1)
+//   warps 2..5  epilogue      (tcgen05.ld -> registers -> fused epilogue -> global / peer stores)
+//
+// Fused epilogues (template parameter EPI):
+//   EPI_PLAIN        C = acc (+ bias)
+//   EPI_SWIGLU       B holds [gate ; up] stacked along N; C[m, j] = silu(gate_j) * up_j  (N/2 wide)
+//   EPI_GATED_RESID  C = R + gate[m / rows_per_batch, n] * (acc + bias)   (AdaLN gated residual)
+//   EPI_QKV_ROPE     columns are heads of 128: per-head RMSNorm (q/k) + rotary embedding, and
+//                    each 128-column chunk is written through a routing table, so a chunk
+//                    can land in another GPU's buffer (sequence->head all-to-all of Ulysses
+//                    context parallelism done by the epilogue's stores).
+//
+// All mbarrier waits are bounded; on expiry the kernel records a status code and exits
+// through the common tail (TMEM is freed).
+#include "common.cuh"
+#include "kernels.h"
+
+namespace cb {
+
+constexpr int BM = 128, BN = 256, BK = 64, STAGES = 4;
+constexpr int A_BYTES = BM * BK * 2;      // 16 KB
+constexpr int B_BYTES = BN * BK * 2;      // 32 KB
+constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
+constexpr int GEMM_THREADS = 192;
+constexpr int GEMM_SMEM = STAGES * STAGE_BYTES + 1024 /*align*/ + 256 /*barriers*/;
+
+struct GemmParams {
+  int M, N, K;
+  int b_row1;            // row offset in B of the second 128-row half of the tile
+  int n_tiles, m_tiles;  // tile counts (n_tiles counts 256-wide (or 128-wide for SWIGLU) tiles)
+  bf16* C;
+  long long ldc;
+  const bf16* bias;      // [N] or null
+  const bf16* R;         // residual [M, ldr]
+  long long ldr;
+  const bf16* gate;      // [batches, N]
+  int rows_per_batch;
+  // EPI_QKV_ROPE
+  const long long* route_ptr;  // per 128-col chunk: destination base address (bf16*)
+  const long long* route_ld;   // per chunk: row stride in elements
+  const float* cos_tab;        // [rope_rows, 64]
+  const float* sin_tab;
+  int rope_rows;
+  const bf16* gamma_q;         // [128]
+  const bf16* gamma_k;
+  int n_q_heads, n_k_heads;
+  float eps;
+  int* status;
+};
+
+__device__ __forceinline__ void tile_coords(int t, int m_tiles, int n_tiles, int& tm, int& tn) {
+  // Rasterise in bands of 16 m-tiles so that CTAs running together share A and B tiles in L2.
+  constexpr int GM = 16;
+  const int band = t / (GM * n_tiles);
+  const int first_m = band * GM;
+  const int band_m = min(GM, m_tiles - first_m);
+  const int r = t - band * GM * n_tiles;
+  tm = first_m + r % band_m;
+  tn = r / band_m;
+}
+
+template <int EPI>
+__global__ void __launch_bounds__(GEMM_THREADS, 1)
+gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
+                 const GemmParams p) {
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+  const uint32_t bar_base = smem_base + STAGES * STAGE_BYTES;
+  // barriers: full[STAGES], empty[STAGES], tfull[2], tempty[2]; then tmem slot, abort flag
+  auto full_bar = [&](int s) { return bar_base + 8u * s; };
+  auto empty_bar = [&](int s) { return bar_base + 8u * (STAGES + s); };
+  auto tfull_bar = [&](int b) { return bar_base + 8u * (2 * STAGES + b); };
+  auto tempty_bar = [&](int b) { return bar_base + 8u * (2 * STAGES + 2 + b); };
+  const uint32_t tmem_slot = bar_base + 8u * (2 * STAGES + 4);
+  uint8_t* gen_base = smem_raw + (smem_base - smem_u32(smem_raw));
+  volatile int* abort_flag =
+      reinterpret_cast<volatile int*>(gen_base + STAGES * STAGE_BYTES + 8 * (2 * STAGES + 4) + 8);
+  volatile uint32_t* tmem_slot_ptr =
+      reinterpret_cast<volatile uint32_t*>(gen_base + STAGES * STAGE_BYTES + 8 * (2 * STAGES + 4));
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const int total_tiles = p.m_tiles * p.n_tiles;
+  const int k_blocks = (p.K + BK - 1) / BK;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES; ++s) {
+      mbar_init(full_bar(s), 1);
+      mbar_init(empty_bar(s), 1);
+    }
+    for (int b = 0; b < 2; ++b) {
+      mbar_init(tfull_bar(b), 1);
+      mbar_init(tempty_bar(b), 4);
+    }
+    *abort_flag = 0;
+    fence_barrier_init();
+    prefetch_tmap(&tmA);
+    prefetch_tmap(&tmB);
+  }
+  if (warp == 1) {
+    tmem_alloc(tmem_slot, 512);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot_ptr;
+
+  if (warp == 0) {
+    if (lane == 0) {
+      // ---------------- TMA producer
+      int it = 0;
+      bool ok = true;
+      for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
+        int tm, tn;
+        tile_coords(t, p.m_tiles, p.n_tiles, tm, tn);
+        const int m0 = tm * BM;
+        const int n0 = (EPI == EPI_SWIGLU) ? tn * 128 : tn * BN;
+        for (int kb = 0; kb < k_blocks; ++kb, ++it) {
+          const int s = it % STAGES;
+          const uint32_t ph = (it / STAGES) & 1;
+          if (!mbar_wait(empty_bar(s), ph ^ 1, abort_flag, p.status, ST_TIMEOUT_TMA)) {
+            ok = false;
+            break;
+          }
+          const uint32_t sa = smem_base + s * STAGE_BYTES;
+          mbar_arrive_expect_tx(full_bar(s), STAGE_BYTES);
+          tma_load_2d(sa, &tmA, full_bar(s), kb * BK, m0);
+          tma_load_2d(sa + A_BYTES, &tmB, full_bar(s), kb * BK, n0);
+          tma_load_2d(sa + A_BYTES + B_BYTES / 2, &tmB, full_bar(s), kb * BK, n0 + p.b_row1);
+        }
+      }
+      if (!ok) {
+        // Drain our own copies in flight (bounded) before the CTA leaves.
+        volatile int no_abort = 0;
+        const int first = it > STAGES ? it - STAGES : 0;
+        for (int j = first; j < it; ++j)
+          mbar_wait(full_bar(j % STAGES), (j / STAGES) & 1, &no_abort, nullptr, 0);
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0) {
+      // ---------------- MMA issuer
+      constexpr uint32_t idesc = make_idesc_bf16(BM, BN, 0, 0);
+      int it = 0, tcount = 0;
+      bool ok = true;
+      for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x, ++tcount) {
+        const int b = tcount & 1;
+        const uint32_t bph = (tcount >> 1) & 1;
+        if (!mbar_wait(tempty_bar(b), bph ^ 1, abort_flag, p.status, ST_TIMEOUT_MMA)) break;
+        tc_fence_after();
+        const uint32_t d_tmem = tmem_base + b * BN;
+        for (int kb = 0; kb < k_blocks; ++kb, ++it) {
+          const int s = it % STAGES;
+          const uint32_t ph = (it / STAGES) & 1;
+          if (!mbar_wait(full_bar(s), ph, abort_flag, p.status, ST_TIMEOUT_MMA)) {
+            ok = false;
+            break;
+          }
+          tc_fence_after();
+          const uint32_t sa = smem_base + s * STAGE_BYTES;
+          const uint64_t adesc = make_smem_desc_sw128(sa, 16, 1024);
+          const uint64_t bdesc = make_smem_desc_sw128(sa + A_BYTES, 16, 1024);
+#pragma unroll
+          for (int k = 0; k < BK / 16; ++k) {
+            // advance 32 bytes (16 bf16) along K inside the 128-byte swizzle row: +2 in >>4 units
+            mma_ss(d_tmem, adesc + 2 * k, bdesc + 2 * k, idesc, (kb > 0 || k > 0) ? 1u : 0u);
+          }
+          tc_commit(empty_bar(s));
+        }
+        if (ok) tc_commit(tfull_bar(b));
+      }
+    }
+  } else {
+    // ---------------- epilogue warps (2..5); TMEM lane quadrant = warp % 4
+    const int quad = warp & 3;
+    const int row_in_tile = quad * 32 + lane;
+    int tcount = 0;
+    for (int t = blockIdx.x; t < total_tiles; t += gridDim.x, ++tcount) {
+      const int b = tcount & 1;
+      const uint32_t bph = (tcount >> 1) & 1;
+      int tm, tn;
+      tile_coords(t, p.m_tiles, p.n_tiles, tm, tn);
+      const int m = tm * BM + row_in_tile;
+      if (!mbar_wait(tfull_bar(b), bph, abort_flag, p.status, ST_TIMEOUT_EPI)) break;
+      tc_fence_after();
+      const uint32_t t_addr = tmem_base + (uint32_t(quad * 32) << 16) + b * BN;
+      const bool row_ok = m < p.M;
+
+      if constexpr (EPI == EPI_PLAIN || EPI == EPI_GATED_RESID) {
+        const int n0 = tn * BN;
+#pragma unroll 1
+        for (int c = 0; c < BN; c += 32) {
+          uint32_t v[32];
+          tmem_ld32(t_addr + c, v);
+          tmem_wait_ld();
+          const int n = n0 + c;
+          if (row_ok && n < p.N) {
+            float f[32];
+#pragma unroll
+            for (int i = 0; i < 32; ++i) f[i] = __uint_as_float(v[i]);
+            const bool full32 = (n + 32 <= p.N);
+            if (p.bias) {
+#pragma unroll
+              for (int i = 0; i < 32; ++i)
+                if (full32 || n + i < p.N) f[i] += __bfloat162float(p.bias[n + i]);
+            }
+            if constexpr (EPI == EPI_GATED_RESID) {
+              const bf16* g = p.gate ? p.gate + (long long)(m / p.rows_per_batch) * p.N + n : nullptr;
+              const bf16* r = p.R + (long long)m * p.ldr + n;
+              if (full32) {
+                const uint4* r4 = reinterpret_cast<const uint4*>(r);
+                const uint4* g4 = reinterpret_cast<const uint4*>(g);
+#pragma unroll
+                for (int q = 0; q < 4; ++q) {
+                  const uint4 rv = r4[q];
+                  const uint32_t ru[4] = {rv.x, rv.y, rv.z, rv.w};
+                  uint32_t gu[4] = {0x3f803f80u, 0x3f803f80u, 0x3f803f80u, 0x3f803f80u};
+                  if (g) {
+                    const uint4 gv = g4[q];
+                    gu[0] = gv.x; gu[1] = gv.y; gu[2] = gv.z; gu[3] = gv.w;
+                  }
+#pragma unroll
+                  for (int e = 0; e < 4; ++e) {
+                    f[q * 8 + e * 2] = bf16lo(ru[e]) + bf16lo(gu[e]) * f[q * 8 + e * 2];
+                    f[q * 8 + e * 2 + 1] = bf16hi(ru[e]) + bf16hi(gu[e]) * f[q * 8 + e * 2 + 1];
+                  }
+                }
+              } else {
+                for (int i = 0; i < 32 && n + i < p.N; ++i) {
+                  const float gg = g ? __bfloat162float(g[i]) : 1.f;
+                  f[i] = __bfloat162float(r[i]) + gg * f[i];
+                }
+              }
+            }
+            bf16* dst = p.C + (long long)m * p.ldc + n;
+            if (full32) {
+              uint4* d4 = reinterpret_cast<uint4*>(dst);
+#pragma unroll
+              for (int q = 0; q < 4; ++q) {
+                uint4 o;
+                o.x = pack_bf16(f[q * 8 + 0], f[q * 8 + 1]);
+                o.y = pack_bf16(f[q * 8 + 2], f[q * 8 + 3]);
+                o.z = pack_bf16(f[q * 8 + 4], f[q * 8 + 5]);
+                o.w = pack_bf16(f[q * 8 + 6], f[q * 8 + 7]);
+                d4[q] = o;
+              }
+            } else {
+              for (int i = 0; i < 32 && n + i < p.N; ++i) dst[i] = __float2bfloat16(f[i]);
+            }
+          }
+        }
+      } else if constexpr (EPI == EPI_SWIGLU) {
+        // accumulator columns [0,128) = gate, [128,256) = up, for output columns tn*128 ...
+        const int n0 = tn * 128;
+        const int n_out = p.N / 2;
+#pragma unroll 1
+        for (int c = 0; c < 128; c += 32) {
+          uint32_t g[32], u[32];
+          tmem_ld32(t_addr + c, g);
+          tmem_ld32(t_addr + 128 + c, u);
+          tmem_wait_ld();
+          const int n = n0 + c;
+          if (row_ok && n < n_out) {
+            float f[32];
+#pragma unroll
+            for (int i = 0; i < 32; ++i) {
+              const float gv = __uint_as_float(g[i]);
+              const float uv = __uint_as_float(u[i]);
+              f[i] = gv / (1.f + __expf(-gv)) * uv;
+            }
+            bf16* dst = p.C + (long long)m * p.ldc + n;
+            if (n + 32 <= n_out) {
+              uint4* d4 = reinterpret_cast<uint4*>(dst);
+#pragma unroll
+              for (int q = 0; q < 4; ++q) {
+                uint4 o;
+                o.x = pack_bf16(f[q * 8 + 0], f[q * 8 + 1]);
+                o.y = pack_bf16(f[q * 8 + 2], f[q * 8 + 3]);
+                o.z = pack_bf16(f[q * 8 + 4], f[q * 8 + 5]);
+                o.w = pack_bf16(f[q * 8 + 6], f[q * 8 + 7]);
+                d4[q] = o;
+              }
+            } else {
+              for (int i = 0; i < 32 && n + i < n_out; ++i) dst[i] = __float2bfloat16(f[i]);
+            }
+          }
+        }
+      } else {  // EPI_QKV_ROPE: two heads (128-column chunks) per tile
+#pragma unroll 1
+        for (int hc = 0; hc < 2; ++hc) {
+          const int chunk = tn * 2 + hc;
+          const int n = chunk * 128;
+          float f[128];
+#pragma unroll
+          for (int c = 0; c < 128; c += 32) {
+            uint32_t v[32];
+            tmem_ld32(t_addr + hc * 128 + c, v);
+            tmem_wait_ld();
+#pragma unroll
+            for (int i = 0; i < 32; ++i) f[c + i] = __uint_as_float(v[i]);
+          }
+          if (row_ok && n < p.N) {
+            if (p.bias) {
+#pragma unroll
+              for (int i = 0; i < 128; ++i) f[i] += __bfloat162float(p.bias[n + i]);
+            }
+            const int kind = chunk < p.n_q_heads ? 1 : (chunk < p.n_q_heads + p.n_k_heads ? 2 : 0);
+            if (kind != 0) {
+              const bf16* gam = kind == 1 ? p.gamma_q : p.gamma_k;
+              if (gam) {
+                float ss = 0.f;
+#pragma unroll
+                for (int i = 0; i < 128; ++i) ss += f[i] * f[i];
+                const float rinv = rsqrtf(ss * (1.f / 128.f) + p.eps);
+#pragma unroll
+                for (int i = 0; i < 128; ++i) f[i] = f[i] * rinv * __bfloat162float(gam[i]);
+              }
+              if (p.cos_tab) {
+                const float4* ct =
+                    reinterpret_cast<const float4*>(p.cos_tab + (long long)(m % p.rope_rows) * 64);
+                const float4* st =
+                    reinterpret_cast<const float4*>(p.sin_tab + (long long)(m % p.rope_rows) * 64);
+#pragma unroll
+                for (int q = 0; q < 16; ++q) {
+                  const float4 c4 = ct[q], s4 = st[q];
+                  const float cc[4] = {c4.x, c4.y, c4.z, c4.w};
+                  const float sn[4] = {s4.x, s4.y, s4.z, s4.w};
+#pragma unroll
+                  for (int e = 0; e < 4; ++e) {
+                    const int i = q * 4 + e;
+                    const float a = f[i], bb = f[i + 64];
+                    f[i] = a * cc[e] - bb * sn[e];
+                    f[i + 64] = bb * cc[e] + a * sn[e];
+                  }
+                }
+              }
+            }
+            bf16* dst;
+            if (p.route_ptr) {
+              dst = reinterpret_cast<bf16*>(p.route_ptr[chunk]) + (long long)m * p.route_ld[chunk];
+            } else {
+              dst = p.C + (long long)m * p.ldc + n;
+            }
+            uint4* d4 = reinterpret_cast<uint4*>(dst);
+#pragma unroll
+            for (int q = 0; q < 16; ++q) {
+              uint4 o;
+              o.x = pack_bf16(f[q * 8 + 0], f[q * 8 + 1]);
+              o.y = pack_bf16(f[q * 8 + 2], f[q * 8 + 3]);
+              o.z = pack_bf16(f[q * 8 + 4], f[q * 8 + 5]);
+              o.w = pack_bf16(f[q * 8 + 6], f[q * 8 + 7]);
+              d4[q] = o;
+            }
+          }
+        }
+      }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(tempty_bar(b));
+    }
+  }
+
+  // ---------------- common tail
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, 512);
+  }
+}
+
+}  // namespace cb
+
+// ====================================================================== host
+namespace {
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*,
+                                  const cuuint64_t*, const cuuint64_t*, const cuuint32_t*,
+                                  const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+EncodeTiledFn get_encode() {
+  static EncodeTiledFn fn = nullptr;
+  if (!fn) {
+    void* ptr = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &q) !=
+            cudaSuccess ||
+        q != cudaDriverEntryPointSuccess || !ptr)
+      throw std::runtime_error("cuTensorMapEncodeTiled entry point not found");
+    fn = reinterpret_cast<EncodeTiledFn>(ptr);
+  }
+  return fn;
+}
+}  // namespace
+
+namespace cbh {
+CUtensorMap make_tmap_bf16(const void* base, int rank, const uint64_t* dims,
+                           const uint64_t* strides_bytes, const uint32_t* box, bool swizzle128) {
+  CUtensorMap m;
+  cuuint64_t gdim[5], gstr[5];
+  cuuint32_t bx[5], es[5];
+  for (int i = 0; i < rank; ++i) {
+    gdim[i] = dims[i];
+    bx[i] = box[i];
+    es[i] = 1;
+    if (i + 1 < rank) gstr[i] = strides_bytes[i];
+  }
+  if ((reinterpret_cast<uintptr_t>(base) & 15) != 0)
+    throw std::runtime_error("TMA base address must be 16-byte aligned");
+  for (int i = 0; i + 1 < rank; ++i)
+    if (gstr[i] % 16 != 0) throw std::runtime_error("TMA strides must be multiples of 16 bytes");
+  CUresult r = get_encode()(&m, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, rank, const_cast<void*>(base),
+                            gdim, gstr, bx, es, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                            swizzle128 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_NONE,
+                            CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS)
+    throw std::runtime_error("cuTensorMapEncodeTiled failed with code " + std::to_string((int)r));
+  return m;
+}
+const char* status_str(int st) {
+  switch (st) {
+    case cb::ST_OK: return "ok";
+    case cb::ST_TIMEOUT_TMA: return "timeout: TMA producer waiting for a free stage";
+    case cb::ST_TIMEOUT_MMA: return "timeout: MMA issuer waiting for data";
+    case cb::ST_TIMEOUT_EPI: return "timeout: epilogue waiting for accumulators";
+    case cb::ST_TIMEOUT_SOFTMAX: return "timeout: softmax waiting for scores";
+    case cb::ST_TIMEOUT_PEER: return "timeout: waiting for a peer signal";
+    case cb::ST_BAD_ARG: return "bad argument";
+  }
+  return "unknown";
+}
+}  // namespace cbh
+
+namespace cosmos {
+
+static int sm_count() {
+  static int n = 0;
+  if (!n) {
+    int dev = 0;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev);
+  }
+  return n;
+}
+
+template <int EPI>
+static void launch(const CUtensorMap& ta, const CUtensorMap& tb, const cb::GemmParams& p, int grid,
+                   cudaStream_t stream) {
+  static bool configured = false;
+  if (!configured) {
+    cudaFuncSetAttribute(cb::gemm_bf16_kernel<EPI>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                         cb::GEMM_SMEM);
+    configured = true;
+  }
+  cb::gemm_bf16_kernel<EPI><<<grid, cb::GEMM_THREADS, cb::GEMM_SMEM, stream>>>(ta, tb, p);
+}
+
+void gemm_bf16(const GemmArgs& a, cudaStream_t stream) {
+  if (a.K % 8 != 0 || a.lda % 8 != 0 || a.ldb % 8 != 0)
+    throw std::runtime_error("gemm_bf16: K and leading dimensions must be multiples of 8");
+  if (a.epi == EPI_SWIGLU && (a.N % 2 != 0 || (a.N / 2) % 8 != 0))
+    throw std::runtime_error("gemm_bf16: SwiGLU epilogue needs N/2 to be a multiple of 8");
+  if (a.epi == EPI_QKV_ROPE && a.N % 128 != 0)
+    throw std::runtime_error("gemm_bf16: QKV epilogue needs N to be a multiple of 128");
+  if ((a.epi == EPI_PLAIN || a.epi == EPI_GATED_RESID) && (a.ldc % 8 != 0))
+    throw std::runtime_error("gemm_bf16: ldc must be a multiple of 8");
+
+  const uint64_t dimsA[2] = {(uint64_t)a.K, (uint64_t)a.M};
+  const uint64_t strA[1] = {(uint64_t)a.lda * 2};
+  const uint32_t boxA[2] = {cb::BK, cb::BM};
+  const uint64_t dimsB[2] = {(uint64_t)a.K, (uint64_t)a.N};
+  const uint64_t strB[1] = {(uint64_t)a.ldb * 2};
+  const uint32_t boxB[2] = {cb::BK, 128};
+  CUtensorMap ta = cbh::make_tmap_bf16(a.A, 2, dimsA, strA, boxA, true);
+  CUtensorMap tb = cbh::make_tmap_bf16(a.B, 2, dimsB, strB, boxB, true);
+
+  cb::GemmParams p{};
+  p.M = a.M; p.N = a.N; p.K = a.K;
+  p.m_tiles = (a.M + cb::BM - 1) / cb::BM;
+  if (a.epi == EPI_SWIGLU) {
+    p.n_tiles = (a.N / 2 + 127) / 128;
+    p.b_row1 = a.N / 2;
+  } else {
+    p.n_tiles = (a.N + cb::BN - 1) / cb::BN;
+    p.b_row1 = 128;
+  }
+  p.C = reinterpret_cast<bf16*>(a.C); p.ldc = a.ldc;
+  p.bias = reinterpret_cast<const bf16*>(a.bias);
+  p.R = reinterpret_cast<const bf16*>(a.R); p.ldr = a.ldr;
+  p.gate = reinterpret_cast<const bf16*>(a.gate);
+  p.rows_per_batch = a.rows_per_batch > 0 ? a.rows_per_batch : (a.M > 0 ? a.M : 1);
+  p.route_ptr = a.route_ptr; p.route_ld = a.route_ld;
+  p.cos_tab = a.cos_tab; p.sin_tab = a.sin_tab; p.rope_rows = a.rope_rows > 0 ? a.rope_rows : 1;
+  p.gamma_q = reinterpret_cast<const bf16*>(a.gamma_q);
+  p.gamma_k = reinterpret_cast<const bf16*>(a.gamma_k);
+  p.n_q_heads = a.n_q_heads; p.n_k_heads = a.n_k_heads; p.eps = a.eps;
+  p.status = a.status;
+  const int total = p.m_tiles * p.n_tiles;
+  if (total == 0) return;
+  int grid = a.max_ctas > 0 ? a.max_ctas : sm_count();
+  if (grid > total) grid = total;
+  switch (a.epi) {
+    case EPI_PLAIN: launch<EPI_PLAIN>(ta, tb, p, grid, stream); break;
+    case EPI_SWIGLU: launch<EPI_SWIGLU>(ta, tb, p, grid, stream); break;
+    case EPI_GATED_RESID: launch<EPI_GATED_RESID>(ta, tb, p, grid, stream); break;
+    case EPI_QKV_ROPE: launch<EPI_QKV_ROPE>(ta, tb, p, grid, stream); break;
+    default: throw std::runtime_error("gemm_bf16: unknown epilogue");
+  }
+}
+
+}  // namespace cosmos

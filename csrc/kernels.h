@@ -1,0 +1,93 @@
+// Host-callable launchers of the sm_100a kernel library. Plain C++ (no torch types) so the
+// .cu files compile in seconds; the torch glue lives in bindings.cpp.
+#pragma once
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+enum GemmEpilogue : int {
+  EPI_PLAIN = 0,
+  EPI_SWIGLU = 1,
+  EPI_GATED_RESID = 2,
+  EPI_QKV_ROPE = 3,
+};
+
+enum AttnMask : int {
+  MASK_FULL = 0,    // every query sees every key
+  MASK_CAUSAL = 1,  // query i sees keys j <= i + (Skv - Sq)
+  MASK_MOT = 2,     // rows < n_ar: causal over the first n_ar keys; rows >= n_ar: all keys
+};
+
+namespace cosmos {
+
+struct GemmArgs {
+  const void* A = nullptr;  // [M, K] bf16, row stride lda
+  const void* B = nullptr;  // [N, K] bf16, row stride ldb  (nn.Linear weight layout)
+  void* C = nullptr;        // [M, N] (or [M, N/2] for SwiGLU), row stride ldc
+  int M = 0, N = 0, K = 0;
+  long long lda = 0, ldb = 0, ldc = 0;
+  int epi = EPI_PLAIN;
+  const void* bias = nullptr;  // [N] bf16
+  const void* R = nullptr;     // residual, row stride ldr
+  long long ldr = 0;
+  const void* gate = nullptr;  // [M / rows_per_batch, N] bf16 (null = 1)
+  int rows_per_batch = 0;
+  const long long* route_ptr = nullptr;  // device arrays, one entry per 128-column chunk
+  const long long* route_ld = nullptr;
+  const float* cos_tab = nullptr;  // [rope_rows, 64]
+  const float* sin_tab = nullptr;
+  int rope_rows = 0;
+  const void* gamma_q = nullptr;  // [128] bf16
+  const void* gamma_k = nullptr;
+  int n_q_heads = 0, n_k_heads = 0;
+  float eps = 1e-6f;
+  int* status = nullptr;  // device status word (0 = ok)
+  int max_ctas = 0;       // 0 = one CTA per SM
+};
+void gemm_bf16(const GemmArgs& a, cudaStream_t stream);
+
+struct AttnArgs {
+  // Q [B, Sq, Hq, 128], K/V [B, Skv, Hkv, 128], O [B, Sq, Hq, 128]; element strides given.
+  const void* Q = nullptr;
+  const void* K = nullptr;
+  const void* V = nullptr;
+  void* O = nullptr;
+  float* lse = nullptr;  // optional [B, Hq, Sq] natural-log sum-exp of scaled scores
+  int B = 1, Sq = 0, Skv = 0, Hq = 0, Hkv = 0;
+  long long q_stride_b = 0, q_stride_s = 0, q_stride_h = 0;
+  long long k_stride_b = 0, k_stride_s = 0, k_stride_h = 0;
+  long long v_stride_b = 0, v_stride_s = 0, v_stride_h = 0;
+  long long o_stride_b = 0, o_stride_s = 0, o_stride_h = 0;
+  float scale = 0.f;  // softmax scale (1/sqrt(d))
+  int mask = MASK_FULL;
+  int n_ar = 0;  // MASK_MOT only
+  // Optional routing of output rows to other buffers (head->sequence all-to-all of Ulysses
+  // context parallelism done by the epilogue): rows [r*rows_per_dest, (r+1)*rows_per_dest)
+  // go to dest_ptr[r] with row index local to that block.
+  const long long* dest_ptr = nullptr;
+  int rows_per_dest = 0;
+  int* status = nullptr;
+};
+void flash_attn_fwd(const AttnArgs& a, cudaStream_t stream);
+
+// ---- bandwidth kernels (elementwise.cu) ----
+void rmsnorm(const void* x, const void* gamma, void* y, long long rows, int d, float eps,
+             const void* residual_in, void* residual_out, cudaStream_t s);
+// y = rmsnorm(x) * gamma * (1 + scale[b]) + shift[b]; scale/shift rows of length d, one per batch.
+void adaln_rmsnorm(const void* x, const void* gamma, const void* shift, const void* scale, void* y,
+                   long long rows, int d, int rows_per_batch, long long mod_stride, float eps,
+                   cudaStream_t s);
+// x: [rows, heads, 128] in place; cos/sin [rope_rows, 64] fp32; optional per-head rmsnorm gamma.
+void mrope_apply(void* x, long long rows, int heads, long long row_stride, const float* cos_t,
+                 const float* sin_t, int rope_rows, const void* gamma, float eps, cudaStream_t s);
+// y = x + gate[b] * f
+void gated_residual(const void* x, const void* f, const void* gate, void* y, long long rows, int d,
+                    int rows_per_batch, long long gate_stride, cudaStream_t s);
+void swiglu(const void* gate_up, void* y, long long rows, int dff, cudaStream_t s);
+// Flow-matching Euler step with classifier-free guidance, fp32 latents:
+//   v = vu + g * (vc - vu) [optionally renormalised to |vc| per row]; x += dt * v
+// vc/vu may point into another GPU's memory (CFG-parallel exchange by peer loads).
+void cfg_euler_step(float* x, const void* vc, const void* vu, float guidance, float dt,
+                    int normalize, long long rows, int d, cudaStream_t s);
+void l2_flush(void* buf, size_t bytes, cudaStream_t s);
+
+}  // namespace cosmos

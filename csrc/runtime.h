@@ -1,0 +1,9 @@
+// Native host-side runtime pieces: the paged-KV block allocator used by the Reasoner's
+// decode path and the request scheduler's slot bookkeeping. Registered as torch custom
+// classes so Python holds them by reference and calls cost no interpreter-level loops.
+#pragma once
+#include <torch/library.h>
+
+namespace cosmos {
+void register_runtime_ops(torch::Library& m);
+}

@@ -1,0 +1,247 @@
+"""Numerics of the sm_100a kernels against the plain-PyTorch fp32 definitions."""
+import math
+
+import pytest
+import torch
+
+from cosmos_b200 import ops
+from cosmos_b200.ops import reference as ref
+
+pytestmark = pytest.mark.gpu
+
+DEV = "cuda"
+
+
+def _rand(*shape, scale=1.0, dtype=torch.bfloat16):
+    return (torch.randn(*shape, device=DEV, dtype=torch.float32) * scale).to(dtype)
+
+
+def _close(got, want, atol, rtol, what=""):
+    got = got.float()
+    want = want.float()
+    err = (got - want).abs()
+    tol = atol + rtol * want.abs()
+    bad = (err > tol).sum().item()
+    assert bad == 0, f"{what}: {bad}/{err.numel()} elements off, max err {err.max().item():.4g}"
+
+
+@pytest.fixture(autouse=True)
+def _status_clean():
+    ops.load_extension()
+    yield
+    torch.cuda.synchronize()
+    ops.check_status()
+
+
+def test_extension_is_loaded():
+    assert ops.load_extension(), "kernel library must load on a GPU host"
+    assert hasattr(torch.ops.cosmos_b200, "gemm")
+
+
+@pytest.mark.parametrize("m,n,k", [(128, 256, 64), (256, 512, 256), (1000, 768, 320), (77, 136, 72),
+                                    (4096, 4096, 1024), (300, 6144, 4096)])
+def test_gemm_plain(m, n, k):
+    torch.manual_seed(0)
+    a = _rand(m, k)
+    w = _rand(n, k, scale=1 / math.sqrt(k))
+    got = ops.gemm(a, w)
+    want = a.float() @ w.float().t()
+    _close(got, want, 2e-2, 2e-2, f"gemm {m}x{n}x{k}")
+
+
+def test_gemm_bias_and_strided_a():
+    torch.manual_seed(1)
+    m, n, k = 513, 384, 256
+    big = _rand(m, k + 64)
+    a = big[:, :k]
+    w = _rand(n, k, scale=1 / math.sqrt(k))
+    bias = _rand(n)
+    got = ops.gemm(a, w, bias)
+    want = a.float() @ w.float().t() + bias.float()
+    _close(got, want, 2e-2, 2e-2, "gemm+bias")
+
+
+@pytest.mark.parametrize("m,dff,k", [(256, 512, 128), (700, 1536, 512), (130, 200, 64)])
+def test_gemm_swiglu(m, dff, k):
+    torch.manual_seed(2)
+    a = _rand(m, k)
+    w = _rand(2 * dff, k, scale=1 / math.sqrt(k))
+    got = ops.gemm(a, w, epi=ops.EPI_SWIGLU)
+    want = ref.gemm(a.float(), w.float(), epi=ops.EPI_SWIGLU)
+    assert got.shape == (m, dff)
+    _close(got, want, 2e-2, 2e-2, "gemm swiglu")
+
+
+@pytest.mark.parametrize("m,n,k,rpb", [(512, 256, 128, 256), (600, 520, 192, 300), (384, 1024, 512, 384)])
+def test_gemm_gated_residual(m, n, k, rpb):
+    torch.manual_seed(3)
+    a = _rand(m, k)
+    w = _rand(n, k, scale=1 / math.sqrt(k))
+    r = _rand(m, n)
+    gate = _rand(m // rpb, n)
+    got = ops.gemm(a, w, None, ops.EPI_GATED_RESID, r, gate, rpb)
+    want = ref.gemm(a.float(), w.float(), None, ops.EPI_GATED_RESID, r.float(), gate.float(), rpb)
+    _close(got, want, 3e-2, 2e-2, "gemm gated residual")
+    got2 = ops.gemm(a, w, None, ops.EPI_GATED_RESID, r, None, rpb)
+    want2 = r.float() + a.float() @ w.float().t()
+    _close(got2, want2, 3e-2, 2e-2, "gemm residual without gate")
+
+
+@pytest.mark.parametrize("m,hq,hk", [(256, 4, 2), (333, 8, 2)])
+def test_gemm_qkv_rope(m, hq, hk):
+    torch.manual_seed(4)
+    k = 256
+    n = (hq + 2 * hk) * 128
+    a = _rand(m, k)
+    w = _rand(n, k, scale=1 / math.sqrt(k))
+    ang = torch.rand(m, 64, device=DEV) * 6.28
+    cos, sin = ang.cos().contiguous(), ang.sin().contiguous()
+    gq = (1 + 0.1 * torch.randn(128, device=DEV)).bfloat16()
+    gk = (1 + 0.1 * torch.randn(128, device=DEV)).bfloat16()
+    got = ops.gemm_qkv_rope(a, w, None, cos, sin, gq, gk, hq, hk, 1e-6)
+    want = ref.gemm_qkv_rope(a.float(), w.float(), None, cos, sin, gq.float(), gk.float(), hq, hk, 1e-6)
+    _close(got, want, 3e-2, 2e-2, "qkv rope epilogue")
+
+
+def test_gemm_qkv_rope_routed():
+    """Head chunks written through the routing table land where the table says."""
+    torch.manual_seed(5)
+    m, k, hq, hk = 256, 128, 2, 1
+    n = (hq + 2 * hk) * 128
+    a = _rand(m, k)
+    w = _rand(n, k, scale=1 / math.sqrt(k))
+    bufs = [torch.zeros(m, 128, device=DEV, dtype=torch.bfloat16) for _ in range(n // 128)]
+    ptr = torch.tensor([b.data_ptr() for b in bufs], device=DEV, dtype=torch.int64)
+    ld = torch.full((n // 128,), 128, device=DEV, dtype=torch.int64)
+    ops.gemm_qkv_rope(a, w, None, None, None, None, None, hq, hk, 1e-6, ptr, ld)
+    want = (a.float() @ w.float().t())
+    for i, b in enumerate(bufs):
+        _close(b, want[:, i * 128:(i + 1) * 128], 2e-2, 2e-2, f"routed chunk {i}")
+
+
+@pytest.mark.parametrize("b,sq,skv,hq,hkv,mask", [
+    (1, 256, 256, 1, 1, ops.MASK_FULL),
+    (1, 512, 1024, 4, 1, ops.MASK_FULL),
+    (2, 300, 777, 4, 2, ops.MASK_FULL),
+    (1, 1024, 1024, 2, 1, ops.MASK_CAUSAL),
+    (1, 500, 500, 4, 2, ops.MASK_CAUSAL),
+    (1, 200, 456, 2, 2, ops.MASK_CAUSAL),
+    (1, 2048, 2304, 8, 2, ops.MASK_FULL),
+])
+def test_attention(b, sq, skv, hq, hkv, mask):
+    torch.manual_seed(6)
+    q = _rand(b, sq, hq, 128)
+    k = _rand(b, skv, hkv, 128)
+    v = _rand(b, skv, hkv, 128)
+    got, lse = ops.attention(q, k, v, mask=mask, return_lse=True)
+    want, lse_ref = ref.attention(q.float(), k.float(), v.float(), None, mask, 0, True)
+    _close(got, want, 2e-2, 2e-2, "attention out")
+    _close(lse, lse_ref, 2e-2, 1e-3, "attention lse")
+
+
+def test_attention_mot_mask():
+    torch.manual_seed(7)
+    s, n_ar = 640, 200
+    q = _rand(1, s, 4, 128)
+    k = _rand(1, s, 2, 128)
+    v = _rand(1, s, 2, 128)
+    got, _ = ops.attention(q, k, v, mask=ops.MASK_MOT, n_ar=n_ar)
+    want, _ = ref.attention(q.float(), k.float(), v.float(), None, ops.MASK_MOT, n_ar)
+    _close(got, want, 2e-2, 2e-2, "attention MoT mask")
+
+
+def test_attention_large_scores_rescale():
+    """Scores whose running max grows block after block exercise the lazy O rescale."""
+    torch.manual_seed(8)
+    sq, skv = 256, 1024
+    q = _rand(1, sq, 1, 128)
+    k = _rand(1, skv, 1, 128)
+    ramp = torch.linspace(0.2, 3.0, skv, device=DEV)[None, :, None, None]
+    k = (k.float() * ramp).bfloat16()
+    v = _rand(1, skv, 1, 128)
+    got, _ = ops.attention(q, k, v, scale=1.0)
+    want, _ = ref.attention(q.float(), k.float(), v.float(), 1.0)
+    _close(got, want, 3e-2, 3e-2, "attention with growing max")
+
+
+def test_attention_strided_qkv_views():
+    """q/k/v as views into one fused [S, (Hq+2Hkv)*128] projection buffer."""
+    torch.manual_seed(9)
+    s, hq, hkv = 384, 4, 1
+    qkv = _rand(1, s, (hq + 2 * hkv) * 128)
+    q = qkv[..., :hq * 128].view(1, s, hq, 128)
+    k = qkv[..., hq * 128:(hq + hkv) * 128].view(1, s, hkv, 128)
+    v = qkv[..., (hq + hkv) * 128:].view(1, s, hkv, 128)
+    got, _ = ops.attention(q, k, v)
+    want, _ = ref.attention(q.float(), k.float(), v.float())
+    _close(got, want, 2e-2, 2e-2, "attention on strided views")
+
+
+def test_attention_routed_output():
+    torch.manual_seed(10)
+    s, h, parts = 512, 2, 4
+    q, k, v = _rand(1, s, h, 128), _rand(1, s, h, 128), _rand(1, s, h, 128)
+    rows = s // parts
+    bufs = [torch.zeros(1, rows, h, 128, device=DEV, dtype=torch.bfloat16) for _ in range(parts)]
+    ptr = torch.tensor([b.data_ptr() for b in bufs], device=DEV, dtype=torch.int64)
+    ops.attention(q, k, v, dest_ptr=ptr, rows_per_dest=rows, out=bufs[0])
+    want, _ = ref.attention(q.float(), k.float(), v.float())
+    for i, bfr in enumerate(bufs):
+        _close(bfr, want[:, i * rows:(i + 1) * rows], 2e-2, 2e-2, f"routed rows {i}")
+
+
+@pytest.mark.parametrize("rows,d", [(64, 128), (1000, 512), (333, 4096), (50, 5120)])
+def test_rmsnorm(rows, d):
+    torch.manual_seed(11)
+    x, g, r = _rand(rows, d), _rand(d), _rand(rows, d)
+    y, _ = ops.rmsnorm(x, g, 1e-6)
+    want, _ = ref.rmsnorm(x.float(), g.float(), 1e-6)
+    _close(y, want, 2e-2, 1e-2, "rmsnorm")
+    y2, res = ops.rmsnorm(x, g, 1e-6, r)
+    w2, wres = ref.rmsnorm(x.float(), g.float(), 1e-6, r.float())
+    _close(y2, w2, 2e-2, 1e-2, "rmsnorm+res")
+    _close(res, wres, 2e-2, 1e-2, "residual out")
+
+
+def test_adaln_rmsnorm():
+    torch.manual_seed(12)
+    b, s, d = 2, 300, 512
+    x = _rand(b * s, d)
+    mod = _rand(b, 6 * d, scale=0.3)
+    shift, scale = mod[:, :d], mod[:, d:2 * d]
+    y = ops.adaln_rmsnorm(x, None, shift, scale, s, 1e-6)
+    want = ref.adaln_rmsnorm(x.float(), None, shift.float(), scale.float(), s, 1e-6)
+    _close(y, want, 2e-2, 1e-2, "adaln")
+
+
+def test_mrope_and_qknorm():
+    torch.manual_seed(13)
+    s, h = 500, 6
+    x = _rand(s, h, 128)
+    ang = torch.rand(s, 64, device=DEV) * 6.28
+    cos, sin = ang.cos().contiguous(), ang.sin().contiguous()
+    g = (1 + 0.1 * torch.randn(128, device=DEV)).bfloat16()
+    want = ref.mrope(x.float(), cos, sin, g.float(), 1e-6)
+    got = ops.mrope(x.clone(), cos, sin, g, 1e-6)
+    _close(got, want, 2e-2, 1e-2, "mrope")
+
+
+def test_gated_residual_and_swiglu():
+    torch.manual_seed(14)
+    b, s, d = 2, 200, 256
+    x, f, gate = _rand(b * s, d), _rand(b * s, d), _rand(b, d)
+    _close(ops.gated_residual(x, f, gate, s), ref.gated_residual(x.float(), f.float(), gate.float(), s),
+           2e-2, 1e-2, "gated residual")
+    gu = _rand(b * s, 2 * d)
+    _close(ops.swiglu(gu), ref.swiglu(gu.float()), 2e-2, 1e-2, "swiglu")
+
+
+@pytest.mark.parametrize("normalize", [False, True])
+def test_cfg_euler_step(normalize):
+    torch.manual_seed(15)
+    rows, d = 1000, 64
+    x = torch.randn(rows, d, device=DEV)
+    vc, vu = _rand(rows, d), _rand(rows, d)
+    want = ref.cfg_euler_step(x.clone(), vc, vu, 7.0, -0.03, normalize)
+    got = ops.cfg_euler_step(x.clone(), vc, vu, 7.0, -0.03, normalize)
+    _close(got, want, 1e-5, 1e-5, "cfg euler step")
