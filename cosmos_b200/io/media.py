@@ -1,0 +1,105 @@
+"""Media I/O: images via PIL, videos via an `ffmpeg` binary when one is on PATH and via the
+built-in Motion-JPEG MP4 muxer otherwise. Outputs follow the reference layout
+(`<out>/<name>/vision.mp4`, images as PNG; stereo 48 kHz audio muxed into the MP4,
+reference README.md:109-111)."""
+from __future__ import annotations
+
+import shutil
+import subprocess
+from pathlib import Path
+from typing import Optional, Tuple
+
+import numpy as np
+
+from . import mp4
+
+
+def have_ffmpeg() -> bool:
+    return shutil.which("ffmpeg") is not None
+
+
+def read_image(path, size: Optional[Tuple[int, int]] = None) -> np.ndarray:
+    """-> [H, W, 3] uint8; `size` = (width, height) resizes with centre crop to the aspect ratio."""
+    from PIL import Image
+
+    img = Image.open(path).convert("RGB")
+    if size is not None:
+        img = _resize_center_crop(img, size)
+    return np.asarray(img)
+
+
+def _resize_center_crop(img, size):
+    from PIL import Image
+
+    w, h = size
+    sw, sh = img.size
+    scale = max(w / sw, h / sh)
+    nw, nh = max(w, round(sw * scale)), max(h, round(sh * scale))
+    img = img.resize((nw, nh), Image.BICUBIC)
+    left, top = (nw - w) // 2, (nh - h) // 2
+    return img.crop((left, top, left + w, top + h))
+
+
+def write_image(path, frame: np.ndarray) -> None:
+    from PIL import Image
+
+    Image.fromarray(np.ascontiguousarray(frame)).save(path)
+
+
+def read_video(path, max_frames: Optional[int] = None, size: Optional[Tuple[int, int]] = None
+               ) -> Tuple[np.ndarray, float]:
+    """-> (frames [T, H, W, 3] uint8, fps). Supports .npy/.npz frame arrays, image files (1 frame),
+    Motion-JPEG MP4 natively, and anything else through ffmpeg when available."""
+    from PIL import Image
+
+    path = Path(path)
+    suffix = path.suffix.lower()
+    if suffix == ".npy":
+        frames, fps = np.load(path), 24.0
+    elif suffix == ".npz":
+        z = np.load(path)
+        frames, fps = z["frames"], float(z["fps"]) if "fps" in z else 24.0
+    elif suffix in (".png", ".jpg", ".jpeg", ".bmp", ".webp"):
+        frames, fps = read_image(path)[None], 1.0
+    else:
+        try:
+            frames, fps = mp4.read_mp4_mjpeg(path, max_frames)
+        except ValueError:
+            if not have_ffmpeg():
+                raise
+            frames, fps = _ffmpeg_read(path, max_frames)
+    if max_frames is not None:
+        frames = frames[:max_frames]
+    if size is not None and (frames.shape[2], frames.shape[1]) != tuple(size):
+        frames = np.stack([np.asarray(_resize_center_crop(Image.fromarray(f), size)) for f in frames])
+    return frames, fps
+
+
+def _ffmpeg_read(path, max_frames):
+    probe = subprocess.run(["ffprobe", "-v", "error", "-select_streams", "v:0", "-show_entries",
+                            "stream=width,height,r_frame_rate", "-of", "csv=p=0", str(path)],
+                           capture_output=True, text=True, check=True).stdout.strip().split(",")
+    w, h = int(probe[0]), int(probe[1])
+    num, den = probe[2].split("/")
+    cmd = ["ffmpeg", "-v", "error", "-i", str(path)]
+    if max_frames:
+        cmd += ["-frames:v", str(max_frames)]
+    cmd += ["-f", "rawvideo", "-pix_fmt", "rgb24", "-"]
+    raw = subprocess.run(cmd, capture_output=True, check=True).stdout
+    return np.frombuffer(raw, np.uint8).reshape(-1, h, w, 3), float(num) / float(den)
+
+
+def write_video(path, frames: np.ndarray, fps: float, quality: int = 8, audio: Optional[np.ndarray] = None,
+                sample_rate: int = 48000, prefer_ffmpeg: bool = True) -> str:
+    """Writes `frames` [T, H, W, 3] uint8 as MP4; returns the codec used ('h264' or 'mjpeg')."""
+    frames = np.ascontiguousarray(frames)
+    if prefer_ffmpeg and have_ffmpeg() and audio is None:
+        t, h, w, _ = frames.shape
+        crf = int(np.clip(36 - 2 * quality, 10, 40))
+        cmd = ["ffmpeg", "-y", "-v", "error", "-f", "rawvideo", "-pix_fmt", "rgb24", "-s", f"{w}x{h}", "-r",
+               str(fps), "-i", "-", "-c:v", "libx264", "-pix_fmt", "yuv420p", "-crf", str(crf), str(path)]
+        r = subprocess.run(cmd, input=frames.tobytes(), capture_output=True)
+        if r.returncode == 0:
+            return "h264"
+    mp4.write_mp4_mjpeg(path, frames, fps, quality, audio, sample_rate)
+    return "mjpeg"

@@ -1,0 +1,96 @@
+"""Text tokenizers. A checkpoint directory that ships Hugging Face tokenizer files is loaded
+through `transformers.AutoTokenizer`; otherwise (random-init / offline runs) a deterministic
+byte-level tokenizer is used: ids 0..255 are UTF-8 bytes, followed by the special tokens.
+The chat template mirrors the Qwen-style layout the reference's Reasoner uses
+(`<|im_start|>role\\n...<|im_end|>`; reference cookbooks/cosmos3/reasoner/reasoner_prompt_guide.md:29-75).
+"""
+from __future__ import annotations
+
+from pathlib import Path
+from typing import Dict, List, Optional, Sequence
+
+
+class ByteTokenizer:
+    SPECIALS = ["<|pad|>", "<|endoftext|>", "<|im_start|>", "<|im_end|>", "<|vision_start|>", "<|vision_end|>",
+                "<|image_pad|>", "<|video_pad|>", "<think>", "</think>", "<|bog|>"]
+
+    def __init__(self, vocab_size: int = 32000):
+        assert vocab_size >= 256 + len(self.SPECIALS)
+        self.vocab_size = vocab_size
+        self.special_ids: Dict[str, int] = {s: 256 + i for i, s in enumerate(self.SPECIALS)}
+        self.pad_id = self.special_ids["<|pad|>"]
+        self.eos_id = self.special_ids["<|im_end|>"]
+        self.eot_id = self.special_ids["<|endoftext|>"]
+        self.image_pad_id = self.special_ids["<|image_pad|>"]
+        self.video_pad_id = self.special_ids["<|video_pad|>"]
+
+    def encode(self, text: str) -> List[int]:
+        ids: List[int] = []
+        i = 0
+        while i < len(text):
+            if text[i] == "<":
+                hit = next((s for s in self.SPECIALS if text.startswith(s, i)), None)
+                if hit:
+                    ids.append(self.special_ids[hit])
+                    i += len(hit)
+                    continue
+            ids.extend(text[i].encode("utf-8"))
+            i += 1
+        return ids
+
+    def decode(self, ids: Sequence[int], skip_special: bool = True) -> str:
+        out = bytearray()
+        parts: List[str] = []
+        inv = {v: k for k, v in self.special_ids.items()}
+        for t in ids:
+            t = int(t)
+            if t < 256:
+                out.append(t)
+            else:
+                if out:
+                    parts.append(out.decode("utf-8", errors="replace"))
+                    out = bytearray()
+                if not skip_special and t in inv:
+                    parts.append(inv[t])
+        if out:
+            parts.append(out.decode("utf-8", errors="replace"))
+        return "".join(parts)
+
+    def pad_or_truncate(self, ids: List[int], length: int) -> List[int]:
+        """Conditioning length is fixed: truncate or right-pad (reference README.md:389, 512 tokens)."""
+        return (ids + [self.pad_id] * length)[:length]
+
+    def apply_chat_template(self, messages: List[dict], add_generation_prompt: bool = True,
+                            n_vision_tokens: Sequence[int] = ()) -> List[int]:
+        """messages: [{'role', 'content'}], content a string or a list of parts with 'type' in
+        {'text', 'image_url', 'video_url'}; each media part expands to vision_start + pads + vision_end."""
+        ids: List[int] = []
+        vis = list(n_vision_tokens)
+        for m in messages:
+            ids += self.encode(f"<|im_start|>{m['role']}\n")
+            content = m["content"]
+            if isinstance(content, str):
+                ids += self.encode(content)
+            else:
+                for part in content:
+                    kind = part.get("type")
+                    if kind == "text":
+                        ids += self.encode(part["text"])
+                    elif kind in ("image_url", "video_url", "image", "video"):
+                        n = vis.pop(0) if vis else 0
+                        pad = self.image_pad_id if kind.startswith("image") else self.video_pad_id
+                        ids += [self.special_ids["<|vision_start|>"]] + [pad] * n + [self.special_ids["<|vision_end|>"]]
+                    else:
+                        raise ValueError(f"unknown content part type {kind!r}")
+            ids += self.encode("<|im_end|>\n")
+        if add_generation_prompt:
+            ids += self.encode("<|im_start|>assistant\n")
+        return ids
+
+
+def load_tokenizer(checkpoint_path: Optional[str], vocab_size: int):
+    if checkpoint_path and Path(checkpoint_path).is_dir() and (Path(checkpoint_path) / "tokenizer.json").exists():
+        from transformers import AutoTokenizer
+
+        return AutoTokenizer.from_pretrained(checkpoint_path)
+    return ByteTokenizer(vocab_size)

@@ -118,8 +118,11 @@ flash_attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot_ptr;
 
+  // Register re-partitioning: the CTA owns 384 x 168 registers; 128 x 56 + 256 x 224 uses
+  // exactly that many. A split that needs more would block in setmaxnreg.inc forever.
+  static_assert(128 * 56 + 256 * 224 <= ATT_THREADS * 168, "setmaxnreg split exceeds the CTA's registers");
   if (warp < 4) {
-    asm volatile("setmaxnreg.dec.sync.aligned.u32 64;");
+    asm volatile("setmaxnreg.dec.sync.aligned.u32 56;");
     if (warp == 0 && lane == 0) {
       // ---------------- TMA producer
       mbar_arrive_expect_tx(q_full, 2 * TILE_BYTES);
@@ -332,6 +335,7 @@ flash_attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
   tc_fence_before();
   __syncthreads();
   if (warp == 1) {
+    __syncwarp();
     tc_fence_after();
     tmem_dealloc(tmem_base, 512);
   }

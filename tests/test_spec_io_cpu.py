@@ -1,0 +1,137 @@
+"""Spec parser/validator, pose utilities, MP4 muxer, tokenizer: CPU-only contract tests."""
+import json
+from pathlib import Path
+
+import numpy as np
+import pytest
+
+from cosmos_b200.data.vfm.action import pose_utils
+from cosmos_b200.io import media, mp4
+from cosmos_b200.io.spec import InferenceSpec, SpecError, load_specs, spec_from_dict
+from cosmos_b200.utils.tokenizer import ByteTokenizer
+
+REF = Path("/root/reference")
+
+
+def test_t2v_defaults_match_recipe():
+    s = spec_from_dict({"model_mode": "text2video", "name": "a", "prompt": "x"})
+    assert (s.num_steps, s.guidance, s.shift, s.num_frames, s.fps, s.resolution) == (35, 6.0, 10.0, 189, 24, "720")
+    assert not s.is_transfer and s.is_generator
+
+
+def test_json_vs_jsonl_and_relative_paths(tmp_path):
+    (tmp_path / "p.json").write_text(json.dumps({"subjects": [], "fps": 24}))
+    one = {"model_mode": "text2video", "name": "a", "prompt_path": "p.json"}
+    (tmp_path / "one.json").write_text(json.dumps(one))
+    (tmp_path / "many.jsonl").write_text(json.dumps(one) + "\n\n" + json.dumps({**one, "name": "b"}) + "\n")
+    a = load_specs(tmp_path / "one.json")
+    assert len(a) == 1 and a[0].resolve(a[0].prompt_path) == tmp_path / "p.json"
+    assert a[0].prompt_text() == '{"subjects":[],"fps":24}'  # compact JSON string
+    b = load_specs(tmp_path / "many.jsonl")
+    assert [s.name for s in b] == ["a", "b"]
+    (tmp_path / "dup.jsonl").write_text(json.dumps(one) + "\n" + json.dumps(one) + "\n")
+    with pytest.raises(SpecError):
+        load_specs(tmp_path / "dup.jsonl")
+
+
+@pytest.mark.parametrize("bad", [
+    {"model_mode": "text2video", "name": "a", "bogus_key": 1},
+    {"model_mode": "nope", "name": "a"},
+    {"model_mode": "reasoner", "name": "a", "enable_sound": True},
+    {"model_mode": "text2video", "name": "a", "num_frames": 120},
+    {"model_mode": "text2video", "name": "a", "resolution": "1080"},
+    {"model_mode": "text2video", "name": "a", "fps": 25},
+    {"model_mode": "text2video", "name": "a", "vision_path": "x.jpg"},
+    {"model_mode": "image2video", "name": "a"},
+    {"model_mode": "text2image", "name": "a", "num_frames": 5},
+    {"model_mode": "text2video", "name": "a", "control_guidance": 1.5},
+    {"model_mode": "text2video", "name": "a", "edge": {"control_path": "c.mp4"}},
+    {"model_mode": "video2video", "name": "a", "vision_path": "v.mp4", "edge": {"control_path": "c.mp4"},
+     "num_outputs": 2},
+    {"model_mode": "forward_dynamics", "name": "a", "vision_path": "i.jpg", "domain_name": "av"},
+    {"model_mode": "forward_dynamics", "name": "a", "vision_path": "i.jpg", "domain_name": "mars",
+     "action_chunk_size": 60, "action_path": "a.json"},
+    {"model_mode": "text2video", "name": "a", "guidance": "high"},
+    {"model_mode": "text2video", "name": "a/b"},
+    {"model_mode": "video2video", "name": "a", "vision_path": "v.mp4", "num_frames": 193,
+     "condition_frame_indexes_vision": [49]},
+])
+def test_strict_rejection(bad):
+    with pytest.raises(SpecError):
+        spec_from_dict(bad)
+
+
+def test_action_modes_and_overrides():
+    s = spec_from_dict({"model_mode": "forward_dynamics", "name": "fd", "vision_path": "i.jpg", "domain_name": "av",
+                        "action_chunk_size": 60, "action_path": "a.json", "image_size": 480, "view_point": "ego_view"})
+    assert s.num_frames == 61 and s.guidance == 1.0 and s.fps == 10 and s.resolution == "480"
+    s2 = spec_from_dict({"model_mode": "inverse_dynamics", "name": "id", "vision_path": "v.mp4",
+                         "domain_name": "av", "action_chunk_size": 60, "raw_action_dim": 9},
+                        overrides={"image_size": 256, "seed": 7})
+    assert s2.image_size == 256 and s2.seed == 7 and s2.resolution == "256"
+
+
+@pytest.mark.skipif(not REF.exists(), reason="reference assets not mounted")
+def test_reference_transfer_specs_parse():
+    specs_dir = REF / "cookbooks/cosmos3/generator/transfer/specs"
+    for name in ("edge", "blur", "depth", "seg", "wsm"):
+        (s,) = load_specs(specs_dir / f"{name}.json")
+        assert s.is_transfer and name in s.controls and s.model_mode == "video2video"
+        assert s.num_steps == 50 and s.share_vision_temporal_positions is True
+        assert s.control_guidance in (1.5, 2.0, 3.0)
+    (w,) = load_specs(specs_dir / "wsm.json")
+    assert (w.num_frames, w.fps, w.guidance) == (101, 10, 1.0)
+
+
+def test_rot6d_roundtrip_and_orthonormal():
+    rng = np.random.default_rng(0)
+    q, _ = np.linalg.qr(rng.normal(size=(5, 3, 3)))
+    q[np.linalg.det(q) < 0, :, 2] *= -1
+    d6 = pose_utils.rotmat_to_rot6d(q)
+    r = pose_utils.rot6d_to_rotmat(d6)
+    assert np.allclose(r, q, atol=1e-9)
+    assert np.allclose(r @ np.swapaxes(r, -1, -2), np.eye(3), atol=1e-9)
+
+
+@pytest.mark.skipif(not REF.exists(), reason="reference assets not mounted")
+@pytest.mark.parametrize("traj", ["forward", "left", "right"])
+def test_pose_roundtrip_on_reference_trajectories(traj):
+    path = REF / f"cookbooks/cosmos3/generator/action/assets/actions/av_traj_{traj}.json"
+    act = np.asarray(json.loads(path.read_text()), dtype=np.float64)
+    assert act.shape == (60, 9)
+    poses = pose_utils.pose_rel_to_abs(act, "rot6d", "backward_framewise", 1.35)
+    assert poses.shape == (61, 4, 4) and np.allclose(poses[0], np.eye(4))
+    back = pose_utils.pose_abs_to_rel(poses, "rot6d", "backward_framewise", 1.35)
+    # the stored rot6d need not be exactly orthonormal; compare through the rotation it encodes
+    assert np.allclose(back[:, :3], act[:, :3], atol=1e-8)
+    assert np.allclose(pose_utils.rot6d_to_rotmat(back[:, 3:]), pose_utils.rot6d_to_rotmat(act[:, 3:]), atol=1e-8)
+
+
+def test_mp4_roundtrip_with_audio(tmp_path):
+    rng = np.random.default_rng(1)
+    base = rng.integers(0, 255, size=(1, 48, 64, 3), dtype=np.uint8)
+    frames = np.repeat(base, 5, axis=0)
+    frames[:, :, :, 0] = (np.arange(5)[:, None, None] * 40).astype(np.uint8)
+    audio = np.sin(np.linspace(0, 100, 9600))[:, None].repeat(2, 1)
+    p = tmp_path / "vision.mp4"
+    mp4.write_mp4_mjpeg(p, frames, 24, 10, audio, 48000)
+    got, fps = mp4.read_mp4_mjpeg(p)
+    assert got.shape == frames.shape and abs(fps - 24) < 0.01
+    assert np.abs(got[..., 0].astype(int).mean(axis=(1, 2)) - frames[..., 0].mean(axis=(1, 2))).max() < 6
+    data = p.read_bytes()
+    assert data[4:8] == b"ftyp" and b"moov" in data and b"jpeg" in data and b"twos" in data
+    codec = media.write_video(tmp_path / "v2.mp4", frames, 24)
+    f2, _ = media.read_video(tmp_path / "v2.mp4") if codec == "mjpeg" else (frames, 24)
+    assert f2.shape == frames.shape
+
+
+def test_byte_tokenizer_roundtrip_and_chat():
+    tok = ByteTokenizer(32000)
+    text = "héllo <think>x</think>"
+    ids = tok.encode(text)
+    assert tok.decode(ids, skip_special=False) == text
+    assert len(tok.pad_or_truncate(ids, 512)) == 512
+    chat = tok.apply_chat_template([{"role": "user", "content": [
+        {"type": "image_url", "image_url": {"url": "x"}}, {"type": "text", "text": "what?"}]}], True, [4])
+    assert chat.count(tok.image_pad_id) == 4
+    assert tok.decode(chat, skip_special=False).endswith("<|im_start|>assistant\n")
