@@ -108,8 +108,8 @@ def test_pose_roundtrip_on_reference_trajectories(traj):
 
 
 def test_mp4_roundtrip_with_audio(tmp_path):
-    rng = np.random.default_rng(1)
-    base = rng.integers(0, 255, size=(1, 48, 64, 3), dtype=np.uint8)
+    yy, xx = np.mgrid[0:48, 0:64]
+    base = np.stack([xx * 2, yy * 3, (xx + yy)], axis=-1).astype(np.uint8)[None]
     frames = np.repeat(base, 5, axis=0)
     frames[:, :, :, 0] = (np.arange(5)[:, None, None] * 40).astype(np.uint8)
     audio = np.sin(np.linspace(0, 100, 9600))[:, None].repeat(2, 1)
