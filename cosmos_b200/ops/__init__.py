@@ -54,8 +54,32 @@ def _use_cuda(t: torch.Tensor) -> bool:
     return True
 
 
+class _Counted:
+    """Proxy over torch.ops.cosmos_b200 that counts kernel launches (one per op call)."""
+
+    def __init__(self):
+        self.launches = 0
+
+    def __getattr__(self, name):
+        fn = getattr(torch.ops.cosmos_b200, name)
+
+        def call(*a, **kw):
+            self.launches += 1
+            return fn(*a, **kw)
+
+        return call
+
+
+_counted = _Counted()
+
+
 def _k():
-    return torch.ops.cosmos_b200
+    return _counted
+
+
+def launch_count() -> int:
+    """Number of sm_100a kernel launches issued through this module so far."""
+    return _counted.launches
 
 
 STATUS_MESSAGES = {
@@ -73,7 +97,7 @@ def check_status(reset: bool = True) -> None:
     """Synchronises and raises if any kernel recorded a failure (bounded wait expired)."""
     if not _loaded or not torch.cuda.is_available():
         return
-    w = _k().status_word()
+    w = torch.ops.cosmos_b200.status_word()
     code = int(w.item())
     if code != 0:
         if reset:

@@ -1,0 +1,54 @@
+"""Process bootstrap and engine construction for a mesh.
+
+`init_distributed` reads the torchrun environment (MASTER_ADDR, MASTER_PORT, RANK, WORLD_SIZE,
+LOCAL_RANK; reference cookbooks/cosmos3/reasoner/README.md:41-42), starts NCCL (GPU) or gloo
+(CPU) and builds the mesh from explicit degrees or a preset (`latency` / `throughput`).
+"""
+from __future__ import annotations
+
+import datetime
+import os
+from typing import Optional
+
+import torch
+import torch.distributed as dist
+
+from ..config import ParallelConfig, preset_parallelism
+from .mesh import Mesh
+
+
+def init_distributed(world: Optional[int] = None, rank: Optional[int] = None, local_rank: Optional[int] = None,
+                     preset: Optional[str] = "latency", pc: Optional[ParallelConfig] = None,
+                     backend: Optional[str] = None, n_kv_heads: int = 8, use_cfg: bool = True,
+                     timeout_s: int = 600) -> Mesh:
+    world = int(os.environ.get("WORLD_SIZE", "1")) if world is None else world
+    rank = int(os.environ.get("RANK", "0")) if rank is None else rank
+    local_rank = int(os.environ.get("LOCAL_RANK", "0")) if local_rank is None else local_rank
+    if world > 1 and not dist.is_initialized():
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        os.environ.setdefault("MASTER_PORT", "29500")
+        if backend is None:
+            backend = "nccl" if torch.cuda.is_available() else "gloo"
+        kw = {}
+        if backend == "nccl":
+            kw["device_id"] = torch.device("cuda", local_rank)
+        dist.init_process_group(backend, rank=rank, world_size=world,
+                                timeout=datetime.timedelta(seconds=timeout_s), **kw)
+    if pc is None:
+        pc = preset_parallelism(preset or "latency", world, use_cfg=use_cfg, n_kv_heads=n_kv_heads)
+    return Mesh(pc, world, rank)
+
+
+def build_engine_for_mesh(model, mesh: Mesh, fused: bool = True):
+    """GeneratorEngine whose attention context and CFG handling match the mesh."""
+    from ..models.generator import GeneratorEngine
+
+    ctx = None
+    cfg_group = None
+    if mesh.size("cp") > 1:
+        from .ulysses import make_cp_context
+        ctx = make_cp_context(model.cfg, mesh, fused=fused)
+    if mesh.size("cfgp") > 1:
+        from .cfgp import CFGParallel
+        cfg_group = CFGParallel(mesh, fused=fused)
+    return GeneratorEngine(model, ctx=ctx, cfg_group=cfg_group)

@@ -1,0 +1,333 @@
+"""`Cosmos3OmniPipeline`: the Python API of the Generator, with the call signature of the
+reference's Diffusers pipeline (reference README.md:236-275 and
+cookbooks/cosmos3/generator/audiovisual/run_with_diffusers.ipynb:535-610):
+
+    pipe = Cosmos3OmniPipeline.from_pretrained("nvidia/Cosmos3-Nano", torch_dtype=torch.bfloat16)
+    pipe.scheduler = UniPCMultistepScheduler.from_config(pipe.scheduler.config, flow_shift=10.0)
+    out = pipe(prompt=..., negative_prompt=..., image=None, num_frames=189, height=720, width=1280,
+               fps=24, num_inference_steps=35, guidance_scale=6.0, enable_sound=False, generator=g)
+    out.video, out.sound
+
+Offline there are no published weights: `from_pretrained` loads a safetensors directory when one
+is given and otherwise builds the named architecture with seeded random weights.
+"""
+from __future__ import annotations
+
+import json
+import time
+from dataclasses import dataclass, field
+from pathlib import Path
+from typing import Any, Dict, List, Optional, Sequence, Tuple, Union
+
+import numpy as np
+import torch
+import torch.nn as nn
+
+from . import ops
+from .config import (MoTConfig, SamplingConfig, get_model_config, latent_shape, resolve_size)
+from .models import rope, sampler as samplers
+from .models.generator import GeneratorEngine, GenState
+from .models.mot import MoTModel, patchify, unpatchify
+from .models.sound import SoundTokenizer
+from .models.vae import CausalVideoVAE
+from .utils.guardrails import Guardrails
+from .utils.tokenizer import load_tokenizer
+
+
+@dataclass
+class SchedulerConfig:
+    flow_shift: float = 10.0
+    solver: str = "unipc"
+    num_train_timesteps: int = 1000
+    sigma_max: Optional[float] = None
+
+
+class _Scheduler:
+    solver = "euler"
+
+    def __init__(self, config: Optional[SchedulerConfig] = None, **kw):
+        self.config = config or SchedulerConfig()
+        for k, v in kw.items():
+            setattr(self.config, k, v)
+        self.config.solver = self.solver
+
+    @classmethod
+    def from_config(cls, config: SchedulerConfig, **overrides):
+        cfg = SchedulerConfig(**{**config.__dict__, **overrides})
+        return cls(cfg)
+
+
+class UniPCMultistepScheduler(_Scheduler):
+    """Flow-matching UniPC multistep scheduler (`flow_shift` = sigma warp)."""
+    solver = "unipc"
+
+
+class FlowMatchEulerScheduler(_Scheduler):
+    solver = "euler"
+
+
+@dataclass
+class Cosmos3Output:
+    video: Any = None          # list of PIL images when num_frames == 1, else uint8 array [T, H, W, 3]
+    sound: Optional[np.ndarray] = None  # [N, 2] float32 in [-1, 1] at pipe.sound_tokenizer.config.sampling_rate
+    action: Optional[np.ndarray] = None
+    latents: Optional[torch.Tensor] = None
+    timings: Dict[str, float] = field(default_factory=dict)
+
+
+RESOLUTION_TEMPLATE = " The video has a resolution of {w}x{h}."
+DURATION_TEMPLATE = " The video is {sec:.1f} seconds long at {fps} frames per second."
+
+
+class Cosmos3OmniPipeline:
+    def __init__(self, model: MoTModel, vae: CausalVideoVAE, sound_tokenizer: SoundTokenizer, tokenizer,
+                 scheduler: Optional[_Scheduler] = None, safety_checker: Optional[Guardrails] = None,
+                 enable_safety_checker: bool = True, engine: Optional[GeneratorEngine] = None):
+        self.transformer = model
+        self.vae = vae
+        self.sound_tokenizer = sound_tokenizer
+        self.tokenizer = tokenizer
+        self.scheduler = scheduler or UniPCMultistepScheduler()
+        self.safety_checker = safety_checker if enable_safety_checker else None
+        self.engine = engine or GeneratorEngine(model)
+        self.cfg: MoTConfig = model.cfg
+        self._step_state: Optional[Tuple[GenState, SamplingConfig, torch.Tensor]] = None
+
+    # ------------------------------------------------------------------ construction
+    @classmethod
+    def from_pretrained(cls, name_or_path: str, torch_dtype=torch.bfloat16, device_map: Optional[str] = None,
+                        safety_checker=None, enable_safety_checker: bool = True, seed: int = 0,
+                        config_overrides: Optional[dict] = None, towers: Sequence[str] = ("ar", "dm"),
+                        vae_widths: Sequence[int] = (32, 64, 128, 128), engine_kwargs: Optional[dict] = None):
+        device = "cpu"
+        if device_map in ("cuda", "auto") and torch.cuda.is_available():
+            device = f"cuda:{torch.cuda.current_device()}"
+        elif isinstance(device_map, str) and device_map.startswith("cuda"):
+            device = device_map
+        path = Path(name_or_path)
+        ckpt_dir = path if (path.is_dir() and (path / "transformer").is_dir()) else None
+        if ckpt_dir is not None and (ckpt_dir / "transformer" / "config.json").exists():
+            cfg = MoTConfig(**{k: (tuple(v) if isinstance(v, list) else v) for k, v in
+                               json.loads((ckpt_dir / "transformer" / "config.json").read_text()).items()})
+        else:
+            cfg = get_model_config(name_or_path, **(config_overrides or {}))
+        model = MoTModel(cfg, dtype=torch_dtype, device=device, towers=towers)
+        model.init_weights(seed)
+        vae = CausalVideoVAE(cfg.latent_channels, vae_widths).to(device=device, dtype=torch_dtype)
+        snd = SoundTokenizer(cfg.sound_latent_dim).to(device=device, dtype=torch_dtype)
+        if ckpt_dir is not None:
+            from .ckpt import safetensors_io as sio
+            sio.load_model(model, ckpt_dir / "transformer")
+            if (ckpt_dir / "vae").is_dir():
+                sio.load_into(ckpt_dir / "vae", dict(vae.state_dict()))
+            if (ckpt_dir / "sound_tokenizer").is_dir():
+                sio.load_into(ckpt_dir / "sound_tokenizer", dict(snd.state_dict()))
+        model.eval(), vae.eval(), snd.eval()
+        tok = load_tokenizer(str(ckpt_dir) if ckpt_dir else None, cfg.vocab_size)
+        guard = safety_checker if safety_checker is not None else Guardrails()
+        eng = GeneratorEngine(model, **(engine_kwargs or {}))
+        return cls(model, vae, snd, tok, None, guard, enable_safety_checker, eng)
+
+    def save_pretrained(self, out_dir) -> None:
+        from .ckpt import safetensors_io as sio
+        out = Path(out_dir)
+        sio.save_model(self.transformer, out / "transformer")
+        sio.save_sharded(dict(self.vae.state_dict()), out / "vae")
+        sio.save_sharded(dict(self.sound_tokenizer.state_dict()), out / "sound_tokenizer")
+        (out / "scheduler").mkdir(parents=True, exist_ok=True)
+        (out / "scheduler" / "scheduler_config.json").write_text(json.dumps(self.scheduler.config.__dict__))
+        (out / "model_index.json").write_text(json.dumps({
+            "_class_name": "Cosmos3OmniPipeline", "transformer": "MoTModel", "vae": "CausalVideoVAE",
+            "sound_tokenizer": "SoundTokenizer", "scheduler": type(self.scheduler).__name__}, indent=1))
+
+    def to(self, device):
+        self.transformer.to(device), self.vae.to(device), self.sound_tokenizer.to(device)
+        self.engine = GeneratorEngine(self.transformer, cfg_group=self.engine.cfg_group)
+        return self
+
+    @property
+    def device(self):
+        return next(self.transformer.parameters()).device
+
+    # ------------------------------------------------------------------ text
+    def encode_text(self, text: str) -> torch.Tensor:
+        n = self.cfg.max_text_len
+        ids = self.tokenizer.encode(text)
+        if hasattr(self.tokenizer, "pad_or_truncate"):
+            ids = self.tokenizer.pad_or_truncate(ids, n)
+        else:
+            pad = self.tokenizer.pad_token_id or 0
+            ids = (list(ids) + [pad] * n)[:n]
+        ids = [min(int(i), self.cfg.vocab_size - 1) for i in ids]
+        return torch.tensor([ids], dtype=torch.long, device=self.device)
+
+    # ------------------------------------------------------------------ preparation
+    def prepare(self, prompt: str, negative_prompt: Optional[str] = None, image=None, video=None,
+                num_frames: int = 189, height: int = 720, width: int = 1280, fps: int = 24,
+                num_inference_steps: int = 35, guidance_scale: float = 6.0, enable_sound: bool = False,
+                add_resolution_template: bool = True, add_duration_template: bool = True,
+                condition_frame_indexes: Optional[Sequence[int]] = None, action=None, domain: int = 0,
+                action_dim: Optional[int] = None, denoise_action: bool = False, n_action: int = 0,
+                seed: int = 0, sampling: Optional[SamplingConfig] = None) -> Tuple[GenState, SamplingConfig]:
+        cfg = self.cfg
+        if self.safety_checker is not None:
+            self.safety_checker.check_prompt(prompt)
+        text = prompt
+        if add_resolution_template:
+            text += RESOLUTION_TEMPLATE.format(w=width, h=height)
+        if add_duration_template and num_frames > 1:
+            text += DURATION_TEMPLATE.format(sec=num_frames / float(fps), fps=fps)
+        sc = sampling or SamplingConfig(num_steps=num_inference_steps, guidance=guidance_scale,
+                                        shift=self.scheduler.config.flow_shift,
+                                        sigma_max=self.scheduler.config.sigma_max,
+                                        scheduler=self.scheduler.config.solver, seed=seed)
+        ids_c = self.encode_text(text)
+        ids_u = self.encode_text(negative_prompt or "") if sc.guidance != 1.0 else None
+        grid = latent_shape(cfg, num_frames, width, height)
+        n_sound = 0
+        if enable_sound:
+            n_sound = self.sound_tokenizer.latent_frames(num_frames / float(fps))
+        n_act = n_action or (0 if action is None else len(action))
+        st = self.engine.make_state(ids_c, ids_u, grid, n_sound, n_act, domain=domain, action_dim=action_dim, fps=fps)
+        s_dm = st.pos.shape[1]
+        feat = max(cfg.patch_dim, cfg.sound_latent_dim if n_sound else 0, action_dim or 0 if n_act else 0)
+        cond = torch.zeros(s_dm, dtype=torch.bool, device=self.device)
+        clean = torch.zeros(1, s_dm, feat, dtype=torch.float32, device=self.device)
+        tokens_per_frame = (grid[1] // cfg.patch_hw) * (grid[2] // cfg.patch_hw)
+        vdt = next(self.vae.parameters()).dtype
+        frames = None
+        if image is not None:
+            frames = _to_frames(image, width, height)[:1]
+            condition_frame_indexes = [0] if condition_frame_indexes is None else condition_frame_indexes
+        elif video is not None:
+            frames = _to_frames(video, width, height)
+            condition_frame_indexes = list(condition_frame_indexes or [0])
+        if frames is not None:
+            n_lat = max(condition_frame_indexes) + 1
+            n_pix = 1 + (n_lat - 1) * cfg.vae_t_compress
+            fr = frames[:n_pix]
+            if fr.shape[0] < n_pix:
+                fr = np.concatenate([fr, np.repeat(fr[-1:], n_pix - fr.shape[0], 0)])
+            x = CausalVideoVAE.from_uint8(torch.from_numpy(fr)[None].to(self.device)).to(vdt)
+            with torch.no_grad():
+                z = self.vae.encode(x, chunk_frames=4 if n_pix > 1 else None).float()
+            ztok = patchify(z, cfg)[0]
+            for li in condition_frame_indexes:
+                a, b = li * tokens_per_frame, (li + 1) * tokens_per_frame
+                cond[a:b] = True
+                clean[0, a:b, :cfg.patch_dim] = ztok[a:b]
+        if action is not None and not denoise_action:
+            a = torch.as_tensor(np.asarray(action), dtype=torch.float32, device=self.device)
+            off = st.n_video + st.n_sound
+            cond[off:off + a.shape[0]] = True
+            clean[0, off:off + a.shape[0], :a.shape[1]] = a
+        if cond.any():
+            st.cond_mask, st.clean_tokens = cond, clean
+        return st, sc
+
+    # ------------------------------------------------------------------ step-wise public API
+    @torch.no_grad()
+    def begin(self, st: GenState, sc: SamplingConfig, noise: Optional[torch.Tensor] = None) -> torch.Tensor:
+        """Starts a step-wise generation; returns the initial fp32 latent tokens [1, S, F]."""
+        s_dm = st.pos.shape[1]
+        f = st.clean_tokens.shape[-1] if st.clean_tokens is not None else self.cfg.patch_dim
+        if noise is None:
+            g = torch.Generator(device=self.device)
+            g.manual_seed(sc.seed)
+            noise = torch.randn(1, s_dm, f, generator=g, device=self.device, dtype=torch.float32)
+        sig = samplers.shifted_sigmas(sc.num_steps, sc.shift, sc.sigma_max, device="cpu")
+        self._step_state = (st, sc, sig)
+        self._sampler = samplers.make_sampler(sc.scheduler, sig)
+        return noise * float(sig[0]) if sc.sigma_max is not None else noise
+
+    @torch.no_grad()
+    def step(self, latents: torch.Tensor, i: int) -> torch.Tensor:
+        """Advances device-resident latents by denoise step i."""
+        st, sc, sig = self._step_state
+        smp = self._sampler
+        smp.i = i
+        return self.engine.denoise_step(latents, float(sig[i]), float(sig[i + 1]), st, sc, smp)
+
+    @torch.no_grad()
+    def step_from_host(self, latents_host: torch.Tensor, i: int, out_host: Optional[torch.Tensor] = None
+                       ) -> torch.Tensor:
+        """One denoise step on host-resident latents: pinned host -> device copy, the guided step
+        on the GPU(s), and the updated latents copied back to (pinned) host memory."""
+        dev_lat = latents_host.to(self.device, non_blocking=True)
+        new = self.step(dev_lat, i)
+        if out_host is None:
+            out_host = torch.empty_like(latents_host)
+        out_host.copy_(new, non_blocking=True)
+        torch.cuda.current_stream().synchronize() if self.device.type == "cuda" else None
+        return out_host
+
+    # ------------------------------------------------------------------ decode
+    @torch.no_grad()
+    def decode(self, tokens: torch.Tensor, st: GenState, chunk_latents: Optional[int] = 4):
+        cfg = self.cfg
+        vdt = next(self.vae.parameters()).dtype
+        z = unpatchify(tokens[:, :st.n_video, :cfg.patch_dim], cfg, st.grid).to(vdt)
+        video = self.vae.decode(z, chunk_latents=chunk_latents if st.grid[0] > (chunk_latents or 0) else None)
+        frames = CausalVideoVAE.to_uint8(video)[0].cpu().numpy()
+        sound = None
+        if st.n_sound:
+            lat = tokens[:, st.n_video:st.n_video + st.n_sound, :cfg.sound_latent_dim]
+            sound = self.sound_tokenizer.decode(lat.to(vdt))[0].float().cpu().numpy()
+        action = None
+        if st.n_action:
+            off = st.n_video + st.n_sound
+            action = tokens[0, off:off + st.n_action, :st.action_dim].float().cpu().numpy()
+        return frames, sound, action
+
+    # ------------------------------------------------------------------ __call__
+    @torch.no_grad()
+    def __call__(self, prompt: str, negative_prompt: Optional[str] = None, image=None, video=None,
+                 num_frames: int = 189, height: int = 720, width: int = 1280, fps: int = 24,
+                 num_inference_steps: int = 35, guidance_scale: float = 6.0, enable_sound: bool = False,
+                 add_resolution_template: bool = True, add_duration_template: bool = True,
+                 generator: Optional[torch.Generator] = None, output_type: str = "np",
+                 sampling: Optional[SamplingConfig] = None, callback=None, **prep_kw) -> Cosmos3Output:
+        t0 = time.perf_counter()
+        seed = int(generator.initial_seed()) if generator is not None else (sampling.seed if sampling else 0)
+        st, sc = self.prepare(prompt, negative_prompt, image, video, num_frames, height, width, fps,
+                              num_inference_steps, guidance_scale, enable_sound, add_resolution_template,
+                              add_duration_template, seed=seed, sampling=sampling, **prep_kw)
+        t1 = time.perf_counter()
+        x = self.begin(st, sc)
+        for i in range(sc.num_steps):
+            x = self.step(x, i)
+            if callback is not None:
+                callback(i, sc.num_steps)
+        if self.device.type == "cuda":
+            torch.cuda.synchronize()
+            ops.check_status()
+        t2 = time.perf_counter()
+        if output_type == "latent":
+            return Cosmos3Output(latents=x, timings={"prepare_s": t1 - t0, "sample_s": t2 - t1})
+        frames, sound, action = self.decode(x, st)
+        if self.safety_checker is not None:
+            frames = self.safety_checker.blur_faces(frames)
+        t3 = time.perf_counter()
+        video_out: Any = frames
+        if num_frames == 1 and output_type == "pil":
+            from PIL import Image
+            video_out = [Image.fromarray(frames[0])]
+        return Cosmos3Output(video=video_out, sound=sound, action=action, latents=x,
+                             timings={"prepare_s": t1 - t0, "sample_s": t2 - t1, "decode_s": t3 - t2})
+
+
+def _to_frames(media, width: int, height: int) -> np.ndarray:
+    """PIL image / uint8 array [H, W, 3] or [T, H, W, 3] / path -> uint8 [T, height, width, 3]."""
+    from PIL import Image
+    from .io import media as mio
+
+    if isinstance(media, (str, Path)):
+        return mio.read_video(media, size=(width, height))[0]
+    if isinstance(media, Image.Image):
+        return np.asarray(mio._resize_center_crop(media.convert("RGB"), (width, height)))[None]
+    arr = np.asarray(media)
+    if arr.ndim == 3:
+        arr = arr[None]
+    if (arr.shape[2], arr.shape[1]) != (width, height):
+        arr = np.stack([np.asarray(mio._resize_center_crop(Image.fromarray(f), (width, height))) for f in arr])
+    return arr.astype(np.uint8)

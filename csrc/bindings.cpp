@@ -323,6 +323,59 @@ void l2_flush_(Tensor buf) {
   cosmos::l2_flush(buf.data_ptr(), buf.nbytes(), cur_stream());
 }
 
+const long long* ptr_table(const Tensor& t, const char* name) {
+  TORCH_CHECK(t.is_cuda() && t.scalar_type() == at::kLong && t.is_contiguous(), name,
+              " must be a contiguous int64 CUDA tensor of addresses");
+  return reinterpret_cast<const long long*>(t.data_ptr<int64_t>());
+}
+
+void comm_barrier(const Tensor& pads, int64_t rank, int64_t world, int64_t slot, int64_t epoch) {
+  c10::cuda::CUDAGuard guard(pads.device());
+  TORCH_CHECK(pads.numel() >= world, "one signal pad address per rank is needed");
+  cosmos::comm_barrier(ptr_table(pads, "pads"), (int)rank, (int)world, (int)slot, (int)epoch,
+                       status_tensor(pads.get_device()).data_ptr<int>(), cur_stream());
+}
+
+void allreduce_oneshot(const Tensor& bufs, const Tensor& pads, Tensor out, int64_t rank, int64_t world,
+                       int64_t slot, int64_t epoch) {
+  check_bf16_cuda(out, "out");
+  c10::cuda::CUDAGuard guard(out.device());
+  TORCH_CHECK(out.is_contiguous() && bufs.numel() >= world && pads.numel() >= world);
+  cosmos::allreduce_oneshot(ptr_table(bufs, "bufs"), ptr_table(pads, "pads"), out.data_ptr(), out.numel(),
+                            (int)rank, (int)world, (int)slot, (int)epoch,
+                            status_tensor(out.get_device()).data_ptr<int>(), cur_stream());
+}
+
+// mode 0: reduce + update; mode 1: reduce into `reduced` and add sum(g^2) to sq; mode 2: update from `reduced`
+void rs_adamw(const Tensor& grads, int64_t world, int64_t shard_off, Tensor master, Tensor m, Tensor v,
+              Tensor param_shard, double grad_scale, double lr, double b1, double b2, double eps, double wd,
+              int64_t step, int64_t mode, const OptT& sq, const OptT& reduced) {
+  c10::cuda::CUDAGuard guard(master.device());
+  TORCH_CHECK(master.scalar_type() == at::kFloat && m.scalar_type() == at::kFloat && v.scalar_type() == at::kFloat);
+  check_bf16_cuda(param_shard, "param_shard");
+  const int64_t n = master.numel();
+  TORCH_CHECK(m.numel() == n && v.numel() == n && param_shard.numel() == n, "shard size mismatch");
+  TORCH_CHECK(master.is_contiguous() && m.is_contiguous() && v.is_contiguous() && param_shard.is_contiguous());
+  float* sqp = nullptr;
+  float* redp = nullptr;
+  if (mode == 1) {
+    TORCH_CHECK(sq.has_value() && reduced.has_value() && reduced->numel() == n && reduced->scalar_type() == at::kFloat);
+    sqp = sq->data_ptr<float>(); redp = reduced->data_ptr<float>();
+  } else if (mode == 2) {
+    TORCH_CHECK(reduced.has_value() && reduced->numel() == n && reduced->scalar_type() == at::kFloat);
+    redp = reduced->data_ptr<float>();
+  }
+  cosmos::rs_adamw(ptr_table(grads, "grads"), (int)world, shard_off, n, master.data_ptr<float>(),
+                   m.data_ptr<float>(), v.data_ptr<float>(), param_shard.data_ptr(), (float)grad_scale, (float)lr,
+                   (float)b1, (float)b2, (float)eps, (float)wd, (int)step, sqp, redp, cur_stream());
+}
+
+void allgather_pull(const Tensor& srcs, int64_t world, Tensor dst, int64_t bytes_per_rank) {
+  c10::cuda::CUDAGuard guard(dst.device());
+  TORCH_CHECK(dst.is_cuda() && dst.is_contiguous() && dst.nbytes() >= (size_t)(bytes_per_rank * world));
+  cosmos::allgather_pull(ptr_table(srcs, "srcs"), (int)world, dst.data_ptr(), bytes_per_rank, cur_stream());
+}
+
 }  // namespace
 
 TORCH_LIBRARY(cosmos_b200, m) {
@@ -337,5 +390,9 @@ TORCH_LIBRARY(cosmos_b200, m) {
   m.def("swiglu", &swiglu);
   m.def("cfg_euler_step_", &cfg_euler_step_);
   m.def("l2_flush_", &l2_flush_);
+  m.def("comm_barrier", &comm_barrier);
+  m.def("allreduce_oneshot", &allreduce_oneshot);
+  m.def("rs_adamw", &rs_adamw);
+  m.def("allgather_pull", &allgather_pull);
   cosmos::register_runtime_ops(m);
 }

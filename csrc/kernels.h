@@ -90,4 +90,19 @@ void cfg_euler_step(float* x, const void* vc, const void* vu, float guidance, fl
                     int normalize, long long rows, int d, cudaStream_t s);
 void l2_flush(void* buf, size_t bytes, cudaStream_t s);
 
+// ---- communication kernels over peer mappings (comm.cu) ----
+// pads_dev / bufs_dev / grads_dev / srcs_dev: device arrays with one address per rank of the group.
+// Signal pads are int32 arrays laid out as [slot][64]; epochs must grow monotonically per slot.
+void comm_barrier(const long long* pads_dev, int rank, int world, int slot, int epoch, int* status,
+                  cudaStream_t s);
+// Uses slots [slot, slot + 8) and epochs (epoch, epoch + 1).
+void allreduce_oneshot(const long long* bufs_dev, const long long* pads_dev, void* out,
+                       long long n_elems, int rank, int world, int slot, int epoch, int* status,
+                       cudaStream_t s);
+void rs_adamw(const long long* grads_dev, int world, long long shard_off, long long n, float* master,
+              float* m, float* v, void* param_shard, float grad_scale, float lr, float b1, float b2,
+              float eps, float wd, int step, float* sq_out, float* reduced_out, cudaStream_t s);
+void allgather_pull(const long long* srcs_dev, int world, void* dst, long long bytes_per_rank,
+                    cudaStream_t s);
+
 }  // namespace cosmos
