@@ -37,6 +37,9 @@ class GenState:
     cond_mask: Optional[torch.Tensor] = None   # [S_dm] True = clean conditioning token (never updated)
     clean_tokens: Optional[torch.Tensor] = None  # [1, S_dm, F] values for the cond_mask positions
     control_tokens: Optional[torch.Tensor] = None
+    # context parallelism: this rank holds DM tokens [shard_start, shard_start + S_dm) of total_tokens
+    shard_start: int = 0
+    total_tokens: int = 0
 
 
 class GeneratorEngine:
@@ -157,8 +160,18 @@ class GeneratorEngine:
         pp = rope.generator_positions(ids_cond.shape[1], tgrid, n_sound, n_action, dev)
         parts = [pp["video"]] + ([pp["sound"]] if n_sound else []) + ([pp["action"]] if n_action else [])
         pos = torch.cat(parts, dim=1)
+        total = pos.shape[1]
+        n_video, start = pp["video"].shape[1], 0
+        cp, cp_rank = getattr(self.ctx, "cp", 1), getattr(self.ctx, "rank", 0)
+        if cp > 1:
+            if n_sound or n_action or total % cp:
+                raise ValueError("context parallelism needs a video-only token sequence divisible by cp")
+            n_video = total // cp
+            start = cp_rank * n_video
+            pos = pos[:, start:start + n_video].contiguous()
         cos_sin = rope.rope_tables(pos, cfg.head_dim, cfg.rope_theta, cfg.mrope_section)
         kv_c = self.encode_prompt(ids_cond)
         kv_u = self.encode_prompt(ids_uncond) if ids_uncond is not None else None
         return GenState(grid=grid, pos=pos, cos_sin=cos_sin, ar_kv_cond=kv_c, ar_kv_uncond=kv_u,
-                        n_video=pp["video"].shape[1], n_sound=n_sound, n_action=n_action, **kw)
+                        n_video=n_video, n_sound=n_sound, n_action=n_action, shard_start=start,
+                        total_tokens=total, **kw)

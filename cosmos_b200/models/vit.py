@@ -1,0 +1,71 @@
+"""Vision encoder of the Reasoner (AR side): a ViT over 16x16 patches with temporal patch 2 and
+2x2 spatial merge, producing one d_model embedding per merged patch (Qwen3-VL conventions, which
+the reference's Reasoner follows: reference README.md:145,286 and
+cookbooks/cosmos3/reasoner/reasoner_prompt_guide.md:77-99)."""
+from __future__ import annotations
+
+from typing import Tuple
+
+import torch
+import torch.nn as nn
+import torch.nn.functional as F
+
+from ..config import MoTConfig
+
+
+class ViTBlock(nn.Module):
+    def __init__(self, dim: int, heads: int):
+        super().__init__()
+        self.heads = heads
+        self.n1, self.n2 = nn.LayerNorm(dim, eps=1e-6), nn.LayerNorm(dim, eps=1e-6)
+        self.qkv, self.proj = nn.Linear(dim, 3 * dim), nn.Linear(dim, dim)
+        self.fc1, self.fc2 = nn.Linear(dim, 4 * dim), nn.Linear(4 * dim, dim)
+
+    def forward(self, x):
+        b, s, d = x.shape
+        q, k, v = self.qkv(self.n1(x)).view(b, s, 3, self.heads, d // self.heads).unbind(2)
+        a = torch.softmax(torch.einsum("bqhd,bkhd->bhqk", q.float(), k.float()) / (d // self.heads) ** 0.5, dim=-1)
+        o = torch.einsum("bhqk,bkhd->bqhd", a, v.float()).reshape(b, s, d).to(x.dtype)
+        x = x + self.proj(o)
+        return x + self.fc2(F.gelu(self.fc1(self.n2(x)), approximate="tanh"))
+
+
+class VisionEncoder(nn.Module):
+    def __init__(self, cfg: MoTConfig):
+        super().__init__()
+        self.cfg = cfg
+        p, tp, hdim = cfg.vit_patch, cfg.vit_temporal_patch, cfg.vit_hidden
+        self.patch = nn.Linear(3 * tp * p * p, hdim)
+        self.pos = nn.Parameter(torch.zeros(48 * 48, hdim))
+        self.blocks = nn.ModuleList([ViTBlock(hdim, cfg.vit_heads) for _ in range(cfg.vit_depth)])
+        self.norm = nn.LayerNorm(hdim, eps=1e-6)
+        m = cfg.vit_spatial_merge
+        self.merge = nn.Sequential(nn.Linear(hdim * m * m, hdim * m * m), nn.GELU(), nn.Linear(hdim * m * m, cfg.d_model))
+        nn.init.normal_(self.pos, std=0.02)
+
+    def grid(self, frames: int, height: int, width: int) -> Tuple[int, int, int]:
+        """Token grid (t, h, w) after temporal patching and spatial merge."""
+        c = self.cfg
+        t = max(1, (frames + c.vit_temporal_patch - 1) // c.vit_temporal_patch)
+        unit = c.vit_patch * c.vit_spatial_merge
+        return t, height // unit, width // unit
+
+    def forward(self, video: torch.Tensor) -> Tuple[torch.Tensor, Tuple[int, int, int]]:
+        """video [T, 3, H, W] in [-1, 1] (H, W multiples of patch*merge) -> ([t*h*w, d_model], (t, h, w))."""
+        c = self.cfg
+        p, tp, m = c.vit_patch, c.vit_temporal_patch, c.vit_spatial_merge
+        t_in, _, hh, ww = video.shape
+        if t_in % tp:
+            video = torch.cat([video, video[-1:].expand(tp - t_in % tp, -1, -1, -1)])
+        t = video.shape[0] // tp
+        gh, gw = hh // p, ww // p
+        x = video.view(t, tp, 3, gh, p, gw, p).permute(0, 3, 5, 2, 1, 4, 6).reshape(t, gh * gw, -1)
+        x = self.patch(x.to(self.patch.weight.dtype))
+        pos = F.interpolate(self.pos.view(1, 48, 48, -1).permute(0, 3, 1, 2).float(), size=(gh, gw), mode="bilinear",
+                            align_corners=False).permute(0, 2, 3, 1).reshape(1, gh * gw, -1).to(x.dtype)
+        x = x + pos
+        for blk in self.blocks:  # attention within each temporal slice
+            x = blk(x)
+        x = self.norm(x).view(t, gh // m, m, gw // m, m, -1).permute(0, 1, 3, 2, 4, 5)
+        x = x.reshape(t * (gh // m) * (gw // m), -1)
+        return self.merge(x), (t, gh // m, gw // m)

@@ -230,11 +230,14 @@ class Cosmos3OmniPipeline:
     def begin(self, st: GenState, sc: SamplingConfig, noise: Optional[torch.Tensor] = None) -> torch.Tensor:
         """Starts a step-wise generation; returns the initial fp32 latent tokens [1, S, F]."""
         s_dm = st.pos.shape[1]
+        total = st.total_tokens or s_dm
         f = st.clean_tokens.shape[-1] if st.clean_tokens is not None else self.cfg.patch_dim
         if noise is None:
             g = torch.Generator(device=self.device)
             g.manual_seed(sc.seed)
-            noise = torch.randn(1, s_dm, f, generator=g, device=self.device, dtype=torch.float32)
+            noise = torch.randn(1, total, f, generator=g, device=self.device, dtype=torch.float32)
+        if noise.shape[1] != s_dm:  # context-parallel shard of the full-sequence noise
+            noise = noise[:, st.shard_start:st.shard_start + s_dm].contiguous()
         sig = samplers.shifted_sigmas(sc.num_steps, sc.shift, sc.sigma_max, device="cpu")
         self._step_state = (st, sc, sig)
         self._sampler = samplers.make_sampler(sc.scheduler, sig)
@@ -261,12 +264,24 @@ class Cosmos3OmniPipeline:
         torch.cuda.current_stream().synchronize() if self.device.type == "cuda" else None
         return out_host
 
+    def gather_tokens(self, tokens: torch.Tensor, st: GenState) -> torch.Tensor:
+        """All-gathers context-parallel token shards into the full sequence (no-op without cp)."""
+        ctx = self.engine.ctx
+        if getattr(ctx, "cp", 1) == 1 or not st.total_tokens or st.total_tokens == tokens.shape[1]:
+            return tokens
+        import torch.distributed as dist
+        parts = [torch.empty_like(tokens) for _ in range(ctx.cp)]
+        dist.all_gather(parts, tokens.contiguous(), group=ctx.group)
+        return torch.cat(parts, dim=1)
+
     # ------------------------------------------------------------------ decode
     @torch.no_grad()
     def decode(self, tokens: torch.Tensor, st: GenState, chunk_latents: Optional[int] = 4):
         cfg = self.cfg
         vdt = next(self.vae.parameters()).dtype
-        z = unpatchify(tokens[:, :st.n_video, :cfg.patch_dim], cfg, st.grid).to(vdt)
+        tokens = self.gather_tokens(tokens, st)
+        n_video = st.n_video if not st.total_tokens or st.total_tokens == st.pos.shape[1] else st.total_tokens
+        z = unpatchify(tokens[:, :n_video, :cfg.patch_dim], cfg, st.grid).to(vdt)
         video = self.vae.decode(z, chunk_latents=chunk_latents if st.grid[0] > (chunk_latents or 0) else None)
         frames = CausalVideoVAE.to_uint8(video)[0].cpu().numpy()
         sound = None

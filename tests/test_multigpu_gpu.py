@@ -1,0 +1,32 @@
+"""Multi-GPU tests of the fused compute+collective paths; need >= 2 GPUs (skipped otherwise)."""
+import json
+import os
+import subprocess
+import sys
+
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def _torchrun(nproc, script, *args, timeout=420):
+    env = dict(os.environ, NCCL_NVLS_ENABLE="0")
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={nproc}",
+           "--master-addr", "127.0.0.1", "--master-port", "29531", os.path.join(ROOT, "tests", script), *args]
+    return subprocess.run(cmd, capture_output=True, text=True, timeout=timeout, env=env, cwd=ROOT)
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs 2 GPUs")
+def test_fused_ulysses_and_cfgp_two_gpus():
+    r = _torchrun(2, "mp_fused_worker.py", json.dumps([{"cp": 2}, {"cfgp": 2}]))
+    assert r.returncode == 0, r.stdout[-3000:] + r.stderr[-3000:]
+    assert r.stdout.count("OK") == 2, r.stdout
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 4, reason="needs 4 GPUs")
+def test_fused_cfgp_x_ulysses_four_gpus():
+    r = _torchrun(4, "mp_fused_worker.py", json.dumps([{"cfgp": 2, "cp": 2}, {"cp": 4}]))
+    assert r.returncode == 0, r.stdout[-3000:] + r.stderr[-3000:]
+    assert r.stdout.count("OK") == 2, r.stdout
