@@ -199,3 +199,38 @@ def l2_flush(buf: torch.Tensor) -> None:
         _k().l2_flush_(buf)
     else:
         buf.zero_()
+
+
+# --------------------------------------------------------------------------- paged KV decode
+def paged_decode_ref(q, k_cache, v_cache, block_table, seq_lens, scale: Optional[float] = None):
+    """fp32 definition: gather each sequence's pages, then softmax(q k^T) v per head (GQA)."""
+    b, hq, d = q.shape
+    page, hkv = k_cache.shape[1], k_cache.shape[2]
+    scale = scale if scale is not None else 1.0 / math.sqrt(d)
+    out = torch.zeros(b, hq, d, dtype=torch.float32, device=q.device)
+    for i in range(b):
+        n = int(seq_lens[i])
+        if n == 0:
+            continue
+        pages = block_table[i, :(n + page - 1) // page].long()
+        k = k_cache[pages].reshape(-1, hkv, d)[:n].float()
+        v = v_cache[pages].reshape(-1, hkv, d)[:n].float()
+        k = k.repeat_interleave(hq // hkv, dim=1)
+        v = v.repeat_interleave(hq // hkv, dim=1)
+        s = torch.einsum("hd,nhd->hn", q[i].float(), k) * scale
+        out[i] = torch.einsum("hn,nhd->hd", torch.softmax(s, dim=-1), v)
+    return out.to(q.dtype)
+
+
+def paged_decode(q, k_cache, v_cache, block_table, seq_lens, scale: Optional[float] = None,
+                 n_splits: Optional[int] = None, scratch=None, max_len: Optional[int] = None):
+    """q [B, Hq, 128] against a paged cache [pages, page_size, Hkv, 128] -> [B, Hq, 128].
+    `max_len` (an upper bound of seq_lens known on the host) picks the kv split count without
+    a device synchronisation."""
+    scale = scale if scale is not None else 1.0 / math.sqrt(q.shape[-1])
+    if _use_cuda(q) and q.shape[-1] == 128:
+        if n_splits is None:
+            ml = max_len if max_len is not None else block_table.shape[1] * k_cache.shape[1]
+            n_splits = int(torch.ops.cosmos_b200.paged_decode_pick_splits(q.shape[0], k_cache.shape[2], ml))
+        return _k().paged_decode(q.contiguous(), k_cache, v_cache, block_table, seq_lens, scale, n_splits, scratch)
+    return paged_decode_ref(q, k_cache, v_cache, block_table, seq_lens, scale)

@@ -1,0 +1,451 @@
+"""OpenAI-compatible HTTP server with a resident model (FastAPI).
+
+Endpoints and fields follow the reference's serving surfaces (reference README.md:293-392,453-575;
+cookbooks/cosmos3/generator/audiovisual/run_with_vllm_omni.ipynb:408-449;
+action/run_fd_with_vllm.ipynb:361-440; action/README.md:100-104):
+
+  POST /v1/images/generations   JSON  {prompt,size,n,num_inference_steps,guidance_scale,flow_shift,seed,extra_args}
+                                 -> {"data":[{"b64_json": PNG}]}
+  POST /v1/videos/sync          multipart form -> MP4 bytes
+  POST /v1/videos               multipart form -> {"id"} (async job; actions via extra_params)
+  GET  /v1/videos/{id}          -> {"status","progress","action":{data,shape,dtype}}
+  GET  /v1/videos/{id}/content  -> MP4 bytes
+  POST /v1/chat/completions     OpenAI chat (image_url / video_url / text parts; top_k, repetition_penalty)
+  GET  /v1/models, /health, /v1/health/ready
+
+The model stays resident; autoregressive action chunks loop in-process instead of reloading the
+model per chunk. Generation jobs run on one worker thread (max_num_seqs 1 for the Generator, as in
+the reference's deploy config, README.md:405-417); serving metrics (TTFT, request latency, output
+tokens/s) are exported at /metrics.
+"""
+from __future__ import annotations
+
+import base64
+import io
+import json
+import tempfile
+import threading
+import time
+import uuid
+from concurrent.futures import ThreadPoolExecutor
+from dataclasses import dataclass, field
+from pathlib import Path
+from typing import Any, Dict, List, Optional
+
+import numpy as np
+import torch
+
+from ..config import DecodingConfig, SamplingConfig
+from ..io import media, mp4
+
+try:  # module-level so that FastAPI can resolve the (string) annotations of the route handlers
+    from fastapi import FastAPI, HTTPException, Request
+    from fastapi.responses import JSONResponse, Response
+except ImportError:  # the endpoint logic in Cosmos3Server stays usable without FastAPI
+    FastAPI = HTTPException = Request = JSONResponse = Response = None
+
+
+@dataclass
+class Job:
+    id: str
+    status: str = "queued"       # queued | in_progress | completed | failed | cancelled
+    progress: int = 0
+    error: Optional[str] = None
+    video_path: Optional[str] = None
+    action: Optional[np.ndarray] = None
+    created: float = field(default_factory=time.time)
+
+
+class Metrics:
+    def __init__(self):
+        self.lock = threading.Lock()
+        self.requests = 0
+        self.ttft_ms: List[float] = []
+        self.latency_ms: List[float] = []
+        self.output_tokens = 0
+        self.t_first = None
+
+    def record(self, ttft_ms: Optional[float], latency_ms: float, out_tokens: int = 0):
+        with self.lock:
+            self.requests += 1
+            self.t_first = self.t_first or time.time()
+            if ttft_ms is not None:
+                self.ttft_ms.append(ttft_ms)
+            self.latency_ms.append(latency_ms)
+            self.output_tokens += out_tokens
+
+    def snapshot(self) -> Dict[str, Any]:
+        with self.lock:
+            span = max(time.time() - (self.t_first or time.time()), 1e-9)
+            avg = lambda v: (sum(v) / len(v)) if v else None  # noqa: E731
+            return {"requests": self.requests, "avg_ttft_ms": avg(self.ttft_ms),
+                    "avg_request_latency_ms": avg(self.latency_ms),
+                    "output_token_throughput_per_s": self.output_tokens / span,
+                    "request_throughput_per_s": self.requests / span}
+
+
+def parse_size(size: str):
+    w, h = size.lower().split("x")
+    return int(w), int(h)
+
+
+class Cosmos3Server:
+    """Holds the pipeline/reasoner and implements the endpoint logic independent of FastAPI."""
+
+    def __init__(self, pipe, reasoner=None, vit=None, model_name: str = "nvidia/Cosmos3-Nano",
+                 guardrails_default: bool = True, allowed_local_media_path: str = "/"):
+        self.pipe, self.reasoner, self.vit = pipe, reasoner, vit
+        self.model_name = model_name
+        self.guardrails_default = guardrails_default
+        self.allowed_root = Path(allowed_local_media_path)
+        self.jobs: Dict[str, Job] = {}
+        self.pool = ThreadPoolExecutor(max_workers=1)
+        self.gen_lock = threading.Lock()
+        self.metrics = Metrics()
+        self.ready = True
+        self.tmp = Path(tempfile.mkdtemp(prefix="cosmos_b200_jobs_"))
+
+    # ------------------------------------------------------------------ generation
+    def _generate(self, prompt: str, negative_prompt: Optional[str], width: int, height: int, num_frames: int,
+                  fps: int, steps: int, guidance: float, flow_shift: float, seed: int, image=None, video=None,
+                  generate_sound: bool = False, extra: Optional[dict] = None, job: Optional[Job] = None):
+        extra = extra or {}
+        sc = SamplingConfig(num_steps=steps, guidance=guidance, shift=flow_shift, seed=seed,
+                            scheduler=extra.get("scheduler", "unipc"))
+        kw: Dict[str, Any] = {}
+        mode = extra.get("action_mode")
+        if mode:
+            from ..data.vfm.action.av_dataset import DOMAIN_ACTION_DIM
+            dom = extra.get("domain_name", "av")
+            kw["domain"] = list(self.pipe.cfg.action_domains).index(dom)
+            kw["action_dim"] = int(extra.get("raw_action_dim") or DOMAIN_ACTION_DIM.get(dom, 9))
+            chunk = int(extra.get("action_chunk_size", 16))
+            num_frames = chunk + 1
+            if mode == "forward_dynamics":
+                act = extra.get("action")
+                if act is None and extra.get("action_path"):
+                    act = json.loads(self._local(extra["action_path"]).read_text())
+                kw["action"] = np.asarray(act, dtype=np.float32)[:chunk]
+            else:  # inverse_dynamics / policy: actions are denoised
+                kw["n_action"], kw["denoise_action"] = chunk, True
+                if mode == "inverse_dynamics":
+                    kw["condition_frame_indexes"] = list(range((num_frames - 1) // 4 + 1))
+        if extra.get("condition_frame_indexes_vision"):
+            kw["condition_frame_indexes"] = list(extra["condition_frame_indexes_vision"])
+        checker = self.pipe.safety_checker
+        if not extra.get("guardrails", self.guardrails_default):
+            self.pipe.safety_checker = None
+
+        def cb(i, n):
+            if job is not None:
+                job.progress = int(100 * (i + 1) / n)
+
+        try:
+            with self.gen_lock:
+                return self.pipe(prompt=prompt, negative_prompt=negative_prompt, image=image, video=video,
+                                 num_frames=num_frames, height=height, width=width, fps=fps,
+                                 num_inference_steps=steps, guidance_scale=guidance, enable_sound=generate_sound,
+                                 add_resolution_template=bool(extra.get("use_resolution_template", True)),
+                                 sampling=sc, callback=cb, **kw)
+        finally:
+            self.pipe.safety_checker = checker
+
+    def _local(self, p: str) -> Path:
+        path = Path(p).resolve()
+        if self.allowed_root not in path.parents and path != self.allowed_root:
+            raise PermissionError(f"{p} is outside --allowed-local-media-path")
+        return path
+
+    def images_generations(self, body: dict) -> dict:
+        t0 = time.time()
+        w, h = parse_size(body.get("size", "1280x720"))
+        out_data = []
+        for k in range(int(body.get("n", 1))):
+            out = self._generate(body["prompt"], body.get("negative_prompt"), w, h, 1, 24,
+                                 int(body.get("num_inference_steps", 35)), float(body.get("guidance_scale", 6.0)),
+                                 float(body.get("flow_shift", 10.0)), int(body.get("seed", 0)) + k,
+                                 extra=body.get("extra_args"))
+            buf = io.BytesIO()
+            from PIL import Image
+            Image.fromarray(out.video[0]).save(buf, format="PNG")
+            out_data.append({"b64_json": base64.b64encode(buf.getvalue()).decode()})
+        self.metrics.record(None, (time.time() - t0) * 1e3)
+        return {"created": int(t0), "data": out_data}
+
+    def _video_request(self, form: dict, ref_bytes: Optional[bytes], ref_name: str, job: Optional[Job]) -> Job:
+        job = job or Job(id="sync")
+        job.status = "in_progress"
+        try:
+            w, h = parse_size(form.get("size", "1280x720"))
+            extra = form.get("extra_params") or {}
+            if isinstance(extra, str):
+                extra = json.loads(extra) if extra else {}
+            image = video = None
+            if ref_bytes:
+                p = self.tmp / f"{uuid.uuid4().hex}_{Path(ref_name or 'ref.bin').name}"
+                p.write_bytes(ref_bytes)
+                if p.suffix.lower() in (".png", ".jpg", ".jpeg", ".webp", ".bmp"):
+                    image = str(p)
+                else:
+                    video = str(p)
+            action_mode = bool(extra.get("action_mode"))
+            out = self._generate(form.get("prompt", ""), form.get("negative_prompt") or None, w, h,
+                                 int(form.get("num_frames", 189)), int(form.get("fps", 24)),
+                                 int(form.get("num_inference_steps", 30 if action_mode else 35)),
+                                 float(form.get("guidance_scale", 1.0 if action_mode else 6.0)),
+                                 float(form.get("flow_shift", 10.0)), int(form.get("seed", 0)), image, video,
+                                 str(form.get("generate_sound", "false")).lower() == "true", extra, job)
+            path = self.tmp / f"{job.id}_{uuid.uuid4().hex}.mp4"
+            frames = out.video if out.video.ndim == 4 else out.video[None]
+            media.write_video(path, frames, int(form.get("fps", 24)), 8, out.sound,
+                              self.pipe.sound_tokenizer.config.sampling_rate)
+            job.video_path, job.action = str(path), out.action
+            job.status, job.progress = "completed", 100
+        except Exception as e:  # noqa: BLE001 - reported through the job status
+            job.status, job.error = "failed", f"{type(e).__name__}: {e}"
+        return job
+
+    def videos_sync(self, form: dict, ref_bytes=None, ref_name="") -> bytes:
+        t0 = time.time()
+        job = self._video_request(form, ref_bytes, ref_name, None)
+        if job.status != "completed":
+            raise RuntimeError(job.error or "generation failed")
+        self.metrics.record(None, (time.time() - t0) * 1e3)
+        return Path(job.video_path).read_bytes()
+
+    def videos_submit(self, form: dict, ref_bytes=None, ref_name="") -> dict:
+        job = Job(id=f"video_{uuid.uuid4().hex[:16]}")
+        self.jobs[job.id] = job
+        self.pool.submit(self._video_request, form, ref_bytes, ref_name, job)
+        return {"id": job.id, "object": "video", "status": job.status}
+
+    def videos_status(self, job_id: str) -> dict:
+        job = self.jobs[job_id]
+        out = {"id": job.id, "object": "video", "status": job.status, "progress": job.progress}
+        if job.error:
+            out["error"] = {"message": job.error}
+        if job.action is not None:
+            a = np.asarray(job.action, dtype=np.float32)
+            out["action"] = {"data": a.tolist(), "shape": list(a.shape), "dtype": "float32"}
+        return out
+
+    def videos_cancel(self, job_id: str) -> dict:
+        job = self.jobs[job_id]
+        if job.status == "queued":
+            job.status = "cancelled"
+        return self.videos_status(job_id)
+
+    # ------------------------------------------------------------------ chat
+    def chat_completions(self, body: dict) -> dict:
+        if self.reasoner is None:
+            raise RuntimeError("this server was started without the Reasoner")
+        t0 = time.time()
+        tok = self.pipe.tokenizer
+        messages = body["messages"]
+        extra = body.get("extra_body") or {}
+        vision_embeds, grids, n_vis, norm_msgs = [], [], [], []
+        dev = self.pipe.device
+        for m in messages:
+            content = m["content"]
+            if isinstance(content, list):
+                parts = []
+                for part in content:
+                    kind = part.get("type")
+                    if kind in ("image_url", "video_url"):
+                        frames = self._load_media(part[kind]["url"], kind == "video_url", extra)
+                        emb, grid = self._encode_vision(frames, dev)
+                        vision_embeds.append(emb)
+                        grids.append(grid)
+                        n_vis.append(grid[0] * grid[1] * grid[2])
+                    parts.append(part)
+                norm_msgs.append({"role": m["role"], "content": parts})
+            else:
+                norm_msgs.append(m)
+        ids = tok.apply_chat_template(norm_msgs, True, n_vis)
+        dc = DecodingConfig(max_new_tokens=int(body.get("max_tokens", body.get("max_completion_tokens", 4096))),
+                            do_sample=float(body.get("temperature", 0.7)) > 0,
+                            temperature=float(body.get("temperature", 0.7)), top_p=float(body.get("top_p", 0.8)),
+                            top_k=int(body.get("top_k", extra.get("top_k", 20))),
+                            repetition_penalty=float(body.get("repetition_penalty", extra.get("repetition_penalty", 1.0))),
+                            presence_penalty=float(body.get("presence_penalty", 1.5)), seed=body.get("seed"))
+        first = {}
+
+        def on_token(_t):
+            first.setdefault("t", time.time())
+
+        ve = torch.cat(vision_embeds) if vision_embeds else None
+        # image and video pads share one mask here: every pad position takes the next vision row
+        pad_id = tok.video_pad_id if any(g[0] > 1 for g in grids) else tok.image_pad_id
+        if ve is not None and len({tok.image_pad_id, tok.video_pad_id}) == 2:
+            ids = [pad_id if t in (tok.image_pad_id, tok.video_pad_id) else t for t in ids]
+        with self.gen_lock:
+            out_ids, usage = self.reasoner.generate(ids, dc, (tok.eos_id, tok.eot_id), ve, pad_id if ve is not None else None,
+                                                    grids, on_token)
+        text = tok.decode(out_ids)
+        t1 = time.time()
+        self.metrics.record((first.get("t", t1) - t0) * 1e3, (t1 - t0) * 1e3, usage["completion_tokens"])
+        return {"id": f"chatcmpl-{uuid.uuid4().hex[:24]}", "object": "chat.completion", "created": int(t0),
+                "model": body.get("model", self.model_name),
+                "choices": [{"index": 0, "message": {"role": "assistant", "content": text},
+                             "finish_reason": "stop" if out_ids and out_ids[-1] in (tok.eos_id, tok.eot_id) else "length"}],
+                "usage": {**usage, "total_tokens": usage["prompt_tokens"] + usage["completion_tokens"]}}
+
+    def _load_media(self, url: str, is_video: bool, extra: dict) -> np.ndarray:
+        if url.startswith("data:"):
+            raw = base64.b64decode(url.split(",", 1)[1])
+            suffix = ".mp4" if is_video else ".png"
+            p = self.tmp / f"{uuid.uuid4().hex}{suffix}"
+            p.write_bytes(raw)
+        elif url.startswith("file://"):
+            p = self._local(url[7:])
+        else:
+            p = self._local(url)
+        frames, src_fps = media.read_video(p)
+        if is_video:
+            vk = (extra.get("media_io_kwargs") or {}).get("video", {})
+            mk = extra.get("mm_processor_kwargs") or {}
+            if "num_frames" in vk:
+                idx = np.linspace(0, len(frames) - 1, int(vk["num_frames"])).round().astype(int)
+                frames = frames[idx]
+            else:
+                fps = float(vk.get("fps", mk.get("fps", 2)))
+                step = max(1, int(round(src_fps / max(fps, 1e-6))))
+                frames = frames[::step]
+        return frames[:32]
+
+    def _encode_vision(self, frames: np.ndarray, dev):
+        from PIL import Image
+        from ..models.vae import CausalVideoVAE
+        unit = self.pipe.cfg.vit_patch * self.pipe.cfg.vit_spatial_merge
+        h = min(max(unit, frames.shape[1] // unit * unit), 14 * unit)
+        w = min(max(unit, frames.shape[2] // unit * unit), 14 * unit)
+        fr = np.stack([np.asarray(Image.fromarray(f).resize((w, h))) for f in frames])
+        vid = CausalVideoVAE.from_uint8(torch.from_numpy(fr)[None])[0].permute(1, 0, 2, 3).to(dev)
+        with torch.no_grad():
+            return self.vit(vid)
+
+    def models(self) -> dict:
+        return {"object": "list", "data": [{"id": self.model_name, "object": "model", "owned_by": "cosmos_b200"}]}
+
+
+def create_app(server: Cosmos3Server):
+    if FastAPI is None:
+        raise RuntimeError("fastapi is not installed")
+    app = FastAPI(title="cosmos_b200")
+
+    async def _form(request: Request):
+        ctype = request.headers.get("content-type", "")
+        if ctype.startswith("application/json"):
+            return await request.json(), None, ""
+        form = await request.form()
+        fields, ref, name = {}, None, ""
+        for k, v in form.multi_items():
+            if hasattr(v, "read"):
+                ref, name = await v.read(), getattr(v, "filename", "") or ""
+            else:
+                fields[k] = v
+        return fields, ref, name
+
+    @app.get("/health")
+    @app.get("/v1/health/ready")
+    def health():
+        if not server.ready:
+            raise HTTPException(503, "loading")
+        return {"status": "ok"}
+
+    @app.get("/v1/models")
+    def models():
+        return server.models()
+
+    @app.get("/metrics")
+    def metrics():
+        return server.metrics.snapshot()
+
+    @app.post("/v1/images/generations")
+    async def images(request: Request):
+        try:
+            return server.images_generations(await request.json())
+        except Exception as e:  # noqa: BLE001
+            raise HTTPException(400, f"{type(e).__name__}: {e}")
+
+    @app.post("/v1/videos/sync")
+    async def videos_sync(request: Request):
+        fields, ref, name = await _form(request)
+        try:
+            return Response(server.videos_sync(fields, ref, name), media_type="video/mp4")
+        except Exception as e:  # noqa: BLE001
+            raise HTTPException(400, f"{type(e).__name__}: {e}")
+
+    @app.post("/v1/videos")
+    async def videos(request: Request):
+        fields, ref, name = await _form(request)
+        return server.videos_submit(fields, ref, name)
+
+    @app.get("/v1/videos/{job_id}")
+    def video_status(job_id: str):
+        if job_id not in server.jobs:
+            raise HTTPException(404, "no such job")
+        return server.videos_status(job_id)
+
+    @app.delete("/v1/videos/{job_id}")
+    def video_cancel(job_id: str):
+        if job_id not in server.jobs:
+            raise HTTPException(404, "no such job")
+        return server.videos_cancel(job_id)
+
+    @app.get("/v1/videos/{job_id}/content")
+    def video_content(job_id: str):
+        job = server.jobs.get(job_id)
+        if job is None:
+            raise HTTPException(404, "no such job")
+        if job.status != "completed":
+            raise HTTPException(409, f"job is {job.status}")
+        return Response(Path(job.video_path).read_bytes(), media_type="video/mp4")
+
+    @app.post("/v1/chat/completions")
+    async def chat(request: Request):
+        try:
+            return server.chat_completions(await request.json())
+        except Exception as e:  # noqa: BLE001
+            raise HTTPException(400, f"{type(e).__name__}: {e}")
+
+    return app
+
+
+def main(argv=None) -> int:
+    import argparse
+
+    ap = argparse.ArgumentParser(description="cosmos_b200 serve (Generator + Reasoner)")
+    ap.add_argument("model", nargs="?", default="nvidia/Cosmos3-Nano")
+    ap.add_argument("--port", type=int, default=8000)
+    ap.add_argument("--host", default="127.0.0.1")
+    ap.add_argument("--omni", action="store_true", help="accepted for CLI compatibility")
+    ap.add_argument("--model-class-name", default="Cosmos3OmniDiffusersPipeline")
+    ap.add_argument("--allowed-local-media-path", default="/")
+    ap.add_argument("--init-timeout", type=int, default=1800)
+    ap.add_argument("--tensor-parallel-size", type=int, default=1)
+    ap.add_argument("--cfg-parallel-size", type=int, default=1)
+    ap.add_argument("--ulysses-degree", type=int, default=1)
+    ap.add_argument("--enable-layerwise-offload", action="store_true")
+    ap.add_argument("--no-guardrails", action="store_true")
+    ap.add_argument("--dtype", default="bf16")
+    args = ap.parse_args(argv)
+    import uvicorn
+
+    from ..models.reasoner import ReasonerEngine
+    from ..models.vit import VisionEncoder
+    from ..pipeline import Cosmos3OmniPipeline
+
+    dev = "cuda" if torch.cuda.is_available() else None
+    dtype = torch.bfloat16 if (dev and args.dtype == "bf16") else torch.float32
+    pipe = Cosmos3OmniPipeline.from_pretrained(args.model, torch_dtype=dtype, device_map=dev,
+                                               enable_safety_checker=not args.no_guardrails)
+    vit = VisionEncoder(pipe.cfg).to(device=pipe.device, dtype=dtype).eval()
+    server = Cosmos3Server(pipe, ReasonerEngine(pipe.transformer, vit), vit, args.model, not args.no_guardrails,
+                           args.allowed_local_media_path)
+    uvicorn.run(create_app(server), host=args.host, port=args.port, log_level="info")
+    return 0
+
+
+if __name__ == "__main__":
+    raise SystemExit(main())

@@ -323,6 +323,45 @@ void l2_flush_(Tensor buf) {
   cosmos::l2_flush(buf.data_ptr(), buf.nbytes(), cur_stream());
 }
 
+// Decode attention over a paged KV cache; `scratch` (fp32) holds the split-KV partials.
+Tensor paged_decode(const Tensor& q, const Tensor& k_cache, const Tensor& v_cache, const Tensor& block_table,
+                    const Tensor& seq_lens, double scale, int64_t n_splits, const OptT& scratch) {
+  check_bf16_cuda(q, "q"); check_bf16_cuda(k_cache, "k_cache"); check_bf16_cuda(v_cache, "v_cache");
+  c10::cuda::CUDAGuard guard(q.device());
+  TORCH_CHECK(q.dim() == 3 && q.size(2) == 128 && q.is_contiguous(), "q must be contiguous [B, Hq, 128]");
+  TORCH_CHECK(k_cache.dim() == 4 && k_cache.size(3) == 128 && k_cache.is_contiguous() &&
+                  v_cache.is_contiguous() && v_cache.sizes() == k_cache.sizes(),
+              "caches must be contiguous [pages, page_size, Hkv, 128]");
+  TORCH_CHECK(block_table.scalar_type() == at::kInt && block_table.is_cuda() && block_table.is_contiguous() &&
+                  block_table.dim() == 2 && block_table.size(0) == q.size(0), "block_table must be int32 [B, max_pages]");
+  TORCH_CHECK(seq_lens.scalar_type() == at::kInt && seq_lens.is_cuda() && seq_lens.numel() == q.size(0));
+  cosmos::PagedDecodeArgs a;
+  a.q = q.data_ptr(); a.k_cache = k_cache.data_ptr(); a.v_cache = v_cache.data_ptr();
+  a.block_table = block_table.data_ptr<int>(); a.seq_lens = seq_lens.data_ptr<int>();
+  a.B = (int)q.size(0); a.Hq = (int)q.size(1); a.Hkv = (int)k_cache.size(2);
+  a.page_size = (int)k_cache.size(1); a.max_pages = (int)block_table.size(1);
+  a.scale = (float)scale; a.n_splits = (int)n_splits;
+  Tensor out = at::empty_like(q);
+  a.out = out.data_ptr();
+  Tensor ws;
+  if (n_splits > 1) {
+    const size_t need = cosmos::paged_decode_scratch_bytes(a.B, a.Hq, a.n_splits);
+    if (scratch.has_value() && scratch->defined()) {
+      TORCH_CHECK(scratch->is_cuda() && scratch->is_contiguous() && scratch->nbytes() >= need, "scratch too small");
+      ws = *scratch;
+    } else {
+      ws = at::empty({(int64_t)(need / 4)}, q.options().dtype(at::kFloat));
+    }
+    a.scratch = ws.data_ptr(); a.scratch_bytes = ws.nbytes();
+  }
+  cosmos::paged_decode(a, cur_stream());
+  return out;
+}
+
+int64_t paged_decode_pick_splits(int64_t B, int64_t Hkv, int64_t max_len) {
+  return cosmos::paged_decode_pick_splits((int)B, (int)Hkv, (int)max_len);
+}
+
 const long long* ptr_table(const Tensor& t, const char* name) {
   TORCH_CHECK(t.is_cuda() && t.scalar_type() == at::kLong && t.is_contiguous(), name,
               " must be a contiguous int64 CUDA tensor of addresses");
@@ -390,6 +429,8 @@ TORCH_LIBRARY(cosmos_b200, m) {
   m.def("swiglu", &swiglu);
   m.def("cfg_euler_step_", &cfg_euler_step_);
   m.def("l2_flush_", &l2_flush_);
+  m.def("paged_decode", &paged_decode);
+  m.def("paged_decode_pick_splits", &paged_decode_pick_splits);
   m.def("comm_barrier", &comm_barrier);
   m.def("allreduce_oneshot", &allreduce_oneshot);
   m.def("rs_adamw", &rs_adamw);

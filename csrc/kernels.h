@@ -90,6 +90,24 @@ void cfg_euler_step(float* x, const void* vc, const void* vu, float guidance, fl
                     int normalize, long long rows, int d, cudaStream_t s);
 void l2_flush(void* buf, size_t bytes, cudaStream_t s);
 
+// ---- paged-KV decode attention (paged_decode.cu) ----
+struct PagedDecodeArgs {
+  const void* q = nullptr;        // [B, Hq, 128] bf16
+  const void* k_cache = nullptr;  // [num_pages, page_size, Hkv, 128] bf16
+  const void* v_cache = nullptr;
+  const int* block_table = nullptr;  // [B, max_pages]
+  const int* seq_lens = nullptr;     // [B]
+  void* out = nullptr;               // [B, Hq, 128] bf16
+  int B = 0, Hq = 0, Hkv = 0, page_size = 0, max_pages = 0;
+  float scale = 0.f;
+  int n_splits = 1;
+  void* scratch = nullptr;  // >= paged_decode_scratch_bytes(B, Hq, n_splits) when n_splits > 1
+  size_t scratch_bytes = 0;
+};
+int paged_decode_pick_splits(int B, int Hkv, int max_len);
+size_t paged_decode_scratch_bytes(int B, int Hq, int n_splits);
+void paged_decode(const PagedDecodeArgs& a, cudaStream_t s);
+
 // ---- communication kernels over peer mappings (comm.cu) ----
 // pads_dev / bufs_dev / grads_dev / srcs_dev: device arrays with one address per rank of the group.
 // Signal pads are int32 arrays laid out as [slot][64]; epochs must grow monotonically per slot.

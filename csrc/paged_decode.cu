@@ -1,0 +1,243 @@
+// K14: decode-time attention over a paged KV cache (one new query token per sequence).
+//
+//   q        [B, Hq, 128] bf16
+//   k_cache  [num_pages, page_size, Hkv, 128] bf16   (v_cache alike)
+//   table    [B, max_pages] int32 page ids, seq_lens [B] int32
+//   out      [B, Hq, 128] bf16
+//
+// Decode attention is bandwidth bound (every cached K/V byte is read once per step), so the
+// kernel is organised around loads: a CTA owns one (sequence, kv head, kv split) and all
+// Hq/Hkv query heads that share the kv head, so K/V are read once for the whole GQA group.
+// Phase 1 (thread = token): 128-dim dot products against the group's queries (held in shared
+// memory, broadcast reads). Phase 2 (thread = pair of output dims): P.V with coalesced V loads.
+// Long sequences are split along kv across CTAs; each split writes an unnormalised partial
+// (acc, running max, running sum) to a scratch buffer and a second kernel merges the splits.
+#include "common.cuh"
+#include "kernels.h"
+
+namespace cb {
+
+constexpr int PD_THREADS = 128;
+constexpr int PD_TILE = 128;   // tokens per tile
+constexpr int PD_MAX_GROUP = 8;
+
+template <int GROUP>
+__global__ void __launch_bounds__(PD_THREADS)
+paged_decode_kernel(const bf16* __restrict__ q, const bf16* __restrict__ kc, const bf16* __restrict__ vc,
+                    const int* __restrict__ table, const int* __restrict__ seq_lens, int max_pages,
+                    int page_size, int Hq, int Hkv, int n_splits, float scale_log2,
+                    float* __restrict__ part_acc,   // [B, Hq, n_splits, 128]
+                    float* __restrict__ part_ml,    // [B, Hq, n_splits, 2]
+                    bf16* __restrict__ out) {       // used directly when n_splits == 1
+  const int split = blockIdx.x, kvh = blockIdx.y, b = blockIdx.z;
+  const int tid = threadIdx.x;
+  const int len = seq_lens[b];
+  const int chunk = ((len + n_splits - 1) / n_splits + PD_TILE - 1) / PD_TILE * PD_TILE;
+  const int kv_begin = split * chunk;
+  const int kv_end = min(len, kv_begin + chunk);
+
+  __shared__ float q_s[GROUP][128];
+  __shared__ float p_s[GROUP][PD_TILE];
+  __shared__ long long row_s[PD_TILE];
+  __shared__ float red_s[GROUP][4];
+  __shared__ float acc_s[GROUP][128];
+
+  for (int i = tid; i < GROUP * 128; i += PD_THREADS) {
+    const int g = i >> 7, d = i & 127;
+    q_s[g][d] = __bfloat162float(q[((long long)b * Hq + kvh * GROUP + g) * 128 + d]) * scale_log2;
+  }
+  __syncthreads();
+
+  float m_run[GROUP], l_run[GROUP];
+  float acc[GROUP][2];
+#pragma unroll
+  for (int g = 0; g < GROUP; ++g) {
+    m_run[g] = -1e30f; l_run[g] = 0.f; acc[g][0] = 0.f; acc[g][1] = 0.f;
+  }
+  const int d2 = tid & 63, half = tid >> 6;
+  const long long row_stride = (long long)Hkv * 128;
+
+  for (int t0 = kv_begin; t0 < kv_end; t0 += PD_TILE) {
+    // ---- phase 1: scores of this thread's token against the GROUP queries
+    const int pos = t0 + tid;
+    const bool valid = pos < kv_end;
+    float s[GROUP];
+#pragma unroll
+    for (int g = 0; g < GROUP; ++g) s[g] = 0.f;
+    long long row = 0;
+    if (valid) {
+      const int page = table[(long long)b * max_pages + pos / page_size];
+      row = ((long long)page * page_size + pos % page_size) * row_stride + (long long)kvh * 128;
+      const uint4* kp = reinterpret_cast<const uint4*>(kc + row);
+#pragma unroll 4
+      for (int c = 0; c < 16; ++c) {
+        const uint4 kk = kp[c];
+        const float f[8] = {bf16lo(kk.x), bf16hi(kk.x), bf16lo(kk.y), bf16hi(kk.y),
+                            bf16lo(kk.z), bf16hi(kk.z), bf16lo(kk.w), bf16hi(kk.w)};
+#pragma unroll
+        for (int g = 0; g < GROUP; ++g) {
+          const float* qq = &q_s[g][c * 8];
+#pragma unroll
+          for (int e = 0; e < 8; ++e) s[g] = fmaf(f[e], qq[e], s[g]);
+        }
+      }
+    }
+    row_s[tid] = row;
+    // tile max per head
+    float mx[GROUP];
+#pragma unroll
+    for (int g = 0; g < GROUP; ++g) {
+      float v = valid ? s[g] : -1e30f;
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+      mx[g] = v;
+    }
+    if ((tid & 31) == 0) {
+#pragma unroll
+      for (int g = 0; g < GROUP; ++g) red_s[g][tid >> 5] = mx[g];
+    }
+    __syncthreads();
+    float corr[GROUP];
+#pragma unroll
+    for (int g = 0; g < GROUP; ++g) {
+      const float tm = fmaxf(fmaxf(red_s[g][0], red_s[g][1]), fmaxf(red_s[g][2], red_s[g][3]));
+      const float m_new = fmaxf(m_run[g], tm);
+      corr[g] = exp2f(m_run[g] - m_new);
+      m_run[g] = m_new;
+      const float p = valid ? exp2f(s[g] - m_new) : 0.f;
+      p_s[g][tid] = p;
+      float ps = p;
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1) ps += __shfl_xor_sync(0xffffffffu, ps, o);
+      mx[g] = ps;  // reuse as the warp's partial sum
+    }
+    __syncthreads();  // p_s, row_s visible; red_s reads done
+    if ((tid & 31) == 0) {
+#pragma unroll
+      for (int g = 0; g < GROUP; ++g) red_s[g][tid >> 5] = mx[g];
+    }
+    __syncthreads();
+#pragma unroll
+    for (int g = 0; g < GROUP; ++g) {
+      l_run[g] = l_run[g] * corr[g] + (red_s[g][0] + red_s[g][1] + red_s[g][2] + red_s[g][3]);
+      acc[g][0] *= corr[g];
+      acc[g][1] *= corr[g];
+    }
+    // ---- phase 2: acc[g][dims 2*d2, 2*d2+1] += sum_t p[g][t] * V[t][dims]; this thread takes
+    // the tokens of its half of the tile
+    const int n_tok = min(PD_TILE, kv_end - t0);
+    const int tb = half * 64, te = min(n_tok, tb + 64);
+#pragma unroll 4
+    for (int t = tb; t < te; ++t) {
+      const uint32_t vv = *reinterpret_cast<const uint32_t*>(vc + row_s[t] + 2 * d2);
+      const float v0 = bf16lo(vv), v1 = bf16hi(vv);
+#pragma unroll
+      for (int g = 0; g < GROUP; ++g) {
+        const float p = p_s[g][t];
+        acc[g][0] = fmaf(p, v0, acc[g][0]);
+        acc[g][1] = fmaf(p, v1, acc[g][1]);
+      }
+    }
+    __syncthreads();  // before p_s / row_s / red_s are overwritten
+  }
+
+  // combine the two halves
+  if (half == 1) {
+#pragma unroll
+    for (int g = 0; g < GROUP; ++g) {
+      acc_s[g][2 * d2] = acc[g][0];
+      acc_s[g][2 * d2 + 1] = acc[g][1];
+    }
+  }
+  __syncthreads();
+  if (half == 0) {
+#pragma unroll
+    for (int g = 0; g < GROUP; ++g) {
+      const float a0 = acc[g][0] + acc_s[g][2 * d2], a1 = acc[g][1] + acc_s[g][2 * d2 + 1];
+      const int h = kvh * GROUP + g;
+      if (n_splits == 1) {
+        const float inv = l_run[g] > 0.f ? 1.f / l_run[g] : 0.f;
+        *reinterpret_cast<uint32_t*>(out + ((long long)b * Hq + h) * 128 + 2 * d2) =
+            pack_bf16(a0 * inv, a1 * inv);
+      } else {
+        const long long base = ((long long)b * Hq + h) * n_splits + split;
+        float2* dst = reinterpret_cast<float2*>(part_acc + base * 128 + 2 * d2);
+        *dst = make_float2(a0, a1);
+        if (d2 == 0) {
+          part_ml[base * 2] = m_run[g];
+          part_ml[base * 2 + 1] = l_run[g];
+        }
+      }
+    }
+  }
+}
+
+// out[b, h, :] = sum_s w_s acc_s / sum_s w_s l_s,  w_s = 2^(m_s - max m)
+__global__ void __launch_bounds__(128)
+paged_decode_merge_kernel(const float* __restrict__ part_acc, const float* __restrict__ part_ml,
+                          int n_splits, bf16* __restrict__ out) {
+  const long long bh = blockIdx.x;
+  const int d = threadIdx.x;
+  float m = -1e30f;
+  for (int s = 0; s < n_splits; ++s) m = fmaxf(m, part_ml[(bh * n_splits + s) * 2]);
+  float num = 0.f, den = 0.f;
+  for (int s = 0; s < n_splits; ++s) {
+    const float w = exp2f(part_ml[(bh * n_splits + s) * 2] - m);
+    num += w * part_acc[(bh * n_splits + s) * 128 + d];
+    den += w * part_ml[(bh * n_splits + s) * 2 + 1];
+  }
+  out[bh * 128 + d] = __float2bfloat16(den > 0.f ? num / den : 0.f);
+}
+
+}  // namespace cb
+
+namespace cosmos {
+
+int paged_decode_pick_splits(int B, int Hkv, int max_len) {
+  // enough CTAs to fill the machine about 4x over, but no split shorter than 256 tokens
+  const int want = (148 * 4 + B * Hkv - 1) / (B * Hkv);
+  const int cap = (max_len + 255) / 256;
+  int s = want < cap ? want : cap;
+  if (s < 1) s = 1;
+  if (s > 64) s = 64;
+  return s;
+}
+
+size_t paged_decode_scratch_bytes(int B, int Hq, int n_splits) {
+  return n_splits <= 1 ? 0 : (size_t)B * Hq * n_splits * (128 + 2) * sizeof(float);
+}
+
+template <int GROUP>
+static void launch_pd(const PagedDecodeArgs& a, float* pa, float* pm, cudaStream_t s) {
+  dim3 grid(a.n_splits, a.Hkv, a.B);
+  cb::paged_decode_kernel<GROUP><<<grid, cb::PD_THREADS, 0, s>>>(
+      (const bf16*)a.q, (const bf16*)a.k_cache, (const bf16*)a.v_cache, a.block_table, a.seq_lens,
+      a.max_pages, a.page_size, a.Hq, a.Hkv, a.n_splits, a.scale * 1.4426950408889634f, pa, pm,
+      (bf16*)a.out);
+}
+
+void paged_decode(const PagedDecodeArgs& a, cudaStream_t s) {
+  if (a.B <= 0) return;
+  if (a.Hkv <= 0 || a.Hq % a.Hkv != 0) throw std::runtime_error("paged_decode: Hq % Hkv != 0");
+  const int group = a.Hq / a.Hkv;
+  if (a.n_splits < 1 || a.n_splits > 64) throw std::runtime_error("paged_decode: n_splits must be in [1, 64]");
+  float* pa = nullptr;
+  float* pm = nullptr;
+  if (a.n_splits > 1) {
+    if (!a.scratch || a.scratch_bytes < paged_decode_scratch_bytes(a.B, a.Hq, a.n_splits))
+      throw std::runtime_error("paged_decode: scratch buffer missing or too small");
+    pa = reinterpret_cast<float*>(a.scratch);
+    pm = pa + (size_t)a.B * a.Hq * a.n_splits * 128;
+  }
+  switch (group) {
+    case 1: launch_pd<1>(a, pa, pm, s); break;
+    case 2: launch_pd<2>(a, pa, pm, s); break;
+    case 4: launch_pd<4>(a, pa, pm, s); break;
+    case 8: launch_pd<8>(a, pa, pm, s); break;
+    default: throw std::runtime_error("paged_decode: GQA group size must be 1, 2, 4 or 8");
+  }
+  if (a.n_splits > 1)
+    cb::paged_decode_merge_kernel<<<a.B * a.Hq, 128, 0, s>>>(pa, pm, a.n_splits, (bf16*)a.out);
+}
+
+}  // namespace cosmos

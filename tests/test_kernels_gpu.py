@@ -245,3 +245,23 @@ def test_cfg_euler_step(normalize):
     want = ref.cfg_euler_step(x.clone(), vc, vu, 7.0, -0.03, normalize)
     got = ops.cfg_euler_step(x.clone(), vc, vu, 7.0, -0.03, normalize)
     _close(got, want, 1e-5, 1e-5, "cfg euler step")
+
+
+@pytest.mark.parametrize("b,hq,hkv,page,lens,splits", [
+    (2, 4, 1, 16, [100, 37], 1),
+    (3, 8, 2, 32, [700, 1, 333], 4),
+    (4, 4, 4, 16, [513, 512, 511, 64], 3),
+    (2, 8, 1, 16, [2000, 1500], None),
+])
+def test_paged_decode(b, hq, hkv, page, lens, splits):
+    torch.manual_seed(16)
+    max_pages = (max(lens) + page - 1) // page + 1
+    n_pages = b * max_pages + 3
+    kc = _rand(n_pages, page, hkv, 128)
+    vc = _rand(n_pages, page, hkv, 128)
+    perm = torch.randperm(n_pages, device=DEV)[:b * max_pages].view(b, max_pages).int()
+    sl = torch.tensor(lens, device=DEV, dtype=torch.int32)
+    q = _rand(b, hq, 128)
+    got = ops.paged_decode(q, kc, vc, perm, sl, n_splits=splits, max_len=max(lens))
+    want = ops.paged_decode_ref(q.float(), kc.float(), vc.float(), perm, sl)
+    _close(got, want, 2e-2, 2e-2, "paged decode")

@@ -1,0 +1,106 @@
+"""HTTP surface on CPU with the tiny model: every endpoint of the serving table once."""
+import base64
+import io
+import json
+import time
+
+import numpy as np
+import pytest
+import torch
+
+fastapi = pytest.importorskip("fastapi")
+pytest.importorskip("httpx")
+from fastapi.testclient import TestClient  # noqa: E402
+
+from cosmos_b200.io import mp4  # noqa: E402
+from cosmos_b200.models.reasoner import ReasonerEngine  # noqa: E402
+from cosmos_b200.models.vit import VisionEncoder  # noqa: E402
+from cosmos_b200.pipeline import Cosmos3OmniPipeline  # noqa: E402
+from cosmos_b200.serve.server import Cosmos3Server, create_app  # noqa: E402
+
+
+@pytest.fixture(scope="module")
+def client():
+    torch.manual_seed(0)
+    pipe = Cosmos3OmniPipeline.from_pretrained("tiny", torch_dtype=torch.float32, vae_widths=(8, 16, 16, 16),
+                                               config_overrides=dict(max_text_len=32, n_layers=2))
+    vit = VisionEncoder(pipe.cfg).eval()
+    srv = Cosmos3Server(pipe, ReasonerEngine(pipe.transformer, vit), vit, "nvidia/Cosmos3-Nano")
+    return TestClient(create_app(srv))
+
+
+def test_health_and_models(client):
+    assert client.get("/health").status_code == 200
+    assert client.get("/v1/health/ready").json()["status"] == "ok"
+    assert client.get("/v1/models").json()["data"][0]["id"] == "nvidia/Cosmos3-Nano"
+
+
+def test_images_generations(client):
+    r = client.post("/v1/images/generations", json={"prompt": "a cat", "size": "64x64", "n": 1,
+                                                    "num_inference_steps": 2, "guidance_scale": 4.0, "flow_shift": 3.0,
+                                                    "seed": 1, "extra_args": {"use_resolution_template": False}})
+    assert r.status_code == 200, r.text
+    png = base64.b64decode(r.json()["data"][0]["b64_json"])
+    assert png[:8] == b"\x89PNG\r\n\x1a\n"
+
+
+def test_videos_sync_returns_mp4(client):
+    r = client.post("/v1/videos/sync", data={"prompt": "a robot", "negative_prompt": "blurry", "size": "64x64",
+                                             "num_frames": "5", "fps": "24", "num_inference_steps": "2",
+                                             "guidance_scale": "3.0", "flow_shift": "3.0", "seed": "0"})
+    assert r.status_code == 200, r.text
+    assert r.content[4:8] == b"ftyp"
+
+
+def test_async_action_job_forward_and_inverse(client, tmp_path):
+    img = io.BytesIO()
+    from PIL import Image
+    Image.fromarray((np.random.rand(64, 64, 3) * 255).astype(np.uint8)).save(img, format="PNG")
+    extra = {"action_mode": "forward_dynamics", "domain_name": "av", "raw_action_dim": 9, "action_chunk_size": 4,
+             "action": np.zeros((4, 9)).tolist(), "guardrails": False}
+    r = client.post("/v1/videos", data={"prompt": "drive", "size": "64x64", "num_inference_steps": "2",
+                                        "extra_params": json.dumps(extra)},
+                    files={"input_reference": ("frame.png", img.getvalue(), "image/png")})
+    jid = r.json()["id"]
+    for _ in range(200):
+        st = client.get(f"/v1/videos/{jid}").json()
+        if st["status"] in ("completed", "failed"):
+            break
+        time.sleep(0.1)
+    assert st["status"] == "completed", st
+    content = client.get(f"/v1/videos/{jid}/content")
+    assert content.status_code == 200 and content.content[4:8] == b"ftyp"
+    clip = tmp_path / "clip.mp4"
+    clip.write_bytes(content.content)
+    frames, _ = mp4.read_mp4_mjpeg(clip)
+    assert frames.shape[0] == 5
+    extra = {"action_mode": "inverse_dynamics", "domain_name": "av", "raw_action_dim": 9, "action_chunk_size": 4}
+    r = client.post("/v1/videos", data={"prompt": "drive", "size": "64x64", "num_inference_steps": "2",
+                                        "extra_params": json.dumps(extra)},
+                    files={"input_reference": ("clip.mp4", content.content, "video/mp4")})
+    jid = r.json()["id"]
+    for _ in range(200):
+        st = client.get(f"/v1/videos/{jid}").json()
+        if st["status"] in ("completed", "failed"):
+            break
+        time.sleep(0.1)
+    assert st["status"] == "completed", st
+    assert st["action"]["shape"] == [4, 9] and st["action"]["dtype"] == "float32"
+    assert client.get("/v1/videos/nope").status_code == 404
+
+
+def test_chat_completions_text_and_image(client):
+    img = io.BytesIO()
+    from PIL import Image
+    Image.fromarray((np.random.rand(64, 64, 3) * 255).astype(np.uint8)).save(img, format="PNG")
+    url = "data:image/png;base64," + base64.b64encode(img.getvalue()).decode()
+    body = {"model": "nvidia/Cosmos3-Nano", "max_tokens": 5, "temperature": 0.0, "top_k": 20,
+            "messages": [{"role": "user", "content": [{"type": "image_url", "image_url": {"url": url}},
+                                                       {"type": "text", "text": "What is in the image?"}]}]}
+    r = client.post("/v1/chat/completions", json=body)
+    assert r.status_code == 200, r.text
+    out = r.json()
+    assert out["choices"][0]["message"]["role"] == "assistant"
+    assert out["usage"]["completion_tokens"] <= 5 and out["usage"]["prompt_tokens"] > 4
+    m = client.get("/metrics").json()
+    assert m["requests"] >= 1 and m["avg_request_latency_ms"] > 0
