@@ -1,4 +1,5 @@
 """Spawns `world` CPU ranks over gloo on 127.0.0.1 and runs `fn(rank, world, *args)` in each."""
+import io
 import os
 import socket
 import traceback
@@ -21,7 +22,9 @@ def _worker(rank, world, port, fn, args, q):
     try:
         dist.init_process_group("gloo", rank=rank, world_size=world)
         out = fn(rank, world, *args)
-        q.put((rank, "ok", out))
+        buf = io.BytesIO()
+        torch.save(out, buf)  # bytes, so that no shared-memory handle outlives this process
+        q.put((rank, "ok", buf.getvalue()))
     except Exception:  # noqa: BLE001 - reported to the parent
         q.put((rank, "err", traceback.format_exc()))
     finally:
@@ -42,7 +45,7 @@ def run_ranks(fn, world: int, *args, timeout: float = 180.0):
             rank, status, out = q.get(timeout=timeout)
             if status != "ok":
                 raise RuntimeError(f"rank {rank} failed:\n{out}")
-            results[rank] = out
+            results[rank] = torch.load(io.BytesIO(out), weights_only=False)
     finally:
         for p in procs:
             p.join(timeout=10)
