@@ -166,11 +166,13 @@ def main():
         sampler.start()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     sync()
+    torch.cuda.cudart().cudaProfilerStart()  # lets a profiler started with --profile-from-start off see only the timed steps
     e0.record()
     for _ in range(args.steps):
         x = pipe.step(x, step_i); step_i += 1
     e1.record()
     sync()
+    torch.cuda.cudart().cudaProfilerStop()
     clocks = sampler.stop() if sampler else None
     launches = ops.launch_count() - launches0
     ms = e0.elapsed_time(e1) / args.steps

@@ -213,7 +213,7 @@ def dm_block(cfg: MoTConfig, p: Dict[str, torch.Tensor], x, t_mod, cos, sin, ar_
     h = ops.adaln_rmsnorm(x, p["norm1"], sh1, sc1, s, cfg.rms_eps)
     q, k, v = ctx.qkv_project(h, p["wqkv"], cos, sin, p["q_norm"], p["k_norm"], cfg, prefix=ar_kv)
     o = ctx.attend(q, k, v, ops.MASK_FULL)
-    x = ctx.out_project(o.reshape(b, s, -1), p["wo"], x, g1, s)
+    x = ctx.out_project(o.reshape(o.shape[0], o.shape[1], -1), p["wo"], x, g1, s)
     h = ops.adaln_rmsnorm(x, p["norm2"], sh2, sc2, s, cfg.rms_eps)
     return ctx.mlp(h, p["w_gate_up"], p["w_down"], x, g2, s)
 
@@ -225,7 +225,7 @@ def ar_block(cfg: MoTConfig, p: Dict[str, torch.Tensor], x, cos, sin, past: Opti
     h, _ = ops.rmsnorm(x, p["norm1"], cfg.rms_eps)
     q, k, v = ctx.qkv_project(h, p["wqkv"], cos, sin, p["q_norm"], p["k_norm"], cfg, prefix=past)
     o = ctx.attend(q, k, v, ops.MASK_CAUSAL)
-    x = ctx.out_project(o.reshape(b, s, -1), p["wo"], x, None, s)
+    x = ctx.out_project(o.reshape(o.shape[0], o.shape[1], -1), p["wo"], x, None, s)
     h, _ = ops.rmsnorm(x, p["norm2"], cfg.rms_eps)
     x = ctx.mlp(h, p["w_gate_up"], p["w_down"], x, None, s)
     return x, (k, v)

@@ -45,9 +45,15 @@ def build_engine_for_mesh(model, mesh: Mesh, fused: bool = True):
 
     ctx = None
     cfg_group = None
+    if mesh.size("cp") > 1 and mesh.size("tp") > 1:
+        raise ValueError("use either context parallelism or tensor parallelism (whose head split is the Ulysses layout)")
     if mesh.size("cp") > 1:
         from .ulysses import make_cp_context
         ctx = make_cp_context(model.cfg, mesh, fused=fused)
+    if mesh.size("tp") > 1:
+        from .tp import TPContext
+        dev = next(model.parameters()).device
+        ctx = TPContext(model.cfg, mesh.group("tp"), mesh.group_ranks["tp"], dev, fused=fused)
     if mesh.size("cfgp") > 1:
         from .cfgp import CFGParallel
         cfg_group = CFGParallel(mesh, fused=fused)

@@ -35,7 +35,8 @@ def _single(steps):
     return _gen_worker(0, 1, {}, steps)
 
 
-@pytest.mark.parametrize("world,pc", [(2, dict(cp=2)), (2, dict(cfgp=2)), (4, dict(cfgp=2, cp=2))])
+@pytest.mark.parametrize("world,pc", [(2, dict(cp=2)), (2, dict(cfgp=2)), (4, dict(cfgp=2, cp=2)),
+                                      (2, dict(cp=2, cp_mode="ring")), (2, dict(tp=2)), (4, dict(cfgp=2, tp=2))])
 def test_generator_parallel_matches_single(world, pc):
     want = _single(2)
     outs = run_ranks(_gen_worker, world, pc, 2)
