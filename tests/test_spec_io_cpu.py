@@ -135,3 +135,32 @@ def test_byte_tokenizer_roundtrip_and_chat():
         {"type": "image_url", "image_url": {"url": "x"}}, {"type": "text", "text": "what?"}]}], True, [4])
     assert chat.count(tok.image_pad_id) == 4
     assert tok.decode(chat, skip_special=False).endswith("<|im_start|>assistant\n")
+
+
+@pytest.mark.skipif(not REF.exists(), reason="reference assets not mounted")
+def test_droid_lerobot_dataset_items():
+    from cosmos_b200.data.vfm.action.datasets import DROIDLeRobotDataset
+
+    root = REF / "cookbooks/cosmos3/generator/action/assets/droid_lerobot_example"
+    ds = DROIDLeRobotDataset(root, action_chunk_size=16, decode_video=False)
+    assert ds.fps == 15 and len(ds) == (722 - 16 + 15) // 16
+    item = ds[0]
+    assert item["action"].shape == (16, 10) and item["action"].dtype == np.float32
+    assert item["conditioning_fps"] == 15 and isinstance(item["ai_caption"], str)
+    r = pose_utils.rot6d_to_rotmat(item["action"][:, 3:9].astype(np.float64))
+    assert np.allclose(r @ np.swapaxes(r, -1, -2), np.eye(3), atol=1e-5)
+    assert np.abs(item["action"][:, :3]).max() < 0.2  # metres moved per frame at 15 fps
+
+
+def test_policy_runner_returns_action_chunk():
+    import torch
+    from cosmos_b200.pipeline import Cosmos3OmniPipeline
+    from cosmos_b200.scripts.action_policy_server_robolab import PolicyRunner
+
+    pipe = Cosmos3OmniPipeline.from_pretrained("tiny", torch_dtype=torch.float32, vae_widths=(8, 16, 16, 16),
+                                               config_overrides=dict(max_text_len=16, n_layers=1))
+    runner = PolicyRunner(pipe)
+    img = (np.random.rand(48, 64, 3) * 255).astype(np.uint8)
+    out = runner.act({"instruction": "pick up the cube", "image": img.tolist(), "domain_name": "droid_lerobot",
+                      "action_chunk_size": 4, "image_size": 64, "num_steps": 2})
+    assert out["shape"] == [4, 10] and np.isfinite(np.asarray(out["action"])).all()
