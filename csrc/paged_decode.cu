@@ -241,3 +241,93 @@ void paged_decode(const PagedDecodeArgs& a, cudaStream_t s) {
 }
 
 }  // namespace cosmos
+
+// ====================================================================== allocation-free entry point
+// Declared and documented in paged_decode_noalloc.h (no counterpart in the reference).
+#include <cstdio>
+#include <cstring>
+#include <mutex>
+
+#include "paged_decode_noalloc.h"
+
+namespace {
+
+constexpr size_t kNoAllocFloats = (size_t)COSMOS_PAGED_DECODE_NOALLOC_MAX_ROWS * (128 + 2);
+
+// Split-KV partials of the allocation-free entry point. In host code this name is only a
+// stand-in for the symbol; the device address comes from cudaGetSymbolAddress below.
+static __device__ __align__(256) float g_noalloc_scratch[kNoAllocFloats];
+
+constexpr int kMaxDevices = 64;
+float* g_noalloc_ptr[kMaxDevices] = {};
+std::mutex g_noalloc_mu;
+
+int fail(int code, char* errbuf, int errbuf_len, const char* msg) {
+  if (errbuf && errbuf_len > 0) {
+    std::strncpy(errbuf, msg, (size_t)errbuf_len - 1);
+    errbuf[errbuf_len - 1] = '\0';
+  }
+  return code;
+}
+
+// Once per device, with that device current: resolve the scratch array's device address.
+int noalloc_scratch(float** out, char* errbuf, int errbuf_len) {
+  int dev = -1;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess || dev < 0 || dev >= kMaxDevices)
+    return fail(COSMOS_NOALLOC_CUDA_ERROR, errbuf, errbuf_len, "cudaGetDevice failed or device index out of range");
+  std::lock_guard<std::mutex> lock(g_noalloc_mu);
+  if (!g_noalloc_ptr[dev]) {
+    float* p = nullptr;
+    e = cudaGetSymbolAddress((void**)&p, g_noalloc_scratch);
+    if (e != cudaSuccess || !p) {
+      char msg[160];
+      std::snprintf(msg, sizeof(msg), "cudaGetSymbolAddress failed: %s", cudaGetErrorString(e));
+      return fail(COSMOS_NOALLOC_CUDA_ERROR, errbuf, errbuf_len, msg);
+    }
+    g_noalloc_ptr[dev] = p;
+  }
+  *out = g_noalloc_ptr[dev];
+  return COSMOS_NOALLOC_OK;
+}
+
+}  // namespace
+
+extern "C" int cosmos_paged_decode_noalloc(const void* q, const void* k_cache, const void* v_cache,
+                                           const int* block_table, const int* seq_lens, void* out, int B,
+                                           int Hq, int Hkv, int page_size, int max_pages, float scale,
+                                           int n_splits, void* stream, char* errbuf, int errbuf_len) {
+  if (!q || !k_cache || !v_cache || !block_table || !seq_lens || !out)
+    return fail(COSMOS_NOALLOC_BAD_ARGUMENT, errbuf, errbuf_len, "null pointer argument");
+  if (B <= 0 || Hq <= 0 || Hkv <= 0 || page_size <= 0 || max_pages <= 0 || Hq % Hkv != 0)
+    return fail(COSMOS_NOALLOC_BAD_ARGUMENT, errbuf, errbuf_len, "bad shape (need B, Hq, Hkv, page_size, max_pages > 0 and Hq % Hkv == 0)");
+  const int group = Hq / Hkv;
+  if (group != 1 && group != 2 && group != 4 && group != 8)
+    return fail(COSMOS_NOALLOC_BAD_ARGUMENT, errbuf, errbuf_len, "Hq / Hkv must be 1, 2, 4 or 8");
+  if (n_splits < 1 || n_splits > 64)
+    return fail(COSMOS_NOALLOC_BAD_ARGUMENT, errbuf, errbuf_len, "n_splits must be in [1, 64]");
+  const long long rows = (long long)B * Hq * n_splits;
+  if (rows > COSMOS_PAGED_DECODE_NOALLOC_MAX_ROWS) {
+    char msg[200];
+    std::snprintf(msg, sizeof(msg),
+                  "problem too large for the built-in scratch: B*Hq*n_splits = %lld > %d rows; lower n_splits "
+                  "or use the allocating entry point", rows, COSMOS_PAGED_DECODE_NOALLOC_MAX_ROWS);
+    return fail(COSMOS_NOALLOC_TOO_LARGE, errbuf, errbuf_len, msg);
+  }
+  float* scratch = nullptr;
+  const int rc = noalloc_scratch(&scratch, errbuf, errbuf_len);
+  if (rc != COSMOS_NOALLOC_OK) return rc;
+  cosmos::PagedDecodeArgs a;
+  a.q = q; a.k_cache = k_cache; a.v_cache = v_cache; a.block_table = block_table; a.seq_lens = seq_lens;
+  a.out = out; a.B = B; a.Hq = Hq; a.Hkv = Hkv; a.page_size = page_size; a.max_pages = max_pages;
+  a.scale = scale; a.n_splits = n_splits;
+  a.scratch = scratch; a.scratch_bytes = kNoAllocFloats * sizeof(float);
+  try {
+    cosmos::paged_decode(a, reinterpret_cast<cudaStream_t>(stream));
+  } catch (const std::exception& ex) {
+    return fail(COSMOS_NOALLOC_BAD_ARGUMENT, errbuf, errbuf_len, ex.what());
+  }
+  const cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess) return fail(COSMOS_NOALLOC_CUDA_ERROR, errbuf, errbuf_len, cudaGetErrorString(e));
+  return COSMOS_NOALLOC_OK;
+}
