@@ -182,7 +182,7 @@ def qkv_project_local(h, w, cos, sin, q_norm, k_norm, cfg: MoTConfig):
     hq, hk, hd = cfg.n_heads, cfg.n_kv_heads, cfg.head_dim
     gq = q_norm if cfg.qk_norm else None
     gk = k_norm if cfg.qk_norm else None
-    if hd == 128 and h.is_cuda and h.dtype == torch.bfloat16:
+    if hd == 128 and h.is_cuda and h.dtype == torch.bfloat16 and not ops._grad_needed(h, w, q_norm, k_norm):
         qkv = ops.gemm_qkv_rope(h.reshape(b * s, -1), w, None, cos, sin, gq, gk, hq, hk, cfg.rms_eps)
         qkv = qkv.view(b, s, hq + 2 * hk, hd)
         return qkv[:, :, :hq], qkv[:, :, hq:hq + hk], qkv[:, :, hq + hk:]

@@ -44,8 +44,17 @@ def extension_loaded() -> bool:
     return _loaded
 
 
-def _use_cuda(t: torch.Tensor) -> bool:
+def _grad_needed(*tensors) -> bool:
+    return torch.is_grad_enabled() and any(isinstance(t, torch.Tensor) and t.requires_grad for t in tensors)
+
+
+def _use_cuda(t: torch.Tensor, *others) -> bool:
+    """True when the call should run the sm_100a kernel: CUDA bf16 input and no autograd graph to
+    build. Calls that need gradients run the differentiable PyTorch definition instead (the
+    forward kernels have no backward counterparts yet)."""
     if not (t.is_cuda and t.dtype == torch.bfloat16):
+        return False
+    if _grad_needed(t, *others):
         return False
     if not load_extension():
         raise RuntimeError(
@@ -108,7 +117,7 @@ def check_status(reset: bool = True) -> None:
 # --------------------------------------------------------------------------- ops
 def gemm(a, w, bias=None, epi: int = EPI_PLAIN, resid=None, gate=None, rows_per_batch: int = 0, out=None):
     """a [.., K] @ w[N, K]^T with a fused epilogue (see csrc/gemm_tcgen05.cu)."""
-    if _use_cuda(a):
+    if _use_cuda(a, w, bias, resid, gate):
         return _k().gemm(a, w, bias, epi, resid, gate, rows_per_batch, out)
     r = ref.gemm(a, w, bias, epi, resid, gate, rows_per_batch)
     if out is not None:
@@ -123,7 +132,7 @@ def linear(x, w, bias=None):
 
 def gemm_qkv_rope(a, w, bias, cos, sin, gamma_q, gamma_k, n_q_heads: int, n_k_heads: int,
                   eps: float = 1e-6, route_ptr=None, route_ld=None, out=None):
-    if _use_cuda(a):
+    if _use_cuda(a, w, bias, gamma_q, gamma_k):
         return _k().gemm_qkv_rope(a, w, bias, cos, sin, gamma_q, gamma_k, n_q_heads, n_k_heads, eps,
                                   route_ptr, route_ld, out)
     assert route_ptr is None, "routed epilogue is CUDA-only"
@@ -139,7 +148,7 @@ def attention(q, k, v, scale: Optional[float] = None, mask: int = MASK_FULL, n_a
               ) -> Tuple[torch.Tensor, Optional[torch.Tensor]]:
     """Flash attention, q [B, Sq, Hq, D], k/v [B, Skv, Hkv, D] -> (o [B, Sq, Hq, D], lse|None)."""
     scale = scale if scale is not None else 1.0 / math.sqrt(q.shape[-1])
-    if _use_cuda(q) and q.shape[-1] == 128:
+    if _use_cuda(q, k, v) and q.shape[-1] == 128:
         o, lse = _k().attn_fwd(q, k, v, scale, mask, n_ar, return_lse, dest_ptr, rows_per_dest, out)
         return o, (lse if return_lse else None)
     assert dest_ptr is None, "routed epilogue is CUDA-only"
@@ -152,14 +161,14 @@ def attention(q, k, v, scale: Optional[float] = None, mask: int = MASK_FULL, n_a
 
 def rmsnorm(x, gamma=None, eps: float = 1e-6, residual=None):
     """Returns (y, x + residual | None)."""
-    if _use_cuda(x):
+    if _use_cuda(x, gamma, residual):
         y, r = _k().rmsnorm(x.contiguous(), gamma, eps, None if residual is None else residual.contiguous())
         return y, (r if residual is not None else None)
     return ref.rmsnorm(x, gamma, eps, residual)
 
 
 def adaln_rmsnorm(x, gamma, shift, scale, rows_per_batch: int, eps: float = 1e-6):
-    if _use_cuda(x):
+    if _use_cuda(x, gamma, shift, scale):
         return _k().adaln_rmsnorm(x.contiguous(), gamma, shift, scale, rows_per_batch, eps)
     return ref.adaln_rmsnorm(x, gamma, shift, scale, rows_per_batch, eps)
 
@@ -167,20 +176,20 @@ def adaln_rmsnorm(x, gamma, shift, scale, rows_per_batch: int, eps: float = 1e-6
 def mrope(x, cos=None, sin=None, gamma=None, eps: float = 1e-6):
     """Per-head RMSNorm + rotary embedding on x [.., rows, H, 128]; returns a new tensor on CPU,
     works in place on CUDA (and returns x)."""
-    if _use_cuda(x) and x.shape[-1] == 128:
+    if _use_cuda(x, gamma) and x.shape[-1] == 128:
         _k().mrope_(x, cos, sin, gamma, eps)
         return x
     return ref.mrope(x, cos, sin, gamma, eps)
 
 
 def gated_residual(x, f, gate=None, rows_per_batch: int = 1):
-    if _use_cuda(x):
+    if _use_cuda(x, f, gate):
         return _k().gated_residual(x.contiguous(), f.contiguous(), gate, rows_per_batch)
     return ref.gated_residual(x, f, gate, rows_per_batch)
 
 
 def swiglu(gate_up):
-    if _use_cuda(gate_up):
+    if _use_cuda(gate_up, gate_up):
         return _k().swiglu(gate_up.contiguous())
     return ref.swiglu(gate_up)
 
