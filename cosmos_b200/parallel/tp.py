@@ -156,19 +156,20 @@ class TPContext(AttnContext):
             return ops.gated_residual(resid, partial_fn(slice(0, s), None), gate, rows_per_batch)
         s_loc = s // tp
         if self.fused and like.is_cuda and like.dtype == torch.bfloat16 and not torch.is_grad_enabled():
-            key = ("rs", s_loc, d)
+            b = like.shape[0]
+            key = ("rs", b, s_loc, d)
             if key not in self._ws:
-                nb = s_loc * d * 2
-                buf = self.sg.alloc(f"tp_rs_{s_loc}_{d}", tp * nb)
-                mine = buf.view(0, (tp, s_loc, d), like.dtype)
-                peers = [buf._handle.get_buffer(p, (s_loc, d), like.dtype, r * s_loc * d) for p in range(tp)]
+                nb = b * s_loc * d * 2
+                buf = self.sg.alloc(f"tp_rs_{b}_{s_loc}_{d}", tp * nb)
+                mine = buf.view(0, (tp, b, s_loc, d), like.dtype)
+                peers = [buf._handle.get_buffer(p, (b, s_loc, d), like.dtype, r * b * s_loc * d) for p in range(tp)]
                 self._ws[key] = (mine, peers)
             mine, peers = self._ws[key]
             for i in range(tp):
                 p = (r + i) % tp  # own block first, then staggered so that no peer is hit by all ranks at once
                 partial_fn(slice(p * s_loc, (p + 1) * s_loc), peers[p])
             self.sg.barrier(slot=8)
-            acc = mine.float().sum(0).to(like.dtype)[None]
+            acc = mine.float().sum(0).to(like.dtype)
             out = ops.gated_residual(resid, acc, gate, rows_per_batch)
             self.sg.barrier(slot=9)  # partial buffers may be overwritten again
             return out
@@ -245,7 +246,7 @@ class TPContext(AttnContext):
         b, s, _ = o.shape
 
         def partial(rows, out):
-            return ops.gemm(o[:, rows], wl, out=None if out is None else out[None])
+            return ops.gemm(o[:, rows], wl, out=out)
 
         return self._reduce_scatter_seq(partial, s, w.shape[0], resid, gate, rows_per_batch, o)
 
@@ -261,6 +262,6 @@ class TPContext(AttnContext):
         b, s, _ = a.shape
 
         def partial(rows, out):
-            return ops.gemm(a[:, rows], wd, out=None if out is None else out[None])
+            return ops.gemm(a[:, rows], wd, out=out)
 
         return self._reduce_scatter_seq(partial, s, w_down.shape[0], resid, gate, rows_per_batch, a)

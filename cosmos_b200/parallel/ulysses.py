@@ -173,5 +173,5 @@ def make_cp_context(cfg: MoTConfig, mesh: Mesh, fused: bool = True) -> AttnConte
     ranks = mesh.group_ranks["cp"]
     if mesh.pc.cp_mode == "ring":
         from .ring import RingAttn
-        return RingAttn(cfg, mesh.group("cp"), ranks, device)
+        return RingAttn(cfg, mesh.group("cp"), ranks, device, fused)
     return UlyssesAttn(cfg, mesh.group("cp"), ranks, device, fused)

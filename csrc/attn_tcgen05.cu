@@ -47,12 +47,35 @@ __device__ __forceinline__ float ex2(float x) {
   return y;
 }
 
+// exp2 on the FMA/ALU pipes: round-to-nearest split x = n + f, f in [-0.5, 0.5], degree-3 minimax
+// polynomial for 2^f (max relative error 7.5e-5, far below bf16 rounding of P), exponent add for 2^n.
+// Used for a fixed share of the softmax elements to take load off the 16-lane MUFU pipe, which
+// otherwise needs as many cycles per score tile as the tensor cores.
+__device__ __forceinline__ float ex2_poly(float x) {
+  x = fmaxf(x, -126.f);
+  const float magic = 12582912.f;  // 1.5 * 2^23: the integer part lands in the low mantissa bits
+  const float t = x + magic;
+  const float n = t - magic;
+  const float f = x - n;
+  float p = fmaf(0.0551716648f, f, 0.2426111251f);
+  p = fmaf(p, f, 0.6932609677f);
+  p = fmaf(p, f, 0.9999280572f);
+  return __int_as_float(__float_as_int(p) + (__float_as_int(t) << 23));
+}
+
+template <int EMU>
+__device__ __forceinline__ float ex2_mix(float x, int i) {
+  if (EMU > 0 && (i % EMU) == EMU - 1) return ex2_poly(x);
+  return ex2(x);
+}
+
 __device__ __forceinline__ int kv_limit(int qi, const AttnParams& p) {
   if (p.mask == MASK_CAUSAL) return min(p.Skv, qi + 1 + (p.Skv - p.Sq));
   if (p.mask == MASK_MOT) return qi < p.n_ar ? qi + 1 : p.Skv;
   return p.Skv;
 }
 
+template <int EMU>
 __global__ void __launch_bounds__(ATT_THREADS, 1)
 flash_attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
                       const __grid_constant__ CUtensorMap tmV, const AttnParams p) {
@@ -279,8 +302,8 @@ flash_attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
       float lsum = 0.f;
 #pragma unroll
       for (int i = 0; i < 64; ++i) {
-        const float p0 = ex2(fmaf(__uint_as_float(s[2 * i]), sl2, -m_used));
-        const float p1 = ex2(fmaf(__uint_as_float(s[2 * i + 1]), sl2, -m_used));
+        const float p0 = ex2_mix<EMU>(fmaf(__uint_as_float(s[2 * i]), sl2, -m_used), 2 * i);
+        const float p1 = ex2_mix<EMU>(fmaf(__uint_as_float(s[2 * i + 1]), sl2, -m_used), 2 * i + 1);
         lsum += p0 + p1;
         pk[i] = pack_bf16(p0, p1);
       }
@@ -364,8 +387,10 @@ void flash_attn_fwd(const AttnArgs& a, cudaStream_t stream) {
     throw std::runtime_error("flash_attn_fwd: output strides must be multiples of 8 elements");
   static bool configured = false;
   if (!configured) {
-    cudaFuncSetAttribute(cb::flash_attn_fwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                         cb::ATT_SMEM);
+    cudaFuncSetAttribute(cb::flash_attn_fwd_kernel<0>, cudaFuncAttributeMaxDynamicSharedMemorySize, cb::ATT_SMEM);
+    cudaFuncSetAttribute(cb::flash_attn_fwd_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, cb::ATT_SMEM);
+    cudaFuncSetAttribute(cb::flash_attn_fwd_kernel<3>, cudaFuncAttributeMaxDynamicSharedMemorySize, cb::ATT_SMEM);
+    cudaFuncSetAttribute(cb::flash_attn_fwd_kernel<4>, cudaFuncAttributeMaxDynamicSharedMemorySize, cb::ATT_SMEM);
     configured = true;
   }
   // B == 1 tensors may carry a zero batch stride; TMA needs a non-zero multiple of 16 bytes.
@@ -386,7 +411,13 @@ void flash_attn_fwd(const AttnArgs& a, cudaStream_t stream) {
   p.dest_ptr = a.dest_ptr; p.rows_per_dest = a.rows_per_dest > 0 ? a.rows_per_dest : 1;
   p.status = a.status;
   dim3 grid((a.Sq + 2 * cb::TQ - 1) / (2 * cb::TQ), a.Hq, a.B);
-  cb::flash_attn_fwd_kernel<<<grid, cb::ATT_THREADS, cb::ATT_SMEM, stream>>>(tq, tk, tv, p);
+  // a.exp_emulation: 0 = all exp2 on the MUFU pipe, k = every k-th element on the FMA pipe
+  switch (a.exp_emulation) {
+    case 0: cb::flash_attn_fwd_kernel<0><<<grid, cb::ATT_THREADS, cb::ATT_SMEM, stream>>>(tq, tk, tv, p); break;
+    case 2: cb::flash_attn_fwd_kernel<2><<<grid, cb::ATT_THREADS, cb::ATT_SMEM, stream>>>(tq, tk, tv, p); break;
+    case 3: cb::flash_attn_fwd_kernel<3><<<grid, cb::ATT_THREADS, cb::ATT_SMEM, stream>>>(tq, tk, tv, p); break;
+    default: cb::flash_attn_fwd_kernel<4><<<grid, cb::ATT_THREADS, cb::ATT_SMEM, stream>>>(tq, tk, tv, p); break;
+  }
 }
 
 }  // namespace cosmos

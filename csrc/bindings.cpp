@@ -5,6 +5,7 @@
 #include <c10/cuda/CUDAGuard.h>
 #include <torch/library.h>
 
+#include <cstdlib>
 #include <map>
 #include <mutex>
 #include <optional>
@@ -205,6 +206,10 @@ std::tuple<Tensor, Tensor> attn_fwd(const Tensor& q, const Tensor& k, const Tens
     a.rows_per_dest = (int)rows_per_dest;
   }
   a.status = status_tensor(q.get_device()).data_ptr<int>();
+  {
+    static const int emu = [] { const char* e = std::getenv("COSMOS_ATTN_EXP_EMU"); return e ? std::atoi(e) : 4; }();
+    a.exp_emulation = emu;
+  }
   cosmos::flash_attn_fwd(a, cur_stream());
   return {o, lse};
 }

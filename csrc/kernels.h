@@ -66,6 +66,7 @@ struct AttnArgs {
   const long long* dest_ptr = nullptr;
   int rows_per_dest = 0;
   int* status = nullptr;
+  int exp_emulation = 4;  // every k-th softmax element uses the polynomial exp2 (0 = none; 2, 3, 4)
 };
 void flash_attn_fwd(const AttnArgs& a, cudaStream_t stream);
 

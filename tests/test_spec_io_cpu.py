@@ -164,3 +164,40 @@ def test_policy_runner_returns_action_chunk():
     out = runner.act({"instruction": "pick up the cube", "image": img.tolist(), "domain_name": "droid_lerobot",
                       "action_chunk_size": 4, "image_size": 64, "num_steps": 2})
     assert out["shape"] == [4, 10] and np.isfinite(np.asarray(out["action"])).all()
+
+
+@pytest.mark.skipif(not REF.exists(), reason="reference assets not mounted")
+def test_physics_iq_specs_validate(tmp_path):
+    from cosmos_b200.evaluation import physics_iq as piq
+
+    for setting in ("i2v", "v2v"):
+        prompts = piq.load_prompts(REF / f"evaluation/cosmos3/Physics_IQ/assets/{setting}_prompts.json")
+        assert len(prompts) == piq.N_CASES
+        specs = piq.build_specs(setting, prompts, tmp_path, limit=3)
+        f = piq.write_jsonl(specs, tmp_path / f"{setting}.jsonl")
+        loaded = load_specs(f)
+        assert len(loaded) == 3 and loaded[0].num_steps == 50 and loaded[0].sigma_max == 80.0
+    assert loaded[0].condition_frame_indexes_vision == list(range(19)) and loaded[0].num_frames == 193
+    frames = np.zeros((193, 4, 4, 3), np.uint8)
+    assert piq.scored_frames(frames, "v2v").shape[0] == 120
+    assert piq.scored_frames(frames[:121], "i2v").shape[0] == 120
+    cmd = piq.inference_command("s.jsonl", "out", gpus=4)
+    assert "--cp-size=4" in cmd and "--no-guardrails" in cmd
+
+
+@pytest.mark.skipif(not REF.exists(), reason="reference assets not mounted")
+def test_preview_helpers_on_reference_specs(tmp_path):
+    from cosmos_b200.utils import preview_helpers as ph
+
+    d = REF / "cookbooks/cosmos3/generator/transfer/specs"
+    spec = ph.load_transfer_spec("depth", d)
+    assert spec["depth"]["control_path"].endswith("control_depth.mp4")
+    assert ph.resolve_spec_path(spec["prompt_path"], d).name == "prompt.json"
+    with pytest.raises(ValueError):
+        ph.load_transfer_spec("nope", d)
+    yy, xx = np.mgrid[0:32, 0:48]
+    clip = np.repeat(np.stack([xx * 4, yy * 6, xx + yy], -1).astype(np.uint8)[None], 3, 0)
+    src = tmp_path / "vision.mp4"
+    mp4.write_mp4_mjpeg(src, clip, 10)
+    prev = ph.make_preview(src)
+    assert prev.exists() and prev.name == "vision_preview.mp4"
