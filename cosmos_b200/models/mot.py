@@ -247,12 +247,22 @@ def joint_block(cfg: MoTConfig, p_ar, p_dm, x_ar, x_dm, t_mod, cos_ar, sin_ar, c
     v = torch.cat([va, vd], dim=1)
     o = ctx.attend(q, k, v, ops.MASK_MOT, n_ar=s_ar)
     oa, od = o[:, :s_ar].reshape(b, s_ar, -1), o[:, s_ar:].reshape(b, s_dm, -1)
-    x_ar = ctx.out_project(oa, p_ar["wo"], x_ar, None, s_ar)
-    x_dm = ctx.out_project(od, p_dm["wo"], x_dm, g1, s_dm)
+    grouped = type(ctx) in (AttnContext, WorkspaceAttn)  # local execution: one grouped launch per projection
+    if grouped:
+        x_ar, x_dm = ops.gemm_grouped2(oa, p_ar["wo"], od, p_dm["wo"], ops.EPI_GATED_RESID, x_ar, x_dm, None, g1,
+                                       s_ar, s_dm)
+    else:
+        x_ar = ctx.out_project(oa, p_ar["wo"], x_ar, None, s_ar)
+        x_dm = ctx.out_project(od, p_dm["wo"], x_dm, g1, s_dm)
     h_ar, _ = ops.rmsnorm(x_ar, p_ar["norm2"], cfg.rms_eps)
     h_dm = ops.adaln_rmsnorm(x_dm, p_dm["norm2"], sh2, sc2, s_dm, cfg.rms_eps)
-    x_ar = ctx.mlp(h_ar, p_ar["w_gate_up"], p_ar["w_down"], x_ar, None, s_ar)
-    x_dm = ctx.mlp(h_dm, p_dm["w_gate_up"], p_dm["w_down"], x_dm, g2, s_dm)
+    if grouped:
+        a_ar, a_dm = ops.gemm_grouped2(h_ar, p_ar["w_gate_up"], h_dm, p_dm["w_gate_up"], ops.EPI_SWIGLU)
+        x_ar, x_dm = ops.gemm_grouped2(a_ar, p_ar["w_down"], a_dm, p_dm["w_down"], ops.EPI_GATED_RESID, x_ar, x_dm,
+                                       None, g2, s_ar, s_dm)
+    else:
+        x_ar = ctx.mlp(h_ar, p_ar["w_gate_up"], p_ar["w_down"], x_ar, None, s_ar)
+        x_dm = ctx.mlp(h_dm, p_dm["w_gate_up"], p_dm["w_down"], x_dm, g2, s_dm)
     return x_ar, x_dm
 
 

@@ -126,6 +126,16 @@ def gemm(a, w, bias=None, epi: int = EPI_PLAIN, resid=None, gate=None, rows_per_
     return r
 
 
+def gemm_grouped2(a0, w0, a1, w1, epi: int = EPI_PLAIN, resid0=None, resid1=None, gate0=None, gate1=None,
+                  rows_per_batch0: int = 0, rows_per_batch1: int = 0):
+    """Two GEMMs with their own weights in ONE persistent launch (MoT per-modality routing: AR
+    tokens x AR weights, DM tokens x DM weights). Returns (c0, c1)."""
+    if _use_cuda(a0, w0, a1, w1, resid0, resid1, gate0, gate1) and a1.is_cuda and a1.dtype == torch.bfloat16:
+        return _k().gemm_grouped2(a0, w0, a1, w1, epi, resid0, resid1, gate0, gate1, rows_per_batch0, rows_per_batch1)
+    return (gemm(a0, w0, None, epi, resid0, gate0, rows_per_batch0),
+            gemm(a1, w1, None, epi, resid1, gate1, rows_per_batch1))
+
+
 def linear(x, w, bias=None):
     return gemm(x, w, bias)
 

@@ -46,6 +46,7 @@ def main():
     ap.add_argument("--iters", type=int, default=5)
     ap.add_argument("--small", action="store_true", help="sizes for a profiler capture")
     ap.add_argument("--cublas", action="store_true", help="also time torch.matmul / SDPA for comparison")
+    ap.add_argument("--attn-shape", default=None, help="sq,skv,hq,hkv for a single attention case")
     args = ap.parse_args()
     ops.load_extension()
     tf_peak, bw_peak, src = _peaks()
@@ -71,6 +72,8 @@ def main():
             print(json.dumps(rec), flush=True)
     if "attn" in what:
         cfgs = [(4096, 4096, 8, 2)] if args.small else [(16384, 16384, 8, 2), (32768, 32768, 8, 2)]
+        if args.attn_shape:
+            cfgs = [tuple(int(v) for v in args.attn_shape.split(","))]
         for sq, skv, hq, hkv in cfgs:
             q = torch.randn(1, sq, hq, 128, device=dev).bfloat16()
             k = torch.randn(1, skv, hkv, 128, device=dev).bfloat16()

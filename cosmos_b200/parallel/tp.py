@@ -192,9 +192,11 @@ class TPContext(AttnContext):
             mine, ptrs = self._ws[key]
             mine.copy_(x.reshape(-1))
             out = torch.empty_like(x)
-            self._ar_epoch += 2  # the kernel uses epochs (e, e + 1) on signal slots 16..23
-            torch.ops.cosmos_b200.allreduce_oneshot(ptrs, self.sg.pads_dev, out.view(-1), self.rank, self.tp, 16,
-                                                    self._ar_epoch - 1)
+            if not hasattr(self, "_ar_counters"):
+                self._ar_counters = torch.zeros(64, dtype=torch.int32, device=x.device)
+            # epochs of signal slots 16..23 are tracked on the device, so the call is CUDA-graph safe
+            torch.ops.cosmos_b200.allreduce_oneshot(ptrs, self.sg.pads_dev, out.view(-1), self.rank, self.tp, 16, 0,
+                                                    self._ar_counters)
             return out
         y = x.contiguous()
         dist.all_reduce(y, group=self.group)

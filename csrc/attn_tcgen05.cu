@@ -89,9 +89,9 @@ flash_attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
   auto kv_full = [&](int s) { return bar_base + 8u * (1 + s); };
   auto kv_empty = [&](int s) { return bar_base + 8u * (1 + NSLOT + s); };
   auto s_full = [&](int t) { return bar_base + 8u * (1 + 2 * NSLOT + t); };
-  auto p_full = [&](int t) { return bar_base + 8u * (3 + 2 * NSLOT + t); };
-  auto o_final = [&](int t) { return bar_base + 8u * (5 + 2 * NSLOT + t); };
-  constexpr int NBAR = 7 + 2 * NSLOT;
+  auto p_full = [&](int t, int h) { return bar_base + 8u * (3 + 2 * NSLOT + 2 * t + h); };
+  auto o_final = [&](int t) { return bar_base + 8u * (7 + 2 * NSLOT + t); };
+  constexpr int NBAR = 9 + 2 * NSLOT;
   const uint32_t tmem_slot = bar_base + 8u * NBAR;
   volatile uint32_t* tmem_slot_ptr =
       reinterpret_cast<volatile uint32_t*>(gen_base + 7 * TILE_BYTES + 8 * NBAR);
@@ -123,7 +123,8 @@ flash_attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
     }
     for (int t = 0; t < 2; ++t) {
       mbar_init(s_full(t), 1);
-      mbar_init(p_full(t), 128);
+      mbar_init(p_full(t, 0), 128);
+      mbar_init(p_full(t, 1), 128);
       mbar_init(o_final(t), 1);
     }
     *abort_flag = 0;
@@ -198,13 +199,17 @@ flash_attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
           mma_ss(d, a0 + off, b0 + off, idesc_qk, kk > 0 ? 1u : 0u);
         }
       };
-      auto issue_pv = [&](int t, int slot, bool acc) {
+      // P is handed over in two halves of 64 keys, so the first four k-steps of PV run while the
+      // softmax warps still compute the exponentials of the second half.
+      auto issue_pv = [&](int t, int slot, bool acc, int half) {
         const uint32_t d = tmem_base + 256 + t * 128;
         const uint32_t a0 = tmem_base + t * 128;
         const uint64_t b0 = v_desc0 + uint64_t(slot * (TILE_BYTES >> 4));
 #pragma unroll
-        for (int kk = 0; kk < 8; ++kk)
+        for (int k4 = 0; k4 < 4; ++k4) {
+          const int kk = half * 4 + k4;
           mma_ts(d, a0 + kk * 8, b0 + uint64_t(kk * (2048 >> 4)), idesc_pv, (acc || kk > 0) ? 1u : 0u);
+        }
       };
       bool ok = mbar_wait(q_full, 0, abort_flag, p.status, ST_TIMEOUT_MMA);
       if (ok) ok = mbar_wait(kv_full(0), 0, abort_flag, p.status, ST_TIMEOUT_MMA);
@@ -226,10 +231,14 @@ flash_attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
         if (!ok) break;
 #pragma unroll 1
         for (int t = 0; t < 2; ++t) {
-          ok = mbar_wait(p_full(t), j & 1, abort_flag, p.status, ST_TIMEOUT_MMA);
+          ok = mbar_wait(p_full(t, 0), j & 1, abort_flag, p.status, ST_TIMEOUT_MMA);
           if (!ok) break;
           tc_fence_after();
-          issue_pv(t, sv, j > 0);
+          issue_pv(t, sv, j > 0, 0);
+          ok = mbar_wait(p_full(t, 1), j & 1, abort_flag, p.status, ST_TIMEOUT_MMA);
+          if (!ok) break;
+          tc_fence_after();
+          issue_pv(t, sv, j > 0, 1);
           if (more) {
             issue_qk(t, sk);
             tc_commit(s_full(t));
@@ -298,21 +307,24 @@ flash_attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
           if (need) m_used = m_new;
         }
       }
-      uint32_t pk[64];
       float lsum = 0.f;
 #pragma unroll
-      for (int i = 0; i < 64; ++i) {
-        const float p0 = ex2_mix<EMU>(fmaf(__uint_as_float(s[2 * i]), sl2, -m_used), 2 * i);
-        const float p1 = ex2_mix<EMU>(fmaf(__uint_as_float(s[2 * i + 1]), sl2, -m_used), 2 * i + 1);
-        lsum += p0 + p1;
-        pk[i] = pack_bf16(p0, p1);
+      for (int half = 0; half < 2; ++half) {
+        uint32_t pk[32];
+#pragma unroll
+        for (int i = 0; i < 32; ++i) {
+          const int e = half * 64 + 2 * i;
+          const float p0 = ex2_mix<EMU>(fmaf(__uint_as_float(s[e]), sl2, -m_used), e);
+          const float p1 = ex2_mix<EMU>(fmaf(__uint_as_float(s[e + 1]), sl2, -m_used), e + 1);
+          lsum += p0 + p1;
+          pk[i] = pack_bf16(p0, p1);
+        }
+        tmem_st32(s_addr + half * 32, pk);
+        tmem_wait_st();
+        tc_fence_before();
+        mbar_arrive(p_full(t, half));
       }
       l += lsum;
-      tmem_st32(s_addr, *reinterpret_cast<uint32_t(*)[32]>(&pk[0]));
-      tmem_st32(s_addr + 32, *reinterpret_cast<uint32_t(*)[32]>(&pk[32]));
-      tmem_wait_st();
-      tc_fence_before();
-      mbar_arrive(p_full(t));
     }
     if (ok) ok = mbar_wait(o_final(t), 0, abort_flag, p.status, ST_TIMEOUT_SOFTMAX);
     if (ok) {
@@ -413,10 +425,10 @@ void flash_attn_fwd(const AttnArgs& a, cudaStream_t stream) {
   dim3 grid((a.Sq + 2 * cb::TQ - 1) / (2 * cb::TQ), a.Hq, a.B);
   // a.exp_emulation: 0 = all exp2 on the MUFU pipe, k = every k-th element on the FMA pipe
   switch (a.exp_emulation) {
-    case 0: cb::flash_attn_fwd_kernel<0><<<grid, cb::ATT_THREADS, cb::ATT_SMEM, stream>>>(tq, tk, tv, p); break;
     case 2: cb::flash_attn_fwd_kernel<2><<<grid, cb::ATT_THREADS, cb::ATT_SMEM, stream>>>(tq, tk, tv, p); break;
     case 3: cb::flash_attn_fwd_kernel<3><<<grid, cb::ATT_THREADS, cb::ATT_SMEM, stream>>>(tq, tk, tv, p); break;
-    default: cb::flash_attn_fwd_kernel<4><<<grid, cb::ATT_THREADS, cb::ATT_SMEM, stream>>>(tq, tk, tv, p); break;
+    case 4: cb::flash_attn_fwd_kernel<4><<<grid, cb::ATT_THREADS, cb::ATT_SMEM, stream>>>(tq, tk, tv, p); break;
+    default: cb::flash_attn_fwd_kernel<0><<<grid, cb::ATT_THREADS, cb::ATT_SMEM, stream>>>(tq, tk, tv, p); break;
   }
 }
 

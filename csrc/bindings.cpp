@@ -95,10 +95,73 @@ Tensor gemm(const Tensor& A_, const Tensor& W, const OptT& bias, int64_t epi, co
     g.rows_per_batch = (int)rows_per_batch;
   }
   g.status = status_tensor(A.get_device()).data_ptr<int>();
+  Tensor partial;
+  const int ks = cosmos::gemm_pick_k_splits(g.M, g.N, g.K, g.epi);
+  if (ks > 1 && C.stride(0) % 4 == 0) {  // skinny problem (decode): split K across CTAs, fp32 partials as scratch
+    partial = at::empty({ks, M, N}, A.options().dtype(at::kFloat));
+    g.k_splits = ks;
+    g.partial = partial.data_ptr<float>();
+  }
   cosmos::gemm_bf16(g, cur_stream());
   auto shape = A_.sizes().vec();
   shape.back() = n_out;
   return C.reshape(shape);
+}
+
+// Grouped GEMM over two token segments with their own weights (MoT per-modality routing), one launch.
+// epi in {PLAIN, SWIGLU, GATED_RESID}; returns (C0, C1).
+std::tuple<Tensor, Tensor> gemm_grouped2(const Tensor& A0_, const Tensor& W0, const Tensor& A1_, const Tensor& W1,
+                                         int64_t epi, const OptT& resid0, const OptT& resid1, const OptT& gate0,
+                                         const OptT& gate1, int64_t rpb0, int64_t rpb1) {
+  TORCH_CHECK(epi == EPI_PLAIN || epi == EPI_SWIGLU || epi == EPI_GATED_RESID, "unsupported epilogue for grouped GEMM");
+  c10::cuda::CUDAGuard guard(A0_.device());
+  const Tensor* As[2] = {&A0_, &A1_};
+  const Tensor* Ws[2] = {&W0, &W1};
+  const OptT* Rs[2] = {&resid0, &resid1};
+  const OptT* Gs[2] = {&gate0, &gate1};
+  const int64_t rpbs[2] = {rpb0, rpb1};
+  cosmos::GemmArgs args[2];
+  Tensor A2[2], C[2], R2[2];
+  for (int i = 0; i < 2; ++i) {
+    check_bf16_cuda(*As[i], "A"); check_bf16_cuda(*Ws[i], "W");
+    A2[i] = as_2d(*As[i]);
+    TORCH_CHECK(A2[i].stride(1) == 1 && Ws[i]->dim() == 2 && Ws[i]->stride(1) == 1 && A2[i].size(1) == Ws[i]->size(1),
+                "bad A/W in problem ", i);
+    const int64_t M = A2[i].size(0), N = Ws[i]->size(0), K = A2[i].size(1);
+    const int64_t n_out = (epi == EPI_SWIGLU) ? N / 2 : N;
+    C[i] = at::empty({M, n_out}, A2[i].options());
+    cosmos::GemmArgs& g = args[i];
+    g.A = A2[i].data_ptr(); g.B = Ws[i]->data_ptr(); g.C = C[i].data_ptr();
+    g.M = (int)M; g.N = (int)N; g.K = (int)K;
+    g.lda = A2[i].stride(0); g.ldb = Ws[i]->stride(0); g.ldc = C[i].stride(0);
+    g.epi = (int)epi;
+    if (epi == EPI_GATED_RESID) {
+      TORCH_CHECK(Rs[i]->has_value() && (*Rs[i])->defined(), "gated-residual epilogue needs residuals");
+      R2[i] = as_2d(**Rs[i]);
+      check_bf16_cuda(R2[i], "resid");
+      TORCH_CHECK(R2[i].size(0) == M && R2[i].size(1) == N && R2[i].stride(1) == 1 && R2[i].stride(0) % 8 == 0);
+      g.R = R2[i].data_ptr(); g.ldr = R2[i].stride(0);
+      if (Gs[i]->has_value() && (*Gs[i])->defined()) {
+        check_bf16_cuda(**Gs[i], "gate");
+        TORCH_CHECK((*Gs[i])->is_contiguous() && (*Gs[i])->size(-1) == N && rpbs[i] > 0 &&
+                    (*Gs[i])->numel() / N * rpbs[i] >= M, "bad gate in problem ", i);
+        g.gate = (*Gs[i])->data_ptr();
+      }
+      g.rows_per_batch = (int)rpbs[i];
+    }
+    g.status = status_tensor(A0_.get_device()).data_ptr<int>();
+  }
+  if (args[0].M == 0) {
+    if (args[1].M > 0) cosmos::gemm_bf16(args[1], cur_stream());
+  } else {
+    cosmos::gemm_bf16_grouped(args, 2, cur_stream());
+  }
+  auto shape_of = [&](int i) {
+    auto sh = As[i]->sizes().vec();
+    sh.back() = C[i].size(1);
+    return sh;
+  };
+  return {C[0].reshape(shape_of(0)), C[1].reshape(shape_of(1))};
 }
 
 // QKV projection with per-head RMSNorm + rotary embedding in the epilogue and optional
@@ -207,7 +270,7 @@ std::tuple<Tensor, Tensor> attn_fwd(const Tensor& q, const Tensor& k, const Tens
   }
   a.status = status_tensor(q.get_device()).data_ptr<int>();
   {
-    static const int emu = [] { const char* e = std::getenv("COSMOS_ATTN_EXP_EMU"); return e ? std::atoi(e) : 4; }();
+    static const int emu = [] { const char* e = std::getenv("COSMOS_ATTN_EXP_EMU"); return e ? std::atoi(e) : 0; }();
     a.exp_emulation = emu;
   }
   cosmos::flash_attn_fwd(a, cur_stream());
@@ -381,13 +444,28 @@ void comm_barrier(const Tensor& pads, int64_t rank, int64_t world, int64_t slot,
 }
 
 void allreduce_oneshot(const Tensor& bufs, const Tensor& pads, Tensor out, int64_t rank, int64_t world,
-                       int64_t slot, int64_t epoch) {
+                       int64_t slot, int64_t epoch, const OptT& counters) {
   check_bf16_cuda(out, "out");
   c10::cuda::CUDAGuard guard(out.device());
   TORCH_CHECK(out.is_contiguous() && bufs.numel() >= world && pads.numel() >= world);
+  int* cnt = nullptr;
+  if (counters.has_value() && counters->defined()) {
+    TORCH_CHECK(counters->is_cuda() && counters->scalar_type() == at::kInt && counters->numel() >= slot + 8);
+    cnt = counters->data_ptr<int>();
+  }
   cosmos::allreduce_oneshot(ptr_table(bufs, "bufs"), ptr_table(pads, "pads"), out.data_ptr(), out.numel(),
-                            (int)rank, (int)world, (int)slot, (int)epoch,
+                            (int)rank, (int)world, (int)slot, (int)epoch, cnt,
                             status_tensor(out.get_device()).data_ptr<int>(), cur_stream());
+}
+
+void kv_cache_write(const Tensor& k, const Tensor& v, const Tensor& slots, Tensor k_cache, Tensor v_cache) {
+  check_bf16_cuda(k, "k"); check_bf16_cuda(v, "v"); check_bf16_cuda(k_cache, "k_cache"); check_bf16_cuda(v_cache, "v_cache");
+  c10::cuda::CUDAGuard guard(k.device());
+  TORCH_CHECK(k.is_contiguous() && v.is_contiguous() && k.sizes() == v.sizes() && k.dim() == 3 && k.size(2) == 128);
+  TORCH_CHECK(k_cache.is_contiguous() && v_cache.is_contiguous() && k_cache.dim() == 4 && k_cache.size(2) == k.size(1));
+  TORCH_CHECK(slots.is_cuda() && slots.scalar_type() == at::kLong && slots.is_contiguous() && slots.numel() == k.size(0));
+  cosmos::kv_cache_write(k.data_ptr(), v.data_ptr(), reinterpret_cast<const long long*>(slots.data_ptr<int64_t>()),
+                         k_cache.data_ptr(), v_cache.data_ptr(), k.size(0), (int)k.size(1), cur_stream());
 }
 
 // mode 0: reduce + update; mode 1: reduce into `reduced` and add sum(g^2) to sq; mode 2: update from `reduced`
@@ -426,6 +504,7 @@ TORCH_LIBRARY(cosmos_b200, m) {
   m.def("status_word", &status_word);
   m.def("gemm", &gemm);
   m.def("gemm_qkv_rope", &gemm_qkv_rope);
+  m.def("gemm_grouped2", &gemm_grouped2);
   m.def("attn_fwd", &attn_fwd);
   m.def("rmsnorm", &rmsnorm);
   m.def("adaln_rmsnorm", &adaln_rmsnorm);
@@ -438,6 +517,7 @@ TORCH_LIBRARY(cosmos_b200, m) {
   m.def("paged_decode_pick_splits", &paged_decode_pick_splits);
   m.def("comm_barrier", &comm_barrier);
   m.def("allreduce_oneshot", &allreduce_oneshot);
+  m.def("kv_cache_write", &kv_cache_write);
   m.def("rs_adamw", &rs_adamw);
   m.def("allgather_pull", &allgather_pull);
   cosmos::register_runtime_ops(m);

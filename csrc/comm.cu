@@ -51,11 +51,20 @@ __global__ void barrier_kernel(const long long* pads, int rank, int world, int s
 // out[i] = sum_r peer_r[i] (bf16, fp32 accumulate); bufs[r] = rank r's input buffer.
 // Launched on every rank after all inputs are written; the leading barrier makes the peers'
 // writes visible, the trailing one keeps a fast rank from overwriting its input early.
+// With `counters` (a local device array, one int per signal slot) the kernel keeps the barrier
+// epoch itself: it reads counters[slot] + 1, uses that and the next value, and stores the result
+// back. No launch argument changes from call to call then, so the call can sit in a CUDA graph.
 __global__ void __launch_bounds__(512)
 allreduce_oneshot_kernel(const long long* bufs, const long long* pads, bf16* out, long long n_vec,
-                         int rank, int world, int slot, int epoch, int* status) {
+                         int rank, int world, int slot, int epoch, int* counters, int* status) {
   // every block runs the barrier on its own slot row, so blocks do not depend on each other
   const int myslot = slot + blockIdx.x;
+  if (counters) {
+    __shared__ int e_s;
+    if (threadIdx.x == 0) e_s = counters[myslot] + 1;
+    __syncthreads();
+    epoch = e_s;
+  }
   const bool ok = barrier_device(pads, rank, world, myslot, epoch, status);
   if (!__syncthreads_and(ok ? 1 : 0)) return;
   for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n_vec;
@@ -73,6 +82,7 @@ allreduce_oneshot_kernel(const long long* bufs, const long long* pads, bf16* out
   }
   __syncthreads();
   barrier_device(pads, rank, world, myslot, epoch + 1, status);
+  if (counters && threadIdx.x == 0) counters[myslot] = epoch + 1;
 }
 
 // Fused reduce-scatter + AdamW on this rank's shard [shard_off, shard_off + n) of a flat
@@ -141,15 +151,15 @@ void comm_barrier(const long long* pads_dev, int rank, int world, int slot, int 
 }
 
 void allreduce_oneshot(const long long* bufs_dev, const long long* pads_dev, void* out,
-                       long long n_elems, int rank, int world, int slot, int epoch, int* status,
-                       cudaStream_t s) {
+                       long long n_elems, int rank, int world, int slot, int epoch, int* counters,
+                       int* status, cudaStream_t s) {
   if (n_elems % 8 != 0) throw std::runtime_error("allreduce_oneshot: element count must be % 8");
   if (world > 64) throw std::runtime_error("allreduce_oneshot: at most 64 ranks per group");
   const long long n_vec = n_elems / 8;
   int blocks = (int)std::min<long long>((n_vec + 511) / 512, 8);
   if (blocks < 1) blocks = 1;
   cb::allreduce_oneshot_kernel<<<blocks, 512, 0, s>>>(bufs_dev, pads_dev, (bf16*)out, n_vec, rank,
-                                                     world, slot, epoch, status);
+                                                     world, slot, epoch, counters, status);
 }
 
 void rs_adamw(const long long* grads_dev, int world, long long shard_off, long long n, float* master,

@@ -52,6 +52,20 @@ struct GemmParams {
   int n_q_heads, n_k_heads;
   float eps;
   int* status;
+  // split-K (skinny problems, e.g. decode): the K range is divided among k_splits CTAs per output
+  // tile; each writes its raw fp32 accumulators to partial[ks][M][N] and a second kernel reduces
+  // them and applies the epilogue.
+  int k_splits;
+  float* partial;
+};
+
+// Up to two independent problems served by one persistent launch (grouped GEMM): tiles
+// [0, tiles0) belong to problem 0, the rest to problem 1. Used for the per-modality weight
+// routing of the Mixture-of-Transformers layers (AR tokens x AR weights, DM tokens x DM weights).
+struct GemmGroup {
+  GemmParams p[2];
+  int tiles0;
+  int total;
 };
 
 __device__ __forceinline__ void tile_coords(int t, int m_tiles, int n_tiles, int& tm, int& tn) {
@@ -68,7 +82,8 @@ __device__ __forceinline__ void tile_coords(int t, int m_tiles, int n_tiles, int
 template <int EPI>
 __global__ void __launch_bounds__(GEMM_THREADS, 1)
 gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
-                 const GemmParams p) {
+                 const __grid_constant__ CUtensorMap tmA1, const __grid_constant__ CUtensorMap tmB1,
+                 const __grid_constant__ GemmGroup g) {
   extern __shared__ uint8_t smem_raw[];
   const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
   const uint32_t bar_base = smem_base + STAGES * STAGE_BYTES;
@@ -86,8 +101,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
-  const int total_tiles = p.m_tiles * p.n_tiles;
-  const int k_blocks = (p.K + BK - 1) / BK;
+  const int total_tiles = g.total;
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < STAGES; ++s) {
@@ -102,6 +116,10 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     fence_barrier_init();
     prefetch_tmap(&tmA);
     prefetch_tmap(&tmB);
+    if (g.total > g.tiles0) {
+      prefetch_tmap(&tmA1);
+      prefetch_tmap(&tmB1);
+    }
   }
   if (warp == 1) {
     tmem_alloc(tmem_slot, 512);
@@ -118,11 +136,19 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       int it = 0;
       bool ok = true;
       for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
+        const int second = t >= g.tiles0;
+        const GemmParams& p = g.p[second];
+        const CUtensorMap* mA = second ? &tmA1 : &tmA;
+        const CUtensorMap* mB = second ? &tmB1 : &tmB;
+        const int k_blocks = (p.K + BK - 1) / BK;
+        const int tl = second ? t - g.tiles0 : t;
+        const int ks = tl % p.k_splits;
+        const int kb0 = ks * k_blocks / p.k_splits, kb1 = (ks + 1) * k_blocks / p.k_splits;
         int tm, tn;
-        tile_coords(t, p.m_tiles, p.n_tiles, tm, tn);
+        tile_coords(tl / p.k_splits, p.m_tiles, p.n_tiles, tm, tn);
         const int m0 = tm * BM;
         const int n0 = (EPI == EPI_SWIGLU) ? tn * 128 : tn * BN;
-        for (int kb = 0; kb < k_blocks; ++kb, ++it) {
+        for (int kb = kb0; kb < kb1; ++kb, ++it) {
           const int s = it % STAGES;
           const uint32_t ph = (it / STAGES) & 1;
           if (!mbar_wait(empty_bar(s), ph ^ 1, abort_flag, p.status, ST_TIMEOUT_TMA)) {
@@ -131,9 +157,9 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
           }
           const uint32_t sa = smem_base + s * STAGE_BYTES;
           mbar_arrive_expect_tx(full_bar(s), STAGE_BYTES);
-          tma_load_2d(sa, &tmA, full_bar(s), kb * BK, m0);
-          tma_load_2d(sa + A_BYTES, &tmB, full_bar(s), kb * BK, n0);
-          tma_load_2d(sa + A_BYTES + B_BYTES / 2, &tmB, full_bar(s), kb * BK, n0 + p.b_row1);
+          tma_load_2d(sa, mA, full_bar(s), kb * BK, m0);
+          tma_load_2d(sa + A_BYTES, mB, full_bar(s), kb * BK, n0);
+          tma_load_2d(sa + A_BYTES + B_BYTES / 2, mB, full_bar(s), kb * BK, n0 + p.b_row1);
         }
       }
       if (!ok) {
@@ -151,12 +177,17 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       int it = 0, tcount = 0;
       bool ok = true;
       for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x, ++tcount) {
+        const int second = t >= g.tiles0;
+        const GemmParams& p = g.p[second];
+        const int k_blocks = (p.K + BK - 1) / BK;
+        const int ks = (second ? t - g.tiles0 : t) % p.k_splits;
+        const int kb0 = ks * k_blocks / p.k_splits, kb1 = (ks + 1) * k_blocks / p.k_splits;
         const int b = tcount & 1;
         const uint32_t bph = (tcount >> 1) & 1;
         if (!mbar_wait(tempty_bar(b), bph ^ 1, abort_flag, p.status, ST_TIMEOUT_MMA)) break;
         tc_fence_after();
         const uint32_t d_tmem = tmem_base + b * BN;
-        for (int kb = 0; kb < k_blocks; ++kb, ++it) {
+        for (int kb = kb0; kb < kb1; ++kb, ++it) {
           const int s = it % STAGES;
           const uint32_t ph = (it / STAGES) & 1;
           if (!mbar_wait(full_bar(s), ph, abort_flag, p.status, ST_TIMEOUT_MMA)) {
@@ -170,7 +201,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
 #pragma unroll
           for (int k = 0; k < BK / 16; ++k) {
             // advance 32 bytes (16 bf16) along K inside the 128-byte swizzle row: +2 in >>4 units
-            mma_ss(d_tmem, adesc + 2 * k, bdesc + 2 * k, idesc, (kb > 0 || k > 0) ? 1u : 0u);
+            mma_ss(d_tmem, adesc + 2 * k, bdesc + 2 * k, idesc, (kb > kb0 || k > 0) ? 1u : 0u);
           }
           tc_commit(empty_bar(s));
         }
@@ -185,15 +216,43 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     for (int t = blockIdx.x; t < total_tiles; t += gridDim.x, ++tcount) {
       const int b = tcount & 1;
       const uint32_t bph = (tcount >> 1) & 1;
+      const int second = t >= g.tiles0;
+      const GemmParams& p = g.p[second];
+      const int tl = second ? t - g.tiles0 : t;
       int tm, tn;
-      tile_coords(t, p.m_tiles, p.n_tiles, tm, tn);
+      tile_coords(tl / p.k_splits, p.m_tiles, p.n_tiles, tm, tn);
       const int m = tm * BM + row_in_tile;
       if (!mbar_wait(tfull_bar(b), bph, abort_flag, p.status, ST_TIMEOUT_EPI)) break;
       tc_fence_after();
       const uint32_t t_addr = tmem_base + (uint32_t(quad * 32) << 16) + b * BN;
       const bool row_ok = m < p.M;
 
-      if constexpr (EPI == EPI_PLAIN || EPI == EPI_GATED_RESID) {
+      if (EPI != EPI_QKV_ROPE && p.k_splits > 1) {
+        // raw fp32 partial sums; accumulator column c maps to output column col(c)
+        float* dst_row = p.partial + ((long long)(tl % p.k_splits) * p.M + m) * p.N;
+#pragma unroll 1
+        for (int c = 0; c < BN; c += 32) {
+          uint32_t v[32];
+          tmem_ld32(t_addr + c, v);
+          tmem_wait_ld();
+          const int col = (EPI == EPI_SWIGLU) ? (c < 128 ? tn * 128 + c : p.N / 2 + tn * 128 + (c - 128))
+                                              : tn * BN + c;
+          const int col_end = (EPI == EPI_SWIGLU) ? (c < 128 ? p.N / 2 : p.N) : p.N;
+          if (row_ok && col < col_end) {
+            if (col + 32 <= col_end) {
+              float4* d4 = reinterpret_cast<float4*>(dst_row + col);
+#pragma unroll
+              for (int q = 0; q < 8; ++q)
+                d4[q] = make_float4(__uint_as_float(v[q * 4]), __uint_as_float(v[q * 4 + 1]),
+                                    __uint_as_float(v[q * 4 + 2]), __uint_as_float(v[q * 4 + 3]));
+            } else {
+#pragma unroll
+              for (int i = 0; i < 32; ++i)
+                if (col + i < col_end) dst_row[col + i] = __uint_as_float(v[i]);
+            }
+          }
+        }
+      } else if constexpr (EPI == EPI_PLAIN || EPI == EPI_GATED_RESID) {
         const int n0 = tn * BN;
 #pragma unroll 1
         for (int c = 0; c < BN; c += 32) {
@@ -377,6 +436,53 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
   }
 }
 
+// Second pass of split-K: out = epilogue(sum_ks partial[ks]). One thread per 4 output columns.
+__global__ void __launch_bounds__(256)
+splitk_reduce_kernel(const float* __restrict__ partial, int k_splits, int M, int N, int epi, bf16* __restrict__ C,
+                     long long ldc, const bf16* __restrict__ bias, const bf16* __restrict__ R, long long ldr,
+                     const bf16* __restrict__ gate, int rows_per_batch) {
+  const int n_out = epi == EPI_SWIGLU ? N / 2 : N;
+  const int vec_per_row = n_out / 4;
+  const long long total = (long long)M * vec_per_row;
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total;
+       i += (long long)gridDim.x * blockDim.x) {
+    const int m = (int)(i / vec_per_row);
+    const int n = (int)(i - (long long)m * vec_per_row) * 4;
+    float4 a = make_float4(0, 0, 0, 0), u = make_float4(0, 0, 0, 0);
+    for (int ks = 0; ks < k_splits; ++ks) {
+      const float* row = partial + ((long long)ks * M + m) * N;
+      const float4 x = *reinterpret_cast<const float4*>(row + n);
+      a.x += x.x; a.y += x.y; a.z += x.z; a.w += x.w;
+      if (epi == EPI_SWIGLU) {
+        const float4 y = *reinterpret_cast<const float4*>(row + N / 2 + n);
+        u.x += y.x; u.y += y.y; u.z += y.z; u.w += y.w;
+      }
+    }
+    float f[4] = {a.x, a.y, a.z, a.w};
+    if (epi == EPI_SWIGLU) {
+      const float uu[4] = {u.x, u.y, u.z, u.w};
+#pragma unroll
+      for (int e = 0; e < 4; ++e) f[e] = f[e] / (1.f + __expf(-f[e])) * uu[e];
+    } else {
+      if (bias) {
+#pragma unroll
+        for (int e = 0; e < 4; ++e) f[e] += __bfloat162float(bias[n + e]);
+      }
+      if (epi == EPI_GATED_RESID) {
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          const float gg = gate ? __bfloat162float(gate[(long long)(m / rows_per_batch) * N + n + e]) : 1.f;
+          f[e] = __bfloat162float(R[(long long)m * ldr + n + e]) + gg * f[e];
+        }
+      }
+    }
+    uint2 o;
+    o.x = pack_bf16(f[0], f[1]);
+    o.y = pack_bf16(f[2], f[3]);
+    *reinterpret_cast<uint2*>(C + (long long)m * ldc + n) = o;
+  }
+}
+
 }  // namespace cb
 
 // ====================================================================== host
@@ -451,18 +557,18 @@ static int sm_count() {
 }
 
 template <int EPI>
-static void launch(const CUtensorMap& ta, const CUtensorMap& tb, const cb::GemmParams& p, int grid,
-                   cudaStream_t stream) {
+static void launch(const CUtensorMap* maps, const cb::GemmGroup& g, int grid, cudaStream_t stream) {
   static bool configured = false;
   if (!configured) {
     cudaFuncSetAttribute(cb::gemm_bf16_kernel<EPI>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                          cb::GEMM_SMEM);
     configured = true;
   }
-  cb::gemm_bf16_kernel<EPI><<<grid, cb::GEMM_THREADS, cb::GEMM_SMEM, stream>>>(ta, tb, p);
+  cb::gemm_bf16_kernel<EPI><<<grid, cb::GEMM_THREADS, cb::GEMM_SMEM, stream>>>(maps[0], maps[1], maps[2],
+                                                                               maps[3], g);
 }
 
-void gemm_bf16(const GemmArgs& a, cudaStream_t stream) {
+static void fill_problem(const GemmArgs& a, cb::GemmParams& p, CUtensorMap& ta, CUtensorMap& tb) {
   if (a.K % 8 != 0 || a.lda % 8 != 0 || a.ldb % 8 != 0)
     throw std::runtime_error("gemm_bf16: K and leading dimensions must be multiples of 8");
   if (a.epi == EPI_SWIGLU && (a.N % 2 != 0 || (a.N / 2) % 8 != 0))
@@ -471,17 +577,15 @@ void gemm_bf16(const GemmArgs& a, cudaStream_t stream) {
     throw std::runtime_error("gemm_bf16: QKV epilogue needs N to be a multiple of 128");
   if ((a.epi == EPI_PLAIN || a.epi == EPI_GATED_RESID) && (a.ldc % 8 != 0))
     throw std::runtime_error("gemm_bf16: ldc must be a multiple of 8");
-
   const uint64_t dimsA[2] = {(uint64_t)a.K, (uint64_t)a.M};
   const uint64_t strA[1] = {(uint64_t)a.lda * 2};
   const uint32_t boxA[2] = {cb::BK, cb::BM};
   const uint64_t dimsB[2] = {(uint64_t)a.K, (uint64_t)a.N};
   const uint64_t strB[1] = {(uint64_t)a.ldb * 2};
   const uint32_t boxB[2] = {cb::BK, 128};
-  CUtensorMap ta = cbh::make_tmap_bf16(a.A, 2, dimsA, strA, boxA, true);
-  CUtensorMap tb = cbh::make_tmap_bf16(a.B, 2, dimsB, strB, boxB, true);
-
-  cb::GemmParams p{};
+  ta = cbh::make_tmap_bf16(a.A, 2, dimsA, strA, boxA, true);
+  tb = cbh::make_tmap_bf16(a.B, 2, dimsB, strB, boxB, true);
+  p = cb::GemmParams{};
   p.M = a.M; p.N = a.N; p.K = a.K;
   p.m_tiles = (a.M + cb::BM - 1) / cb::BM;
   if (a.epi == EPI_SWIGLU) {
@@ -502,17 +606,87 @@ void gemm_bf16(const GemmArgs& a, cudaStream_t stream) {
   p.gamma_k = reinterpret_cast<const bf16*>(a.gamma_k);
   p.n_q_heads = a.n_q_heads; p.n_k_heads = a.n_k_heads; p.eps = a.eps;
   p.status = a.status;
-  const int total = p.m_tiles * p.n_tiles;
-  if (total == 0) return;
-  int grid = a.max_ctas > 0 ? a.max_ctas : sm_count();
-  if (grid > total) grid = total;
-  switch (a.epi) {
-    case EPI_PLAIN: launch<EPI_PLAIN>(ta, tb, p, grid, stream); break;
-    case EPI_SWIGLU: launch<EPI_SWIGLU>(ta, tb, p, grid, stream); break;
-    case EPI_GATED_RESID: launch<EPI_GATED_RESID>(ta, tb, p, grid, stream); break;
-    case EPI_QKV_ROPE: launch<EPI_QKV_ROPE>(ta, tb, p, grid, stream); break;
+  p.k_splits = 1;
+  p.partial = nullptr;
+}
+
+int gemm_pick_k_splits(int M, int N, int K, int epi) {
+  if (epi == EPI_QKV_ROPE) return 1;
+  const int m_tiles = (M + cb::BM - 1) / cb::BM;
+  const int n_tiles = epi == EPI_SWIGLU ? (N / 2 + 127) / 128 : (N + cb::BN - 1) / cb::BN;
+  const int tiles = m_tiles * n_tiles;
+  const int k_blocks = (K + cb::BK - 1) / cb::BK;
+  const int sms = sm_count();
+  if (tiles * 2 > sms || k_blocks < 8 || N % 8 != 0) return 1;
+  int ks = (sms + tiles - 1) / tiles;
+  if (ks > k_blocks / 4) ks = k_blocks / 4;  // at least 4 k-blocks (256 columns of K) per split
+  if (ks > 32) ks = 32;
+  return ks < 2 ? 1 : ks;
+}
+
+// One launch for one or two problems that share the epilogue kind.
+void gemm_bf16_grouped(const GemmArgs* args, int n, cudaStream_t stream) {
+  if (n < 1 || n > 2) throw std::runtime_error("gemm_bf16_grouped: 1 or 2 problems per launch");
+  if (n == 2 && args[0].epi != args[1].epi)
+    throw std::runtime_error("gemm_bf16_grouped: both problems must use the same epilogue");
+  cb::GemmGroup g{};
+  CUtensorMap maps[4];
+  fill_problem(args[0], g.p[0], maps[0], maps[1]);
+  g.tiles0 = g.p[0].m_tiles * g.p[0].n_tiles;
+  g.total = g.tiles0;
+  if (n == 2 && args[1].M > 0) {
+    fill_problem(args[1], g.p[1], maps[2], maps[3]);
+    g.total += g.p[1].m_tiles * g.p[1].n_tiles;
+  } else {
+    maps[2] = maps[0];
+    maps[3] = maps[1];
+  }
+  if (g.total == 0) return;
+  int grid = args[0].max_ctas > 0 ? args[0].max_ctas : sm_count();
+  if (grid > g.total) grid = g.total;
+  switch (args[0].epi) {
+    case EPI_PLAIN: launch<EPI_PLAIN>(maps, g, grid, stream); break;
+    case EPI_SWIGLU: launch<EPI_SWIGLU>(maps, g, grid, stream); break;
+    case EPI_GATED_RESID: launch<EPI_GATED_RESID>(maps, g, grid, stream); break;
+    case EPI_QKV_ROPE: launch<EPI_QKV_ROPE>(maps, g, grid, stream); break;
     default: throw std::runtime_error("gemm_bf16: unknown epilogue");
   }
+}
+
+void gemm_bf16(const GemmArgs& a, cudaStream_t stream) {
+  if (a.M <= 0 || a.N <= 0) return;
+  if (a.k_splits <= 1) {
+    gemm_bf16_grouped(&a, 1, stream);
+    return;
+  }
+  // split-K: pass 1 writes fp32 partials, pass 2 reduces and applies the epilogue
+  if (a.epi == EPI_QKV_ROPE) throw std::runtime_error("gemm_bf16: split-K does not support the QKV epilogue");
+  if (!a.partial || a.N % 8 != 0) throw std::runtime_error("gemm_bf16: split-K needs a partial buffer and N % 8 == 0");
+  cb::GemmGroup g{};
+  CUtensorMap maps[4];
+  fill_problem(a, g.p[0], maps[0], maps[1]);
+  const int k_blocks = (a.K + cb::BK - 1) / cb::BK;
+  const int ks = a.k_splits < k_blocks ? a.k_splits : k_blocks;
+  g.p[0].k_splits = ks;
+  g.p[0].partial = a.partial;
+  g.tiles0 = g.total = g.p[0].m_tiles * g.p[0].n_tiles * ks;
+  maps[2] = maps[0];
+  maps[3] = maps[1];
+  int grid = sm_count();
+  if (grid > g.total) grid = g.total;
+  switch (a.epi) {
+    case EPI_PLAIN: launch<EPI_PLAIN>(maps, g, grid, stream); break;
+    case EPI_SWIGLU: launch<EPI_SWIGLU>(maps, g, grid, stream); break;
+    case EPI_GATED_RESID: launch<EPI_GATED_RESID>(maps, g, grid, stream); break;
+    default: throw std::runtime_error("gemm_bf16: unknown epilogue");
+  }
+  const int n_out = a.epi == EPI_SWIGLU ? a.N / 2 : a.N;
+  const long long vecs = (long long)a.M * (n_out / 4);
+  const int blocks = (int)std::min<long long>((vecs + 255) / 256, 148 * 8);
+  cb::splitk_reduce_kernel<<<blocks, 256, 0, stream>>>(
+      a.partial, ks, a.M, a.N, a.epi, reinterpret_cast<bf16*>(a.C), a.ldc,
+      reinterpret_cast<const bf16*>(a.bias), reinterpret_cast<const bf16*>(a.R), a.ldr,
+      reinterpret_cast<const bf16*>(a.gate), a.rows_per_batch > 0 ? a.rows_per_batch : (a.M > 0 ? a.M : 1));
 }
 
 }  // namespace cosmos

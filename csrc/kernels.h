@@ -42,8 +42,15 @@ struct GemmArgs {
   float eps = 1e-6f;
   int* status = nullptr;  // device status word (0 = ok)
   int max_ctas = 0;       // 0 = one CTA per SM
+  int k_splits = 1;       // > 1: split-K with fp32 partials in `partial` ([k_splits, M, N] floats)
+  float* partial = nullptr;
 };
+// Split count that fills the machine for a skinny problem (1 = do not split).
+int gemm_pick_k_splits(int M, int N, int K, int epi);
 void gemm_bf16(const GemmArgs& a, cudaStream_t stream);
+// K12: one persistent launch over one or two problems with the same epilogue kind (per-modality
+// weight routing: tokens are already grouped into an AR segment and a DM segment).
+void gemm_bf16_grouped(const GemmArgs* args, int n, cudaStream_t stream);
 
 struct AttnArgs {
   // Q [B, Sq, Hq, 128], K/V [B, Skv, Hkv, 128], O [B, Sq, Hq, 128]; element strides given.
@@ -66,7 +73,9 @@ struct AttnArgs {
   const long long* dest_ptr = nullptr;
   int rows_per_dest = 0;
   int* status = nullptr;
-  int exp_emulation = 4;  // every k-th softmax element uses the polynomial exp2 (0 = none; 2, 3, 4)
+  // Every k-th softmax element computes exp2 with a polynomial on the FMA pipe (2, 3, 4; 0 = none).
+  // Measured on B200 the softmax warps are latency/issue bound rather than MUFU bound, so 0 is fastest.
+  int exp_emulation = 0;
 };
 void flash_attn_fwd(const AttnArgs& a, cudaStream_t stream);
 
@@ -108,16 +117,20 @@ struct PagedDecodeArgs {
 int paged_decode_pick_splits(int B, int Hkv, int max_len);
 size_t paged_decode_scratch_bytes(int B, int Hq, int n_splits);
 void paged_decode(const PagedDecodeArgs& a, cudaStream_t s);
+// Scatters new K/V rows [N, Hkv, 128] into the paged caches at flat slots (page * page_size + offset).
+void kv_cache_write(const void* k, const void* v, const long long* slots, void* k_cache, void* v_cache,
+                    long long n_rows, int Hkv, cudaStream_t s);
 
 // ---- communication kernels over peer mappings (comm.cu) ----
 // pads_dev / bufs_dev / grads_dev / srcs_dev: device arrays with one address per rank of the group.
 // Signal pads are int32 arrays laid out as [slot][64]; epochs must grow monotonically per slot.
 void comm_barrier(const long long* pads_dev, int rank, int world, int slot, int epoch, int* status,
                   cudaStream_t s);
-// Uses slots [slot, slot + 8) and epochs (epoch, epoch + 1).
+// Uses slots [slot, slot + 8) and epochs (epoch, epoch + 1); with `counters` (device ints, one per
+// slot) the kernel tracks the epochs itself and `epoch` is ignored (CUDA-graph friendly).
 void allreduce_oneshot(const long long* bufs_dev, const long long* pads_dev, void* out,
-                       long long n_elems, int rank, int world, int slot, int epoch, int* status,
-                       cudaStream_t s);
+                       long long n_elems, int rank, int world, int slot, int epoch, int* counters,
+                       int* status, cudaStream_t s);
 void rs_adamw(const long long* grads_dev, int world, long long shard_off, long long n, float* master,
               float* m, float* v, void* param_shard, float grad_scale, float lr, float b1, float b2,
               float eps, float wd, int step, float* sq_out, float* reduced_out, cudaStream_t s);

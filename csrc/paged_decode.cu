@@ -242,6 +242,34 @@ void paged_decode(const PagedDecodeArgs& a, cudaStream_t s) {
 
 }  // namespace cosmos
 
+namespace cb {
+__global__ void __launch_bounds__(256)
+kv_cache_write_kernel(const uint4* __restrict__ k, const uint4* __restrict__ v, const long long* __restrict__ slots,
+                      uint4* __restrict__ kc, uint4* __restrict__ vc, long long n_rows, int vec_per_row) {
+  const long long total = n_rows * vec_per_row;
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total;
+       i += (long long)gridDim.x * blockDim.x) {
+    const long long r = i / vec_per_row;
+    const long long c = i - r * vec_per_row;
+    const long long dst = slots[r] * vec_per_row + c;
+    kc[dst] = k[i];
+    vc[dst] = v[i];
+  }
+}
+}  // namespace cb
+
+namespace cosmos {
+void kv_cache_write(const void* k, const void* v, const long long* slots, void* k_cache, void* v_cache,
+                    long long n_rows, int Hkv, cudaStream_t s) {
+  if (n_rows <= 0) return;
+  const int vec_per_row = Hkv * 128 / 8;
+  const long long total = n_rows * vec_per_row;
+  const int blocks = (int)std::min<long long>((total + 255) / 256, 148 * 8);
+  cb::kv_cache_write_kernel<<<blocks, 256, 0, s>>>((const uint4*)k, (const uint4*)v, slots, (uint4*)k_cache,
+                                                  (uint4*)v_cache, n_rows, vec_per_row);
+}
+}  // namespace cosmos
+
 // ====================================================================== allocation-free entry point
 // Declared and documented in paged_decode_noalloc.h (no counterpart in the reference).
 #include <cstdio>

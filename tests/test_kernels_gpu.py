@@ -265,3 +265,38 @@ def test_paged_decode(b, hq, hkv, page, lens, splits):
     got = ops.paged_decode(q, kc, vc, perm, sl, n_splits=splits, max_len=max(lens))
     want = ops.paged_decode_ref(q.float(), kc.float(), vc.float(), perm, sl)
     _close(got, want, 2e-2, 2e-2, "paged decode")
+
+
+@pytest.mark.parametrize("epi", [ops.EPI_PLAIN, ops.EPI_SWIGLU, ops.EPI_GATED_RESID])
+def test_gemm_grouped_two_segments(epi):
+    """MoT routing: an AR segment and a DM segment with their own weights in one launch."""
+    torch.manual_seed(17)
+    k, n = 256, 512
+    m0, m1 = 200, 1100
+    a0, a1 = _rand(m0, k), _rand(2, m1 // 2, k)
+    w0, w1 = _rand(n, k, scale=1 / 16), _rand(n, k, scale=1 / 16)
+    n_out = n // 2 if epi == ops.EPI_SWIGLU else n
+    r0 = r1 = g1 = None
+    if epi == ops.EPI_GATED_RESID:
+        r0, r1, g1 = _rand(m0, n_out), _rand(2, m1 // 2, n_out), _rand(2, n_out)
+    c0, c1 = ops.gemm_grouped2(a0, w0, a1, w1, epi, r0, r1, None, g1, m0, m1 // 2)
+    f = lambda t: None if t is None else t.float()  # noqa: E731
+    want0 = ref.gemm(a0.float(), w0.float(), None, epi, f(r0), None, m0)
+    want1 = ref.gemm(a1.float(), w1.float(), None, epi, f(r1), f(g1), m1 // 2)
+    assert c0.shape == want0.shape and c1.shape == want1.shape
+    _close(c0, want0, 3e-2, 2e-2, "grouped segment 0")
+    _close(c1, want1, 3e-2, 2e-2, "grouped segment 1")
+
+
+@pytest.mark.parametrize("m,n,k,epi", [(32, 768, 4096, ops.EPI_PLAIN), (32, 3072, 4096, ops.EPI_SWIGLU),
+                                        (32, 4096, 1536, ops.EPI_GATED_RESID), (7, 512, 1024, ops.EPI_PLAIN),
+                                        (64, 1000, 2048, ops.EPI_PLAIN)])
+def test_gemm_skinny_split_k(m, n, k, epi):
+    """Decode-sized problems take the split-K path (fp32 partials + reduce/epilogue kernel)."""
+    torch.manual_seed(18)
+    a = _rand(m, k)
+    w = _rand(n, k, scale=1 / math.sqrt(k))
+    r = _rand(m, n) if epi == ops.EPI_GATED_RESID else None
+    got = ops.gemm(a, w, None, epi, r, None, m)
+    want = ref.gemm(a.float(), w.float(), None, epi, None if r is None else r.float(), None, m)
+    _close(got, want, 3e-2, 2e-2, f"skinny gemm {m}x{n}x{k} epi {epi}")
