@@ -119,7 +119,11 @@ def gemm(a, w, bias=None, epi: int = EPI_PLAIN, resid=None, gate=None, rows_per_
     """a [.., K] @ w[N, K]^T with a fused epilogue (see csrc/gemm_tcgen05.cu)."""
     if _use_cuda(a, w, bias, resid, gate):
         return _k().gemm(a, w, bias, epi, resid, gate, rows_per_batch, out)
-    r = ref.gemm(a, w, bias, epi, resid, gate, rows_per_batch)
+    if a.is_cuda and a.dtype != torch.float32:
+        from . import diff
+        r = diff.gemm(a, w, bias, epi, resid, gate, rows_per_batch)
+    else:
+        r = ref.gemm(a, w, bias, epi, resid, gate, rows_per_batch)
     if out is not None:
         out.copy_(r.reshape(out.shape))
         return out
@@ -162,7 +166,11 @@ def attention(q, k, v, scale: Optional[float] = None, mask: int = MASK_FULL, n_a
         o, lse = _k().attn_fwd(q, k, v, scale, mask, n_ar, return_lse, dest_ptr, rows_per_dest, out)
         return o, (lse if return_lse else None)
     assert dest_ptr is None, "routed epilogue is CUDA-only"
-    o, lse = ref.attention(q, k, v, scale, mask, n_ar, return_lse)
+    if q.is_cuda and q.dtype != torch.float32 and _grad_needed(q, k, v):
+        from . import diff
+        o, lse = diff.attention(q, k, v, scale, mask, n_ar, return_lse)
+    else:
+        o, lse = ref.attention(q, k, v, scale, mask, n_ar, return_lse)
     if out is not None:
         out.copy_(o)
         o = out

@@ -98,7 +98,7 @@ class Cosmos3OmniPipeline:
     def from_pretrained(cls, name_or_path: str, torch_dtype=torch.bfloat16, device_map: Optional[str] = None,
                         safety_checker=None, enable_safety_checker: bool = True, seed: int = 0,
                         config_overrides: Optional[dict] = None, towers: Sequence[str] = ("ar", "dm"),
-                        vae_widths: Sequence[int] = (32, 64, 128, 128), engine_kwargs: Optional[dict] = None):
+                        vae_widths: Sequence[int] = (64, 128, 256, 256), engine_kwargs: Optional[dict] = None):
         device = "cpu"
         if device_map in ("cuda", "auto") and torch.cuda.is_available():
             device = f"cuda:{torch.cuda.current_device()}"
@@ -264,6 +264,19 @@ class Cosmos3OmniPipeline:
         torch.cuda.current_stream().synchronize() if self.device.type == "cuda" else None
         return out_host
 
+    def _cl_decoder(self):
+        """The sm_100a tokenizer decoder when the VAE is on CUDA in bf16 with 64-multiple widths."""
+        if getattr(self, "_cl", None) is not None:
+            return self._cl
+        p0 = next(self.vae.parameters())
+        widths_ok = all(m.weight.shape[0] % 64 == 0 for m in [self.vae.dec_in] + [u.conv for u in self.vae.dec_up])
+        if p0.is_cuda and p0.dtype == torch.bfloat16 and widths_ok and ops.load_extension() and \
+                self.vae.dec_out.weight.shape[1] == 64:
+            from .models.vae_cuda import CLDecoder
+            self._cl = CLDecoder(self.vae)
+            return self._cl
+        return None
+
     def gather_tokens(self, tokens: torch.Tensor, st: GenState) -> torch.Tensor:
         """All-gathers context-parallel token shards into the full sequence (no-op without cp)."""
         ctx = self.engine.ctx
@@ -282,8 +295,13 @@ class Cosmos3OmniPipeline:
         tokens = self.gather_tokens(tokens, st)
         n_video = st.n_video if not st.total_tokens or st.total_tokens == st.pos.shape[1] else st.total_tokens
         z = unpatchify(tokens[:, :n_video, :cfg.patch_dim], cfg, st.grid).to(vdt)
-        video = self.vae.decode(z, chunk_latents=chunk_latents if st.grid[0] > (chunk_latents or 0) else None)
-        frames = CausalVideoVAE.to_uint8(video)[0].cpu().numpy()
+        cl = self._cl_decoder()
+        if cl is not None:
+            # tensor-core implicit-GEMM decoder on padded channels-last volumes (2 latent frames per chunk)
+            frames = cl.decode(z, chunk_latents=2)[0].cpu().numpy()
+        else:
+            video = self.vae.decode(z, chunk_latents=chunk_latents if st.grid[0] > (chunk_latents or 0) else None)
+            frames = CausalVideoVAE.to_uint8(video)[0].cpu().numpy()
         sound = None
         if st.n_sound:
             lat = tokens[:, st.n_video:st.n_video + st.n_sound, :cfg.sound_latent_dim]

@@ -108,6 +108,70 @@ Tensor gemm(const Tensor& A_, const Tensor& W, const OptT& bias, int64_t epi, co
   return C.reshape(shape);
 }
 
+// General-major GEMM C[M, N] = op(A) op(B)^T for the backward passes:
+//   a_mn = false: A is [M, K];  a_mn = true: A is stored as [K, M] (read transposed in place)
+//   b_mn = false: B is [N, K];  b_mn = true: B is stored as [K, N]
+// dX = dY W      -> gemm_ex(dY [M, N], W [N, K], false, true)   (contraction over N)
+// dW = dY^T X    -> gemm_ex(dY [M, N], X [M, K], true, true)    (contraction over M)
+Tensor gemm_ex(const Tensor& A, const Tensor& B, bool a_mn, bool b_mn, const OptT& out) {
+  check_bf16_cuda(A, "A"); check_bf16_cuda(B, "B");
+  c10::cuda::CUDAGuard guard(A.device());
+  TORCH_CHECK(A.dim() == 2 && B.dim() == 2 && A.stride(1) == 1 && B.stride(1) == 1, "A and B must be 2-D row-major");
+  const int64_t M = a_mn ? A.size(1) : A.size(0), K = a_mn ? A.size(0) : A.size(1);
+  const int64_t N = b_mn ? B.size(1) : B.size(0), Kb = b_mn ? B.size(0) : B.size(1);
+  TORCH_CHECK(K == Kb, "contraction sizes differ: ", K, " vs ", Kb);
+  TORCH_CHECK(A.stride(0) % 8 == 0 && B.stride(0) % 8 == 0, "row strides must be multiples of 8");
+  Tensor C;
+  if (out.has_value() && out->defined()) {
+    C = *out;
+    check_bf16_cuda(C, "out");
+    TORCH_CHECK(C.dim() == 2 && C.size(0) == M && C.size(1) == N && C.stride(1) == 1 && C.stride(0) % 8 == 0);
+  } else {
+    C = at::empty({M, (N + 7) / 8 * 8}, A.options()).narrow(1, 0, N);
+  }
+  cosmos::GemmArgs g;
+  g.A = A.data_ptr(); g.B = B.data_ptr(); g.C = C.data_ptr();
+  g.M = (int)M; g.N = (int)N; g.K = (int)K;
+  g.lda = A.stride(0); g.ldb = B.stride(0); g.ldc = C.stride(0);
+  g.a_mn = a_mn; g.b_mn = b_mn;
+  g.epi = EPI_PLAIN;
+  g.status = status_tensor(A.get_device()).data_ptr<int>();
+  cosmos::gemm_bf16(g, cur_stream());
+  return C;
+}
+
+// Attention-backward score GEMMs for one head (scores materialised as bf16 [Sq, Skv]):
+//   mode 0: P  = exp(q k^T * scale - lse[:, None]) under the forward mask
+//   mode 1: dS = P * (dO v^T - D[:, None]) * scale        (P passed in `p_in`)
+// a [Sq, 128] (q or dO), b [Skv, 128] (k or v), rowvec fp32 [Sq].
+Tensor attn_bwd_scores(const Tensor& a, const Tensor& b, const Tensor& rowvec, double scale, int64_t mask,
+                       int64_t n_ar, int64_t mode, const OptT& p_in, const OptT& out) {
+  check_bf16_cuda(a, "a"); check_bf16_cuda(b, "b");
+  c10::cuda::CUDAGuard guard(a.device());
+  TORCH_CHECK(a.dim() == 2 && b.dim() == 2 && a.stride(1) == 1 && b.stride(1) == 1 && a.size(1) == b.size(1));
+  TORCH_CHECK(rowvec.is_cuda() && rowvec.scalar_type() == at::kFloat && rowvec.is_contiguous() && rowvec.numel() == a.size(0));
+  const int64_t M = a.size(0), N = b.size(0), K = a.size(1);
+  const int64_t ld = (N + 7) / 8 * 8;
+  Tensor C = out.has_value() && out->defined() ? *out : at::empty({M, ld}, a.options()).narrow(1, 0, N);
+  TORCH_CHECK(C.size(0) == M && C.size(1) == N && C.stride(1) == 1 && C.stride(0) % 8 == 0);
+  cosmos::GemmArgs g;
+  g.A = a.data_ptr(); g.B = b.data_ptr(); g.C = C.data_ptr();
+  g.M = (int)M; g.N = (int)N; g.K = (int)K;
+  g.lda = a.stride(0); g.ldb = b.stride(0); g.ldc = C.stride(0);
+  g.rowvec = rowvec.data_ptr<float>(); g.attn_scale = (float)scale; g.attn_mask = (int)mask; g.attn_n_ar = (int)n_ar;
+  if (mode == 0) {
+    g.epi = EPI_ATTN_P;
+  } else {
+    g.epi = EPI_ATTN_DS;
+    TORCH_CHECK(p_in.has_value() && p_in->defined() && p_in->size(0) == M && p_in->size(1) == N && p_in->stride(1) == 1);
+    check_bf16_cuda(*p_in, "p_in");
+    g.R = p_in->data_ptr(); g.ldr = p_in->stride(0);
+  }
+  g.status = status_tensor(a.get_device()).data_ptr<int>();
+  cosmos::gemm_bf16(g, cur_stream());
+  return C;
+}
+
 // Grouped GEMM over two token segments with their own weights (MoT per-modality routing), one launch.
 // epi in {PLAIN, SWIGLU, GATED_RESID}; returns (C0, C1).
 std::tuple<Tensor, Tensor> gemm_grouped2(const Tensor& A0_, const Tensor& W0, const Tensor& A1_, const Tensor& W1,
@@ -272,7 +336,33 @@ std::tuple<Tensor, Tensor> attn_fwd(const Tensor& q, const Tensor& k, const Tens
   {
     static const int emu = [] { const char* e = std::getenv("COSMOS_ATTN_EXP_EMU"); return e ? std::atoi(e) : 0; }();
     a.exp_emulation = emu;
+    static const int pipe = [] { const char* e = std::getenv("COSMOS_ATTN_PIPELINE"); return e ? std::atoi(e) : 1; }();
+    a.pipeline = pipe;
   }
+  cosmos::flash_attn_fwd(a, cur_stream());
+  return {o, lse};
+}
+
+// attn_fwd with an explicit pipeline generation (1 or 2), for A/B tests
+std::tuple<Tensor, Tensor> attn_fwd_v(const Tensor& q, const Tensor& k, const Tensor& v, double scale, int64_t mask,
+                                      int64_t n_ar, bool return_lse, int64_t pipeline) {
+  check_bf16_cuda(q, "q"); check_bf16_cuda(k, "k"); check_bf16_cuda(v, "v");
+  c10::cuda::CUDAGuard guard(q.device());
+  TORCH_CHECK(q.dim() == 4 && q.size(3) == 128 && q.stride(3) == 1 && k.stride(3) == 1 && v.stride(3) == 1);
+  const int64_t B = q.size(0), Sq = q.size(1), Hq = q.size(2), Skv = k.size(1), Hkv = k.size(2);
+  Tensor o = at::empty({B, Sq, Hq, 128}, q.options());
+  Tensor lse = at::empty({B, Hq, Sq}, q.options().dtype(at::kFloat));
+  cosmos::AttnArgs a;
+  a.lse = return_lse ? lse.data_ptr<float>() : nullptr;
+  a.Q = q.data_ptr(); a.K = k.data_ptr(); a.V = v.data_ptr(); a.O = o.data_ptr();
+  a.B = (int)B; a.Sq = (int)Sq; a.Skv = (int)Skv; a.Hq = (int)Hq; a.Hkv = (int)Hkv;
+  a.q_stride_b = q.stride(0); a.q_stride_s = q.stride(1); a.q_stride_h = q.stride(2);
+  a.k_stride_b = k.stride(0); a.k_stride_s = k.stride(1); a.k_stride_h = k.stride(2);
+  a.v_stride_b = v.stride(0); a.v_stride_s = v.stride(1); a.v_stride_h = v.stride(2);
+  a.o_stride_b = o.stride(0); a.o_stride_s = o.stride(1); a.o_stride_h = o.stride(2);
+  a.scale = (float)scale; a.mask = (int)mask; a.n_ar = (int)n_ar;
+  a.pipeline = (int)pipeline;
+  a.status = status_tensor(q.get_device()).data_ptr<int>();
   cosmos::flash_attn_fwd(a, cur_stream());
   return {o, lse};
 }
@@ -430,6 +520,75 @@ int64_t paged_decode_pick_splits(int64_t B, int64_t Hkv, int64_t max_len) {
   return cosmos::paged_decode_pick_splits((int)B, (int)Hkv, (int)max_len);
 }
 
+// Causal 3x3x3 convolution as an implicit GEMM. x: padded channels-last volume [F, Hp, Wp, C]
+// (C % 64 == 0; F includes `tpad` = 2 leading context frames); w: [Cout, 27 * C]; out: a padded
+// volume [F, Hp, Wp, Cout] whose interior rows are written (border rows are left untouched);
+// resid (optional) has the layout of out and is added.
+void conv3d_cl(const Tensor& x, const Tensor& w, const OptT& bias, const OptT& resid, Tensor out, int64_t tpad) {
+  check_bf16_cuda(x, "x"); check_bf16_cuda(w, "w"); check_bf16_cuda(out, "out");
+  c10::cuda::CUDAGuard guard(x.device());
+  TORCH_CHECK(x.dim() == 4 && x.is_contiguous() && out.dim() == 4 && out.is_contiguous(), "volumes must be contiguous [F, Hp, Wp, C]");
+  const int64_t F = x.size(0), Hp = x.size(1), Wp = x.size(2), C = x.size(3), Cout = out.size(3);
+  TORCH_CHECK(out.size(0) == F && out.size(1) == Hp && out.size(2) == Wp, "out must have the padded shape of x");
+  TORCH_CHECK(w.dim() == 2 && w.is_contiguous() && w.size(0) == Cout && w.size(1) == 27 * C, "w must be [Cout, 27 * C]");
+  TORCH_CHECK(F * Hp * Wp < (1ll << 31), "volume too large for 32-bit row indices; decode in temporal chunks");
+  cosmos::GemmArgs g;
+  g.A = x.data_ptr(); g.B = w.data_ptr(); g.C = out.data_ptr();
+  g.M = (int)(F * Hp * Wp); g.N = (int)Cout; g.K = (int)(27 * C);
+  g.lda = C; g.ldb = 27 * C; g.ldc = Cout;
+  g.epi = EPI_CONV;
+  g.conv_c = (int)C; g.conv_hp = (int)Hp; g.conv_wp = (int)Wp; g.conv_tpad = (int)tpad;
+  if (bias.has_value() && bias->defined()) {
+    check_bf16_cuda(*bias, "bias");
+    TORCH_CHECK(bias->numel() == Cout && bias->is_contiguous());
+    g.bias = bias->data_ptr();
+  }
+  if (resid.has_value() && resid->defined()) {
+    check_bf16_cuda(*resid, "resid");
+    TORCH_CHECK(resid->is_contiguous() && resid->sizes() == out.sizes());
+    g.R = resid->data_ptr(); g.ldr = Cout;
+  }
+  g.status = status_tensor(x.get_device()).data_ptr<int>();
+  cosmos::gemm_bf16(g, cur_stream());
+}
+
+Tensor rmsnorm_silu(const Tensor& x, const Tensor& gamma, double eps) {
+  check_bf16_cuda(x, "x"); check_bf16_cuda(gamma, "gamma");
+  c10::cuda::CUDAGuard guard(x.device());
+  TORCH_CHECK(x.is_contiguous() && gamma.is_contiguous() && gamma.numel() == x.size(-1));
+  Tensor y = at::empty_like(x);
+  cosmos::rmsnorm_silu(x.data_ptr(), gamma.data_ptr(), y.data_ptr(), x.numel() / x.size(-1), (int)x.size(-1),
+                       (float)eps, cur_stream());
+  return y;
+}
+
+void upsample_cl(const Tensor& src, Tensor dst, int64_t tpad, bool temporal, bool first_chunk) {
+  check_bf16_cuda(src, "src"); check_bf16_cuda(dst, "dst");
+  c10::cuda::CUDAGuard guard(src.device());
+  TORCH_CHECK(src.dim() == 4 && dst.dim() == 4 && src.is_contiguous() && dst.is_contiguous() && src.size(3) == dst.size(3));
+  const int64_t hs = src.size(1) - 2, ws = src.size(2) - 2;
+  TORCH_CHECK(dst.size(1) == 2 * hs + 2 && dst.size(2) == 2 * ws + 2, "dst must be the x2 padded volume");
+  const int64_t t_src = src.size(0) - tpad, t_dst = dst.size(0) - tpad;
+  const int64_t want = temporal ? (first_chunk ? 2 * t_src - 1 : 2 * t_src) : t_src;
+  TORCH_CHECK(t_dst == want, "dst frame count mismatch");
+  cosmos::upsample_cl(src.data_ptr(), dst.data_ptr(), (int)t_dst, (int)hs, (int)ws, (int)src.size(3), (int)tpad,
+                      temporal ? 1 : 0, first_chunk ? 1 : 0, cur_stream());
+}
+
+// x: padded CL volume [T + 2, H + 2, W + 2, 64]; w [3, 27, 64] fp32; bias [3] fp32 -> uint8 [T, H, W, 3]
+Tensor conv_out_rgb(const Tensor& x, const Tensor& w, const Tensor& bias) {
+  check_bf16_cuda(x, "x");
+  c10::cuda::CUDAGuard guard(x.device());
+  TORCH_CHECK(x.dim() == 4 && x.is_contiguous() && x.size(3) == 64, "x must be [T+2, H+2, W+2, 64]");
+  TORCH_CHECK(w.is_cuda() && w.scalar_type() == at::kFloat && w.is_contiguous() && w.numel() == 3 * 27 * 64);
+  TORCH_CHECK(bias.is_cuda() && bias.scalar_type() == at::kFloat && bias.numel() == 3);
+  const int64_t T = x.size(0) - 2, H = x.size(1) - 2, W = x.size(2) - 2;
+  Tensor out = at::empty({T, H, W, 3}, x.options().dtype(at::kByte));
+  cosmos::conv_out_rgb(x.data_ptr(), w.data_ptr<float>(), bias.data_ptr<float>(), out.data_ptr(), (int)T, (int)H,
+                       (int)W, cur_stream());
+  return out;
+}
+
 const long long* ptr_table(const Tensor& t, const char* name) {
   TORCH_CHECK(t.is_cuda() && t.scalar_type() == at::kLong && t.is_contiguous(), name,
               " must be a contiguous int64 CUDA tensor of addresses");
@@ -505,7 +664,10 @@ TORCH_LIBRARY(cosmos_b200, m) {
   m.def("gemm", &gemm);
   m.def("gemm_qkv_rope", &gemm_qkv_rope);
   m.def("gemm_grouped2", &gemm_grouped2);
+  m.def("gemm_ex", &gemm_ex);
+  m.def("attn_bwd_scores", &attn_bwd_scores);
   m.def("attn_fwd", &attn_fwd);
+  m.def("attn_fwd_v", &attn_fwd_v);
   m.def("rmsnorm", &rmsnorm);
   m.def("adaln_rmsnorm", &adaln_rmsnorm);
   m.def("mrope_", &mrope_);
@@ -513,6 +675,10 @@ TORCH_LIBRARY(cosmos_b200, m) {
   m.def("swiglu", &swiglu);
   m.def("cfg_euler_step_", &cfg_euler_step_);
   m.def("l2_flush_", &l2_flush_);
+  m.def("conv3d_cl", &conv3d_cl);
+  m.def("rmsnorm_silu", &rmsnorm_silu);
+  m.def("upsample_cl", &upsample_cl);
+  m.def("conv_out_rgb", &conv_out_rgb);
   m.def("paged_decode", &paged_decode);
   m.def("paged_decode_pick_splits", &paged_decode_pick_splits);
   m.def("comm_barrier", &comm_barrier);

@@ -26,6 +26,7 @@ __device__ __forceinline__ uint4 pack8(const float (&f)[8]) {
 // MAXV = max number of 8-element vectors a lane holds (d <= 32 * 8 * MAXV).
 // MODE 0: y = norm(x [+ res]) * gamma            (res_out = x + res when given)
 // MODE 1: y = norm(x) * gamma * (1 + scale) + shift
+// MODE 2: y = silu(norm(x) * gamma)
 template <int MAXV, int MODE>
 __global__ void __launch_bounds__(256)
 rmsnorm_kernel(const bf16* __restrict__ x, const bf16* __restrict__ gamma, bf16* __restrict__ y,
@@ -76,6 +77,76 @@ rmsnorm_kernel(const bf16* __restrict__ x, const bf16* __restrict__ gamma, bf16*
         unpack8(scr[vi], sc);
 #pragma unroll
         for (int e = 0; e < 8; ++e) o[e] = o[e] * (1.f + sc[e]) + sh[e];
+      }
+      if (MODE == 2) {
+#pragma unroll
+        for (int e = 0; e < 8; ++e) o[e] = o[e] / (1.f + __expf(-o[e]));
+      }
+      reinterpret_cast<uint4*>(y + row * d)[vi] = pack8(o);
+    }
+  }
+}
+
+// Wide rows (d >= 1024): one CTA per row, VPT 16-byte vectors per thread, so a thread holds few
+// registers and many rows are in flight per SM (the warp-per-row kernel above keeps a whole
+// 8 KB row in one warp's registers, which limits occupancy and reaches under half of HBM speed).
+template <int VPT, int MODE>
+__global__ void __launch_bounds__(256)
+rmsnorm_row_kernel(const bf16* __restrict__ x, const bf16* __restrict__ gamma, bf16* __restrict__ y, int d,
+                   float eps, const bf16* __restrict__ res_in, bf16* __restrict__ res_out,
+                   const bf16* __restrict__ shift, const bf16* __restrict__ scale, int rows_per_batch,
+                   long long mod_stride) {
+  __shared__ float red[8];
+  const long long row = blockIdx.x;
+  const int nvec = d >> 3;
+  const uint4* xr = reinterpret_cast<const uint4*>(x + row * d);
+  const uint4* rr = res_in ? reinterpret_cast<const uint4*>(res_in + row * d) : nullptr;
+  float v[VPT][8];
+  float ss = 0.f;
+#pragma unroll
+  for (int i = 0; i < VPT; ++i) {
+    const int vi = threadIdx.x + i * blockDim.x;
+    if (vi < nvec) {
+      unpack8(xr[vi], v[i]);
+      if (rr) {
+        float r[8];
+        unpack8(rr[vi], r);
+#pragma unroll
+        for (int e = 0; e < 8; ++e) v[i][e] += r[e];
+        if (res_out) reinterpret_cast<uint4*>(res_out + row * d)[vi] = pack8(v[i]);
+      }
+#pragma unroll
+      for (int e = 0; e < 8; ++e) ss += v[i][e] * v[i][e];
+    }
+  }
+  ss = warp_sum(ss);
+  if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = ss;
+  __syncthreads();
+  float tot = 0.f;
+  for (int w = 0; w < (int)(blockDim.x >> 5); ++w) tot += red[w];
+  const float rinv = rsqrtf(tot / (float)d + eps);
+  const uint4* gr = reinterpret_cast<const uint4*>(gamma);
+  const long long b = MODE == 1 ? row / rows_per_batch : 0;
+  const uint4* shr = MODE == 1 ? reinterpret_cast<const uint4*>(shift + b * mod_stride) : nullptr;
+  const uint4* scr = MODE == 1 ? reinterpret_cast<const uint4*>(scale + b * mod_stride) : nullptr;
+#pragma unroll
+  for (int i = 0; i < VPT; ++i) {
+    const int vi = threadIdx.x + i * blockDim.x;
+    if (vi < nvec) {
+      float g[8], o[8];
+      if (gamma) unpack8(gr[vi], g);
+#pragma unroll
+      for (int e = 0; e < 8; ++e) o[e] = v[i][e] * rinv * (gamma ? g[e] : 1.f);
+      if (MODE == 1) {
+        float sh[8], sc[8];
+        unpack8(shr[vi], sh);
+        unpack8(scr[vi], sc);
+#pragma unroll
+        for (int e = 0; e < 8; ++e) o[e] = o[e] * (1.f + sc[e]) + sh[e];
+      }
+      if (MODE == 2) {
+#pragma unroll
+        for (int e = 0; e < 8; ++e) o[e] = o[e] / (1.f + __expf(-o[e]));
       }
       reinterpret_cast<uint4*>(y + row * d)[vi] = pack8(o);
     }
@@ -231,6 +302,22 @@ static void launch_norm(const void* x, const void* gamma, void* y, long long row
                         const void* rin, void* rout, const void* shift, const void* scale,
                         int rows_per_batch, long long mod_stride, cudaStream_t s) {
   if (rows == 0) return;
+  if (d >= 1024) {
+    // one CTA per row, 4 vectors per thread (d = 4096 -> 128 threads)
+    const int nvec = d / 8;
+    int threads = ((nvec + 3) / 4 + 31) / 32 * 32;
+    if (threads > 256) {
+      if (nvec > 256 * 8) throw std::runtime_error("rmsnorm: feature size above 16384 is not supported");
+      cb::rmsnorm_row_kernel<8, MODE><<<(unsigned)rows, 256, 0, s>>>(
+          (const bf16*)x, (const bf16*)gamma, (bf16*)y, d, eps, (const bf16*)rin, (bf16*)rout,
+          (const bf16*)shift, (const bf16*)scale, rows_per_batch, mod_stride);
+    } else {
+      cb::rmsnorm_row_kernel<4, MODE><<<(unsigned)rows, threads, 0, s>>>(
+          (const bf16*)x, (const bf16*)gamma, (bf16*)y, d, eps, (const bf16*)rin, (bf16*)rout,
+          (const bf16*)shift, (const bf16*)scale, rows_per_batch, mod_stride);
+    }
+    return;
+  }
   const int wpb = 8;
   const unsigned grid = (unsigned)((rows + wpb - 1) / wpb);
 #define COSMOS_NORM(MAXV)                                                                        \
@@ -259,6 +346,11 @@ void adaln_rmsnorm(const void* x, const void* gamma, const void* shift, const vo
   if (mod_stride % 8 != 0) throw std::runtime_error("adaln_rmsnorm: modulation stride % 8 != 0");
   launch_norm<1>(x, gamma, y, rows, d, eps, nullptr, nullptr, shift, scale,
                  rows_per_batch > 0 ? rows_per_batch : 1, mod_stride, s);
+}
+
+void rmsnorm_silu(const void* x, const void* gamma, void* y, long long rows, int d, float eps, cudaStream_t s) {
+  check_d(d, "rmsnorm_silu");
+  launch_norm<2>(x, gamma, y, rows, d, eps, nullptr, nullptr, nullptr, nullptr, 1, 0, s);
 }
 
 void mrope_apply(void* x, long long rows, int heads, long long row_stride, const float* cos_t,

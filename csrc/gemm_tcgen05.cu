@@ -57,6 +57,16 @@ struct GemmParams {
   // them and applies the epilogue.
   int k_splits;
   float* partial;
+  const float* rowvec;   // EPI_ATTN_P: lse[M]; EPI_ATTN_DS: D[M]
+  float attn_scale;
+  int attn_mask, attn_n_ar;
+  // operand majors: 0 = K-major ([rows, K] storage), 1 = MN-major ([K, rows] storage, i.e. the
+  // transposed operand is read in place; used by the backward GEMMs dX = dY W and dW = dY^T X)
+  int a_mn, b_mn;
+  // implicit-GEMM convolution (EPI_CONV)
+  int conv_cblocks;      // input channels / 64
+  int conv_hp, conv_wp, conv_tpad;
+  int conv_shift[27];    // row offset of each filter tap in the flattened padded volume
 };
 
 // Up to two independent problems served by one persistent launch (grouped GEMM): tiles
@@ -157,9 +167,24 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
           }
           const uint32_t sa = smem_base + s * STAGE_BYTES;
           mbar_arrive_expect_tx(full_bar(s), STAGE_BYTES);
-          tma_load_2d(sa, mA, full_bar(s), kb * BK, m0);
-          tma_load_2d(sa + A_BYTES, mB, full_bar(s), kb * BK, n0);
-          tma_load_2d(sa + A_BYTES + B_BYTES / 2, mB, full_bar(s), kb * BK, n0 + p.b_row1);
+          if constexpr (EPI == EPI_CONV) {
+            const int tap = kb / p.conv_cblocks;
+            tma_load_2d(sa, mA, full_bar(s), (kb - tap * p.conv_cblocks) * BK, m0 + p.conv_shift[tap]);
+          } else if (p.a_mn) {
+            tma_load_2d(sa, mA, full_bar(s), m0, kb * BK);
+            tma_load_2d(sa + A_BYTES / 2, mA, full_bar(s), m0 + 64, kb * BK);
+          } else {
+            tma_load_2d(sa, mA, full_bar(s), kb * BK, m0);
+          }
+          if (p.b_mn) {
+#pragma unroll
+            for (int h = 0; h < 4; ++h)
+              tma_load_2d(sa + A_BYTES + h * (B_BYTES / 4), mB, full_bar(s),
+                          n0 + (h & 1) * 64 + (h >> 1) * p.b_row1, kb * BK);
+          } else {
+            tma_load_2d(sa + A_BYTES, mB, full_bar(s), kb * BK, n0);
+            tma_load_2d(sa + A_BYTES + B_BYTES / 2, mB, full_bar(s), kb * BK, n0 + p.b_row1);
+          }
         }
       }
       if (!ok) {
@@ -173,7 +198,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
   } else if (warp == 1) {
     if (lane == 0) {
       // ---------------- MMA issuer
-      constexpr uint32_t idesc = make_idesc_bf16(BM, BN, 0, 0);
+      // (instruction descriptor is built per tile: the operand majors are per-problem)
       int it = 0, tcount = 0;
       bool ok = true;
       for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x, ++tcount) {
@@ -196,12 +221,17 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
           }
           tc_fence_after();
           const uint32_t sa = smem_base + s * STAGE_BYTES;
-          const uint64_t adesc = make_smem_desc_sw128(sa, 16, 1024);
-          const uint64_t bdesc = make_smem_desc_sw128(sa + A_BYTES, 16, 1024);
+          // K-major: 128-byte rows along K, +32 B per k-step. MN-major: 64-element chunks along M/N
+          // 8 KB apart (LBO), k advances by rows of 128 B, +2048 B per k-step of 16.
+          const uint64_t adesc = p.a_mn ? make_smem_desc_sw128(sa, 8192, 1024) : make_smem_desc_sw128(sa, 16, 1024);
+          const uint64_t bdesc = p.b_mn ? make_smem_desc_sw128(sa + A_BYTES, 8192, 1024)
+                                        : make_smem_desc_sw128(sa + A_BYTES, 16, 1024);
+          const uint32_t a_step = p.a_mn ? 128u : 2u, b_step = p.b_mn ? 128u : 2u;
+          const uint32_t idesc = make_idesc_bf16(BM, BN, p.a_mn, p.b_mn);
 #pragma unroll
           for (int k = 0; k < BK / 16; ++k) {
             // advance 32 bytes (16 bf16) along K inside the 128-byte swizzle row: +2 in >>4 units
-            mma_ss(d_tmem, adesc + 2 * k, bdesc + 2 * k, idesc, (kb > kb0 || k > 0) ? 1u : 0u);
+            mma_ss(d_tmem, adesc + a_step * k, bdesc + b_step * k, idesc, (kb > kb0 || k > 0) ? 1u : 0u);
           }
           tc_commit(empty_bar(s));
         }
@@ -227,7 +257,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       const uint32_t t_addr = tmem_base + (uint32_t(quad * 32) << 16) + b * BN;
       const bool row_ok = m < p.M;
 
-      if (EPI != EPI_QKV_ROPE && p.k_splits > 1) {
+      if ((EPI == EPI_PLAIN || EPI == EPI_SWIGLU || EPI == EPI_GATED_RESID) && p.k_splits > 1) {
         // raw fp32 partial sums; accumulator column c maps to output column col(c)
         float* dst_row = p.partial + ((long long)(tl % p.k_splits) * p.M + m) * p.N;
 #pragma unroll 1
@@ -348,6 +378,115 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
               }
             } else {
               for (int i = 0; i < 32 && n + i < n_out; ++i) dst[i] = __float2bfloat16(f[i]);
+            }
+          }
+        }
+      } else if constexpr (EPI == EPI_ATTN_P || EPI == EPI_ATTN_DS) {
+        const int n0 = tn * BN;
+        const float rv = row_ok ? p.rowvec[m] : 0.f;
+        int lim = p.N;
+        if (p.attn_mask == MASK_CAUSAL) lim = min(p.N, m + 1 + (p.N - p.M));
+        if (p.attn_mask == MASK_MOT) lim = m < p.attn_n_ar ? m + 1 : p.N;
+        const float sl2 = p.attn_scale * 1.4426950408889634f;
+        const float rv2 = rv * 1.4426950408889634f;
+#pragma unroll 1
+        for (int c = 0; c < BN; c += 32) {
+          const int n = n0 + c;
+          if (n >= p.N) break;
+          uint32_t v[32];
+          tmem_ld32(t_addr + c, v);
+          tmem_wait_ld();
+          if (row_ok) {
+            float f[32];
+            const bool full32 = (n + 32 <= p.N);
+            if constexpr (EPI == EPI_ATTN_P) {
+#pragma unroll
+              for (int i = 0; i < 32; ++i)
+                f[i] = (n + i < lim) ? exp2f(fmaf(__uint_as_float(v[i]), sl2, -rv2)) : 0.f;
+            } else {
+              const bf16* pr = p.R + (long long)m * p.ldr + n;
+              if (full32) {
+                const uint4* r4 = reinterpret_cast<const uint4*>(pr);
+#pragma unroll
+                for (int q = 0; q < 4; ++q) {
+                  const uint4 rr = r4[q];
+                  const uint32_t ru[4] = {rr.x, rr.y, rr.z, rr.w};
+#pragma unroll
+                  for (int e = 0; e < 4; ++e) {
+                    f[q * 8 + 2 * e] = bf16lo(ru[e]) * (__uint_as_float(v[q * 8 + 2 * e]) - rv) * p.attn_scale;
+                    f[q * 8 + 2 * e + 1] = bf16hi(ru[e]) * (__uint_as_float(v[q * 8 + 2 * e + 1]) - rv) * p.attn_scale;
+                  }
+                }
+              } else {
+#pragma unroll
+                for (int i = 0; i < 32; ++i)
+                  f[i] = (n + i < p.N) ? __bfloat162float(pr[i]) * (__uint_as_float(v[i]) - rv) * p.attn_scale : 0.f;
+              }
+            }
+            bf16* dst = p.C + (long long)m * p.ldc + n;
+            if (full32) {
+              uint4* d4 = reinterpret_cast<uint4*>(dst);
+#pragma unroll
+              for (int q = 0; q < 4; ++q) {
+                uint4 o;
+                o.x = pack_bf16(f[q * 8 + 0], f[q * 8 + 1]);
+                o.y = pack_bf16(f[q * 8 + 2], f[q * 8 + 3]);
+                o.z = pack_bf16(f[q * 8 + 4], f[q * 8 + 5]);
+                o.w = pack_bf16(f[q * 8 + 6], f[q * 8 + 7]);
+                d4[q] = o;
+              }
+            } else {
+#pragma unroll
+              for (int i = 0; i < 32; ++i)
+                if (n + i < p.N) dst[i] = __float2bfloat16(f[i]);
+            }
+          }
+        }
+      } else if constexpr (EPI == EPI_CONV) {
+        const int plane = p.conv_hp * p.conv_wp;
+        const int frame = m / plane;
+        const int rem = m - frame * plane;
+        const int hh = rem / p.conv_wp, ww = rem - hh * p.conv_wp;
+        const bool interior = row_ok && frame >= p.conv_tpad && hh >= 1 && hh <= p.conv_hp - 2 && ww >= 1 &&
+                              ww <= p.conv_wp - 2;
+        const int n0 = tn * BN;
+#pragma unroll 1
+        for (int c = 0; c < BN; c += 32) {
+          const int n = n0 + c;
+          if (n >= p.N) break;  // uniform across the warp
+          uint32_t v[32];
+          tmem_ld32(t_addr + c, v);
+          tmem_wait_ld();
+          if (interior) {
+            float f[32];
+#pragma unroll
+            for (int i = 0; i < 32; ++i) f[i] = __uint_as_float(v[i]);
+            if (p.bias) {
+#pragma unroll
+              for (int i = 0; i < 32; ++i) f[i] += __bfloat162float(p.bias[n + i]);
+            }
+            if (p.R) {
+              const uint4* r4 = reinterpret_cast<const uint4*>(p.R + (long long)m * p.ldr + n);
+#pragma unroll
+              for (int q = 0; q < 4; ++q) {
+                const uint4 rv = r4[q];
+                const uint32_t ru[4] = {rv.x, rv.y, rv.z, rv.w};
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                  f[q * 8 + e * 2] += bf16lo(ru[e]);
+                  f[q * 8 + e * 2 + 1] += bf16hi(ru[e]);
+                }
+              }
+            }
+            uint4* d4 = reinterpret_cast<uint4*>(p.C + (long long)m * p.ldc + n);
+#pragma unroll
+            for (int q = 0; q < 4; ++q) {
+              uint4 o;
+              o.x = pack_bf16(f[q * 8 + 0], f[q * 8 + 1]);
+              o.y = pack_bf16(f[q * 8 + 2], f[q * 8 + 3]);
+              o.z = pack_bf16(f[q * 8 + 4], f[q * 8 + 5]);
+              o.w = pack_bf16(f[q * 8 + 6], f[q * 8 + 7]);
+              d4[q] = o;
             }
           }
         }
@@ -518,6 +657,16 @@ CUtensorMap make_tmap_bf16(const void* base, int rank, const uint64_t* dims,
     es[i] = 1;
     if (i + 1 < rank) gstr[i] = strides_bytes[i];
   }
+  // The driver-API encode needs a current context in the calling thread; autograd's backward
+  // threads may not have one bound yet, so bind the runtime's primary context once per thread.
+  static thread_local bool ctx_bound = false;
+  if (!ctx_bound) {
+    int dev = 0;
+    cudaGetDevice(&dev);
+    cudaSetDevice(dev);
+    cudaFree(nullptr);
+    ctx_bound = true;
+  }
   if ((reinterpret_cast<uintptr_t>(base) & 15) != 0)
     throw std::runtime_error("TMA base address must be 16-byte aligned");
   for (int i = 0; i + 1 < rank; ++i)
@@ -569,23 +718,49 @@ static void launch(const CUtensorMap* maps, const cb::GemmGroup& g, int grid, cu
 }
 
 static void fill_problem(const GemmArgs& a, cb::GemmParams& p, CUtensorMap& ta, CUtensorMap& tb) {
-  if (a.K % 8 != 0 || a.lda % 8 != 0 || a.ldb % 8 != 0)
+  if ((!a.a_mn && a.K % 8 != 0) || a.lda % 8 != 0 || a.ldb % 8 != 0)
     throw std::runtime_error("gemm_bf16: K and leading dimensions must be multiples of 8");
   if (a.epi == EPI_SWIGLU && (a.N % 2 != 0 || (a.N / 2) % 8 != 0))
     throw std::runtime_error("gemm_bf16: SwiGLU epilogue needs N/2 to be a multiple of 8");
   if (a.epi == EPI_QKV_ROPE && a.N % 128 != 0)
     throw std::runtime_error("gemm_bf16: QKV epilogue needs N to be a multiple of 128");
-  if ((a.epi == EPI_PLAIN || a.epi == EPI_GATED_RESID) && (a.ldc % 8 != 0))
+  if ((a.epi == EPI_PLAIN || a.epi == EPI_GATED_RESID || a.epi == EPI_CONV) && (a.ldc % 8 != 0))
     throw std::runtime_error("gemm_bf16: ldc must be a multiple of 8");
-  const uint64_t dimsA[2] = {(uint64_t)a.K, (uint64_t)a.M};
+  if (a.epi == EPI_CONV) {
+    if (a.conv_c <= 0 || a.conv_c % 64 != 0 || a.K != 27 * a.conv_c || a.N % 32 != 0 || a.conv_hp < 3 ||
+        a.conv_wp < 3 || a.ldc % 8 != 0)
+      throw std::runtime_error("gemm_bf16: conv needs C % 64 == 0, K == 27 * C, Cout % 32 == 0 and a padded volume");
+  }
+  // for the convolution the A matrix is the [rows, C] volume; the K loop revisits it once per tap
+  const uint64_t dimsA[2] = {(uint64_t)(a.epi == EPI_CONV ? a.conv_c : a.K), (uint64_t)a.M};
   const uint64_t strA[1] = {(uint64_t)a.lda * 2};
   const uint32_t boxA[2] = {cb::BK, cb::BM};
   const uint64_t dimsB[2] = {(uint64_t)a.K, (uint64_t)a.N};
   const uint64_t strB[1] = {(uint64_t)a.ldb * 2};
   const uint32_t boxB[2] = {cb::BK, 128};
-  ta = cbh::make_tmap_bf16(a.A, 2, dimsA, strA, boxA, true);
-  tb = cbh::make_tmap_bf16(a.B, 2, dimsB, strB, boxB, true);
+  if (a.a_mn) {
+    if (a.epi == EPI_CONV) throw std::runtime_error("gemm_bf16: the convolution needs a K-major A");
+    const uint64_t d[2] = {(uint64_t)a.M, (uint64_t)a.K};
+    const uint32_t bx[2] = {64, cb::BK};
+    ta = cbh::make_tmap_bf16(a.A, 2, d, strA, bx, true);
+  } else {
+    ta = cbh::make_tmap_bf16(a.A, 2, dimsA, strA, boxA, true);
+  }
+  if (a.b_mn) {
+    const uint64_t d[2] = {(uint64_t)a.N, (uint64_t)a.K};
+    const uint32_t bx[2] = {64, cb::BK};
+    tb = cbh::make_tmap_bf16(a.B, 2, d, strB, bx, true);
+  } else {
+    tb = cbh::make_tmap_bf16(a.B, 2, dimsB, strB, boxB, true);
+  }
   p = cb::GemmParams{};
+  p.rowvec = a.rowvec; p.attn_scale = a.attn_scale; p.attn_mask = a.attn_mask; p.attn_n_ar = a.attn_n_ar;
+  if ((a.epi == EPI_ATTN_P || a.epi == EPI_ATTN_DS) && (!a.rowvec || a.ldc % 8 != 0))
+    throw std::runtime_error("gemm_bf16: attention-backward epilogues need a row vector and ldc % 8 == 0");
+  if (a.epi == EPI_ATTN_DS && (!a.R || a.ldr % 8 != 0))
+    throw std::runtime_error("gemm_bf16: the dS epilogue needs P as the residual operand");
+  p.a_mn = a.a_mn ? 1 : 0;
+  p.b_mn = a.b_mn ? 1 : 0;
   p.M = a.M; p.N = a.N; p.K = a.K;
   p.m_tiles = (a.M + cb::BM - 1) / cb::BM;
   if (a.epi == EPI_SWIGLU) {
@@ -608,10 +783,19 @@ static void fill_problem(const GemmArgs& a, cb::GemmParams& p, CUtensorMap& ta, 
   p.status = a.status;
   p.k_splits = 1;
   p.partial = nullptr;
+  if (a.epi == EPI_CONV) {
+    p.conv_cblocks = a.conv_c / 64;
+    p.conv_hp = a.conv_hp; p.conv_wp = a.conv_wp; p.conv_tpad = a.conv_tpad;
+    int tap = 0;
+    for (int dt = 0; dt < 3; ++dt)
+      for (int dh = 0; dh < 3; ++dh)
+        for (int dw = 0; dw < 3; ++dw)
+          p.conv_shift[tap++] = (dt - 2) * a.conv_hp * a.conv_wp + (dh - 1) * a.conv_wp + (dw - 1);
+  }
 }
 
 int gemm_pick_k_splits(int M, int N, int K, int epi) {
-  if (epi == EPI_QKV_ROPE) return 1;
+  if (epi != EPI_PLAIN && epi != EPI_SWIGLU && epi != EPI_GATED_RESID) return 1;
   const int m_tiles = (M + cb::BM - 1) / cb::BM;
   const int n_tiles = epi == EPI_SWIGLU ? (N / 2 + 127) / 128 : (N + cb::BN - 1) / cb::BN;
   const int tiles = m_tiles * n_tiles;
@@ -649,6 +833,9 @@ void gemm_bf16_grouped(const GemmArgs* args, int n, cudaStream_t stream) {
     case EPI_SWIGLU: launch<EPI_SWIGLU>(maps, g, grid, stream); break;
     case EPI_GATED_RESID: launch<EPI_GATED_RESID>(maps, g, grid, stream); break;
     case EPI_QKV_ROPE: launch<EPI_QKV_ROPE>(maps, g, grid, stream); break;
+    case EPI_CONV: launch<EPI_CONV>(maps, g, grid, stream); break;
+    case EPI_ATTN_P: launch<EPI_ATTN_P>(maps, g, grid, stream); break;
+    case EPI_ATTN_DS: launch<EPI_ATTN_DS>(maps, g, grid, stream); break;
     default: throw std::runtime_error("gemm_bf16: unknown epilogue");
   }
 }

@@ -9,6 +9,11 @@ enum GemmEpilogue : int {
   EPI_SWIGLU = 1,
   EPI_GATED_RESID = 2,
   EPI_QKV_ROPE = 3,
+  EPI_CONV = 4,  // implicit-GEMM causal 3x3x3 convolution on a zero-padded channels-last volume
+  // attention backward (scores are materialised per head): C = exp(acc * scale - lse[m]) under the mask
+  EPI_ATTN_P = 5,
+  // C = P[m, n] * (acc - D[m]) * scale, with P passed as the residual operand
+  EPI_ATTN_DS = 6,
 };
 
 enum AttnMask : int {
@@ -42,8 +47,21 @@ struct GemmArgs {
   float eps = 1e-6f;
   int* status = nullptr;  // device status word (0 = ok)
   int max_ctas = 0;       // 0 = one CTA per SM
+  // EPI_ATTN_P / EPI_ATTN_DS: per-row fp32 vector (lse or D), softmax scale, and the mask of the
+  // forward pass (AttnMask, n_ar); rows are queries, columns keys.
+  const float* rowvec = nullptr;
+  float attn_scale = 1.f;
+  int attn_mask = 0, attn_n_ar = 0;
+  // Operand majors. a_mn: A is stored as [K, M] (row stride lda) and read transposed in place;
+  // b_mn: B is stored as [K, N] (row stride ldb). M (resp. N) and the strides must be % 8 == 0.
+  bool a_mn = false, b_mn = false;
   int k_splits = 1;       // > 1: split-K with fp32 partials in `partial` ([k_splits, M, N] floats)
   float* partial = nullptr;
+  // EPI_CONV: A is the padded input volume flattened to [frames * hp * wp, C] (C % 64 == 0), B the
+  // weights as [Cout, 27 * C] (tap-major: kt, kh, kw, then channel), K = 27 * C. Output rows are
+  // the same padded positions; only interior rows (frame >= conv_tpad, 1 <= h <= hp-2,
+  // 1 <= w <= wp-2) are written, so a zero border stays zero.
+  int conv_c = 0, conv_hp = 0, conv_wp = 0, conv_tpad = 0;
 };
 // Split count that fills the machine for a skinny problem (1 = do not split).
 int gemm_pick_k_splits(int M, int N, int K, int epi);
@@ -76,6 +94,9 @@ struct AttnArgs {
   // Every k-th softmax element computes exp2 with a polynomial on the FMA pipe (2, 3, 4; 0 = none).
   // Measured on B200 the softmax warps are latency/issue bound rather than MUFU bound, so 0 is fastest.
   int exp_emulation = 0;
+  // 1 = 128-key blocks, one score buffer per query tile; 2 = 64-key sub-blocks with two score
+  // sub-buffers per tile (deeper pipelining between softmax and tensor cores).
+  int pipeline = 1;
 };
 void flash_attn_fwd(const AttnArgs& a, cudaStream_t stream);
 
@@ -99,6 +120,14 @@ void swiglu(const void* gate_up, void* y, long long rows, int dff, cudaStream_t 
 void cfg_euler_step(float* x, const void* vc, const void* vu, float guidance, float dt,
                     int normalize, long long rows, int d, cudaStream_t s);
 void l2_flush(void* buf, size_t bytes, cudaStream_t s);
+// y = silu(rmsnorm(x) * gamma) over rows of d channels (channels-last tokenizer activations)
+void rmsnorm_silu(const void* x, const void* gamma, void* y, long long rows, int d, float eps, cudaStream_t s);
+
+// ---- tokenizer decoder helpers on padded channels-last volumes (conv3d.cu) ----
+void upsample_cl(const void* src, void* dst, int t_dst, int hs, int ws, int c, int tpad, int temporal,
+                 int first_chunk, cudaStream_t s);
+void conv_out_rgb(const void* x, const float* wgt, const float* bias, void* out, int t_out, int h, int w,
+                  cudaStream_t s);
 
 // ---- paged-KV decode attention (paged_decode.cu) ----
 struct PagedDecodeArgs {

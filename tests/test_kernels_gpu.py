@@ -300,3 +300,107 @@ def test_gemm_skinny_split_k(m, n, k, epi):
     got = ops.gemm(a, w, None, epi, r, None, m)
     want = ref.gemm(a.float(), w.float(), None, epi, None if r is None else r.float(), None, m)
     _close(got, want, 3e-2, 2e-2, f"skinny gemm {m}x{n}x{k} epi {epi}")
+
+
+def test_conv3d_implicit_gemm_matches_conv3d():
+    """One causal 3x3x3 convolution on a padded channels-last volume vs F.conv3d."""
+    import torch.nn.functional as F
+    torch.manual_seed(19)
+    t, h, w, cin, cout = 5, 12, 20, 64, 128
+    x = _rand(1, cin, t, h, w)
+    wt = _rand(cout, cin, 3, 3, 3, scale=1 / math.sqrt(27 * cin))
+    b = _rand(cout)
+    r = _rand(1, cout, t, h, w)
+    want = F.conv3d(F.pad(x.float(), (1, 1, 1, 1, 2, 0)), wt.float(), b.float()) + r.float()
+    vol = torch.zeros(t + 2, h + 2, w + 2, cin, device=DEV, dtype=torch.bfloat16)
+    vol[2:, 1:-1, 1:-1] = x[0].permute(1, 2, 3, 0)
+    rv = torch.zeros(t + 2, h + 2, w + 2, cout, device=DEV, dtype=torch.bfloat16)
+    rv[2:, 1:-1, 1:-1] = r[0].permute(1, 2, 3, 0)
+    wp = wt.permute(0, 2, 3, 4, 1).reshape(cout, 27 * cin).contiguous()
+    out = torch.zeros(t + 2, h + 2, w + 2, cout, device=DEV, dtype=torch.bfloat16)
+    torch.ops.cosmos_b200.conv3d_cl(vol, wp, b, rv, out, 2)
+    got = out[2:, 1:-1, 1:-1].permute(3, 0, 1, 2)[None]
+    _close(got, want, 3e-2, 2e-2, "implicit-GEMM conv3d")
+    assert out[:2].abs().max() == 0 and out[:, 0].abs().max() == 0 and out[:, :, -1].abs().max() == 0
+
+
+def test_vae_channels_last_decoder_matches_pytorch():
+    from cosmos_b200.models.vae import CausalVideoVAE
+    from cosmos_b200.models.vae_cuda import CLDecoder
+    torch.manual_seed(20)
+    vae = CausalVideoVAE(16, (64, 128, 256, 256)).to(DEV).float().eval()
+    z = torch.randn(1, 16, 3, 6, 8, device=DEV)
+    with torch.no_grad():
+        want = CausalVideoVAE.to_uint8(vae.decode(z))
+    dec = CLDecoder(vae)
+    got = dec.decode(z, chunk_latents=2)
+    assert got.shape == want.shape == (1, 9, 48, 64, 3)
+    diff = (got.int() - want.int()).abs()
+    assert diff.float().mean() < 1.5 and (diff > 8).float().mean() < 0.01, (diff.float().mean(), diff.max())
+    one = dec.decode(z, chunk_latents=3)
+    assert (one.int() - got.int()).abs().max() <= 1  # chunking does not change the result
+
+
+@pytest.mark.parametrize("m,n,k", [(256, 512, 384), (300, 264, 1000), (1024, 4096, 2048)])
+def test_gemm_operand_majors(m, n, k):
+    """Backward-pass GEMMs read transposed operands in place (MN-major shared-memory tiles)."""
+    torch.manual_seed(21)
+    dy = _rand(m, n)                       # [tokens, out]
+    w = _rand(n, k, scale=1 / math.sqrt(n))  # [out, in]
+    x = _rand(m, k)                        # [tokens, in]
+    dx = torch.ops.cosmos_b200.gemm_ex(dy, w, False, True, None)       # dY @ W
+    _close(dx, dy.float() @ w.float(), 3e-2, 2e-2, "dX = dY W")
+    dw = torch.ops.cosmos_b200.gemm_ex(dy, x, True, True, None)        # dY^T @ X
+    _close(dw, (dy.float().t() @ x.float()) / 1.0, 6e-2, 3e-2, "dW = dY^T X")
+
+
+def test_linear_autograd_on_own_kernels():
+    from cosmos_b200.ops import autograd as own
+    torch.manual_seed(22)
+    x = _rand(2, 300, 256).requires_grad_(True)
+    w = _rand(512, 256, scale=1 / 16).requires_grad_(True)
+    y = own.linear(x, w)
+    g = _rand(2, 300, 512)
+    y.backward(g)
+    xf, wf = x.detach().float().requires_grad_(True), w.detach().float().requires_grad_(True)
+    (xf @ wf.t()).backward(g.float())
+    _close(y, xf @ wf.t(), 3e-2, 2e-2, "linear fwd")
+    _close(x.grad, xf.grad, 3e-2, 2e-2, "linear dX")
+    _close(w.grad, wf.grad, 8e-2, 3e-2, "linear dW")
+
+
+@pytest.mark.parametrize("sq,skv,hq,hkv,mask", [(384, 384, 4, 2, ops.MASK_FULL), (300, 300, 2, 1, ops.MASK_CAUSAL),
+                                                 (256, 520, 2, 2, ops.MASK_FULL)])
+def test_attention_autograd_on_own_kernels(sq, skv, hq, hkv, mask):
+    from cosmos_b200.ops import autograd as own
+    torch.manual_seed(23)
+    q = _rand(1, sq, hq, 128).requires_grad_(True)
+    k = _rand(1, skv, hkv, 128).requires_grad_(True)
+    v = _rand(1, skv, hkv, 128).requires_grad_(True)
+    g = _rand(1, sq, hq, 128)
+    o = own.attention(q, k, v, None, mask, 0)
+    o.backward(g)
+    qf, kf, vf = (t.detach().float().requires_grad_(True) for t in (q, k, v))
+    of, _ = ref.attention(qf, kf, vf, None, mask, 0)
+    of.backward(g.float())
+    _close(o, of, 2e-2, 2e-2, "attention fwd")
+    _close(q.grad, qf.grad, 3e-2, 3e-2, "dQ")
+    _close(k.grad, kf.grad, 3e-2, 3e-2, "dK")
+    _close(v.grad, vf.grad, 3e-2, 3e-2, "dV")
+
+
+@pytest.mark.parametrize("b,sq,skv,hq,hkv,mask", [
+    (1, 256, 256, 1, 1, ops.MASK_FULL), (1, 512, 1000, 4, 1, ops.MASK_FULL), (2, 300, 777, 4, 2, ops.MASK_FULL),
+    (1, 1024, 1024, 2, 1, ops.MASK_CAUSAL), (1, 500, 500, 4, 2, ops.MASK_CAUSAL), (1, 200, 456, 2, 2, ops.MASK_CAUSAL),
+    (1, 2048, 2304, 8, 2, ops.MASK_FULL), (1, 256, 64, 1, 1, ops.MASK_FULL), (1, 256, 2000, 1, 1, ops.MASK_FULL)])
+def test_attention_pipeline_v2(b, sq, skv, hq, hkv, mask):
+    """The 64-key sub-block pipeline (two score sub-buffers per query tile)."""
+    torch.manual_seed(24)
+    q, k, v = _rand(b, sq, hq, 128), _rand(b, skv, hkv, 128), _rand(b, skv, hkv, 128)
+    if skv == 2000:  # growing scores: exercises the lazy rescale with a PV in flight
+        ramp = torch.linspace(0.2, 3.0, skv, device=DEV)[None, :, None, None]
+        k = (k.float() * ramp).bfloat16()
+    got, lse = torch.ops.cosmos_b200.attn_fwd_v(q, k, v, 1.0 / math.sqrt(128), mask, 0, True, 2)
+    want, lse_ref = ref.attention(q.float(), k.float(), v.float(), None, mask, 0, True)
+    _close(got, want, 3e-2, 3e-2, "attention v2 out")
+    _close(lse, lse_ref, 2e-2, 1e-3, "attention v2 lse")
