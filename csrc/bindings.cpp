@@ -336,33 +336,9 @@ std::tuple<Tensor, Tensor> attn_fwd(const Tensor& q, const Tensor& k, const Tens
   {
     static const int emu = [] { const char* e = std::getenv("COSMOS_ATTN_EXP_EMU"); return e ? std::atoi(e) : 0; }();
     a.exp_emulation = emu;
-    static const int pipe = [] { const char* e = std::getenv("COSMOS_ATTN_PIPELINE"); return e ? std::atoi(e) : 1; }();
-    a.pipeline = pipe;
+    static const int dbg = [] { const char* e = std::getenv("COSMOS_ATTN_DEBUG"); return e ? std::atoi(e) : 0; }();
+    a.debug = dbg;
   }
-  cosmos::flash_attn_fwd(a, cur_stream());
-  return {o, lse};
-}
-
-// attn_fwd with an explicit pipeline generation (1 or 2), for A/B tests
-std::tuple<Tensor, Tensor> attn_fwd_v(const Tensor& q, const Tensor& k, const Tensor& v, double scale, int64_t mask,
-                                      int64_t n_ar, bool return_lse, int64_t pipeline) {
-  check_bf16_cuda(q, "q"); check_bf16_cuda(k, "k"); check_bf16_cuda(v, "v");
-  c10::cuda::CUDAGuard guard(q.device());
-  TORCH_CHECK(q.dim() == 4 && q.size(3) == 128 && q.stride(3) == 1 && k.stride(3) == 1 && v.stride(3) == 1);
-  const int64_t B = q.size(0), Sq = q.size(1), Hq = q.size(2), Skv = k.size(1), Hkv = k.size(2);
-  Tensor o = at::empty({B, Sq, Hq, 128}, q.options());
-  Tensor lse = at::empty({B, Hq, Sq}, q.options().dtype(at::kFloat));
-  cosmos::AttnArgs a;
-  a.lse = return_lse ? lse.data_ptr<float>() : nullptr;
-  a.Q = q.data_ptr(); a.K = k.data_ptr(); a.V = v.data_ptr(); a.O = o.data_ptr();
-  a.B = (int)B; a.Sq = (int)Sq; a.Skv = (int)Skv; a.Hq = (int)Hq; a.Hkv = (int)Hkv;
-  a.q_stride_b = q.stride(0); a.q_stride_s = q.stride(1); a.q_stride_h = q.stride(2);
-  a.k_stride_b = k.stride(0); a.k_stride_s = k.stride(1); a.k_stride_h = k.stride(2);
-  a.v_stride_b = v.stride(0); a.v_stride_s = v.stride(1); a.v_stride_h = v.stride(2);
-  a.o_stride_b = o.stride(0); a.o_stride_s = o.stride(1); a.o_stride_h = o.stride(2);
-  a.scale = (float)scale; a.mask = (int)mask; a.n_ar = (int)n_ar;
-  a.pipeline = (int)pipeline;
-  a.status = status_tensor(q.get_device()).data_ptr<int>();
   cosmos::flash_attn_fwd(a, cur_stream());
   return {o, lse};
 }
@@ -667,7 +643,6 @@ TORCH_LIBRARY(cosmos_b200, m) {
   m.def("gemm_ex", &gemm_ex);
   m.def("attn_bwd_scores", &attn_bwd_scores);
   m.def("attn_fwd", &attn_fwd);
-  m.def("attn_fwd_v", &attn_fwd_v);
   m.def("rmsnorm", &rmsnorm);
   m.def("adaln_rmsnorm", &adaln_rmsnorm);
   m.def("mrope_", &mrope_);

@@ -718,8 +718,9 @@ static void launch(const CUtensorMap* maps, const cb::GemmGroup& g, int grid, cu
 }
 
 static void fill_problem(const GemmArgs& a, cb::GemmParams& p, CUtensorMap& ta, CUtensorMap& tb) {
-  if ((!a.a_mn && a.K % 8 != 0) || a.lda % 8 != 0 || a.ldb % 8 != 0)
-    throw std::runtime_error("gemm_bf16: K and leading dimensions must be multiples of 8");
+  // TMA needs 16-byte row strides; a ragged K is fine (out-of-range columns are zero-filled)
+  if (a.lda % 8 != 0 || a.ldb % 8 != 0)
+    throw std::runtime_error("gemm_bf16: leading dimensions must be multiples of 8");
   if (a.epi == EPI_SWIGLU && (a.N % 2 != 0 || (a.N / 2) % 8 != 0))
     throw std::runtime_error("gemm_bf16: SwiGLU epilogue needs N/2 to be a multiple of 8");
   if (a.epi == EPI_QKV_ROPE && a.N % 128 != 0)
@@ -802,7 +803,7 @@ int gemm_pick_k_splits(int M, int N, int K, int epi) {
   const int k_blocks = (K + cb::BK - 1) / cb::BK;
   const int sms = sm_count();
   if (tiles * 2 > sms || k_blocks < 8 || N % 8 != 0) return 1;
-  int ks = (sms + tiles - 1) / tiles;
+  int ks = sms / tiles;                      // one wave: tiles * ks <= number of SMs
   if (ks > k_blocks / 4) ks = k_blocks / 4;  // at least 4 k-blocks (256 columns of K) per split
   if (ks > 32) ks = 32;
   return ks < 2 ? 1 : ks;

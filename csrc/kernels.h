@@ -94,9 +94,7 @@ struct AttnArgs {
   // Every k-th softmax element computes exp2 with a polynomial on the FMA pipe (2, 3, 4; 0 = none).
   // Measured on B200 the softmax warps are latency/issue bound rather than MUFU bound, so 0 is fastest.
   int exp_emulation = 0;
-  // 1 = 128-key blocks, one score buffer per query tile; 2 = 64-key sub-blocks with two score
-  // sub-buffers per tile (deeper pipelining between softmax and tensor cores).
-  int pipeline = 1;
+  int debug = 0;  // timing experiments (results are wrong): 1 = no QK MMAs, 2 = no PV MMAs, 4 = no exponentials
 };
 void flash_attn_fwd(const AttnArgs& a, cudaStream_t stream);
 

@@ -40,7 +40,7 @@ paged_decode_kernel(const bf16* __restrict__ q, const bf16* __restrict__ kc, con
   __shared__ float p_s[GROUP][PD_TILE];
   __shared__ long long row_s[PD_TILE];
   __shared__ float red_s[GROUP][4];
-  __shared__ float acc_s[GROUP][128];
+  __shared__ float acc_s[4][GROUP][128];
 
   for (int i = tid; i < GROUP * 128; i += PD_THREADS) {
     const int g = i >> 7, d = i & 127;
@@ -49,12 +49,15 @@ paged_decode_kernel(const bf16* __restrict__ q, const bf16* __restrict__ kc, con
   __syncthreads();
 
   float m_run[GROUP], l_run[GROUP];
-  float acc[GROUP][2];
+  float acc[GROUP][8];
 #pragma unroll
   for (int g = 0; g < GROUP; ++g) {
-    m_run[g] = -1e30f; l_run[g] = 0.f; acc[g][0] = 0.f; acc[g][1] = 0.f;
+    m_run[g] = -1e30f; l_run[g] = 0.f;
+#pragma unroll
+    for (int e = 0; e < 8; ++e) acc[g][e] = 0.f;
   }
-  const int d2 = tid & 63, half = tid >> 6;
+  // phase-2 mapping: 16 threads cover one 256-byte V row with 16-byte loads; 8 token groups
+  const int c16 = tid & 15, tg = tid >> 4;
   const long long row_stride = (long long)Hkv * 128;
 
   for (int t0 = kv_begin; t0 < kv_end; t0 += PD_TILE) {
@@ -69,7 +72,7 @@ paged_decode_kernel(const bf16* __restrict__ q, const bf16* __restrict__ kc, con
       const int page = table[(long long)b * max_pages + pos / page_size];
       row = ((long long)page * page_size + pos % page_size) * row_stride + (long long)kvh * 128;
       const uint4* kp = reinterpret_cast<const uint4*>(kc + row);
-#pragma unroll 4
+#pragma unroll 8
       for (int c = 0; c < 16; ++c) {
         const uint4 kk = kp[c];
         const float f[8] = {bf16lo(kk.x), bf16hi(kk.x), bf16lo(kk.y), bf16hi(kk.y),
@@ -120,50 +123,58 @@ paged_decode_kernel(const bf16* __restrict__ q, const bf16* __restrict__ kc, con
 #pragma unroll
     for (int g = 0; g < GROUP; ++g) {
       l_run[g] = l_run[g] * corr[g] + (red_s[g][0] + red_s[g][1] + red_s[g][2] + red_s[g][3]);
-      acc[g][0] *= corr[g];
-      acc[g][1] *= corr[g];
+#pragma unroll
+      for (int e = 0; e < 8; ++e) acc[g][e] *= corr[g];
     }
-    // ---- phase 2: acc[g][dims 2*d2, 2*d2+1] += sum_t p[g][t] * V[t][dims]; this thread takes
-    // the tokens of its half of the tile
+    // ---- phase 2: acc[g][dims 8*c16 .. +7] += sum_t p[g][t] * V[t][dims] over this thread's tokens
     const int n_tok = min(PD_TILE, kv_end - t0);
-    const int tb = half * 64, te = min(n_tok, tb + 64);
 #pragma unroll 4
-    for (int t = tb; t < te; ++t) {
-      const uint32_t vv = *reinterpret_cast<const uint32_t*>(vc + row_s[t] + 2 * d2);
-      const float v0 = bf16lo(vv), v1 = bf16hi(vv);
+    for (int t = tg; t < n_tok; t += 8) {
+      const uint4 vv = *reinterpret_cast<const uint4*>(vc + row_s[t] + 8 * c16);
+      const float f[8] = {bf16lo(vv.x), bf16hi(vv.x), bf16lo(vv.y), bf16hi(vv.y),
+                          bf16lo(vv.z), bf16hi(vv.z), bf16lo(vv.w), bf16hi(vv.w)};
 #pragma unroll
       for (int g = 0; g < GROUP; ++g) {
-        const float p = p_s[g][t];
-        acc[g][0] = fmaf(p, v0, acc[g][0]);
-        acc[g][1] = fmaf(p, v1, acc[g][1]);
+        const float pp = p_s[g][t];
+#pragma unroll
+        for (int e = 0; e < 8; ++e) acc[g][e] = fmaf(pp, f[e], acc[g][e]);
       }
     }
     __syncthreads();  // before p_s / row_s / red_s are overwritten
   }
 
-  // combine the two halves
-  if (half == 1) {
+  // combine the 8 token groups: lanes l and l^16 of a warp, then the 4 warps through shared memory
 #pragma unroll
-    for (int g = 0; g < GROUP; ++g) {
-      acc_s[g][2 * d2] = acc[g][0];
-      acc_s[g][2 * d2 + 1] = acc[g][1];
-    }
+  for (int g = 0; g < GROUP; ++g)
+#pragma unroll
+    for (int e = 0; e < 8; ++e) acc[g][e] += __shfl_xor_sync(0xffffffffu, acc[g][e], 16);
+  if ((tid & 31) < 16) {
+#pragma unroll
+    for (int g = 0; g < GROUP; ++g)
+#pragma unroll
+      for (int e = 0; e < 8; ++e) acc_s[tid >> 5][g][8 * c16 + e] = acc[g][e];
   }
   __syncthreads();
-  if (half == 0) {
+  if (tid < 16) {
 #pragma unroll
     for (int g = 0; g < GROUP; ++g) {
-      const float a0 = acc[g][0] + acc_s[g][2 * d2], a1 = acc[g][1] + acc_s[g][2 * d2 + 1];
+      float a[8];
+#pragma unroll
+      for (int e = 0; e < 8; ++e)
+        a[e] = acc_s[0][g][8 * c16 + e] + acc_s[1][g][8 * c16 + e] + acc_s[2][g][8 * c16 + e] + acc_s[3][g][8 * c16 + e];
       const int h = kvh * GROUP + g;
       if (n_splits == 1) {
         const float inv = l_run[g] > 0.f ? 1.f / l_run[g] : 0.f;
-        *reinterpret_cast<uint32_t*>(out + ((long long)b * Hq + h) * 128 + 2 * d2) =
-            pack_bf16(a0 * inv, a1 * inv);
+        uint4 o;
+        o.x = pack_bf16(a[0] * inv, a[1] * inv); o.y = pack_bf16(a[2] * inv, a[3] * inv);
+        o.z = pack_bf16(a[4] * inv, a[5] * inv); o.w = pack_bf16(a[6] * inv, a[7] * inv);
+        *reinterpret_cast<uint4*>(out + ((long long)b * Hq + h) * 128 + 8 * c16) = o;
       } else {
         const long long base = ((long long)b * Hq + h) * n_splits + split;
-        float2* dst = reinterpret_cast<float2*>(part_acc + base * 128 + 2 * d2);
-        *dst = make_float2(a0, a1);
-        if (d2 == 0) {
+        float4* dst = reinterpret_cast<float4*>(part_acc + base * 128 + 8 * c16);
+        dst[0] = make_float4(a[0], a[1], a[2], a[3]);
+        dst[1] = make_float4(a[4], a[5], a[6], a[7]);
+        if (c16 == 0) {
           part_ml[base * 2] = m_run[g];
           part_ml[base * 2 + 1] = l_run[g];
         }
@@ -194,8 +205,9 @@ paged_decode_merge_kernel(const float* __restrict__ part_acc, const float* __res
 namespace cosmos {
 
 int paged_decode_pick_splits(int B, int Hkv, int max_len) {
-  // enough CTAs to fill the machine about 4x over, but no split shorter than 256 tokens
-  const int want = (148 * 4 + B * Hkv - 1) / (B * Hkv);
+  // Several waves of CTAs (about 5 CTAs fit per SM) so that the last, partly filled wave costs
+  // little, but no split shorter than 256 tokens.
+  const int want = (148 * 24 + B * Hkv - 1) / (B * Hkv);
   const int cap = (max_len + 255) / 256;
   int s = want < cap ? want : cap;
   if (s < 1) s = 1;
