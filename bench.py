@@ -225,8 +225,8 @@ def main():
         }
         print(json.dumps(rec), flush=True)
     if world > 1:
-        dist.barrier()
-        dist.destroy_process_group()
+        from cosmos_b200.parallel.runtime import finish
+        finish(hard=(__name__ == "__main__"))
     return 0
 
 

@@ -1,7 +1,7 @@
 """Micro-benchmarks of the hot kernels: CUDA-event timing after warm-up, L2 flushed between
 iterations, achieved TFLOP/s (or GB/s) and fraction of the measured peaks.
 
-    python -m cosmos_b200.ops.bench_kernels [--what gemm,attn,norm] [--iters 5] [--small]
+    python -m cosmos_b200.ops.bench_kernels [--what gemm,attn,norm,paged,vae] [--iters 5] [--small]
 """
 from __future__ import annotations
 
@@ -98,6 +98,42 @@ def main():
         gbs = 2.0 * rows * d * 2 / ms / 1e6
         rec = {"kernel": "adaln_rmsnorm", "shape": [rows, d], "ms": round(ms, 4), "gbs": round(gbs, 1),
                f"frac_of_{src}_hbm": round(gbs / bw_peak, 3)}
+        out.append(rec)
+        print(json.dumps(rec), flush=True)
+    if "paged" in what:
+        # decode attention over a paged cache: batch 32, 32 q heads / 8 kv heads, 8448 cached tokens
+        b, hq, hkv, ctx, page = (8, 32, 8, 2048, 16) if args.small else (32, 32, 8, 8448, 16)
+        n_pages = b * ((ctx + page - 1) // page)
+        kc = torch.randn(n_pages, page, hkv, 128, device=dev).bfloat16()
+        vc = torch.randn(n_pages, page, hkv, 128, device=dev).bfloat16()
+        table = torch.randperm(n_pages, device=dev).int().view(b, -1)
+        lens = torch.full((b,), ctx, dtype=torch.int32, device=dev)
+        q = torch.randn(b, hq, 128, device=dev).bfloat16()
+        ms = timeit(lambda: ops.paged_decode(q, kc, vc, table, lens, 128 ** -0.5), args.iters, flush)
+        gbs = 2.0 * b * ctx * hkv * 128 * 2 / ms / 1e6
+        rec = {"kernel": "paged_decode", "shape": [b, hq, hkv, ctx], "ms": round(ms, 4), "gbs": round(gbs, 1),
+               f"frac_of_{src}_hbm": round(gbs / bw_peak, 3)}
+        out.append(rec)
+        print(json.dumps(rec), flush=True)
+    if "vae" in what:
+        # tokenizer decode of one clip through the channels-last implicit-GEMM decoder
+        from cosmos_b200.models.vae import CausalVideoVAE
+        from cosmos_b200.models.vae_cuda import CLDecoder
+
+        t_lat, h_lat, w_lat = (3, 30, 40) if args.small else (31, 90, 160)
+        torch.manual_seed(0)
+        vae = CausalVideoVAE(16, (64, 128, 256, 256)).to(device=dev, dtype=torch.bfloat16).eval()
+        dec = CLDecoder(vae)
+        z = torch.randn(1, 16, t_lat, h_lat, w_lat, device=dev).bfloat16()
+        frames = None
+
+        def run():
+            nonlocal frames
+            frames = dec.decode(z)
+
+        ms = timeit(run, max(1, min(args.iters, 3)), flush)
+        rec = {"kernel": "vae_decode_cl", "latent": [t_lat, h_lat, w_lat], "frames": list(frames.shape[1:4]),
+               "ms": round(ms, 2)}
         out.append(rec)
         print(json.dumps(rec), flush=True)
     torch.cuda.synchronize()

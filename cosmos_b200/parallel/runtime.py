@@ -39,6 +39,27 @@ def init_distributed(world: Optional[int] = None, rank: Optional[int] = None, lo
     return Mesh(pc, world, rank)
 
 
+def finish(hard: bool = True) -> None:
+    """End of a launcher-run entry point: the ranks meet once more, flush their output and leave.
+    With `hard` the process exits without interpreter / communicator teardown: a communicator whose
+    collectives were captured in a CUDA graph, or whose buffers peers still map, can block in
+    destroy_process_group, and a rank that blocks there keeps the launcher (and the GPUs) busy
+    long after the work is done."""
+    import sys
+
+    if dist.is_available() and dist.is_initialized():
+        if torch.cuda.is_available():
+            torch.cuda.synchronize()
+        dist.barrier()
+        if not hard:
+            dist.destroy_process_group()
+            return
+    sys.stdout.flush()
+    sys.stderr.flush()
+    if hard and dist.is_available() and dist.is_initialized():
+        os._exit(0)
+
+
 def build_engine_for_mesh(model, mesh: Mesh, fused: bool = True):
     """GeneratorEngine whose attention context and CFG handling match the mesh."""
     from ..models.generator import GeneratorEngine

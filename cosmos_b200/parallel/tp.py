@@ -194,7 +194,7 @@ class TPContext(AttnContext):
             out = torch.empty_like(x)
             if not hasattr(self, "_ar_counters"):
                 self._ar_counters = torch.zeros(64, dtype=torch.int32, device=x.device)
-            # epochs of signal slots 16..23 are tracked on the device, so the call is CUDA-graph safe
+            # epochs of signal slots 16..47 (one row per block) are tracked on the device, so the call is CUDA-graph safe
             torch.ops.cosmos_b200.allreduce_oneshot(ptrs, self.sg.pads_dev, out.view(-1), self.rank, self.tp, 16, 0,
                                                     self._ar_counters)
             return out

@@ -247,9 +247,8 @@ def main(argv: Optional[List[str]] = None) -> int:
         (out_root / name).write_text(json.dumps({"average": avg, "samples": records, "parallelism": mesh.describe(),
                                                  "world_size": world}, indent=1))
     if world > 1:
-        import torch.distributed as dist
-        dist.barrier()
-        dist.destroy_process_group()
+        from ..parallel.runtime import finish
+        finish(hard=(__name__ == "__main__"))
     return 0
 
 

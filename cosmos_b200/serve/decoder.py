@@ -299,8 +299,8 @@ def main(argv=None) -> int:
                           "fraction_of_hbm_floor": round(floor_ms / (ms / args.new_tokens), 3),
                           "data": "synthetic KV (N(0,1)), random-init weights"}), flush=True)
     if world > 1:
-        dist.barrier()
-        dist.destroy_process_group()
+        from ..parallel.runtime import finish
+        finish(hard=(__name__ == "__main__"))
     return 0
 
 

@@ -222,8 +222,8 @@ def main(argv=None) -> int:
         print(json.dumps({"metric": "train_tokens_per_s", "value": tokens_per_step / avg, "step_s": avg,
                           "tokens_per_step": tokens_per_step, "parallelism": mesh.describe(), "model": cfg.name}))
     if world > 1:
-        dist.barrier()
-        dist.destroy_process_group()
+        from .parallel.runtime import finish
+        finish(hard=(__name__ == "__main__"))
     return 0
 
 

@@ -48,28 +48,6 @@ __device__ __forceinline__ float ex2(float x) {
   return y;
 }
 
-// exp2 on the FMA/ALU pipes: round-to-nearest split x = n + f, f in [-0.5, 0.5], degree-3 minimax
-// polynomial for 2^f (max relative error 7.5e-5, far below bf16 rounding of P), exponent add for 2^n.
-// Used for a fixed share of the softmax elements to take load off the 16-lane MUFU pipe, which
-// otherwise needs as many cycles per score tile as the tensor cores.
-__device__ __forceinline__ float ex2_poly(float x) {
-  x = fmaxf(x, -126.f);
-  const float magic = 12582912.f;  // 1.5 * 2^23: the integer part lands in the low mantissa bits
-  const float t = x + magic;
-  const float n = t - magic;
-  const float f = x - n;
-  float p = fmaf(0.0551716648f, f, 0.2426111251f);
-  p = fmaf(p, f, 0.6932609677f);
-  p = fmaf(p, f, 0.9999280572f);
-  return __int_as_float(__float_as_int(p) + (__float_as_int(t) << 23));
-}
-
-template <int EMU>
-__device__ __forceinline__ float ex2_mix(float x, int i) {
-  if (EMU > 0 && (i % EMU) == EMU - 1) return ex2_poly(x);
-  return ex2(x);
-}
-
 // Packed / three-input fp32 instructions of sm_100: they halve the instruction count of the softmax
 // inner loop, which (not the tensor or MUFU pipe) is what bounds this kernel.
 __device__ __forceinline__ float max3(float a, float b, float c) {
@@ -96,13 +74,39 @@ __device__ __forceinline__ uint64_t add2(uint64_t a, uint64_t b) {
   return r;
 }
 
+// Two exponentials at once on the FMA pipe with packed fp32 instructions (about five issue slots
+// per element, against one slot but eight cycles of the 4-lane-per-scheduler MUFU pipe):
+// round-to-nearest split x = n + f with f in [-0.5, 0.5], degree-3 minimax polynomial for 2^f
+// (max relative error 7.5e-5, far below the bf16 rounding of P), exponent add for 2^n.
+__device__ __forceinline__ void ex2_poly2(uint64_t x2, float& r0, float& r1) {
+  float a, b;
+  unpack2(x2, a, b);
+  a = fmaxf(a, -126.f);
+  b = fmaxf(b, -126.f);
+  const uint64_t xc = pack2(a, b);
+  const uint64_t t2 = add2(xc, pack2(12582912.f, 12582912.f));
+  const uint64_t n2 = add2(t2, pack2(-12582912.f, -12582912.f));
+  const uint64_t f2 = fma2(n2, pack2(-1.f, -1.f), xc);
+  uint64_t p2 = fma2(pack2(0.0551716648f, 0.0551716648f), f2, pack2(0.2426111251f, 0.2426111251f));
+  p2 = fma2(p2, f2, pack2(0.6932609677f, 0.6932609677f));
+  p2 = fma2(p2, f2, pack2(0.9999280572f, 0.9999280572f));
+  float pa, pb, ta, tb;
+  unpack2(p2, pa, pb);
+  unpack2(t2, ta, tb);
+  r0 = __int_as_float(__float_as_int(pa) + (__float_as_int(ta) << 23));
+  r1 = __int_as_float(__float_as_int(pb) + (__float_as_int(tb) << 23));
+}
+
 __device__ __forceinline__ int kv_limit(int qi, const AttnParams& p) {
   if (p.mask == MASK_CAUSAL) return min(p.Skv, qi + 1 + (p.Skv - p.Sq));
   if (p.mask == MASK_MOT) return qi < p.n_ar ? qi + 1 : p.Skv;
   return p.Skv;
 }
 
-template <int EMU>
+// EMU: 0 = every exp2 on the MUFU pipe, k = every k-th PAIR of scores on the FMA pipe.
+// DBG: honour AttnParams::debug (timing experiments); the production instantiation ignores it so
+// that the inner loops carry no tests of it.
+template <int EMU, bool DBG>
 __global__ void __launch_bounds__(ATT_THREADS, 1)
 flash_attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
                       const __grid_constant__ CUtensorMap tmV, const AttnParams p) {
@@ -126,6 +130,7 @@ flash_attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
+  const int dbg = DBG ? p.debug : 0;
   const int qt = (p.mask == MASK_FULL) ? blockIdx.x : (gridDim.x - 1 - blockIdx.x);
   const int head = blockIdx.y;
   const int batch = blockIdx.z;
@@ -220,7 +225,7 @@ flash_attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
         const uint32_t d = tmem_base + t * 128;
         const uint64_t a0 = q_desc0 + uint64_t(t * (TILE_BYTES >> 4));
         const uint64_t b0 = k_desc0 + uint64_t(slot * (TILE_BYTES >> 4));
-        if (p.debug & 1) return;
+        if (dbg & 1) return;
 #pragma unroll
         for (int kk = 0; kk < 8; ++kk) {
           const uint32_t off = (kk >> 2) * (HALF_BYTES >> 4) + 2 * (kk & 3);
@@ -233,7 +238,7 @@ flash_attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
         const uint32_t d = tmem_base + 256 + t * 128;
         const uint32_t a0 = tmem_base + t * 128;
         const uint64_t b0 = v_desc0 + uint64_t(slot * (TILE_BYTES >> 4));
-        if (p.debug & 2) return;
+        if (dbg & 2) return;
 #pragma unroll
         for (int k4 = 0; k4 < 4; ++k4) {
           const int kk = half * 4 + k4;
@@ -355,10 +360,14 @@ flash_attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
           const int e = half * 64 + 2 * i;
           const uint64_t x2 = fma2(pack2(__uint_as_float(s[e]), __uint_as_float(s[e + 1])), sl2_2, negm_2);
           float p0, p1;
-          unpack2(x2, p0, p1);
-          if (!(p.debug & 4)) {
-            p0 = ex2_mix<EMU>(p0, e);
-            p1 = ex2_mix<EMU>(p1, e + 1);
+          if (EMU > 0 && (i % (EMU > 0 ? EMU : 1)) == EMU - 1) {
+            ex2_poly2(x2, p0, p1);
+          } else {
+            unpack2(x2, p0, p1);
+            if (!(dbg & 4)) {
+              p0 = ex2(p0);
+              p1 = ex2(p1);
+            }
           }
           ls2[i & 3] = add2(ls2[i & 3], pack2(p0, p1));
           pk[i] = pack_bf16(p0, p1);
@@ -446,13 +455,27 @@ void flash_attn_fwd(const AttnArgs& a, cudaStream_t stream) {
     throw std::runtime_error("flash_attn_fwd: MoT mask needs Skv == Sq");
   if ((a.o_stride_s % 8) || (a.o_stride_h % 8) || (a.o_stride_b % 8))
     throw std::runtime_error("flash_attn_fwd: output strides must be multiples of 8 elements");
-  static bool configured = false;
-  if (!configured) {
-    cudaFuncSetAttribute(cb::flash_attn_fwd_kernel<0>, cudaFuncAttributeMaxDynamicSharedMemorySize, cb::ATT_SMEM);
-    cudaFuncSetAttribute(cb::flash_attn_fwd_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, cb::ATT_SMEM);
-    cudaFuncSetAttribute(cb::flash_attn_fwd_kernel<3>, cudaFuncAttributeMaxDynamicSharedMemorySize, cb::ATT_SMEM);
-    cudaFuncSetAttribute(cb::flash_attn_fwd_kernel<4>, cudaFuncAttributeMaxDynamicSharedMemorySize, cb::ATT_SMEM);
-    configured = true;
+  using Kern = void (*)(const CUtensorMap, const CUtensorMap, const CUtensorMap, const cb::AttnParams);
+  // a.exp_emulation: 0 = all exp2 on the MUFU pipe, k = every k-th pair of scores on the FMA pipe
+  Kern kern = cb::flash_attn_fwd_kernel<0, false>;
+  if (a.debug) {
+    kern = a.exp_emulation == 4 ? cb::flash_attn_fwd_kernel<4, true> : cb::flash_attn_fwd_kernel<0, true>;
+  } else {
+    switch (a.exp_emulation) {
+      case 2: kern = cb::flash_attn_fwd_kernel<2, false>; break;
+      case 3: kern = cb::flash_attn_fwd_kernel<3, false>; break;
+      case 4: kern = cb::flash_attn_fwd_kernel<4, false>; break;
+      case 6: kern = cb::flash_attn_fwd_kernel<6, false>; break;
+      default: break;
+    }
+  }
+  static thread_local Kern configured[8] = {};
+  bool seen = false;
+  for (Kern k : configured) seen |= (k == kern);
+  if (!seen) {
+    cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, cb::ATT_SMEM);
+    for (Kern& k : configured)
+      if (!k) { k = kern; break; }
   }
   // B == 1 tensors may carry a zero batch stride; TMA needs a non-zero multiple of 16 bytes.
   auto fix = [](long long sb, long long ss, int S) { return sb > 0 ? sb : ss * S; };
@@ -473,13 +496,7 @@ void flash_attn_fwd(const AttnArgs& a, cudaStream_t stream) {
   p.status = a.status;
   p.debug = a.debug;
   dim3 grid((a.Sq + 2 * cb::TQ - 1) / (2 * cb::TQ), a.Hq, a.B);
-  // a.exp_emulation: 0 = all exp2 on the MUFU pipe, k = every k-th element on the FMA pipe
-  switch (a.exp_emulation) {
-    case 2: cb::flash_attn_fwd_kernel<2><<<grid, cb::ATT_THREADS, cb::ATT_SMEM, stream>>>(tq, tk, tv, p); break;
-    case 3: cb::flash_attn_fwd_kernel<3><<<grid, cb::ATT_THREADS, cb::ATT_SMEM, stream>>>(tq, tk, tv, p); break;
-    case 4: cb::flash_attn_fwd_kernel<4><<<grid, cb::ATT_THREADS, cb::ATT_SMEM, stream>>>(tq, tk, tv, p); break;
-    default: cb::flash_attn_fwd_kernel<0><<<grid, cb::ATT_THREADS, cb::ATT_SMEM, stream>>>(tq, tk, tv, p); break;
-  }
+  kern<<<grid, cb::ATT_THREADS, cb::ATT_SMEM, stream>>>(tq, tk, tv, p);
 }
 
 }  // namespace cosmos

@@ -67,13 +67,21 @@ allreduce_oneshot_kernel(const long long* bufs, const long long* pads, bf16* out
   }
   const bool ok = barrier_device(pads, rank, world, myslot, epoch, status);
   if (!__syncthreads_and(ok ? 1 : 0)) return;
+  // All peers' vectors of one index are requested before the first add (eight NVLink round trips
+  // in flight per thread instead of one after the other); ranks beyond eight go in further rounds.
   for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n_vec;
        i += (long long)gridDim.x * blockDim.x) {
     float acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
-    for (int r = 0; r < world; ++r) {
-      const uint4 v = reinterpret_cast<const uint4*>(bufs[r])[i];
-      acc[0] += bf16lo(v.x); acc[1] += bf16hi(v.x); acc[2] += bf16lo(v.y); acc[3] += bf16hi(v.y);
-      acc[4] += bf16lo(v.z); acc[5] += bf16hi(v.z); acc[6] += bf16lo(v.w); acc[7] += bf16hi(v.w);
+    for (int r0 = 0; r0 < world; r0 += 8) {
+      uint4 v[8];
+#pragma unroll
+      for (int r = 0; r < 8; ++r)
+        v[r] = (r0 + r < world) ? reinterpret_cast<const uint4*>(bufs[r0 + r])[i] : make_uint4(0, 0, 0, 0);
+#pragma unroll
+      for (int r = 0; r < 8; ++r) {
+        acc[0] += bf16lo(v[r].x); acc[1] += bf16hi(v[r].x); acc[2] += bf16lo(v[r].y); acc[3] += bf16hi(v[r].y);
+        acc[4] += bf16lo(v[r].z); acc[5] += bf16hi(v[r].z); acc[6] += bf16lo(v[r].w); acc[7] += bf16hi(v[r].w);
+      }
     }
     uint4 o;
     o.x = pack_bf16(acc[0], acc[1]); o.y = pack_bf16(acc[2], acc[3]);
@@ -156,8 +164,10 @@ void allreduce_oneshot(const long long* bufs_dev, const long long* pads_dev, voi
   if (n_elems % 8 != 0) throw std::runtime_error("allreduce_oneshot: element count must be % 8");
   if (world > 64) throw std::runtime_error("allreduce_oneshot: at most 64 ranks per group");
   const long long n_vec = n_elems / 8;
-  int blocks = (int)std::min<long long>((n_vec + 511) / 512, 8);
+  // one signal-slot row per block: slots [slot, slot + blocks) must be reserved for this call site
+  int blocks = (int)std::min<long long>((n_vec + 511) / 512, 32);
   if (blocks < 1) blocks = 1;
+  if (slot + blocks > 64) throw std::runtime_error("allreduce_oneshot: signal slots out of range");
   cb::allreduce_oneshot_kernel<<<blocks, 512, 0, s>>>(bufs_dev, pads_dev, (bf16*)out, n_vec, rank,
                                                      world, slot, epoch, counters, status);
 }

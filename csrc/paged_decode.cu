@@ -21,8 +21,21 @@ constexpr int PD_THREADS = 128;
 constexpr int PD_TILE = 128;   // tokens per tile
 constexpr int PD_MAX_GROUP = 8;
 
+// 16-byte read-only load; NO_L1 skips L1 allocation for fully coalesced rows that are used once
+template <bool NO_L1>
+__device__ __forceinline__ uint4 ld_nc_u4(const uint4* p) {
+  uint4 v;
+  if (NO_L1)
+    asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0, %1, %2, %3}, [%4];"
+                 : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p));
+  else
+    asm volatile("ld.global.nc.v4.u32 {%0, %1, %2, %3}, [%4];"
+                 : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p));
+  return v;
+}
+
 template <int GROUP>
-__global__ void __launch_bounds__(PD_THREADS)
+__global__ void __launch_bounds__(PD_THREADS, 3)
 paged_decode_kernel(const bf16* __restrict__ q, const bf16* __restrict__ kc, const bf16* __restrict__ vc,
                     const int* __restrict__ table, const int* __restrict__ seq_lens, int max_pages,
                     int page_size, int Hq, int Hkv, int n_splits, float scale_log2,
@@ -71,10 +84,31 @@ paged_decode_kernel(const bf16* __restrict__ q, const bf16* __restrict__ kc, con
     if (valid) {
       const int page = table[(long long)b * max_pages + pos / page_size];
       row = ((long long)page * page_size + pos % page_size) * row_stride + (long long)kvh * 128;
+    }
+    row_s[tid] = row;
+    __syncthreads();
+    // All of this tile's K and V bytes are requested here, before the first use: the 256-byte K
+    // row of this thread's token and, for phase 2, 16 bytes of each of 16 V rows. With three
+    // CTAs per SM that keeps ~190 KB in flight per SM, which covers the DRAM latency; the
+    // softmax between the two phases then runs under the V loads.
+    const int n_tok = min(PD_TILE, kv_end - t0);
+    uint4 kbuf[16];
+    uint4 vbuf[PD_TILE / 8];
+    {
       const uint4* kp = reinterpret_cast<const uint4*>(kc + row);
-#pragma unroll 8
+#pragma unroll
+      for (int c = 0; c < 16; ++c) kbuf[c] = valid ? ld_nc_u4<false>(kp + c) : make_uint4(0, 0, 0, 0);
+#pragma unroll
+      for (int i = 0; i < PD_TILE / 8; ++i) {
+        const int t = tg + 8 * i;
+        vbuf[i] = t < n_tok ? ld_nc_u4<true>(reinterpret_cast<const uint4*>(vc + row_s[t] + 8 * c16))
+                            : make_uint4(0, 0, 0, 0);
+      }
+    }
+    if (valid) {
+#pragma unroll
       for (int c = 0; c < 16; ++c) {
-        const uint4 kk = kp[c];
+        const uint4 kk = kbuf[c];
         const float f[8] = {bf16lo(kk.x), bf16hi(kk.x), bf16lo(kk.y), bf16hi(kk.y),
                             bf16lo(kk.z), bf16hi(kk.z), bf16lo(kk.w), bf16hi(kk.w)};
 #pragma unroll
@@ -85,7 +119,6 @@ paged_decode_kernel(const bf16* __restrict__ q, const bf16* __restrict__ kc, con
         }
       }
     }
-    row_s[tid] = row;
     // tile max per head
     float mx[GROUP];
 #pragma unroll
@@ -127,10 +160,10 @@ paged_decode_kernel(const bf16* __restrict__ q, const bf16* __restrict__ kc, con
       for (int e = 0; e < 8; ++e) acc[g][e] *= corr[g];
     }
     // ---- phase 2: acc[g][dims 8*c16 .. +7] += sum_t p[g][t] * V[t][dims] over this thread's tokens
-    const int n_tok = min(PD_TILE, kv_end - t0);
-#pragma unroll 4
-    for (int t = tg; t < n_tok; t += 8) {
-      const uint4 vv = *reinterpret_cast<const uint4*>(vc + row_s[t] + 8 * c16);
+#pragma unroll
+    for (int i = 0; i < PD_TILE / 8; ++i) {
+      const int t = tg + 8 * i;
+      const uint4 vv = vbuf[i];
       const float f[8] = {bf16lo(vv.x), bf16hi(vv.x), bf16lo(vv.y), bf16hi(vv.y),
                           bf16lo(vv.z), bf16hi(vv.z), bf16lo(vv.w), bf16hi(vv.w)};
 #pragma unroll
