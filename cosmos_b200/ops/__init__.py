@@ -232,7 +232,7 @@ def l2_flush(buf: torch.Tensor) -> None:
 def paged_decode_ref(q, k_cache, v_cache, block_table, seq_lens, scale: Optional[float] = None):
     """fp32 definition: gather each sequence's pages, then softmax(q k^T) v per head (GQA)."""
     b, hq, d = q.shape
-    page, hkv = k_cache.shape[1], k_cache.shape[2]
+    hkv, page = k_cache.shape[1], k_cache.shape[2]
     scale = scale if scale is not None else 1.0 / math.sqrt(d)
     out = torch.zeros(b, hq, d, dtype=torch.float32, device=q.device)
     for i in range(b):
@@ -240,8 +240,8 @@ def paged_decode_ref(q, k_cache, v_cache, block_table, seq_lens, scale: Optional
         if n == 0:
             continue
         pages = block_table[i, :(n + page - 1) // page].long()
-        k = k_cache[pages].reshape(-1, hkv, d)[:n].float()
-        v = v_cache[pages].reshape(-1, hkv, d)[:n].float()
+        k = k_cache[pages].transpose(1, 2).reshape(-1, hkv, d)[:n].float()   # [tokens, Hkv, d]
+        v = v_cache[pages].transpose(1, 2).reshape(-1, hkv, d)[:n].float()
         k = k.repeat_interleave(hq // hkv, dim=1)
         v = v.repeat_interleave(hq // hkv, dim=1)
         s = torch.einsum("hd,nhd->hn", q[i].float(), k) * scale
@@ -249,15 +249,34 @@ def paged_decode_ref(q, k_cache, v_cache, block_table, seq_lens, scale: Optional
     return out.to(q.dtype)
 
 
+def decode_qkv_post(qkv, n_q_heads: int, cos, sin, q_gamma, k_gamma, eps: float, slots, k_cache, v_cache):
+    """Decode-step glue after the QKV projection. qkv [B, Hq + 2 Hkv, 128]; q and k heads get their
+    RMS-norm and the rotary rotation (cos/sin [B, 64]); k and v of sequence b are written into the
+    paged caches [pages, Hkv, page_size, 128] at slot slots[b]; returns q [B, Hq, 128].
+    One kernel on CUDA; on CPU the same steps with the reference ops."""
+    hkv = (qkv.shape[1] - n_q_heads) // 2
+    if _use_cuda(qkv, q_gamma) and qkv.shape[-1] == 128:
+        return _k().decode_qkv_post(qkv.contiguous(), n_q_heads, cos.contiguous(), sin.contiguous(), q_gamma, k_gamma,
+                                    eps, slots.contiguous(), k_cache, v_cache)
+    q = ref.mrope(qkv[:, :n_q_heads], cos, sin, q_gamma, eps)
+    k = ref.mrope(qkv[:, n_q_heads:n_q_heads + hkv], cos, sin, k_gamma, eps)
+    v = qkv[:, n_q_heads + hkv:]
+    page_size = k_cache.shape[2]
+    page, off = slots // page_size, slots % page_size
+    k_cache[page, :, off] = k.to(k_cache.dtype)
+    v_cache[page, :, off] = v.to(v_cache.dtype)
+    return q
+
+
 def paged_decode(q, k_cache, v_cache, block_table, seq_lens, scale: Optional[float] = None,
                  n_splits: Optional[int] = None, scratch=None, max_len: Optional[int] = None):
-    """q [B, Hq, 128] against a paged cache [pages, page_size, Hkv, 128] -> [B, Hq, 128].
+    """q [B, Hq, 128] against a paged cache [pages, Hkv, page_size, 128] -> [B, Hq, 128].
     `max_len` (an upper bound of seq_lens known on the host) picks the kv split count without
     a device synchronisation."""
     scale = scale if scale is not None else 1.0 / math.sqrt(q.shape[-1])
     if _use_cuda(q) and q.shape[-1] == 128:
         if n_splits is None:
-            ml = max_len if max_len is not None else block_table.shape[1] * k_cache.shape[1]
-            n_splits = int(torch.ops.cosmos_b200.paged_decode_pick_splits(q.shape[0], k_cache.shape[2], ml))
+            ml = max_len if max_len is not None else block_table.shape[1] * k_cache.shape[2]
+            n_splits = int(torch.ops.cosmos_b200.paged_decode_pick_splits(q.shape[0], k_cache.shape[1], ml))
         return _k().paged_decode(q.contiguous(), k_cache, v_cache, block_table, seq_lens, scale, n_splits, scratch)
     return paged_decode_ref(q, k_cache, v_cache, block_table, seq_lens, scale)

@@ -104,8 +104,8 @@ def main():
         # decode attention over a paged cache: batch 32, 32 q heads / 8 kv heads, 8448 cached tokens
         b, hq, hkv, ctx, page = (8, 32, 8, 2048, 16) if args.small else (32, 32, 8, 8448, 16)
         n_pages = b * ((ctx + page - 1) // page)
-        kc = torch.randn(n_pages, page, hkv, 128, device=dev).bfloat16()
-        vc = torch.randn(n_pages, page, hkv, 128, device=dev).bfloat16()
+        kc = torch.randn(n_pages, hkv, page, 128, device=dev).bfloat16()
+        vc = torch.randn(n_pages, hkv, page, 128, device=dev).bfloat16()
         table = torch.randperm(n_pages, device=dev).int().view(b, -1)
         lens = torch.full((b,), ctx, dtype=torch.int32, device=dev)
         q = torch.randn(b, hq, 128, device=dev).bfloat16()

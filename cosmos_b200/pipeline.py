@@ -312,6 +312,55 @@ class Cosmos3OmniPipeline:
             action = tokens[0, off:off + st.n_action, :st.action_dim].float().cpu().numpy()
         return frames, sound, action
 
+    # ------------------------------------------------------------------ long videos
+    @torch.no_grad()
+    def generate_chunked(self, prompt: str, negative_prompt: Optional[str] = None, video=None,
+                         num_frames: int = 121, height: int = 720, width: int = 1280, fps: int = 24,
+                         frames_per_chunk: int = 121, num_conditional_frames: int = 1,
+                         num_first_chunk_conditional_frames: int = 0, sampling: Optional[SamplingConfig] = None,
+                         callback=None, **call_kw) -> Cosmos3Output:
+        """Generates `num_frames` frames chunk by chunk (`num_video_frames_per_chunk`,
+        `num_conditional_frames`, `num_first_chunk_conditional_frames` of the reference's transfer
+        specs, cookbooks/cosmos3/generator/transfer/specs/edge.json:11-13). The first chunk is
+        conditioned on the leading frames of `video` (if any), every later chunk on the last
+        `num_conditional_frames` frames generated so far, which enter as clean latent frames; the
+        overlap is dropped from the output. Each chunk uses seed + chunk index."""
+        import dataclasses
+
+        tc = self.cfg.vae_t_compress
+        n_first = num_first_chunk_conditional_frames if video is not None else 0
+        plan = _chunk_plan(num_frames, frames_per_chunk, n_first, num_conditional_frames, tc)
+        src = _to_frames(video, width, height) if video is not None else None
+        frames_out: List[np.ndarray] = []
+        sounds, timings = [], {}
+        tail = None
+        last = None
+        for k, (c, new, total) in enumerate(plan):
+            cond = None
+            if k == 0 and c:
+                cond = src[:c]
+            elif k > 0 and c:
+                cond = tail[-c:]
+            kw = dict(call_kw)
+            if cond is not None:
+                kw["condition_frame_indexes"] = list(range(1 + (c - 1) // tc))
+            sc = dataclasses.replace(sampling, seed=sampling.seed + k) if sampling is not None else None
+            if sc is None and "generator" not in kw:
+                kw["generator"] = torch.Generator().manual_seed(k)
+            last = self(prompt, negative_prompt, video=cond, num_frames=total, height=height, width=width, fps=fps,
+                        sampling=sc, callback=callback, **kw)
+            fr = np.asarray(last.video)
+            frames_out.append(fr[c:c + new])
+            tail = fr[:c + new]
+            if last.sound is not None:
+                sounds.append(np.asarray(last.sound))
+            for name, v in last.timings.items():
+                timings[name] = timings.get(name, 0.0) + v
+        timings["chunks"] = len(plan)
+        sound = np.concatenate(sounds, axis=0) if sounds else None
+        return Cosmos3Output(video=np.concatenate(frames_out, axis=0), sound=sound, action=last.action,
+                             latents=last.latents, timings=timings)
+
     # ------------------------------------------------------------------ __call__
     @torch.no_grad()
     def __call__(self, prompt: str, negative_prompt: Optional[str] = None, image=None, video=None,
@@ -347,6 +396,26 @@ class Cosmos3OmniPipeline:
             video_out = [Image.fromarray(frames[0])]
         return Cosmos3Output(video=video_out, sound=sound, action=action, latents=x,
                              timings={"prepare_s": t1 - t0, "sample_s": t2 - t1, "decode_s": t3 - t2})
+
+
+def _chunk_plan(num_frames: int, frames_per_chunk: int, n_cond_first: int, n_cond: int, t_compress: int
+                ) -> List[Tuple[int, int, int]]:
+    """(conditioning frames, new frames, pixel frames generated) per chunk for a long video: every
+    chunk holds at most `frames_per_chunk` pixel frames, the first `n_cond` (first chunk:
+    `n_cond_first`) of them repeat the tail of what exists already, and the generated length is
+    rounded up to the tokenizer's 1 + k * t_compress frame grid."""
+    if frames_per_chunk <= max(n_cond, n_cond_first):
+        raise ValueError("num_video_frames_per_chunk must exceed the number of conditional frames")
+    plan, done, k = [], 0, 0
+    while done < num_frames:
+        c = n_cond_first if k == 0 else n_cond
+        new = min(frames_per_chunk - c, num_frames - done)
+        total = c + new
+        total = 1 + -(-(total - 1) // t_compress) * t_compress
+        plan.append((c, new, total))
+        done += new
+        k += 1
+    return plan
 
 
 def _to_frames(media, width: int, height: int) -> np.ndarray:

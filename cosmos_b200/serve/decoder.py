@@ -97,10 +97,8 @@ class TPDecoder:
         else:
             h, x = ops.rmsnorm(resid_delta, p["norm1"], cfg.rms_eps, residual=x)
         qkv = ops.gemm(h, p["wqkv"]).view(b, self.hq + 2 * self.hk, self.hd)
-        q = ops.mrope(qkv[:, :self.hq].contiguous(), cos, sin, p["q_norm"], cfg.rms_eps)
-        k = ops.mrope(qkv[:, self.hq:self.hq + self.hk].contiguous(), cos, sin, p["k_norm"], cfg.rms_eps)
-        v = qkv[:, self.hq + self.hk:].contiguous()
-        self.cache.write(li, k, v, slots)
+        q = ops.decode_qkv_post(qkv, self.hq, cos, sin, p["q_norm"], p["k_norm"], cfg.rms_eps, slots,
+                                self.cache.k[li], self.cache.v[li])
         o = ops.paged_decode(q, self.cache.k[li], self.cache.v[li], table, lens, max_len=max_len)
         y = self._allreduce(ops.gemm(o.view(b, -1), p["wo"]))
         h, x = ops.rmsnorm(y, p["norm2"], cfg.rms_eps, residual=x)

@@ -1,7 +1,8 @@
 """Paged KV cache of the Reasoner: fixed-size pages per layer, a native (C++) block allocator
 that owns the page tables, and device-side tables that the decode-attention kernel reads.
 
-Layout per layer: k_cache, v_cache [num_pages, page_size, Hkv_local, head_dim] bf16. A sequence
+Layout per layer: k_cache, v_cache [num_pages, Hkv_local, page_size, head_dim] bf16 (the rows of one
+(page, head) are contiguous, which is what the decode kernel streams). A sequence
 owns a list of pages; token i of the sequence lives in page table[i // page_size] at offset
 i % page_size. Pages for the whole generation (prompt + max new tokens) can be reserved up front,
 which keeps the block table static during decode (a requirement for CUDA-graph replay).
@@ -71,7 +72,7 @@ class PagedKVCache:
                  max_pages_per_seq: int, dtype=torch.bfloat16, device="cuda"):
         self.n_layers, self.page_size, self.max_pages = n_layers, page_size, max_pages_per_seq
         self.alloc = make_allocator(num_pages, page_size, max_pages_per_seq)
-        shape = (num_pages, page_size, n_kv_heads, head_dim)
+        shape = (num_pages, n_kv_heads, page_size, head_dim)
         self.k = [torch.zeros(shape, dtype=dtype, device=device) for _ in range(n_layers)]
         self.v = [torch.zeros(shape, dtype=dtype, device=device) for _ in range(n_layers)]
         self.device = torch.device(device)
@@ -102,6 +103,14 @@ class PagedKVCache:
             torch.ops.cosmos_b200.kv_cache_write(k.contiguous(), v.contiguous(), slots.contiguous(),
                                                  self.k[layer], self.v[layer])
         else:
-            hk, d = k.shape[1], k.shape[2]
-            self.k[layer].view(-1, hk, d).index_copy_(0, slots, k)
-            self.v[layer].view(-1, hk, d).index_copy_(0, slots, v)
+            page, off = slots // self.page_size, slots % self.page_size
+            self.k[layer][page, :, off] = k
+            self.v[layer][page, :, off] = v
+
+    def gather(self, layer: int, table_row: torch.Tensor, n: int):
+        """The first n cached tokens of one sequence as contiguous K, V [n, Hkv, D]."""
+        pages = table_row[:(n + self.page_size - 1) // self.page_size].long()
+        hk, d = self.k[layer].shape[1], self.k[layer].shape[3]
+        k = self.k[layer][pages].transpose(1, 2).reshape(-1, hk, d)[:n]
+        v = self.v[layer][pages].transpose(1, 2).reshape(-1, hk, d)[:n]
+        return k, v

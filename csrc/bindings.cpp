@@ -465,15 +465,15 @@ Tensor paged_decode(const Tensor& q, const Tensor& k_cache, const Tensor& v_cach
   TORCH_CHECK(q.dim() == 3 && q.size(2) == 128 && q.is_contiguous(), "q must be contiguous [B, Hq, 128]");
   TORCH_CHECK(k_cache.dim() == 4 && k_cache.size(3) == 128 && k_cache.is_contiguous() &&
                   v_cache.is_contiguous() && v_cache.sizes() == k_cache.sizes(),
-              "caches must be contiguous [pages, page_size, Hkv, 128]");
+              "caches must be contiguous [pages, Hkv, page_size, 128]");
   TORCH_CHECK(block_table.scalar_type() == at::kInt && block_table.is_cuda() && block_table.is_contiguous() &&
                   block_table.dim() == 2 && block_table.size(0) == q.size(0), "block_table must be int32 [B, max_pages]");
   TORCH_CHECK(seq_lens.scalar_type() == at::kInt && seq_lens.is_cuda() && seq_lens.numel() == q.size(0));
   cosmos::PagedDecodeArgs a;
   a.q = q.data_ptr(); a.k_cache = k_cache.data_ptr(); a.v_cache = v_cache.data_ptr();
   a.block_table = block_table.data_ptr<int>(); a.seq_lens = seq_lens.data_ptr<int>();
-  a.B = (int)q.size(0); a.Hq = (int)q.size(1); a.Hkv = (int)k_cache.size(2);
-  a.page_size = (int)k_cache.size(1); a.max_pages = (int)block_table.size(1);
+  a.B = (int)q.size(0); a.Hq = (int)q.size(1); a.Hkv = (int)k_cache.size(1);
+  a.page_size = (int)k_cache.size(2); a.max_pages = (int)block_table.size(1);
   a.scale = (float)scale; a.n_splits = (int)n_splits;
   Tensor out = at::empty_like(q);
   a.out = out.data_ptr();
@@ -597,10 +597,36 @@ void kv_cache_write(const Tensor& k, const Tensor& v, const Tensor& slots, Tenso
   check_bf16_cuda(k, "k"); check_bf16_cuda(v, "v"); check_bf16_cuda(k_cache, "k_cache"); check_bf16_cuda(v_cache, "v_cache");
   c10::cuda::CUDAGuard guard(k.device());
   TORCH_CHECK(k.is_contiguous() && v.is_contiguous() && k.sizes() == v.sizes() && k.dim() == 3 && k.size(2) == 128);
-  TORCH_CHECK(k_cache.is_contiguous() && v_cache.is_contiguous() && k_cache.dim() == 4 && k_cache.size(2) == k.size(1));
+  TORCH_CHECK(k_cache.is_contiguous() && v_cache.is_contiguous() && k_cache.dim() == 4 && k_cache.size(1) == k.size(1) &&
+              k_cache.size(3) == 128 && v_cache.sizes() == k_cache.sizes());
   TORCH_CHECK(slots.is_cuda() && slots.scalar_type() == at::kLong && slots.is_contiguous() && slots.numel() == k.size(0));
   cosmos::kv_cache_write(k.data_ptr(), v.data_ptr(), reinterpret_cast<const long long*>(slots.data_ptr<int64_t>()),
-                         k_cache.data_ptr(), v_cache.data_ptr(), k.size(0), (int)k.size(1), cur_stream());
+                         k_cache.data_ptr(), v_cache.data_ptr(), k.size(0), (int)k.size(1), (int)k_cache.size(2), cur_stream());
+}
+
+Tensor decode_qkv_post(const Tensor& qkv, int64_t n_q_heads, const Tensor& cos_t, const Tensor& sin_t,
+                       const Tensor& gamma_q, const Tensor& gamma_k, double eps, const Tensor& slots,
+                       Tensor k_cache, Tensor v_cache) {
+  check_bf16_cuda(qkv, "qkv"); check_bf16_cuda(gamma_q, "gamma_q"); check_bf16_cuda(gamma_k, "gamma_k");
+  check_bf16_cuda(k_cache, "k_cache"); check_bf16_cuda(v_cache, "v_cache");
+  c10::cuda::CUDAGuard guard(qkv.device());
+  TORCH_CHECK(qkv.dim() == 3 && qkv.size(2) == 128 && qkv.is_contiguous(), "qkv must be contiguous [B, Hq + 2 Hkv, 128]");
+  const int64_t B = qkv.size(0), Hq = n_q_heads;
+  TORCH_CHECK(Hq > 0 && (qkv.size(1) - Hq) > 0 && (qkv.size(1) - Hq) % 2 == 0, "bad head split");
+  const int64_t Hkv = (qkv.size(1) - Hq) / 2;
+  TORCH_CHECK(k_cache.dim() == 4 && k_cache.is_contiguous() && v_cache.is_contiguous() && k_cache.size(1) == Hkv &&
+              k_cache.size(3) == 128 && v_cache.sizes() == k_cache.sizes(), "caches must be contiguous [pages, Hkv, page_size, 128]");
+  TORCH_CHECK(cos_t.is_cuda() && cos_t.scalar_type() == at::kFloat && cos_t.is_contiguous() && cos_t.numel() == B * 64 &&
+              sin_t.is_cuda() && sin_t.scalar_type() == at::kFloat && sin_t.is_contiguous() && sin_t.numel() == B * 64,
+              "cos/sin must be contiguous fp32 [B, 64]");
+  TORCH_CHECK(gamma_q.numel() == 128 && gamma_k.numel() == 128 && gamma_q.is_contiguous() && gamma_k.is_contiguous());
+  TORCH_CHECK(slots.is_cuda() && slots.scalar_type() == at::kLong && slots.is_contiguous() && slots.numel() == B);
+  Tensor q = at::empty({B, Hq, 128}, qkv.options());
+  cosmos::decode_qkv_post(qkv.data_ptr(), (int)B, (int)Hq, (int)Hkv, cos_t.data_ptr<float>(), sin_t.data_ptr<float>(),
+                          gamma_q.data_ptr(), gamma_k.data_ptr(), (float)eps,
+                          reinterpret_cast<const long long*>(slots.data_ptr<int64_t>()), q.data_ptr(),
+                          k_cache.data_ptr(), v_cache.data_ptr(), (int)k_cache.size(2), cur_stream());
+  return q;
 }
 
 // mode 0: reduce + update; mode 1: reduce into `reduced` and add sum(g^2) to sq; mode 2: update from `reduced`
@@ -659,6 +685,7 @@ TORCH_LIBRARY(cosmos_b200, m) {
   m.def("comm_barrier", &comm_barrier);
   m.def("allreduce_oneshot", &allreduce_oneshot);
   m.def("kv_cache_write", &kv_cache_write);
+  m.def("decode_qkv_post", &decode_qkv_post);
   m.def("rs_adamw", &rs_adamw);
   m.def("allgather_pull", &allgather_pull);
   cosmos::register_runtime_ops(m);

@@ -130,7 +130,7 @@ void conv_out_rgb(const void* x, const float* wgt, const float* bias, void* out,
 // ---- paged-KV decode attention (paged_decode.cu) ----
 struct PagedDecodeArgs {
   const void* q = nullptr;        // [B, Hq, 128] bf16
-  const void* k_cache = nullptr;  // [num_pages, page_size, Hkv, 128] bf16
+  const void* k_cache = nullptr;  // [num_pages, Hkv, page_size, 128] bf16
   const void* v_cache = nullptr;
   const int* block_table = nullptr;  // [B, max_pages]
   const int* seq_lens = nullptr;     // [B]
@@ -146,7 +146,13 @@ size_t paged_decode_scratch_bytes(int B, int Hq, int n_splits);
 void paged_decode(const PagedDecodeArgs& a, cudaStream_t s);
 // Scatters new K/V rows [N, Hkv, 128] into the paged caches at flat slots (page * page_size + offset).
 void kv_cache_write(const void* k, const void* v, const long long* slots, void* k_cache, void* v_cache,
-                    long long n_rows, int Hkv, cudaStream_t s);
+                    long long n_rows, int Hkv, int page_size, cudaStream_t s);
+
+// Decode-step glue after the QKV GEMM: q/k RMS-norm + rotary, q to a contiguous buffer, k and v into
+// their paged-cache rows (slot = page * page_size + offset, one per sequence). cos/sin [B, 64] fp32.
+void decode_qkv_post(const void* qkv, int B, int Hq, int Hkv, const float* cos_t, const float* sin_t,
+                     const void* gamma_q, const void* gamma_k, float eps, const long long* slots, void* q_out,
+                     void* k_cache, void* v_cache, int page_size, cudaStream_t s);
 
 // ---- communication kernels over peer mappings (comm.cu) ----
 // pads_dev / bufs_dev / grads_dev / srcs_dev: device arrays with one address per rank of the group.

@@ -1,7 +1,8 @@
 // K14: decode-time attention over a paged KV cache (one new query token per sequence).
 //
 //   q        [B, Hq, 128] bf16
-//   k_cache  [num_pages, page_size, Hkv, 128] bf16   (v_cache alike)
+//   k_cache  [num_pages, Hkv, page_size, 128] bf16   (v_cache alike; the page_size rows of one
+//            (page, kv head) are contiguous, so a CTA streams whole 256 * page_size byte blocks)
 //   table    [B, max_pages] int32 page ids, seq_lens [B] int32
 //   out      [B, Hq, 128] bf16
 //
@@ -71,7 +72,6 @@ paged_decode_kernel(const bf16* __restrict__ q, const bf16* __restrict__ kc, con
   }
   // phase-2 mapping: 16 threads cover one 256-byte V row with 16-byte loads; 8 token groups
   const int c16 = tid & 15, tg = tid >> 4;
-  const long long row_stride = (long long)Hkv * 128;
 
   for (int t0 = kv_begin; t0 < kv_end; t0 += PD_TILE) {
     // ---- phase 1: scores of this thread's token against the GROUP queries
@@ -83,7 +83,7 @@ paged_decode_kernel(const bf16* __restrict__ q, const bf16* __restrict__ kc, con
     long long row = 0;
     if (valid) {
       const int page = table[(long long)b * max_pages + pos / page_size];
-      row = ((long long)page * page_size + pos % page_size) * row_stride + (long long)kvh * 128;
+      row = (((long long)page * Hkv + kvh) * page_size + pos % page_size) * 128;
     }
     row_s[tid] = row;
     __syncthreads();
@@ -288,15 +288,22 @@ void paged_decode(const PagedDecodeArgs& a, cudaStream_t s) {
 }  // namespace cosmos
 
 namespace cb {
+// k, v [n_rows, Hkv, 128] -> cache rows: slot = page * page_size + offset selects the token row,
+// head h of it lives at ((page * Hkv + h) * page_size + offset) * 128.
 __global__ void __launch_bounds__(256)
 kv_cache_write_kernel(const uint4* __restrict__ k, const uint4* __restrict__ v, const long long* __restrict__ slots,
-                      uint4* __restrict__ kc, uint4* __restrict__ vc, long long n_rows, int vec_per_row) {
+                      uint4* __restrict__ kc, uint4* __restrict__ vc, long long n_rows, int Hkv, int page_size) {
+  const int vec_per_row = Hkv * 16;
   const long long total = n_rows * vec_per_row;
   for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total;
        i += (long long)gridDim.x * blockDim.x) {
     const long long r = i / vec_per_row;
-    const long long c = i - r * vec_per_row;
-    const long long dst = slots[r] * vec_per_row + c;
+    const int c = (int)(i - r * vec_per_row);
+    const int h = c >> 4;
+    const long long slot = slots[r];
+    const long long page = slot / page_size;
+    const int off = (int)(slot - page * page_size);
+    const long long dst = (((page * Hkv + h) * page_size + off) << 4) + (c & 15);
     kc[dst] = k[i];
     vc[dst] = v[i];
   }
@@ -305,13 +312,79 @@ kv_cache_write_kernel(const uint4* __restrict__ k, const uint4* __restrict__ v, 
 
 namespace cosmos {
 void kv_cache_write(const void* k, const void* v, const long long* slots, void* k_cache, void* v_cache,
-                    long long n_rows, int Hkv, cudaStream_t s) {
+                    long long n_rows, int Hkv, int page_size, cudaStream_t s) {
   if (n_rows <= 0) return;
-  const int vec_per_row = Hkv * 128 / 8;
-  const long long total = n_rows * vec_per_row;
+  const long long total = n_rows * Hkv * 16;
   const int blocks = (int)std::min<long long>((total + 255) / 256, 148 * 8);
   cb::kv_cache_write_kernel<<<blocks, 256, 0, s>>>((const uint4*)k, (const uint4*)v, slots, (uint4*)k_cache,
-                                                  (uint4*)v_cache, n_rows, vec_per_row);
+                                                  (uint4*)v_cache, n_rows, Hkv, page_size);
+}
+}  // namespace cosmos
+
+// ====================================================================== fused decode-step glue
+// One launch between the QKV GEMM and the decode attention of a decode step: q heads get the q
+// RMS-norm and the rotary rotation and go to a contiguous q buffer; k heads get the k RMS-norm and
+// the rotation and go straight into their cache row; v heads are copied into theirs.
+// One warp per (sequence, head); a lane holds elements [2l, 2l+1] of both 64-channel halves.
+namespace cb {
+__device__ __forceinline__ float warp_sum_f(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  return v;
+}
+
+__global__ void __launch_bounds__(256)
+decode_qkv_post_kernel(const bf16* __restrict__ qkv, int B, int Hq, int Hkv, const float* __restrict__ cos_t,
+                       const float* __restrict__ sin_t, const bf16* __restrict__ gamma_q,
+                       const bf16* __restrict__ gamma_k, float eps, const long long* __restrict__ slots,
+                       bf16* __restrict__ q_out, bf16* __restrict__ kc, bf16* __restrict__ vc, int page_size) {
+  const int lane = threadIdx.x & 31;
+  const int heads = Hq + 2 * Hkv;
+  const long long w = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  if (w >= (long long)B * heads) return;
+  const int b = (int)(w / heads), h = (int)(w % heads);
+  const bf16* p = qkv + ((long long)b * heads + h) * 128;
+  const uint32_t lo = reinterpret_cast<const uint32_t*>(p)[lane];
+  const uint32_t hi = reinterpret_cast<const uint32_t*>(p + 64)[lane];
+  bf16* dst;
+  if (h < Hq) {
+    dst = q_out + ((long long)b * Hq + h) * 128;
+  } else {
+    const long long slot = slots[b];
+    const long long page = slot / page_size;
+    const int off = (int)(slot - page * page_size);
+    const int hk = (h - Hq) % Hkv;
+    dst = (h < Hq + Hkv ? kc : vc) + (((page * Hkv + hk) * page_size + off) << 7);
+  }
+  uint32_t out_lo = lo, out_hi = hi;
+  if (h < Hq + Hkv) {
+    const bf16* gamma = h < Hq ? gamma_q : gamma_k;
+    float a0 = bf16lo(lo), a1 = bf16hi(lo), b0 = bf16lo(hi), b1 = bf16hi(hi);
+    const float ss = warp_sum_f(a0 * a0 + a1 * a1 + b0 * b0 + b1 * b1);
+    const float rinv = rsqrtf(ss * (1.f / 128.f) + eps);
+    a0 *= rinv * __bfloat162float(gamma[2 * lane]);
+    a1 *= rinv * __bfloat162float(gamma[2 * lane + 1]);
+    b0 *= rinv * __bfloat162float(gamma[64 + 2 * lane]);
+    b1 *= rinv * __bfloat162float(gamma[64 + 2 * lane + 1]);
+    const float2 c = reinterpret_cast<const float2*>(cos_t + (long long)b * 64)[lane];
+    const float2 sn = reinterpret_cast<const float2*>(sin_t + (long long)b * 64)[lane];
+    out_lo = pack_bf16(a0 * c.x - b0 * sn.x, a1 * c.y - b1 * sn.y);
+    out_hi = pack_bf16(b0 * c.x + a0 * sn.x, b1 * c.y + a1 * sn.y);
+  }
+  reinterpret_cast<uint32_t*>(dst)[lane] = out_lo;
+  reinterpret_cast<uint32_t*>(dst + 64)[lane] = out_hi;
+}
+}  // namespace cb
+
+namespace cosmos {
+void decode_qkv_post(const void* qkv, int B, int Hq, int Hkv, const float* cos_t, const float* sin_t,
+                     const void* gamma_q, const void* gamma_k, float eps, const long long* slots, void* q_out,
+                     void* k_cache, void* v_cache, int page_size, cudaStream_t s) {
+  const long long warps = (long long)B * (Hq + 2 * Hkv);
+  if (warps <= 0) return;
+  cb::decode_qkv_post_kernel<<<(unsigned)((warps + 7) / 8), 256, 0, s>>>(
+      (const bf16*)qkv, B, Hq, Hkv, cos_t, sin_t, (const bf16*)gamma_q, (const bf16*)gamma_k, eps, slots,
+      (bf16*)q_out, (bf16*)k_cache, (bf16*)v_cache, page_size);
 }
 }  // namespace cosmos
 

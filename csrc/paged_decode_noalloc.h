@@ -26,7 +26,7 @@ extern "C" {
 #define COSMOS_NOALLOC_CUDA_ERROR 3
 
 // Decode attention for one new token per sequence over a paged KV cache.
-//   q [B, Hq, 128] bf16, k_cache / v_cache [pages, page_size, Hkv, 128] bf16 (contiguous),
+//   q [B, Hq, 128] bf16, k_cache / v_cache [pages, Hkv, page_size, 128] bf16 (contiguous),
 //   block_table [B, max_pages] int32, seq_lens [B] int32, out [B, Hq, 128] bf16; all device
 //   pointers on the current device. `stream` is a cudaStream_t (NULL = default stream).
 //   `n_splits` in [1, 64] splits every sequence along kv across CTAs.

@@ -257,14 +257,43 @@ def test_paged_decode(b, hq, hkv, page, lens, splits):
     torch.manual_seed(16)
     max_pages = (max(lens) + page - 1) // page + 1
     n_pages = b * max_pages + 3
-    kc = _rand(n_pages, page, hkv, 128)
-    vc = _rand(n_pages, page, hkv, 128)
+    kc = _rand(n_pages, hkv, page, 128)
+    vc = _rand(n_pages, hkv, page, 128)
     perm = torch.randperm(n_pages, device=DEV)[:b * max_pages].view(b, max_pages).int()
     sl = torch.tensor(lens, device=DEV, dtype=torch.int32)
     q = _rand(b, hq, 128)
     got = ops.paged_decode(q, kc, vc, perm, sl, n_splits=splits, max_len=max(lens))
     want = ops.paged_decode_ref(q.float(), kc.float(), vc.float(), perm, sl)
     _close(got, want, 2e-2, 2e-2, "paged decode")
+
+
+@pytest.mark.parametrize("b,hq,hkv,page", [(5, 4, 1, 16), (32, 32, 8, 16), (3, 8, 2, 4)])
+def test_decode_qkv_post(b, hq, hkv, page):
+    """The fused decode glue (q/k norm + rotary + cache write) against the fp32 definition of each step."""
+    torch.manual_seed(18)
+    n_pages = 2 * b + 1
+    qkv = _rand(b, hq + 2 * hkv, 128)
+    ang = torch.rand(b, 64, device=DEV) * 6.0
+    cos, sin = ang.cos().contiguous(), ang.sin().contiguous()
+    gq, gk = (1 + 0.1 * torch.randn(128, device=DEV)).bfloat16(), (1 + 0.1 * torch.randn(128, device=DEV)).bfloat16()
+    slots = (torch.randperm(n_pages * page, device=DEV)[:b]).long()
+    kc, vc = _rand(n_pages, hkv, page, 128), _rand(n_pages, hkv, page, 128)
+    kc0, vc0 = kc.clone(), vc.clone()
+    q = ops.decode_qkv_post(qkv, hq, cos, sin, gq, gk, 1e-6, slots, kc, vc)
+    torch.cuda.synchronize()
+    ops.check_status()
+    f = qkv.float()
+    q_want = ref.mrope(f[:, :hq], cos, sin, gq.float(), 1e-6)
+    k_want = ref.mrope(f[:, hq:hq + hkv], cos, sin, gk.float(), 1e-6)
+    _close(q, q_want, 2e-2, 2e-2, "q")
+    pg, off = slots // page, slots % page
+    _close(kc[pg, :, off], k_want, 2e-2, 2e-2, "k rows")
+    assert torch.equal(vc[pg, :, off], qkv[:, hq + hkv:])
+    # every other cache row is untouched
+    mask = torch.ones(n_pages, page, dtype=torch.bool, device=DEV)
+    mask[pg, off] = False
+    assert torch.equal(kc.transpose(1, 2)[mask], kc0.transpose(1, 2)[mask])
+    assert torch.equal(vc.transpose(1, 2)[mask], vc0.transpose(1, 2)[mask])
 
 
 @pytest.mark.parametrize("epi", [ops.EPI_PLAIN, ops.EPI_SWIGLU, ops.EPI_GATED_RESID])

@@ -166,6 +166,34 @@ def test_policy_runner_returns_action_chunk():
     assert out["shape"] == [4, 10] and np.isfinite(np.asarray(out["action"])).all()
 
 
+def test_chunked_long_video_generation():
+    """Chunk plan arithmetic, and a 13-frame clip generated as chunks of 9 frames with one
+    conditioning frame carried from chunk to chunk."""
+    import torch
+    from cosmos_b200.pipeline import Cosmos3OmniPipeline, _chunk_plan
+
+    assert _chunk_plan(121, 121, 0, 1, 4) == [(0, 121, 121)]
+    assert _chunk_plan(241, 121, 0, 1, 4) == [(0, 121, 121), (1, 120, 121)]
+    assert _chunk_plan(13, 9, 0, 1, 4) == [(0, 9, 9), (1, 4, 5)]
+    assert _chunk_plan(20, 9, 5, 1, 4) == [(5, 4, 9), (1, 8, 9), (1, 8, 9)]
+    with pytest.raises(ValueError):
+        _chunk_plan(20, 1, 0, 1, 4)
+    pipe = Cosmos3OmniPipeline.from_pretrained("tiny", torch_dtype=torch.float32, vae_widths=(8, 16, 16, 16),
+                                               config_overrides=dict(max_text_len=16, n_layers=1))
+    seen = []
+    orig = pipe.prepare
+
+    def spy(*a, **kw):
+        seen.append((a[4] if len(a) > 4 else kw.get("num_frames"), kw.get("condition_frame_indexes")))
+        return orig(*a, **kw)
+
+    pipe.prepare = spy
+    out = pipe.generate_chunked("a ball rolls", num_frames=13, height=32, width=32, fps=8, frames_per_chunk=9,
+                                num_conditional_frames=1, num_inference_steps=2, guidance_scale=1.0)
+    assert np.asarray(out.video).shape == (13, 32, 32, 3) and out.timings["chunks"] == 2
+    assert seen == [(9, None), (5, [0])]
+
+
 @pytest.mark.skipif(not REF.exists(), reason="reference assets not mounted")
 def test_physics_iq_specs_validate(tmp_path):
     from cosmos_b200.evaluation import physics_iq as piq

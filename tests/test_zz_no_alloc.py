@@ -33,8 +33,8 @@ def _case(seed, b, hq, hkv, page, lens):
     g = torch.Generator(device="cuda").manual_seed(seed)
     max_pages = (max(lens) + page - 1) // page + 1
     n_pages = b * max_pages + 2
-    kc = torch.randn(n_pages, page, hkv, 128, device="cuda", generator=g).bfloat16()
-    vc = torch.randn(n_pages, page, hkv, 128, device="cuda", generator=g).bfloat16()
+    kc = torch.randn(n_pages, hkv, page, 128, device="cuda", generator=g).bfloat16()
+    vc = torch.randn(n_pages, hkv, page, 128, device="cuda", generator=g).bfloat16()
     table = torch.randperm(n_pages, device="cuda", generator=g)[:b * max_pages].view(b, max_pages).int().contiguous()
     sl = torch.tensor(lens, device="cuda", dtype=torch.int32)
     q = torch.randn(b, hq, 128, device="cuda", generator=g).bfloat16()
@@ -46,7 +46,7 @@ def _call(fn, q, kc, vc, table, sl, n_splits):
     err = ctypes.create_string_buffer(256)
     stream = torch.cuda.current_stream().cuda_stream
     rc = fn(q.data_ptr(), kc.data_ptr(), vc.data_ptr(), table.data_ptr(), sl.data_ptr(), out.data_ptr(),
-            q.shape[0], q.shape[1], kc.shape[2], kc.shape[1], table.shape[1], 1.0 / 128 ** 0.5, n_splits,
+            q.shape[0], q.shape[1], kc.shape[1], kc.shape[2], table.shape[1], 1.0 / 128 ** 0.5, n_splits,
             ctypes.c_void_p(stream), err, 256)
     return rc, out, err.value.decode()
 
