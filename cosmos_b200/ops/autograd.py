@@ -5,7 +5,11 @@ kernels (training path on CUDA bf16):
              bwd  dX = dY W, dW = dY^T X         the same kernel reading the transposed operands in
                                                  place (MN-major shared-memory tiles)
   attention  fwd  flash attention (tcgen05) with the log-sum-exp saved
-             bwd  per head, with scores materialised as bf16 [Sq, Skv]:
+             bwd  flash backward on tcgen05 (csrc/attn_bwd_tcgen05.cu): a dK/dV kernel with the K/V
+                  tile stationary and a dQ kernel with the Q tile stationary; scores are recomputed
+                  on chip, nothing of size S^2 reaches memory.
+                  COSMOS_ATTN_BWD_MATERIALIZED=1 selects the older per-head variant with scores
+                  materialised as bf16 [Sq, Skv]:
                   P  = exp(Q K^T scale - lse)    GEMM with the exp in its epilogue (fp32 scores never leave TMEM)
                   dS = P (dO V^T - D) scale      GEMM with P as an epilogue operand
                   dV = P^T dO, dQ = dS K, dK = dS^T Q   plain GEMMs on transposed operands
@@ -17,6 +21,7 @@ Element-wise pieces of the layer (norms, SwiGLU, rotary, residuals) use PyTorch 
 from __future__ import annotations
 
 import math
+import os
 from typing import Optional
 
 import torch
@@ -26,6 +31,9 @@ from .reference import MASK_CAUSAL, MASK_FULL, MASK_MOT
 
 def _k():
     return torch.ops.cosmos_b200
+
+
+_MATERIALIZED = os.environ.get("COSMOS_ATTN_BWD_MATERIALIZED", "0") == "1"
 
 
 class LinearFn(torch.autograd.Function):
@@ -71,6 +79,10 @@ class AttentionFn(torch.autograd.Function):
         skv, hkv = k.shape[1], k.shape[2]
         group = hq // hkv
         do = do.contiguous()
+        if not _MATERIALIZED:
+            delta = (do.float() * o.float()).sum(-1).permute(0, 2, 1).contiguous()  # [B, Hq, Sq]
+            dq, dk, dv = _k().attn_bwd(q, k, v, do, lse, delta, scale, mask, n_ar)
+            return dq, dk, dv, None, None, None
         dq = torch.empty_like(q)
         dk = torch.zeros(b, skv, hkv, d, dtype=torch.float32, device=q.device)
         dv = torch.zeros_like(dk)

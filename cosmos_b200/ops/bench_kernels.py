@@ -1,7 +1,7 @@
 """Micro-benchmarks of the hot kernels: CUDA-event timing after warm-up, L2 flushed between
 iterations, achieved TFLOP/s (or GB/s) and fraction of the measured peaks.
 
-    python -m cosmos_b200.ops.bench_kernels [--what gemm,attn,norm,paged,vae] [--iters 5] [--small]
+    python -m cosmos_b200.ops.bench_kernels [--what gemm,attn,attnbwd,norm,paged,vae] [--iters 5] [--small]
 """
 from __future__ import annotations
 
@@ -98,6 +98,23 @@ def main():
         gbs = 2.0 * rows * d * 2 / ms / 1e6
         rec = {"kernel": "adaln_rmsnorm", "shape": [rows, d], "ms": round(ms, 4), "gbs": round(gbs, 1),
                f"frac_of_{src}_hbm": round(gbs / bw_peak, 3)}
+        out.append(rec)
+        print(json.dumps(rec), flush=True)
+    if "attnbwd" in what:
+        # flash attention backward (dK/dV kernel + dQ kernel) at the per-rank training shape
+        sq, hq, hkv = (4096, 8, 2) if args.small else (14336, 32, 8)
+        q = torch.randn(1, sq, hq, 128, device=dev).bfloat16()
+        k = torch.randn(1, sq, hkv, 128, device=dev).bfloat16()
+        v = torch.randn(1, sq, hkv, 128, device=dev).bfloat16()
+        do = torch.randn(1, sq, hq, 128, device=dev).bfloat16()
+        o, lse = torch.ops.cosmos_b200.attn_fwd(q, k, v, 128 ** -0.5, ops.MASK_FULL, 0, True, None, 0, None)
+        delta = (do.float() * o.float()).sum(-1).permute(0, 2, 1).contiguous()
+        ms = timeit(lambda: torch.ops.cosmos_b200.attn_bwd(q, k, v, do, lse, delta, 128 ** -0.5, ops.MASK_FULL, 0),
+                    args.iters, flush)
+        fl = 7 * 2.0 * sq * sq * 128 * hq  # 4 MMAs in the dK/dV kernel + 3 in the dQ kernel
+        rec = {"kernel": "flash_attn_bwd_tcgen05", "shape": [sq, sq, hq, hkv], "ms": round(ms, 4),
+               "tflops_executed": round(fl / ms / 1e9, 1), "tflops_algorithmic": round(fl * 5 / 7 / ms / 1e9, 1),
+               f"frac_of_{src}_bf16": round(fl / ms / 1e9 / tf_peak, 3)}
         out.append(rec)
         print(json.dumps(rec), flush=True)
     if "paged" in what:

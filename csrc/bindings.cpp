@@ -343,6 +343,43 @@ std::tuple<Tensor, Tensor> attn_fwd(const Tensor& q, const Tensor& k, const Tens
   return {o, lse};
 }
 
+// Flash attention backward: q/k/v/do [B, S, H, 128] (unit inner stride), lse/delta [B, Hq, Sq] fp32
+// -> (dq, dk, dv) contiguous bf16.
+std::tuple<Tensor, Tensor, Tensor> attn_bwd(const Tensor& q, const Tensor& k, const Tensor& v, const Tensor& dout,
+                                            const Tensor& lse, const Tensor& delta, double scale, int64_t mask,
+                                            int64_t n_ar) {
+  check_bf16_cuda(q, "q"); check_bf16_cuda(k, "k"); check_bf16_cuda(v, "v"); check_bf16_cuda(dout, "do");
+  c10::cuda::CUDAGuard guard(q.device());
+  TORCH_CHECK(q.dim() == 4 && k.dim() == 4 && v.dim() == 4 && dout.dim() == 4, "q/k/v/do must be [B, S, H, 128]");
+  TORCH_CHECK(q.size(3) == 128 && k.size(3) == 128 && v.size(3) == 128, "head_dim must be 128");
+  TORCH_CHECK(k.sizes() == v.sizes() && q.size(0) == k.size(0) && dout.sizes() == q.sizes(), "shape mismatch");
+  for (const Tensor* t : {&q, &k, &v, &dout}) {
+    TORCH_CHECK(t->stride(3) == 1, "inner stride must be 1");
+    for (int d = 0; d < 3; ++d) TORCH_CHECK(t->stride(d) % 8 == 0, "strides must be multiples of 8");
+  }
+  const int64_t B = q.size(0), Sq = q.size(1), Hq = q.size(2), Skv = k.size(1), Hkv = k.size(2);
+  TORCH_CHECK(lse.is_cuda() && lse.scalar_type() == at::kFloat && lse.is_contiguous() && lse.numel() == B * Hq * Sq,
+              "lse must be contiguous fp32 [B, Hq, Sq]");
+  TORCH_CHECK(delta.is_cuda() && delta.scalar_type() == at::kFloat && delta.is_contiguous() &&
+                  delta.numel() == B * Hq * Sq, "delta must be contiguous fp32 [B, Hq, Sq]");
+  Tensor dq = at::empty({B, Sq, Hq, 128}, q.options());
+  Tensor dk = at::empty({B, Skv, Hkv, 128}, q.options());
+  Tensor dv = at::empty({B, Skv, Hkv, 128}, q.options());
+  cosmos::AttnBwdArgs a;
+  a.Q = q.data_ptr(); a.K = k.data_ptr(); a.V = v.data_ptr(); a.dO = dout.data_ptr();
+  a.lse = lse.data_ptr<float>(); a.delta = delta.data_ptr<float>();
+  a.dQ = dq.data_ptr(); a.dK = dk.data_ptr(); a.dV = dv.data_ptr();
+  a.B = (int)B; a.Sq = (int)Sq; a.Skv = (int)Skv; a.Hq = (int)Hq; a.Hkv = (int)Hkv;
+  a.q_stride_b = q.stride(0); a.q_stride_s = q.stride(1); a.q_stride_h = q.stride(2);
+  a.k_stride_b = k.stride(0); a.k_stride_s = k.stride(1); a.k_stride_h = k.stride(2);
+  a.v_stride_b = v.stride(0); a.v_stride_s = v.stride(1); a.v_stride_h = v.stride(2);
+  a.do_stride_b = dout.stride(0); a.do_stride_s = dout.stride(1); a.do_stride_h = dout.stride(2);
+  a.scale = (float)scale; a.mask = (int)mask; a.n_ar = (int)n_ar;
+  a.status = status_tensor(q.get_device()).data_ptr<int>();
+  cosmos::flash_attn_bwd(a, cur_stream());
+  return {dq, dk, dv};
+}
+
 std::tuple<Tensor, Tensor> rmsnorm(const Tensor& x, const OptT& gamma, double eps, const OptT& residual) {
   check_bf16_cuda(x, "x");
   c10::cuda::CUDAGuard guard(x.device());
@@ -669,6 +706,7 @@ TORCH_LIBRARY(cosmos_b200, m) {
   m.def("gemm_ex", &gemm_ex);
   m.def("attn_bwd_scores", &attn_bwd_scores);
   m.def("attn_fwd", &attn_fwd);
+  m.def("attn_bwd", &attn_bwd);
   m.def("rmsnorm", &rmsnorm);
   m.def("adaln_rmsnorm", &adaln_rmsnorm);
   m.def("mrope_", &mrope_);

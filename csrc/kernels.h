@@ -98,6 +98,31 @@ struct AttnArgs {
 };
 void flash_attn_fwd(const AttnArgs& a, cudaStream_t stream);
 
+// Flash attention backward (attn_bwd_tcgen05.cu): dQ, dK, dV from Q, K, V, dO, the forward's
+// log-sum-exp and delta = rowsum(dO * O). Inputs [B, S, H, 128] bf16 with element strides; outputs
+// contiguous [B, Sq, Hq, 128] / [B, Skv, Hkv, 128] bf16; lse, delta [B, Hq, Sq] fp32.
+struct AttnBwdArgs {
+  const void* Q = nullptr;
+  const void* K = nullptr;
+  const void* V = nullptr;
+  const void* dO = nullptr;
+  const float* lse = nullptr;
+  const float* delta = nullptr;
+  void* dQ = nullptr;
+  void* dK = nullptr;
+  void* dV = nullptr;
+  int B = 1, Sq = 0, Skv = 0, Hq = 0, Hkv = 0;
+  long long q_stride_b = 0, q_stride_s = 0, q_stride_h = 0;
+  long long k_stride_b = 0, k_stride_s = 0, k_stride_h = 0;
+  long long v_stride_b = 0, v_stride_s = 0, v_stride_h = 0;
+  long long do_stride_b = 0, do_stride_s = 0, do_stride_h = 0;
+  float scale = 0.f;
+  int mask = MASK_FULL;
+  int n_ar = 0;
+  int* status = nullptr;
+};
+void flash_attn_bwd(const AttnBwdArgs& a, cudaStream_t stream);
+
 // ---- bandwidth kernels (elementwise.cu) ----
 void rmsnorm(const void* x, const void* gamma, void* y, long long rows, int d, float eps,
              const void* residual_in, void* residual_out, cudaStream_t s);

@@ -398,19 +398,27 @@ def test_linear_autograd_on_own_kernels():
     _close(w.grad, wf.grad, 8e-2, 3e-2, "linear dW")
 
 
-@pytest.mark.parametrize("sq,skv,hq,hkv,mask", [(384, 384, 4, 2, ops.MASK_FULL), (300, 300, 2, 1, ops.MASK_CAUSAL),
-                                                 (256, 520, 2, 2, ops.MASK_FULL)])
-def test_attention_autograd_on_own_kernels(sq, skv, hq, hkv, mask):
+@pytest.mark.parametrize("materialized", [False, True])
+@pytest.mark.parametrize("b,sq,skv,hq,hkv,mask,n_ar", [
+    (1, 384, 384, 4, 2, ops.MASK_FULL, 0), (1, 300, 300, 2, 1, ops.MASK_CAUSAL, 0),
+    (1, 256, 520, 2, 2, ops.MASK_FULL, 0), (2, 640, 640, 8, 2, ops.MASK_MOT, 200),
+    (1, 130, 700, 4, 1, ops.MASK_CAUSAL, 0), (2, 1024, 1024, 4, 4, ops.MASK_FULL, 0)])
+def test_attention_autograd_on_own_kernels(b, sq, skv, hq, hkv, mask, n_ar, materialized, monkeypatch):
     from cosmos_b200.ops import autograd as own
+    monkeypatch.setattr(own, "_MATERIALIZED", materialized)
+    if materialized and b * hq > 8:
+        pytest.skip("the per-head variant is covered by the smaller cases")
     torch.manual_seed(23)
-    q = _rand(1, sq, hq, 128).requires_grad_(True)
-    k = _rand(1, skv, hkv, 128).requires_grad_(True)
-    v = _rand(1, skv, hkv, 128).requires_grad_(True)
-    g = _rand(1, sq, hq, 128)
-    o = own.attention(q, k, v, None, mask, 0)
+    q = _rand(b, sq, hq, 128).requires_grad_(True)
+    k = _rand(b, skv, hkv, 128).requires_grad_(True)
+    v = _rand(b, skv, hkv, 128).requires_grad_(True)
+    g = _rand(b, sq, hq, 128)
+    o = own.attention(q, k, v, None, mask, n_ar)
     o.backward(g)
+    torch.cuda.synchronize()
+    ops.check_status()
     qf, kf, vf = (t.detach().float().requires_grad_(True) for t in (q, k, v))
-    of, _ = ref.attention(qf, kf, vf, None, mask, 0)
+    of, _ = ref.attention(qf, kf, vf, None, mask, n_ar)
     of.backward(g.float())
     _close(o, of, 2e-2, 2e-2, "attention fwd")
     _close(q.grad, qf.grad, 3e-2, 3e-2, "dQ")
