@@ -187,6 +187,11 @@ def qkv_project_local(h, w, cos, sin, q_norm, k_norm, cfg: MoTConfig):
         qkv = qkv.view(b, s, hq + 2 * hk, hd)
         return qkv[:, :, :hq], qkv[:, :, hq:hq + hk], qkv[:, :, hq + hk:]
     qkv = ops.gemm(h, w).view(b, s, hq + 2 * hk, hd)
+    if hd == 128 and ops._train_cuda(qkv, q_norm, k_norm):
+        # training on CUDA: norm + rotary + q/k/v split as one autograd function on the kernels
+        from ..ops import autograd as own
+        q, k, v = own.qkv_post(qkv.reshape(b * s, hq + 2 * hk, hd), hq, cos, sin, gq, gk, cfg.rms_eps)
+        return q.view(b, s, hq, hd), k.view(b, s, hk, hd), v.view(b, s, hk, hd)
     q, k, v = qkv[:, :, :hq], qkv[:, :, hq:hq + hk], qkv[:, :, hq + hk:]
     q = ops.ref.mrope(q, cos, sin, gq, cfg.rms_eps)
     k = ops.ref.mrope(k, cos, sin, gk, cfg.rms_eps)

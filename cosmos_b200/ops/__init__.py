@@ -63,6 +63,18 @@ def _use_cuda(t: torch.Tensor, *others) -> bool:
     return True
 
 
+def _train_cuda(t: torch.Tensor, *others) -> bool:
+    """True when a call that needs gradients should run the autograd functions built on the sm_100a
+    kernels (ops/autograd.py): CUDA bf16 input, gradients required, kernel library present.
+    COSMOS_TRAIN_LIBRARY_BACKWARD=1 selects the PyTorch / library baseline instead."""
+    import os
+    if not (t.is_cuda and t.dtype == torch.bfloat16 and _grad_needed(t, *others)):
+        return False
+    if os.environ.get("COSMOS_TRAIN_LIBRARY_BACKWARD") == "1":
+        return False
+    return load_extension()
+
+
 class _Counted:
     """Proxy over torch.ops.cosmos_b200 that counts kernel launches (one per op call)."""
 
@@ -182,12 +194,20 @@ def rmsnorm(x, gamma=None, eps: float = 1e-6, residual=None):
     if _use_cuda(x, gamma, residual):
         y, r = _k().rmsnorm(x.contiguous(), gamma, eps, None if residual is None else residual.contiguous())
         return y, (r if residual is not None else None)
+    if residual is None and _train_cuda(x, gamma) and x.shape[-1] % 8 == 0 and x.shape[-1] <= 8192:
+        from . import autograd as own
+        return own.rmsnorm(x, gamma, eps), None
     return ref.rmsnorm(x, gamma, eps, residual)
 
 
 def adaln_rmsnorm(x, gamma, shift, scale, rows_per_batch: int, eps: float = 1e-6):
     if _use_cuda(x, gamma, shift, scale):
         return _k().adaln_rmsnorm(x.contiguous(), gamma, shift, scale, rows_per_batch, eps)
+    d = x.shape[-1]
+    if (_train_cuda(x, gamma, shift, scale) and d % 8 == 0 and d <= 8192 and shift.dtype == torch.bfloat16
+            and (x.numel() // d) % rows_per_batch == 0 and shift.numel() // d in (1, (x.numel() // d) // rows_per_batch)):
+        from . import autograd as own
+        return own.adaln_rmsnorm(x, gamma, shift, scale, rows_per_batch, eps)
     return ref.adaln_rmsnorm(x, gamma, shift, scale, rows_per_batch, eps)
 
 
@@ -203,12 +223,29 @@ def mrope(x, cos=None, sin=None, gamma=None, eps: float = 1e-6):
 def gated_residual(x, f, gate=None, rows_per_batch: int = 1):
     if _use_cuda(x, f, gate):
         return _k().gated_residual(x.contiguous(), f.contiguous(), gate, rows_per_batch)
+    if _train_cuda(x, f, gate) and _gate_ok(x, gate, rows_per_batch):
+        from . import autograd as own
+        return own.gated_residual(x, f, gate, rows_per_batch)
     return ref.gated_residual(x, f, gate, rows_per_batch)
+
+
+def _gate_ok(x, gate, rows_per_batch: int) -> bool:
+    d = x.shape[-1]
+    if d % 8 != 0 or x.dtype != torch.bfloat16:
+        return False
+    if gate is None:
+        return True
+    rows = x.numel() // d
+    return (gate.dtype == torch.bfloat16 and rows_per_batch > 0 and rows % rows_per_batch == 0
+            and gate.numel() // d in (1, rows // rows_per_batch))
 
 
 def swiglu(gate_up):
     if _use_cuda(gate_up, gate_up):
         return _k().swiglu(gate_up.contiguous())
+    if _train_cuda(gate_up) and gate_up.shape[-1] % 16 == 0:
+        from . import autograd as own
+        return own.swiglu(gate_up)
     return ref.swiglu(gate_up)
 
 

@@ -29,11 +29,20 @@ def gemm(a, w, bias=None, epi: int = EPI_PLAIN, resid=None, gate=None, rows_per_
             acc = acc + bias
     else:
         acc = F.linear(a, w, bias)
+    own_ew = _own_kernels(acc) and acc.shape[-1] % 16 == 0
     if epi == EPI_SWIGLU:
+        if own_ew:
+            from . import autograd as own
+            return own.swiglu(acc)
         g, u = acc.chunk(2, dim=-1)
         return F.silu(g) * u
     if epi == EPI_GATED_RESID:
         n = acc.shape[-1]
+        if own_ew and resid.dtype == torch.bfloat16:
+            from . import _gate_ok
+            if _gate_ok(acc, gate, rows_per_batch):
+                from . import autograd as own
+                return own.gated_residual(resid.reshape(acc.shape), acc, gate, rows_per_batch if gate is not None else 1)
         flat = acc.reshape(-1, n)
         if gate is not None:
             flat = flat * ref._rows_to_batch(gate, flat.shape[0], rows_per_batch)

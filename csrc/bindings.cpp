@@ -476,6 +476,130 @@ Tensor swiglu(const Tensor& gate_up) {
   return y;
 }
 
+// ---- backward of the bandwidth kernels
+// Returns (dx, part): part [B, blocks, 3, d] fp32 per-block column sums (d shift, d scale, d gamma) when
+// `want_cols`, else an empty tensor. gamma / scale optional; scale [B or 1, d] (unit inner stride).
+std::tuple<Tensor, Tensor> rmsnorm_bwd(const Tensor& x, const Tensor& dy, const OptT& gamma, const OptT& scale,
+                                       int64_t rows_per_batch, double eps, bool want_cols) {
+  check_bf16_cuda(x, "x"); check_bf16_cuda(dy, "dy");
+  c10::cuda::CUDAGuard guard(x.device());
+  TORCH_CHECK(x.is_contiguous() && dy.is_contiguous() && x.sizes() == dy.sizes(), "x / dy must be contiguous and alike");
+  const int64_t d = x.size(-1), rows = x.numel() / d;
+  if (rows_per_batch <= 0) rows_per_batch = rows;
+  TORCH_CHECK(rows % rows_per_batch == 0, "rows must be a multiple of rows_per_batch");
+  const int64_t B = rows / rows_per_batch;
+  long long ms = 0;
+  if (gamma.has_value() && gamma->defined()) { check_bf16_cuda(*gamma, "gamma"); TORCH_CHECK(gamma->numel() == d && gamma->is_contiguous()); }
+  const void* scp = nullptr;
+  if (scale.has_value() && scale->defined()) {
+    check_bf16_cuda(*scale, "scale");
+    TORCH_CHECK(scale->size(-1) == d && scale->stride(-1) == 1);
+    Tensor s2 = scale->dim() == 1 ? scale->unsqueeze(0) : scale->reshape({-1, d});
+    TORCH_CHECK(s2.size(0) == 1 || s2.size(0) == B, "scale must have one row or one row per batch");
+    ms = s2.size(0) == 1 ? 0 : s2.stride(0);
+    TORCH_CHECK(ms % 8 == 0);
+    scp = s2.data_ptr();
+  }
+  Tensor dx = at::empty_like(x);
+  Tensor rinv = at::empty({rows}, x.options().dtype(at::kFloat));
+  Tensor part = want_cols ? at::empty({B, (int64_t)cosmos::rmsnorm_bwd_blocks((int)rows_per_batch), 3, d},
+                                      x.options().dtype(at::kFloat))
+                          : at::empty({0}, x.options().dtype(at::kFloat));
+  cosmos::rmsnorm_bwd(x.data_ptr(), dy.data_ptr(), opt_ptr(gamma), scp, rows, (int)d, (int)rows_per_batch, ms,
+                      (float)eps, dx.data_ptr(), rinv.data_ptr<float>(), want_cols ? part.data_ptr<float>() : nullptr,
+                      cur_stream());
+  return {dx, part};
+}
+
+// y = resid + gate[b] * f  ->  (df, part [B, blocks, d] per-block sums of dy * f)
+std::tuple<Tensor, Tensor> gated_residual_bwd(const Tensor& dy, const Tensor& f, const Tensor& gate,
+                                              int64_t rows_per_batch) {
+  check_bf16_cuda(dy, "dy"); check_bf16_cuda(f, "f"); check_bf16_cuda(gate, "gate");
+  c10::cuda::CUDAGuard guard(dy.device());
+  TORCH_CHECK(dy.is_contiguous() && f.is_contiguous() && dy.sizes() == f.sizes());
+  const int64_t d = dy.size(-1), rows = dy.numel() / d;
+  if (rows_per_batch <= 0) rows_per_batch = rows;
+  TORCH_CHECK(rows % rows_per_batch == 0, "rows must be a multiple of rows_per_batch");
+  const int64_t B = rows / rows_per_batch;
+  TORCH_CHECK(gate.size(-1) == d && gate.stride(-1) == 1);
+  Tensor g2 = gate.dim() == 1 ? gate.unsqueeze(0) : gate.reshape({-1, d});
+  TORCH_CHECK(g2.size(0) == 1 || g2.size(0) == B, "gate must have one row or one row per batch");
+  const long long gs = g2.size(0) == 1 ? 0 : g2.stride(0);
+  TORCH_CHECK(gs % 8 == 0);
+  Tensor df = at::empty_like(dy);
+  Tensor part = at::empty({B, (int64_t)cosmos::rmsnorm_bwd_blocks((int)rows_per_batch), d}, dy.options().dtype(at::kFloat));
+  cosmos::gated_residual_bwd(dy.data_ptr(), f.data_ptr(), g2.data_ptr(), rows, (int)d, (int)rows_per_batch, gs,
+                             df.data_ptr(), part.data_ptr<float>(), cur_stream());
+  return {df, part};
+}
+
+Tensor swiglu_bwd(const Tensor& gate_up, const Tensor& dy) {
+  check_bf16_cuda(gate_up, "gate_up"); check_bf16_cuda(dy, "dy");
+  c10::cuda::CUDAGuard guard(gate_up.device());
+  TORCH_CHECK(gate_up.is_contiguous() && dy.is_contiguous() && gate_up.size(-1) % 16 == 0 &&
+              dy.size(-1) * 2 == gate_up.size(-1) && dy.numel() * 2 == gate_up.numel());
+  const int64_t dff = dy.size(-1), rows = dy.numel() / dff;
+  Tensor out = at::empty_like(gate_up);
+  cosmos::swiglu_bwd(gate_up.data_ptr(), dy.data_ptr(), out.data_ptr(), rows, (int)dff, cur_stream());
+  return out;
+}
+
+static void rope_tables(const OptT& cos_t, const OptT& sin_t, const float*& c, const float*& s, int& rr) {
+  c = s = nullptr;
+  rr = 1;
+  if (cos_t.has_value() && cos_t->defined()) {
+    TORCH_CHECK(sin_t.has_value() && sin_t->defined(), "cos without sin");
+    TORCH_CHECK(cos_t->is_cuda() && cos_t->scalar_type() == at::kFloat && cos_t->is_contiguous() && cos_t->size(-1) == 64 &&
+                sin_t->is_cuda() && sin_t->scalar_type() == at::kFloat && sin_t->is_contiguous() && sin_t->sizes() == cos_t->sizes(),
+                "cos/sin must be contiguous fp32 [rope_rows, 64]");
+    c = cos_t->data_ptr<float>();
+    s = sin_t->data_ptr<float>();
+    rr = (int)(cos_t->numel() / 64);
+  }
+}
+
+// qkv [rows.., Hq + 2 Hkv, 128] -> (q [rows, Hq, 128], k [rows, Hkv, 128], v [rows, Hkv, 128])
+std::tuple<Tensor, Tensor, Tensor> qkv_post_fwd(const Tensor& qkv, int64_t n_q_heads, const OptT& cos_t,
+                                                const OptT& sin_t, const OptT& gamma_q, const OptT& gamma_k,
+                                                double eps) {
+  check_bf16_cuda(qkv, "qkv");
+  c10::cuda::CUDAGuard guard(qkv.device());
+  TORCH_CHECK(qkv.dim() >= 3 && qkv.size(-1) == 128 && qkv.is_contiguous(), "qkv must be contiguous [.., heads, 128]");
+  const int64_t heads = qkv.size(-2), rows = qkv.numel() / (heads * 128), Hq = n_q_heads;
+  TORCH_CHECK(Hq > 0 && heads > Hq && (heads - Hq) % 2 == 0, "bad head split");
+  const int64_t Hkv = (heads - Hq) / 2;
+  const float *c, *s;
+  int rr;
+  rope_tables(cos_t, sin_t, c, s, rr);
+  Tensor q = at::empty({rows, Hq, 128}, qkv.options()), k = at::empty({rows, Hkv, 128}, qkv.options()),
+         v = at::empty({rows, Hkv, 128}, qkv.options());
+  cosmos::qkv_post_fwd(qkv.data_ptr(), rows, (int)Hq, (int)Hkv, c, s, rr, opt_ptr(gamma_q), opt_ptr(gamma_k),
+                       (float)eps, q.data_ptr(), k.data_ptr(), v.data_ptr(), cur_stream());
+  return {q, k, v};
+}
+
+// -> (d_qkv like qkv, part [blocks, 2, 128] per-block sums of d gamma_q / d gamma_k)
+std::tuple<Tensor, Tensor> qkv_post_bwd(const Tensor& qkv, const Tensor& dq, const Tensor& dk, const Tensor& dv,
+                                        const OptT& cos_t, const OptT& sin_t, const OptT& gamma_q,
+                                        const OptT& gamma_k, double eps) {
+  check_bf16_cuda(qkv, "qkv"); check_bf16_cuda(dq, "dq"); check_bf16_cuda(dk, "dk"); check_bf16_cuda(dv, "dv");
+  c10::cuda::CUDAGuard guard(qkv.device());
+  TORCH_CHECK(qkv.is_contiguous() && dq.is_contiguous() && dk.is_contiguous() && dv.is_contiguous());
+  const int64_t heads = qkv.size(-2), rows = qkv.numel() / (heads * 128);
+  const int64_t Hq = dq.numel() / (rows * 128), Hkv = dk.numel() / (rows * 128);
+  TORCH_CHECK(Hq + 2 * Hkv == heads && dv.numel() == dk.numel(), "gradient shapes do not match qkv");
+  const float *c, *s;
+  int rr;
+  rope_tables(cos_t, sin_t, c, s, rr);
+  Tensor d_qkv = at::empty_like(qkv);
+  const int blocks = cosmos::qkv_post_bwd_blocks(rows, (int)Hq, (int)Hkv);
+  Tensor part = at::empty({blocks, 2, 128}, qkv.options().dtype(at::kFloat));
+  cosmos::qkv_post_bwd(qkv.data_ptr(), dq.data_ptr(), dk.data_ptr(), dv.data_ptr(), rows, (int)Hq, (int)Hkv, c, s, rr,
+                       opt_ptr(gamma_q), opt_ptr(gamma_k), (float)eps, d_qkv.data_ptr(), part.data_ptr<float>(),
+                       cur_stream());
+  return {d_qkv, part};
+}
+
 // x fp32 [rows, d] updated in place: x += dt * cfg(vc, vu)
 void cfg_euler_step_(Tensor x, const Tensor& vc, const OptT& vu, double guidance, double dt, bool normalize) {
   c10::cuda::CUDAGuard guard(x.device());
@@ -707,6 +831,11 @@ TORCH_LIBRARY(cosmos_b200, m) {
   m.def("attn_bwd_scores", &attn_bwd_scores);
   m.def("attn_fwd", &attn_fwd);
   m.def("attn_bwd", &attn_bwd);
+  m.def("rmsnorm_bwd", &rmsnorm_bwd);
+  m.def("gated_residual_bwd", &gated_residual_bwd);
+  m.def("swiglu_bwd", &swiglu_bwd);
+  m.def("qkv_post_fwd", &qkv_post_fwd);
+  m.def("qkv_post_bwd", &qkv_post_bwd);
   m.def("rmsnorm", &rmsnorm);
   m.def("adaln_rmsnorm", &adaln_rmsnorm);
   m.def("mrope_", &mrope_);

@@ -179,6 +179,28 @@ void decode_qkv_post(const void* qkv, int B, int Hq, int Hkv, const float* cos_t
                      const void* gamma_q, const void* gamma_k, float eps, const long long* slots, void* q_out,
                      void* k_cache, void* v_cache, int page_size, cudaStream_t s);
 
+// ---- backward of the bandwidth kernels (elementwise_bwd.cu) ----
+// RMSNorm / AdaLN-RMSNorm: dx [rows, d]; with `part` != null also per-block column sums
+// part[B][rmsnorm_bwd_blocks(rows_per_batch)][3][d] (d shift, d scale, d gamma), B = rows / rows_per_batch.
+// gamma / scale may be null (treated as 1 / 0); scale rows are mod_stride elements apart.
+int rmsnorm_bwd_blocks(int rows_per_batch);
+void rmsnorm_bwd(const void* x, const void* dy, const void* gamma, const void* scale, long long rows, int d,
+                 int rows_per_batch, long long mod_stride, float eps, void* dx, float* rinv, float* part,
+                 cudaStream_t s);
+// y = resid + gate[b] * f: df = dy * gate[b], part[B][blocks][d] = per-block sums of dy * f.
+void gated_residual_bwd(const void* dy, const void* f, const void* gate, long long rows, int d, int rows_per_batch,
+                        long long gate_stride, void* df, float* part, cudaStream_t s);
+void swiglu_bwd(const void* gate_up, const void* dy, void* d_gate_up, long long rows, int dff, cudaStream_t s);
+// qkv [rows, Hq + 2 Hkv, 128] -> q, k, v with q/k RMS-norm and rotary; and its backward
+// (part[qkv_post_bwd_blocks][2][128] = per-block sums of d gamma_q, d gamma_k).
+void qkv_post_fwd(const void* qkv, long long rows, int Hq, int Hkv, const float* cos_t, const float* sin_t,
+                  int rope_rows, const void* gamma_q, const void* gamma_k, float eps, void* q, void* k, void* v,
+                  cudaStream_t s);
+int qkv_post_bwd_blocks(long long rows, int Hq, int Hkv);
+void qkv_post_bwd(const void* qkv, const void* dq, const void* dk, const void* dv, long long rows, int Hq, int Hkv,
+                  const float* cos_t, const float* sin_t, int rope_rows, const void* gamma_q, const void* gamma_k,
+                  float eps, void* d_qkv, float* part, cudaStream_t s);
+
 // ---- communication kernels over peer mappings (comm.cu) ----
 // pads_dev / bufs_dev / grads_dev / srcs_dev: device arrays with one address per rank of the group.
 // Signal pads are int32 arrays laid out as [slot][64]; epochs must grow monotonically per slot.
