@@ -306,14 +306,20 @@ def decode_qkv_post(qkv, n_q_heads: int, cos, sin, q_gamma, k_gamma, eps: float,
 
 
 def paged_decode(q, k_cache, v_cache, block_table, seq_lens, scale: Optional[float] = None,
-                 n_splits: Optional[int] = None, scratch=None, max_len: Optional[int] = None):
+                 n_splits: Optional[int] = None, scratch=None, max_len: Optional[int] = None, impl: int = 0):
     """q [B, Hq, 128] against a paged cache [pages, Hkv, page_size, 128] -> [B, Hq, 128].
     `max_len` (an upper bound of seq_lens known on the host) picks the kv split count without
-    a device synchronisation."""
+    a device synchronisation. impl 0 = tensor-core kernel (TMA page copies + tcgen05) when the page
+    size is 8..128 and the GQA group is 1, 2, 4 or 8, else the CUDA-core kernel; impl 1 forces the latter."""
     scale = scale if scale is not None else 1.0 / math.sqrt(q.shape[-1])
     if _use_cuda(q) and q.shape[-1] == 128:
+        page = k_cache.shape[2]
+        group = q.shape[1] // k_cache.shape[1]
+        if not (page in (8, 16, 32, 64, 128) and group in (1, 2, 4, 8)):
+            impl = 1
         if n_splits is None:
-            ml = max_len if max_len is not None else block_table.shape[1] * k_cache.shape[2]
-            n_splits = int(torch.ops.cosmos_b200.paged_decode_pick_splits(q.shape[0], k_cache.shape[1], ml))
-        return _k().paged_decode(q.contiguous(), k_cache, v_cache, block_table, seq_lens, scale, n_splits, scratch)
+            ml = max_len if max_len is not None else block_table.shape[1] * page
+            n_splits = int(torch.ops.cosmos_b200.paged_decode_pick_splits(q.shape[0], k_cache.shape[1], ml, impl))
+        return _k().paged_decode(q.contiguous(), k_cache, v_cache, block_table, seq_lens, scale, n_splits, scratch,
+                                 impl)
     return paged_decode_ref(q, k_cache, v_cache, block_table, seq_lens, scale)

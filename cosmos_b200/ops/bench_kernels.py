@@ -126,12 +126,14 @@ def main():
         table = torch.randperm(n_pages, device=dev).int().view(b, -1)
         lens = torch.full((b,), ctx, dtype=torch.int32, device=dev)
         q = torch.randn(b, hq, 128, device=dev).bfloat16()
-        ms = timeit(lambda: ops.paged_decode(q, kc, vc, table, lens, 128 ** -0.5), args.iters, flush)
-        gbs = 2.0 * b * ctx * hkv * 128 * 2 / ms / 1e6
-        rec = {"kernel": "paged_decode", "shape": [b, hq, hkv, ctx], "ms": round(ms, 4), "gbs": round(gbs, 1),
-               f"frac_of_{src}_hbm": round(gbs / bw_peak, 3)}
-        out.append(rec)
-        print(json.dumps(rec), flush=True)
+        for impl, name in ((0, "paged_decode_tc (TMA + tcgen05)"), (1, "paged_decode (CUDA cores)")):
+            ms = timeit(lambda: ops.paged_decode(q, kc, vc, table, lens, 128 ** -0.5, max_len=ctx, impl=impl),
+                        args.iters, flush)
+            gbs = 2.0 * b * ctx * hkv * 128 * 2 / ms / 1e6
+            rec = {"kernel": name, "shape": [b, hq, hkv, ctx], "ms": round(ms, 4), "gbs": round(gbs, 1),
+                   f"frac_of_{src}_hbm": round(gbs / bw_peak, 3)}
+            out.append(rec)
+            print(json.dumps(rec), flush=True)
     if "vae" in what:
         # tokenizer decode of one clip through the channels-last implicit-GEMM decoder
         from cosmos_b200.models.vae import CausalVideoVAE

@@ -619,8 +619,9 @@ void l2_flush_(Tensor buf) {
 }
 
 // Decode attention over a paged KV cache; `scratch` (fp32) holds the split-KV partials.
+// impl: 0 = tensor-core kernel (TMA + tcgen05) when page size and GQA group allow it, 1 = CUDA-core kernel
 Tensor paged_decode(const Tensor& q, const Tensor& k_cache, const Tensor& v_cache, const Tensor& block_table,
-                    const Tensor& seq_lens, double scale, int64_t n_splits, const OptT& scratch) {
+                    const Tensor& seq_lens, double scale, int64_t n_splits, const OptT& scratch, int64_t impl) {
   check_bf16_cuda(q, "q"); check_bf16_cuda(k_cache, "k_cache"); check_bf16_cuda(v_cache, "v_cache");
   c10::cuda::CUDAGuard guard(q.device());
   TORCH_CHECK(q.dim() == 3 && q.size(2) == 128 && q.is_contiguous(), "q must be contiguous [B, Hq, 128]");
@@ -636,6 +637,8 @@ Tensor paged_decode(const Tensor& q, const Tensor& k_cache, const Tensor& v_cach
   a.B = (int)q.size(0); a.Hq = (int)q.size(1); a.Hkv = (int)k_cache.size(1);
   a.page_size = (int)k_cache.size(2); a.max_pages = (int)block_table.size(1);
   a.scale = (float)scale; a.n_splits = (int)n_splits;
+  a.num_pages = (int)k_cache.size(0); a.impl = (int)impl;
+  a.status = status_tensor(q.get_device()).data_ptr<int>();
   Tensor out = at::empty_like(q);
   a.out = out.data_ptr();
   Tensor ws;
@@ -653,8 +656,9 @@ Tensor paged_decode(const Tensor& q, const Tensor& k_cache, const Tensor& v_cach
   return out;
 }
 
-int64_t paged_decode_pick_splits(int64_t B, int64_t Hkv, int64_t max_len) {
-  return cosmos::paged_decode_pick_splits((int)B, (int)Hkv, (int)max_len);
+int64_t paged_decode_pick_splits(int64_t B, int64_t Hkv, int64_t max_len, int64_t impl) {
+  return impl == 1 ? cosmos::paged_decode_pick_splits((int)B, (int)Hkv, (int)max_len)
+                   : cosmos::paged_decode_tc_pick_splits((int)B, (int)Hkv, (int)max_len);
 }
 
 // Causal 3x3x3 convolution as an implicit GEMM. x: padded channels-last volume [F, Hp, Wp, C]

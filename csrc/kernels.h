@@ -165,8 +165,15 @@ struct PagedDecodeArgs {
   int n_splits = 1;
   void* scratch = nullptr;  // >= paged_decode_scratch_bytes(B, Hq, n_splits) when n_splits > 1
   size_t scratch_bytes = 0;
+  int num_pages = 0;        // pages in the cache tensors; needed by the tensor-core kernel (TMA bounds)
+  int* status = nullptr;    // status word for bounded waits (tensor-core kernel)
+  int impl = 0;             // 0 = tensor-core kernel when the shape allows it, 1 = CUDA-core kernel
 };
+// kv splits for the CUDA-core kernel (several CTAs per SM) and for the tensor-core kernel (one per SM)
 int paged_decode_pick_splits(int B, int Hkv, int max_len);
+int paged_decode_tc_pick_splits(int B, int Hkv, int max_len);
+bool paged_decode_tc_supported(const PagedDecodeArgs& a);
+void paged_decode_tc_launch(const PagedDecodeArgs& a, float* pa, float* pm, cudaStream_t s);
 size_t paged_decode_scratch_bytes(int B, int Hq, int n_splits);
 void paged_decode(const PagedDecodeArgs& a, cudaStream_t s);
 // Scatters new K/V rows [N, Hkv, 128] into the paged caches at flat slots (page * page_size + offset).

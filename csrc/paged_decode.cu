@@ -274,12 +274,16 @@ void paged_decode(const PagedDecodeArgs& a, cudaStream_t s) {
     pa = reinterpret_cast<float*>(a.scratch);
     pm = pa + (size_t)a.B * a.Hq * a.n_splits * 128;
   }
-  switch (group) {
-    case 1: launch_pd<1>(a, pa, pm, s); break;
-    case 2: launch_pd<2>(a, pa, pm, s); break;
-    case 4: launch_pd<4>(a, pa, pm, s); break;
-    case 8: launch_pd<8>(a, pa, pm, s); break;
-    default: throw std::runtime_error("paged_decode: GQA group size must be 1, 2, 4 or 8");
+  if (a.impl == 0 && paged_decode_tc_supported(a)) {
+    paged_decode_tc_launch(a, pa, pm, s);
+  } else {
+    switch (group) {
+      case 1: launch_pd<1>(a, pa, pm, s); break;
+      case 2: launch_pd<2>(a, pa, pm, s); break;
+      case 4: launch_pd<4>(a, pa, pm, s); break;
+      case 8: launch_pd<8>(a, pa, pm, s); break;
+      default: throw std::runtime_error("paged_decode: GQA group size must be 1, 2, 4 or 8");
+    }
   }
   if (a.n_splits > 1)
     cb::paged_decode_merge_kernel<<<a.B * a.Hq, 128, 0, s>>>(pa, pm, a.n_splits, (bf16*)a.out);

@@ -252,8 +252,12 @@ def test_cfg_euler_step(normalize):
     (3, 8, 2, 32, [700, 1, 333], 4),
     (4, 4, 4, 16, [513, 512, 511, 64], 3),
     (2, 8, 1, 16, [2000, 1500], None),
+    (3, 4, 2, 8, [1000, 129, 128], 2),
+    (2, 32, 8, 128, [3000, 4097], None),
 ])
-def test_paged_decode(b, hq, hkv, page, lens, splits):
+@pytest.mark.parametrize("impl", [0, 1])
+def test_paged_decode(b, hq, hkv, page, lens, splits, impl):
+    """impl 0: TMA + tcgen05 kernel, impl 1: CUDA-core kernel; both against the fp32 definition."""
     torch.manual_seed(16)
     max_pages = (max(lens) + page - 1) // page + 1
     n_pages = b * max_pages + 3
@@ -262,7 +266,9 @@ def test_paged_decode(b, hq, hkv, page, lens, splits):
     perm = torch.randperm(n_pages, device=DEV)[:b * max_pages].view(b, max_pages).int()
     sl = torch.tensor(lens, device=DEV, dtype=torch.int32)
     q = _rand(b, hq, 128)
-    got = ops.paged_decode(q, kc, vc, perm, sl, n_splits=splits, max_len=max(lens))
+    got = ops.paged_decode(q, kc, vc, perm, sl, n_splits=splits, max_len=max(lens), impl=impl)
+    torch.cuda.synchronize()
+    ops.check_status()
     want = ops.paged_decode_ref(q.float(), kc.float(), vc.float(), perm, sl)
     _close(got, want, 2e-2, 2e-2, "paged decode")
 

@@ -57,7 +57,7 @@ def test_noalloc_matches_allocating_entry_point_twice():
     for seed, (b, hq, hkv, page, lens, splits) in enumerate([(3, 8, 2, 16, [900, 17, 400], 5),
                                                               (2, 4, 1, 32, [1500, 1200], 8)]):
         q, kc, vc, table, sl = _case(100 + seed, b, hq, hkv, page, lens)
-        want = ops.paged_decode(q, kc, vc, table, sl, n_splits=splits)
+        want = ops.paged_decode(q, kc, vc, table, sl, n_splits=splits, impl=1)  # the same CUDA-core kernel
         before = torch.cuda.memory_allocated()
         rc, got, msg = _call(fn, q, kc, vc, table, sl, splits)
         torch.cuda.synchronize()
