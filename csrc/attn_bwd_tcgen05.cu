@@ -13,8 +13,10 @@
 //   dQ kernel: one CTA owns a 128-row Q / dO tile and streams K/V tiles:
 //       S = Q K^T, dP = dO V^T (SS), dS = P (dP - D) scale -> TMEM (bf16), dQ += dS K (TS).
 //
-// Warp roles (256 threads): warp 0 TMA producer, warp 1 MMA issuer, warps 4..7 element-wise math
-// and epilogue (one TMEM lane = one K/V row resp. one Q row per thread).
+// Warp roles (384 threads): warp 0 TMA producer, warp 1 MMA issuer, warps 4..11 element-wise math
+// and epilogue: two warpgroups, each thread owns one TMEM lane (a K/V row resp. a Q row) and one
+// 64-column half of the score tile; a warpgroup writes its bf16 P / dS into the first half of its
+// own fp32 score columns, so the two never touch each other's inputs.
 // D = rowsum(dO * O) and the log-sum-exp of the forward pass come in as [B, Hq, Sq] fp32.
 // Masks as in the forward kernel (full, causal, Mixture-of-Transformers block mask).
 // Every wait is bounded; on expiry the kernel records a status code and unwinds.
@@ -23,7 +25,7 @@
 
 namespace cb {
 
-constexpr int BWD_THREADS = 256;
+constexpr int BWD_THREADS = 384;
 constexpr int BT = 128;                         // tile rows (queries and keys), = head_dim
 constexpr int BTILE_BYTES = BT * 128 * 2;       // 32 KB
 constexpr int BHALF_BYTES = BTILE_BYTES / 2;    // one 64-column half
@@ -100,7 +102,7 @@ __device__ __forceinline__ void bwd_init_barriers(const BwdSmem& sm, volatile in
     mbar_init(sm.bar + 8u * (BB_EMPTY + s), 1);
   }
   mbar_init(sm.bar + 8u * BB_S, 1);
-  mbar_init(sm.bar + 8u * BB_P, 128);
+  mbar_init(sm.bar + 8u * BB_P, 256);
   mbar_init(sm.bar + 8u * BB_DONE, 1);
   *abort_flag = 0;
   fence_barrier_init();
@@ -123,10 +125,10 @@ __device__ __forceinline__ void bwd_drain(const BwdSmem& sm, bool fixed_issued, 
     mbar_wait(sm.bar + 8u * (BB_FULL + i % BWD_NST), (i / BWD_NST) & 1, &no_abort, nullptr, 0);
 }
 
-// fp32 accumulator rows (this thread's TMEM lane, 128 columns at `taddr`) -> 128 bf16 at dst.
-__device__ __forceinline__ void bwd_store_row(uint32_t taddr, bf16* dst, bool row_ok) {
+// fp32 accumulator row (this thread's TMEM lane, columns [c_begin, c_end) at `taddr`) -> bf16 at dst.
+__device__ __forceinline__ void bwd_store_row(uint32_t taddr, bf16* dst, bool row_ok, int c_begin, int c_end) {
 #pragma unroll 1
-  for (int c = 0; c < 128; c += 32) {
+  for (int c = c_begin; c < c_end; c += 32) {
     uint32_t o[32];
     tmem_ld32(taddr + c, o);
     tmem_wait_ld();
@@ -243,18 +245,22 @@ flash_attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid
       ok = mbar_wait(sm.bar + 8u * BB_P, it & 1, abort_flag, p.status, ST_TIMEOUT_MMA);
       if (!ok) break;
       tc_fence_after();
+      // bf16 P^T / dS^T of query columns [64 w, 64 w + 64) sit at 32-bit columns [64 w, 64 w + 32)
 #pragma unroll
       for (int kk = 0; kk < 8; ++kk)
-        mma_ts(T_DV, T_ST + kk * 8, do_mn + uint64_t(kk * (2048 >> 4)), idesc_ts, (it > 0 || kk > 0) ? 1u : 0u);
+        mma_ts(T_DV, T_ST + (kk >> 2) * 64 + (kk & 3) * 8, do_mn + uint64_t(kk * (2048 >> 4)), idesc_ts,
+               (it > 0 || kk > 0) ? 1u : 0u);
 #pragma unroll
       for (int kk = 0; kk < 8; ++kk)
-        mma_ts(T_DK, T_DPT + kk * 8, q_mn + uint64_t(kk * (2048 >> 4)), idesc_ts, (it > 0 || kk > 0) ? 1u : 0u);
+        mma_ts(T_DK, T_DPT + (kk >> 2) * 64 + (kk & 3) * 8, q_mn + uint64_t(kk * (2048 >> 4)), idesc_ts,
+               (it > 0 || kk > 0) ? 1u : 0u);
       tc_commit(sm.bar + 8u * (BB_EMPTY + s));
     }
     if (ok && n_it > 0) tc_commit(sm.bar + 8u * BB_DONE);
   } else if (warp >= 4) {
     // ---------------- element-wise math: this thread owns K/V row kv0 + r (TMEM lane r)
     const int quad = warp & 3;
+    const int wg = (warp - 4) >> 2;  // which 64-column half of the score tile
     const int r = quad * 32 + lane;
     const int kv = kv0 + r;
     const uint32_t lane_addr = uint32_t(quad * 32) << 16;
@@ -263,13 +269,13 @@ flash_attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid
       const int head = kvh * p.group + it / n_qt;
       const int q0 = (i0 + it % n_qt) * BT;
       const int buf = it & 1;
-      {
+      if (wg == 0) {
         const int qi = q0 + r;
         const long long off = ((long long)batch * p.Hq + head) * p.Sq + qi;
         lse_s[buf * BT + r] = qi < p.Sq ? p.lse[off] * 1.4426950408889634f : INFINITY;
         dlt_s[buf * BT + r] = qi < p.Sq ? p.delta[off] : 0.f;
       }
-      named_bar_sync(1, 128);
+      named_bar_sync(1, 256);
       if (!mbar_wait(sm.bar + 8u * BB_S, it & 1, abort_flag, p.status, ST_TIMEOUT_SOFTMAX)) {
         ok = false;
         break;
@@ -278,8 +284,8 @@ flash_attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid
       const bool need_mask = bwd_tile_needs_mask(kv0, q0, p);
       const float* ls = lse_s + buf * BT;
       const float* dl = dlt_s + buf * BT;
-#pragma unroll 1
-      for (int c = 0; c < 2; ++c) {  // 64 query columns per round
+      {
+        const int c = wg;  // this warpgroup's 64 query columns
         uint32_t pk[32], dsk[32];
 #pragma unroll
         for (int hh = 0; hh < 2; ++hh) {
@@ -305,10 +311,10 @@ flash_attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid
             dsk[hh * 16 + i] = pack_bf16(ds0, ds1);
           }
         }
-        // bf16 P^T / dS^T alias the fp32 scores: 64 columns become 32 32-bit columns at 32 * c,
-        // which only covers score columns that are already in registers
-        tmem_st32(T_ST + lane_addr + 32 * c, pk);
-        tmem_st32(T_DPT + lane_addr + 32 * c, dsk);
+        // bf16 P^T / dS^T alias the fp32 scores: the 64 columns of this warpgroup become 32 32-bit
+        // columns at 64 * c, which only covers score columns that this thread already holds
+        tmem_st32(T_ST + lane_addr + 64 * c, pk);
+        tmem_st32(T_DPT + lane_addr + 64 * c, dsk);
       }
       tmem_wait_st();
       tc_fence_before();
@@ -319,17 +325,15 @@ flash_attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid
     bf16* dv_row = p.dV + (((long long)batch * p.Skv + kv) * p.Hkv + kvh) * 128;
     if (n_it == 0) {
       if (row_ok) {
-        for (int c = 0; c < 16; ++c) {
-          reinterpret_cast<uint4*>(dk_row)[c] = make_uint4(0, 0, 0, 0);
-          reinterpret_cast<uint4*>(dv_row)[c] = make_uint4(0, 0, 0, 0);
-        }
+        for (int c = 0; c < 16; ++c) reinterpret_cast<uint4*>(wg == 0 ? dv_row : dk_row)[c] = make_uint4(0, 0, 0, 0);
       }
     } else {
       if (ok) ok = mbar_wait(sm.bar + 8u * BB_DONE, 0, abort_flag, p.status, ST_TIMEOUT_SOFTMAX);
       if (ok) {
         tc_fence_after();
-        bwd_store_row(T_DV + lane_addr, dv_row, row_ok);
-        bwd_store_row(T_DK + lane_addr, dk_row, row_ok);
+        // one accumulator per warpgroup
+        if (wg == 0) bwd_store_row(T_DV + lane_addr, dv_row, row_ok, 0, 128);
+        else bwd_store_row(T_DK + lane_addr, dk_row, row_ok, 0, 128);
       }
     }
   }
@@ -435,13 +439,15 @@ flash_attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_c
       tc_fence_after();
 #pragma unroll
       for (int kk = 0; kk < 8; ++kk)
-        mma_ts(T_DQ, T_S + kk * 8, k_mn + uint64_t(kk * (2048 >> 4)), idesc_ts, (j > 0 || kk > 0) ? 1u : 0u);
+        mma_ts(T_DQ, T_S + (kk >> 2) * 64 + (kk & 3) * 8, k_mn + uint64_t(kk * (2048 >> 4)), idesc_ts,
+               (j > 0 || kk > 0) ? 1u : 0u);
       tc_commit(sm.bar + 8u * (BB_EMPTY + s));
     }
     if (ok) tc_commit(sm.bar + 8u * BB_DONE);
   } else if (warp >= 4) {
     // ---------------- element-wise math: this thread owns query row q0 + r (TMEM lane r)
     const int quad = warp & 3;
+    const int wg = (warp - 4) >> 2;  // which 64-column half of the score tile
     const int r = quad * 32 + lane;
     const int qi = q0 + r;
     const uint32_t lane_addr = uint32_t(quad * 32) << 16;
@@ -458,8 +464,8 @@ flash_attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_c
       tc_fence_after();
       const int kv0 = j * BT;
       const bool need_mask = bwd_tile_needs_mask(kv0, q0, p);
-#pragma unroll 1
-      for (int c = 0; c < 2; ++c) {  // 64 key columns per round
+      {
+        const int c = wg;  // this warpgroup's 64 key columns
         uint32_t dsk[32];
 #pragma unroll
         for (int hh = 0; hh < 2; ++hh) {
@@ -482,7 +488,7 @@ flash_attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_c
             dsk[hh * 16 + i] = pack_bf16(ds0, ds1);
           }
         }
-        tmem_st32(T_S + lane_addr + 32 * c, dsk);  // bf16 dS aliases the scores already in registers
+        tmem_st32(T_S + lane_addr + 64 * c, dsk);  // bf16 dS aliases score columns this thread already holds
       }
       tmem_wait_st();
       tc_fence_before();
@@ -492,7 +498,7 @@ flash_attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_c
     if (ok) {
       tc_fence_after();
       bf16* dq_row = p.dQ + (((long long)batch * p.Sq + qi) * p.Hq + head) * 128;
-      bwd_store_row(T_DQ + lane_addr, dq_row, row_ok);
+      bwd_store_row(T_DQ + lane_addr, dq_row, row_ok, 64 * wg, 64 * wg + 64);
     }
   }
 
