@@ -332,9 +332,12 @@ class MoTModel(nn.Module):
         return F.embedding(ids, self.embed)
 
     def ar_forward(self, x: torch.Tensor, pos: torch.Tensor, past: Optional[List[KV]] = None,
-                   ctx: AttnContext = LOCAL_ATTN, layer_params: Optional[Callable] = None
+                   ctx: AttnContext = LOCAL_ATTN, layer_params: Optional[Callable] = None,
+                   deepstack: Optional[Sequence[torch.Tensor]] = None, vision_mask: Optional[torch.Tensor] = None
                    ) -> Tuple[torch.Tensor, List[KV]]:
-        """x [B, S, d] embeddings, pos [3, S] -> (hidden [B, S, d] before the final norm, per-layer KV)."""
+        """x [B, S, d] embeddings, pos [3, S] -> (hidden [B, S, d] before the final norm, per-layer KV).
+        `deepstack` (features [n_vision, d] from the vision encoder) are added to the output of layer i,
+        i < len(deepstack), at the positions flagged by `vision_mask` [B, S]."""
         cfg = self.cfg
         cos, sin = rope.rope_tables(pos, cfg.head_dim, cfg.rope_theta, cfg.mrope_section)
         kvs: List[KV] = []
@@ -342,6 +345,10 @@ class MoTModel(nn.Module):
             p = layer.views() if layer_params is None else layer_params("ar", i)
             x, kv = ar_block(cfg, p, x, cos, sin, None if past is None else past[i], ctx)
             kvs.append(kv)
+            if deepstack is not None and vision_mask is not None and i < len(deepstack):
+                n = int(vision_mask.sum())
+                x = x.clone()
+                x[vision_mask] = x[vision_mask] + deepstack[i].to(x.dtype).reshape(-1, x.shape[-1])[:n]
         return x, kvs
 
     def lm_logits(self, hidden: torch.Tensor) -> torch.Tensor:

@@ -101,9 +101,10 @@ class ReasonerEngine:
         return torch.cat(parts, dim=1)[:, :s]
 
     @torch.no_grad()
-    def prefill(self, x: torch.Tensor, pos: torch.Tensor) -> Tuple[torch.Tensor, List[KV]]:
+    def prefill(self, x: torch.Tensor, pos: torch.Tensor, deepstack=None, vision_mask=None
+                ) -> Tuple[torch.Tensor, List[KV]]:
         """x [B, S, d] -> (logits of the last position [B, V] fp32, per-layer KV)."""
-        h, kvs = self.model.ar_forward(x, pos, None, self.ctx)
+        h, kvs = self.model.ar_forward(x, pos, None, self.ctx, deepstack=deepstack, vision_mask=vision_mask)
         return self.model.lm_logits(h[:, -1:]).float()[:, 0], kvs
 
     @torch.no_grad()
@@ -117,8 +118,8 @@ class ReasonerEngine:
     @torch.no_grad()
     def generate(self, ids: Sequence[int], dc: DecodingConfig, eos_ids: Sequence[int] = (),
                  vision_embeds: Optional[torch.Tensor] = None, vision_token_id: Optional[int] = None,
-                 grids: Sequence[Tuple[int, int, int]] = (), on_token: Optional[Callable[[int], None]] = None
-                 ) -> Tuple[List[int], dict]:
+                 grids: Sequence[Tuple[int, int, int]] = (), on_token: Optional[Callable[[int], None]] = None,
+                 deepstack: Optional[Sequence[torch.Tensor]] = None) -> Tuple[List[int], dict]:
         dev = next(self.model.parameters()).device
         ids_t = torch.tensor([list(ids)], dtype=torch.long, device=dev)
         vmask = (ids_t == vision_token_id) if vision_token_id is not None and vision_embeds is not None else None
@@ -128,7 +129,7 @@ class ReasonerEngine:
         if dc.seed is not None:
             gen = torch.Generator(device=dev)
             gen.manual_seed(dc.seed)
-        logits, kvs = self.prefill(x, pos)
+        logits, kvs = self.prefill(x, pos, deepstack if vmask is not None else None, vmask)
         next_pos = rope.next_start(pos)
         out: List[int] = []
         for _ in range(dc.max_new_tokens):

@@ -1,10 +1,12 @@
 """Vision encoder of the Reasoner (AR side): a ViT over 16x16 patches with temporal patch 2 and
 2x2 spatial merge, producing one d_model embedding per merged patch (Qwen3-VL conventions, which
 the reference's Reasoner follows: reference README.md:145,286 and
-cookbooks/cosmos3/reasoner/reasoner_prompt_guide.md:77-99)."""
+cookbooks/cosmos3/reasoner/reasoner_prompt_guide.md:77-99). With `cfg.vit_deepstack` the features
+after the listed blocks go through mergers of their own and are handed to the language tower, which
+adds them to the hidden states of its first layers at the vision positions (DeepStack)."""
 from __future__ import annotations
 
-from typing import Tuple
+from typing import List, Tuple
 
 import torch
 import torch.nn as nn
@@ -41,6 +43,11 @@ class VisionEncoder(nn.Module):
         self.norm = nn.LayerNorm(hdim, eps=1e-6)
         m = cfg.vit_spatial_merge
         self.merge = nn.Sequential(nn.Linear(hdim * m * m, hdim * m * m), nn.GELU(), nn.Linear(hdim * m * m, cfg.d_model))
+        self.deepstack = tuple(i for i in cfg.vit_deepstack if 0 <= i < cfg.vit_depth)
+        self.deepstack_norm = nn.ModuleList([nn.LayerNorm(hdim * m * m, eps=1e-6) for _ in self.deepstack])
+        self.deepstack_merge = nn.ModuleList([
+            nn.Sequential(nn.Linear(hdim * m * m, hdim * m * m), nn.GELU(), nn.Linear(hdim * m * m, cfg.d_model))
+            for _ in self.deepstack])
         nn.init.normal_(self.pos, std=0.02)
 
     def grid(self, frames: int, height: int, width: int) -> Tuple[int, int, int]:
@@ -50,8 +57,9 @@ class VisionEncoder(nn.Module):
         unit = c.vit_patch * c.vit_spatial_merge
         return t, height // unit, width // unit
 
-    def forward(self, video: torch.Tensor) -> Tuple[torch.Tensor, Tuple[int, int, int]]:
-        """video [T, 3, H, W] in [-1, 1] (H, W multiples of patch*merge) -> ([t*h*w, d_model], (t, h, w))."""
+    def forward(self, video: torch.Tensor, return_deepstack: bool = False):
+        """video [T, 3, H, W] in [-1, 1] (H, W multiples of patch*merge) -> ([t*h*w, d_model], (t, h, w))
+        and, with `return_deepstack`, the list of DeepStack features [t*h*w, d_model] (one per listed block)."""
         c = self.cfg
         p, tp, m = c.vit_patch, c.vit_temporal_patch, c.vit_spatial_merge
         t_in, _, hh, ww = video.shape
@@ -64,8 +72,18 @@ class VisionEncoder(nn.Module):
         pos = F.interpolate(self.pos.view(1, 48, 48, -1).permute(0, 3, 1, 2).float(), size=(gh, gw), mode="bilinear",
                             align_corners=False).permute(0, 2, 3, 1).reshape(1, gh * gw, -1).to(x.dtype)
         x = x + pos
-        for blk in self.blocks:  # attention within each temporal slice
+        def merged(y):  # [t, gh * gw, hidden] -> [t * (gh/m) * (gw/m), hidden * m * m]
+            y = y.view(t, gh // m, m, gw // m, m, -1).permute(0, 1, 3, 2, 4, 5)
+            return y.reshape(t * (gh // m) * (gw // m), -1)
+
+        deep: List[torch.Tensor] = []
+        for i, blk in enumerate(self.blocks):  # attention within each temporal slice
             x = blk(x)
-        x = self.norm(x).view(t, gh // m, m, gw // m, m, -1).permute(0, 1, 3, 2, 4, 5)
-        x = x.reshape(t * (gh // m) * (gw // m), -1)
-        return self.merge(x), (t, gh // m, gw // m)
+            if i in self.deepstack:
+                k = self.deepstack.index(i)
+                deep.append(self.deepstack_merge[k](self.deepstack_norm[k](merged(x))))
+        out = self.merge(merged(self.norm(x)))
+        grid = (t, gh // m, gw // m)
+        if return_deepstack:
+            return out, grid, deep
+        return out, grid

@@ -171,6 +171,22 @@ class FSDP:
                                                sq, red)
                 reduced[key] = red
             sq.mul_(inv_ws * inv_ws)
+        elif self._local_kernel():
+            # gradients are already local (one rank, or the NCCL reduce-scatter ran in backward): the same
+            # optimizer kernel with this rank's gradient shard as its only source
+            ptrs: Dict[Tuple[str, int], torch.Tensor] = {}
+            for key, u in self.units.items():
+                g = u.shard.grad
+                if g is None:
+                    continue
+                g = g.contiguous()
+                u.shard.grad = g  # keep the tensor alive until the update kernel below has read it
+                ptrs[key] = torch.tensor([g.data_ptr()], dtype=torch.int64, device=u.device)
+                red = torch.empty(u.ns, dtype=torch.float32, device=u.device)
+                torch.ops.cosmos_b200.rs_adamw(ptrs[key], 1, 0, u.master, u.exp_avg, u.exp_avg_sq, u.shard.data, 1.0, 0.0,
+                                               b1, b2, self.eps, 0.0, self.step_count, 1, sq, red)
+                reduced[key] = red
+            sq.mul_(inv_ws * inv_ws)
         else:
             for key, u in self.units.items():
                 if u.shard.grad is not None:
@@ -194,6 +210,11 @@ class FSDP:
                                                u.shard.data, clip * inv_ws, self.lr, b1, b2, self.eps, self.wd,
                                                self.step_count, 2, None, reduced[key])
                 u._has_grad = False
+            elif self._local_kernel():
+                torch.ops.cosmos_b200.rs_adamw(ptrs[key], 1, 0, u.master, u.exp_avg, u.exp_avg_sq, u.shard.data,
+                                               clip * inv_ws, self.lr, b1, b2, self.eps, self.wd, self.step_count, 2,
+                                               None, reduced[key])
+                u.shard.grad = None
             else:
                 _adamw(u.master, u.exp_avg, u.exp_avg_sq, reduced[key] * clip, self.lr, b1, b2, self.eps, self.wd,
                        bc1, bc2)
@@ -206,6 +227,14 @@ class FSDP:
         if self.fused:
             self.sg.barrier(slot=4)  # peers are done reading this step's gradients
         return total
+
+    def _local_kernel(self) -> bool:
+        """AdamW through the optimizer kernel on this rank's own gradient shards (no peer reads)."""
+        if self.fused or not self.units:
+            return False
+        u = next(iter(self.units.values()))
+        from .. import ops
+        return u.device.type == "cuda" and u.dtype == torch.bfloat16 and ops.load_extension(build_if_missing=False)
 
     # ------------------------------------------------------------------ checkpointing
     def state_tensors(self) -> Dict[str, torch.Tensor]:

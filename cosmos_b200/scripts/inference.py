@@ -154,7 +154,7 @@ def run_reasoner_sample(engine, tokenizer, vit, spec: InferenceSpec, out_dir: Pa
     from ..models.vae import CausalVideoVAE
 
     messages_content = []
-    vision_embeds, grids, n_vis = None, [], []
+    vision_embeds, grids, n_vis, deep = None, [], [], None
     if spec.vision_path:
         frames, _ = media.read_video(spec.resolve(spec.vision_path), max_frames=16)
         unit = engine.cfg.vit_patch * engine.cfg.vit_spatial_merge
@@ -165,7 +165,7 @@ def run_reasoner_sample(engine, tokenizer, vit, spec: InferenceSpec, out_dir: Pa
         fr = np.stack([np.asarray(Image.fromarray(f).resize((w, h))) for f in frames])
         vid = CausalVideoVAE.from_uint8(torch.from_numpy(fr)[None])[0].permute(1, 0, 2, 3).to(device)
         with torch.no_grad():
-            vision_embeds, grid = vit(vid)
+            vision_embeds, grid, deep = vit(vid, return_deepstack=True)
         grids, n_vis = [grid], [grid[0] * grid[1] * grid[2]]
         messages_content.append({"type": "image_url" if frames.shape[0] == 1 else "video_url"})
     messages_content.append({"type": "text", "text": spec.prompt_text()})
@@ -177,7 +177,7 @@ def run_reasoner_sample(engine, tokenizer, vit, spec: InferenceSpec, out_dir: Pa
     t0 = time.perf_counter()
     out_ids, usage = engine.generate(ids, dc, eos_ids=(tokenizer.eos_id, tokenizer.eot_id),
                                      vision_embeds=vision_embeds, vision_token_id=pad_id if grids else None,
-                                     grids=grids)
+                                     grids=grids, deepstack=deep)
     dt = time.perf_counter() - t0
     text = tokenizer.decode(out_ids)
     if is_writer:

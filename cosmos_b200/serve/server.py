@@ -243,7 +243,7 @@ class Cosmos3Server:
         tok = self.pipe.tokenizer
         messages = body["messages"]
         extra = body.get("extra_body") or {}
-        vision_embeds, grids, n_vis, norm_msgs = [], [], [], []
+        vision_embeds, grids, n_vis, norm_msgs, deep = [], [], [], [], []
         dev = self.pipe.device
         for m in messages:
             content = m["content"]
@@ -253,8 +253,9 @@ class Cosmos3Server:
                     kind = part.get("type")
                     if kind in ("image_url", "video_url"):
                         frames = self._load_media(part[kind]["url"], kind == "video_url", extra)
-                        emb, grid = self._encode_vision(frames, dev)
+                        emb, grid, ds = self._encode_vision(frames, dev)
                         vision_embeds.append(emb)
+                        deep.append(ds)
                         grids.append(grid)
                         n_vis.append(grid[0] * grid[1] * grid[2])
                     parts.append(part)
@@ -274,13 +275,15 @@ class Cosmos3Server:
             first.setdefault("t", time.time())
 
         ve = torch.cat(vision_embeds) if vision_embeds else None
+        # DeepStack features of all media items, level by level
+        ds = [torch.cat([d[k] for d in deep]) for k in range(len(deep[0]))] if deep and deep[0] else None
         # image and video pads share one mask here: every pad position takes the next vision row
         pad_id = tok.video_pad_id if any(g[0] > 1 for g in grids) else tok.image_pad_id
         if ve is not None and len({tok.image_pad_id, tok.video_pad_id}) == 2:
             ids = [pad_id if t in (tok.image_pad_id, tok.video_pad_id) else t for t in ids]
         with self.gen_lock:
             out_ids, usage = self.reasoner.generate(ids, dc, (tok.eos_id, tok.eot_id), ve, pad_id if ve is not None else None,
-                                                    grids, on_token)
+                                                    grids, on_token, deepstack=ds)
         text = tok.decode(out_ids)
         t1 = time.time()
         self.metrics.record((first.get("t", t1) - t0) * 1e3, (t1 - t0) * 1e3, usage["completion_tokens"])
@@ -322,7 +325,7 @@ class Cosmos3Server:
         fr = np.stack([np.asarray(Image.fromarray(f).resize((w, h))) for f in frames])
         vid = CausalVideoVAE.from_uint8(torch.from_numpy(fr)[None])[0].permute(1, 0, 2, 3).to(dev)
         with torch.no_grad():
-            return self.vit(vid)
+            return self.vit(vid, return_deepstack=True)
 
     def models(self) -> dict:
         return {"object": "list", "data": [{"id": self.model_name, "object": "model", "owned_by": "cosmos_b200"}]}
@@ -412,6 +415,23 @@ def create_app(server: Cosmos3Server):
     return app
 
 
+def apply_deploy_config(args) -> None:
+    """Folds a deploy-config YAML into the parsed arguments: `stages[*].model_config.guardrails: false`
+    switches the guardrails off, `model_class_name` overrides the flag of the same name."""
+    if not getattr(args, "deploy_config", None):
+        return
+    import yaml
+
+    with open(args.deploy_config) as f:
+        cfg = yaml.safe_load(f) or {}
+    for stage in cfg.get("stages") or []:
+        mc = stage.get("model_config") or {}
+        if mc.get("guardrails") is False:
+            args.no_guardrails = True
+        if stage.get("model_class_name"):
+            args.model_class_name = stage["model_class_name"]
+
+
 def main(argv=None) -> int:
     import argparse
 
@@ -429,7 +449,14 @@ def main(argv=None) -> int:
     ap.add_argument("--enable-layerwise-offload", action="store_true")
     ap.add_argument("--no-guardrails", action="store_true")
     ap.add_argument("--dtype", default="bf16")
+    ap.add_argument("--deploy-config", default=None,
+                    help="YAML with stages[].model_config.{guardrails, offload_guardrail_models} "
+                         "(reference README.md:405-423)")
+    ap.add_argument("--mm-encoder-tp-mode", default="data", choices=["data", "weights"],
+                    help="the vision encoder is replicated on every rank (data); accepted for CLI compatibility")
+    ap.add_argument("--media-io-kwargs", default=None, help='JSON, e.g. {"video": {"num_frames": -1}}')
     args = ap.parse_args(argv)
+    apply_deploy_config(args)
     import uvicorn
 
     from ..models.reasoner import ReasonerEngine

@@ -167,3 +167,33 @@ def test_vae_shapes_and_chunked_equivalence():
         assert torch.allclose(z[:, :, :2], z2[:, :, :2], atol=1e-6)
     u8 = vae.to_uint8(rec)
     assert u8.shape == (1, 9, 32, 32, 3) and u8.dtype == torch.uint8
+
+
+def test_deepstack_vision_features_enter_first_layers():
+    """DeepStack: the vision encoder returns one merged feature map per listed block; the AR tower adds
+    map i to the output of layer i at the vision positions, so zeros change nothing and, the tower being
+    causal, positions before the first vision token never change."""
+    from cosmos_b200.models.vit import VisionEncoder
+    cfg = tiny_config(n_layers=3, vit_deepstack=(0, 1))
+    torch.manual_seed(0)
+    vit = VisionEncoder(cfg).float()
+    video = torch.rand(2, 3, 64, 64) * 2 - 1
+    emb, grid, deep = vit(video, return_deepstack=True)
+    n = grid[0] * grid[1] * grid[2]
+    assert emb.shape == (n, cfg.d_model) and len(deep) == 2 and all(d.shape == (n, cfg.d_model) for d in deep)
+    emb2, grid2 = vit(video)
+    assert torch.equal(emb, emb2) and grid2 == grid
+    model = MoTModel(cfg, dtype=torch.float32, device="cpu")
+    model.init_weights(seed=1)
+    s, first = n + 6, 3
+    x = torch.randn(1, s, cfg.d_model)
+    pos = rope.text_positions(s, 0, "cpu")
+    mask = torch.zeros(1, s, dtype=torch.bool)
+    mask[0, first:first + n] = True
+    with torch.no_grad():
+        base, _ = model.ar_forward(x, pos)
+        zero, _ = model.ar_forward(x, pos, deepstack=[torch.zeros_like(d) for d in deep], vision_mask=mask)
+        full, _ = model.ar_forward(x, pos, deepstack=deep, vision_mask=mask)
+    assert torch.allclose(base, zero)
+    assert torch.allclose(base[:, :first], full[:, :first], atol=1e-6)
+    assert (base[:, first:] - full[:, first:]).abs().max() > 1e-4

@@ -104,3 +104,19 @@ def test_chat_completions_text_and_image(client):
     assert out["usage"]["completion_tokens"] <= 5 and out["usage"]["prompt_tokens"] > 4
     m = client.get("/metrics").json()
     assert m["requests"] >= 1 and m["avg_request_latency_ms"] > 0
+
+
+def test_deploy_config_switches_guardrails_off(tmp_path):
+    import argparse
+    from cosmos_b200.serve.server import apply_deploy_config
+
+    cfg = tmp_path / "no_guardrails.yaml"
+    cfg.write_text("async_chunk: false\nstages:\n  - stage_id: 0\n    max_num_seqs: 1\n"
+                   "    model_class_name: Cosmos3OmniDiffusersPipeline\n    model_config:\n      guardrails: false\n"
+                   "      offload_guardrail_models: false\n")
+    args = argparse.Namespace(deploy_config=str(cfg), no_guardrails=False, model_class_name="x")
+    apply_deploy_config(args)
+    assert args.no_guardrails is True and args.model_class_name == "Cosmos3OmniDiffusersPipeline"
+    args = argparse.Namespace(deploy_config=None, no_guardrails=False, model_class_name="x")
+    apply_deploy_config(args)
+    assert args.no_guardrails is False
