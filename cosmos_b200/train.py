@@ -41,6 +41,9 @@ class TrainConfig:
     t_mean: float = 0.0
     t_std: float = 1.0
     fused: bool = True
+    # seconds a rank waits on the host for its peers before a step; None = no liveness protocol
+    # (parallel/health.py: bounded per-step rendezvous + heartbeats over the c10d store)
+    health_timeout_s: Optional[float] = None
 
 
 class Trainer:
@@ -63,6 +66,12 @@ class Trainer:
             from .parallel.ulysses import UlyssesAttn
             self.ctx = UlyssesAttn(self.cfg, mesh.group("cp"), mesh.group_ranks["cp"], dev, fused=False)
         self.cp, self.cp_rank = mesh.size("cp"), mesh.index("cp")
+        self.hb = None
+        if tc.health_timeout_s is not None and mesh.world > 1 and dist.is_initialized():
+            from torch.distributed.distributed_c10d import _get_default_store
+
+            from .parallel.health import Heartbeat
+            self.hb = Heartbeat(_get_default_store(), mesh.rank, mesh.world)
 
     def loss(self, latents: torch.Tensor, text_ids: torch.Tensor, generator: Optional[torch.Generator] = None,
              t: Optional[torch.Tensor] = None, eps: Optional[torch.Tensor] = None) -> torch.Tensor:
@@ -102,6 +111,15 @@ class Trainer:
         return F.mse_loss(pred.float(), target.float())
 
     def train_step(self, latents, text_ids, generator=None, **kw) -> Dict[str, float]:
+        """One optimizer step. With `health_timeout_s` the step starts only after every rank has shown up
+        for it on the host (PeerFailure otherwise), and a failure of this rank is announced to the others."""
+        if self.hb is not None:
+            from .parallel.health import guarded_step
+            return guarded_step(self.hb, lambda: self._train_step(latents, text_ids, generator, **kw),
+                                self.tc.health_timeout_s)
+        return self._train_step(latents, text_ids, generator, **kw)
+
+    def _train_step(self, latents, text_ids, generator=None, **kw) -> Dict[str, float]:
         loss = self.loss(latents, text_ids, generator, **kw)
         loss.backward()
         gnorm = self.fsdp.step()
@@ -173,6 +191,8 @@ def main(argv=None) -> int:
     ap.add_argument("--save-dir", default=None)
     ap.add_argument("--resume", action="store_true")
     ap.add_argument("--layers", type=int, default=0)
+    ap.add_argument("--health-timeout", type=float, default=None,
+                    help="seconds to wait on the host for every rank before each step (peer failure detection)")
     args = ap.parse_args(argv)
     from .parallel.runtime import init_distributed
 
@@ -192,7 +212,8 @@ def main(argv=None) -> int:
     shard_ws = dshard * args.cp_size
     model = MoTModel(cfg, dtype=dtype, device=dev, pad_to=128 * shard_ws)
     model.init_weights(seed=0)
-    tr = Trainer(model, mesh, TrainConfig(lr=args.lr, checkpoint_blocks=not args.no_checkpoint, train_ar=args.train_ar))
+    tr = Trainer(model, mesh, TrainConfig(lr=args.lr, checkpoint_blocks=not args.no_checkpoint, train_ar=args.train_ar,
+                                         health_timeout_s=args.health_timeout))
     step0 = tr.load(args.save_dir) if (args.resume and args.save_dir) else 0
     c, t, h, w = (int(v) for v in args.latent.split(","))
     # ranks of one cp group see the same clip; different dp ranks see different clips
