@@ -8,8 +8,11 @@ in a Diffusers-style component layout:
     <root>/sound_tokenizer/{config.json, model.safetensors}
     <root>/scheduler/scheduler_config.json
 
-Loading streams tensor by tensor (`safe_open`), so a rank can read only what it needs and copy
-straight into its (possibly sharded) parameter storage. Training state (optimizer shards,
+Loading goes through the package's own memory-mapped reader (C++, `csrc/safetensors_reader.cpp`:
+every offset of the header is validated against the file before a byte is copied, and a tensor or
+any element range of it is copied straight from the mapping into the destination, CPU or CUDA), so
+a rank reads only what it needs, e.g. its shard of a flat parameter (`read_range`). Without the
+built extension the `safetensors` package's `safe_open` is used. Training state (optimizer shards,
 RNG, step) is saved per rank with an atomic rename.
 """
 from __future__ import annotations
@@ -61,6 +64,54 @@ def _atomic_save(tensors, path: Path, metadata=None) -> None:
     os.replace(tmp, path)
 
 
+class _PyReader:
+    """`safe_open`-based stand-in with the interface of the native `SafetensorsFile`."""
+
+    def __init__(self, path: str):
+        self._f = safe_open(path, "pt")
+        self._meta = self._f.metadata() or {}
+
+    def keys(self):
+        return list(self._f.keys())
+
+    def has(self, name):
+        return name in self._f.keys()
+
+    def shape(self, name):
+        return list(self._f.get_slice(name).get_shape())
+
+    def get(self, name):
+        return self._f.get_tensor(name)
+
+    def metadata(self, key):
+        return self._meta.get(key, "")
+
+    def metadata_keys(self):
+        return sorted(self._meta)
+
+    def read_into(self, name, dst, elem_offset):
+        src = self._f.get_tensor(name).reshape(-1)[elem_offset:elem_offset + dst.numel()]
+        dst.view(-1).copy_(src)
+
+
+def open_reader(path):
+    """Reader for one .safetensors file: the native memory-mapped one when the extension is built."""
+    from .. import ops
+
+    if ops.load_extension(build_if_missing=False):
+        return torch.classes.cosmos_b200.SafetensorsFile(str(path))
+    return _PyReader(str(path))
+
+
+def read_range(model_dir, name: str, dst: torch.Tensor, elem_offset: int = 0) -> None:
+    """Fills `dst` (contiguous, any device) with elements [elem_offset, elem_offset + dst.numel()) of the
+    flattened checkpoint tensor `name`: a rank's shard of a parameter without touching the rest."""
+    files = tensor_files(model_dir)
+    if name not in files:
+        raise KeyError(f"checkpoint has no tensor {name}")
+    open_reader(files[name]).read_into(name, dst, int(elem_offset))
+
+
 def tensor_files(model_dir) -> Dict[str, Path]:
     """tensor name -> file that holds it."""
     model_dir = Path(model_dir)
@@ -71,8 +122,7 @@ def tensor_files(model_dir) -> Dict[str, Path]:
     single = model_dir / "model.safetensors"
     if not single.exists():
         raise FileNotFoundError(f"no safetensors checkpoint under {model_dir}")
-    with safe_open(str(single), "pt") as f:
-        return {k: single for k in f.keys()}
+    return {k: single for k in open_reader(single).keys()}
 
 
 def load_into(model_dir, targets: Dict[str, torch.Tensor], strict: bool = True,
@@ -89,13 +139,25 @@ def load_into(model_dir, targets: Dict[str, torch.Tensor], strict: bool = True,
             by_file.setdefault(files[k], []).append(k)
     with torch.no_grad():
         for path, names in by_file.items():
-            with safe_open(str(path), "pt") as f:
-                for k in names:
-                    src = slicer(k, f.get_slice(k)) if slicer else f.get_tensor(k)
-                    dst = targets[k]
-                    if tuple(src.shape) != tuple(dst.shape):
-                        raise ValueError(f"{k}: checkpoint shape {tuple(src.shape)} != model {tuple(dst.shape)}")
-                    dst.copy_(src.to(dst.dtype))
+            if slicer is not None:
+                with safe_open(str(path), "pt") as f:
+                    for k in names:
+                        src = slicer(k, f.get_slice(k))
+                        dst = targets[k]
+                        if tuple(src.shape) != tuple(dst.shape):
+                            raise ValueError(f"{k}: checkpoint shape {tuple(src.shape)} != model {tuple(dst.shape)}")
+                        dst.copy_(src.to(dst.dtype))
+                continue
+            f = open_reader(path)
+            for k in names:
+                dst = targets[k]
+                shape = tuple(f.shape(k))
+                if shape != tuple(dst.shape):
+                    raise ValueError(f"{k}: checkpoint shape {shape} != model {tuple(dst.shape)}")
+                if dst.is_contiguous():
+                    f.read_into(k, dst, 0)  # straight from the mapping into the parameter storage
+                else:
+                    dst.copy_(f.get(k).to(dst.dtype))
     return missing
 
 
@@ -140,9 +202,9 @@ def save_train_state(path, step: int, tensors: Dict[str, torch.Tensor], extra: O
 
 
 def load_train_state(path):
-    with safe_open(str(path), "pt") as f:
-        meta = f.metadata()
-        tensors = {k: f.get_tensor(k) for k in f.keys()}
+    f = open_reader(path)
+    meta = {k: f.metadata(k) for k in f.metadata_keys()}
+    tensors = {k: f.get(k) for k in f.keys()}
     rng = tensors.pop("__rng_cpu", None)
     if rng is not None:
         torch.set_rng_state(rng)

@@ -860,4 +860,5 @@ TORCH_LIBRARY(cosmos_b200, m) {
   m.def("rs_adamw", &rs_adamw);
   m.def("allgather_pull", &allgather_pull);
   cosmos::register_runtime_ops(m);
+  cosmos::register_safetensors(m);
 }

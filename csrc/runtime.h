@@ -1,9 +1,11 @@
 // Native host-side runtime pieces: the paged-KV block allocator used by the Reasoner's
-// decode path and the request scheduler's slot bookkeeping. Registered as torch custom
+// decode path, the request scheduler's slot bookkeeping, and the checkpoint reader. Registered as torch custom
 // classes so Python holds them by reference and calls cost no interpreter-level loops.
 #pragma once
 #include <torch/library.h>
 
 namespace cosmos {
 void register_runtime_ops(torch::Library& m);
+// memory-mapped safetensors reader (safetensors_reader.cpp)
+void register_safetensors(torch::Library& m);
 }
