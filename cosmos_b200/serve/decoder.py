@@ -81,6 +81,7 @@ class TPDecoder:
             ranks = list(range(tp)) if group is None else dist.get_process_group_ranks(group)
             self._tpctx = TPContext(cfg, group, ranks, self.device, fused=self.fused, sequence_parallel=False)
         self.graph = None
+        self.step_inc: Optional[torch.Tensor] = None  # int32 [B] of 0/1 set by the serving engine; None = all ones
 
     # ------------------------------------------------------------------ helpers
     def _allreduce(self, x: torch.Tensor) -> torch.Tensor:
@@ -113,7 +114,11 @@ class TPDecoder:
         ang = pos.float()[:, None] * self.inv_freq[None]
         cos, sin = ang.cos().contiguous(), ang.sin().contiguous()
         slots = PagedKVCache.slots(self.table, pos[:, None], self.page_size)[:, 0].contiguous()
-        self.lens.add_(1)                            # attention sees the token being written
+        # attention sees the token being written; idle slots of a serving batch do not advance
+        if self.step_inc is None:
+            self.lens.add_(1)
+        else:
+            self.lens.add_(self.step_inc)
         x = self.embed[self.tokens]
         delta = None
         for li in range(self.cfg.n_layers):

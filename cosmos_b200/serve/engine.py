@@ -1,0 +1,293 @@
+"""Continuous batching for the Reasoner: requests join and leave a fixed set of decode slots while
+the batch keeps stepping (the serving pattern behind the reference's published Reasoner numbers,
+which are measured through vLLM at client concurrency 1..256, reference
+inference_benchmarks.md:239-241,501-535).
+
+`BatchEngine` owns a `TPDecoder` whose batch is `max_batch` slots. A slot is either idle (length 0,
+block table pointing at a scratch page, its lane of the step ignored) or bound to a request. Each
+engine step (1) admits waiting requests into idle slots while KV pages last — the prompt runs
+through the AR tower once and its K/V go into the request's pages, (2) runs ONE decode step for all
+slots (the same CUDA graph whatever the mix of requests, because the per-slot state lives in device
+tensors that the host edits in place), (3) reads the new tokens back, appends them to their
+requests and retires the ones that hit an end token or their token budget, freeing pages and slot.
+Decoding is greedy (the arg-max runs on the device across the vocab shards).
+
+`EngineWorker` runs the loop in a thread and hands out futures, so concurrent HTTP requests of
+`serve/server.py` share decode steps.
+"""
+from __future__ import annotations
+
+import threading
+import time
+from collections import deque
+from concurrent.futures import Future
+from dataclasses import dataclass, field
+from typing import Deque, Dict, List, Optional, Sequence
+
+import torch
+
+from ..config import MoTConfig
+from ..models import rope
+from .decoder import TPDecoder
+from .paged import PagedKVCache
+
+
+@dataclass
+class Request:
+    rid: int
+    ids: List[int]
+    max_new_tokens: int
+    eos_ids: Sequence[int] = ()
+    out: List[int] = field(default_factory=list)
+    slot: int = -1
+    t_submit: float = 0.0
+    t_first: float = 0.0
+    t_done: float = 0.0
+    finish_reason: str = ""
+    future: Optional[Future] = None
+
+
+class BatchEngine:
+    def __init__(self, model, max_batch: int = 8, max_len: int = 4096, page_size: int = 16, device=None,
+                 dtype=None, use_graph: Optional[bool] = None):
+        self.model = model
+        self.cfg: MoTConfig = model.cfg
+        p = next(model.parameters())
+        self.device = torch.device(device) if device is not None else p.device
+        dtype = dtype or p.dtype
+        self.max_batch, self.max_len = max_batch, max_len
+        self.dec = TPDecoder(self.cfg, 1, 0, None, self.device, page_size=page_size, max_batch=max_batch,
+                             max_len=max_len, dtype=dtype)
+        self.dec.load_from(model)
+        cache = self.dec.cache
+        # one page is set aside for idle slots: their (ignored) K/V writes land there
+        self.scratch_seq = -1
+        assert cache.reserve(self.scratch_seq, 1), "KV pool too small"
+        self.scratch_page = int(cache.alloc.blocks(self.scratch_seq)[0])
+        self.max_pages = cache.max_pages
+        dev = self.device
+        self.dec.table = torch.full((max_batch, self.max_pages), self.scratch_page, dtype=torch.int32, device=dev)
+        self.dec.lens = torch.zeros(max_batch, dtype=torch.int32, device=dev)
+        self.dec.tokens = torch.zeros(max_batch, dtype=torch.long, device=dev)
+        self.dec.next_tokens = torch.zeros(max_batch, dtype=torch.long, device=dev)
+        self.dec.step_inc = torch.zeros(max_batch, dtype=torch.int32, device=dev)
+        self.dec.max_len = max_len
+        self.slots: List[Optional[Request]] = [None] * max_batch
+        self.waiting: Deque[Request] = deque()
+        self.finished: Dict[int, Request] = {}
+        self._next_rid = 0
+        self.steps = 0
+        self.use_graph = (self.device.type == "cuda") if use_graph is None else use_graph
+        self._graph_ready = False
+
+    # ------------------------------------------------------------------ requests
+    def submit(self, ids: Sequence[int], max_new_tokens: int = 256, eos_ids: Sequence[int] = ()) -> Request:
+        if len(ids) < 1:
+            raise ValueError("empty prompt")
+        if len(ids) + max_new_tokens > self.max_len:
+            raise ValueError(f"prompt ({len(ids)}) + max_new_tokens ({max_new_tokens}) exceeds max_len {self.max_len}")
+        r = Request(self._next_rid, [min(int(t), self.cfg.vocab_size - 1) for t in ids], int(max_new_tokens),
+                    tuple(eos_ids), t_submit=time.time())
+        self._next_rid += 1
+        self.waiting.append(r)
+        return r
+
+    def has_work(self) -> bool:
+        return bool(self.waiting) or any(s is not None for s in self.slots)
+
+    def n_active(self) -> int:
+        return sum(s is not None for s in self.slots)
+
+    # ------------------------------------------------------------------ admission (prefill)
+    @torch.no_grad()
+    def _admit(self, r: Request, slot: int) -> None:
+        dec, cache, dev = self.dec, self.dec.cache, self.device
+        n = len(r.ids)
+        ids = torch.tensor([r.ids], dtype=torch.long, device=dev)
+        h, kvs = self.model.ar_forward(self.model.embed_tokens(ids), rope.text_positions(n, 0, dev))
+        table, _ = cache.tables([r.rid])
+        dec.table[slot].copy_(table[0])
+        rows = PagedKVCache.slots(dec.table[slot:slot + 1], torch.arange(n, device=dev)[None], dec.page_size)[0]
+        for li, (k, v) in enumerate(kvs):
+            cache.write(li, k[0].contiguous(), v[0].contiguous(), rows)
+        first = int(self.model.lm_logits(h[:, -1:]).float()[0, 0].argmax())
+        r.slot, r.t_first = slot, time.time()
+        self.slots[slot] = r
+        dec.lens[slot] = n
+        dec.tokens[slot] = first
+        dec.step_inc[slot] = 1
+        self._accept(r, first)
+
+    def _accept(self, r: Request, tok: int) -> None:
+        """Books a generated token; retires the request when it ends."""
+        r.out.append(tok)
+        if tok in r.eos_ids:
+            self._retire(r, "stop")
+        elif len(r.out) >= r.max_new_tokens:
+            self._retire(r, "length")
+
+    def _retire(self, r: Request, reason: str) -> None:
+        s = r.slot
+        r.finish_reason, r.t_done = reason, time.time()
+        self.dec.cache.release(r.rid)
+        self.dec.table[s].fill_(self.scratch_page)
+        self.dec.lens[s] = 0
+        self.dec.step_inc[s] = 0
+        self.dec.tokens[s] = 0
+        self.slots[s] = None
+        self.finished[r.rid] = r
+        if r.future is not None and not r.future.done():
+            r.future.set_result(r)
+
+    # ------------------------------------------------------------------ one engine step
+    @torch.no_grad()
+    def step(self) -> List[Request]:
+        """Admits what fits, runs one decode step for the batch, returns the requests that finished."""
+        done_before = set(self.finished)
+        cache = self.dec.cache
+        for slot in range(self.max_batch):
+            if not self.waiting:
+                break
+            if self.slots[slot] is not None:
+                continue
+            r = self.waiting[0]
+            if not cache.reserve(r.rid, len(r.ids) + r.max_new_tokens):
+                break  # pages are short: the request stays first in line until others retire
+            self.waiting.popleft()
+            self._admit(r, slot)
+        if any(s is not None for s in self.slots):
+            if self.use_graph and not self._graph_ready:
+                self._capture()
+            new = self.dec.step().tolist()  # one device-to-host read per step (end-token detection)
+            self.steps += 1
+            for slot, r in enumerate(self.slots):
+                if r is not None:
+                    self._accept(r, int(new[slot]))
+        return [self.finished[k] for k in self.finished if k not in done_before]
+
+    def _capture(self) -> None:
+        """Graph capture without side effects on the requests: the warm-up and capture steps run with every
+        slot parked on the scratch page (length 0, no advance), then the live state is put back."""
+        dec = self.dec
+        keep = (dec.table.clone(), dec.lens.clone(), dec.tokens.clone(), dec.step_inc.clone())
+        dec.table.fill_(self.scratch_page)
+        dec.lens.zero_()
+        dec.step_inc.zero_()
+        dec.capture(warmup=2)
+        for dst, src in zip((dec.table, dec.lens, dec.tokens, dec.step_inc), keep):
+            dst.copy_(src)
+        self._graph_ready = True
+
+    def run_until_done(self, max_steps: int = 1 << 20) -> None:
+        n = 0
+        while self.has_work() and n < max_steps:
+            self.step()
+            n += 1
+
+
+class EngineWorker:
+    """Runs a BatchEngine in a background thread; `submit` returns a Future that resolves to the Request."""
+
+    def __init__(self, engine: BatchEngine):
+        self.engine = engine
+        self._cv = threading.Condition()
+        self._pending: Deque = deque()
+        self._stop = False
+        self._thread = threading.Thread(target=self._loop, name="cosmos-batch-engine", daemon=True)
+        self._thread.start()
+
+    def submit(self, ids: Sequence[int], max_new_tokens: int = 256, eos_ids: Sequence[int] = ()) -> Future:
+        fut: Future = Future()
+        with self._cv:
+            self._pending.append((list(ids), max_new_tokens, tuple(eos_ids), fut))
+            self._cv.notify()
+        return fut
+
+    def close(self) -> None:
+        with self._cv:
+            self._stop = True
+            self._cv.notify()
+        self._thread.join(timeout=30)
+
+    def _loop(self) -> None:
+        eng = self.engine
+        while True:
+            with self._cv:
+                while not self._pending and not eng.has_work() and not self._stop:
+                    self._cv.wait()
+                if self._stop:
+                    return
+                new = list(self._pending)
+                self._pending.clear()
+            for ids, n, eos, fut in new:
+                try:
+                    eng.submit(ids, n, eos).future = fut
+                except Exception as e:  # noqa: BLE001 - delivered to the caller through the future
+                    fut.set_exception(e)
+            try:
+                eng.step()
+            except Exception as e:  # noqa: BLE001 - fail every request in flight rather than hang the callers
+                for r in list(eng.waiting) + [s for s in eng.slots if s is not None]:
+                    if r.future is not None and not r.future.done():
+                        r.future.set_exception(e)
+                eng.waiting.clear()
+                for s, r in enumerate(eng.slots):
+                    if r is not None:
+                        eng.slots[s] = None
+                raise
+
+
+def main(argv=None) -> int:
+    """Serving benchmark: `--requests` prompts of `--prompt-len` random tokens arrive at once and are served
+    with at most `--max-num-seqs` in the decode batch; prints output tokens per second, time to first token
+    and request latency (the metrics of the reference's Reasoner tables, inference_benchmarks.md:501-535)."""
+    import argparse
+    import json
+
+    from ..config import get_model_config
+    from ..models.mot import MoTModel
+
+    ap = argparse.ArgumentParser(description=main.__doc__)
+    ap.add_argument("--model", default="Cosmos3-Nano")
+    ap.add_argument("--requests", type=int, default=256)
+    ap.add_argument("--max-num-seqs", type=int, default=64)
+    ap.add_argument("--prompt-len", type=int, default=306, help="50 text tokens + a short clip's vision tokens")
+    ap.add_argument("--new-tokens", type=int, default=100)
+    ap.add_argument("--layers", type=int, default=0)
+    args = ap.parse_args(argv)
+    cuda = torch.cuda.is_available()
+    dev = torch.device("cuda", 0) if cuda else torch.device("cpu")
+    dtype = torch.bfloat16 if cuda else torch.float32
+    cfg = get_model_config(args.model, **({"n_layers": args.layers} if args.layers else {}))
+    model = MoTModel(cfg, dtype=dtype, device=dev, towers=("ar",))  # the Reasoner needs the AR tower only
+    model.init_weights(seed=0)
+    eng = BatchEngine(model, max_batch=args.max_num_seqs, max_len=args.prompt_len + args.new_tokens + 16)
+    g = torch.Generator().manual_seed(0)
+    warm = eng.submit(torch.randint(0, cfg.vocab_size, (args.prompt_len,), generator=g).tolist(), 4)
+    eng.run_until_done()  # graph capture and workspace set-up happen here
+    assert len(warm.out) == 4
+    steps0 = eng.steps
+    if cuda:
+        torch.cuda.synchronize()
+    t0 = time.time()
+    reqs = [eng.submit(torch.randint(0, cfg.vocab_size, (args.prompt_len,), generator=g).tolist(), args.new_tokens)
+            for _ in range(args.requests)]
+    eng.run_until_done()
+    if cuda:
+        torch.cuda.synchronize()
+    dt = time.time() - t0
+    toks = sum(len(r.out) for r in reqs)
+    ttft = sorted((r.t_first - r.t_submit) * 1e3 for r in reqs)
+    lat = sorted((r.t_done - r.t_submit) * 1e3 for r in reqs)
+    print(json.dumps({"metric": "reasoner_serving_output_tokens_per_s", "value": round(toks / dt, 1),
+                      "requests": args.requests, "max_num_seqs": args.max_num_seqs, "prompt_len": args.prompt_len,
+                      "new_tokens": args.new_tokens, "wall_s": round(dt, 3), "decode_steps": eng.steps - steps0,
+                      "ttft_ms_avg": round(sum(ttft) / len(ttft), 1), "ttft_ms_p50": round(ttft[len(ttft) // 2], 1),
+                      "request_latency_ms_avg": round(sum(lat) / len(lat), 1), "model": cfg.name,
+                      "layers": cfg.n_layers, "n_gpus": 1, "cuda_graph": eng.use_graph,
+                      "data": "random prompt token ids, random-init weights, greedy decoding"}), flush=True)
+    return 0
+
+
+if __name__ == "__main__":
+    raise SystemExit(main())

@@ -93,8 +93,10 @@ class Cosmos3Server:
     """Holds the pipeline/reasoner and implements the endpoint logic independent of FastAPI."""
 
     def __init__(self, pipe, reasoner=None, vit=None, model_name: str = "nvidia/Cosmos3-Nano",
-                 guardrails_default: bool = True, allowed_local_media_path: str = "/"):
+                 guardrails_default: bool = True, allowed_local_media_path: str = "/", batch_engine=None):
         self.pipe, self.reasoner, self.vit = pipe, reasoner, vit
+        # serve/engine.py::EngineWorker: text-only greedy chat requests share decode steps (continuous batching)
+        self.batch_engine = batch_engine
         self.model_name = model_name
         self.guardrails_default = guardrails_default
         self.allowed_root = Path(allowed_local_media_path)
@@ -269,6 +271,17 @@ class Cosmos3Server:
                             top_k=int(body.get("top_k", extra.get("top_k", 20))),
                             repetition_penalty=float(body.get("repetition_penalty", extra.get("repetition_penalty", 1.0))),
                             presence_penalty=float(body.get("presence_penalty", 1.5)), seed=body.get("seed"))
+        if self.batch_engine is not None and not vision_embeds and dc.temperature == 0.0:
+            # text-only greedy request: joins the running decode batch instead of taking the generation lock
+            r = self.batch_engine.submit(ids, dc.max_new_tokens, (tok.eos_id, tok.eot_id)).result()
+            t1 = time.time()
+            self.metrics.record((r.t_first - t0) * 1e3, (t1 - t0) * 1e3, len(r.out))
+            return {"id": f"chatcmpl-{uuid.uuid4().hex[:24]}", "object": "chat.completion", "created": int(t0),
+                    "model": body.get("model", self.model_name),
+                    "choices": [{"index": 0, "message": {"role": "assistant", "content": tok.decode(r.out)},
+                                 "finish_reason": r.finish_reason}],
+                    "usage": {"prompt_tokens": len(ids), "completion_tokens": len(r.out),
+                              "total_tokens": len(ids) + len(r.out)}}
         first = {}
 
         def on_token(_t):
@@ -455,6 +468,9 @@ def main(argv=None) -> int:
     ap.add_argument("--mm-encoder-tp-mode", default="data", choices=["data", "weights"],
                     help="the vision encoder is replicated on every rank (data); accepted for CLI compatibility")
     ap.add_argument("--media-io-kwargs", default=None, help='JSON, e.g. {"video": {"num_frames": -1}}')
+    ap.add_argument("--max-num-seqs", type=int, default=8,
+                    help="decode slots of the continuous-batching engine for text-only greedy chat requests (0 = off)")
+    ap.add_argument("--max-model-len", type=int, default=8192)
     args = ap.parse_args(argv)
     apply_deploy_config(args)
     import uvicorn
@@ -468,8 +484,12 @@ def main(argv=None) -> int:
     pipe = Cosmos3OmniPipeline.from_pretrained(args.model, torch_dtype=dtype, device_map=dev,
                                                enable_safety_checker=not args.no_guardrails)
     vit = VisionEncoder(pipe.cfg).to(device=pipe.device, dtype=dtype).eval()
+    worker = None
+    if args.max_num_seqs > 0:
+        from .engine import BatchEngine, EngineWorker
+        worker = EngineWorker(BatchEngine(pipe.transformer, max_batch=args.max_num_seqs, max_len=args.max_model_len))
     server = Cosmos3Server(pipe, ReasonerEngine(pipe.transformer, vit), vit, args.model, not args.no_guardrails,
-                           args.allowed_local_media_path)
+                           args.allowed_local_media_path, batch_engine=worker)
     uvicorn.run(create_app(server), host=args.host, port=args.port, log_level="info")
     return 0
 

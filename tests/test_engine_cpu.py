@@ -1,0 +1,89 @@
+"""Continuous batching: requests of different lengths join and leave the decode batch at different
+times; every token the engine emits must be the (near-)arg-max of the reference engine's logits when
+that engine is fed the same prefix (teacher forcing keeps near-ties from cascading)."""
+import torch
+
+from cosmos_b200.config import tiny_config
+from cosmos_b200.models import rope
+from cosmos_b200.models.mot import MoTModel
+from cosmos_b200.models.reasoner import ReasonerEngine
+from cosmos_b200.serve.engine import BatchEngine, EngineWorker
+
+
+def _model():
+    torch.manual_seed(0)
+    cfg = tiny_config(n_layers=2, vocab_size=300)
+    m = MoTModel(cfg, dtype=torch.float32, device="cpu")
+    m.init_weights(seed=11)
+    return m
+
+
+def _check_against_reference(model, req):
+    ref = ReasonerEngine(model)
+    ids = torch.tensor([req.ids], dtype=torch.long)
+    logits, kvs = ref.prefill(ref.embed(ids), rope.text_positions(len(req.ids), 0, "cpu"))
+    pos = len(req.ids)
+    for tok in req.out:
+        lg = logits[0]
+        assert lg[tok] >= lg.max() - 1e-3, (req.rid, tok, float(lg[tok]), float(lg.max()))
+        logits, kvs = ref.decode_one(torch.tensor([tok]), pos, kvs)
+        pos += 1
+
+
+def test_requests_join_and_leave_the_running_batch():
+    model = _model()
+    eng = BatchEngine(model, max_batch=3, max_len=64, page_size=4, use_graph=False)
+    g = torch.Generator().manual_seed(3)
+    prompts = [torch.randint(0, 300, (n,), generator=g).tolist() for n in (5, 9, 3, 12, 7)]
+    budgets = [6, 4, 8, 4, 5]
+    reqs = [eng.submit(prompts[0], budgets[0]), eng.submit(prompts[1], budgets[1])]
+    eng.step()
+    assert eng.n_active() == 2 and not eng.waiting
+    reqs += [eng.submit(prompts[2], budgets[2]), eng.submit(prompts[3], budgets[3])]   # only one slot is free
+    eng.step()
+    assert eng.n_active() == 3 and len(eng.waiting) == 1
+    reqs.append(eng.submit(prompts[4], budgets[4]))
+    eng.run_until_done(max_steps=100)
+    assert not eng.has_work() and eng.n_active() == 0
+    for r, b in zip(reqs, budgets):
+        assert r.finish_reason == "length" and len(r.out) == b
+        _check_against_reference(model, r)
+    # all pages went back to the pool (the scratch page stays reserved)
+    alloc = eng.dec.cache.alloc
+    assert alloc.num_free() == eng.max_batch * eng.max_pages + 1 - 1
+    # fewer engine steps than running the requests one after the other would need
+    assert eng.steps < sum(budgets) - len(budgets)
+
+
+def test_end_token_retires_a_request_and_page_shortage_defers_admission():
+    model = _model()
+    eng = BatchEngine(model, max_batch=2, max_len=32, page_size=4, use_graph=False)
+    probe = eng.submit([1, 2, 3, 4], 6)
+    eng.run_until_done()
+    eos = probe.out[2]                      # the third token of this prompt becomes the end token
+    r = eng.submit([1, 2, 3, 4], 6, eos_ids=(eos,))
+    eng.run_until_done()
+    assert r.finish_reason == "stop" and r.out == probe.out[:r.out.index(eos) + 1]
+    # a request that needs more pages than are free right now waits, it is not dropped
+    small = BatchEngine(model, max_batch=2, max_len=32, page_size=4, use_graph=False)
+    while small.dec.cache.alloc.num_free() > 9:      # leave 9 pages = 36 tokens
+        assert small.dec.cache.reserve(-100 - small.dec.cache.alloc.num_free(), 4)
+    a = small.submit(list(range(10)), 14)            # 24 tokens = 6 pages
+    b = small.submit(list(range(8)), 12)             # 20 tokens = 5 pages: does not fit next to a
+    small.step()
+    assert small.n_active() == 1 and len(small.waiting) == 1
+    small.run_until_done()
+    assert len(a.out) == 14 and len(b.out) == 12
+
+
+def test_worker_thread_serves_concurrent_callers():
+    model = _model()
+    worker = EngineWorker(BatchEngine(model, max_batch=4, max_len=48, page_size=4, use_graph=False))
+    try:
+        futs = [worker.submit([i + 1, i + 2, i + 3], 5) for i in range(6)]
+        outs = [f.result(timeout=120) for f in futs]
+        assert all(len(r.out) == 5 for r in outs)
+        for r in outs:
+            _check_against_reference(model, r)
+    finally:
+        worker.close()

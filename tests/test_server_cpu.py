@@ -120,3 +120,36 @@ def test_deploy_config_switches_guardrails_off(tmp_path):
     args = argparse.Namespace(deploy_config=None, no_guardrails=False, model_class_name="x")
     apply_deploy_config(args)
     assert args.no_guardrails is False
+
+
+def test_concurrent_text_chats_share_the_batching_engine():
+    """Text-only greedy chat requests go through the continuous-batching engine: eight concurrent HTTP
+    requests complete in fewer decode steps than their token budgets add up to."""
+    from concurrent.futures import ThreadPoolExecutor
+
+    from cosmos_b200.serve.engine import BatchEngine, EngineWorker
+
+    torch.manual_seed(0)
+    pipe = Cosmos3OmniPipeline.from_pretrained("tiny", torch_dtype=torch.float32, vae_widths=(8, 16, 16, 16),
+                                               config_overrides=dict(max_text_len=32, n_layers=2))
+    worker = EngineWorker(BatchEngine(pipe.transformer, max_batch=4, max_len=256, page_size=4, use_graph=False))
+    try:
+        srv = Cosmos3Server(pipe, ReasonerEngine(pipe.transformer, None), None, "nvidia/Cosmos3-Nano",
+                            batch_engine=worker)
+        c = TestClient(create_app(srv))
+
+        def ask(i):
+            body = {"model": "nvidia/Cosmos3-Nano", "max_tokens": 6, "temperature": 0.0,
+                    "messages": [{"role": "user", "content": f"question number {i}"}]}
+            return c.post("/v1/chat/completions", json=body)
+
+        with ThreadPoolExecutor(8) as ex:
+            rs = list(ex.map(ask, range(8)))
+        assert all(r.status_code == 200 for r in rs), [r.text for r in rs if r.status_code != 200]
+        outs = [r.json() for r in rs]
+        assert all(o["usage"]["completion_tokens"] <= 6 and o["choices"][0]["finish_reason"] in ("stop", "length")
+                   for o in outs)
+        total = sum(o["usage"]["completion_tokens"] for o in outs)
+        assert worker.engine.steps < total
+    finally:
+        worker.close()
