@@ -5,8 +5,8 @@ inference_benchmarks.md:239-241,501-535).
 
 `BatchEngine` owns a `TPDecoder` whose batch is `max_batch` slots. A slot is either idle (length 0,
 block table pointing at a scratch page, its lane of the step ignored) or bound to a request. Each
-engine step (1) admits waiting requests into idle slots while KV pages last — the prompt runs
-through the AR tower once and its K/V go into the request's pages, (2) runs ONE decode step for all
+engine step (1) admits waiting requests into idle slots while KV pages last — the prompts of the
+admitted group run through the AR tower in one padded forward and their K/V go into the requests' pages, (2) runs ONE decode step for all
 slots (the same CUDA graph whatever the mix of requests, because the per-slot state lives in device
 tensors that the host edits in place), (3) reads the new tokens back, appends them to their
 requests and retires the ones that hit an end token or their token budget, freeing pages and slot.
@@ -77,6 +77,7 @@ class BatchEngine:
         self.finished: Dict[int, Request] = {}
         self._next_rid = 0
         self.steps = 0
+        self.max_prefill_tokens = 16384  # padded prompt tokens per prefill forward
         self.use_graph = (self.device.type == "cuda") if use_graph is None else use_graph
         self._graph_ready = False
 
@@ -100,23 +101,38 @@ class BatchEngine:
 
     # ------------------------------------------------------------------ admission (prefill)
     @torch.no_grad()
-    def _admit(self, r: Request, slot: int) -> None:
+    def _admit_group(self, group: List[Request], slots: List[int]) -> None:
+        """Prefills several requests in ONE forward of the AR tower: prompts are right-padded to the longest
+        of the group (causal attention keeps the padding from reaching real tokens), the K/V rows of the real
+        tokens of all requests go into their pages with one cache write per layer, and each request's first
+        token is the arg-max at its own last position."""
         dec, cache, dev = self.dec, self.dec.cache, self.device
-        n = len(r.ids)
-        ids = torch.tensor([r.ids], dtype=torch.long, device=dev)
-        h, kvs = self.model.ar_forward(self.model.embed_tokens(ids), rope.text_positions(n, 0, dev))
-        table, _ = cache.tables([r.rid])
-        dec.table[slot].copy_(table[0])
-        rows = PagedKVCache.slots(dec.table[slot:slot + 1], torch.arange(n, device=dev)[None], dec.page_size)[0]
+        lens = [len(r.ids) for r in group]
+        n_max, bsz = max(lens), len(group)
+        ids = torch.zeros(bsz, n_max, dtype=torch.long)
+        for i, r in enumerate(group):
+            ids[i, :lens[i]] = torch.tensor(r.ids, dtype=torch.long)
+        ids = ids.to(dev)
+        h, kvs = self.model.ar_forward(self.model.embed_tokens(ids), rope.text_positions(n_max, 0, dev))
+        table, _ = cache.tables([r.rid for r in group])
+        slot_idx = torch.tensor(slots, dtype=torch.long, device=dev)
+        dec.table[slot_idx] = table
+        len_t = torch.tensor(lens, device=dev)
+        pos = torch.arange(n_max, device=dev)[None].expand(bsz, -1)
+        real = pos < len_t[:, None]                                          # [B, n_max]
+        rows = PagedKVCache.slots(table, pos.clamp(max=cache.max_pages * dec.page_size - 1), dec.page_size)[real]
         for li, (k, v) in enumerate(kvs):
-            cache.write(li, k[0].contiguous(), v[0].contiguous(), rows)
-        first = int(self.model.lm_logits(h[:, -1:]).float()[0, 0].argmax())
-        r.slot, r.t_first = slot, time.time()
-        self.slots[slot] = r
-        dec.lens[slot] = n
-        dec.tokens[slot] = first
-        dec.step_inc[slot] = 1
-        self._accept(r, first)
+            cache.write(li, k[real].contiguous(), v[real].contiguous(), rows)
+        last = h[torch.arange(bsz, device=dev), len_t - 1][:, None]          # [B, 1, d]
+        first = self.model.lm_logits(last).float()[:, 0].argmax(dim=-1)
+        dec.lens[slot_idx] = len_t.to(dec.lens.dtype)
+        dec.tokens[slot_idx] = first
+        dec.step_inc[slot_idx] = 1
+        now = time.time()
+        for r, slot, tok in zip(group, slots, first.tolist()):
+            r.slot, r.t_first = slot, now
+            self.slots[slot] = r
+            self._accept(r, int(tok))
 
     def _accept(self, r: Request, tok: int) -> None:
         """Books a generated token; retires the request when it ends."""
@@ -145,16 +161,29 @@ class BatchEngine:
         """Admits what fits, runs one decode step for the batch, returns the requests that finished."""
         done_before = set(self.finished)
         cache = self.dec.cache
-        for slot in range(self.max_batch):
-            if not self.waiting:
+        free = [i for i in range(self.max_batch) if self.slots[i] is None]
+        while self.waiting and free:
+            # a group of waiting requests whose padded prompts fit the prefill token budget
+            group: List[Request] = []
+            slots: List[int] = []
+            n_max = 0
+            while self.waiting and free:
+                r = self.waiting[0]
+                new_max = max(n_max, len(r.ids))
+                if group and new_max * (len(group) + 1) > self.max_prefill_tokens:
+                    break
+                if not cache.reserve(r.rid, len(r.ids) + r.max_new_tokens):
+                    break  # pages are short: the request stays first in line until others retire
+                self.waiting.popleft()
+                group.append(r)
+                slots.append(free.pop(0))
+                n_max = new_max
+            if not group:
                 break
-            if self.slots[slot] is not None:
-                continue
-            r = self.waiting[0]
-            if not cache.reserve(r.rid, len(r.ids) + r.max_new_tokens):
-                break  # pages are short: the request stays first in line until others retire
-            self.waiting.popleft()
-            self._admit(r, slot)
+            self._admit_group(group, slots)
+            free = [i for i in range(self.max_batch) if self.slots[i] is None]
+            if self.waiting and not cache.alloc.can_allocate(len(self.waiting[0].ids) + self.waiting[0].max_new_tokens):
+                break
         if any(s is not None for s in self.slots):
             if self.use_graph and not self._graph_ready:
                 self._capture()
