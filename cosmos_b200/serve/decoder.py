@@ -82,6 +82,7 @@ class TPDecoder:
             self._tpctx = TPContext(cfg, group, ranks, self.device, fused=self.fused, sequence_parallel=False)
         self.graph = None
         self.step_inc: Optional[torch.Tensor] = None  # int32 [B] of 0/1 set by the serving engine; None = all ones
+        self.sampling: Optional[Dict[str, torch.Tensor]] = None  # see enable_sampling
 
     # ------------------------------------------------------------------ helpers
     def _allreduce(self, x: torch.Tensor) -> torch.Tensor:
@@ -126,7 +127,11 @@ class TPDecoder:
         h, _ = ops.rmsnorm(delta, self.final_norm, self.cfg.rms_eps, residual=x)
         logits = ops.gemm(h, self.lm_head).float()   # [B, V/tp]
         self.last_logits = logits                    # this rank's vocab shard, kept for inspection
+        if self.sampling is not None:
+            logits = self._penalise(logits)
         val, idx = logits.max(dim=-1)
+        if self.sampling is not None:
+            idx = self._sample(logits, idx)
         idx = idx + self.rank * self.v_loc
         if self.tp > 1:
             packed = torch.stack([val, idx.float()], dim=-1)      # [B, 2]
@@ -135,6 +140,58 @@ class TPDecoder:
             best = allp[..., 0].argmax(dim=0)
             idx = allp[best, torch.arange(b, device=self.device), 1].long()
         self.next_tokens.copy_(idx.clamp(max=self.cfg.vocab_size - 1))
+
+    # ------------------------------------------------------------------ sampling (tp = 1)
+    SAMPLE_K = 64  # candidates kept per slot; a request's top_k is clamped to it
+
+    def enable_sampling(self, batch: int) -> None:
+        """Per-slot sampling state, all on the device so that the step stays one CUDA graph:
+        temperature (0 = greedy), top_k, top_p, presence / repetition penalty, `seen_out` / `seen_any`
+        ([B, V] flags of tokens generated / seen in prompt or output) and a buffer of uniform noise that
+        the host refills before every step (the Gumbel-max draw inside the graph then needs no generator)."""
+        assert self.tp == 1, "device-side sampling is implemented for one rank"
+        dev, v = self.device, self.v_loc
+        self.sampling = {
+            "temperature": torch.zeros(batch, device=dev), "top_k": torch.ones(batch, dtype=torch.long, device=dev),
+            "top_p": torch.ones(batch, device=dev), "presence": torch.zeros(batch, device=dev),
+            "repetition": torch.ones(batch, device=dev),
+            "seen_out": torch.zeros(batch, v, dtype=torch.bool, device=dev),
+            "seen_any": torch.zeros(batch, v, dtype=torch.bool, device=dev),
+            "noise": torch.full((batch, self.SAMPLE_K), 0.5, device=dev),
+        }
+
+    def refill_noise(self, generator: Optional[torch.Generator] = None) -> None:
+        if self.sampling is not None:
+            self.sampling["noise"].uniform_(1e-7, 1.0, generator=generator)
+
+    def _penalise(self, logits: torch.Tensor) -> torch.Tensor:
+        """Repetition penalty (CTRL style) on tokens seen in prompt or output, presence penalty on generated
+        tokens; the token consumed by this step (self.tokens) counts as generated."""
+        sp = self.sampling
+        row = torch.arange(logits.shape[0], device=logits.device)
+        sp["seen_out"][row, self.tokens] = True
+        sp["seen_any"][row, self.tokens] = True
+        rep = sp["repetition"][:, None]
+        pen = torch.where(logits > 0, logits / rep, logits * rep)
+        logits = torch.where(sp["seen_any"], pen, logits)
+        return logits - sp["presence"][:, None] * sp["seen_out"].float()
+
+    def _sample(self, logits: torch.Tensor, greedy_idx: torch.Tensor) -> torch.Tensor:
+        """Top-k / top-p sampling among the SAMPLE_K best logits of every slot with the Gumbel-max trick."""
+        sp = self.sampling
+        k = min(self.SAMPLE_K, logits.shape[-1])
+        vals, cand = torch.topk(logits, k, dim=-1)                    # sorted, best first
+        t = sp["temperature"][:, None]
+        z = vals / torch.where(t > 0, t, torch.ones_like(t))
+        rank = torch.arange(k, device=logits.device)[None]
+        z = torch.where(rank < sp["top_k"][:, None].clamp(1, k), z, torch.full_like(z, float("-inf")))
+        p = torch.softmax(z, dim=-1)
+        keep = (torch.cumsum(p, dim=-1) - p) < sp["top_p"][:, None]   # always keeps the most likely token
+        z = torch.where(keep, z, torch.full_like(z, float("-inf")))
+        g = -torch.log(-torch.log(sp["noise"][:, :k]))
+        pick = torch.argmax(z + g, dim=-1)
+        sampled = cand.gather(1, pick[:, None])[:, 0]
+        return torch.where(sp["temperature"] > 0, sampled, greedy_idx)
 
     # ------------------------------------------------------------------ public
     @torch.no_grad()

@@ -10,7 +10,8 @@ admitted group run through the AR tower in one padded forward and their K/V go i
 slots (the same CUDA graph whatever the mix of requests, because the per-slot state lives in device
 tensors that the host edits in place), (3) reads the new tokens back, appends them to their
 requests and retires the ones that hit an end token or their token budget, freeing pages and slot.
-Decoding is greedy (the arg-max runs on the device across the vocab shards).
+Sampling (temperature, top-k, top-p, presence and repetition penalties, per request) runs on the device
+inside the same graph; temperature 0 is greedy.
 
 `EngineWorker` runs the loop in a thread and hands out futures, so concurrent HTTP requests of
 `serve/server.py` share decode steps.
@@ -38,6 +39,11 @@ class Request:
     ids: List[int]
     max_new_tokens: int
     eos_ids: Sequence[int] = ()
+    temperature: float = 0.0       # 0 = greedy
+    top_k: int = 20
+    top_p: float = 1.0
+    presence_penalty: float = 0.0
+    repetition_penalty: float = 1.0
     out: List[int] = field(default_factory=list)
     slot: int = -1
     t_submit: float = 0.0
@@ -72,6 +78,9 @@ class BatchEngine:
         self.dec.next_tokens = torch.zeros(max_batch, dtype=torch.long, device=dev)
         self.dec.step_inc = torch.zeros(max_batch, dtype=torch.int32, device=dev)
         self.dec.max_len = max_len
+        self.dec.enable_sampling(max_batch)
+        self.noise_gen = torch.Generator(device=dev)
+        self.noise_gen.manual_seed(0)
         self.slots: List[Optional[Request]] = [None] * max_batch
         self.waiting: Deque[Request] = deque()
         self.finished: Dict[int, Request] = {}
@@ -82,13 +91,16 @@ class BatchEngine:
         self._graph_ready = False
 
     # ------------------------------------------------------------------ requests
-    def submit(self, ids: Sequence[int], max_new_tokens: int = 256, eos_ids: Sequence[int] = ()) -> Request:
+    def submit(self, ids: Sequence[int], max_new_tokens: int = 256, eos_ids: Sequence[int] = (),
+               temperature: float = 0.0, top_k: int = 20, top_p: float = 1.0, presence_penalty: float = 0.0,
+               repetition_penalty: float = 1.0) -> Request:
         if len(ids) < 1:
             raise ValueError("empty prompt")
         if len(ids) + max_new_tokens > self.max_len:
             raise ValueError(f"prompt ({len(ids)}) + max_new_tokens ({max_new_tokens}) exceeds max_len {self.max_len}")
         r = Request(self._next_rid, [min(int(t), self.cfg.vocab_size - 1) for t in ids], int(max_new_tokens),
-                    tuple(eos_ids), t_submit=time.time())
+                    tuple(eos_ids), float(temperature), int(top_k) if top_k and top_k > 0 else TPDecoder.SAMPLE_K,
+                    float(top_p), float(presence_penalty), float(repetition_penalty), t_submit=time.time())
         self._next_rid += 1
         self.waiting.append(r)
         return r
@@ -124,7 +136,19 @@ class BatchEngine:
         for li, (k, v) in enumerate(kvs):
             cache.write(li, k[real].contiguous(), v[real].contiguous(), rows)
         last = h[torch.arange(bsz, device=dev), len_t - 1][:, None]          # [B, 1, d]
-        first = self.model.lm_logits(last).float()[:, 0].argmax(dim=-1)
+        logits = self.model.lm_logits(last).float()[:, 0]                    # [B, V]
+        # per-slot sampling state; the prompt tokens count as "seen" for the repetition penalty
+        sp = dec.sampling
+        for name, vals in (("temperature", [r.temperature for r in group]), ("top_p", [r.top_p for r in group]),
+                           ("presence", [r.presence_penalty for r in group]),
+                           ("repetition", [r.repetition_penalty for r in group])):
+            sp[name][slot_idx] = torch.tensor(vals, dtype=torch.float32, device=dev)
+        sp["top_k"][slot_idx] = torch.tensor([r.top_k for r in group], dtype=torch.long, device=dev)
+        seen = torch.zeros(bsz, dec.v_loc, dtype=torch.bool, device=dev)
+        seen.scatter_(1, ids.clamp(max=dec.v_loc - 1), real)
+        sp["seen_any"][slot_idx] = seen
+        sp["seen_out"][slot_idx] = False
+        first = self._first_tokens(logits, slot_idx, seen)
         dec.lens[slot_idx] = len_t.to(dec.lens.dtype)
         dec.tokens[slot_idx] = first
         dec.step_inc[slot_idx] = 1
@@ -133,6 +157,22 @@ class BatchEngine:
             r.slot, r.t_first = slot, now
             self.slots[slot] = r
             self._accept(r, int(tok))
+
+    def _first_tokens(self, logits: torch.Tensor, slot_idx: torch.Tensor, seen: torch.Tensor) -> torch.Tensor:
+        """First token of every request of a prefill group with the decoder's own sampler (same rules as the
+        decode steps: repetition penalty over the prompt, top-k / top-p / temperature per request)."""
+        dec, sp = self.dec, self.dec.sampling
+        rep = sp["repetition"][slot_idx][:, None]
+        pen = torch.where(logits > 0, logits / rep, logits * rep)
+        logits = torch.where(seen, pen, logits)[:, :dec.v_loc]
+        greedy = logits.argmax(dim=-1)
+        sub = {k: (v[slot_idx] if v.shape[0] == self.max_batch else v) for k, v in sp.items()}
+        sub["noise"] = torch.rand(len(slot_idx), dec.SAMPLE_K, device=logits.device, generator=self.noise_gen).clamp_min(1e-7)
+        keep, dec.sampling = dec.sampling, sub
+        try:
+            return dec._sample(logits, greedy)
+        finally:
+            dec.sampling = keep
 
     def _accept(self, r: Request, tok: int) -> None:
         """Books a generated token; retires the request when it ends."""
@@ -187,6 +227,7 @@ class BatchEngine:
         if any(s is not None for s in self.slots):
             if self.use_graph and not self._graph_ready:
                 self._capture()
+            self.dec.refill_noise(self.noise_gen)
             new = self.dec.step().tolist()  # one device-to-host read per step (end-token detection)
             self.steps += 1
             for slot, r in enumerate(self.slots):
@@ -225,10 +266,11 @@ class EngineWorker:
         self._thread = threading.Thread(target=self._loop, name="cosmos-batch-engine", daemon=True)
         self._thread.start()
 
-    def submit(self, ids: Sequence[int], max_new_tokens: int = 256, eos_ids: Sequence[int] = ()) -> Future:
+    def submit(self, ids: Sequence[int], max_new_tokens: int = 256, eos_ids: Sequence[int] = (), **sampling) -> Future:
+        """`sampling`: temperature, top_k, top_p, presence_penalty, repetition_penalty (see BatchEngine.submit)."""
         fut: Future = Future()
         with self._cv:
-            self._pending.append((list(ids), max_new_tokens, tuple(eos_ids), fut))
+            self._pending.append((list(ids), max_new_tokens, tuple(eos_ids), sampling, fut))
             self._cv.notify()
         return fut
 
@@ -248,9 +290,9 @@ class EngineWorker:
                     return
                 new = list(self._pending)
                 self._pending.clear()
-            for ids, n, eos, fut in new:
+            for ids, n, eos, sampling, fut in new:
                 try:
-                    eng.submit(ids, n, eos).future = fut
+                    eng.submit(ids, n, eos, **sampling).future = fut
                 except Exception as e:  # noqa: BLE001 - delivered to the caller through the future
                     fut.set_exception(e)
             try:
@@ -283,6 +325,7 @@ def main(argv=None) -> int:
     ap.add_argument("--prompt-len", type=int, default=306, help="50 text tokens + a short clip's vision tokens")
     ap.add_argument("--new-tokens", type=int, default=100)
     ap.add_argument("--layers", type=int, default=0)
+    ap.add_argument("--temperature", type=float, default=0.0, help="0 = greedy; else top-k 20 / top-p 0.8 sampling")
     args = ap.parse_args(argv)
     cuda = torch.cuda.is_available()
     dev = torch.device("cuda", 0) if cuda else torch.device("cpu")
@@ -299,7 +342,9 @@ def main(argv=None) -> int:
     if cuda:
         torch.cuda.synchronize()
     t0 = time.time()
-    reqs = [eng.submit(torch.randint(0, cfg.vocab_size, (args.prompt_len,), generator=g).tolist(), args.new_tokens)
+    reqs = [eng.submit(torch.randint(0, cfg.vocab_size, (args.prompt_len,), generator=g).tolist(), args.new_tokens,
+                       temperature=args.temperature, top_k=20, top_p=0.8 if args.temperature > 0 else 1.0,
+                       presence_penalty=1.5 if args.temperature > 0 else 0.0)
             for _ in range(args.requests)]
     eng.run_until_done()
     if cuda:
@@ -314,7 +359,8 @@ def main(argv=None) -> int:
                       "ttft_ms_avg": round(sum(ttft) / len(ttft), 1), "ttft_ms_p50": round(ttft[len(ttft) // 2], 1),
                       "request_latency_ms_avg": round(sum(lat) / len(lat), 1), "model": cfg.name,
                       "layers": cfg.n_layers, "n_gpus": 1, "cuda_graph": eng.use_graph,
-                      "data": "random prompt token ids, random-init weights, greedy decoding"}), flush=True)
+                      "temperature": args.temperature,
+                      "data": "random prompt token ids, random-init weights"}), flush=True)
     return 0
 
 

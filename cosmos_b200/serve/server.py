@@ -95,7 +95,7 @@ class Cosmos3Server:
     def __init__(self, pipe, reasoner=None, vit=None, model_name: str = "nvidia/Cosmos3-Nano",
                  guardrails_default: bool = True, allowed_local_media_path: str = "/", batch_engine=None):
         self.pipe, self.reasoner, self.vit = pipe, reasoner, vit
-        # serve/engine.py::EngineWorker: text-only greedy chat requests share decode steps (continuous batching)
+        # serve/engine.py::EngineWorker: text-only chat requests share decode steps (continuous batching)
         self.batch_engine = batch_engine
         self.model_name = model_name
         self.guardrails_default = guardrails_default
@@ -271,9 +271,13 @@ class Cosmos3Server:
                             top_k=int(body.get("top_k", extra.get("top_k", 20))),
                             repetition_penalty=float(body.get("repetition_penalty", extra.get("repetition_penalty", 1.0))),
                             presence_penalty=float(body.get("presence_penalty", 1.5)), seed=body.get("seed"))
-        if self.batch_engine is not None and not vision_embeds and dc.temperature == 0.0:
-            # text-only greedy request: joins the running decode batch instead of taking the generation lock
-            r = self.batch_engine.submit(ids, dc.max_new_tokens, (tok.eos_id, tok.eot_id)).result()
+        if self.batch_engine is not None and not vision_embeds and dc.seed is None:
+            # text-only request: joins the running decode batch instead of taking the generation lock
+            # (sampling runs on the device; a request that pins a seed takes the single-request path)
+            r = self.batch_engine.submit(ids, dc.max_new_tokens, (tok.eos_id, tok.eot_id),
+                                         temperature=dc.temperature if dc.do_sample else 0.0, top_k=dc.top_k,
+                                         top_p=dc.top_p, presence_penalty=dc.presence_penalty,
+                                         repetition_penalty=dc.repetition_penalty).result()
             t1 = time.time()
             self.metrics.record((r.t_first - t0) * 1e3, (t1 - t0) * 1e3, len(r.out))
             return {"id": f"chatcmpl-{uuid.uuid4().hex[:24]}", "object": "chat.completion", "created": int(t0),
@@ -469,7 +473,7 @@ def main(argv=None) -> int:
                     help="the vision encoder is replicated on every rank (data); accepted for CLI compatibility")
     ap.add_argument("--media-io-kwargs", default=None, help='JSON, e.g. {"video": {"num_frames": -1}}')
     ap.add_argument("--max-num-seqs", type=int, default=8,
-                    help="decode slots of the continuous-batching engine for text-only greedy chat requests (0 = off)")
+                    help="decode slots of the continuous-batching engine for text-only chat requests (0 = off)")
     ap.add_argument("--max-model-len", type=int, default=8192)
     args = ap.parse_args(argv)
     apply_deploy_config(args)

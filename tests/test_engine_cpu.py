@@ -87,3 +87,54 @@ def test_worker_thread_serves_concurrent_callers():
             _check_against_reference(model, r)
     finally:
         worker.close()
+
+
+def test_device_side_sampling_follows_the_truncated_softmax():
+    """Top-k / top-p sampling inside the decode step: over many draws the frequencies match the softmax of
+    the kept candidates, tokens outside top-k or beyond the top-p mass never appear, and top_k = 1 is greedy."""
+    from cosmos_b200.serve.decoder import TPDecoder
+
+    cfg = tiny_config(n_layers=1, vocab_size=300)
+    dec = TPDecoder(cfg, 1, 0, None, "cpu", page_size=4, max_batch=4, max_len=16, dtype=torch.float32)
+    dec.enable_sampling(4)
+    sp = dec.sampling
+    logits = torch.full((4, 300), -20.0)
+    base = torch.tensor([2.0, 1.5, 1.0, 0.5, 0.0, -0.5])
+    logits[:, 10:16] = base
+    greedy = logits.argmax(-1)
+    sp["temperature"][:] = torch.tensor([1.0, 1.0, 0.0, 0.7])
+    sp["top_k"][:] = torch.tensor([3, 64, 5, 1])
+    sp["top_p"][:] = torch.tensor([1.0, 0.6, 1.0, 1.0])
+    g = torch.Generator().manual_seed(0)
+    n = 4000
+    counts = torch.zeros(4, 300)
+    for _ in range(n):
+        dec.refill_noise(g)
+        tok = dec._sample(logits, greedy)
+        counts[torch.arange(4), tok] += 1
+    f = counts / n
+    want0 = torch.softmax(base[:3], -1)                       # slot 0: top_k = 3
+    assert torch.allclose(f[0, 10:13], want0, atol=0.03) and f[0, 13:].sum() == 0
+    p = torch.softmax(base, -1)                               # slot 1: top_p = 0.6 keeps tokens while the mass before them < 0.6
+    kept = (torch.cumsum(p, 0) - p) < 0.6
+    want1 = torch.where(kept, p, torch.zeros_like(p))
+    want1 = want1 / want1.sum()
+    assert torch.allclose(f[1, 10:16], want1, atol=0.03)
+    assert f[2, 10] == 1.0 and f[3, 10] == 1.0                # temperature 0 and top_k = 1 are greedy
+    # presence / repetition penalties act on seen tokens only
+    dec.tokens = torch.tensor([10, 11, 12, 13])
+    sp["presence"][:] = torch.tensor([1.5, 0.0, 0.0, 0.0])
+    sp["repetition"][:] = torch.tensor([1.0, 2.0, 1.0, 1.0])
+    out = dec._penalise(logits.clone())
+    assert torch.isclose(out[0, 10], torch.tensor(0.5)) and torch.isclose(out[1, 11], torch.tensor(0.75))
+    assert torch.equal(out[2], logits[2]) and torch.isclose(out[1, 10], torch.tensor(2.0))
+
+
+def test_sampled_requests_run_through_the_engine():
+    model = _model()
+    eng = BatchEngine(model, max_batch=3, max_len=48, page_size=4, use_graph=False)
+    a = eng.submit([5, 6, 7], 8, temperature=0.8, top_k=20, top_p=0.9, presence_penalty=1.5)
+    b = eng.submit([5, 6, 7], 8)                              # greedy neighbour in the same batch
+    eng.run_until_done()
+    assert len(a.out) == 8 and len(b.out) == 8
+    _check_against_reference(model, b)                        # the sampled neighbour does not disturb it
