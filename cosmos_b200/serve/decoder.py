@@ -168,9 +168,9 @@ class TPDecoder:
         """Repetition penalty (CTRL style) on tokens seen in prompt or output, presence penalty on generated
         tokens; the token consumed by this step (self.tokens) counts as generated."""
         sp = self.sampling
-        row = torch.arange(logits.shape[0], device=logits.device)
-        sp["seen_out"][row, self.tokens] = True
-        sp["seen_any"][row, self.tokens] = True
+        idx = self.tokens[:, None]
+        sp["seen_out"].scatter_(1, idx, True)   # scalar-valued scatter: no host tensor, so it can sit in the graph
+        sp["seen_any"].scatter_(1, idx, True)
         rep = sp["repetition"][:, None]
         pen = torch.where(logits > 0, logits / rep, logits * rep)
         logits = torch.where(sp["seen_any"], pen, logits)
