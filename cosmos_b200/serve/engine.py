@@ -9,7 +9,7 @@ engine step (1) admits waiting requests into idle slots while KV pages last — 
 admitted group run through the AR tower in one padded forward and their K/V go into the requests' pages, (2) runs ONE decode step for all
 slots (the same CUDA graph whatever the mix of requests, because the per-slot state lives in device
 tensors that the host edits in place), (3) reads the new tokens back, appends them to their
-requests and retires the ones that hit an end token or their token budget, freeing pages and slot.
+requests and retires the ones that hit an end token or their token limit, freeing pages and slot.
 Sampling (temperature, top-k, top-p, presence and repetition penalties, per request) runs on the device
 inside the same graph; temperature 0 is greedy.
 
@@ -203,7 +203,7 @@ class BatchEngine:
         cache = self.dec.cache
         free = [i for i in range(self.max_batch) if self.slots[i] is None]
         while self.waiting and free:
-            # a group of waiting requests whose padded prompts fit the prefill token budget
+            # a group of waiting requests whose padded prompts fit the prefill token limit
             group: List[Request] = []
             slots: List[int] = []
             n_max = 0

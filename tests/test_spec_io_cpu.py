@@ -1,5 +1,6 @@
 """Spec parser/validator, pose utilities, MP4 muxer, tokenizer: CPU-only contract tests."""
 import json
+import os
 from pathlib import Path
 
 import numpy as np
@@ -10,7 +11,8 @@ from cosmos_b200.io import media, mp4
 from cosmos_b200.io.spec import InferenceSpec, SpecError, load_specs, spec_from_dict
 from cosmos_b200.utils.tokenizer import ByteTokenizer
 
-REF = Path("/root/reference")
+# the reference checkout, when it sits next to this repository (its cookbook specs serve as parsing fixtures)
+REF = Path(os.environ.get("COSMOS_REFERENCE_DIR", Path(__file__).resolve().parents[2] / "reference"))
 
 
 def test_t2v_defaults_match_recipe():
