@@ -208,7 +208,7 @@ class Cosmos3OmniPipeline:
             fr = frames[:n_pix]
             if fr.shape[0] < n_pix:
                 fr = np.concatenate([fr, np.repeat(fr[-1:], n_pix - fr.shape[0], 0)])
-            x = CausalVideoVAE.from_uint8(torch.from_numpy(fr)[None].to(self.device)).to(vdt)
+            x = CausalVideoVAE.from_uint8(torch.from_numpy(np.array(fr))[None].to(self.device)).to(vdt)
             with torch.no_grad():
                 z = self.vae.encode(x, chunk_frames=4 if n_pix > 1 else None).float()
             ztok = patchify(z, cfg)[0]
