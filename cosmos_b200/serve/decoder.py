@@ -83,6 +83,7 @@ class TPDecoder:
         self.graph = None
         self.step_inc: Optional[torch.Tensor] = None  # int32 [B] of 0/1 set by the serving engine; None = all ones
         self.sampling: Optional[Dict[str, torch.Tensor]] = None  # see enable_sampling
+        self.pos_delta: Optional[torch.Tensor] = None  # int64 [B]: rotary position minus cache position
 
     # ------------------------------------------------------------------ helpers
     def _allreduce(self, x: torch.Tensor) -> torch.Tensor:
@@ -111,8 +112,11 @@ class TPDecoder:
     def _step_impl(self) -> None:
         """Consumes self.tokens / self.lens (device), writes self.next_tokens and advances lens."""
         b = self.tokens.shape[0]
-        pos = self.lens.long()                       # position of the new token = current length
-        ang = pos.float()[:, None] * self.inv_freq[None]
+        pos = self.lens.long()                       # cache position of the new token = current length
+        # rotary position: the same for text; prompts with vision grids advance slower than one per token
+        # (3-D ids), so the serving engine keeps a per-slot offset
+        rpos = pos if self.pos_delta is None else pos + self.pos_delta
+        ang = rpos.float()[:, None] * self.inv_freq[None]
         cos, sin = ang.cos().contiguous(), ang.sin().contiguous()
         slots = PagedKVCache.slots(self.table, pos[:, None], self.page_size)[:, 0].contiguous()
         # attention sees the token being written; idle slots of a serving batch do not advance

@@ -44,6 +44,12 @@ class Request:
     top_p: float = 1.0
     presence_penalty: float = 0.0
     repetition_penalty: float = 1.0
+    # prompts with media: embeddings [n, d] with the vision rows spliced in, 3-D rotary ids [3, n], the vision
+    # mask [n] and DeepStack features; such a request is prefilled on its own
+    embeds: Optional[torch.Tensor] = None
+    positions: Optional[torch.Tensor] = None
+    vision_mask: Optional[torch.Tensor] = None
+    deepstack: Optional[Sequence[torch.Tensor]] = None
     out: List[int] = field(default_factory=list)
     slot: int = -1
     t_submit: float = 0.0
@@ -79,6 +85,7 @@ class BatchEngine:
         self.dec.step_inc = torch.zeros(max_batch, dtype=torch.int32, device=dev)
         self.dec.max_len = max_len
         self.dec.enable_sampling(max_batch)
+        self.dec.pos_delta = torch.zeros(max_batch, dtype=torch.long, device=dev)
         self.noise_gen = torch.Generator(device=dev)
         self.noise_gen.manual_seed(0)
         self.slots: List[Optional[Request]] = [None] * max_batch
@@ -93,14 +100,19 @@ class BatchEngine:
     # ------------------------------------------------------------------ requests
     def submit(self, ids: Sequence[int], max_new_tokens: int = 256, eos_ids: Sequence[int] = (),
                temperature: float = 0.0, top_k: int = 20, top_p: float = 1.0, presence_penalty: float = 0.0,
-               repetition_penalty: float = 1.0) -> Request:
+               repetition_penalty: float = 1.0, embeds: Optional[torch.Tensor] = None,
+               positions: Optional[torch.Tensor] = None, vision_mask: Optional[torch.Tensor] = None,
+               deepstack: Optional[Sequence[torch.Tensor]] = None) -> Request:
         if len(ids) < 1:
             raise ValueError("empty prompt")
         if len(ids) + max_new_tokens > self.max_len:
             raise ValueError(f"prompt ({len(ids)}) + max_new_tokens ({max_new_tokens}) exceeds max_len {self.max_len}")
         r = Request(self._next_rid, [min(int(t), self.cfg.vocab_size - 1) for t in ids], int(max_new_tokens),
                     tuple(eos_ids), float(temperature), int(top_k) if top_k and top_k > 0 else TPDecoder.SAMPLE_K,
-                    float(top_p), float(presence_penalty), float(repetition_penalty), t_submit=time.time())
+                    float(top_p), float(presence_penalty), float(repetition_penalty), embeds, positions, vision_mask,
+                    deepstack, t_submit=time.time())
+        if embeds is not None and (positions is None or embeds.shape[0] != len(r.ids)):
+            raise ValueError("a request with embeddings needs positions [3, n] and one embedding row per prompt token")
         self._next_rid += 1
         self.waiting.append(r)
         return r
@@ -125,7 +137,16 @@ class BatchEngine:
         for i, r in enumerate(group):
             ids[i, :lens[i]] = torch.tensor(r.ids, dtype=torch.long)
         ids = ids.to(dev)
-        h, kvs = self.model.ar_forward(self.model.embed_tokens(ids), rope.text_positions(n_max, 0, dev))
+        media = group[0].embeds is not None
+        if media:  # admitted alone (its rotary ids are its own)
+            r0 = group[0]
+            x = r0.embeds.to(device=dev, dtype=self.model.embed.dtype)[None]
+            vm = None if r0.vision_mask is None else r0.vision_mask.to(dev).reshape(1, -1)
+            h, kvs = self.model.ar_forward(x, r0.positions.to(dev), deepstack=r0.deepstack, vision_mask=vm)
+            delta = [int(rope.next_start(r0.positions)) - lens[0]]
+        else:
+            h, kvs = self.model.ar_forward(self.model.embed_tokens(ids), rope.text_positions(n_max, 0, dev))
+            delta = [0] * bsz
         table, _ = cache.tables([r.rid for r in group])
         slot_idx = torch.tensor(slots, dtype=torch.long, device=dev)
         dec.table[slot_idx] = table
@@ -150,6 +171,7 @@ class BatchEngine:
         sp["seen_out"][slot_idx] = False
         first = self._first_tokens(logits, slot_idx, seen)
         dec.lens[slot_idx] = len_t.to(dec.lens.dtype)
+        dec.pos_delta[slot_idx] = torch.tensor(delta, dtype=torch.long, device=dev)
         dec.tokens[slot_idx] = first
         dec.step_inc[slot_idx] = 1
         now = time.time()
@@ -210,7 +232,8 @@ class BatchEngine:
             while self.waiting and free:
                 r = self.waiting[0]
                 new_max = max(n_max, len(r.ids))
-                if group and new_max * (len(group) + 1) > self.max_prefill_tokens:
+                if group and (new_max * (len(group) + 1) > self.max_prefill_tokens or r.embeds is not None
+                              or group[0].embeds is not None):
                     break
                 if not cache.reserve(r.rid, len(r.ids) + r.max_new_tokens):
                     break  # pages are short: the request stays first in line until others retire

@@ -95,7 +95,7 @@ class Cosmos3Server:
     def __init__(self, pipe, reasoner=None, vit=None, model_name: str = "nvidia/Cosmos3-Nano",
                  guardrails_default: bool = True, allowed_local_media_path: str = "/", batch_engine=None):
         self.pipe, self.reasoner, self.vit = pipe, reasoner, vit
-        # serve/engine.py::EngineWorker: text-only chat requests share decode steps (continuous batching)
+        # serve/engine.py::EngineWorker: chat requests share decode steps (continuous batching)
         self.batch_engine = batch_engine
         self.model_name = model_name
         self.guardrails_default = guardrails_default
@@ -271,21 +271,6 @@ class Cosmos3Server:
                             top_k=int(body.get("top_k", extra.get("top_k", 20))),
                             repetition_penalty=float(body.get("repetition_penalty", extra.get("repetition_penalty", 1.0))),
                             presence_penalty=float(body.get("presence_penalty", 1.5)), seed=body.get("seed"))
-        if self.batch_engine is not None and not vision_embeds and dc.seed is None:
-            # text-only request: joins the running decode batch instead of taking the generation lock
-            # (sampling runs on the device; a request that pins a seed takes the single-request path)
-            r = self.batch_engine.submit(ids, dc.max_new_tokens, (tok.eos_id, tok.eot_id),
-                                         temperature=dc.temperature if dc.do_sample else 0.0, top_k=dc.top_k,
-                                         top_p=dc.top_p, presence_penalty=dc.presence_penalty,
-                                         repetition_penalty=dc.repetition_penalty).result()
-            t1 = time.time()
-            self.metrics.record((r.t_first - t0) * 1e3, (t1 - t0) * 1e3, len(r.out))
-            return {"id": f"chatcmpl-{uuid.uuid4().hex[:24]}", "object": "chat.completion", "created": int(t0),
-                    "model": body.get("model", self.model_name),
-                    "choices": [{"index": 0, "message": {"role": "assistant", "content": tok.decode(r.out)},
-                                 "finish_reason": r.finish_reason}],
-                    "usage": {"prompt_tokens": len(ids), "completion_tokens": len(r.out),
-                              "total_tokens": len(ids) + len(r.out)}}
         first = {}
 
         def on_token(_t):
@@ -298,6 +283,30 @@ class Cosmos3Server:
         pad_id = tok.video_pad_id if any(g[0] > 1 for g in grids) else tok.image_pad_id
         if ve is not None and len({tok.image_pad_id, tok.video_pad_id}) == 2:
             ids = [pad_id if t in (tok.image_pad_id, tok.video_pad_id) else t for t in ids]
+        if self.batch_engine is not None and dc.seed is None:
+            # joins the running decode batch instead of taking the generation lock (sampling runs on the
+            # device; a request that pins a seed takes the single-request path). A prompt with media is
+            # prefilled on its own (vision rows spliced in, 3-D rotary ids, DeepStack features) and then decodes
+            # with everybody else.
+            extra_kw = {}
+            if ve is not None:
+                ids_t = torch.tensor([ids], dtype=torch.long, device=dev)
+                vmask = ids_t == pad_id
+                x = self.reasoner.embed(ids_t.clamp(max=self.pipe.cfg.vocab_size - 1), ve, vmask)
+                extra_kw = dict(embeds=x[0], positions=self.reasoner.positions(ids_t, vmask, grids),
+                                vision_mask=vmask[0], deepstack=ds)
+            r = self.batch_engine.submit(ids, dc.max_new_tokens, (tok.eos_id, tok.eot_id),
+                                         temperature=dc.temperature if dc.do_sample else 0.0, top_k=dc.top_k,
+                                         top_p=dc.top_p, presence_penalty=dc.presence_penalty,
+                                         repetition_penalty=dc.repetition_penalty, **extra_kw).result()
+            t1 = time.time()
+            self.metrics.record((r.t_first - t0) * 1e3, (t1 - t0) * 1e3, len(r.out))
+            return {"id": f"chatcmpl-{uuid.uuid4().hex[:24]}", "object": "chat.completion", "created": int(t0),
+                    "model": body.get("model", self.model_name),
+                    "choices": [{"index": 0, "message": {"role": "assistant", "content": tok.decode(r.out)},
+                                 "finish_reason": r.finish_reason}],
+                    "usage": {"prompt_tokens": len(ids), "completion_tokens": len(r.out),
+                              "total_tokens": len(ids) + len(r.out)}}
         with self.gen_lock:
             out_ids, usage = self.reasoner.generate(ids, dc, (tok.eos_id, tok.eot_id), ve, pad_id if ve is not None else None,
                                                     grids, on_token, deepstack=ds)
@@ -473,7 +482,7 @@ def main(argv=None) -> int:
                     help="the vision encoder is replicated on every rank (data); accepted for CLI compatibility")
     ap.add_argument("--media-io-kwargs", default=None, help='JSON, e.g. {"video": {"num_frames": -1}}')
     ap.add_argument("--max-num-seqs", type=int, default=8,
-                    help="decode slots of the continuous-batching engine for text-only chat requests (0 = off)")
+                    help="decode slots of the continuous-batching engine for chat requests (0 = off)")
     ap.add_argument("--max-model-len", type=int, default=8192)
     args = ap.parse_args(argv)
     apply_deploy_config(args)

@@ -138,3 +138,40 @@ def test_sampled_requests_run_through_the_engine():
     eng.run_until_done()
     assert len(a.out) == 8 and len(b.out) == 8
     _check_against_reference(model, b)                        # the sampled neighbour does not disturb it
+
+
+def test_request_with_vision_embeddings_joins_the_batch():
+    """A prompt with a vision grid (3-D rotary ids, DeepStack features) is prefilled on its own and then
+    decodes in the same batch as text requests; its tokens follow the single-request engine's logits."""
+    from cosmos_b200.models.vit import VisionEncoder
+
+    torch.manual_seed(0)
+    cfg = tiny_config(n_layers=2, vocab_size=300, vit_deepstack=(0,))
+    model = MoTModel(cfg, dtype=torch.float32, device="cpu")
+    model.init_weights(seed=11)
+    vit = VisionEncoder(cfg).float().eval()
+    with torch.no_grad():
+        emb, grid, deep = vit(torch.rand(2, 3, 64, 64) * 2 - 1, return_deepstack=True)
+    n_vis = grid[0] * grid[1] * grid[2]
+    pad = 299
+    ids = [5, 6] + [pad] * n_vis + [7, 8, 9]
+    ref = ReasonerEngine(model, vit)
+    ids_t = torch.tensor([ids])
+    vmask = ids_t == pad
+    x = ref.embed(ids_t, emb, vmask)
+    pos = ref.positions(ids_t, vmask, [grid])
+    assert rope.next_start(pos) < len(ids)               # the grid advances the ids slower than one per token
+
+    eng = BatchEngine(model, max_batch=3, max_len=64, page_size=4, use_graph=False)
+    text = eng.submit([1, 2, 3, 4], 6)
+    vis = eng.submit(ids, 6, embeds=x[0], positions=pos, vision_mask=vmask[0], deepstack=deep)
+    eng.run_until_done()
+    assert len(vis.out) == 6 and len(text.out) == 6
+    _check_against_reference(model, text)
+    logits, kvs = ref.prefill(x, pos, deep, vmask)
+    p = rope.next_start(pos)
+    for tok in vis.out:
+        lg = logits[0]
+        assert lg[tok] >= lg.max() - 1e-3, (tok, float(lg[tok]), float(lg.max()))
+        logits, kvs = ref.decode_one(torch.tensor([tok]), p, kvs)
+        p += 1

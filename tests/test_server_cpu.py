@@ -151,5 +151,19 @@ def test_concurrent_text_chats_share_the_batching_engine():
                    for o in outs)
         total = sum(o["usage"]["completion_tokens"] for o in outs)
         assert worker.engine.steps < total
+        # a request with an image goes through the same engine (prefilled alone, decoded with the batch)
+        from cosmos_b200.models.vit import VisionEncoder
+        from PIL import Image
+        vit = VisionEncoder(pipe.cfg).eval()
+        srv.vit, srv.reasoner = vit, ReasonerEngine(pipe.transformer, vit)
+        img = io.BytesIO()
+        Image.fromarray((np.random.rand(64, 64, 3) * 255).astype(np.uint8)).save(img, format="PNG")
+        url = "data:image/png;base64," + base64.b64encode(img.getvalue()).decode()
+        steps0 = worker.engine.steps
+        r = c.post("/v1/chat/completions", json={"model": "nvidia/Cosmos3-Nano", "max_tokens": 4, "temperature": 0.7,
+                   "messages": [{"role": "user", "content": [{"type": "image_url", "image_url": {"url": url}},
+                                                              {"type": "text", "text": "what is this?"}]}]})
+        assert r.status_code == 200, r.text
+        assert r.json()["usage"]["completion_tokens"] <= 4 and worker.engine.steps > steps0
     finally:
         worker.close()
