@@ -369,15 +369,18 @@ class Cosmos3OmniPipeline:
                  add_resolution_template: bool = True, add_duration_template: bool = True,
                  generator: Optional[torch.Generator] = None, output_type: str = "np",
                  sampling: Optional[SamplingConfig] = None, callback=None, **prep_kw) -> Cosmos3Output:
+        from .utils.obs import nvtx_range
         t0 = time.perf_counter()
         seed = int(generator.initial_seed()) if generator is not None else (sampling.seed if sampling else 0)
-        st, sc = self.prepare(prompt, negative_prompt, image, video, num_frames, height, width, fps,
-                              num_inference_steps, guidance_scale, enable_sound, add_resolution_template,
-                              add_duration_template, seed=seed, sampling=sampling, **prep_kw)
+        with nvtx_range("generate/prepare"):
+            st, sc = self.prepare(prompt, negative_prompt, image, video, num_frames, height, width, fps,
+                                  num_inference_steps, guidance_scale, enable_sound, add_resolution_template,
+                                  add_duration_template, seed=seed, sampling=sampling, **prep_kw)
         t1 = time.perf_counter()
         x = self.begin(st, sc)
         for i in range(sc.num_steps):
-            x = self.step(x, i)
+            with nvtx_range(f"generate/step{i}"):
+                x = self.step(x, i)
             if callback is not None:
                 callback(i, sc.num_steps)
         if self.device.type == "cuda":
@@ -386,7 +389,8 @@ class Cosmos3OmniPipeline:
         t2 = time.perf_counter()
         if output_type == "latent":
             return Cosmos3Output(latents=x, timings={"prepare_s": t1 - t0, "sample_s": t2 - t1})
-        frames, sound, action = self.decode(x, st)
+        with nvtx_range("generate/decode"):
+            frames, sound, action = self.decode(x, st)
         if self.safety_checker is not None:
             frames = self.safety_checker.blur_faces(frames)
         t3 = time.perf_counter()

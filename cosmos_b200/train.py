@@ -120,9 +120,13 @@ class Trainer:
         return self._train_step(latents, text_ids, generator, **kw)
 
     def _train_step(self, latents, text_ids, generator=None, **kw) -> Dict[str, float]:
-        loss = self.loss(latents, text_ids, generator, **kw)
-        loss.backward()
-        gnorm = self.fsdp.step()
+        from .utils.obs import nvtx_range
+        with nvtx_range("train/forward"):
+            loss = self.loss(latents, text_ids, generator, **kw)
+        with nvtx_range("train/backward"):
+            loss.backward()
+        with nvtx_range("train/optimizer"):
+            gnorm = self.fsdp.step()
         lv = loss.detach().float()
         if self.mesh.world > 1 and dist.is_initialized():
             dist.all_reduce(lv)
@@ -191,6 +195,7 @@ def main(argv=None) -> int:
     ap.add_argument("--save-dir", default=None)
     ap.add_argument("--resume", action="store_true")
     ap.add_argument("--layers", type=int, default=0)
+    ap.add_argument("--log-jsonl", default=None, help="append one JSON record per step to this file (rank 0)")
     ap.add_argument("--health-timeout", type=float, default=None,
                     help="seconds to wait on the host for every rank before each step (peer failure detection)")
     args = ap.parse_args(argv)
@@ -221,6 +226,8 @@ def main(argv=None) -> int:
     g = torch.Generator(device=dev).manual_seed(1000 + data_rank)
     tokens_per_step = args.micro_batch * (t // cfg.patch_t) * (h // cfg.patch_hw) * (w // cfg.patch_hw)
     tokens_per_step = (tokens_per_step + args.micro_batch * args.text_len) * mesh.size("dp_shard") * mesh.size("dp_replicate")
+    from .utils.obs import JsonlLogger
+    logger = JsonlLogger(args.log_jsonl, stdout=True)  # rank 0 only
     times = []
     for s in range(step0, step0 + args.warmup + args.steps):
         lat = torch.randn(args.micro_batch, c, t, h, w, generator=g, device=dev, dtype=dtype)
@@ -234,8 +241,7 @@ def main(argv=None) -> int:
         dt = time.perf_counter() - t0
         if s >= step0 + args.warmup:
             times.append(dt)
-        if rank == 0:
-            print(json.dumps({"step": s + 1, **out, "step_s": round(dt, 4)}), flush=True)
+        logger.log(step=s + 1, **out, step_s=round(dt, 4))
     if args.save_dir:
         tr.save(args.save_dir, step0 + args.warmup + args.steps)
     if rank == 0 and times:
