@@ -50,6 +50,7 @@ class Request:
     positions: Optional[torch.Tensor] = None
     vision_mask: Optional[torch.Tensor] = None
     deepstack: Optional[Sequence[torch.Tensor]] = None
+    on_token: Optional[object] = None   # callable(token id), called from the engine thread for every new token
     out: List[int] = field(default_factory=list)
     slot: int = -1
     t_submit: float = 0.0
@@ -102,7 +103,7 @@ class BatchEngine:
                temperature: float = 0.0, top_k: int = 20, top_p: float = 1.0, presence_penalty: float = 0.0,
                repetition_penalty: float = 1.0, embeds: Optional[torch.Tensor] = None,
                positions: Optional[torch.Tensor] = None, vision_mask: Optional[torch.Tensor] = None,
-               deepstack: Optional[Sequence[torch.Tensor]] = None) -> Request:
+               deepstack: Optional[Sequence[torch.Tensor]] = None, on_token=None) -> Request:
         if len(ids) < 1:
             raise ValueError("empty prompt")
         if len(ids) + max_new_tokens > self.max_len:
@@ -110,7 +111,7 @@ class BatchEngine:
         r = Request(self._next_rid, [min(int(t), self.cfg.vocab_size - 1) for t in ids], int(max_new_tokens),
                     tuple(eos_ids), float(temperature), int(top_k) if top_k and top_k > 0 else TPDecoder.SAMPLE_K,
                     float(top_p), float(presence_penalty), float(repetition_penalty), embeds, positions, vision_mask,
-                    deepstack, t_submit=time.time())
+                    deepstack, on_token, t_submit=time.time())
         if embeds is not None and (positions is None or embeds.shape[0] != len(r.ids)):
             raise ValueError("a request with embeddings needs positions [3, n] and one embedding row per prompt token")
         self._next_rid += 1
@@ -199,6 +200,8 @@ class BatchEngine:
     def _accept(self, r: Request, tok: int) -> None:
         """Books a generated token; retires the request when it ends."""
         r.out.append(tok)
+        if r.on_token is not None:
+            r.on_token(tok)
         if tok in r.eos_ids:
             self._retire(r, "stop")
         elif len(r.out) >= r.max_new_tokens:

@@ -238,7 +238,49 @@ class Cosmos3Server:
         return self.videos_status(job_id)
 
     # ------------------------------------------------------------------ chat
-    def chat_completions(self, body: dict) -> dict:
+    def chat_stream(self, body: dict):
+        """Server-sent events for `"stream": true`: one `chat.completion.chunk` per piece of decoded text as
+        the tokens come out of the decode batch, a last chunk with the finish reason, then `[DONE]`."""
+        import queue
+
+        q: "queue.Queue" = queue.Queue()
+        cid, t0 = f"chatcmpl-{uuid.uuid4().hex[:24]}", int(time.time())
+        model = body.get("model", self.model_name)
+        result: dict = {}
+
+        def run():
+            try:
+                result["final"] = self.chat_completions(body, on_token=q.put)
+            except Exception as e:  # noqa: BLE001 - reported to the client as an error event
+                result["error"] = f"{type(e).__name__}: {e}"
+            q.put(None)
+
+        threading.Thread(target=run, daemon=True).start()
+
+        def chunk(delta: dict, finish=None) -> str:
+            return "data: " + json.dumps({"id": cid, "object": "chat.completion.chunk", "created": t0, "model": model,
+                                          "choices": [{"index": 0, "delta": delta, "finish_reason": finish}]}) + "\n\n"
+
+        tok = self.pipe.tokenizer
+        ids: List[int] = []
+        sent = ""
+        yield chunk({"role": "assistant", "content": ""})
+        while True:
+            t = q.get()
+            if t is None:
+                break
+            ids.append(int(t))
+            text = tok.decode(ids)
+            if len(text) > len(sent) and not text.endswith("\ufffd"):  # hold back an incomplete multi-byte character
+                yield chunk({"content": text[len(sent):]})
+                sent = text
+        if "error" in result:
+            yield "data: " + json.dumps({"error": {"message": result["error"]}}) + "\n\n"
+        else:
+            yield chunk({}, result["final"]["choices"][0]["finish_reason"])
+        yield "data: [DONE]\n\n"
+
+    def chat_completions(self, body: dict, on_token=None) -> dict:
         if self.reasoner is None:
             raise RuntimeError("this server was started without the Reasoner")
         t0 = time.time()
@@ -272,9 +314,12 @@ class Cosmos3Server:
                             repetition_penalty=float(body.get("repetition_penalty", extra.get("repetition_penalty", 1.0))),
                             presence_penalty=float(body.get("presence_penalty", 1.5)), seed=body.get("seed"))
         first = {}
+        user_cb = on_token
 
         def on_token(_t):
             first.setdefault("t", time.time())
+            if user_cb is not None:
+                user_cb(_t)
 
         ve = torch.cat(vision_embeds) if vision_embeds else None
         # DeepStack features of all media items, level by level
@@ -298,7 +343,8 @@ class Cosmos3Server:
             r = self.batch_engine.submit(ids, dc.max_new_tokens, (tok.eos_id, tok.eot_id),
                                          temperature=dc.temperature if dc.do_sample else 0.0, top_k=dc.top_k,
                                          top_p=dc.top_p, presence_penalty=dc.presence_penalty,
-                                         repetition_penalty=dc.repetition_penalty, **extra_kw).result()
+                                         repetition_penalty=dc.repetition_penalty, on_token=user_cb,
+                                         **extra_kw).result()
             t1 = time.time()
             self.metrics.record((r.t_first - t0) * 1e3, (t1 - t0) * 1e3, len(r.out))
             return {"id": f"chatcmpl-{uuid.uuid4().hex[:24]}", "object": "chat.completion", "created": int(t0),
@@ -434,7 +480,11 @@ def create_app(server: Cosmos3Server):
     @app.post("/v1/chat/completions")
     async def chat(request: Request):
         try:
-            return server.chat_completions(await request.json())
+            body = await request.json()
+            if body.get("stream"):
+                from starlette.responses import StreamingResponse
+                return StreamingResponse(server.chat_stream(body), media_type="text/event-stream")
+            return server.chat_completions(body)
         except Exception as e:  # noqa: BLE001
             raise HTTPException(400, f"{type(e).__name__}: {e}")
 

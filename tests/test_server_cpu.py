@@ -167,3 +167,20 @@ def test_concurrent_text_chats_share_the_batching_engine():
         assert r.json()["usage"]["completion_tokens"] <= 4 and worker.engine.steps > steps0
     finally:
         worker.close()
+
+
+def test_chat_streaming_sends_chunks_then_done(client):
+    """`"stream": true`: server-sent events whose deltas add up to the non-streamed answer (greedy)."""
+    body = {"model": "nvidia/Cosmos3-Nano", "max_tokens": 6, "temperature": 0.0,
+            "messages": [{"role": "user", "content": "say something"}]}
+    whole = client.post("/v1/chat/completions", json=body).json()
+    with client.stream("POST", "/v1/chat/completions", json={**body, "stream": True}) as r:
+        assert r.status_code == 200 and r.headers["content-type"].startswith("text/event-stream")
+        events = [line[6:] for line in r.iter_lines() if line.startswith("data: ")]
+    assert events[-1] == "[DONE]"
+    chunks = [json.loads(e) for e in events[:-1]]
+    assert all(c["object"] == "chat.completion.chunk" for c in chunks)
+    assert chunks[0]["choices"][0]["delta"].get("role") == "assistant"
+    text = "".join(c["choices"][0]["delta"].get("content", "") for c in chunks)
+    assert text == whole["choices"][0]["message"]["content"]
+    assert chunks[-1]["choices"][0]["finish_reason"] in ("stop", "length")
