@@ -1,0 +1,118 @@
+"""Hugging Face front end for the Reasoner: `Cosmos3ReasonerForConditionalGeneration` with the usual
+`from_pretrained` / `generate` calls, registered with the `transformers` auto classes under the model
+type `cosmos3_reasoner` (what the reference's `packages/transformers-cosmos3` and `packages/vllm-cosmos3`
+plug-ins provide for its checkpoints: reference cookbooks/cosmos3/reasoner/run_with_vllm.ipynb:132-133,
+cookbooks/cosmos3/README.md:165-166). The model underneath is this package's AR tower + vision encoder;
+generation runs through `ReasonerEngine` (contiguous KV) and follows the decoding defaults of
+`DecodingConfig`.
+"""
+from __future__ import annotations
+
+from typing import Optional, Sequence
+
+import torch
+
+from .config import DecodingConfig, MoTConfig, get_model_config
+from .models.mot import MoTModel
+from .models.reasoner import ReasonerEngine
+from .models.vit import VisionEncoder
+
+try:  # transformers is optional: without it the class below is a plain nn.Module with the same methods
+    from transformers import AutoConfig, AutoModelForCausalLM, PretrainedConfig, PreTrainedModel
+    _HAVE_HF = True
+except Exception:  # noqa: BLE001 - any import problem means "no transformers"
+    PretrainedConfig, PreTrainedModel = object, torch.nn.Module
+    _HAVE_HF = False
+
+
+class Cosmos3ReasonerConfig(PretrainedConfig):
+    model_type = "cosmos3_reasoner"
+
+    def __init__(self, arch: str = "Cosmos3-Nano", overrides: Optional[dict] = None, **kw):
+        self.arch = arch
+        self.overrides = dict(overrides or {})
+        if _HAVE_HF:
+            super().__init__(**kw)
+
+    def mot_config(self) -> MoTConfig:
+        return get_model_config(self.arch, **self.overrides)
+
+
+class Cosmos3ReasonerForConditionalGeneration(PreTrainedModel):
+    config_class = Cosmos3ReasonerConfig
+    base_model_prefix = "model"
+
+    def __init__(self, config: Cosmos3ReasonerConfig, dtype=torch.float32, device="cpu"):
+        if _HAVE_HF:
+            super().__init__(config)
+        else:
+            super().__init__()
+            self.config = config
+        cfg = config.mot_config()
+        self.model = MoTModel(cfg, dtype=dtype, device=device, towers=("ar",))
+        self.visual = VisionEncoder(cfg).to(device=device, dtype=dtype)
+        self.model.init_weights(seed=0)
+
+    def _init_weights(self, module):  # weights come from init_weights / a checkpoint, not from HF's initialiser
+        return
+
+    @classmethod
+    def from_pretrained(cls, name_or_path: str, torch_dtype=torch.float32, device_map: Optional[str] = None,
+                        config_overrides: Optional[dict] = None, **_):
+        """`name_or_path`: an architecture name (random-init weights) or a directory with `transformer/` safetensors
+        in this package's checkpoint layout."""
+        from pathlib import Path
+
+        from .ckpt import safetensors_io as sio
+
+        p = Path(name_or_path)
+        arch = name_or_path
+        if (p / "transformer" / "config.json").exists():
+            import json
+            arch = json.loads((p / "transformer" / "config.json").read_text()).get("name", "Cosmos3-Nano")
+        arch = arch.split("/")[-1]
+        m = cls(Cosmos3ReasonerConfig(arch, config_overrides), dtype=torch_dtype, device=device_map or "cpu")
+        if (p / "transformer").exists():
+            state = {k: v for k, v in sio.model_state(m.model).items()}
+            sio.load_into(p / "transformer", {k: v.data for k, v in state.items()}, strict=False)
+        return m.eval()
+
+    def forward(self, input_ids: torch.Tensor, **_):
+        """Teacher-forced logits [B, S, V] of text-only input (no KV reuse)."""
+        from .models import rope
+        cfg = self.model.cfg
+        x = self.model.embed_tokens(input_ids.clamp(max=cfg.vocab_size - 1))
+        h, _ = self.model.ar_forward(x, rope.text_positions(input_ids.shape[1], 0, input_ids.device))
+        return self.model.lm_logits(h).float()
+
+    @torch.no_grad()
+    def generate(self, input_ids, pixel_values: Optional[torch.Tensor] = None, image_token_id: Optional[int] = None,
+                 max_new_tokens: int = 64, do_sample: bool = False, temperature: float = 0.7, top_p: float = 0.8,
+                 top_k: int = 20, repetition_penalty: float = 1.0, presence_penalty: float = 0.0,
+                 eos_token_id: Optional[Sequence[int]] = None, seed: Optional[int] = None, **_) -> torch.Tensor:
+        """input_ids [1, S] (or a list); `pixel_values` [T, 3, H, W] in [-1, 1] fills the positions that hold
+        `image_token_id`. Returns prompt + completion ids [1, S + n]."""
+        ids = input_ids[0].tolist() if torch.is_tensor(input_ids) else list(input_ids)
+        eng = ReasonerEngine(self.model, self.visual)
+        ve = grids = deep = None
+        if pixel_values is not None:
+            ve, grid, deep = self.visual(pixel_values.to(next(self.visual.parameters()).dtype), return_deepstack=True)
+            grids = [grid]
+        dc = DecodingConfig(max_new_tokens=max_new_tokens, do_sample=do_sample, temperature=temperature, top_p=top_p,
+                            top_k=top_k, repetition_penalty=repetition_penalty, presence_penalty=presence_penalty,
+                            seed=seed)
+        eos = () if eos_token_id is None else ([eos_token_id] if isinstance(eos_token_id, int) else list(eos_token_id))
+        out, _ = eng.generate(ids, dc, eos, ve, image_token_id if ve is not None else None, grids or (), deepstack=deep)
+        return torch.tensor([ids + out], dtype=torch.long)
+
+
+def register() -> bool:
+    """Registers the config / model with the transformers auto classes (idempotent). False without transformers."""
+    if not _HAVE_HF:
+        return False
+    try:
+        AutoConfig.register(Cosmos3ReasonerConfig.model_type, Cosmos3ReasonerConfig)
+        AutoModelForCausalLM.register(Cosmos3ReasonerConfig, Cosmos3ReasonerForConditionalGeneration)
+    except ValueError:
+        pass  # already registered
+    return True
