@@ -150,6 +150,69 @@ def run_generator_sample(pipe, spec: InferenceSpec, out_dir: Path, quality: int,
     return rec
 
 
+def _reasoner_prompt(tokenizer, vit, cfg, spec: InferenceSpec, device):
+    """Token ids of the chat prompt and, for a prompt with media, the vision rows, grid, pad id and DeepStack features."""
+    from ..models.vae import CausalVideoVAE
+
+    content, vision_embeds, grids, n_vis, deep = [], None, [], [], None
+    if spec.vision_path:
+        frames, _ = media.read_video(spec.resolve(spec.vision_path), max_frames=16)
+        unit = cfg.vit_patch * cfg.vit_spatial_merge
+        h = min(max(unit, frames.shape[1] // unit * unit), 14 * unit)
+        w = min(max(unit, frames.shape[2] // unit * unit), 14 * unit)
+        from PIL import Image
+        fr = np.stack([np.asarray(Image.fromarray(f).resize((w, h))) for f in frames])
+        vid = CausalVideoVAE.from_uint8(torch.from_numpy(fr)[None])[0].permute(1, 0, 2, 3).to(device)
+        with torch.no_grad():
+            vision_embeds, grid, deep = vit(vid, return_deepstack=True)
+        grids, n_vis = [grid], [grid[0] * grid[1] * grid[2]]
+        content.append({"type": "image_url" if frames.shape[0] == 1 else "video_url"})
+    content.append({"type": "text", "text": spec.prompt_text()})
+    ids = tokenizer.apply_chat_template([{"role": "user", "content": content}], True, n_vis)
+    pad_id = tokenizer.video_pad_id if (grids and grids[0][0] > 1) else tokenizer.image_pad_id
+    return ids, vision_embeds, grids, pad_id, deep
+
+
+def run_reasoner_batch(pipe, vit, specs: List[InferenceSpec], out_root: Path, is_writer: bool, device,
+                       max_num_seqs: int = 32) -> List[Dict]:
+    """All reasoner samples of a spec file through the continuous-batching engine (`serve/engine.py`): they
+    share decode steps (one CUDA graph per step on a GPU), each with its own sampling parameters."""
+    from ..models.reasoner import ReasonerEngine
+    from ..serve.engine import BatchEngine
+
+    tok, ref = pipe.tokenizer, ReasonerEngine(pipe.transformer, vit)
+    prompts = [_reasoner_prompt(tok, vit, pipe.cfg, s, device) for s in specs]
+    longest = max(len(p[0]) + s.max_new_tokens for p, s in zip(prompts, specs))
+    eng = BatchEngine(pipe.transformer, max_batch=min(max_num_seqs, len(specs)), max_len=longest + 16)
+    t0 = time.perf_counter()
+    reqs = []
+    for s, (ids, ve, grids, pad_id, deep) in zip(specs, prompts):
+        kw = {}
+        if ve is not None:
+            ids_t = torch.tensor([ids], dtype=torch.long, device=device)
+            vmask = ids_t == pad_id
+            x = ref.embed(ids_t.clamp(max=pipe.cfg.vocab_size - 1), ve, vmask)
+            kw = dict(embeds=x[0], positions=ref.positions(ids_t, vmask, grids), vision_mask=vmask[0], deepstack=deep)
+        reqs.append(eng.submit(ids, s.max_new_tokens, (tok.eos_id, tok.eot_id),
+                               temperature=s.temperature if s.do_sample else 0.0, top_k=s.top_k, top_p=s.top_p,
+                               presence_penalty=s.presence_penalty, repetition_penalty=s.repetition_penalty, **kw))
+    eng.run_until_done()
+    if device.type == "cuda":
+        torch.cuda.synchronize()
+    wall = time.perf_counter() - t0
+    records = []
+    for s, r in zip(specs, reqs):
+        if is_writer:
+            d = out_root / s.name
+            d.mkdir(parents=True, exist_ok=True)
+            (d / "reasoner_text.txt").write_text(tok.decode(r.out))
+        dt = max(r.t_done - r.t_submit, 1e-9)
+        records.append({"name": s.name, "model_mode": "reasoner", "generation_time_s": dt,
+                        "tokens_per_s": len(r.out) / dt, "prompt_tokens": len(r.ids), "completion_tokens": len(r.out),
+                        "batch_wall_s": wall, "batch_tokens_per_s": sum(len(q.out) for q in reqs) / max(wall, 1e-9)})
+    return records
+
+
 def run_reasoner_sample(engine, tokenizer, vit, spec: InferenceSpec, out_dir: Path, is_writer: bool, device) -> Dict:
     from ..models.vae import CausalVideoVAE
 
@@ -229,8 +292,21 @@ def main(argv: Optional[List[str]] = None) -> int:
     replica, n_rep = mesh.index("dp_replicate"), mesh.size("dp_replicate")
     is_writer = all(mesh.index(a) == 0 for a in ("dp_shard", "cfgp", "cp", "tp"))
     records = []
+    mine = [s for i, s in enumerate(specs) if i % n_rep == replica]
+    batched = set()
+    # several reasoner samples (or any on a GPU) go through the batching engine; seeds pinned per sample and
+    # multi-rank layouts keep the per-sample path
+    rs = [s for s in mine if s.model_mode == "reasoner"]
+    if rs and world == 1 and (use_cuda or len(rs) > 1) and os.environ.get("COSMOS_REASONER_SINGLE") != "1":
+        from ..models.vit import VisionEncoder
+        vit = VisionEncoder(pipe.cfg).to(device=device, dtype=dtype).eval()
+        for rec in run_reasoner_batch(pipe, vit, rs, out_root, is_writer, device):
+            records.append(rec)
+            if is_writer:
+                print(json.dumps(rec), flush=True)
+        batched = {s.name for s in rs}
     for i, spec in enumerate(specs):
-        if i % n_rep != replica:
+        if i % n_rep != replica or spec.name in batched:
             continue
         out_dir = out_root / spec.name
         if spec.model_mode == "reasoner":
