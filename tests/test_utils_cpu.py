@@ -1,0 +1,68 @@
+"""Small contracts of utility modules: prompt upsampler fallback and schema keys, AV domain constants,
+phase timer / JSONL logger, CUDA-graph wrapper (GPU only)."""
+import json
+
+import pytest
+import torch
+
+
+def test_prompt_upsampler_returns_compact_json_with_template_fields():
+    from cosmos_b200.config import DecodingConfig, tiny_config
+    from cosmos_b200.models.mot import MoTModel
+    from cosmos_b200.models.reasoner import ReasonerEngine
+    from cosmos_b200.utils import prompt_upsampler as pu
+    from cosmos_b200.utils.tokenizer import load_tokenizer
+
+    assert pu.UPSAMPLER_DECODING.seed == 3407 and pu.UPSAMPLER_DECODING.presence_penalty == 1.5
+    assert {"subjects", "lighting", "cinematography", "actions", "audio_description"} <= set(pu.TOP_LEVEL_KEYS)
+    cfg = tiny_config(n_layers=1)
+    model = MoTModel(cfg, dtype=torch.float32, device="cpu")
+    model.init_weights(seed=2)
+    tok = load_tokenizer(None, cfg.vocab_size)
+    out = pu.upsample_prompt(ReasonerEngine(model), tok, "a cat jumps", 1280, 720, 5.0, 24,
+                             decoding=DecodingConfig(max_new_tokens=4, do_sample=False))
+    obj = json.loads(out)                                   # random weights: the fallback wraps the raw prompt
+    assert obj["temporal_caption"] == "a cat jumps" and obj["resolution"] == {"W": 1280, "H": 720}
+    assert obj["fps"] == 24 and obj["duration"] == 5.0 and ": " not in out
+
+
+def test_av_domain_constants_match_the_action_conventions():
+    from cosmos_b200.data.vfm.action import av_dataset as av
+    from cosmos_b200.io.spec import DOMAINS
+
+    assert (av.AV_ROTATION_FORMAT, av.AV_POSE_CONVENTION, av.AV_TRANSLATION_SCALE) == ("rot6d", "backward_framewise", 1.35)
+    assert av.DOMAIN_ACTION_DIM["av"] == 9 and av.DOMAIN_ACTION_DIM["droid_lerobot"] == 10
+    assert set(DOMAINS) <= set(av.DOMAIN_ACTION_DIM)
+    assert av.DOMAIN_DEFAULTS["av"]["action_chunk_size"] == 60 and av.DOMAIN_DEFAULTS["umi"]["image_size"] == 256
+
+
+def test_phase_timer_and_jsonl_logger(tmp_path):
+    from cosmos_b200.utils.obs import JsonlLogger, PhaseTimer, write_benchmark_json
+
+    t = PhaseTimer()
+    with t.phase("a"):
+        torch.randn(64, 64) @ torch.randn(64, 64)
+    with t.phase("a"):
+        pass
+    with t.phase("b"):
+        pass
+    s = t.summary_ms()
+    assert set(s) == {"a", "b"} and s["a"] >= 0
+    log = JsonlLogger(str(tmp_path / "log.jsonl"), stdout=False)
+    log.log(step=1, loss=0.5)
+    log.log(step=2, loss=0.25)
+    rows = [json.loads(line) for line in (tmp_path / "log.jsonl").read_text().splitlines()]
+    assert [r["step"] for r in rows] == [1, 2] and "ts" in rows[0]
+    p = write_benchmark_json(tmp_path, [{"generation_time_s": 2.0}, {"generation_time_s": 4.0}])
+    assert json.loads(p.read_text())["average"]["generation_time_s"] == 3.0
+
+
+@pytest.mark.gpu
+def test_graphed_callable_replays_with_new_inputs():
+    from cosmos_b200.utils.graphs import GraphedCallable
+
+    w = torch.randn(64, 64, device="cuda")
+    g = GraphedCallable(lambda x: torch.relu(x @ w), [torch.randn(8, 64, device="cuda")])
+    for _ in range(3):
+        x = torch.randn(8, 64, device="cuda")
+        torch.testing.assert_close(g(x), torch.relu(x @ w))
