@@ -1,7 +1,7 @@
 """Micro-benchmarks of the hot kernels: CUDA-event timing after warm-up, L2 flushed between
 iterations, achieved TFLOP/s (or GB/s) and fraction of the measured peaks.
 
-    python -m cosmos_b200.ops.bench_kernels [--what gemm,attn,attnbwd,norm,paged,vae] [--iters 5] [--small]
+    python -m cosmos_b200.ops.bench_kernels [--what gemm,qkvroute,attn,attnbwd,norm,paged,vae] [--iters 5] [--small]
 """
 from __future__ import annotations
 
@@ -70,6 +70,30 @@ def main():
                 rec["cublas_ms"] = round(ms2, 4)
             out.append(rec)
             print(json.dumps(rec), flush=True)
+    if "qkvroute" in what:
+        # the QKV projection whose epilogue applies q/k RMS-norm + rotary and scatters every 128-column head chunk
+        # through a routing table: the seq -> head all-to-all of Ulysses context parallelism as epilogue stores.
+        # On one GPU the table points at local buffers (the kernel issues the same stores; with peers they are
+        # peer mappings), which is what a single-GPU profiler capture can see of the fused kernel.
+        m, d, hq, hk = (8192, 4096, 32, 8) if args.small else (27904, 4096, 32, 8)   # 111,616 tokens / cp 4
+        n = (hq + 2 * hk) * 128
+        a = torch.randn(m, d, device=dev).bfloat16()
+        w = (torch.randn(n, d, device=dev) / math.sqrt(d)).bfloat16()
+        ang = torch.rand(m, 64, device=dev) * 6.0
+        cos, sin = ang.cos().contiguous(), ang.sin().contiguous()
+        gq = torch.ones(128, device=dev).bfloat16()
+        gk = torch.ones(128, device=dev).bfloat16()
+        bufs = [torch.empty(m, 128, device=dev, dtype=torch.bfloat16) for _ in range(n // 128)]
+        ptr = torch.tensor([b.data_ptr() for b in bufs], device=dev, dtype=torch.int64)
+        ld = torch.full((n // 128,), 128, device=dev, dtype=torch.int64)
+        ms = timeit(lambda: ops.gemm_qkv_rope(a, w, None, cos, sin, gq, gk, hq, hk, 1e-6, ptr, ld), args.iters, flush)
+        tf = 2.0 * m * n * d / ms / 1e9
+        ms0 = timeit(lambda: ops.gemm(a, w), args.iters, flush)
+        rec = {"kernel": "gemm_bf16_tcgen05 + q/k norm + rotary + routed head stores", "shape": [m, n, d],
+               "ms": round(ms, 4), "tflops": round(tf, 1), f"frac_of_{src}_bf16": round(tf / tf_peak, 3),
+               "plain_epilogue_ms": round(ms0, 4)}
+        out.append(rec)
+        print(json.dumps(rec), flush=True)
     if "attn" in what:
         cfgs = [(4096, 4096, 8, 2)] if args.small else [(16384, 16384, 8, 2), (32768, 32768, 8, 2)]
         if args.attn_shape:
