@@ -132,17 +132,17 @@ class TPDecoder:
         logits = ops.gemm(h, self.lm_head).float()   # [B, V/tp]
         self.last_logits = logits                    # this rank's vocab shard, kept for inspection
         if self.sampling is not None:
-            logits = self._penalise(logits)
-        val, idx = logits.max(dim=-1)
-        if self.sampling is not None:
-            idx = self._sample(logits, idx)
-        idx = idx + self.rank * self.v_loc
-        if self.tp > 1:
-            packed = torch.stack([val, idx.float()], dim=-1)      # [B, 2]
-            allp = torch.empty(self.tp, b, 2, device=self.device)
-            dist.all_gather_into_tensor(allp, packed, group=self.group)
-            best = allp[..., 0].argmax(dim=0)
-            idx = allp[best, torch.arange(b, device=self.device), 1].long()
+            idx = self._sample(self._penalise(logits), distributed=True)   # global ids across the vocab shards
+        else:
+            val, idx = logits.max(dim=-1)
+            idx = idx + self.rank * self.v_loc
+            if self.tp > 1:
+                packed = torch.stack([val, idx.float()], dim=-1)      # [B, 2]
+                allp = torch.empty(self.tp * b, 2, device=self.device)            # rank-major concatenation
+                dist.all_gather_into_tensor(allp, packed, group=self.group)
+                allp = allp.view(self.tp, b, 2)
+                best = allp[..., 0].argmax(dim=0)
+                idx = allp[best, torch.arange(b, device=self.device), 1].long()
         self.next_tokens.copy_(idx.clamp(max=self.cfg.vocab_size - 1))
 
     # ------------------------------------------------------------------ sampling (tp = 1)
@@ -153,8 +153,7 @@ class TPDecoder:
         temperature (0 = greedy), top_k, top_p, presence / repetition penalty, `seen_out` / `seen_any`
         ([B, V] flags of tokens generated / seen in prompt or output) and a buffer of uniform noise that
         the host refills before every step (the Gumbel-max draw inside the graph then needs no generator)."""
-        assert self.tp == 1, "device-side sampling is implemented for one rank"
-        dev, v = self.device, self.v_loc
+        dev, v = self.device, self.v_loc  # `seen_*` cover this rank's vocabulary shard
         self.sampling = {
             "temperature": torch.zeros(batch, device=dev), "top_k": torch.ones(batch, dtype=torch.long, device=dev),
             "top_p": torch.ones(batch, device=dev), "presence": torch.zeros(batch, device=dev),
@@ -172,19 +171,36 @@ class TPDecoder:
         """Repetition penalty (CTRL style) on tokens seen in prompt or output, presence penalty on generated
         tokens; the token consumed by this step (self.tokens) counts as generated."""
         sp = self.sampling
-        idx = self.tokens[:, None]
-        sp["seen_out"].scatter_(1, idx, True)   # scalar-valued scatter: no host tensor, so it can sit in the graph
-        sp["seen_any"].scatter_(1, idx, True)
+        loc = self.tokens - self.rank * self.v_loc            # position in this rank's vocabulary shard
+        mine = ((loc >= 0) & (loc < self.v_loc))[:, None]
+        idx = loc.clamp(0, self.v_loc - 1)[:, None]
+        # device-side scatter (no host tensor involved, so it can sit in the graph); tokens of other shards write
+        # back what was there
+        sp["seen_out"].scatter_(1, idx, sp["seen_out"].gather(1, idx) | mine)
+        sp["seen_any"].scatter_(1, idx, sp["seen_any"].gather(1, idx) | mine)
         rep = sp["repetition"][:, None]
         pen = torch.where(logits > 0, logits / rep, logits * rep)
         logits = torch.where(sp["seen_any"], pen, logits)
         return logits - sp["presence"][:, None] * sp["seen_out"].float()
 
-    def _sample(self, logits: torch.Tensor, greedy_idx: torch.Tensor) -> torch.Tensor:
-        """Top-k / top-p sampling among the SAMPLE_K best logits of every slot with the Gumbel-max trick."""
+    def _sample(self, logits: torch.Tensor, distributed: bool) -> torch.Tensor:
+        """Top-k / top-p sampling among the SAMPLE_K best logits of every slot with the Gumbel-max trick; returns
+        token ids in the full vocabulary. `distributed`: `logits` is this rank's vocabulary shard and the
+        candidates of all ranks are merged (every rank ends up with the same choice: same candidates, same noise)."""
         sp = self.sampling
         k = min(self.SAMPLE_K, logits.shape[-1])
         vals, cand = torch.topk(logits, k, dim=-1)                    # sorted, best first
+        if distributed:
+            cand = cand + self.rank * self.v_loc
+            if self.tp > 1:
+                b = logits.shape[0]
+                packed = torch.stack([vals, cand.float()], dim=-1).contiguous()          # [B, k, 2]
+                allp = torch.empty(self.tp * b, k, 2, device=logits.device)   # rank-major concatenation
+                dist.all_gather_into_tensor(allp, packed, group=self.group)
+                allp = allp.view(self.tp, b, k, 2).permute(1, 0, 2, 3).reshape(b, self.tp * k, 2)
+                vals, pos = torch.topk(allp[..., 0], k, dim=-1)
+                cand = allp[..., 1].gather(1, pos).long()
+        greedy_idx = cand[:, 0]
         t = sp["temperature"][:, None]
         z = vals / torch.where(t > 0, t, torch.ones_like(t))
         rank = torch.arange(k, device=logits.device)[None]

@@ -62,14 +62,23 @@ class Request:
 
 class BatchEngine:
     def __init__(self, model, max_batch: int = 8, max_len: int = 4096, page_size: int = 16, device=None,
-                 dtype=None, use_graph: Optional[bool] = None):
+                 dtype=None, use_graph: Optional[bool] = None, group=None):
+        """`group`: tensor-parallel process group (None = one rank). Every rank of the group builds the engine on
+        the same model weights; rank 0 of the group takes the requests (`submit`), the others call `follow()`."""
+        import torch.distributed as dist
+
         self.model = model
         self.cfg: MoTConfig = model.cfg
         p = next(model.parameters())
         self.device = torch.device(device) if device is not None else p.device
         dtype = dtype or p.dtype
         self.max_batch, self.max_len = max_batch, max_len
-        self.dec = TPDecoder(self.cfg, 1, 0, None, self.device, page_size=page_size, max_batch=max_batch,
+        self.group = group
+        self.tp = dist.get_world_size(group) if group is not None else 1
+        self.rank = dist.get_rank(group) if group is not None else 0
+        self._new: List[dict] = []      # requests submitted on rank 0 since the last step (sent to the followers)
+        self._stop = False
+        self.dec = TPDecoder(self.cfg, self.tp, self.rank, group, self.device, page_size=page_size, max_batch=max_batch,
                              max_len=max_len, dtype=dtype)
         self.dec.load_from(model)
         cache = self.dec.cache
@@ -108,15 +117,58 @@ class BatchEngine:
             raise ValueError("empty prompt")
         if len(ids) + max_new_tokens > self.max_len:
             raise ValueError(f"prompt ({len(ids)}) + max_new_tokens ({max_new_tokens}) exceeds max_len {self.max_len}")
-        r = Request(self._next_rid, [min(int(t), self.cfg.vocab_size - 1) for t in ids], int(max_new_tokens),
-                    tuple(eos_ids), float(temperature), int(top_k) if top_k and top_k > 0 else TPDecoder.SAMPLE_K,
-                    float(top_p), float(presence_penalty), float(repetition_penalty), embeds, positions, vision_mask,
-                    deepstack, on_token, t_submit=time.time())
+        if embeds is not None and self.tp > 1:
+            raise NotImplementedError("requests with media are served by one rank (tensor-parallel engine: text only)")
+        params = dict(ids=[min(int(t), self.cfg.vocab_size - 1) for t in ids], max_new_tokens=int(max_new_tokens),
+                      eos_ids=tuple(eos_ids), temperature=float(temperature),
+                      top_k=int(top_k) if top_k and top_k > 0 else TPDecoder.SAMPLE_K, top_p=float(top_p),
+                      presence_penalty=float(presence_penalty), repetition_penalty=float(repetition_penalty))
+        r = self._enqueue(params, embeds, positions, vision_mask, deepstack, on_token)
         if embeds is not None and (positions is None or embeds.shape[0] != len(r.ids)):
+            self.waiting.pop()
             raise ValueError("a request with embeddings needs positions [3, n] and one embedding row per prompt token")
+        if self.tp > 1:
+            self._new.append(params)
+        return r
+
+    def _enqueue(self, params: dict, embeds=None, positions=None, vision_mask=None, deepstack=None, on_token=None
+                 ) -> Request:
+        r = Request(self._next_rid, params["ids"], params["max_new_tokens"], params["eos_ids"], params["temperature"],
+                    params["top_k"], params["top_p"], params["presence_penalty"], params["repetition_penalty"],
+                    embeds, positions, vision_mask, deepstack, on_token, t_submit=time.time())
         self._next_rid += 1
         self.waiting.append(r)
         return r
+
+    def _sync_requests(self) -> None:
+        """Tensor-parallel engines: rank 0 sends what was submitted since the last step (and the stop flag); the
+        followers queue identical requests, so that admission, decoding and retirement run in lock-step."""
+        import torch.distributed as dist
+
+        payload = [(self._new, self._stop)] if self.rank == 0 else [None]
+        dist.broadcast_object_list(payload, src=dist.get_global_rank(self.group, 0), group=self.group)
+        new, stop = payload[0]
+        if self.rank == 0:
+            self._new = []
+        else:
+            self._stop = stop
+            for params in new:
+                self._enqueue(params)
+
+    def follow(self) -> None:
+        """Loop of the ranks other than 0: mirror every step of rank 0 until it calls `shutdown()`."""
+        assert self.tp > 1 and self.rank != 0
+        while True:
+            self.step()
+            if self._stop and not self.has_work():
+                return
+
+    def shutdown(self) -> None:
+        """Rank 0: lets the followers leave `follow()` (after the work in flight is done)."""
+        if self.tp > 1 and self.rank == 0:
+            self.run_until_done()
+            self._stop = True
+            self.step()
 
     def has_work(self) -> bool:
         return bool(self.waiting) or any(s is not None for s in self.slots)
@@ -155,8 +207,10 @@ class BatchEngine:
         pos = torch.arange(n_max, device=dev)[None].expand(bsz, -1)
         real = pos < len_t[:, None]                                          # [B, n_max]
         rows = PagedKVCache.slots(table, pos.clamp(max=cache.max_pages * dec.page_size - 1), dec.page_size)[real]
+        # every rank ran the full prefill; it keeps the K/V heads of its tensor-parallel shard
+        hs = slice(self.rank * dec.hk, (self.rank + 1) * dec.hk)
         for li, (k, v) in enumerate(kvs):
-            cache.write(li, k[real].contiguous(), v[real].contiguous(), rows)
+            cache.write(li, k[real][:, hs].contiguous(), v[real][:, hs].contiguous(), rows)
         last = h[torch.arange(bsz, device=dev), len_t - 1][:, None]          # [B, 1, d]
         logits = self.model.lm_logits(last).float()[:, 0]                    # [B, V]
         # per-slot sampling state; the prompt tokens count as "seen" for the repetition penalty
@@ -166,11 +220,11 @@ class BatchEngine:
                            ("repetition", [r.repetition_penalty for r in group])):
             sp[name][slot_idx] = torch.tensor(vals, dtype=torch.float32, device=dev)
         sp["top_k"][slot_idx] = torch.tensor([r.top_k for r in group], dtype=torch.long, device=dev)
-        seen = torch.zeros(bsz, dec.v_loc, dtype=torch.bool, device=dev)
-        seen.scatter_(1, ids.clamp(max=dec.v_loc - 1), real)
-        sp["seen_any"][slot_idx] = seen
+        seen = torch.zeros(bsz, dec.v_loc * self.tp, dtype=torch.bool, device=dev)   # whole (padded) vocabulary
+        seen.scatter_(1, ids, real)
+        sp["seen_any"][slot_idx] = seen[:, self.rank * dec.v_loc:(self.rank + 1) * dec.v_loc]
         sp["seen_out"][slot_idx] = False
-        first = self._first_tokens(logits, slot_idx, seen)
+        first = self._first_tokens(logits, slot_idx, seen[:, :logits.shape[1]])
         dec.lens[slot_idx] = len_t.to(dec.lens.dtype)
         dec.pos_delta[slot_idx] = torch.tensor(delta, dtype=torch.long, device=dev)
         dec.tokens[slot_idx] = first
@@ -187,13 +241,12 @@ class BatchEngine:
         dec, sp = self.dec, self.dec.sampling
         rep = sp["repetition"][slot_idx][:, None]
         pen = torch.where(logits > 0, logits / rep, logits * rep)
-        logits = torch.where(seen, pen, logits)[:, :dec.v_loc]
-        greedy = logits.argmax(dim=-1)
+        logits = torch.where(seen, pen, logits)
         sub = {k: (v[slot_idx] if v.shape[0] == self.max_batch else v) for k, v in sp.items()}
         sub["noise"] = torch.rand(len(slot_idx), dec.SAMPLE_K, device=logits.device, generator=self.noise_gen).clamp_min(1e-7)
         keep, dec.sampling = dec.sampling, sub
         try:
-            return dec._sample(logits, greedy)
+            return dec._sample(logits, distributed=False)
         finally:
             dec.sampling = keep
 
@@ -225,6 +278,8 @@ class BatchEngine:
     def step(self) -> List[Request]:
         """Admits what fits, runs one decode step for the batch, returns the requests that finished."""
         done_before = set(self.finished)
+        if self.tp > 1:
+            self._sync_requests()
         cache = self.dec.cache
         free = [i for i in range(self.max_batch) if self.slots[i] is None]
         while self.waiting and free:

@@ -23,6 +23,7 @@ from __future__ import annotations
 import base64
 import io
 import json
+import os
 import tempfile
 import threading
 import time
@@ -542,15 +543,35 @@ def main(argv=None) -> int:
     from ..models.vit import VisionEncoder
     from ..pipeline import Cosmos3OmniPipeline
 
-    dev = "cuda" if torch.cuda.is_available() else None
+    if torch.cuda.is_available():
+        torch.cuda.set_device(int(os.environ.get("LOCAL_RANK", "0")))
+    dev = f"cuda:{int(os.environ.get('LOCAL_RANK', '0'))}" if torch.cuda.is_available() else None
     dtype = torch.bfloat16 if (dev and args.dtype == "bf16") else torch.float32
     pipe = Cosmos3OmniPipeline.from_pretrained(args.model, torch_dtype=dtype, device_map=dev,
                                                enable_safety_checker=not args.no_guardrails)
     vit = VisionEncoder(pipe.cfg).to(device=pipe.device, dtype=dtype).eval()
     worker = None
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    group = None
+    if world > 1:
+        # launched with torchrun: the Reasoner's decode batch is tensor-parallel over all ranks; rank 0 serves HTTP
+        # (and runs the Generator endpoints on its own GPU), the other ranks mirror its engine steps
+        import torch.distributed as dist
+
+        from ..parallel.runtime import init_distributed
+        from ..config import ParallelConfig
+        init_distributed(world, int(os.environ.get("RANK", "0")), int(os.environ.get("LOCAL_RANK", "0")),
+                         pc=ParallelConfig(tp=world))
+        group = dist.group.WORLD
+        if args.max_num_seqs <= 0:
+            raise SystemExit("a multi-rank server needs --max-num-seqs > 0 (the tensor-parallel engine)")
     if args.max_num_seqs > 0:
         from .engine import BatchEngine, EngineWorker
-        worker = EngineWorker(BatchEngine(pipe.transformer, max_batch=args.max_num_seqs, max_len=args.max_model_len))
+        engine = BatchEngine(pipe.transformer, max_batch=args.max_num_seqs, max_len=args.max_model_len, group=group)
+        if world > 1 and int(os.environ.get("RANK", "0")) != 0:
+            engine.follow()
+            return 0
+        worker = EngineWorker(engine)
     server = Cosmos3Server(pipe, ReasonerEngine(pipe.transformer, vit), vit, args.model, not args.no_guardrails,
                            args.allowed_local_media_path, batch_engine=worker)
     uvicorn.run(create_app(server), host=args.host, port=args.port, log_level="info")

@@ -101,7 +101,6 @@ def test_device_side_sampling_follows_the_truncated_softmax():
     logits = torch.full((4, 300), -20.0)
     base = torch.tensor([2.0, 1.5, 1.0, 0.5, 0.0, -0.5])
     logits[:, 10:16] = base
-    greedy = logits.argmax(-1)
     sp["temperature"][:] = torch.tensor([1.0, 1.0, 0.0, 0.7])
     sp["top_k"][:] = torch.tensor([3, 64, 5, 1])
     sp["top_p"][:] = torch.tensor([1.0, 0.6, 1.0, 1.0])
@@ -110,7 +109,7 @@ def test_device_side_sampling_follows_the_truncated_softmax():
     counts = torch.zeros(4, 300)
     for _ in range(n):
         dec.refill_noise(g)
-        tok = dec._sample(logits, greedy)
+        tok = dec._sample(logits, distributed=True)
         counts[torch.arange(4), tok] += 1
     f = counts / n
     want0 = torch.softmax(base[:3], -1)                       # slot 0: top_k = 3
@@ -175,3 +174,38 @@ def test_request_with_vision_embeddings_joins_the_batch():
         assert lg[tok] >= lg.max() - 1e-3, (tok, float(lg[tok]), float(lg.max()))
         logits, kvs = ref.decode_one(torch.tensor([tok]), p, kvs)
         p += 1
+
+
+def _tp_engine_ranks(rank, world):
+    """Both ranks build the same model; rank 0 submits, rank 1 follows; returns what each rank decoded."""
+    import torch.distributed as dist
+
+    model = _model()
+    eng = BatchEngine(model, max_batch=3, max_len=48, page_size=4, use_graph=False, group=dist.group.WORLD)
+    if rank == 0:
+        a = eng.submit([5, 9, 2, 7, 1], 6)
+        b = eng.submit([3, 3, 8], 5)
+        eng.step()
+        c = eng.submit([4, 4, 4, 4, 9, 1, 2], 4, temperature=0.9, top_k=10, top_p=0.9, presence_penalty=1.0)
+        d = eng.submit([8, 6], 5)                       # waits for a free slot
+        eng.run_until_done()
+        eng.shutdown()
+        reqs = [a, b, c, d]
+    else:
+        eng.follow()
+        reqs = [eng.finished[i] for i in sorted(eng.finished)]
+    return {"outs": [r.out for r in reqs], "ids": [r.ids for r in reqs], "free": eng.dec.cache.alloc.num_free()}
+
+
+def test_tensor_parallel_engine_runs_in_lock_step_over_gloo():
+    from tests.dist_utils import run_ranks
+
+    out = run_ranks(_tp_engine_ranks, 2, timeout=180)
+    assert out[0]["outs"] == out[1]["outs"] and out[0]["ids"] == out[1]["ids"]      # followers mirror rank 0
+    assert [len(o) for o in out[0]["outs"]] == [6, 5, 4, 5]
+    assert out[0]["free"] == out[1]["free"]
+    model = _model()
+    for ids, toks, greedy in zip(out[0]["ids"], out[0]["outs"], [True, True, False, True]):
+        if greedy:                                       # greedy requests follow the single-process reference
+            from types import SimpleNamespace
+            _check_against_reference(model, SimpleNamespace(ids=ids, out=toks, rid=0))
