@@ -286,6 +286,17 @@ def paged_decode_ref(q, k_cache, v_cache, block_table, seq_lens, scale: Optional
     return out.to(q.dtype)
 
 
+def gemm_reduce_rmsnorm(a, w, residual, gamma, eps: float = 1e-6):
+    """x_new = residual + a @ w^T and h = rmsnorm(x_new) * gamma -> (h, x_new). On CUDA with a skinny problem
+    (decode: a few rows) the split-K reduction pass does the add and the norm as well, so an output projection
+    costs two launches instead of four."""
+    if _use_cuda(a, w, residual, gamma):
+        return _k().gemm_reduce_rmsnorm(a, w, residual.contiguous(), gamma, eps)
+    y = gemm(a, w)
+    h, x_new = rmsnorm(y, gamma, eps, residual=residual)
+    return h, x_new
+
+
 def decode_qkv_post(qkv, n_q_heads: int, cos, sin, q_gamma, k_gamma, eps: float, slots, k_cache, v_cache):
     """Decode-step glue after the QKV projection. qkv [B, Hq + 2 Hkv, 128]; q and k heads get their
     RMS-norm and the rotary rotation (cos/sin [B, 64]); k and v of sequence b are written into the

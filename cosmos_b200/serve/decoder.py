@@ -109,6 +109,22 @@ class TPDecoder:
         y = self._allreduce(ops.gemm(a, p["w_down"]))
         return x, y
 
+    def _layer_single(self, li: int, h: torch.Tensor, x: torch.Tensor, next_gamma: torch.Tensor, cos, sin, slots,
+                      table, lens, max_len: int):
+        """One layer on one rank (no all-reduce): `h` is the normalised input, `x` the residual stream. Both output
+        projections go through `gemm_reduce_rmsnorm`, whose reduction pass adds the residual and applies the next
+        norm (this layer's norm2, then the NEXT layer's norm1 / the final norm), so the layer is nine launches."""
+        p = self.layers[li]
+        cfg = self.cfg
+        b = x.shape[0]
+        qkv = ops.gemm(h, p["wqkv"]).view(b, self.hq + 2 * self.hk, self.hd)
+        q = ops.decode_qkv_post(qkv, self.hq, cos, sin, p["q_norm"], p["k_norm"], cfg.rms_eps, slots,
+                                self.cache.k[li], self.cache.v[li])
+        o = ops.paged_decode(q, self.cache.k[li], self.cache.v[li], table, lens, max_len=max_len)
+        h, x = ops.gemm_reduce_rmsnorm(o.view(b, -1), p["wo"], x, p["norm2"], cfg.rms_eps)
+        a = ops.gemm(h, p["w_gate_up"], epi=ops.EPI_SWIGLU)
+        return ops.gemm_reduce_rmsnorm(a, p["w_down"], x, next_gamma, cfg.rms_eps)
+
     def _step_impl(self) -> None:
         """Consumes self.tokens / self.lens (device), writes self.next_tokens and advances lens."""
         b = self.tokens.shape[0]
@@ -125,10 +141,17 @@ class TPDecoder:
         else:
             self.lens.add_(self.step_inc)
         x = self.embed[self.tokens]
-        delta = None
-        for li in range(self.cfg.n_layers):
-            x, delta = self._layer(li, x, delta, cos, sin, slots, self.table, self.lens, self.max_len)
-        h, _ = ops.rmsnorm(delta, self.final_norm, self.cfg.rms_eps, residual=x)
+        if self.tp == 1:
+            h, _ = ops.rmsnorm(x, self.layers[0]["norm1"], self.cfg.rms_eps)
+            n = self.cfg.n_layers
+            for li in range(n):
+                nxt = self.layers[li + 1]["norm1"] if li + 1 < n else self.final_norm
+                h, x = self._layer_single(li, h, x, nxt, cos, sin, slots, self.table, self.lens, self.max_len)
+        else:
+            delta = None
+            for li in range(self.cfg.n_layers):
+                x, delta = self._layer(li, x, delta, cos, sin, slots, self.table, self.lens, self.max_len)
+            h, _ = ops.rmsnorm(delta, self.final_norm, self.cfg.rms_eps, residual=x)
         logits = ops.gemm(h, self.lm_head).float()   # [B, V/tp]
         self.last_logits = logits                    # this rank's vocab shard, kept for inspection
         if self.sampling is not None:

@@ -108,6 +108,45 @@ Tensor gemm(const Tensor& A_, const Tensor& W, const OptT& bias, int64_t epi, co
   return C.reshape(shape);
 }
 
+std::tuple<Tensor, Tensor> rmsnorm(const Tensor& x, const OptT& gamma, double eps, const OptT& residual);
+
+// Output projection of a decode step with the residual add and the RMS-norm that follow it:
+//   x_new = residual + a w^T,  h = rmsnorm(x_new) * gamma   ->  (h, x_new)
+// For skinny problems (split-K) the reduction pass does all three; otherwise the GEMM and the norm kernel run
+// one after the other.
+std::tuple<Tensor, Tensor> gemm_reduce_rmsnorm(const Tensor& A_, const Tensor& W, const Tensor& residual,
+                                               const OptT& gamma, double eps) {
+  check_bf16_cuda(A_, "a"); check_bf16_cuda(W, "w"); check_bf16_cuda(residual, "residual");
+  c10::cuda::CUDAGuard guard(A_.device());
+  Tensor A = as_2d(A_);
+  const int64_t M = A.size(0), K = A.size(1), N = W.size(0);
+  TORCH_CHECK(W.dim() == 2 && W.size(1) == K && A.stride(1) == 1 && W.stride(1) == 1, "a [.., K] and w [N, K] expected");
+  TORCH_CHECK(A.stride(0) % 8 == 0 && W.stride(0) % 8 == 0 && N % 8 == 0, "rows must be 16-byte aligned");
+  Tensor R = as_2d(residual);
+  TORCH_CHECK(R.size(0) == M && R.size(1) == N && R.stride(1) == 1 && R.stride(0) % 8 == 0, "bad residual shape");
+  if (gamma.has_value() && gamma->defined()) { check_bf16_cuda(*gamma, "gamma"); TORCH_CHECK(gamma->numel() == N && gamma->is_contiguous()); }
+  const int ks = cosmos::gemm_pick_k_splits((int)M, (int)N, (int)K, EPI_PLAIN);
+  Tensor x_new = at::empty({M, N}, A.options());
+  if (ks > 1 && N <= 8192) {
+    Tensor h = at::empty({M, N}, A.options());
+    Tensor partial = at::empty({ks, M, N}, A.options().dtype(at::kFloat));
+    cosmos::GemmArgs g;
+    g.A = A.data_ptr(); g.B = W.data_ptr(); g.C = x_new.data_ptr();
+    g.M = (int)M; g.N = (int)N; g.K = (int)K;
+    g.lda = A.stride(0); g.ldb = W.stride(0); g.ldc = N;
+    g.epi = EPI_PLAIN;
+    g.R = R.data_ptr(); g.ldr = R.stride(0);
+    g.k_splits = ks; g.partial = partial.data_ptr<float>();
+    g.norm_gamma = opt_ptr(gamma); g.norm_out = h.data_ptr(); g.norm_eps = (float)eps;
+    g.status = status_tensor(A.get_device()).data_ptr<int>();
+    cosmos::gemm_bf16(g, cur_stream());
+    return {h.reshape(residual.sizes()), x_new.reshape(residual.sizes())};
+  }
+  Tensor y = gemm(A, W, {}, EPI_PLAIN, {}, {}, 0, {});
+  auto hr = rmsnorm(y, gamma, eps, R.contiguous());
+  return {std::get<0>(hr).reshape(residual.sizes()), std::get<1>(hr).reshape(residual.sizes())};
+}
+
 // General-major GEMM C[M, N] = op(A) op(B)^T for the backward passes:
 //   a_mn = false: A is [M, K];  a_mn = true: A is stored as [K, M] (read transposed in place)
 //   b_mn = false: B is [N, K];  b_mn = true: B is stored as [K, N]
@@ -832,6 +871,7 @@ TORCH_LIBRARY(cosmos_b200, m) {
   m.def("gemm_qkv_rope", &gemm_qkv_rope);
   m.def("gemm_grouped2", &gemm_grouped2);
   m.def("gemm_ex", &gemm_ex);
+  m.def("gemm_reduce_rmsnorm", &gemm_reduce_rmsnorm);
   m.def("attn_bwd_scores", &attn_bwd_scores);
   m.def("attn_fwd", &attn_fwd);
   m.def("attn_bwd", &attn_bwd);

@@ -575,6 +575,63 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
   }
 }
 
+// Second pass of split-K fused with the residual add and the RMS-norm that follow an output projection in a
+// decode step: x = R + sum_ks partial[ks]; X[m] = x; H[m] = x * rsqrt(mean(x^2) + eps) * gamma. One CTA per row.
+__global__ void __launch_bounds__(256)
+splitk_reduce_rmsnorm_kernel(const float* __restrict__ partial, int k_splits, int M, int N, const bf16* __restrict__ R,
+                             long long ldr, const bf16* __restrict__ gamma, float eps, bf16* __restrict__ X,
+                             bf16* __restrict__ H, long long ldc) {
+  __shared__ float red[8];
+  const int m = blockIdx.x, tid = threadIdx.x;
+  const int nvec = N >> 2;
+  constexpr int MAXJ = 8;  // N <= 8192
+  float4 v[MAXJ];
+  float ss = 0.f;
+#pragma unroll
+  for (int j = 0; j < MAXJ; ++j) {
+    const int vi = tid + j * 256;
+    if (vi < nvec) {
+      float4 a = make_float4(0, 0, 0, 0);
+      for (int ks = 0; ks < k_splits; ++ks) {
+        const float4 x = *reinterpret_cast<const float4*>(partial + ((long long)ks * M + m) * N + vi * 4);
+        a.x += x.x; a.y += x.y; a.z += x.z; a.w += x.w;
+      }
+      if (R) {
+        const uint2 r = *reinterpret_cast<const uint2*>(R + (long long)m * ldr + vi * 4);
+        a.x += bf16lo(r.x); a.y += bf16hi(r.x); a.z += bf16lo(r.y); a.w += bf16hi(r.y);
+      }
+      v[j] = a;
+      ss += a.x * a.x + a.y * a.y + a.z * a.z + a.w * a.w;
+    }
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+  if ((tid & 31) == 0) red[tid >> 5] = ss;
+  __syncthreads();
+  float tot = 0.f;
+#pragma unroll
+  for (int w = 0; w < 8; ++w) tot += red[w];
+  const float rinv = rsqrtf(tot / N + eps);
+#pragma unroll
+  for (int j = 0; j < MAXJ; ++j) {
+    const int vi = tid + j * 256;
+    if (vi < nvec) {
+      const float4 a = v[j];
+      uint2 xo, ho;
+      xo.x = pack_bf16(a.x, a.y); xo.y = pack_bf16(a.z, a.w);
+      float g0 = 1.f, g1 = 1.f, g2 = 1.f, g3 = 1.f;
+      if (gamma) {
+        const uint2 g = *reinterpret_cast<const uint2*>(gamma + vi * 4);
+        g0 = bf16lo(g.x); g1 = bf16hi(g.x); g2 = bf16lo(g.y); g3 = bf16hi(g.y);
+      }
+      ho.x = pack_bf16(a.x * rinv * g0, a.y * rinv * g1);
+      ho.y = pack_bf16(a.z * rinv * g2, a.w * rinv * g3);
+      *reinterpret_cast<uint2*>(X + (long long)m * ldc + vi * 4) = xo;
+      *reinterpret_cast<uint2*>(H + (long long)m * ldc + vi * 4) = ho;
+    }
+  }
+}
+
 // Second pass of split-K: out = epilogue(sum_ks partial[ks]). One thread per 4 output columns.
 __global__ void __launch_bounds__(256)
 splitk_reduce_kernel(const float* __restrict__ partial, int k_splits, int M, int N, int epi, bf16* __restrict__ C,
@@ -867,6 +924,14 @@ void gemm_bf16(const GemmArgs& a, cudaStream_t stream) {
     case EPI_SWIGLU: launch<EPI_SWIGLU>(maps, g, grid, stream); break;
     case EPI_GATED_RESID: launch<EPI_GATED_RESID>(maps, g, grid, stream); break;
     default: throw std::runtime_error("gemm_bf16: unknown epilogue");
+  }
+  if (a.norm_out) {
+    if (a.epi != EPI_PLAIN || a.N > 8192 || a.N % 4 != 0 || a.ldc % 4 != 0 || (a.R && a.ldr % 4 != 0))
+      throw std::runtime_error("gemm_bf16: the fused reduce + RMS-norm pass needs a plain epilogue and N <= 8192");
+    cb::splitk_reduce_rmsnorm_kernel<<<a.M, 256, 0, stream>>>(
+        a.partial, ks, a.M, a.N, reinterpret_cast<const bf16*>(a.R), a.ldr, reinterpret_cast<const bf16*>(a.norm_gamma),
+        a.norm_eps, reinterpret_cast<bf16*>(a.C), reinterpret_cast<bf16*>(a.norm_out), a.ldc);
+    return;
   }
   const int n_out = a.epi == EPI_SWIGLU ? a.N / 2 : a.N;
   const long long vecs = (long long)a.M * (n_out / 4);

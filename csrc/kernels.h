@@ -57,6 +57,11 @@ struct GemmArgs {
   bool a_mn = false, b_mn = false;
   int k_splits = 1;       // > 1: split-K with fp32 partials in `partial` ([k_splits, M, N] floats)
   float* partial = nullptr;
+  // split-K only (EPI_PLAIN): the reduction pass also adds the residual R (ldr) and applies an RMS-norm, writing
+  // x_new = R + A B^T to `C` and rmsnorm(x_new) * norm_gamma to `norm_out` (both [M, N] bf16, row stride ldc)
+  const void* norm_gamma = nullptr;
+  void* norm_out = nullptr;
+  float norm_eps = 1e-6f;
   // EPI_CONV: A is the padded input volume flattened to [frames * hp * wp, C] (C % 64 == 0), B the
   // weights as [Cout, 27 * C] (tap-major: kt, kh, kw, then channel), K = 27 * C. Output rows are
   // the same padded positions; only interior rows (frame >= conv_tpad, 1 <= h <= hp-2,

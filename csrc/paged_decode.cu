@@ -20,7 +20,6 @@ namespace cb {
 
 constexpr int PD_THREADS = 128;
 constexpr int PD_TILE = 128;   // tokens per tile
-constexpr int PD_MAX_GROUP = 8;
 
 // 16-byte read-only load; NO_L1 skips L1 allocation for fully coalesced rows that are used once
 template <bool NO_L1>

@@ -554,3 +554,21 @@ def test_training_step_own_kernels_match_library_baseline(monkeypatch):
     assert abs(log_o["grad_norm"] - log_l["grad_norm"]) < 5e-2 * max(1.0, log_l["grad_norm"])
     worst = max((st_o[k].float() - st_l[k].float()).abs().max().item() for k in st_l)
     assert worst < 2e-2, f"parameters differ by {worst}"
+
+
+@pytest.mark.parametrize("m,n,k", [(32, 4096, 4096), (1, 4096, 12288), (7, 1024, 2048), (300, 512, 256)])
+def test_gemm_reduce_rmsnorm(m, n, k):
+    """Output projection + residual + RMS-norm (the split-K reduction pass does all three for skinny problems;
+    the last shape takes the unfused fallback) against the fp32 definition."""
+    torch.manual_seed(41)
+    a = _rand(m, k)
+    w = _rand(n, k, scale=1 / math.sqrt(k))
+    resid = _rand(m, n)
+    gamma = (1 + 0.1 * torch.randn(n, device=DEV)).bfloat16()
+    h, x_new = ops.gemm_reduce_rmsnorm(a, w, resid, gamma, 1e-6)
+    torch.cuda.synchronize()
+    ops.check_status()
+    xf = resid.float() + a.float() @ w.float().t()
+    hf = xf * torch.rsqrt(xf.pow(2).mean(-1, keepdim=True) + 1e-6) * gamma.float()
+    _close(x_new, xf, 3e-2, 2e-2, "x_new")
+    _close(h, hf, 3e-2, 2e-2, "h")
