@@ -39,24 +39,29 @@ def init_distributed(world: Optional[int] = None, rank: Optional[int] = None, lo
     return Mesh(pc, world, rank)
 
 
-def finish(hard: bool = True) -> None:
-    """End of a launcher-run entry point: the ranks meet once more, flush their output and leave.
-    With `hard` the process exits without interpreter / communicator teardown: a communicator whose
-    collectives were captured in a CUDA graph, or whose buffers peers still map, can block in
-    destroy_process_group, and a rank that blocks there keeps the launcher (and the GPUs) busy
-    long after the work is done."""
+def finish(hard: bool = True, grace_s: float = 10.0) -> None:
+    """End of a launcher-run entry point: the ranks meet once more, tear the communicators down, flush and leave.
+    With `hard` the teardown runs in a helper thread and the process exits (`os._exit`) once it is done or after
+    `grace_s` seconds: a communicator whose collectives were captured in a CUDA graph can block in
+    `destroy_process_group`, and a rank that blocks there keeps the launcher and the GPUs busy long after the work is
+    done. The regular teardown is still attempted first, so that no rank frees buffers a peer is reading."""
     import sys
+    import threading
 
-    if dist.is_available() and dist.is_initialized():
+    active = dist.is_available() and dist.is_initialized()
+    if active:
         if torch.cuda.is_available():
             torch.cuda.synchronize()
         dist.barrier()
         if not hard:
             dist.destroy_process_group()
             return
+        t = threading.Thread(target=dist.destroy_process_group, daemon=True)
+        t.start()
+        t.join(grace_s)
     sys.stdout.flush()
     sys.stderr.flush()
-    if hard and dist.is_available() and dist.is_initialized():
+    if hard and active:
         os._exit(0)
 
 
