@@ -572,3 +572,4 @@ def test_gemm_reduce_rmsnorm(m, n, k):
     hf = xf * torch.rsqrt(xf.pow(2).mean(-1, keepdim=True) + 1e-6) * gamma.float()
     _close(x_new, xf, 3e-2, 2e-2, "x_new")
     _close(h, hf, 3e-2, 2e-2, "h")
+
