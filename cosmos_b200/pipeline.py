@@ -150,9 +150,14 @@ class Cosmos3OmniPipeline:
         return next(self.transformer.parameters()).device
 
     # ------------------------------------------------------------------ text
-    def encode_text(self, text: str) -> torch.Tensor:
-        n = self.cfg.max_text_len
+    def encode_text(self, text: str, max_sequence_length: Optional[int] = None) -> torch.Tensor:
+        """Token ids padded / truncated to `max_sequence_length` (at most the configured 512; longer prompts
+        are cut with a warning, reference README.md:389)."""
+        n = self.cfg.max_text_len if not max_sequence_length else max(1, min(int(max_sequence_length), self.cfg.max_text_len))
         ids = self.tokenizer.encode(text)
+        if len(ids) > n:
+            import warnings
+            warnings.warn(f"prompt has {len(ids)} tokens; truncated to max_sequence_length={n}", stacklevel=2)
         if hasattr(self.tokenizer, "pad_or_truncate"):
             ids = self.tokenizer.pad_or_truncate(ids, n)
         else:
@@ -168,7 +173,13 @@ class Cosmos3OmniPipeline:
                 add_resolution_template: bool = True, add_duration_template: bool = True,
                 condition_frame_indexes: Optional[Sequence[int]] = None, action=None, domain: int = 0,
                 action_dim: Optional[int] = None, denoise_action: bool = False, n_action: int = 0,
-                seed: int = 0, sampling: Optional[SamplingConfig] = None) -> Tuple[GenState, SamplingConfig]:
+                seed: int = 0, sampling: Optional[SamplingConfig] = None,
+                max_sequence_length: Optional[int] = None, sound_duration: Optional[float] = None,
+                condition_video_keep: Optional[str] = None) -> Tuple[GenState, SamplingConfig]:
+        """`sound_duration` (seconds) overrides the sound track length, which otherwise equals the clip's
+        `num_frames / fps` (reference cookbooks/cosmos3/generator/audiovisual/run_with_vllm_omni.ipynb:429).
+        `condition_video_keep` says which end of an input video supplies the conditioning frames:
+        "first" (default) or "last" (continue a clip from its final frames)."""
         cfg = self.cfg
         if self.safety_checker is not None:
             self.safety_checker.check_prompt(prompt)
@@ -181,12 +192,12 @@ class Cosmos3OmniPipeline:
                                         shift=self.scheduler.config.flow_shift,
                                         sigma_max=self.scheduler.config.sigma_max,
                                         scheduler=self.scheduler.config.solver, seed=seed)
-        ids_c = self.encode_text(text)
-        ids_u = self.encode_text(negative_prompt or "") if sc.guidance != 1.0 else None
+        ids_c = self.encode_text(text, max_sequence_length)
+        ids_u = self.encode_text(negative_prompt or "", max_sequence_length) if sc.guidance != 1.0 else None
         grid = latent_shape(cfg, num_frames, width, height)
         n_sound = 0
         if enable_sound:
-            n_sound = self.sound_tokenizer.latent_frames(num_frames / float(fps))
+            n_sound = self.sound_tokenizer.latent_frames(float(sound_duration) if sound_duration else num_frames / float(fps))
         n_act = n_action or (0 if action is None else len(action))
         st = self.engine.make_state(ids_c, ids_u, grid, n_sound, n_act, domain=domain, action_dim=action_dim, fps=fps)
         s_dm = st.pos.shape[1]
@@ -205,7 +216,9 @@ class Cosmos3OmniPipeline:
         if frames is not None:
             n_lat = max(condition_frame_indexes) + 1
             n_pix = 1 + (n_lat - 1) * cfg.vae_t_compress
-            fr = frames[:n_pix]
+            if condition_video_keep not in (None, "first", "last"):
+                raise ValueError(f"condition_video_keep must be 'first' or 'last', got {condition_video_keep!r}")
+            fr = frames[-n_pix:] if condition_video_keep == "last" else frames[:n_pix]
             if fr.shape[0] < n_pix:
                 fr = np.concatenate([fr, np.repeat(fr[-1:], n_pix - fr.shape[0], 0)])
             x = CausalVideoVAE.from_uint8(torch.from_numpy(np.array(fr))[None].to(self.device)).to(vdt)

@@ -135,6 +135,9 @@ class Cosmos3Server:
                     kw["condition_frame_indexes"] = list(range((num_frames - 1) // 4 + 1))
         if extra.get("condition_frame_indexes_vision"):
             kw["condition_frame_indexes"] = list(extra["condition_frame_indexes_vision"])
+        for key in ("condition_video_keep", "max_sequence_length", "sound_duration"):
+            if extra.get(key) not in (None, ""):
+                kw[key] = extra[key]
         checker = self.pipe.safety_checker
         if not extra.get("guardrails", self.guardrails_default):
             self.pipe.safety_checker = None
@@ -149,6 +152,7 @@ class Cosmos3Server:
                                  num_frames=num_frames, height=height, width=width, fps=fps,
                                  num_inference_steps=steps, guidance_scale=guidance, enable_sound=generate_sound,
                                  add_resolution_template=bool(extra.get("use_resolution_template", True)),
+                                 add_duration_template=bool(extra.get("use_duration_template", True)),
                                  sampling=sc, callback=cb, **kw)
         finally:
             self.pipe.safety_checker = checker
@@ -192,6 +196,9 @@ class Cosmos3Server:
                 else:
                     video = str(p)
             action_mode = bool(extra.get("action_mode"))
+            for key, cast in (("max_sequence_length", int), ("sound_duration", float)):  # top-level form fields
+                if form.get(key) not in (None, ""):
+                    extra = {**extra, key: cast(form[key])}
             out = self._generate(form.get("prompt", ""), form.get("negative_prompt") or None, w, h,
                                  int(form.get("num_frames", 189)), int(form.get("fps", 24)),
                                  int(form.get("num_inference_steps", 30 if action_mode else 35)),
@@ -287,7 +294,9 @@ class Cosmos3Server:
         t0 = time.time()
         tok = self.pipe.tokenizer
         messages = body["messages"]
-        extra = body.get("extra_body") or {}
+        # The OpenAI client merges `extra_body` into the top level of the request; raw HTTP callers may nest it.
+        extra = {k: body[k] for k in ("mm_processor_kwargs", "media_io_kwargs") if k in body}
+        extra.update(body.get("extra_body") or {})
         vision_embeds, grids, n_vis, norm_msgs, deep = [], [], [], [], []
         dev = self.pipe.device
         for m in messages:
@@ -298,7 +307,7 @@ class Cosmos3Server:
                     kind = part.get("type")
                     if kind in ("image_url", "video_url"):
                         frames = self._load_media(part[kind]["url"], kind == "video_url", extra)
-                        emb, grid, ds = self._encode_vision(frames, dev)
+                        emb, grid, ds = self._encode_vision(frames, dev, (extra.get("mm_processor_kwargs") or {}).get("size"))
                         vision_embeds.append(emb)
                         deep.append(ds)
                         grids.append(grid)
@@ -380,21 +389,24 @@ class Cosmos3Server:
         if is_video:
             vk = (extra.get("media_io_kwargs") or {}).get("video", {})
             mk = extra.get("mm_processor_kwargs") or {}
-            if "num_frames" in vk:
+            if int(vk.get("num_frames", 0)) > 0:
                 idx = np.linspace(0, len(frames) - 1, int(vk["num_frames"])).round().astype(int)
                 frames = frames[idx]
+            elif vk.get("num_frames") == -1 or mk.get("do_sample_frames") is False:
+                pass  # the client pre-sampled the clip: keep every frame
             else:
                 fps = float(vk.get("fps", mk.get("fps", 2)))
                 step = max(1, int(round(src_fps / max(fps, 1e-6))))
                 frames = frames[::step]
         return frames[:32]
 
-    def _encode_vision(self, frames: np.ndarray, dev):
+    def _encode_vision(self, frames: np.ndarray, dev, size: Optional[dict] = None):
         from PIL import Image
         from ..models.vae import CausalVideoVAE
         unit = self.pipe.cfg.vit_patch * self.pipe.cfg.vit_spatial_merge
-        h = min(max(unit, frames.shape[1] // unit * unit), 14 * unit)
-        w = min(max(unit, frames.shape[2] // unit * unit), 14 * unit)
+        size = size or {}
+        h, w = smart_resize(frames.shape[1], frames.shape[2], unit, int(size.get("shortest_edge", 3136)),
+                            int(size.get("longest_edge", 12845056)), max_side=14 * unit)
         fr = np.stack([np.asarray(Image.fromarray(f).resize((w, h))) for f in frames])
         vid = CausalVideoVAE.from_uint8(torch.from_numpy(fr)[None])[0].permute(1, 0, 2, 3).to(dev)
         with torch.no_grad():
@@ -402,6 +414,23 @@ class Cosmos3Server:
 
     def models(self) -> dict:
         return {"object": "list", "data": [{"id": self.model_name, "object": "model", "owned_by": "cosmos_b200"}]}
+
+
+def smart_resize(h: int, w: int, unit: int, min_pixels: int, max_pixels: int, max_side: Optional[int] = None):
+    """Target (height, width) for the vision encoder: multiples of `unit` (patch x spatial merge), aspect
+    ratio kept, pixel count within [min_pixels, max_pixels] (the `size.shortest_edge` / `size.longest_edge`
+    bounds of `mm_processor_kwargs`, reference README.md:574), each side at most `max_side`."""
+    import math
+    hb, wb = max(unit, round(h / unit) * unit), max(unit, round(w / unit) * unit)
+    if hb * wb > max_pixels:
+        beta = math.sqrt(h * w / max_pixels)
+        hb, wb = max(unit, math.floor(h / beta / unit) * unit), max(unit, math.floor(w / beta / unit) * unit)
+    elif hb * wb < min_pixels:
+        beta = math.sqrt(min_pixels / (h * w))
+        hb, wb = math.ceil(h * beta / unit) * unit, math.ceil(w * beta / unit) * unit
+    if max_side:
+        hb, wb = min(hb, max_side), min(wb, max_side)
+    return hb, wb
 
 
 def create_app(server: Cosmos3Server):

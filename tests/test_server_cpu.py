@@ -184,3 +184,48 @@ def test_chat_streaming_sends_chunks_then_done(client):
     text = "".join(c["choices"][0]["delta"].get("content", "") for c in chunks)
     assert text == whole["choices"][0]["message"]["content"]
     assert chunks[-1]["choices"][0]["finish_reason"] in ("stop", "length")
+
+
+def test_video_request_fields_sound_duration_sequence_length_and_keep(client, tmp_path):
+    """`max_sequence_length`, `sound_duration`, `generate_sound` as form fields and `condition_video_keep`,
+    `use_duration_template` inside `extra_params` (reference README.md:389-391)."""
+    from cosmos_b200.io import media
+    src = tmp_path / "src.mp4"
+    media.write_video(src, (np.random.rand(9, 64, 64, 3) * 255).astype(np.uint8), 8, 8, None, 48000)
+    extra = {"condition_frame_indexes_vision": [0, 1], "condition_video_keep": "last", "use_duration_template": False}
+    with pytest.warns(UserWarning, match="truncated to max_sequence_length=8"):
+        r = client.post("/v1/videos/sync",
+                        data={"prompt": "a robot arm stacks red blocks on a table " * 4, "size": "64x64", "num_frames": "9",
+                              "fps": "8", "num_inference_steps": "2", "guidance_scale": "1.0", "seed": "0",
+                              "max_sequence_length": "8", "generate_sound": "true", "sound_duration": "0.5",
+                              "extra_params": json.dumps(extra)},
+                        files={"input_reference": ("src.mp4", src.read_bytes(), "video/mp4")})
+    assert r.status_code == 200, r.text
+    assert r.content[4:8] == b"ftyp"
+    bad = client.post("/v1/videos/sync", data={"prompt": "x", "size": "64x64", "num_frames": "5", "num_inference_steps": "1",
+                                               "extra_params": json.dumps({"condition_video_keep": "middle"})},
+                      files={"input_reference": ("src.mp4", src.read_bytes(), "video/mp4")})
+    assert bad.status_code >= 400
+
+
+def test_chat_video_with_processor_kwargs(client, tmp_path):
+    """`mm_processor_kwargs` {fps, do_sample_frames, size} and `media_io_kwargs` of a chat request."""
+    from cosmos_b200.io import media
+    from cosmos_b200.serve.server import smart_resize
+    src = tmp_path / "clip.mp4"
+    media.write_video(src, (np.random.rand(8, 96, 128, 3) * 255).astype(np.uint8), 8, 8, None, 48000)
+    url = "data:video/mp4;base64," + base64.b64encode(src.read_bytes()).decode()
+    usage = {}
+    for mk in ({"fps": 4, "do_sample_frames": True}, {"do_sample_frames": False},
+               {"fps": 4, "do_sample_frames": True, "size": {"shortest_edge": 1024, "longest_edge": 4096}}):
+        body = {"max_tokens": 2, "temperature": 0.0, "mm_processor_kwargs": mk,
+                "messages": [{"role": "user", "content": [{"type": "video_url", "video_url": {"url": url}},
+                                                           {"type": "text", "text": "Describe the clip."}]}]}
+        r = client.post("/v1/chat/completions", json=body)
+        assert r.status_code == 200, r.text
+        usage[json.dumps(mk)] = r.json()["usage"]["prompt_tokens"]
+    n_sampled, n_all, n_small = usage.values()
+    assert n_all > n_sampled > n_small  # every frame > 4 fps sampling > 4 fps with a tighter pixel bound
+    assert smart_resize(96, 128, 32, 1024, 4096) == (32, 64)
+    assert smart_resize(720, 1280, 32, 3136, 262144) == (384, 672)
+    assert smart_resize(20, 20, 32, 3136, 10 ** 7) == (64, 64)
