@@ -573,3 +573,41 @@ def test_gemm_reduce_rmsnorm(m, n, k):
     _close(x_new, xf, 3e-2, 2e-2, "x_new")
     _close(h, hf, 3e-2, 2e-2, "h")
 
+
+
+def test_kernels_do_not_write_outside_their_outputs():
+    """Canary check: outputs are views into larger buffers whose guard regions hold a bit pattern; after ragged
+    GEMM, QKV-epilogue and attention launches the guards must be untouched."""
+    torch.manual_seed(43)
+    guard = 4096  # elements before and after
+
+    def guarded(rows, cols):
+        buf = torch.full((2 * guard + rows * cols,), -7.0, device=DEV, dtype=torch.bfloat16)
+        return buf, buf[guard:guard + rows * cols].view(rows, cols)
+
+    def intact(buf, what):
+        assert bool((buf[:guard] == -7.0).all()) and bool((buf[-guard:] == -7.0).all()), f"{what}: guard region overwritten"
+
+    for m, n, k in [(300, 264, 1000), (1, 512, 256), (129, 136, 72)]:
+        a, w = _rand(m, k), _rand(n, k, scale=1 / math.sqrt(k))
+        buf, out = guarded(m, n)
+        ops.gemm(a, w, out=out)
+        torch.cuda.synchronize()
+        intact(buf, f"gemm {m}x{n}x{k}")
+        _close(out, a.float() @ w.float().t(), 3e-2, 3e-2, "gemm into a guarded view")
+    # SwiGLU epilogue writes N / 2 columns
+    a, w = _rand(77, 512), _rand(1024, 512, scale=1 / math.sqrt(512))
+    buf, out = guarded(77, 512)
+    ops.gemm(a, w, epi=ops.EPI_SWIGLU, out=out)
+    torch.cuda.synchronize()
+    intact(buf, "gemm swiglu")
+    # attention with ragged lengths writes exactly [B, Sq, Hq, 128]
+    b, sq, skv, hq, hkv = 2, 300, 517, 4, 2
+    q, kk, v = _rand(b, sq, hq, 128), _rand(b, skv, hkv, 128), _rand(b, skv, hkv, 128)
+    buf, out = guarded(b * sq, hq * 128)
+    o, _ = ops.attention(q, kk, v, out=out.view(b, sq, hq, 128))
+    torch.cuda.synchronize()
+    intact(buf, "attention")
+    want, _ = ref.attention(q.float(), kk.float(), v.float())
+    _close(o, want, 2e-2, 2e-2, "attention into a guarded view")
+    ops.check_status()
