@@ -19,7 +19,10 @@ from . import reference as ref
 from .reference import (EPI_GATED_RESID, EPI_PLAIN, EPI_QKV_ROPE, EPI_SWIGLU, MASK_CAUSAL, MASK_FULL,
                         MASK_MOT)
 
-_SO = Path(__file__).resolve().parents[1] / "_C.so"
+# COSMOS_BOUNDS_CHECK=1 selects the debug build of the library (device-side checks of every index that a
+# kernel reads from a tensor; a bad one is reported through the status word and its access skipped).
+_BOUNDS_CHECK = os.environ.get("COSMOS_BOUNDS_CHECK") == "1"
+_SO = Path(__file__).resolve().parents[1] / ("_C_check.so" if _BOUNDS_CHECK else "_C.so")
 _loaded = False
 _load_error: Optional[str] = None
 
@@ -32,7 +35,7 @@ def load_extension(build_if_missing: bool = True) -> bool:
     try:
         if not _SO.exists() and build_if_missing and os.environ.get("COSMOS_B200_NO_BUILD") != "1":
             from ._build import build
-            build()
+            build(bounds_check=_BOUNDS_CHECK)
         torch.ops.load_library(str(_SO))
         _loaded = True
     except Exception as e:  # noqa: BLE001 - reported to the caller on first GPU use
@@ -111,7 +114,10 @@ STATUS_MESSAGES = {
     4: "timeout: softmax waiting for scores",
     5: "timeout: waiting for a peer signal",
     6: "bad argument",
+    7: "index out of range (bounds-checked build)",
 }
+STATUS_SITES = {1: "kv_cache_write slot", 2: "decode_qkv_post slot", 3: "paged_decode page id",
+                4: "paged_decode (tensor-core) page id", 15: "self-test"}
 
 
 def check_status(reset: bool = True) -> None:
@@ -123,7 +129,15 @@ def check_status(reset: bool = True) -> None:
     if code != 0:
         if reset:
             w.zero_()
-        raise RuntimeError(f"cosmos_b200 kernel reported status {code}: {STATUS_MESSAGES.get(code, '?')}")
+        what = STATUS_MESSAGES.get(code & 0xFF, "?")
+        if code >> 8:
+            what += f" at {STATUS_SITES.get(code >> 8, f'site {code >> 8}')}"
+        raise RuntimeError(f"cosmos_b200 kernel reported status {code}: {what}")
+
+
+def bounds_check_enabled() -> bool:
+    """True when the loaded library is the bounds-checked debug build."""
+    return bool(load_extension(build_if_missing=False) and _k().bounds_check_enabled())
 
 
 # --------------------------------------------------------------------------- ops

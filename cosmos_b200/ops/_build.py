@@ -2,7 +2,8 @@
 
 ``.cu`` files contain no torch headers and are compiled one by one with
 ``nvcc -gencode arch=compute_100a,code=sm_100a``; the torch glue (``bindings.cpp``,
-``runtime.cpp``) is compiled with the host compiler and everything is linked into one
+``runtime.cpp``, ``safetensors_reader.cpp``, over the torch-free host runtime in ``csrc/host``) is
+compiled with the host compiler and everything is linked into one
 shared object that ``torch.ops.load_library`` loads. Objects are cached under ``build/``
 keyed by a hash of the source, its headers and the flags, so rebuilds are incremental.
 """
@@ -20,6 +21,7 @@ ROOT = Path(__file__).resolve().parents[2]
 CSRC = ROOT / "csrc"
 BUILD = ROOT / "build"
 SO_PATH = ROOT / "cosmos_b200" / "_C.so"
+SO_PATH_CHECKED = ROOT / "cosmos_b200" / "_C_check.so"  # the same library with -DCOSMOS_BOUNDS_CHECK
 
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
@@ -56,10 +58,15 @@ def _run(cmd):
     return r.stdout
 
 
-def build(verbose: bool = False, force: bool = False) -> Path:
-    """Compile (if stale) and return the path of the shared object."""
+def build(verbose: bool = False, force: bool = False, bounds_check: bool = False) -> Path:
+    """Compile (if stale) and return the path of the shared object. With `bounds_check` the debug
+    variant is built: indices that kernels read from tensors (cache slots, page ids) are compared with
+    their limits on the device and a bad one is reported through the status word and skipped."""
     BUILD.mkdir(exist_ok=True)
-    headers = sorted(CSRC.glob("*.h")) + sorted(CSRC.glob("*.cuh"))
+    so_path = SO_PATH_CHECKED if bounds_check else SO_PATH
+    extra = ["-DCOSMOS_BOUNDS_CHECK"] if bounds_check else []
+    suffix = ".chk" if bounds_check else ""
+    headers = sorted(CSRC.glob("*.h")) + sorted(CSRC.glob("*.cuh")) + sorted((CSRC / "host").glob("*.hpp"))
     cu_files = sorted(CSRC.glob("*.cu"))
     cpp_files = sorted(CSRC.glob("*.cpp"))
     inc, torch_lib, abi = _torch_paths()
@@ -71,17 +78,17 @@ def build(verbose: bool = False, force: bool = False) -> Path:
     jobs = []
     objs = []
     for src in cu_files:
-        tag = _digest([src] + headers, " ".join(NVCC_FLAGS))
-        obj = BUILD / f"{src.stem}.{tag}.o"
+        tag = _digest([src] + headers, " ".join(NVCC_FLAGS + extra))
+        obj = BUILD / f"{src.stem}.{tag}{suffix}.o"
         objs.append(obj)
         if force or not obj.exists():
-            jobs.append([nvcc, *NVCC_FLAGS, "-I", str(CSRC), "-c", str(src), "-o", str(obj)])
+            jobs.append([nvcc, *NVCC_FLAGS, *extra, "-I", str(CSRC), "-c", str(src), "-o", str(obj)])
     for src in cpp_files:
-        tag = _digest([src] + headers, " ".join(cxx_flags) + sys.version)
-        obj = BUILD / f"{src.stem}.{tag}.o"
+        tag = _digest([src] + headers, " ".join(cxx_flags + extra) + sys.version)
+        obj = BUILD / f"{src.stem}.{tag}{suffix}.o"
         objs.append(obj)
         if force or not obj.exists():
-            cmd = ["g++", *cxx_flags, "-I", str(CSRC), "-I", cuda_inc, "-I", py_inc]
+            cmd = ["g++", *cxx_flags, *extra, "-I", str(CSRC), "-I", cuda_inc, "-I", py_inc]
             for i in inc:
                 cmd += ["-isystem", i]
             cmd += ["-DTORCH_API_INCLUDE_EXTENSION_H", "-c", str(src), "-o", str(obj)]
@@ -95,21 +102,21 @@ def build(verbose: bool = False, force: bool = False) -> Path:
                 if verbose and out.strip():
                     print(out)
 
-    stamp = BUILD / "link.stamp"
+    stamp = BUILD / f"link{suffix}.stamp"
     want = " ".join(o.name for o in objs)
-    if force or jobs or not SO_PATH.exists() or not stamp.exists() or stamp.read_text() != want:
-        cmd = ["g++", "-shared", "-o", str(SO_PATH), *map(str, objs),
+    if force or jobs or not so_path.exists() or not stamp.exists() or stamp.read_text() != want:
+        cmd = ["g++", "-shared", "-o", str(so_path), *map(str, objs),
                f"-L{torch_lib}", f"-L{_cuda_home()}/lib64", f"-Wl,-rpath,{torch_lib}",
                "-lc10", "-lc10_cuda", "-ltorch_cpu", "-ltorch_cuda", "-ltorch", "-lcudart"]
         _run(cmd)
         stamp.write_text(want)
         # drop stale objects of earlier source versions
         keep = {o.name for o in objs}
-        for old in BUILD.glob("*.o"):
-            if old.name not in keep:
+        for old in BUILD.glob("*.chk.o" if bounds_check else "*.o"):
+            if old.name not in keep and old.name.endswith(".chk.o") == bounds_check:
                 old.unlink()
-    return SO_PATH
+    return so_path
 
 
 if __name__ == "__main__":
-    print(build(verbose=True, force="--force" in sys.argv))
+    print(build(verbose=True, force="--force" in sys.argv, bounds_check="--bounds-check" in sys.argv))

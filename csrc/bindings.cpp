@@ -805,7 +805,8 @@ void kv_cache_write(const Tensor& k, const Tensor& v, const Tensor& slots, Tenso
               k_cache.size(3) == 128 && v_cache.sizes() == k_cache.sizes());
   TORCH_CHECK(slots.is_cuda() && slots.scalar_type() == at::kLong && slots.is_contiguous() && slots.numel() == k.size(0));
   cosmos::kv_cache_write(k.data_ptr(), v.data_ptr(), reinterpret_cast<const long long*>(slots.data_ptr<int64_t>()),
-                         k_cache.data_ptr(), v_cache.data_ptr(), k.size(0), (int)k.size(1), (int)k_cache.size(2), cur_stream());
+                         k_cache.data_ptr(), v_cache.data_ptr(), k.size(0), (int)k.size(1), (int)k_cache.size(2),
+                         k_cache.size(0) * k_cache.size(2), status_tensor(k.get_device()).data_ptr<int>(), cur_stream());
 }
 
 Tensor decode_qkv_post(const Tensor& qkv, int64_t n_q_heads, const Tensor& cos_t, const Tensor& sin_t,
@@ -829,8 +830,25 @@ Tensor decode_qkv_post(const Tensor& qkv, int64_t n_q_heads, const Tensor& cos_t
   cosmos::decode_qkv_post(qkv.data_ptr(), (int)B, (int)Hq, (int)Hkv, cos_t.data_ptr<float>(), sin_t.data_ptr<float>(),
                           gamma_q.data_ptr(), gamma_k.data_ptr(), (float)eps,
                           reinterpret_cast<const long long*>(slots.data_ptr<int64_t>()), q.data_ptr(),
-                          k_cache.data_ptr(), v_cache.data_ptr(), (int)k_cache.size(2), cur_stream());
+                          k_cache.data_ptr(), v_cache.data_ptr(), (int)k_cache.size(2), k_cache.size(0) * k_cache.size(2),
+                          status_tensor(qkv.get_device()).data_ptr<int>(), cur_stream());
   return q;
+}
+
+bool bounds_check_enabled() { return cosmos::bounds_check_enabled(); }
+void gemm_set_grid_limit(int64_t max_ctas) { cosmos::gemm_set_grid_limit((int)max_ctas); }
+
+// ok[i] = 1 if 0 <= idx[i] < limit[i] (always 1 in a build without the checks); a failed check also
+// records its status code, exactly as inside the kernels. No memory is addressed through idx.
+Tensor bounds_check_selftest(const Tensor& idx, const Tensor& limit) {
+  TORCH_CHECK(idx.is_cuda() && idx.scalar_type() == at::kLong && idx.is_contiguous() && limit.is_cuda() &&
+              limit.scalar_type() == at::kLong && limit.is_contiguous() && limit.numel() == idx.numel());
+  c10::cuda::CUDAGuard guard(idx.device());
+  Tensor ok = at::empty({idx.numel()}, idx.options().dtype(at::kInt));
+  cosmos::bounds_check_selftest(reinterpret_cast<const long long*>(idx.data_ptr<int64_t>()),
+                                reinterpret_cast<const long long*>(limit.data_ptr<int64_t>()), ok.data_ptr<int>(),
+                                (int)idx.numel(), status_tensor(idx.get_device()).data_ptr<int>(), cur_stream());
+  return ok;
 }
 
 // mode 0: reduce + update; mode 1: reduce into `reduced` and add sum(g^2) to sq; mode 2: update from `reduced`
@@ -897,6 +915,9 @@ TORCH_LIBRARY(cosmos_b200, m) {
   m.def("allreduce_oneshot", &allreduce_oneshot);
   m.def("kv_cache_write", &kv_cache_write);
   m.def("decode_qkv_post", &decode_qkv_post);
+  m.def("bounds_check_enabled", &bounds_check_enabled);
+  m.def("gemm_set_grid_limit", &gemm_set_grid_limit);
+  m.def("bounds_check_selftest", &bounds_check_selftest);
   m.def("rs_adamw", &rs_adamw);
   m.def("allgather_pull", &allgather_pull);
   cosmos::register_runtime_ops(m);

@@ -16,6 +16,16 @@ using bf16 = __nv_bfloat16;
 #define COSMOS_WAIT_LIMIT_CYCLES (3000000000ll)  // ~1.5-2 s at B200 clocks
 #endif
 
+#ifdef COSMOS_BOUNDS_CHECK
+#define COSMOS_BC_PARAMS , long long bc_limit, int* bc_status
+#define COSMOS_BC_ARGS(limit, status) , (long long)(limit), (status)
+#define COSMOS_INDEX_OK(idx, site) cb::index_ok((long long)(idx), bc_limit, bc_status, site)
+#else
+#define COSMOS_BC_PARAMS
+#define COSMOS_BC_ARGS(limit, status)
+#define COSMOS_INDEX_OK(idx, site) true
+#endif
+
 namespace cb {
 
 // Status codes written to the device status word (0 = ok).
@@ -27,7 +37,27 @@ enum : int {
   ST_TIMEOUT_SOFTMAX = 4,
   ST_TIMEOUT_PEER = 5,
   ST_BAD_ARG = 6,
+  ST_BAD_INDEX = 7,  // bounds-checked builds only; the site tag sits in bits 8..15 of the status word
 };
+
+// Sites of data-dependent indices (values read from a tensor, not derived from the launch geometry).
+enum : int {
+  SITE_KV_WRITE_SLOT = 1,
+  SITE_DECODE_POST_SLOT = 2,
+  SITE_PAGED_DECODE_PAGE = 3,
+  SITE_PAGED_DECODE_TC_PAGE = 4,
+  SITE_SELFTEST = 15,
+};
+
+// Bounds-checked debug build (-DCOSMOS_BOUNDS_CHECK): every index that a kernel reads from memory is
+// compared with its limit before it is used as an address. A bad one records ST_BAD_INDEX and its site
+// in the status word (first error wins) and the access is skipped; nothing traps. The kernels that
+// take such indices get two extra parameters in that build only, so the regular build is unchanged.
+__device__ __forceinline__ bool index_ok(long long idx, long long limit, int* status, int site) {
+  if (limit <= 0 || (idx >= 0 && idx < limit)) return true;  // limit <= 0: the caller did not say
+  if (status) atomicCAS(status, 0, ST_BAD_INDEX | (site << 8));
+  return false;
+}
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) {
   return static_cast<uint32_t>(__cvta_generic_to_shared(p));

@@ -752,6 +752,10 @@ const char* status_str(int st) {
 
 namespace cosmos {
 
+// Debug knob (gemm_set_grid_limit): caps the number of persistent CTAs, which changes which CTA computes
+// which tile and how many tiles share one CTA's pipeline state. Results must not depend on it.
+static int g_grid_limit = 0;
+
 static int sm_count() {
   static int n = 0;
   if (!n) {
@@ -852,6 +856,8 @@ static void fill_problem(const GemmArgs& a, cb::GemmParams& p, CUtensorMap& ta, 
   }
 }
 
+void gemm_set_grid_limit(int max_ctas) { g_grid_limit = max_ctas > 0 ? max_ctas : 0; }
+
 int gemm_pick_k_splits(int M, int N, int K, int epi) {
   if (epi != EPI_PLAIN && epi != EPI_SWIGLU && epi != EPI_GATED_RESID) return 1;
   const int m_tiles = (M + cb::BM - 1) / cb::BM;
@@ -885,6 +891,7 @@ void gemm_bf16_grouped(const GemmArgs* args, int n, cudaStream_t stream) {
   }
   if (g.total == 0) return;
   int grid = args[0].max_ctas > 0 ? args[0].max_ctas : sm_count();
+  if (g_grid_limit > 0 && grid > g_grid_limit) grid = g_grid_limit;
   if (grid > g.total) grid = g.total;
   switch (args[0].epi) {
     case EPI_PLAIN: launch<EPI_PLAIN>(maps, g, grid, stream); break;

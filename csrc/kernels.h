@@ -70,6 +70,8 @@ struct GemmArgs {
 };
 // Split count that fills the machine for a skinny problem (1 = do not split).
 int gemm_pick_k_splits(int M, int N, int K, int epi);
+// Debug knob for race hunting: at most `max_ctas` persistent CTAs per GEMM launch (0 = one per SM).
+void gemm_set_grid_limit(int max_ctas);
 void gemm_bf16(const GemmArgs& a, cudaStream_t stream);
 // K12: one persistent launch over one or two problems with the same epilogue kind (per-modality
 // weight routing: tokens are already grouped into an AR segment and a DM segment).
@@ -182,14 +184,21 @@ void paged_decode_tc_launch(const PagedDecodeArgs& a, float* pa, float* pm, cuda
 size_t paged_decode_scratch_bytes(int B, int Hq, int n_splits);
 void paged_decode(const PagedDecodeArgs& a, cudaStream_t s);
 // Scatters new K/V rows [N, Hkv, 128] into the paged caches at flat slots (page * page_size + offset).
+// `n_slots` (token rows of the cache) and `status` serve the bounds-checked build, which reports a slot
+// outside the cache instead of writing there.
 void kv_cache_write(const void* k, const void* v, const long long* slots, void* k_cache, void* v_cache,
-                    long long n_rows, int Hkv, int page_size, cudaStream_t s);
+                    long long n_rows, int Hkv, int page_size, long long n_slots, int* status, cudaStream_t s);
 
 // Decode-step glue after the QKV GEMM: q/k RMS-norm + rotary, q to a contiguous buffer, k and v into
 // their paged-cache rows (slot = page * page_size + offset, one per sequence). cos/sin [B, 64] fp32.
 void decode_qkv_post(const void* qkv, int B, int Hq, int Hkv, const float* cos_t, const float* sin_t,
                      const void* gamma_q, const void* gamma_k, float eps, const long long* slots, void* q_out,
-                     void* k_cache, void* v_cache, int page_size, cudaStream_t s);
+                     void* k_cache, void* v_cache, int page_size, long long n_slots, int* status, cudaStream_t s);
+
+// True in a build with -DCOSMOS_BOUNDS_CHECK. The self-test runs the index check on (idx[i], limit[i])
+// pairs and writes 1 / 0 to ok[i]; it touches no memory through the tested indices.
+bool bounds_check_enabled();
+void bounds_check_selftest(const long long* idx, const long long* limit, int* ok, int n, int* status, cudaStream_t s);
 
 // ---- backward of the bandwidth kernels (elementwise_bwd.cu) ----
 // RMSNorm / AdaLN-RMSNorm: dx [rows, d]; with `part` != null also per-block column sums

@@ -41,7 +41,8 @@ paged_decode_kernel(const bf16* __restrict__ q, const bf16* __restrict__ kc, con
                     int page_size, int Hq, int Hkv, int n_splits, float scale_log2,
                     float* __restrict__ part_acc,   // [B, Hq, n_splits, 128]
                     float* __restrict__ part_ml,    // [B, Hq, n_splits, 2]
-                    bf16* __restrict__ out) {       // used directly when n_splits == 1
+                    bf16* __restrict__ out          // used directly when n_splits == 1
+                    COSMOS_BC_PARAMS) {
   const int split = blockIdx.x, kvh = blockIdx.y, b = blockIdx.z;
   const int tid = threadIdx.x;
   const int len = seq_lens[b];
@@ -81,7 +82,8 @@ paged_decode_kernel(const bf16* __restrict__ q, const bf16* __restrict__ kc, con
     for (int g = 0; g < GROUP; ++g) s[g] = 0.f;
     long long row = 0;
     if (valid) {
-      const int page = table[(long long)b * max_pages + pos / page_size];
+      int page = table[(long long)b * max_pages + pos / page_size];
+      if (!COSMOS_INDEX_OK(page, SITE_PAGED_DECODE_PAGE)) page = 0;  // reported; reads a valid page instead
       row = (((long long)page * Hkv + kvh) * page_size + pos % page_size) * 128;
     }
     row_s[tid] = row;
@@ -257,7 +259,7 @@ static void launch_pd(const PagedDecodeArgs& a, float* pa, float* pm, cudaStream
   cb::paged_decode_kernel<GROUP><<<grid, cb::PD_THREADS, 0, s>>>(
       (const bf16*)a.q, (const bf16*)a.k_cache, (const bf16*)a.v_cache, a.block_table, a.seq_lens,
       a.max_pages, a.page_size, a.Hq, a.Hkv, a.n_splits, a.scale * 1.4426950408889634f, pa, pm,
-      (bf16*)a.out);
+      (bf16*)a.out COSMOS_BC_ARGS(a.num_pages, a.status));
 }
 
 void paged_decode(const PagedDecodeArgs& a, cudaStream_t s) {
@@ -295,7 +297,8 @@ namespace cb {
 // head h of it lives at ((page * Hkv + h) * page_size + offset) * 128.
 __global__ void __launch_bounds__(256)
 kv_cache_write_kernel(const uint4* __restrict__ k, const uint4* __restrict__ v, const long long* __restrict__ slots,
-                      uint4* __restrict__ kc, uint4* __restrict__ vc, long long n_rows, int Hkv, int page_size) {
+                      uint4* __restrict__ kc, uint4* __restrict__ vc, long long n_rows, int Hkv, int page_size
+                      COSMOS_BC_PARAMS) {
   const int vec_per_row = Hkv * 16;
   const long long total = n_rows * vec_per_row;
   for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total;
@@ -304,6 +307,7 @@ kv_cache_write_kernel(const uint4* __restrict__ k, const uint4* __restrict__ v, 
     const int c = (int)(i - r * vec_per_row);
     const int h = c >> 4;
     const long long slot = slots[r];
+    if (!COSMOS_INDEX_OK(slot, SITE_KV_WRITE_SLOT)) continue;
     const long long page = slot / page_size;
     const int off = (int)(slot - page * page_size);
     const long long dst = (((page * Hkv + h) * page_size + off) << 4) + (c & 15);
@@ -315,12 +319,14 @@ kv_cache_write_kernel(const uint4* __restrict__ k, const uint4* __restrict__ v, 
 
 namespace cosmos {
 void kv_cache_write(const void* k, const void* v, const long long* slots, void* k_cache, void* v_cache,
-                    long long n_rows, int Hkv, int page_size, cudaStream_t s) {
+                    long long n_rows, int Hkv, int page_size, long long n_slots, int* status, cudaStream_t s) {
+  (void)n_slots; (void)status;  // used by the bounds-checked build
   if (n_rows <= 0) return;
   const long long total = n_rows * Hkv * 16;
   const int blocks = (int)std::min<long long>((total + 255) / 256, 148 * 8);
   cb::kv_cache_write_kernel<<<blocks, 256, 0, s>>>((const uint4*)k, (const uint4*)v, slots, (uint4*)k_cache,
-                                                  (uint4*)v_cache, n_rows, Hkv, page_size);
+                                                  (uint4*)v_cache, n_rows, Hkv, page_size
+                                                  COSMOS_BC_ARGS(n_slots, status));
 }
 }  // namespace cosmos
 
@@ -340,7 +346,8 @@ __global__ void __launch_bounds__(256)
 decode_qkv_post_kernel(const bf16* __restrict__ qkv, int B, int Hq, int Hkv, const float* __restrict__ cos_t,
                        const float* __restrict__ sin_t, const bf16* __restrict__ gamma_q,
                        const bf16* __restrict__ gamma_k, float eps, const long long* __restrict__ slots,
-                       bf16* __restrict__ q_out, bf16* __restrict__ kc, bf16* __restrict__ vc, int page_size) {
+                       bf16* __restrict__ q_out, bf16* __restrict__ kc, bf16* __restrict__ vc, int page_size
+                       COSMOS_BC_PARAMS) {
   const int lane = threadIdx.x & 31;
   const int heads = Hq + 2 * Hkv;
   const long long w = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
@@ -354,6 +361,7 @@ decode_qkv_post_kernel(const bf16* __restrict__ qkv, int B, int Hq, int Hkv, con
     dst = q_out + ((long long)b * Hq + h) * 128;
   } else {
     const long long slot = slots[b];
+    if (!COSMOS_INDEX_OK(slot, SITE_DECODE_POST_SLOT)) return;  // whole warp: b and h are warp-uniform
     const long long page = slot / page_size;
     const int off = (int)(slot - page * page_size);
     const int hk = (h - Hq) % Hkv;
@@ -382,12 +390,42 @@ decode_qkv_post_kernel(const bf16* __restrict__ qkv, int B, int Hq, int Hkv, con
 namespace cosmos {
 void decode_qkv_post(const void* qkv, int B, int Hq, int Hkv, const float* cos_t, const float* sin_t,
                      const void* gamma_q, const void* gamma_k, float eps, const long long* slots, void* q_out,
-                     void* k_cache, void* v_cache, int page_size, cudaStream_t s) {
+                     void* k_cache, void* v_cache, int page_size, long long n_slots, int* status, cudaStream_t s) {
+  (void)n_slots; (void)status;  // used by the bounds-checked build
   const long long warps = (long long)B * (Hq + 2 * Hkv);
   if (warps <= 0) return;
   cb::decode_qkv_post_kernel<<<(unsigned)((warps + 7) / 8), 256, 0, s>>>(
       (const bf16*)qkv, B, Hq, Hkv, cos_t, sin_t, (const bf16*)gamma_q, (const bf16*)gamma_k, eps, slots,
-      (bf16*)q_out, (bf16*)k_cache, (bf16*)v_cache, page_size);
+      (bf16*)q_out, (bf16*)k_cache, (bf16*)v_cache, page_size COSMOS_BC_ARGS(n_slots, status));
+}
+}  // namespace cosmos
+
+// ====================================================================== bounds-check self-test
+namespace cb {
+__global__ void bounds_check_selftest_kernel(const long long* __restrict__ idx, const long long* __restrict__ limit,
+                                             int* __restrict__ ok, int n, int* status) {
+  const int i = blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= n) return;
+#ifdef COSMOS_BOUNDS_CHECK
+  ok[i] = index_ok(idx[i], limit[i], status, SITE_SELFTEST) ? 1 : 0;
+#else
+  (void)idx; (void)limit; (void)status;
+  ok[i] = 1;
+#endif
+}
+}  // namespace cb
+
+namespace cosmos {
+bool bounds_check_enabled() {
+#ifdef COSMOS_BOUNDS_CHECK
+  return true;
+#else
+  return false;
+#endif
+}
+void bounds_check_selftest(const long long* idx, const long long* limit, int* ok, int n, int* status, cudaStream_t s) {
+  if (n <= 0) return;
+  cb::bounds_check_selftest_kernel<<<(n + 127) / 128, 128, 0, s>>>(idx, limit, ok, n, status);
 }
 }  // namespace cosmos
 

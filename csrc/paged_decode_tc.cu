@@ -175,7 +175,12 @@ paged_decode_tc_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_con
         int page = num_pages;
         if (j < I.n_tiles && op < n_ops && tok < I.kv_end) {
           page = table[(long long)I.b * max_pages + tok / page_size];
-          if (page < 0 || page >= num_pages) page = num_pages;
+          if (page < 0 || page >= num_pages) {
+#ifdef COSMOS_BOUNDS_CHECK
+            if (status) atomicCAS(status, 0, ST_BAD_INDEX | (SITE_PAGED_DECODE_TC_PAGE << 8));
+#endif
+            page = num_pages;
+          }
         }
         return page;
       };

@@ -611,3 +611,26 @@ def test_kernels_do_not_write_outside_their_outputs():
     want, _ = ref.attention(q.float(), kk.float(), v.float())
     _close(o, want, 2e-2, 2e-2, "attention into a guarded view")
     ops.check_status()
+
+
+@pytest.mark.parametrize("checked", [False, True])
+def test_bounds_checked_build_selftest(checked):
+    """The debug build with device-side index checks (cosmos_b200/_C_check.so): its check classifies good and
+    bad indices and reports through the status word, and the checked kernels still match their definitions
+    on valid inputs. Runs in a child process because the build is chosen when the library is loaded."""
+    import json
+    import os
+    import subprocess
+    import sys
+    from pathlib import Path
+    root = Path(__file__).resolve().parents[1]
+    if checked and not (root / "cosmos_b200" / "_C_check.so").exists():
+        pytest.skip("bounds-checked build not present (python -m cosmos_b200.ops._build --bounds-check)")
+    env = dict(os.environ, COSMOS_BOUNDS_CHECK="1" if checked else "0", COSMOS_B200_NO_BUILD="1")
+    r = subprocess.run([sys.executable, "-m", "cosmos_b200.ops.bounds_selftest"], cwd=root, env=env, capture_output=True,
+                       text=True, timeout=300)
+    assert r.returncode == 0, r.stdout[-2000:] + r.stderr[-4000:]
+    res = json.loads(r.stdout.strip().splitlines()[-1])
+    assert res["ok"] and res["bounds_check_build"] == checked
+    assert res["selftest_verdicts"] == ([1, 1, 1, 0, 0, 0, 1] if checked else [1] * 7)
+
