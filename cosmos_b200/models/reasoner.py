@@ -9,14 +9,12 @@ benchmark, whose attention runs in the paged-KV decode kernel.
 """
 from __future__ import annotations
 
-import math
 from dataclasses import dataclass
 from typing import Callable, List, Optional, Sequence, Tuple
 
 import torch
 import torch.nn.functional as F
 
-from .. import ops
 from ..config import DecodingConfig, MoTConfig
 from . import rope
 from .mot import KV, LOCAL_ATTN, AttnContext, MoTModel

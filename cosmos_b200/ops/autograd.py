@@ -28,7 +28,7 @@ from typing import Optional
 
 import torch
 
-from .reference import MASK_CAUSAL, MASK_FULL, MASK_MOT
+from .reference import MASK_FULL, MASK_MOT
 
 
 def _k():

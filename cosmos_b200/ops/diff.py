@@ -6,7 +6,6 @@ element-wise epilogues are composed from PyTorch ops. Setting COSMOS_TRAIN_LIBRA
 switches to the library baseline (cuBLAS matmuls and fused SDPA) for A/B comparison."""
 from __future__ import annotations
 
-import math
 import os
 from typing import Optional
 

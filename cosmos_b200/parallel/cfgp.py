@@ -10,7 +10,7 @@ all-gathers the two velocities with NCCL/gloo.
 """
 from __future__ import annotations
 
-from typing import Optional, Tuple
+from typing import Tuple
 
 import torch
 import torch.distributed as dist

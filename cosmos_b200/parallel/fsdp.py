@@ -20,8 +20,7 @@ their gradients all-reduced; they are a small part of the DM tower.
 """
 from __future__ import annotations
 
-import math
-from typing import Callable, Dict, List, Optional, Tuple
+from typing import Dict, List, Optional, Tuple
 
 import torch
 import torch.distributed as dist

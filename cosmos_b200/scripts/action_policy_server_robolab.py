@@ -19,7 +19,6 @@ import argparse
 import base64
 import io
 import time
-from typing import Optional
 
 import numpy as np
 import torch

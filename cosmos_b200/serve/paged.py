@@ -9,7 +9,7 @@ which keeps the block table static during decode (a requirement for CUDA-graph r
 """
 from __future__ import annotations
 
-from typing import List, Optional, Sequence
+from typing import Sequence
 
 import torch
 

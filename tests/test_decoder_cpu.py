@@ -1,7 +1,7 @@
 """Paged-KV batched decoder on CPU (tp = 1) against the contiguous-cache Reasoner engine."""
 import torch
 
-from cosmos_b200.config import DecodingConfig, tiny_config
+from cosmos_b200.config import tiny_config
 from cosmos_b200.models.mot import MoTModel
 from cosmos_b200.models.reasoner import ReasonerEngine
 from cosmos_b200.serve.decoder import TPDecoder

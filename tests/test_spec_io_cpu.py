@@ -8,7 +8,7 @@ import pytest
 
 from cosmos_b200.data.vfm.action import pose_utils
 from cosmos_b200.io import media, mp4
-from cosmos_b200.io.spec import InferenceSpec, SpecError, load_specs, spec_from_dict
+from cosmos_b200.io.spec import SpecError, load_specs, spec_from_dict
 from cosmos_b200.utils.tokenizer import ByteTokenizer
 
 # the reference checkout, when it sits next to this repository (its cookbook specs serve as parsing fixtures)

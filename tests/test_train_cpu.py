@@ -1,6 +1,5 @@
 """Training on CPU ranks over gloo: the FSDP (and FSDP x CP) step must reproduce the single-process
 AdamW step on the same global batch; checkpoint/resume must continue bit-identically."""
-import pytest
 import torch
 
 from tests.dist_utils import run_ranks
