@@ -13,7 +13,7 @@ from __future__ import annotations
 import json
 from dataclasses import dataclass, field, fields
 from pathlib import Path
-from typing import Any, Dict, List, Optional, Sequence, Union
+from typing import Any, Dict, List, Optional, Sequence, Tuple, Union
 
 MODEL_MODES = ("text2image", "text2video", "image2video", "video2video", "forward_dynamics",
                "inverse_dynamics", "policy", "reasoner")
@@ -108,12 +108,22 @@ class InferenceSpec:
             return _read_prompt_file(self.resolve(self.prompt_path))
         return ""
 
-    def negative_prompt_text(self) -> str:
+    def negative_prompt_text(self, size: Optional[Tuple[int, int]] = None) -> str:
+        """The negative prompt after `negative_metadata_mode` / `negative_prompt_keep_metadata` (see
+        io/prompt_schema.py); `size` = (width, height) supplies the metadata when the positive prompt has none."""
+        from .prompt_schema import make_metadata, negative_prompt_for
         if self.negative_prompt is not None:
-            return self.negative_prompt
-        if self.negative_prompt_file is not None:
-            return _read_prompt_file(self.resolve(self.negative_prompt_file))
-        return ""
+            neg = self.negative_prompt
+        elif self.negative_prompt_file is not None:
+            neg = _read_prompt_file(self.resolve(self.negative_prompt_file))
+        else:
+            return ""
+        fallback = None
+        if size is not None:
+            fallback = make_metadata(size[0], size[1], self.num_frames, self.fps,
+                                     self.aspect_ratio)
+        return negative_prompt_for(neg, self.prompt_text(), self.negative_metadata_mode,
+                                   self.negative_prompt_keep_metadata, fallback)
 
     def to_dict(self) -> Dict[str, Any]:
         return {f.name: getattr(self, f.name) for f in fields(self) if f.name != "spec_dir"}

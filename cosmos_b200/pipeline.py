@@ -175,19 +175,26 @@ class Cosmos3OmniPipeline:
                 action_dim: Optional[int] = None, denoise_action: bool = False, n_action: int = 0,
                 seed: int = 0, sampling: Optional[SamplingConfig] = None,
                 max_sequence_length: Optional[int] = None, sound_duration: Optional[float] = None,
-                condition_video_keep: Optional[str] = None) -> Tuple[GenState, SamplingConfig]:
+                condition_video_keep: Optional[str] = None,
+                negative_metadata_same: bool = False) -> Tuple[GenState, SamplingConfig]:
         """`sound_duration` (seconds) overrides the sound track length, which otherwise equals the clip's
         `num_frames / fps` (reference cookbooks/cosmos3/generator/audiovisual/run_with_vllm_omni.ipynb:429).
         `condition_video_keep` says which end of an input video supplies the conditioning frames:
-        "first" (default) or "last" (continue a clip from its final frames)."""
+        "first" (default) or "last" (continue a clip from its final frames).
+        `negative_metadata_same` appends the resolution / duration sentences to a plain-text negative prompt as
+        well (the input spec's `negative_metadata_mode: "same"`; structured prompts carry their metadata as
+        JSON keys, see io/prompt_schema.py)."""
         cfg = self.cfg
         if self.safety_checker is not None:
             self.safety_checker.check_prompt(prompt)
-        text = prompt
+        suffix = ""
         if add_resolution_template:
-            text += RESOLUTION_TEMPLATE.format(w=width, h=height)
+            suffix += RESOLUTION_TEMPLATE.format(w=width, h=height)
         if add_duration_template and num_frames > 1:
-            text += DURATION_TEMPLATE.format(sec=num_frames / float(fps), fps=fps)
+            suffix += DURATION_TEMPLATE.format(sec=num_frames / float(fps), fps=fps)
+        text = prompt + suffix
+        if negative_metadata_same and negative_prompt and not negative_prompt.lstrip().startswith("{"):
+            negative_prompt = negative_prompt + suffix
         sc = sampling or SamplingConfig(num_steps=num_inference_steps, guidance=guidance_scale,
                                         shift=self.scheduler.config.flow_shift,
                                         sigma_max=self.scheduler.config.sigma_max,

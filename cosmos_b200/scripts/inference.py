@@ -116,12 +116,15 @@ def run_generator_sample(pipe, spec: InferenceSpec, out_dir: Path, quality: int,
         else:
             kw["n_action"] = spec.action_chunk_size
             kw["denoise_action"] = True
+    if spec.negative_metadata_mode == "same":
+        kw["negative_metadata_same"] = True
+    negative = spec.negative_prompt_text((width, height)) or None
     t0 = time.perf_counter()
     per_chunk = spec.num_video_frames_per_chunk
     if per_chunk and spec.num_frames > per_chunk and image is None:
         # long clip: generated chunk by chunk, each chunk conditioned on the tail of the previous one
         kw.pop("condition_frame_indexes", None)
-        out = pipe.generate_chunked(prompt=spec.prompt_text(), negative_prompt=spec.negative_prompt_text() or None,
+        out = pipe.generate_chunked(prompt=spec.prompt_text(), negative_prompt=negative,
                                     video=video, num_frames=spec.num_frames, height=height, width=width,
                                     fps=spec.fps, frames_per_chunk=per_chunk,
                                     num_conditional_frames=spec.num_conditional_frames or 1,
@@ -129,7 +132,7 @@ def run_generator_sample(pipe, spec: InferenceSpec, out_dir: Path, quality: int,
                                     sampling=sc, num_inference_steps=spec.num_steps, guidance_scale=spec.guidance,
                                     enable_sound=spec.enable_sound, **kw)
     else:
-        out = pipe(prompt=spec.prompt_text(), negative_prompt=spec.negative_prompt_text() or None, image=image,
+        out = pipe(prompt=spec.prompt_text(), negative_prompt=negative, image=image,
                    video=video, num_frames=spec.num_frames, height=height, width=width, fps=spec.fps,
                    num_inference_steps=spec.num_steps, guidance_scale=spec.guidance, enable_sound=spec.enable_sound,
                    sampling=sc, **kw)
