@@ -104,8 +104,8 @@ class Cosmos3OmniPipeline:
             device = f"cuda:{torch.cuda.current_device()}"
         elif isinstance(device_map, str) and device_map.startswith("cuda"):
             device = device_map
-        path = Path(name_or_path)
-        ckpt_dir = path if (path.is_dir() and (path / "transformer").is_dir()) else None
+        from .ckpt.resolve import resolve_checkpoint_dir
+        ckpt_dir = resolve_checkpoint_dir(name_or_path)   # a directory, or a name with a snapshot in the local hub cache
         if ckpt_dir is not None and (ckpt_dir / "transformer" / "config.json").exists():
             cfg = MoTConfig(**{k: (tuple(v) if isinstance(v, list) else v) for k, v in
                                json.loads((ckpt_dir / "transformer" / "config.json").read_text()).items()})

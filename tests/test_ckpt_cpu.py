@@ -88,3 +88,30 @@ def test_corrupted_checkpoint_is_rejected_with_a_message(tmp_path, how):
         sio.load_model(_model(), tmp_path / "ck")
     msg = str(ei.value)
     assert any(w in msg.lower() for w in ("truncated", "safetensors", "bytes", "json", "header", "deserializ")), msg
+
+
+def test_checkpoint_name_resolves_through_the_local_hub_cache(tmp_path, monkeypatch):
+    """`--checkpoint-path Cosmos3-Nano` means the repo `nvidia/Cosmos3-Nano`; it is looked up in the local hub
+    cache only, and the revision named by refs/main wins over other snapshots."""
+    import torch
+    from cosmos_b200.ckpt.resolve import repo_id, resolve_checkpoint_dir
+    from cosmos_b200.pipeline import Cosmos3OmniPipeline
+    assert repo_id("Cosmos3-Nano") == "nvidia/Cosmos3-Nano" and repo_id("acme/My-Model") == "acme/My-Model"
+    monkeypatch.setenv("HF_HOME", str(tmp_path / "hf"))
+    monkeypatch.delenv("HF_HUB_CACHE", raising=False)
+    assert resolve_checkpoint_dir("Cosmos3-Nano") is None
+    pipe = Cosmos3OmniPipeline.from_pretrained("tiny", torch_dtype=torch.float32, vae_widths=(8, 16, 16, 16),
+                                               config_overrides=dict(n_layers=1, max_text_len=16), seed=5)
+    base = tmp_path / "hf" / "hub" / "models--nvidia--Cosmos3-Nano"
+    (base / "snapshots" / "stale").mkdir(parents=True)          # a snapshot without components is skipped
+    snap = base / "snapshots" / "abc123"
+    pipe.save_pretrained(snap)
+    (base / "refs").mkdir()
+    (base / "refs" / "main").write_text("abc123\n")
+    assert resolve_checkpoint_dir("Cosmos3-Nano") == snap
+    assert resolve_checkpoint_dir("nvidia/Cosmos3-Nano") == snap
+    assert resolve_checkpoint_dir(str(snap)) == snap and resolve_checkpoint_dir(str(tmp_path)) is None
+    again = Cosmos3OmniPipeline.from_pretrained("Cosmos3-Nano", torch_dtype=torch.float32, vae_widths=(8, 16, 16, 16), seed=9)
+    assert again.cfg.n_layers == 1 and again.cfg.max_text_len == 16      # the stored config, not the 16B one
+    a, b = pipe.transformer.state_dict(), again.transformer.state_dict()
+    assert a.keys() == b.keys() and all(torch.equal(a[k], b[k]) for k in a)
