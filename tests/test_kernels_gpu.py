@@ -634,3 +634,31 @@ def test_bounds_checked_build_selftest(checked):
     assert res["ok"] and res["bounds_check_build"] == checked
     assert res["selftest_verdicts"] == ([1, 1, 1, 0, 0, 0, 1] if checked else [1] * 7)
 
+
+
+def test_gemm_result_does_not_depend_on_the_tile_to_cta_assignment():
+    """Race check by schedule: the persistent GEMM is run with one CTA per SM, with 37 and with 3 CTAs, so
+    that tiles land on other CTAs, in another order, and many tiles share one CTA's smem ring and TMEM
+    double buffer. Accumulation order inside a tile and across split-K partials is fixed, so all runs
+    must agree bit for bit."""
+    torch.manual_seed(31)
+    k = torch.ops.cosmos_b200
+    cases = [
+        (lambda: (_rand(1500, 512), _rand(1024, 512, scale=1 / 16)), dict(epi=ops.EPI_PLAIN)),
+        (lambda: (_rand(700, 1024), _rand(2048, 1024, scale=1 / 16)), dict(epi=ops.EPI_SWIGLU)),
+        (lambda: (_rand(8, 4096), _rand(512, 4096, scale=1 / 32)), dict(epi=ops.EPI_PLAIN)),   # split-K path
+    ]
+    try:
+        for make, kw in cases:
+            a, w = make()
+            outs = []
+            for limit in (0, 37, 3):
+                k.gemm_set_grid_limit(limit)
+                outs.append(ops.gemm(a, w, **kw).clone())
+            torch.cuda.synchronize()
+            ops.check_status()
+            assert torch.equal(outs[0], outs[1]) and torch.equal(outs[0], outs[2]), kw
+            want = ref.gemm(a.float(), w.float(), None, kw["epi"])
+            _close(outs[0], want, 3e-2, 2e-2, "gemm")
+    finally:
+        k.gemm_set_grid_limit(0)
