@@ -1,5 +1,5 @@
 // Native host-side runtime pieces: the paged-KV block allocator used by the Reasoner's
-// decode path, the request scheduler's slot bookkeeping, and the checkpoint reader. Registered as torch custom
+// decode path and the checkpoint reader (torch-free cores under csrc/host). Registered as torch custom
 // classes so Python holds them by reference and calls cost no interpreter-level loops.
 #pragma once
 #include <torch/library.h>
