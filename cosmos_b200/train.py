@@ -195,6 +195,12 @@ def main(argv=None) -> int:
     ap.add_argument("--save-dir", default=None)
     ap.add_argument("--resume", action="store_true")
     ap.add_argument("--layers", type=int, default=0)
+    ap.add_argument("--data-root", default=None,
+                    help="folder of captioned clips (data/video_text.py); without it the step runs on synthetic latents")
+    ap.add_argument("--data-fps", type=float, default=None, help="resample clips to this frame rate")
+    ap.add_argument("--data-workers", type=int, default=2, help="host threads that decode and resize ahead of the GPU")
+    ap.add_argument("--data-seed", type=int, default=0)
+    ap.add_argument("--vae-widths", default="32,64,128,128", help="channel widths of the tokenizer VAE (with --data-root)")
     ap.add_argument("--log-jsonl", default=None, help="append one JSON record per step to this file (rank 0)")
     ap.add_argument("--health-timeout", type=float, default=None,
                     help="seconds to wait on the host for every rank before each step (peer failure detection)")
@@ -223,6 +229,21 @@ def main(argv=None) -> int:
     c, t, h, w = (int(v) for v in args.latent.split(","))
     # ranks of one cp group see the same clip; different dp ranks see different clips
     data_rank = mesh.index("dp_replicate") * mesh.size("dp_shard") + mesh.index("dp_shard")
+    data_world = mesh.size("dp_replicate") * mesh.size("dp_shard")
+    feed = batcher = None
+    if args.data_root:
+        from .data.video_text import LatentBatcher, Prefetcher, ShardedSampler, VideoTextDataset
+        from .models.vae import CausalVideoVAE
+        from .utils.tokenizer import load_tokenizer
+        ds = VideoTextDataset(args.data_root, 1 + (t - 1) * cfg.vae_t_compress, w * cfg.vae_s_compress,
+                              h * cfg.vae_s_compress, args.data_fps)
+        sampler = ShardedSampler(len(ds), data_rank, data_world, args.data_seed)
+        state_file = Path(args.save_dir) / f"data_state_rank{rank:05d}.json" if args.save_dir else None
+        if args.resume and state_file is not None and state_file.exists():
+            sampler.load_state_dict(json.loads(state_file.read_text()))
+        vae = CausalVideoVAE(c, tuple(int(v) for v in args.vae_widths.split(","))).to(device=dev, dtype=dtype).eval()
+        batcher = LatentBatcher(vae, load_tokenizer(None, cfg.vocab_size), args.text_len, cfg.vocab_size, dev, dtype)
+        feed = Prefetcher(ds, sampler, args.micro_batch, depth=2, workers=args.data_workers)
     g = torch.Generator(device=dev).manual_seed(1000 + data_rank)
     tokens_per_step = args.micro_batch * (t // cfg.patch_t) * (h // cfg.patch_hw) * (w // cfg.patch_hw)
     tokens_per_step = (tokens_per_step + args.micro_batch * args.text_len) * mesh.size("dp_shard") * mesh.size("dp_replicate")
@@ -230,8 +251,11 @@ def main(argv=None) -> int:
     logger = JsonlLogger(args.log_jsonl, stdout=True)  # rank 0 only
     times = []
     for s in range(step0, step0 + args.warmup + args.steps):
-        lat = torch.randn(args.micro_batch, c, t, h, w, generator=g, device=dev, dtype=dtype)
-        ids = torch.randint(0, cfg.vocab_size, (args.micro_batch, args.text_len), generator=g, device=dev)
+        if feed is not None:
+            lat, ids = batcher(next(feed))
+        else:
+            lat = torch.randn(args.micro_batch, c, t, h, w, generator=g, device=dev, dtype=dtype)
+            ids = torch.randint(0, cfg.vocab_size, (args.micro_batch, args.text_len), generator=g, device=dev)
         if cuda:
             torch.cuda.synchronize()
         t0 = time.perf_counter()
@@ -244,6 +268,10 @@ def main(argv=None) -> int:
         logger.log(step=s + 1, **out, step_s=round(dt, 4))
     if args.save_dir:
         tr.save(args.save_dir, step0 + args.warmup + args.steps)
+        if feed is not None:   # where the data stream of this rank continues after a resume
+            state_file.write_text(json.dumps(feed.resume_state))
+    if feed is not None:
+        feed.close()
     if rank == 0 and times:
         avg = sum(times) / len(times)
         print(json.dumps({"metric": "train_tokens_per_s", "value": tokens_per_step / avg, "step_s": avg,
