@@ -134,6 +134,8 @@ class Cosmos3OmniPipeline:
         sio.save_model(self.transformer, out / "transformer")
         sio.save_sharded(dict(self.vae.state_dict()), out / "vae")
         sio.save_sharded(dict(self.sound_tokenizer.state_dict()), out / "sound_tokenizer")
+        if hasattr(self.tokenizer, "hf"):  # a checkpoint's own tokenizer travels with it
+            self.tokenizer.hf.save_pretrained(str(out / "tokenizer"))
         (out / "scheduler").mkdir(parents=True, exist_ok=True)
         (out / "scheduler" / "scheduler_config.json").write_text(json.dumps(self.scheduler.config.__dict__))
         (out / "model_index.json").write_text(json.dumps({

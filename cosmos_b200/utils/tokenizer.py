@@ -88,9 +88,50 @@ class ByteTokenizer:
         return ids
 
 
-def load_tokenizer(checkpoint_path: Optional[str], vocab_size: int):
-    if checkpoint_path and Path(checkpoint_path).is_dir() and (Path(checkpoint_path) / "tokenizer.json").exists():
-        from transformers import AutoTokenizer
+class HFTokenizer:
+    """A checkpoint's own tokenizer (`tokenizer.json` + config, loaded by `transformers.AutoTokenizer`) behind the
+    interface the framework uses everywhere (`ByteTokenizer` above): `encode` / `decode`, the ids of the end and
+    media-placeholder tokens, `pad_or_truncate`, and the Qwen-style chat layout with every media part expanded to
+    `<|vision_start|>` + n placeholder tokens + `<|vision_end|>` (n = merged vision tokens of that image / clip)."""
 
-        return AutoTokenizer.from_pretrained(checkpoint_path)
+    NEEDED = ("<|im_start|>", "<|im_end|>", "<|vision_start|>", "<|vision_end|>", "<|image_pad|>", "<|video_pad|>")
+
+    def __init__(self, hf):
+        self.hf = hf
+        self.vocab_size = len(hf)
+        unk = hf.unk_token_id
+        ids = {t: hf.convert_tokens_to_ids(t) for t in self.NEEDED + ("<|endoftext|>",)}
+        missing = [t for t in self.NEEDED if ids[t] is None or (unk is not None and ids[t] == unk)]
+        if missing:
+            raise ValueError(f"tokenizer lacks the special tokens {missing}")
+        self.special_ids: Dict[str, int] = {k: int(v) for k, v in ids.items() if v is not None}
+        self.eos_id = self.special_ids["<|im_end|>"]
+        eot = self.special_ids.get("<|endoftext|>")
+        self.eot_id = eot if eot is not None and eot != unk else int(hf.eos_token_id if hf.eos_token_id is not None else self.eos_id)
+        self.pad_id = int(hf.pad_token_id) if hf.pad_token_id is not None else self.eot_id
+        self.pad_token_id = self.pad_id
+        self.image_pad_id = self.special_ids["<|image_pad|>"]
+        self.video_pad_id = self.special_ids["<|video_pad|>"]
+
+    def encode(self, text: str) -> List[int]:
+        return list(self.hf.encode(text, add_special_tokens=False))
+
+    def decode(self, ids: Sequence[int], skip_special: bool = True) -> str:
+        return self.hf.decode([int(t) for t in ids], skip_special_tokens=skip_special)
+
+    def pad_or_truncate(self, ids: List[int], length: int) -> List[int]:
+        return (list(ids) + [self.pad_id] * length)[:length]
+
+    apply_chat_template = ByteTokenizer.apply_chat_template   # same layout, built from encode() and special_ids
+
+
+def load_tokenizer(checkpoint_path: Optional[str], vocab_size: int):
+    """The checkpoint's tokenizer when it ships one (looked for in the directory itself and in `tokenizer/`),
+    else the byte-level stand-in."""
+    if checkpoint_path and Path(checkpoint_path).is_dir():
+        for d in (Path(checkpoint_path), Path(checkpoint_path) / "tokenizer"):
+            if (d / "tokenizer.json").exists():
+                from transformers import AutoTokenizer
+
+                return HFTokenizer(AutoTokenizer.from_pretrained(str(d)))
     return ByteTokenizer(vocab_size)
