@@ -117,8 +117,6 @@ class BatchEngine:
             raise ValueError("empty prompt")
         if len(ids) + max_new_tokens > self.max_len:
             raise ValueError(f"prompt ({len(ids)}) + max_new_tokens ({max_new_tokens}) exceeds max_len {self.max_len}")
-        if embeds is not None and self.tp > 1:
-            raise NotImplementedError("requests with media are served by one rank (tensor-parallel engine: text only)")
         params = dict(ids=[min(int(t), self.cfg.vocab_size - 1) for t in ids], max_new_tokens=int(max_new_tokens),
                       eos_ids=tuple(eos_ids), temperature=float(temperature),
                       top_k=int(top_k) if top_k and top_k > 0 else TPDecoder.SAMPLE_K, top_p=float(top_p),
@@ -128,6 +126,11 @@ class BatchEngine:
             self.waiting.pop()
             raise ValueError("a request with embeddings needs positions [3, n] and one embedding row per prompt token")
         if self.tp > 1:
+            if embeds is not None:
+                # the vision encoder ran once, on this rank; its outputs travel to the followers with the request
+                cpu = lambda t: None if t is None else t.detach().to("cpu")  # noqa: E731
+                params = dict(params, media=dict(embeds=cpu(embeds), positions=cpu(positions), vision_mask=cpu(vision_mask),
+                                                 deepstack=None if deepstack is None else [cpu(t) for t in deepstack]))
             self._new.append(params)
         return r
 
@@ -153,7 +156,7 @@ class BatchEngine:
         else:
             self._stop = stop
             for params in new:
-                self._enqueue(params)
+                self._enqueue(params, **(params.get("media") or {}))
 
     def follow(self) -> None:
         """Loop of the ranks other than 0: mirror every step of rank 0 until it calls `shutdown()`."""

@@ -209,3 +209,50 @@ def test_tensor_parallel_engine_runs_in_lock_step_over_gloo():
         if greedy:                                       # greedy requests follow the single-process reference
             from types import SimpleNamespace
             _check_against_reference(model, SimpleNamespace(ids=ids, out=toks, rid=0))
+
+
+def _tp_engine_media_ranks(rank, world):
+    """Rank 0 encodes an image and submits the request with its embeddings; the follower receives them with the
+    request and mirrors prefill and decode."""
+    import torch.distributed as dist
+    from cosmos_b200.models.vit import VisionEncoder
+
+    torch.manual_seed(0)
+    cfg = tiny_config(n_layers=2, vocab_size=300, vit_deepstack=(0,))
+    model = MoTModel(cfg, dtype=torch.float32, device="cpu")
+    model.init_weights(seed=11)
+    eng = BatchEngine(model, max_batch=2, max_len=64, page_size=4, use_graph=False, group=dist.group.WORLD)
+    if rank == 0:
+        vit = VisionEncoder(cfg).float().eval()
+        with torch.no_grad():
+            emb, grid, deep = vit(torch.rand(1, 3, 64, 64) * 2 - 1, return_deepstack=True)
+        n_vis = grid[0] * grid[1] * grid[2]
+        ids = [5, 6] + [299] * n_vis + [7, 8]
+        ref = ReasonerEngine(model, vit)
+        ids_t = torch.tensor([ids])
+        vmask = ids_t == 299
+        x = ref.embed(ids_t, emb, vmask)
+        pos = ref.positions(ids_t, vmask, [grid])
+        text = eng.submit([1, 2, 3], 4)
+        vis = eng.submit(ids, 5, embeds=x[0], positions=pos, vision_mask=vmask[0], deepstack=deep)
+        eng.run_until_done()
+        eng.shutdown()
+        logits, kvs = ref.prefill(x, pos, deep, vmask)      # the single-request engine as the oracle
+        p = rope.next_start(pos)
+        for tok in vis.out:
+            assert logits[0][tok] >= logits[0].max() - 1e-3
+            logits, kvs = ref.decode_one(torch.tensor([tok]), p, kvs)
+            p += 1
+        reqs = [text, vis]
+    else:
+        eng.follow()
+        reqs = [eng.finished[i] for i in sorted(eng.finished)]
+    return {"outs": [r.out for r in reqs], "had_media": [r.embeds is not None for r in reqs]}
+
+
+def test_tensor_parallel_engine_serves_a_request_with_media():
+    from tests.dist_utils import run_ranks
+
+    out = run_ranks(_tp_engine_media_ranks, 2, timeout=180)
+    assert out[0]["outs"] == out[1]["outs"] and [len(o) for o in out[0]["outs"]] == [4, 5]
+    assert out[0]["had_media"] == out[1]["had_media"] == [False, True]
