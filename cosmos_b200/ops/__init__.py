@@ -52,9 +52,9 @@ def _grad_needed(*tensors) -> bool:
 
 
 def _use_cuda(t: torch.Tensor, *others) -> bool:
-    """True when the call should run the sm_100a kernel: CUDA bf16 input and no autograd graph to
-    build. Calls that need gradients run the differentiable PyTorch definition instead (the
-    forward kernels have no backward counterparts yet)."""
+    """True when the call should run the forward sm_100a kernel directly: CUDA bf16 input and no autograd
+    graph to build. Calls that need gradients go through `_train_cuda` (autograd functions over the forward
+    and backward kernels). A CUDA bf16 call without the kernel library raises: there is no silent fallback."""
     if not (t.is_cuda and t.dtype == torch.bfloat16):
         return False
     if _grad_needed(t, *others):
@@ -75,7 +75,11 @@ def _train_cuda(t: torch.Tensor, *others) -> bool:
         return False
     if os.environ.get("COSMOS_TRAIN_LIBRARY_BACKWARD") == "1":
         return False
-    return load_extension()
+    if not load_extension():
+        raise RuntimeError(
+            "cosmos_b200 kernel library is not available on this GPU host "
+            f"({_load_error}); run `python -m cosmos_b200.ops._build`")
+    return True
 
 
 class _Counted:
