@@ -289,7 +289,14 @@ def load_specs(path: Union[str, Path], overrides: Optional[Dict[str, Any]] = Non
     base = path.resolve().parent
     try:
         if path.suffix == ".jsonl":
-            rows = [json.loads(line) for line in text.splitlines() if line.strip()]
+            rows = []
+            for n, line in enumerate(text.splitlines(), 1):
+                if not line.strip():
+                    continue
+                try:
+                    rows.append(json.loads(line))
+                except json.JSONDecodeError as e:
+                    raise SpecError(f"{path}:{n}: invalid JSON ({e})") from e
         else:
             doc = json.loads(text)
             rows = doc if isinstance(doc, list) else [doc]

@@ -231,3 +231,28 @@ def test_preview_helpers_on_reference_specs(tmp_path):
     mp4.write_mp4_mjpeg(src, clip, 10)
     prev = ph.make_preview(src)
     assert prev.exists() and prev.name == "vision_preview.mp4"
+
+
+def test_truncated_and_damaged_spec_files_are_reported_not_half_read(tmp_path):
+    """Host-side fault injection on the input side: a spec cut off mid-write, a JSONL with one damaged line, an
+    empty file and a non-object sample all stop the run with a message that names the file (and the line)."""
+    good = {"model_mode": "text2video", "name": "a", "prompt": "p", "resolution": "256", "num_frames": 5}
+    whole = json.dumps(good)
+    cut = tmp_path / "cut.json"
+    cut.write_text(whole[:len(whole) // 2])
+    with pytest.raises(SpecError, match=r"cut\.json: invalid JSON"):
+        load_specs(cut)
+    lines = tmp_path / "batch.jsonl"
+    lines.write_text(whole + "\n\n" + whole.replace('"a"', '"b"')[:-7] + "\n" + whole.replace('"a"', '"c"') + "\n")
+    with pytest.raises(SpecError, match=r"batch\.jsonl:3: invalid JSON"):
+        load_specs(lines)
+    empty = tmp_path / "empty.jsonl"
+    empty.write_text("\n\n")
+    with pytest.raises(SpecError, match="no samples"):
+        load_specs(empty)
+    arr = tmp_path / "arr.json"
+    arr.write_text("[1, 2]")
+    with pytest.raises(SpecError, match="must be a JSON object"):
+        load_specs(arr)
+    with pytest.raises(SpecError, match="not found"):
+        load_specs(tmp_path / "missing.json")
