@@ -45,6 +45,7 @@ class SymmGroup:
         self.on_gpu = device.type == "cuda"
         self._epochs: Dict[int, int] = {}
         self._bufs: Dict[str, SymmBuffer] = {}
+        self._meets: Dict[str, int] = {}
         self.pads = self.alloc("__pads__", PAD_WORDS * 4, zero=True)
         self.pads_dev = torch.tensor(self.pads.peer_ptrs, dtype=torch.int64, device=device)
         self.barrier_host()
@@ -56,6 +57,7 @@ class SymmGroup:
                 return self._bufs[name]
             raise ValueError(f"symmetric buffer '{name}' already exists with a smaller size")
         nbytes = (nbytes + 255) // 256 * 256
+        self._meet(name)
         if self.on_gpu and self.world > 1:
             import torch.distributed._symmetric_memory as symm_mem
 
@@ -73,6 +75,23 @@ class SymmGroup:
             buf = SymmBuffer(t, [t.data_ptr()] * max(self.world, 1))
         self._bufs[name] = buf
         return buf
+
+    def _meet(self, name: str) -> None:
+        """Host-side guard in front of the handle exchange: every rank of the group announces that it reached
+        the allocation of `name` and waits, with a limit (COSMOS_SYMM_TIMEOUT_S, default 300 s), for the others.
+        A rank that never gets here is named in a PeerFailure on the survivors instead of leaving them blocked
+        inside the exchange."""
+        if self.world <= 1 or not dist.is_initialized():
+            return
+        import os
+
+        from torch.distributed.distributed_c10d import _get_default_store
+
+        from .health import bounded_rendezvous
+        tag = "symm/" + "-".join(str(r) for r in self.ranks) + f"/{self.device.type}/{name}/{self._meets.get(name, 0)}"
+        self._meets[name] = self._meets.get(name, 0) + 1
+        bounded_rendezvous(_get_default_store(), tag, self.rank, self.world,
+                           float(os.environ.get("COSMOS_SYMM_TIMEOUT_S", "300")))
 
     # ------------------------------------------------------------------ synchronisation
     def next_epoch(self, slot: int, count: int = 1) -> int:

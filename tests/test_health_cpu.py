@@ -108,3 +108,31 @@ def test_heartbeat_age_with_a_fake_clock():
     with pytest.raises(PeerFailure) as ei:
         a.check_peers(max_age_s=1e9)
     assert "shutting down" in str(ei.value)
+
+
+def _symm_alloc_with_a_missing_rank(rank, world):
+    """The handle exchange of a symmetric buffer is guarded on the host: a rank that never reaches the
+    allocation is named on the others instead of leaving them inside the exchange."""
+    import os
+
+    from cosmos_b200.parallel.health import PeerFailure
+    from cosmos_b200.parallel.symm import SymmGroup
+
+    os.environ["COSMOS_SYMM_TIMEOUT_S"] = "1.0"
+    sg = SymmGroup(dist.group.WORLD, list(range(world)), torch.device("cpu"))      # everybody allocates the pads
+    sg.alloc("shared_a", 1024)
+    if rank == 2:
+        time.sleep(2.5)                                                           # drops out before the next buffer
+        return {"missing": "gone"}
+    t0 = time.time()
+    try:
+        sg.alloc("shared_b", 1024)
+    except PeerFailure as e:
+        return {"missing": e.ranks, "waited": time.time() - t0}
+    return {"missing": []}
+
+
+def test_symmetric_allocation_names_the_rank_that_dropped_out():
+    out = run_ranks(_symm_alloc_with_a_missing_rank, 3, timeout=60)
+    for r in (0, 1):
+        assert out[r]["missing"] == [2] and 0.9 < out[r]["waited"] < 2.4
