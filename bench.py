@@ -7,7 +7,8 @@ cond + uncond branches, CFG combine and Euler update), on N GPUs of one node.
         --master-port P bench.py --gpus N --steps K --warmup W
 
 Layout per N: 1 = both branches as one batch on one GPU; 2 = CFG-parallel (one branch per GPU);
-4 and 8 = CFG-parallel x Ulysses context-parallel (N/2 ranks per branch). Total work is fixed
+4 and 8 = CFG-parallel x Ulysses context-parallel (N/2 ranks per branch); `--tp-size / --cp-size / --cfgp-size /
+--cp-mode` pick another layout (e.g. `--model Cosmos3-Super --tp-size 8`). Total work is fixed
 ("strong" scaling). Timing: W untimed warm-up steps, then exactly K steps between CUDA events
 bracketed by barrier + synchronize, max over ranks. Each step streams far more than the 126 MB
 L2 (16 GB of weights, GBs of activations), so no explicit L2 flush is needed between steps.
@@ -104,6 +105,10 @@ def main():
     ap.add_argument("--guidance", type=float, default=7.0)
     ap.add_argument("--layers", type=int, default=0, help="debug only: override the layer count (marks the run invalid)")
     ap.add_argument("--e2e-steps", type=int, default=2)
+    ap.add_argument("--tp-size", type=int, default=0, help="explicit layout instead of the latency preset: tensor parallel")
+    ap.add_argument("--cp-size", type=int, default=0, help="explicit layout: context parallel (Ulysses; --cp-mode ring)")
+    ap.add_argument("--cfgp-size", type=int, default=0, help="explicit layout: CFG parallel (1 or 2)")
+    ap.add_argument("--cp-mode", default="ulysses", choices=["ulysses", "ring"])
     args = ap.parse_args()
     if args.impl == "reference":
         return reference_arm(args)
@@ -125,7 +130,12 @@ def main():
         args.gpus = world
     torch.cuda.set_device(local_rank)
     dev = torch.device("cuda", local_rank)
-    mesh = init_distributed(world, rank, local_rank, preset="latency")
+    pc = None
+    if args.tp_size or args.cp_size or args.cfgp_size:
+        from cosmos_b200.config import ParallelConfig
+        pc = ParallelConfig(tp=max(1, args.tp_size), cp=max(1, args.cp_size), cfgp=max(1, args.cfgp_size), cp_mode=args.cp_mode)
+        pc.validate(world)
+    mesh = init_distributed(world, rank, local_rank, preset="latency", pc=pc)
     if not ops.load_extension():
         raise SystemExit("cosmos_b200 kernel library failed to load")
 
@@ -201,10 +211,10 @@ def main():
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
     ms, e2e_ms = float(t[0]), float(t[1])
     if rank == 0:
-        pub = PUBLISHED_S_PER_VIDEO.get(world)
+        pub = PUBLISHED_S_PER_VIDEO.get(world) if args.model == "Cosmos3-Nano" else None   # the table is Nano's
         base_ms = None if pub is None else pub * 1e3 / PUBLISHED_STEPS
         rec = {
-            "metric": "dit_step_ms (Cosmos3-Nano T2V 720p, one guided denoise step: cond+uncond forward, CFG, Euler)",
+            "metric": f"dit_step_ms ({args.model} T2V {args.resolution}p, one guided denoise step: cond+uncond forward, CFG, Euler)",
             "value": round(ms, 3), "unit": "ms", "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
             "ms_per_step": round(ms, 3), "higher_is_better": False, "scaling": "strong",
             "vs_baseline": None if base_ms is None else round(ms / base_ms, 4),
