@@ -45,6 +45,8 @@ class MoTConfig:
     # ViT block indexes whose features are merged and added to the hidden states of the first AR layers
     # (DeepStack of the Qwen3-VL family the Reasoner follows; () = off)
     vit_deepstack: Tuple[int, ...] = ()
+    vit_ffn: int = 0          # MLP width of a ViT block; 0 = 4 x vit_hidden
+    vit_pos_side: int = 48    # the learned position table covers vit_pos_side x vit_pos_side patches
     max_text_len: int = 512
     init_std: float = 0.02
 
@@ -90,7 +92,7 @@ def nano_config(**kw) -> MoTConfig:
     """Cosmos3-Nano stand-in: two Qwen3-VL-8B-shaped towers (16.4 B parameters)."""
     base = MoTConfig(name="Cosmos3-Nano", d_model=4096, n_layers=36, n_heads=32, n_kv_heads=8, head_dim=128,
                      ffn_dim=12288, vocab_size=151936, mrope_section=(24, 20, 20),
-                     vit_depth=27, vit_hidden=1152, vit_heads=16, vit_deepstack=(8, 16, 24))
+                     vit_depth=27, vit_hidden=1152, vit_heads=16, vit_ffn=4304, vit_deepstack=(8, 16, 24))
     return replace(base, **kw)
 
 
@@ -98,7 +100,7 @@ def super_config(**kw) -> MoTConfig:
     """Cosmos3-Super stand-in: two Qwen3-VL-32B-shaped towers (65.5 B parameters)."""
     base = MoTConfig(name="Cosmos3-Super", d_model=5120, n_layers=64, n_heads=64, n_kv_heads=8, head_dim=128,
                      ffn_dim=25600, vocab_size=151936, mrope_section=(24, 20, 20),
-                     vit_depth=27, vit_hidden=1152, vit_heads=16, vit_deepstack=(8, 16, 24))
+                     vit_depth=27, vit_hidden=1152, vit_heads=16, vit_ffn=4304, vit_deepstack=(8, 16, 24))
     return replace(base, **kw)
 
 

@@ -35,7 +35,7 @@ class Cosmos3ReasonerConfig(PretrainedConfig):
             super().__init__(**kw)
 
     def mot_config(self) -> MoTConfig:
-        return get_model_config(self.arch, **self.overrides)
+        return get_model_config(self.arch, **{k: tuple(v) if isinstance(v, list) else v for k, v in self.overrides.items()})
 
 
 class Cosmos3ReasonerForConditionalGeneration(PreTrainedModel):
@@ -67,6 +67,8 @@ class Cosmos3ReasonerForConditionalGeneration(PreTrainedModel):
 
         p = Path(name_or_path)
         arch = name_or_path
+        if (p / "config.json").exists() and not (p / "transformer").exists():
+            return cls.from_qwen3vl(p, torch_dtype, device_map)
         if (p / "transformer" / "config.json").exists():
             import json
             arch = json.loads((p / "transformer" / "config.json").read_text()).get("name", "Cosmos3-Nano")
@@ -76,6 +78,34 @@ class Cosmos3ReasonerForConditionalGeneration(PreTrainedModel):
             state = {k: v for k, v in sio.model_state(m.model).items()}
             sio.load_into(p / "transformer", {k: v.data for k, v in state.items()}, strict=False)
         return m.eval()
+
+    @classmethod
+    def from_qwen3vl(cls, model_dir, torch_dtype=torch.float32, device_map: Optional[str] = None):
+        """A checkpoint directory in the Hugging Face Qwen3-VL layout (`config.json` with `text_config` and
+        `vision_config`, safetensors shards): the shapes come from its config, the tensors are mapped by
+        ckpt/hf_qwen3vl.py. The Reasoner is Qwen3-VL-based, so this is how it starts from public weights."""
+        import json
+        from pathlib import Path
+        from types import SimpleNamespace
+
+        from .ckpt import hf_qwen3vl as hq
+
+        doc = json.loads((Path(model_dir) / "config.json").read_text())
+        if "text_config" not in doc:
+            raise ValueError(f"{model_dir}/config.json has no text_config: not a Qwen3-VL checkpoint")
+        text, vision = SimpleNamespace(**doc["text_config"]), doc.get("vision_config")
+        text.rms_norm_eps = getattr(text, "rms_norm_eps", 1e-6)
+        kw = hq.config_kwargs_from_hf(text, SimpleNamespace(**vision) if vision else None)
+        kw = {k: (list(v) if isinstance(v, tuple) else v) for k, v in kw.items()}
+        m = cls(Cosmos3ReasonerConfig("tiny", kw), dtype=torch_dtype, device=device_map or "cpu")
+        hq.load_checkpoint_dir(m.model, m.visual if vision else None, model_dir)
+        return m.eval()
+
+    def save_qwen3vl(self, out_dir) -> None:
+        """Writes the AR tower in the Qwen3-VL text layout (safetensors) for runtimes that read that format."""
+        from .ckpt import hf_qwen3vl as hq
+        from .ckpt import safetensors_io as sio
+        sio.save_sharded(hq.export_text_weights(self.model), out_dir)
 
     def forward(self, input_ids: torch.Tensor, **_):
         """Teacher-forced logits [B, S, V] of text-only input (no KV reuse)."""

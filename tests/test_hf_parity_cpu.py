@@ -1,0 +1,144 @@
+"""Parity with the `transformers` implementation of Qwen3-VL, which the reference's Reasoner is based on: with the
+same weights the AR tower gives the text model's hidden states (text-only, 3-D positions of an image grid, DeepStack
+injection), the position-id builder gives `get_rope_index`'s ids, and the vision encoder gives the vision model's
+merged embeddings and DeepStack features."""
+import pytest
+import torch
+
+hfm = pytest.importorskip("transformers.models.qwen3_vl.modeling_qwen3_vl")
+hfc = pytest.importorskip("transformers.models.qwen3_vl.configuration_qwen3_vl")
+
+from cosmos_b200 import ops  # noqa: E402
+from cosmos_b200.ckpt import hf_qwen3vl as hq  # noqa: E402
+from cosmos_b200.config import tiny_config  # noqa: E402
+from cosmos_b200.models.mot import MoTModel  # noqa: E402
+from cosmos_b200.models.reasoner import ReasonerEngine  # noqa: E402
+from cosmos_b200.models.vit import VisionEncoder  # noqa: E402
+
+TEXT = dict(vocab_size=300, hidden_size=64, intermediate_size=128, num_hidden_layers=2, num_attention_heads=4,
+            num_key_value_heads=2, head_dim=16, rms_norm_eps=1e-6,
+            rope_parameters={"rope_type": "default", "rope_theta": 500000.0, "mrope_section": [3, 3, 2], "mrope_interleaved": True})
+VISION = dict(depth=3, hidden_size=32, intermediate_size=48, num_heads=2, patch_size=16, spatial_merge_size=2,
+              temporal_patch_size=2, out_hidden_size=64, num_position_embeddings=36, deepstack_visual_indexes=[0, 2])
+
+
+def _randomise(module):
+    torch.manual_seed(0)
+    for n, p in module.named_parameters():
+        torch.nn.init.normal_(p, 1.0 if ("norm" in n and n.endswith("weight")) else 0.0, 0.1 if "norm" in n else 0.05)
+
+
+def _pair():
+    hf = hfm.Qwen3VLTextModel(hfc.Qwen3VLTextConfig(**TEXT)).eval()
+    _randomise(hf)
+    cfg = tiny_config(**hq.config_kwargs_from_hf(hf.config))
+    ours = MoTModel(cfg, dtype=torch.float32, device="cpu", towers=("ar",))
+    hq.load_text_weights(ours, hf.state_dict())
+    return hf, ours, cfg
+
+
+def _hidden(ours, cfg, emb, pos, **kw):
+    h, _ = ours.ar_forward(emb, pos, **kw)
+    return ops.rmsnorm(h, ours.ar_norm, cfg.rms_eps)[0]
+
+
+def test_ar_tower_reproduces_the_qwen3vl_text_model():
+    hf, ours, cfg = _pair()
+    assert (cfg.d_model, cfg.n_heads, cfg.n_kv_heads, cfg.head_dim, cfg.ffn_dim, cfg.mrope_section) == (64, 4, 2, 16, 128, (3, 3, 2))
+    ids = torch.randint(0, 300, (1, 11))
+    from cosmos_b200.models import rope
+    with torch.no_grad():
+        want = hf(input_ids=ids).last_hidden_state
+        got = _hidden(ours, cfg, ours.embed_tokens(ids), rope.text_positions(11))
+    assert (got - want).abs().max() < 2e-5
+    # an image grid in the prompt: 3-D rotary ids, vision rows spliced in, DeepStack features after the first layers
+    ids = torch.tensor([[5, 6, 292] + [290] * 6 + [293, 7, 8, 9]])
+    vmask = ids == 290
+    pos = ReasonerEngine.positions(ReasonerEngine.__new__(ReasonerEngine), ids, vmask, [(1, 2, 3)])
+    emb = ours.embed_tokens(ids).clone()
+    emb[vmask] = torch.randn(6, 64)
+    deep = [torch.randn(6, 64), torch.randn(6, 64)]
+    with torch.no_grad():
+        want = hf(inputs_embeds=emb, position_ids=pos[:, None], visual_pos_masks=vmask, deepstack_visual_embeds=deep).last_hidden_state
+        got = _hidden(ours, cfg, emb, pos, deepstack=deep, vision_mask=vmask)
+        plain = _hidden(ours, cfg, emb, pos)
+    assert (got - want).abs().max() < 2e-5 and (plain - want).abs().max() > 1e-2      # DeepStack matters and matches
+    # export is the inverse of load
+    back = hq.export_text_weights(ours, prefix="")
+    sd = hf.state_dict()
+    assert all(torch.equal(back[k], sd[k]) for k in sd) and torch.equal(back["lm_head.weight"], sd["embed_tokens.weight"])
+
+
+def test_position_ids_match_get_rope_index():
+    cfg = hfc.Qwen3VLConfig(text_config=TEXT, vision_config=VISION, image_token_id=290, video_token_id=291,
+                            vision_start_token_id=292, vision_end_token_id=293)
+    hf = hfm.Qwen3VLModel(cfg).eval()
+    eng = ReasonerEngine.__new__(ReasonerEngine)
+    ids = torch.tensor([[5, 6, 292] + [290] * 6 + [293, 7, 292] + [290] * 4 + [293, 9]])
+    want, _ = hf.get_rope_index(ids, (ids == 290).int(), image_grid_thw=torch.tensor([[1, 4, 6], [1, 4, 4]]))
+    assert torch.equal(ReasonerEngine.positions(eng, ids, ids == 290, [(1, 2, 3), (1, 2, 2)]), want[:, 0])
+    # a clip is laid out frame group by frame group, each in its own vision_start / vision_end pair
+    ids = torch.tensor([[5, 292] + [291] * 6 + [293, 292] + [291] * 6 + [293, 7, 8]])
+    want, _ = hf.get_rope_index(ids, (ids == 291).int() * 2, video_grid_thw=torch.tensor([[2, 4, 6]]))
+    assert torch.equal(ReasonerEngine.positions(eng, ids, ids == 291, [(1, 2, 3), (1, 2, 3)]), want[:, 0])
+
+
+@pytest.mark.parametrize("frames,height,width", [(1, 64, 96), (4, 96, 64), (3, 160, 192)])
+def test_vision_encoder_reproduces_the_qwen3vl_vision_model(frames, height, width):
+    hv = hfm.Qwen3VLVisionModel(hfc.Qwen3VLVisionConfig(**VISION)).eval()
+    _randomise(hv)
+    cfg = tiny_config(d_model=64, **{k: v for k, v in hq.config_kwargs_from_hf(hfc.Qwen3VLTextConfig(**TEXT), hv.config).items()
+                                     if k.startswith("vit_")})
+    assert (cfg.vit_depth, cfg.vit_hidden, cfg.vit_ffn, cfg.vit_pos_side, cfg.vit_deepstack) == (3, 32, 48, 6, (0, 2))
+    vit = VisionEncoder(cfg).eval()
+    hq.load_vision_weights(vit, hv.state_dict())
+    torch.manual_seed(1)
+    video = torch.rand(frames, 3, height, width) * 2 - 1
+    pixels = hq.hf_image_patches(video, 16, 2, 2)
+    t = (frames + 1) // 2
+    with torch.no_grad():
+        out = hv(pixels, grid_thw=torch.tensor([[t, height // 16, width // 16]]))
+        got, grid, deep = vit(video, return_deepstack=True)
+    want = out.pooler_output if hasattr(out, "pooler_output") else out[0]
+    want_deep = out.deepstack_features if hasattr(out, "deepstack_features") else out[1]
+    assert grid == (t, height // 32, width // 32) and got.shape == want.shape
+    assert (got - want).abs().max() < 5e-5, float((got - want).abs().max())
+    assert len(deep) == len(want_deep) == 2
+    for a, b in zip(deep, want_deep):
+        assert (a - b).abs().max() < 5e-5
+
+
+def test_reasoner_class_loads_a_qwen3vl_checkpoint_directory(tmp_path):
+    """save_pretrained of a (tiny) Qwen3VLForConditionalGeneration -> our Reasoner class reads config and safetensors,
+    gives the same next-token logits for text and for a prompt with an image, and exports the text tower back."""
+    from cosmos_b200.hf import Cosmos3ReasonerForConditionalGeneration
+    cfg = hfc.Qwen3VLConfig(text_config=TEXT, vision_config=VISION, image_token_id=290, video_token_id=291,
+                            vision_start_token_id=292, vision_end_token_id=293, tie_word_embeddings=False)
+    hf = hfm.Qwen3VLForConditionalGeneration(cfg).eval()
+    _randomise(hf)
+    hf.save_pretrained(tmp_path / "qwen", safe_serialization=True)
+    ours = Cosmos3ReasonerForConditionalGeneration.from_pretrained(str(tmp_path / "qwen"))
+    mc = ours.model.cfg
+    assert (mc.d_model, mc.n_layers, mc.vit_depth, mc.vit_deepstack, mc.mrope_section) == (64, 2, 3, (0, 2), (3, 3, 2))
+    ids = torch.randint(0, 280, (1, 9))
+    with torch.no_grad():
+        want = hf(input_ids=ids).logits
+        got = ours(ids)
+    assert (got - want).abs().max() < 5e-5
+    # prompt with one 64 x 96 image: 2 x 3 merged tokens
+    video = torch.rand(1, 3, 64, 96) * 2 - 1
+    ids = torch.tensor([[5, 6, 292] + [290] * 6 + [293, 7, 8, 9]])
+    pixels = hq.hf_image_patches(video, 16, 2, 2)
+    with torch.no_grad():
+        want = hf(input_ids=ids, pixel_values=pixels, image_grid_thw=torch.tensor([[1, 4, 6]]),
+                  mm_token_type_ids=(ids == 290).int()).logits[0, -1]
+        eng = ReasonerEngine(ours.model, ours.visual)
+        emb, grid, deep = ours.visual(video, return_deepstack=True)
+        vmask = ids == 290
+        logits, _ = eng.prefill(eng.embed(ids, emb, vmask), eng.positions(ids, vmask, [grid]), deep, vmask)
+    assert (logits[0] - want).abs().max() < 1e-4 and int(logits[0].argmax()) == int(want.argmax())
+    ours.save_qwen3vl(tmp_path / "export")
+    from cosmos_b200.ckpt import safetensors_io as sio
+    files = sio.tensor_files(tmp_path / "export")
+    key = "model.language_model.layers.1.mlp.down_proj.weight"
+    assert key in files and torch.equal(sio.open_reader(files[key]).get(key), hf.state_dict()[key])
