@@ -5,9 +5,9 @@ in cookbooks/cosmos3/generator/action/run_fd_with_cosmos_framework.ipynb:750-790
 at a LeRobot v3 tree (`meta/info.json`, `data/chunk-*/file-*.parquet`, `videos/<camera>/...`);
 item keys are `action [chunk, 10]`, `video [C, T, H, W] uint8`, `conditioning_fps`, `viewpoint`,
 `ai_caption`. Actions are 10-D per transition: relative end-effector translation (3), rot6d (6),
-gripper (1) (reference action/README.md:29-41). Video decoding uses this package's media reader,
-so AV1 files need an ffmpeg binary; without one, items carry `video=None` and the rest of the
-sample (actions, caption, timing) is still served.
+gripper (1) (reference action/README.md:29-41). Video decoding uses this package's media reader (OpenCV's
+bundled H.264 / AV1 decoders, else an ffmpeg binary), seeking to the item's first frame; on a host with neither,
+items carry `video=None` and the rest of the sample (actions, caption, timing) is still served.
 """
 from __future__ import annotations
 
@@ -111,10 +111,10 @@ class DROIDLeRobotDataset:
             if not files:
                 continue
             try:
-                frames, _ = media.read_video(files[0], max_frames=t0 + self.chunk + 1)
+                frames, _ = media.read_video(files[0], max_frames=self.chunk + 1, start=t0)
             except Exception:  # noqa: BLE001 - codec not decodable on this host
                 continue
-            views.append(frames[t0:t0 + self.chunk + 1])
+            views.append(frames)
         if not views:
             return None
         n = min(v.shape[0] for v in views)

@@ -46,10 +46,11 @@ def write_image(path, frame: np.ndarray) -> None:
     Image.fromarray(np.ascontiguousarray(frame)).save(path)
 
 
-def read_video(path, max_frames: Optional[int] = None, size: Optional[Tuple[int, int]] = None
+def read_video(path, max_frames: Optional[int] = None, size: Optional[Tuple[int, int]] = None, start: int = 0
                ) -> Tuple[np.ndarray, float]:
-    """-> (frames [T, H, W, 3] uint8, fps). Supports .npy/.npz frame arrays, image files (1 frame),
-    Motion-JPEG MP4 natively, and anything else through ffmpeg when available."""
+    """-> (frames [T, H, W, 3] uint8, fps), at most `max_frames` frames from frame `start` on. Supports .npy/.npz
+    frame arrays, image files (1 frame), this package's Motion-JPEG MP4 natively, other codecs (H.264, HEVC,
+    AV1, ...) through OpenCV's bundled decoders (which seek to `start`), else through an ffmpeg binary."""
     from PIL import Image
 
     path = Path(path)
@@ -62,17 +63,59 @@ def read_video(path, max_frames: Optional[int] = None, size: Optional[Tuple[int,
     elif suffix in (".png", ".jpg", ".jpeg", ".bmp", ".webp"):
         frames, fps = read_image(path)[None], 1.0
     else:
+        want = None if max_frames is None else start + max_frames
         try:
-            frames, fps = mp4.read_mp4_mjpeg(path, max_frames)
+            frames, fps = mp4.read_mp4_mjpeg(path, want)
         except ValueError:
-            if not have_ffmpeg():
-                raise
-            frames, fps = _ffmpeg_read(path, max_frames)
+            # not one of this package's own Motion-JPEG files: OpenCV's bundled decoders (H.264, HEVC, AV1, ...)
+            # when OpenCV is installed, else the ffmpeg binary
+            got = _opencv_read(path, max_frames, start)
+            if got is not None:
+                start = 0                      # already skipped by seeking
+            else:
+                if not have_ffmpeg():
+                    raise
+                got = _ffmpeg_read(path, want)
+            frames, fps = got
+    if start:
+        frames = frames[start:]
     if max_frames is not None:
         frames = frames[:max_frames]
     if size is not None and (frames.shape[2], frames.shape[1]) != tuple(size):
         frames = np.stack([np.asarray(_resize_center_crop(Image.fromarray(f), size)) for f in frames])
     return frames, fps
+
+
+def _opencv_read(path, max_frames, start: int = 0) -> Optional[Tuple[np.ndarray, float]]:
+    """Decodes a video with OpenCV's FFmpeg backend -> (frames RGB uint8, fps); None when OpenCV is missing or
+    cannot open the file."""
+    try:
+        import cv2
+    except ImportError:
+        return None
+    cap = cv2.VideoCapture(str(path))
+    try:
+        if not cap.isOpened():
+            return None
+        fps = float(cap.get(cv2.CAP_PROP_FPS)) or 24.0
+        if start:
+            cap.set(cv2.CAP_PROP_POS_FRAMES, int(start))
+            if int(cap.get(cv2.CAP_PROP_POS_FRAMES)) != int(start):   # container without an index: decode and drop
+                cap.set(cv2.CAP_PROP_POS_FRAMES, 0)
+                for _ in range(int(start)):
+                    if not cap.grab():
+                        break
+        frames = []
+        while max_frames is None or len(frames) < max_frames:
+            ok, bgr = cap.read()
+            if not ok:
+                break
+            frames.append(bgr[:, :, ::-1])
+    finally:
+        cap.release()
+    if not frames:
+        return None
+    return np.ascontiguousarray(np.stack(frames)), fps
 
 
 def _ffmpeg_read(path, max_frames):

@@ -256,3 +256,41 @@ def test_truncated_and_damaged_spec_files_are_reported_not_half_read(tmp_path):
         load_specs(arr)
     with pytest.raises(SpecError, match="not found"):
         load_specs(tmp_path / "missing.json")
+
+
+def test_foreign_codecs_are_decoded_through_opencv_with_seeking(tmp_path):
+    """A clip that is not this package's own Motion-JPEG layout (here MPEG-4 part 2 written by OpenCV) goes through
+    OpenCV's decoders; `start` seeks instead of decoding from the beginning."""
+    cv2 = pytest.importorskip("cv2")
+    from cosmos_b200.io import media
+    path = tmp_path / "clip.mp4"
+    w = cv2.VideoWriter(str(path), cv2.VideoWriter_fourcc(*"mp4v"), 12.0, (96, 64))
+    if not w.isOpened():
+        pytest.skip("this OpenCV build has no MPEG-4 encoder")
+    for t in range(20):
+        frame = np.full((64, 96, 3), 16, dtype=np.uint8)
+        frame[:, 4 * t:4 * t + 8] = (0, 0, 255)             # BGR: a red bar that moves right
+        w.write(frame)
+    w.release()
+    frames, fps = media.read_video(path)
+    assert frames.shape == (20, 64, 96, 3) and abs(fps - 12.0) < 1e-3
+    red = frames[..., 0].astype(int) - frames[..., 2].astype(int)
+    cols = [int(red[t].mean(0).argmax()) for t in range(20)]
+    assert all(4 * t <= cols[t] < 4 * t + 8 for t in range(20))                       # RGB order, frame order
+    tail, _ = media.read_video(path, max_frames=3, start=15)
+    assert tail.shape[0] == 3 and np.abs(tail.astype(int) - frames[15:18].astype(int)).max() <= 2
+    small, _ = media.read_video(path, max_frames=2, size=(48, 32))
+    assert small.shape == (2, 32, 48, 3)
+
+
+@pytest.mark.skipif(not REF.exists(), reason="reference assets not mounted")
+def test_droid_lerobot_dataset_items_carry_the_decoded_views():
+    pytest.importorskip("cv2")
+    from cosmos_b200.data.vfm.action.datasets import DROIDLeRobotDataset
+
+    root = REF / "cookbooks/cosmos3/generator/action/assets/droid_lerobot_example"
+    ds = DROIDLeRobotDataset(root, action_chunk_size=16)
+    a, b = ds[0], ds[3]
+    assert a["video"].shape[:2] == (3, 17) and a["video"].shape[2] == 360 and a["video"].shape[3] % 640 == 0
+    assert a["video"].dtype == np.uint8 and b["frame_index"] == 48
+    assert np.abs(a["video"].astype(int) - b["video"].astype(int)).mean() > 0.1      # another part of the episode
