@@ -229,3 +229,21 @@ def test_chat_video_with_processor_kwargs(client, tmp_path):
     assert smart_resize(96, 128, 32, 1024, 4096) == (32, 64)
     assert smart_resize(720, 1280, 32, 3136, 262144) == (384, 672)
     assert smart_resize(20, 20, 32, 3136, 10 ** 7) == (64, 64)
+
+
+def test_chat_reads_a_real_h264_clip_from_the_reference_assets(client):
+    """`video_url` pointing at one of the reference's own example clips (H.264), sampled at 4 frames per second as
+    its notebooks do."""
+    pytest.importorskip("cv2")
+    from pathlib import Path
+    clip = Path(__file__).resolve().parents[2] / "reference" / "cookbooks" / "cosmos3" / "reasoner" / "assets" / "video_caption.mp4"
+    if not clip.exists():
+        pytest.skip("reference assets not mounted")
+    body = {"max_tokens": 3, "temperature": 0.0, "mm_processor_kwargs": {"fps": 4, "do_sample_frames": True},
+            "messages": [{"role": "system", "content": "You are a helpful assistant."},
+                         {"role": "user", "content": [{"type": "video_url", "video_url": {"url": f"file://{clip}"}},
+                                                      {"type": "text", "text": "What's happening in this video?"}]}]}
+    r = client.post("/v1/chat/completions", json=body)
+    assert r.status_code == 200, r.text
+    usage = r.json()["usage"]
+    assert usage["prompt_tokens"] > 60 and 1 <= usage["completion_tokens"] <= 3      # vision rows of several frames
