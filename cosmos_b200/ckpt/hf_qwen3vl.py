@@ -124,6 +124,55 @@ def vision_state_from_hf(state: Mapping[str, torch.Tensor]) -> Dict[str, torch.T
     return out
 
 
+def export_vision_weights(vit, prefix: str = "model.visual.") -> Dict[str, torch.Tensor]:
+    """The vision encoder in the Qwen3-VL vision layout (inverse of `vision_state_from_hf`)."""
+    c = vit.cfg
+    inv_block = {v: k for k, v in _VISION_BLOCK.items()}
+    out: Dict[str, torch.Tensor] = {}
+    for k, t in vit.state_dict().items():
+        t = t.detach().clone()
+        parts = k.split(".")
+        if k == "patch.weight":
+            out[prefix + "patch_embed.proj.weight"] = t.view(t.shape[0], 3, c.vit_temporal_patch, c.vit_patch, c.vit_patch)
+        elif k == "patch.bias":
+            out[prefix + "patch_embed.proj.bias"] = t
+        elif k == "pos":
+            out[prefix + "pos_embed.weight"] = t
+        elif parts[0] == "blocks":
+            out[f"{prefix}blocks.{parts[1]}.{inv_block[parts[2]]}.{parts[3]}"] = t
+        elif parts[0] == "norm":
+            out[f"{prefix}merger.norm.{parts[1]}"] = t
+        elif parts[0] == "merge":
+            out[f"{prefix}merger.linear_fc{1 if parts[1] == '0' else 2}.{parts[2]}"] = t
+        elif parts[0] == "deepstack_norm":
+            out[f"{prefix}deepstack_merger_list.{parts[1]}.norm.{parts[2]}"] = t
+        elif parts[0] == "deepstack_merge":
+            out[f"{prefix}deepstack_merger_list.{parts[1]}.linear_fc{1 if parts[2] == '0' else 2}.{parts[3]}"] = t
+        else:
+            raise KeyError(f"no Qwen3-VL name for '{k}'")
+    return out
+
+
+def hf_config_dict(cfg: MoTConfig, token_ids: Optional[Dict[str, int]] = None) -> Dict[str, object]:
+    """`config.json` of a Qwen3-VL checkpoint with this model's shapes. `token_ids` names the ids of
+    image_token_id / video_token_id / vision_start_token_id / vision_end_token_id in the tokenizer in use."""
+    text = dict(model_type="qwen3_vl_text", vocab_size=cfg.vocab_size, hidden_size=cfg.d_model, intermediate_size=cfg.ffn_dim,
+                num_hidden_layers=cfg.n_layers, num_attention_heads=cfg.n_heads, num_key_value_heads=cfg.n_kv_heads,
+                head_dim=cfg.head_dim, rms_norm_eps=cfg.rms_eps, hidden_act="silu", attention_bias=False,
+                max_position_embeddings=262144, tie_word_embeddings=False,
+                rope_parameters={"rope_type": "default", "rope_theta": float(cfg.rope_theta),
+                                 "mrope_section": list(cfg.mrope_section), "mrope_interleaved": True})
+    vision = dict(model_type="qwen3_vl", depth=cfg.vit_depth, hidden_size=cfg.vit_hidden, intermediate_size=cfg.vit_ffn or 4 * cfg.vit_hidden,
+                  num_heads=cfg.vit_heads, patch_size=cfg.vit_patch, temporal_patch_size=cfg.vit_temporal_patch,
+                  spatial_merge_size=cfg.vit_spatial_merge, out_hidden_size=cfg.d_model, in_channels=3,
+                  num_position_embeddings=cfg.vit_pos_side ** 2, deepstack_visual_indexes=list(cfg.vit_deepstack),
+                  hidden_act="gelu_pytorch_tanh")
+    doc: Dict[str, object] = dict(model_type="qwen3_vl", architectures=["Qwen3VLForConditionalGeneration"], text_config=text,
+                                  vision_config=vision, tie_word_embeddings=False)
+    doc.update(token_ids or {})
+    return doc
+
+
 def load_vision_weights(vit, state: Mapping[str, torch.Tensor], strict: bool = True) -> None:
     vit.load_state_dict(vision_state_from_hf(state), strict=strict)
 

@@ -101,11 +101,19 @@ class Cosmos3ReasonerForConditionalGeneration(PreTrainedModel):
         hq.load_checkpoint_dir(m.model, m.visual if vision else None, model_dir)
         return m.eval()
 
-    def save_qwen3vl(self, out_dir) -> None:
-        """Writes the AR tower in the Qwen3-VL text layout (safetensors) for runtimes that read that format."""
+    def save_qwen3vl(self, out_dir, token_ids: Optional[dict] = None) -> None:
+        """Writes a checkpoint directory in the Hugging Face Qwen3-VL layout (`config.json` + safetensors with the
+        text tower, LM head and vision tower) that `transformers` and engines built on it load as
+        `Qwen3VLForConditionalGeneration`."""
+        import json
+        from pathlib import Path
+
         from .ckpt import hf_qwen3vl as hq
         from .ckpt import safetensors_io as sio
-        sio.save_sharded(hq.export_text_weights(self.model), out_dir)
+        state = hq.export_text_weights(self.model)
+        state.update(hq.export_vision_weights(self.visual))
+        sio.save_sharded(state, out_dir)
+        (Path(out_dir) / "config.json").write_text(json.dumps(hq.hf_config_dict(self.model.cfg, token_ids), indent=1))
 
     def forward(self, input_ids: torch.Tensor, **_):
         """Teacher-forced logits [B, S, V] of text-only input (no KV reuse)."""

@@ -142,3 +142,28 @@ def test_reasoner_class_loads_a_qwen3vl_checkpoint_directory(tmp_path):
     files = sio.tensor_files(tmp_path / "export")
     key = "model.language_model.layers.1.mlp.down_proj.weight"
     assert key in files and torch.equal(sio.open_reader(files[key]).get(key), hf.state_dict()[key])
+
+
+def test_exported_reasoner_loads_in_transformers_and_gives_the_same_logits(tmp_path):
+    """The other direction: a Reasoner of this framework (random weights) saved in the Qwen3-VL layout is loaded by
+    `transformers` itself and agrees on text and on an image prompt."""
+    from cosmos_b200.hf import Cosmos3ReasonerConfig, Cosmos3ReasonerForConditionalGeneration
+    over = dict(n_layers=2, d_model=64, n_heads=4, n_kv_heads=2, head_dim=16, ffn_dim=96, vocab_size=320, mrope_section=[3, 3, 2],
+                vit_depth=2, vit_hidden=32, vit_heads=2, vit_ffn=40, vit_pos_side=5, vit_deepstack=[1])
+    ours = Cosmos3ReasonerForConditionalGeneration(Cosmos3ReasonerConfig("tiny", over)).eval()
+    _randomise(ours.visual)
+    ours.save_qwen3vl(tmp_path / "out", dict(image_token_id=290, video_token_id=291, vision_start_token_id=292, vision_end_token_id=293))
+    hf = hfm.Qwen3VLForConditionalGeneration.from_pretrained(str(tmp_path / "out"), torch_dtype=torch.float32).eval()
+    ids = torch.randint(0, 280, (1, 7))
+    with torch.no_grad():
+        assert (hf(input_ids=ids).logits - ours(ids)).abs().max() < 5e-5
+    video = torch.rand(2, 3, 96, 64) * 2 - 1
+    ids = torch.tensor([[9, 292] + [290] * 6 + [293, 4, 3]])
+    with torch.no_grad():
+        want = hf(input_ids=ids, pixel_values=hq.hf_image_patches(video, 16, 2, 2), image_grid_thw=torch.tensor([[1, 6, 4]]),
+                  mm_token_type_ids=(ids == 290).int()).logits[0, -1]
+        eng = ReasonerEngine(ours.model, ours.visual)
+        emb, grid, deep = ours.visual(video, return_deepstack=True)
+        vmask = ids == 290
+        logits, _ = eng.prefill(eng.embed(ids, emb, vmask), eng.positions(ids, vmask, [grid]), deep, vmask)
+    assert grid == (1, 3, 2) and (logits[0] - want).abs().max() < 1e-4
