@@ -200,3 +200,12 @@ def hf_image_patches(video: torch.Tensor, patch: int, temporal_patch: int, merge
     gh, gw = hh // patch, ww // patch
     x = video.view(t, temporal_patch, c, gh // merge, merge, patch, gw // merge, merge, patch)
     return x.permute(0, 3, 6, 4, 7, 2, 1, 5, 8).reshape(t * gh * gw, c * temporal_patch * patch * patch)
+
+
+def frames_from_hf_patches(pixels: torch.Tensor, grid_thw, patch: int, temporal_patch: int, merge: int) -> torch.Tensor:
+    """Inverse of `hf_image_patches` for one image / clip: processor rows [t * gh * gw, C * tp * p * p] with their
+    grid (t, gh, gw) -> frames [t * tp, 3, gh * p, gw * p]."""
+    t, gh, gw = (int(v) for v in grid_thw)
+    x = pixels.reshape(t, gh // merge, gw // merge, merge, merge, 3, temporal_patch, patch, patch)
+    x = x.permute(0, 6, 5, 1, 3, 7, 2, 4, 8)
+    return x.reshape(t * temporal_patch, 3, gh * patch, gw * patch)

@@ -125,16 +125,35 @@ class Cosmos3ReasonerForConditionalGeneration(PreTrainedModel):
 
     @torch.no_grad()
     def generate(self, input_ids, pixel_values: Optional[torch.Tensor] = None, image_token_id: Optional[int] = None,
+                 image_grid_thw: Optional[torch.Tensor] = None,
                  max_new_tokens: int = 64, do_sample: bool = False, temperature: float = 0.7, top_p: float = 0.8,
                  top_k: int = 20, repetition_penalty: float = 1.0, presence_penalty: float = 0.0,
                  eos_token_id: Optional[Sequence[int]] = None, seed: Optional[int] = None, **_) -> torch.Tensor:
-        """input_ids [1, S] (or a list); `pixel_values` [T, 3, H, W] in [-1, 1] fills the positions that hold
+        """input_ids [1, S] (or a list); `pixel_values` [T, 3, H, W] in [-1, 1] (one image / clip) or the patch rows
+        of a `transformers` Qwen3-VL processor together with `image_grid_thw` fill the positions that hold
         `image_token_id`. Returns prompt + completion ids [1, S + n]."""
         ids = input_ids[0].tolist() if torch.is_tensor(input_ids) else list(input_ids)
         eng = ReasonerEngine(self.model, self.visual)
         ve = grids = deep = None
-        if pixel_values is not None:
-            ve, grid, deep = self.visual(pixel_values.to(next(self.visual.parameters()).dtype), return_deepstack=True)
+        vdt = next(self.visual.parameters()).dtype
+        if pixel_values is not None and pixel_values.dim() == 2:
+            # processor layout of `transformers`: patch rows of all images plus `image_grid_thw` [n, 3]
+            from .ckpt.hf_qwen3vl import frames_from_hf_patches
+            cfg = self.model.cfg
+            if image_grid_thw is None:
+                raise ValueError("pixel_values in patch-row layout need image_grid_thw")
+            embs, grids, deeps, row = [], [], [], 0
+            for g in image_grid_thw.tolist():
+                n = int(g[0] * g[1] * g[2])
+                frames = frames_from_hf_patches(pixel_values[row:row + n], g, cfg.vit_patch, cfg.vit_temporal_patch,
+                                                cfg.vit_spatial_merge)
+                row += n
+                e, grid, d = self.visual(frames.to(vdt), return_deepstack=True)
+                embs.append(e), grids.append(grid), deeps.append(d)
+            ve = torch.cat(embs)
+            deep = [torch.cat([d[k] for d in deeps]) for k in range(len(deeps[0]))] if deeps[0] else None
+        elif pixel_values is not None:
+            ve, grid, deep = self.visual(pixel_values.to(vdt), return_deepstack=True)
             grids = [grid]
         dc = DecodingConfig(max_new_tokens=max_new_tokens, do_sample=do_sample, temperature=temperature, top_p=top_p,
                             top_k=top_k, repetition_penalty=repetition_penalty, presence_penalty=presence_penalty,

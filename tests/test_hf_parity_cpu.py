@@ -167,3 +167,25 @@ def test_exported_reasoner_loads_in_transformers_and_gives_the_same_logits(tmp_p
         vmask = ids == 290
         logits, _ = eng.prefill(eng.embed(ids, emb, vmask), eng.positions(ids, vmask, [grid]), deep, vmask)
     assert grid == (1, 3, 2) and (logits[0] - want).abs().max() < 1e-4
+
+
+def test_generate_takes_processor_style_patch_rows(tmp_path):
+    """Greedy continuation of a two-image prompt: our class fed with `transformers`-processor inputs (patch rows +
+    image_grid_thw) produces the tokens `transformers`' own generate produces from the same checkpoint."""
+    from cosmos_b200.hf import Cosmos3ReasonerForConditionalGeneration
+    cfg = hfc.Qwen3VLConfig(text_config=TEXT, vision_config=VISION, image_token_id=290, video_token_id=291,
+                            vision_start_token_id=292, vision_end_token_id=293, tie_word_embeddings=False)
+    hf = hfm.Qwen3VLForConditionalGeneration(cfg).eval()
+    _randomise(hf)
+    hf.save_pretrained(tmp_path / "qwen", safe_serialization=True)
+    ours = Cosmos3ReasonerForConditionalGeneration.from_pretrained(str(tmp_path / "qwen"))
+    a, b = torch.rand(1, 3, 64, 96) * 2 - 1, torch.rand(1, 3, 64, 64) * 2 - 1
+    pixels = torch.cat([hq.hf_image_patches(a, 16, 2, 2), hq.hf_image_patches(b, 16, 2, 2)])
+    grids = torch.tensor([[1, 4, 6], [1, 4, 4]])
+    assert torch.allclose(hq.frames_from_hf_patches(pixels[:24], grids[0], 16, 2, 2)[:1], a)       # the inverse layout map
+    ids = torch.tensor([[5, 292] + [290] * 6 + [293, 7, 292] + [290] * 4 + [293, 8, 9]])
+    got = ours.generate(ids, pixel_values=pixels, image_grid_thw=grids, image_token_id=290, max_new_tokens=5)
+    with torch.no_grad():
+        want = hf.generate(input_ids=ids, pixel_values=pixels, image_grid_thw=grids, mm_token_type_ids=(ids == 290).int(),
+                           attention_mask=torch.ones_like(ids), max_new_tokens=5, do_sample=False, eos_token_id=None, pad_token_id=0)
+    assert got.shape == (1, ids.shape[1] + 5) and torch.equal(got, want)
