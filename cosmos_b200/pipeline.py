@@ -106,6 +106,21 @@ class Cosmos3OmniPipeline:
             device = device_map
         from .ckpt.resolve import resolve_checkpoint_dir
         ckpt_dir = resolve_checkpoint_dir(name_or_path)   # a directory, or a name with a snapshot in the local hub cache
+        qwen_dir = None
+        if ckpt_dir is None and Path(name_or_path).is_dir() and (Path(name_or_path) / "config.json").exists():
+            doc = json.loads((Path(name_or_path) / "config.json").read_text())
+            if "text_config" in doc:
+                # a Hugging Face Qwen3-VL checkpoint: the Reasoner side (AR tower + vision encoder) alone
+                from types import SimpleNamespace
+
+                from .ckpt import hf_qwen3vl as hq
+                qwen_dir = Path(name_or_path)
+                text = SimpleNamespace(**doc["text_config"])
+                text.rms_norm_eps = getattr(text, "rms_norm_eps", 1e-6)
+                vis = doc.get("vision_config")
+                config_overrides = {**hq.config_kwargs_from_hf(text, SimpleNamespace(**vis) if vis else None),
+                                    **(config_overrides or {})}
+                name_or_path, towers = "tiny", ("ar",)
         if ckpt_dir is not None and (ckpt_dir / "transformer" / "config.json").exists():
             cfg = MoTConfig(**{k: (tuple(v) if isinstance(v, list) else v) for k, v in
                                json.loads((ckpt_dir / "transformer" / "config.json").read_text()).items()})
@@ -122,11 +137,38 @@ class Cosmos3OmniPipeline:
                 sio.load_into(ckpt_dir / "vae", dict(vae.state_dict()))
             if (ckpt_dir / "sound_tokenizer").is_dir():
                 sio.load_into(ckpt_dir / "sound_tokenizer", dict(snd.state_dict()))
+        if qwen_dir is not None:
+            hq.load_checkpoint_dir(model, None, qwen_dir)
         model.eval(), vae.eval(), snd.eval()
-        tok = load_tokenizer(str(ckpt_dir) if ckpt_dir else None, cfg.vocab_size)
+        tok = load_tokenizer(str(ckpt_dir or qwen_dir) if (ckpt_dir or qwen_dir) else None, cfg.vocab_size)
         guard = safety_checker if safety_checker is not None else Guardrails()
         eng = GeneratorEngine(model, **(engine_kwargs or {}))
-        return cls(model, vae, snd, tok, None, guard, enable_safety_checker, eng)
+        pipe = cls(model, vae, snd, tok, None, guard, enable_safety_checker, eng)
+        pipe._vision_source = ckpt_dir or qwen_dir
+        return pipe
+
+    def vision_encoder(self):
+        """The Reasoner's vision encoder for this checkpoint (built on first use, on the transformer's device and
+        dtype): weights from `vision_encoder/` of a checkpoint in this package's layout or from the vision tower of a
+        Qwen3-VL checkpoint directory; seeded random weights when the checkpoint has none."""
+        if getattr(self, "_vit", None) is None:
+            from .models.vit import VisionEncoder
+            p = next(self.transformer.parameters())
+            torch.manual_seed(0)
+            vit = VisionEncoder(self.cfg)
+            src = getattr(self, "_vision_source", None)
+            if src is not None and (Path(src) / "vision_encoder").is_dir():
+                from .ckpt import safetensors_io as sio
+                sio.load_into(Path(src) / "vision_encoder", dict(vit.state_dict()))
+            elif src is not None and (Path(src) / "config.json").exists() and not (Path(src) / "transformer").is_dir():
+                from .ckpt import hf_qwen3vl as hq
+                from .ckpt import safetensors_io as sio
+                files = sio.tensor_files(src)
+                state = {k: sio.open_reader(f).get(k) for k, f in files.items() if "visual." in k}
+                if state:
+                    hq.load_vision_weights(vit, state)
+            self._vit = vit.to(device=p.device, dtype=p.dtype).eval()
+        return self._vit
 
     def save_pretrained(self, out_dir) -> None:
         from .ckpt import safetensors_io as sio
@@ -134,6 +176,8 @@ class Cosmos3OmniPipeline:
         sio.save_model(self.transformer, out / "transformer")
         sio.save_sharded(dict(self.vae.state_dict()), out / "vae")
         sio.save_sharded(dict(self.sound_tokenizer.state_dict()), out / "sound_tokenizer")
+        if getattr(self, "_vit", None) is not None or getattr(self, "_vision_source", None) is not None:
+            sio.save_sharded(dict(self.vision_encoder().state_dict()), out / "vision_encoder")
         if hasattr(self.tokenizer, "hf"):  # a checkpoint's own tokenizer travels with it
             self.tokenizer.hf.save_pretrained(str(out / "tokenizer"))
         (out / "scheduler").mkdir(parents=True, exist_ok=True)

@@ -302,7 +302,7 @@ def main(argv: Optional[List[str]] = None) -> int:
     rs = [s for s in mine if s.model_mode == "reasoner"]
     if rs and world == 1 and (use_cuda or len(rs) > 1) and os.environ.get("COSMOS_REASONER_SINGLE") != "1":
         from ..models.vit import VisionEncoder
-        vit = VisionEncoder(pipe.cfg).to(device=device, dtype=dtype).eval()
+        vit = pipe.vision_encoder()
         for rec in run_reasoner_batch(pipe, vit, rs, out_root, is_writer, device):
             records.append(rec)
             if is_writer:
@@ -316,7 +316,7 @@ def main(argv: Optional[List[str]] = None) -> int:
             if reasoner is None:
                 from ..models.reasoner import ReasonerEngine
                 from ..models.vit import VisionEncoder
-                vit = VisionEncoder(pipe.cfg).to(device=device, dtype=dtype).eval()
+                vit = pipe.vision_encoder()
                 reasoner = ReasonerEngine(pipe.transformer, vit)
             rec = run_reasoner_sample(reasoner, pipe.tokenizer, vit, spec, out_dir, is_writer, device)
         else:

@@ -569,7 +569,6 @@ def main(argv=None) -> int:
     import uvicorn
 
     from ..models.reasoner import ReasonerEngine
-    from ..models.vit import VisionEncoder
     from ..pipeline import Cosmos3OmniPipeline
 
     if torch.cuda.is_available():
@@ -578,7 +577,7 @@ def main(argv=None) -> int:
     dtype = torch.bfloat16 if (dev and args.dtype == "bf16") else torch.float32
     pipe = Cosmos3OmniPipeline.from_pretrained(args.model, torch_dtype=dtype, device_map=dev,
                                                enable_safety_checker=not args.no_guardrails)
-    vit = VisionEncoder(pipe.cfg).to(device=pipe.device, dtype=dtype).eval()
+    vit = pipe.vision_encoder()
     worker = None
     world = int(os.environ.get("WORLD_SIZE", "1"))
     group = None

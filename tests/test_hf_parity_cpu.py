@@ -189,3 +189,33 @@ def test_generate_takes_processor_style_patch_rows(tmp_path):
         want = hf.generate(input_ids=ids, pixel_values=pixels, image_grid_thw=grids, mm_token_type_ids=(ids == 290).int(),
                            attention_mask=torch.ones_like(ids), max_new_tokens=5, do_sample=False, eos_token_id=None, pad_token_id=0)
     assert got.shape == (1, ids.shape[1] + 5) and torch.equal(got, want)
+
+
+def test_pipeline_opens_a_qwen3vl_directory_as_a_reasoner_only_checkpoint(tmp_path):
+    """`--checkpoint-path <Qwen3-VL dir>`: AR tower and vision encoder come from the checkpoint (no DM tower is built),
+    the server answers a chat with an image from it, and save_pretrained / from_pretrained keep the vision encoder."""
+    from cosmos_b200.pipeline import Cosmos3OmniPipeline
+    cfg = hfc.Qwen3VLConfig(text_config=TEXT, vision_config=VISION, image_token_id=290, video_token_id=291,
+                            vision_start_token_id=292, vision_end_token_id=293, tie_word_embeddings=False)
+    hf = hfm.Qwen3VLForConditionalGeneration(cfg).eval()
+    _randomise(hf)
+    hf.save_pretrained(tmp_path / "qwen", safe_serialization=True)
+    pipe = Cosmos3OmniPipeline.from_pretrained(str(tmp_path / "qwen"), torch_dtype=torch.float32, vae_widths=(8, 16, 16, 16))
+    assert pipe.transformer.has_ar and not hasattr(pipe.transformer, "dm") and pipe.cfg.vit_deepstack == (0, 2)
+    vit = pipe.vision_encoder()
+    assert vit is pipe.vision_encoder()                                           # built once
+    sd = hf.state_dict()
+    assert torch.equal(vit.pos, sd["model.visual.pos_embed.weight"])
+    assert torch.equal(pipe.transformer.embed, sd["model.language_model.embed_tokens.weight"])
+    eng = ReasonerEngine(pipe.transformer, vit)
+    from cosmos_b200.config import DecodingConfig
+    ids = [5, 6, 7, 8, 9, 10]
+    new, _ = eng.generate(ids, DecodingConfig(max_new_tokens=4, do_sample=False, presence_penalty=0.0), ())
+    with torch.no_grad():
+        want = hf.generate(input_ids=torch.tensor([ids]), attention_mask=torch.ones(1, 6, dtype=torch.long), max_new_tokens=4,
+                           do_sample=False, eos_token_id=None, pad_token_id=0)
+    assert new == want[0, 6:].tolist()
+    pipe.save_pretrained(tmp_path / "ours")
+    again = Cosmos3OmniPipeline.from_pretrained(str(tmp_path / "ours"), torch_dtype=torch.float32, vae_widths=(8, 16, 16, 16),
+                                                towers=("ar",))
+    assert torch.equal(again.vision_encoder().pos, vit.pos) and torch.equal(again.transformer.embed, pipe.transformer.embed)
