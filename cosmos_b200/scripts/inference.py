@@ -159,7 +159,7 @@ def _reasoner_prompt(tokenizer, vit, cfg, spec: InferenceSpec, device):
 
     content, vision_embeds, grids, n_vis, deep = [], None, [], [], None
     if spec.vision_path:
-        frames, _ = media.read_video(spec.resolve(spec.vision_path), max_frames=16)
+        frames, src_fps = media.read_video(spec.resolve(spec.vision_path), max_frames=16)
         unit = cfg.vit_patch * cfg.vit_spatial_merge
         h = min(max(unit, frames.shape[1] // unit * unit), 14 * unit)
         w = min(max(unit, frames.shape[2] // unit * unit), 14 * unit)
@@ -168,11 +168,17 @@ def _reasoner_prompt(tokenizer, vit, cfg, spec: InferenceSpec, device):
         vid = CausalVideoVAE.from_uint8(torch.from_numpy(fr)[None])[0].permute(1, 0, 2, 3).to(device)
         with torch.no_grad():
             vision_embeds, grid, deep = vit(vid, return_deepstack=True)
-        grids, n_vis = [grid], [grid[0] * grid[1] * grid[2]]
-        content.append({"type": "image_url" if frames.shape[0] == 1 else "video_url"})
+        is_video = frames.shape[0] > 1
+        if is_video:   # one time-stamped vision segment (and rotary grid) per temporal group
+            from ..utils.tokenizer import video_layout
+            times = (np.arange(frames.shape[0]) / max(float(src_fps), 1e-6)).tolist()
+            grids, n_vis = [(1, grid[1], grid[2])] * grid[0], [video_layout(grid, times, cfg.vit_temporal_patch)]
+        else:
+            grids, n_vis = [grid], [grid[0] * grid[1] * grid[2]]
+        content.append({"type": "video_url" if is_video else "image_url"})
     content.append({"type": "text", "text": spec.prompt_text()})
     ids = tokenizer.apply_chat_template([{"role": "user", "content": content}], True, n_vis)
-    pad_id = tokenizer.video_pad_id if (grids and grids[0][0] > 1) else tokenizer.image_pad_id
+    pad_id = tokenizer.video_pad_id if (spec.vision_path and is_video) else tokenizer.image_pad_id
     return ids, vision_embeds, grids, pad_id, deep
 
 
@@ -222,7 +228,7 @@ def run_reasoner_sample(engine, tokenizer, vit, spec: InferenceSpec, out_dir: Pa
     messages_content = []
     vision_embeds, grids, n_vis, deep = None, [], [], None
     if spec.vision_path:
-        frames, _ = media.read_video(spec.resolve(spec.vision_path), max_frames=16)
+        frames, src_fps = media.read_video(spec.resolve(spec.vision_path), max_frames=16)
         unit = engine.cfg.vit_patch * engine.cfg.vit_spatial_merge
         h = max(unit, frames.shape[1] // unit * unit)
         w = max(unit, frames.shape[2] // unit * unit)

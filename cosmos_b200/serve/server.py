@@ -38,6 +38,7 @@ import torch
 
 from ..config import DecodingConfig, SamplingConfig
 from ..io import media, mp4
+from ..utils.tokenizer import video_layout
 
 try:  # module-level so that FastAPI can resolve the (string) annotations of the route handlers
     from fastapi import FastAPI, HTTPException, Request
@@ -298,6 +299,7 @@ class Cosmos3Server:
         extra = {k: body[k] for k in ("mm_processor_kwargs", "media_io_kwargs") if k in body}
         extra.update(body.get("extra_body") or {})
         vision_embeds, grids, n_vis, norm_msgs, deep = [], [], [], [], []
+        has_video = False
         dev = self.pipe.device
         for m in messages:
             content = m["content"]
@@ -306,12 +308,18 @@ class Cosmos3Server:
                 for part in content:
                     kind = part.get("type")
                     if kind in ("image_url", "video_url"):
-                        frames = self._load_media(part[kind]["url"], kind == "video_url", extra)
+                        frames, times = self._load_media(part[kind]["url"], kind == "video_url", extra)
                         emb, grid, ds = self._encode_vision(frames, dev, (extra.get("mm_processor_kwargs") or {}).get("size"))
                         vision_embeds.append(emb)
                         deep.append(ds)
-                        grids.append(grid)
-                        n_vis.append(grid[0] * grid[1] * grid[2])
+                        if kind == "video_url":
+                            # one vision segment (and one rotary grid) per temporal group, each behind its time stamp
+                            has_video = True
+                            grids.extend([(1, grid[1], grid[2])] * grid[0])
+                            n_vis.append(video_layout(grid, times, self.pipe.cfg.vit_temporal_patch))
+                        else:
+                            grids.append(grid)
+                            n_vis.append(grid[0] * grid[1] * grid[2])
                     parts.append(part)
                 norm_msgs.append({"role": m["role"], "content": parts})
             else:
@@ -335,7 +343,7 @@ class Cosmos3Server:
         # DeepStack features of all media items, level by level
         ds = [torch.cat([d[k] for d in deep]) for k in range(len(deep[0]))] if deep and deep[0] else None
         # image and video pads share one mask here: every pad position takes the next vision row
-        pad_id = tok.video_pad_id if any(g[0] > 1 for g in grids) else tok.image_pad_id
+        pad_id = tok.video_pad_id if has_video else tok.image_pad_id
         if ve is not None and len({tok.image_pad_id, tok.video_pad_id}) == 2:
             ids = [pad_id if t in (tok.image_pad_id, tok.video_pad_id) else t for t in ids]
         if self.batch_engine is not None and dc.seed is None:
@@ -375,7 +383,7 @@ class Cosmos3Server:
                              "finish_reason": "stop" if out_ids and out_ids[-1] in (tok.eos_id, tok.eot_id) else "length"}],
                 "usage": {**usage, "total_tokens": usage["prompt_tokens"] + usage["completion_tokens"]}}
 
-    def _load_media(self, url: str, is_video: bool, extra: dict) -> np.ndarray:
+    def _load_media(self, url: str, is_video: bool, extra: dict):
         if url.startswith("data:"):
             raw = base64.b64decode(url.split(",", 1)[1])
             suffix = ".mp4" if is_video else ".png"
@@ -386,19 +394,20 @@ class Cosmos3Server:
         else:
             p = self._local(url)
         frames, src_fps = media.read_video(p)
+        idx = np.arange(len(frames))
         if is_video:
             vk = (extra.get("media_io_kwargs") or {}).get("video", {})
             mk = extra.get("mm_processor_kwargs") or {}
             if int(vk.get("num_frames", 0)) > 0:
                 idx = np.linspace(0, len(frames) - 1, int(vk["num_frames"])).round().astype(int)
-                frames = frames[idx]
             elif vk.get("num_frames") == -1 or mk.get("do_sample_frames") is False:
                 pass  # the client pre-sampled the clip: keep every frame
             else:
                 fps = float(vk.get("fps", mk.get("fps", 2)))
                 step = max(1, int(round(src_fps / max(fps, 1e-6))))
-                frames = frames[::step]
-        return frames[:32]
+                idx = idx[::step]
+        idx = idx[:32]
+        return frames[idx], (idx / max(float(src_fps), 1e-6)).tolist()   # frames and their times in the source clip
 
     def _encode_vision(self, frames: np.ndarray, dev, size: Optional[dict] = None):
         from PIL import Image

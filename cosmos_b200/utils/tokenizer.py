@@ -63,7 +63,9 @@ class ByteTokenizer:
     def apply_chat_template(self, messages: List[dict], add_generation_prompt: bool = True,
                             n_vision_tokens: Sequence[int] = ()) -> List[int]:
         """messages: [{'role', 'content'}], content a string or a list of parts with 'type' in
-        {'text', 'image_url', 'video_url'}; each media part expands to vision_start + pads + vision_end."""
+        {'text', 'image_url', 'video_url'}; each media part expands to vision_start + pads + vision_end.
+        `n_vision_tokens` has one entry per media part, in order: the number of (merged) vision tokens, or for a
+        clip `{"per_frame": tokens per temporal group, "timestamps": [seconds of every group]}` (see `video_layout`)."""
         ids: List[int] = []
         vis = list(n_vision_tokens)
         for m in messages:
@@ -79,13 +81,32 @@ class ByteTokenizer:
                     elif kind in ("image_url", "video_url", "image", "video"):
                         n = vis.pop(0) if vis else 0
                         pad = self.image_pad_id if kind.startswith("image") else self.video_pad_id
-                        ids += [self.special_ids["<|vision_start|>"]] + [pad] * n + [self.special_ids["<|vision_end|>"]]
+                        v0, v1 = self.special_ids["<|vision_start|>"], self.special_ids["<|vision_end|>"]
+                        if isinstance(n, dict):
+                            # a clip: one vision segment per temporal group, each after its time stamp
+                            # ("<1.5 seconds>"), which is how Qwen3-VL lays videos out
+                            for ts in n["timestamps"]:
+                                ids += self.encode(f"<{ts:.1f} seconds>") + [v0] + [pad] * int(n["per_frame"]) + [v1]
+                        else:
+                            ids += [v0] + [pad] * n + [v1]
                     else:
                         raise ValueError(f"unknown content part type {kind!r}")
             ids += self.encode("<|im_end|>\n")
         if add_generation_prompt:
             ids += self.encode("<|im_start|>assistant\n")
         return ids
+
+
+def video_layout(grid, frame_times: Sequence[float], temporal_patch: int = 2) -> dict:
+    """Layout entry of a clip for `apply_chat_template`: grid (t, h, w) of merged vision tokens and the time
+    (seconds) of every sampled frame -> tokens per temporal group and the group time stamps (mean of the first and
+    last frame of each group; a trailing odd frame counts twice, as the vision encoder repeats it)."""
+    t, h, w = grid
+    times = list(frame_times)
+    if len(times) % temporal_patch:
+        times += [times[-1]] * (temporal_patch - len(times) % temporal_patch)
+    stamps = [(times[i] + times[i + temporal_patch - 1]) / 2.0 for i in range(0, len(times), temporal_patch)][:t]
+    return {"per_frame": h * w, "timestamps": stamps}
 
 
 class HFTokenizer:

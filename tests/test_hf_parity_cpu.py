@@ -219,3 +219,32 @@ def test_pipeline_opens_a_qwen3vl_directory_as_a_reasoner_only_checkpoint(tmp_pa
     again = Cosmos3OmniPipeline.from_pretrained(str(tmp_path / "ours"), torch_dtype=torch.float32, vae_widths=(8, 16, 16, 16),
                                                 towers=("ar",))
     assert torch.equal(again.vision_encoder().pos, vit.pos) and torch.equal(again.transformer.embed, pipe.transformer.embed)
+
+
+def test_video_prompt_layout_follows_the_qwen3vl_processor():
+    """Clips enter the prompt as one vision segment per temporal group behind a "<t seconds>" stamp; the stamps are
+    the processor's (`_calculate_timestamps`) and the rotary ids of that layout are `get_rope_index`'s."""
+    from transformers.models.qwen3_vl.processing_qwen3_vl import Qwen3VLProcessor
+    from cosmos_b200.utils.tokenizer import ByteTokenizer, video_layout
+    idx, fps = [0, 6, 12, 18, 24], 24.0                                  # five sampled frames of a 24 fps clip
+    want = Qwen3VLProcessor._calculate_timestamps(None, list(idx), fps, 2)
+    lay = video_layout((3, 2, 3), [i / fps for i in idx], temporal_patch=2)
+    assert lay["per_frame"] == 6 and lay["timestamps"] == pytest.approx(want) and len(want) == 3
+    tok = ByteTokenizer(512)
+    ids = tok.apply_chat_template([{"role": "user", "content": [{"type": "video_url"}, {"type": "text", "text": "what happens?"}]}],
+                                  True, [lay])
+    text = tok.decode(ids, skip_special=False)
+    assert text.count("<|vision_start|>") == 3 and ids.count(tok.video_pad_id) == 18
+    assert "<0.1 seconds><|vision_start|>" in text and "<0.6 seconds><|vision_start|>" in text and "<1.0 seconds><|vision_start|>" in text
+    # the same token pattern in the checkpoint's id space: positions agree with the reference implementation
+    cfg = hfc.Qwen3VLConfig(text_config=TEXT, vision_config=VISION, image_token_id=290, video_token_id=291,
+                            vision_start_token_id=292, vision_end_token_id=293)
+    hf = hfm.Qwen3VLModel(cfg).eval()
+    seq = [5]
+    for _ in range(3):
+        seq += [11, 12, 292] + [291] * 6 + [293]                         # stamp tokens, then the segment
+    seq += [7, 8]
+    t = torch.tensor([seq])
+    want_pos, _ = hf.get_rope_index(t, (t == 291).int() * 2, video_grid_thw=torch.tensor([[3, 4, 6]]))
+    got = ReasonerEngine.positions(ReasonerEngine.__new__(ReasonerEngine), t, t == 291, [(1, 2, 3)] * 3)
+    assert torch.equal(got, want_pos[:, 0])
