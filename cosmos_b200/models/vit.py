@@ -53,8 +53,9 @@ class ViTBlock(nn.Module):
             cos, sin = rot[0][None, :, None], rot[1][None, :, None]
             q = (q.float() * cos + _rotate_half(q.float()) * sin).to(x.dtype)
             k = (k.float() * cos + _rotate_half(k.float()) * sin).to(x.dtype)
-        a = torch.softmax(torch.einsum("bqhd,bkhd->bhqk", q.float(), k.float()) / (d // self.heads) ** 0.5, dim=-1)
-        o = torch.einsum("bhqk,bkhd->bqhd", a, v.float()).reshape(b, s, d).to(x.dtype)
+        # attention within a temporal slice; the library's fused kernel keeps memory linear in the patch count
+        o = F.scaled_dot_product_attention(q.transpose(1, 2), k.transpose(1, 2), v.transpose(1, 2))
+        o = o.transpose(1, 2).reshape(b, s, d)
         x = x + self.proj(o)
         return x + self.fc2(F.gelu(self.fc1(self.n2(x)), approximate="tanh"))
 

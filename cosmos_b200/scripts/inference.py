@@ -160,9 +160,10 @@ def _reasoner_prompt(tokenizer, vit, cfg, spec: InferenceSpec, device):
     content, vision_embeds, grids, n_vis, deep = [], None, [], [], None
     if spec.vision_path:
         frames, src_fps = media.read_video(spec.resolve(spec.vision_path), max_frames=16)
+        from ..serve.server import smart_resize
         unit = cfg.vit_patch * cfg.vit_spatial_merge
-        h = min(max(unit, frames.shape[1] // unit * unit), 14 * unit)
-        w = min(max(unit, frames.shape[2] // unit * unit), 14 * unit)
+        most = 12845056 if frames.shape[0] == 1 else min(12845056, 25165824 // frames.shape[0])
+        h, w = smart_resize(frames.shape[1], frames.shape[2], unit, min(3136, most), most)
         from PIL import Image
         fr = np.stack([np.asarray(Image.fromarray(f).resize((w, h))) for f in frames])
         vid = CausalVideoVAE.from_uint8(torch.from_numpy(fr)[None])[0].permute(1, 0, 2, 3).to(device)

@@ -102,6 +102,7 @@ class Cosmos3Server:
         self.model_name = model_name
         self.guardrails_default = guardrails_default
         self.allowed_root = Path(allowed_local_media_path)
+        self.max_image_pixels = 12845056     # server-side ceiling per frame, whatever a request asks for (--max-image-pixels)
         self.jobs: Dict[str, Job] = {}
         self.pool = ThreadPoolExecutor(max_workers=1)
         self.gen_lock = threading.Lock()
@@ -414,8 +415,11 @@ class Cosmos3Server:
         from ..models.vae import CausalVideoVAE
         unit = self.pipe.cfg.vit_patch * self.pipe.cfg.vit_spatial_merge
         size = size or {}
-        h, w = smart_resize(frames.shape[1], frames.shape[2], unit, int(size.get("shortest_edge", 3136)),
-                            int(size.get("longest_edge", 12845056)), max_side=14 * unit)
+        # pixel bounds per frame: the request's, else 3136 .. 12845056 for an image (reference README.md:574) and, for
+        # a clip, an equal share of 25165824 pixels over its frames (the Qwen3-VL video default)
+        most = 12845056 if frames.shape[0] == 1 else min(12845056, 25165824 // frames.shape[0])
+        most = min(int(size.get("longest_edge", most)), self.max_image_pixels)
+        h, w = smart_resize(frames.shape[1], frames.shape[2], unit, min(int(size.get("shortest_edge", 3136)), most), most)
         fr = np.stack([np.asarray(Image.fromarray(f).resize((w, h))) for f in frames])
         vid = CausalVideoVAE.from_uint8(torch.from_numpy(fr)[None])[0].permute(1, 0, 2, 3).to(dev)
         with torch.no_grad():
@@ -573,6 +577,8 @@ def main(argv=None) -> int:
     ap.add_argument("--max-num-seqs", type=int, default=8,
                     help="decode slots of the continuous-batching engine for chat requests (0 = off)")
     ap.add_argument("--max-model-len", type=int, default=8192)
+    ap.add_argument("--max-image-pixels", type=int, default=12845056,
+                    help="ceiling on the pixels per image / video frame after resizing, whatever a request asks for")
     args = ap.parse_args(argv)
     apply_deploy_config(args)
     import uvicorn
@@ -611,6 +617,7 @@ def main(argv=None) -> int:
         worker = EngineWorker(engine)
     server = Cosmos3Server(pipe, ReasonerEngine(pipe.transformer, vit), vit, args.model, not args.no_guardrails,
                            args.allowed_local_media_path, batch_engine=worker)
+    server.max_image_pixels = args.max_image_pixels
     uvicorn.run(create_app(server), host=args.host, port=args.port, log_level="info")
     return 0
 
