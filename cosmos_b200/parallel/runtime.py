@@ -39,12 +39,13 @@ def init_distributed(world: Optional[int] = None, rank: Optional[int] = None, lo
     return Mesh(pc, world, rank)
 
 
-def finish(hard: bool = True, grace_s: float = 10.0) -> None:
-    """End of a launcher-run entry point: the ranks meet once more, tear the communicators down, flush and leave.
-    With `hard` the teardown runs in a helper thread and the process exits (`os._exit`) once it is done or after
-    `grace_s` seconds: a communicator whose collectives were captured in a CUDA graph can block in
-    `destroy_process_group`, and a rank that blocks there keeps the launcher and the GPUs busy long after the work is
-    done. The regular teardown is still attempted first, so that no rank frees buffers a peer is reading."""
+def finish(hard: bool = True, grace_s: float = 0.0) -> None:
+    """End of a launcher-run entry point: the ranks synchronise their devices, meet at a barrier (after it no rank
+    has a kernel or collective in flight that reads a peer's buffers), flush and leave.
+    With `hard` the process then exits through `os._exit`: a communicator whose collectives were captured in a CUDA
+    graph can block in `destroy_process_group`, and a rank that blocks there keeps the launcher and the GPUs busy
+    long after the work is done. `grace_s > 0` first attempts the regular teardown in a helper thread for at most
+    that long. Without `hard` (in-process callers such as tests) the communicators are destroyed normally."""
     import sys
     import threading
 
@@ -56,9 +57,10 @@ def finish(hard: bool = True, grace_s: float = 10.0) -> None:
         if not hard:
             dist.destroy_process_group()
             return
-        t = threading.Thread(target=dist.destroy_process_group, daemon=True)
-        t.start()
-        t.join(grace_s)
+        if grace_s > 0:
+            t = threading.Thread(target=dist.destroy_process_group, daemon=True)
+            t.start()
+            t.join(grace_s)
     sys.stdout.flush()
     sys.stderr.flush()
     if hard and active:
