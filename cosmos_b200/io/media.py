@@ -86,6 +86,63 @@ def read_video(path, max_frames: Optional[int] = None, size: Optional[Tuple[int,
     return frames, fps
 
 
+def sample_video(path, fps: Optional[float] = None, num_frames: Optional[int] = None, limit: int = 32
+                 ) -> Tuple[np.ndarray, list, float]:
+    """Frames of a clip sampled in time -> (frames [n, H, W, 3] uint8, their times in seconds, source fps).
+    `num_frames` > 0 spreads that many frames evenly over the clip; else `fps` keeps every round(src_fps / fps)-th
+    frame; with neither every frame is kept. At most `limit` frames come back. With OpenCV the frames in between
+    are skipped in the decoder and never converted or stored, so a long clip costs the memory of its samples."""
+    path = Path(path)
+    cap = None
+    if path.suffix.lower() not in (".npy", ".npz", ".png", ".jpg", ".jpeg", ".bmp", ".webp"):
+        try:
+            import cv2
+            cap = cv2.VideoCapture(str(path))
+            if not cap.isOpened():
+                cap = None
+        except ImportError:
+            cap = None
+    if cap is None:
+        frames, src_fps = read_video(path)
+        idx = _sample_indices(len(frames), src_fps, fps, num_frames, limit)
+        return frames[idx], (idx / max(src_fps, 1e-6)).tolist(), src_fps
+    try:
+        import cv2
+        src_fps = float(cap.get(cv2.CAP_PROP_FPS)) or 24.0
+        total = int(cap.get(cv2.CAP_PROP_FRAME_COUNT))
+        if total <= 0:                       # container without a frame count: decode everything once
+            cap.release()
+            frames, src_fps = read_video(path)
+            idx = _sample_indices(len(frames), src_fps, fps, num_frames, limit)
+            return frames[idx], (idx / max(src_fps, 1e-6)).tolist(), src_fps
+        idx = _sample_indices(total, src_fps, fps, num_frames, limit)
+        want, out, kept, pos = set(idx.tolist()), [], [], 0
+        last = int(idx[-1]) if len(idx) else -1
+        while pos <= last:
+            if not cap.grab():
+                break
+            if pos in want:
+                ok, bgr = cap.retrieve()
+                if ok:
+                    out.append(bgr[:, :, ::-1])
+                    kept.append(pos)
+            pos += 1
+    finally:
+        cap.release()
+    if not out:
+        raise ValueError(f"no frame could be decoded from {path}")
+    return np.ascontiguousarray(np.stack(out)), [k / max(src_fps, 1e-6) for k in kept], src_fps
+
+
+def _sample_indices(n: int, src_fps: float, fps: Optional[float], num_frames: Optional[int], limit: int) -> np.ndarray:
+    idx = np.arange(n)
+    if num_frames and num_frames > 0:
+        idx = np.linspace(0, max(n - 1, 0), int(num_frames)).round().astype(np.int64)
+    elif fps:
+        idx = idx[::max(1, int(round(src_fps / max(float(fps), 1e-6))))]
+    return idx[:limit]
+
+
 def _opencv_read(path, max_frames, start: int = 0) -> Optional[Tuple[np.ndarray, float]]:
     """Decodes a video with OpenCV's FFmpeg backend -> (frames RGB uint8, fps); None when OpenCV is missing or
     cannot open the file."""

@@ -394,21 +394,18 @@ class Cosmos3Server:
             p = self._local(url[7:])
         else:
             p = self._local(url)
-        frames, src_fps = media.read_video(p)
-        idx = np.arange(len(frames))
-        if is_video:
-            vk = (extra.get("media_io_kwargs") or {}).get("video", {})
-            mk = extra.get("mm_processor_kwargs") or {}
-            if int(vk.get("num_frames", 0)) > 0:
-                idx = np.linspace(0, len(frames) - 1, int(vk["num_frames"])).round().astype(int)
-            elif vk.get("num_frames") == -1 or mk.get("do_sample_frames") is False:
-                pass  # the client pre-sampled the clip: keep every frame
-            else:
-                fps = float(vk.get("fps", mk.get("fps", 2)))
-                step = max(1, int(round(src_fps / max(fps, 1e-6))))
-                idx = idx[::step]
-        idx = idx[:32]
-        return frames[idx], (idx / max(float(src_fps), 1e-6)).tolist()   # frames and their times in the source clip
+        if not is_video:
+            frames, _ = media.read_video(p, max_frames=1)
+            return frames, [0.0]
+        vk = (extra.get("media_io_kwargs") or {}).get("video", {})
+        mk = extra.get("mm_processor_kwargs") or {}
+        if int(vk.get("num_frames", 0)) > 0:
+            frames, times, _ = media.sample_video(p, num_frames=int(vk["num_frames"]))
+        elif vk.get("num_frames") == -1 or mk.get("do_sample_frames") is False:
+            frames, times, _ = media.sample_video(p)        # the client pre-sampled the clip: keep every frame
+        else:
+            frames, times, _ = media.sample_video(p, fps=float(vk.get("fps", mk.get("fps", 2))))
+        return frames, times                                  # frames and their times in the source clip
 
     def _encode_vision(self, frames: np.ndarray, dev, size: Optional[dict] = None):
         from PIL import Image

@@ -294,3 +294,22 @@ def test_droid_lerobot_dataset_items_carry_the_decoded_views():
     assert a["video"].shape[:2] == (3, 17) and a["video"].shape[2] == 360 and a["video"].shape[3] % 640 == 0
     assert a["video"].dtype == np.uint8 and b["frame_index"] == 48
     assert np.abs(a["video"].astype(int) - b["video"].astype(int)).mean() > 0.1      # another part of the episode
+
+
+def test_sample_video_keeps_only_the_sampled_frames(tmp_path):
+    from cosmos_b200.io import media
+    frames = np.zeros((30, 32, 48, 3), dtype=np.uint8)
+    for t in range(30):
+        frames[t, :, :, 1] = 8 * t                                   # the green level tells the frame apart
+    clip = tmp_path / "own.mp4"
+    media.write_video(clip, frames, 10, 8, None, 48000)              # this package's Motion-JPEG layout
+    got, times, fps = media.sample_video(clip, fps=2.0)
+    assert abs(fps - 10.0) < 1e-6 and got.shape == (6, 32, 48, 3) and times == pytest.approx([0.0, 0.5, 1.0, 1.5, 2.0, 2.5])
+    assert [int(round(g[..., 1].mean() / 8)) for g in got] == [0, 5, 10, 15, 20, 25]
+    got, times, _ = media.sample_video(clip, num_frames=4)
+    assert [int(round(g[..., 1].mean() / 8)) for g in got] == [0, 10, 19, 29] and times[-1] == pytest.approx(2.9)
+    got, times, _ = media.sample_video(clip, limit=7)
+    assert got.shape[0] == 7 and times[1] == pytest.approx(0.1)
+    np.save(tmp_path / "arr.npy", frames)                            # arrays go through the in-memory path
+    got, times, fps = media.sample_video(tmp_path / "arr.npy", fps=12.0)
+    assert fps == 24.0 and got.shape[0] == 15 and times[1] == pytest.approx(2 / 24)
