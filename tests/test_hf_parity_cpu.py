@@ -248,3 +248,37 @@ def test_video_prompt_layout_follows_the_qwen3vl_processor():
     want_pos, _ = hf.get_rope_index(t, (t == 291).int() * 2, video_grid_thw=torch.tensor([[3, 4, 6]]))
     got = ReasonerEngine.positions(ReasonerEngine.__new__(ReasonerEngine), t, t == 291, [(1, 2, 3)] * 3)
     assert torch.equal(got, want_pos[:, 0])
+
+
+def test_cli_runs_a_reasoner_sample_on_a_qwen3vl_directory_with_its_tokenizer(tmp_path):
+    """The inference CLI pointed at a Qwen3-VL checkpoint directory (weights + tokenizer files): the checkpoint's
+    tokenizer builds the chat prompt, the image goes through the checkpoint's vision tower, the text lands in
+    reasoner_text.txt."""
+    import json
+
+    import numpy as np
+    from PIL import Image
+
+    from cosmos_b200.scripts import inference as cli
+    from cosmos_b200.utils.tokenizer import HFTokenizer
+    from tests.test_tokenizer_cpu import _write_tokenizer
+    cfg = hfc.Qwen3VLConfig(text_config=TEXT, vision_config=VISION, image_token_id=290, video_token_id=291,
+                            vision_start_token_id=292, vision_end_token_id=293, tie_word_embeddings=False)
+    hf = hfm.Qwen3VLForConditionalGeneration(cfg).eval()
+    _randomise(hf)
+    ckpt = tmp_path / "qwen"
+    hf.save_pretrained(ckpt, safe_serialization=True)
+    _write_tokenizer(ckpt)
+    Image.fromarray((np.random.rand(64, 96, 3) * 255).astype(np.uint8)).save(tmp_path / "frame.png")
+    (tmp_path / "spec.json").write_text(json.dumps({"name": "r1", "model_mode": "reasoner", "prompt": "what is this ?",
+                                                    "vision_path": "frame.png", "enable_sound": False, "max_new_tokens": 4,
+                                                    "do_sample": False}))
+    rc = cli.main(["-i", str(tmp_path / "spec.json"), "-o", str(tmp_path / "out"), "--checkpoint-path", str(ckpt),
+                   "--no-guardrails", "--benchmark", "--device", "cpu"])
+    assert rc == 0
+    text = (tmp_path / "out" / "r1" / "reasoner_text.txt").read_text()
+    bench = json.loads((tmp_path / "out" / "benchmark.json").read_text())
+    assert isinstance(text, str) and "average" in bench
+    from cosmos_b200.pipeline import Cosmos3OmniPipeline
+    pipe = Cosmos3OmniPipeline.from_pretrained(str(ckpt), torch_dtype=torch.float32, vae_widths=(8, 16, 16, 16))
+    assert isinstance(pipe.tokenizer, HFTokenizer) and pipe.tokenizer.image_pad_id < pipe.cfg.vocab_size
