@@ -247,3 +247,24 @@ def test_chat_reads_a_real_h264_clip_from_the_reference_assets(client):
     assert r.status_code == 200, r.text
     usage = r.json()["usage"]
     assert usage["prompt_tokens"] > 60 and 1 <= usage["completion_tokens"] <= 3      # vision rows of several frames
+
+
+def test_chat_responses_parse_with_the_vllm_openai_schema(client):
+    """The reference serves the Reasoner through vLLM's OpenAI-compatible server; this server's chat answers (plain
+    and streamed) must parse with that server's own response models."""
+    proto = pytest.importorskip("vllm.entrypoints.openai.chat_completion.protocol")
+    body = {"model": "nvidia/Cosmos3-Nano", "max_tokens": 4, "temperature": 0.0,
+            "messages": [{"role": "user", "content": "Describe a robot arm."}]}
+    r = client.post("/v1/chat/completions", json=body)
+    assert r.status_code == 200, r.text
+    parsed = proto.ChatCompletionResponse.model_validate(r.json())
+    assert parsed.choices[0].message.role == "assistant" and parsed.usage.completion_tokens <= 4
+    assert parsed.object == "chat.completion" and parsed.choices[0].finish_reason in ("stop", "length")
+    chunks = []
+    with client.stream("POST", "/v1/chat/completions", json={**body, "stream": True}) as s:
+        for line in s.iter_lines():
+            if line.startswith("data: ") and line != "data: [DONE]":
+                chunks.append(proto.ChatCompletionStreamResponse.model_validate(json.loads(line[6:])))
+    assert chunks and chunks[0].object == "chat.completion.chunk"
+    assert chunks[-1].choices[0].finish_reason in ("stop", "length")
+    assert len({c.id for c in chunks}) == 1                              # one id for the whole stream
