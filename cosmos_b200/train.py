@@ -44,6 +44,24 @@ class TrainConfig:
     # seconds a rank waits on the host for its peers before a step; None = no liveness protocol
     # (parallel/health.py: bounded per-step rendezvous + heartbeats over the c10d store)
     health_timeout_s: Optional[float] = None
+    # optimizer steps see the mean gradient of `grad_accum` consecutive micro-batches
+    grad_accum: int = 1
+    # learning-rate schedule: linear warm-up over `warmup_steps`, then cosine decay to `min_lr_ratio * lr` at
+    # `total_steps` (0 = constant after the warm-up)
+    warmup_steps: int = 0
+    total_steps: int = 0
+    min_lr_ratio: float = 0.1
+
+    def lr_at(self, step: int) -> float:
+        """Learning rate of optimizer step `step` (1-based)."""
+        import math
+        if self.warmup_steps > 0 and step <= self.warmup_steps:
+            return self.lr * step / self.warmup_steps
+        if self.total_steps <= 0:
+            return self.lr
+        span = max(1, self.total_steps - self.warmup_steps)
+        frac = min(1.0, max(0.0, (step - self.warmup_steps) / span))
+        return self.lr * (self.min_lr_ratio + (1.0 - self.min_lr_ratio) * 0.5 * (1.0 + math.cos(math.pi * frac)))
 
 
 class Trainer:
@@ -120,18 +138,26 @@ class Trainer:
         return self._train_step(latents, text_ids, generator, **kw)
 
     def _train_step(self, latents, text_ids, generator=None, **kw) -> Dict[str, float]:
+        """One micro-batch: forward, backward and, on every `grad_accum`-th call, the optimizer step. The returned
+        record carries `grad_norm` and `lr` only for calls that stepped."""
         from .utils.obs import nvtx_range
+        acc = max(1, self.tc.grad_accum)
         with nvtx_range("train/forward"):
             loss = self.loss(latents, text_ids, generator, **kw)
         with nvtx_range("train/backward"):
-            loss.backward()
-        with nvtx_range("train/optimizer"):
-            gnorm = self.fsdp.step()
+            (loss / acc if acc > 1 else loss).backward()
+        self._micro = getattr(self, "_micro", 0) + 1
+        out: Dict[str, float] = {}
+        if self._micro % acc == 0:
+            with nvtx_range("train/optimizer"):
+                self.fsdp.lr = self.tc.lr_at(self.fsdp.step_count + 1)
+                out["grad_norm"] = self.fsdp.step()
+                out["lr"] = self.fsdp.lr
         lv = loss.detach().float()
         if self.mesh.world > 1 and dist.is_initialized():
             dist.all_reduce(lv)
             lv /= self.mesh.world
-        return {"loss": float(lv), "grad_norm": gnorm}
+        return {"loss": float(lv), **out}
 
     # ------------------------------------------------------------------ checkpoint / resume
     def save(self, out_dir, step: int) -> None:
@@ -190,6 +216,10 @@ def main(argv=None) -> int:
     ap.add_argument("--text-len", type=int, default=64)
     ap.add_argument("--micro-batch", type=int, default=1)
     ap.add_argument("--lr", type=float, default=1e-4)
+    ap.add_argument("--grad-accum", type=int, default=1, help="micro-batches per optimizer step")
+    ap.add_argument("--lr-warmup-steps", type=int, default=0)
+    ap.add_argument("--lr-total-steps", type=int, default=0, help="cosine decay to --min-lr-ratio x lr at this step (0 = constant)")
+    ap.add_argument("--min-lr-ratio", type=float, default=0.1)
     ap.add_argument("--no-checkpoint", action="store_true")
     ap.add_argument("--train-ar", action="store_true")
     ap.add_argument("--save-dir", default=None)
@@ -224,7 +254,9 @@ def main(argv=None) -> int:
     model = MoTModel(cfg, dtype=dtype, device=dev, pad_to=128 * shard_ws)
     model.init_weights(seed=0)
     tr = Trainer(model, mesh, TrainConfig(lr=args.lr, checkpoint_blocks=not args.no_checkpoint, train_ar=args.train_ar,
-                                         health_timeout_s=args.health_timeout))
+                                         health_timeout_s=args.health_timeout, grad_accum=args.grad_accum,
+                                         warmup_steps=args.lr_warmup_steps, total_steps=args.lr_total_steps,
+                                         min_lr_ratio=args.min_lr_ratio))
     step0 = tr.load(args.save_dir) if (args.resume and args.save_dir) else 0
     c, t, h, w = (int(v) for v in args.latent.split(","))
     # ranks of one cp group see the same clip; different dp ranks see different clips

@@ -74,3 +74,41 @@ def test_checkpoint_resume_continues_identically(tmp_path):
     resumed, _ = _worker(0, 1, {}, 2, str(tmp_path), True, 1)
     for k in straight:
         assert torch.equal(resumed[k], straight[k]), k
+
+
+def test_gradient_accumulation_equals_the_larger_batch_and_the_schedule_sets_the_rate():
+    """Two micro-batches of one clip with grad_accum = 2 give the optimizer step of one batch of two clips; the
+    learning rate of each optimizer step follows warm-up + cosine."""
+    import math
+
+    from cosmos_b200.config import ParallelConfig
+    from cosmos_b200.models.mot import MoTModel
+    from cosmos_b200.parallel.mesh import Mesh
+    from cosmos_b200.train import TrainConfig, Trainer
+
+    lat, ids, t, eps = _data(2)
+
+    def run(accum):
+        model = MoTModel(_cfg(), pad_to=128)
+        model.init_weights(seed=3)
+        tc = TrainConfig(lr=1e-3, max_grad_norm=0.5, fused=False, grad_accum=accum, warmup_steps=2, total_steps=6, min_lr_ratio=0.1)
+        tr = Trainer(model, Mesh(ParallelConfig(), 1, 0), tc)
+        logs = []
+        for _ in range(3):                                   # three optimizer steps
+            if accum == 1:
+                logs.append(tr.train_step(lat, ids, t=t, eps=eps))
+            else:
+                first = tr.train_step(lat[:1], ids[:1], t=t[:1], eps=eps[:1])
+                assert "grad_norm" not in first and "lr" not in first        # no step yet
+                logs.append(tr.train_step(lat[1:], ids[1:], t=t[1:], eps=eps[1:]))
+        return {k: v.clone() for k, v in tr.fsdp.full_state().items()}, logs
+
+    (a, la), (b, lb) = run(1), run(2)
+    assert [round(x["lr"], 9) for x in la] == [round(x["lr"], 9) for x in lb] == [0.0005, 0.001, round(1e-3 * (0.1 + 0.9 * 0.5 * (1 + math.cos(math.pi / 4))), 9)]
+    assert all(abs(x["grad_norm"] - y["grad_norm"]) < 1e-4 * max(1.0, x["grad_norm"]) for x, y in zip(la, lb))
+    for k in a:
+        assert torch.allclose(a[k], b[k], atol=2e-6, rtol=1e-5), k
+    tc = TrainConfig(lr=2.0, warmup_steps=4, total_steps=12, min_lr_ratio=0.25)
+    assert tc.lr_at(1) == 0.5 and tc.lr_at(4) == 2.0 and abs(tc.lr_at(8) - 2.0 * (0.25 + 0.75 * 0.5)) < 1e-12
+    assert abs(tc.lr_at(12) - 0.5) < 1e-12 and abs(tc.lr_at(40) - 0.5) < 1e-12
+    assert TrainConfig(lr=3.0).lr_at(7) == 3.0
