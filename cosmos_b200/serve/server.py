@@ -103,6 +103,7 @@ class Cosmos3Server:
         self.guardrails_default = guardrails_default
         self.allowed_root = Path(allowed_local_media_path)
         self.max_image_pixels = 12845056     # server-side ceiling per frame, whatever a request asks for (--max-image-pixels)
+        self.max_video_frames = 32           # frames kept per clip unless the request names `max_frames`
         self.jobs: Dict[str, Job] = {}
         self.pool = ThreadPoolExecutor(max_workers=1)
         self.gen_lock = threading.Lock()
@@ -399,12 +400,13 @@ class Cosmos3Server:
             return frames, [0.0]
         vk = (extra.get("media_io_kwargs") or {}).get("video", {})
         mk = extra.get("mm_processor_kwargs") or {}
+        limit = int(vk.get("max_frames", mk.get("max_frames", self.max_video_frames)))
         if int(vk.get("num_frames", 0)) > 0:
-            frames, times, _ = media.sample_video(p, num_frames=int(vk["num_frames"]))
+            frames, times, _ = media.sample_video(p, num_frames=int(vk["num_frames"]), limit=limit)
         elif vk.get("num_frames") == -1 or mk.get("do_sample_frames") is False:
-            frames, times, _ = media.sample_video(p)        # the client pre-sampled the clip: keep every frame
+            frames, times, _ = media.sample_video(p, limit=limit)   # the client pre-sampled the clip: keep every frame
         else:
-            frames, times, _ = media.sample_video(p, fps=float(vk.get("fps", mk.get("fps", 2))))
+            frames, times, _ = media.sample_video(p, fps=float(vk.get("fps", mk.get("fps", 2))), limit=limit)
         return frames, times                                  # frames and their times in the source clip
 
     def _encode_vision(self, frames: np.ndarray, dev, size: Optional[dict] = None):
