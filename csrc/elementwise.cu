@@ -324,12 +324,8 @@ static void launch_norm(const void* x, const void* gamma, void* y, long long row
   cb::rmsnorm_kernel<MAXV, MODE><<<grid, wpb * 32, 0, s>>>(                                      \
       (const bf16*)x, (const bf16*)gamma, (bf16*)y, rows, d, eps, (const bf16*)rin, (bf16*)rout, \
       (const bf16*)shift, (const bf16*)scale, rows_per_batch, mod_stride)
-  if (d <= 256) COSMOS_NORM(1);
-  else if (d <= 1024) COSMOS_NORM(4);
-  else if (d <= 4096) COSMOS_NORM(16);
-  else if (d <= 5120) COSMOS_NORM(20);
-  else if (d <= 8192) COSMOS_NORM(32);
-  else throw std::runtime_error("rmsnorm: feature size above 8192 is not supported");
+  if (d <= 256) COSMOS_NORM(1);   // one warp per row; rows of 1024 elements and more took the row kernel above
+  else COSMOS_NORM(4);
 #undef COSMOS_NORM
 }
 
