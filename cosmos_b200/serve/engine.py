@@ -198,7 +198,8 @@ class BatchEngine:
             r0 = group[0]
             x = r0.embeds.to(device=dev, dtype=self.model.embed.dtype)[None]
             vm = None if r0.vision_mask is None else r0.vision_mask.to(dev).reshape(1, -1)
-            h, kvs = self.model.ar_forward(x, r0.positions.to(dev), deepstack=r0.deepstack, vision_mask=vm)
+            deep = None if r0.deepstack is None else [d.to(device=dev, dtype=x.dtype) for d in r0.deepstack]
+            h, kvs = self.model.ar_forward(x, r0.positions.to(dev), deepstack=deep, vision_mask=vm)
             delta = [int(rope.next_start(r0.positions)) - lens[0]]
         else:
             h, kvs = self.model.ar_forward(self.model.embed_tokens(ids), rope.text_positions(n_max, 0, dev))
