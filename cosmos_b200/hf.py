@@ -135,7 +135,8 @@ class Cosmos3ReasonerForConditionalGeneration(PreTrainedModel):
         ids = input_ids[0].tolist() if torch.is_tensor(input_ids) else list(input_ids)
         eng = ReasonerEngine(self.model, self.visual)
         ve = grids = deep = None
-        vdt = next(self.visual.parameters()).dtype
+        vp = next(self.visual.parameters())
+        vdt, vdev = vp.dtype, vp.device
         if pixel_values is not None and pixel_values.dim() == 2:
             # processor layout of `transformers`: patch rows of all images plus `image_grid_thw` [n, 3]
             from .ckpt.hf_qwen3vl import frames_from_hf_patches
@@ -148,12 +149,12 @@ class Cosmos3ReasonerForConditionalGeneration(PreTrainedModel):
                 frames = frames_from_hf_patches(pixel_values[row:row + n], g, cfg.vit_patch, cfg.vit_temporal_patch,
                                                 cfg.vit_spatial_merge)
                 row += n
-                e, grid, d = self.visual(frames.to(vdt), return_deepstack=True)
+                e, grid, d = self.visual(frames.to(device=vdev, dtype=vdt), return_deepstack=True)
                 embs.append(e), grids.append(grid), deeps.append(d)
             ve = torch.cat(embs)
             deep = [torch.cat([d[k] for d in deeps]) for k in range(len(deeps[0]))] if deeps[0] else None
         elif pixel_values is not None:
-            ve, grid, deep = self.visual(pixel_values.to(vdt), return_deepstack=True)
+            ve, grid, deep = self.visual(pixel_values.to(device=vdev, dtype=vdt), return_deepstack=True)
             grids = [grid]
         dc = DecodingConfig(max_new_tokens=max_new_tokens, do_sample=do_sample, temperature=temperature, top_p=top_p,
                             top_k=top_k, repetition_penalty=repetition_penalty, presence_penalty=presence_penalty,
