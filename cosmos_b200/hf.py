@@ -115,12 +115,47 @@ class Cosmos3ReasonerForConditionalGeneration(PreTrainedModel):
         sio.save_sharded(state, out_dir)
         (Path(out_dir) / "config.json").write_text(json.dumps(hq.hf_config_dict(self.model.cfg, token_ids), indent=1))
 
-    def forward(self, input_ids: torch.Tensor, **_):
-        """Teacher-forced logits [B, S, V] of text-only input (no KV reuse)."""
+    def _encode_images(self, pixel_values: torch.Tensor, image_grid_thw: Optional[torch.Tensor]):
+        """Vision rows, token grids and DeepStack features of the images of a prompt. `pixel_values`: [T, 3, H, W] in
+        [-1, 1] (one image / clip) or the patch rows of a `transformers` Qwen3-VL processor with `image_grid_thw`."""
+        vp = next(self.visual.parameters())
+        vdt, vdev = vp.dtype, vp.device
+        if pixel_values.dim() != 2:
+            ve, grid, deep = self.visual(pixel_values.to(device=vdev, dtype=vdt), return_deepstack=True)
+            return ve, [grid], deep
+        from .ckpt.hf_qwen3vl import frames_from_hf_patches
+        cfg = self.model.cfg
+        if image_grid_thw is None:
+            raise ValueError("pixel_values in patch-row layout need image_grid_thw")
+        embs, grids, deeps, row = [], [], [], 0
+        for g in image_grid_thw.tolist():
+            n = int(g[0] * g[1] * g[2])
+            frames = frames_from_hf_patches(pixel_values[row:row + n], g, cfg.vit_patch, cfg.vit_temporal_patch,
+                                            cfg.vit_spatial_merge)
+            row += n
+            e, grid, d = self.visual(frames.to(device=vdev, dtype=vdt), return_deepstack=True)
+            embs.append(e), grids.append(grid), deeps.append(d)
+        deep = [torch.cat([d[k] for d in deeps]) for k in range(len(deeps[0]))] if deeps[0] else None
+        return torch.cat(embs), grids, deep
+
+    def forward(self, input_ids: torch.Tensor, pixel_values: Optional[torch.Tensor] = None,
+                image_grid_thw: Optional[torch.Tensor] = None, image_token_id: Optional[int] = None, **_):
+        """Teacher-forced logits [1, S, V] (no KV reuse); with `pixel_values` the positions that hold `image_token_id`
+        take the vision rows, 3-D rotary ids and DeepStack features."""
         from .models import rope
         cfg = self.model.cfg
-        x = self.model.embed_tokens(input_ids.clamp(max=cfg.vocab_size - 1))
-        h, _ = self.model.ar_forward(x, rope.text_positions(input_ids.shape[1], 0, input_ids.device))
+        ids = input_ids.clamp(max=cfg.vocab_size - 1)
+        if pixel_values is None:
+            x = self.model.embed_tokens(ids)
+            h, _ = self.model.ar_forward(x, rope.text_positions(ids.shape[1], 0, ids.device))
+            return self.model.lm_logits(h).float()
+        if image_token_id is None:
+            raise ValueError("image_token_id says which positions of input_ids hold the image")
+        eng = ReasonerEngine(self.model, self.visual)
+        ve, grids, deep = self._encode_images(pixel_values, image_grid_thw)
+        vmask = input_ids == image_token_id
+        h, _ = self.model.ar_forward(eng.embed(ids, ve, vmask), eng.positions(ids, vmask, grids), deepstack=deep,
+                                     vision_mask=vmask)
         return self.model.lm_logits(h).float()
 
     @torch.no_grad()
@@ -135,27 +170,8 @@ class Cosmos3ReasonerForConditionalGeneration(PreTrainedModel):
         ids = input_ids[0].tolist() if torch.is_tensor(input_ids) else list(input_ids)
         eng = ReasonerEngine(self.model, self.visual)
         ve = grids = deep = None
-        vp = next(self.visual.parameters())
-        vdt, vdev = vp.dtype, vp.device
-        if pixel_values is not None and pixel_values.dim() == 2:
-            # processor layout of `transformers`: patch rows of all images plus `image_grid_thw` [n, 3]
-            from .ckpt.hf_qwen3vl import frames_from_hf_patches
-            cfg = self.model.cfg
-            if image_grid_thw is None:
-                raise ValueError("pixel_values in patch-row layout need image_grid_thw")
-            embs, grids, deeps, row = [], [], [], 0
-            for g in image_grid_thw.tolist():
-                n = int(g[0] * g[1] * g[2])
-                frames = frames_from_hf_patches(pixel_values[row:row + n], g, cfg.vit_patch, cfg.vit_temporal_patch,
-                                                cfg.vit_spatial_merge)
-                row += n
-                e, grid, d = self.visual(frames.to(device=vdev, dtype=vdt), return_deepstack=True)
-                embs.append(e), grids.append(grid), deeps.append(d)
-            ve = torch.cat(embs)
-            deep = [torch.cat([d[k] for d in deeps]) for k in range(len(deeps[0]))] if deeps[0] else None
-        elif pixel_values is not None:
-            ve, grid, deep = self.visual(pixel_values.to(device=vdev, dtype=vdt), return_deepstack=True)
-            grids = [grid]
+        if pixel_values is not None:
+            ve, grids, deep = self._encode_images(pixel_values, image_grid_thw)
         dc = DecodingConfig(max_new_tokens=max_new_tokens, do_sample=do_sample, temperature=temperature, top_p=top_p,
                             top_k=top_k, repetition_penalty=repetition_penalty, presence_penalty=presence_penalty,
                             seed=seed)

@@ -184,6 +184,9 @@ def test_generate_takes_processor_style_patch_rows(tmp_path):
     grids = torch.tensor([[1, 4, 6], [1, 4, 4]])
     assert torch.allclose(hq.frames_from_hf_patches(pixels[:24], grids[0], 16, 2, 2)[:1], a)       # the inverse layout map
     ids = torch.tensor([[5, 292] + [290] * 6 + [293, 7, 292] + [290] * 4 + [293, 8, 9]])
+    with torch.no_grad():                                     # teacher-forced logits of the whole prompt
+        full = hf(input_ids=ids, pixel_values=pixels, image_grid_thw=grids, mm_token_type_ids=(ids == 290).int()).logits
+        assert (ours(ids, pixel_values=pixels, image_grid_thw=grids, image_token_id=290) - full).abs().max() < 1e-4
     got = ours.generate(ids, pixel_values=pixels, image_grid_thw=grids, image_token_id=290, max_new_tokens=5)
     with torch.no_grad():
         want = hf.generate(input_ids=ids, pixel_values=pixels, image_grid_thw=grids, mm_token_type_ids=(ids == 290).int(),
