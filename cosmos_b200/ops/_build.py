@@ -119,4 +119,11 @@ def build(verbose: bool = False, force: bool = False, bounds_check: bool = False
 
 
 if __name__ == "__main__":
-    print(build(verbose=True, force="--force" in sys.argv, bounds_check="--bounds-check" in sys.argv))
+    import argparse
+
+    ap = argparse.ArgumentParser(description="Build the sm_100a kernel library in-tree.")
+    ap.add_argument("--force", action="store_true", help="recompile every translation unit")
+    ap.add_argument("--bounds-check", action="store_true",
+                    help="build the debug variant (cosmos_b200/_C_check.so, -DCOSMOS_BOUNDS_CHECK) instead")
+    a = ap.parse_args()
+    print(build(verbose=True, force=a.force, bounds_check=a.bounds_check))
