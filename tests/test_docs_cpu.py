@@ -1,4 +1,4 @@
-"""The commands in README.md, cookbooks/ and examples/README.md name modules that exist and flags their parsers
+"""The commands in README.md, cookbooks/, examples/README.md and the profile notes name modules that exist and flags their parsers
 know (checked against each entry point's --help text)."""
 import re
 import subprocess
@@ -8,7 +8,8 @@ from pathlib import Path
 import pytest
 
 ROOT = Path(__file__).resolve().parents[1]
-DOCS = [ROOT / "README.md", ROOT / "examples" / "README.md"] + sorted((ROOT / "cookbooks").glob("*.md"))
+DOCS = ([ROOT / "README.md", ROOT / "examples" / "README.md"] + sorted((ROOT / "cookbooks").glob("*.md"))
+        + sorted((ROOT / "profiles").glob("*.md")))
 LAUNCHER_FLAGS = {"--nproc-per-node", "--master-addr", "--master-port", "--nnodes", "--standalone", "--local-addr"}
 
 
