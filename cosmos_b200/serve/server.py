@@ -116,6 +116,8 @@ class Cosmos3Server:
                   fps: int, steps: int, guidance: float, flow_shift: float, seed: int, image=None, video=None,
                   generate_sound: bool = False, extra: Optional[dict] = None, job: Optional[Job] = None):
         extra = extra or {}
+        if not getattr(self.pipe.transformer, "has_dm", hasattr(self.pipe.transformer, "dm")):
+            raise ValueError("this server was started for the Reasoner only (no Generator tower is loaded)")
         sc = SamplingConfig(num_steps=steps, guidance=guidance, shift=flow_shift, seed=seed,
                             scheduler=extra.get("scheduler", "unipc"))
         kw: Dict[str, Any] = {}
@@ -576,6 +578,11 @@ def main(argv=None) -> int:
     ap.add_argument("--max-num-seqs", type=int, default=8,
                     help="decode slots of the continuous-batching engine for chat requests (0 = off)")
     ap.add_argument("--max-model-len", type=int, default=8192)
+    ap.add_argument("--hf-overrides", default=None,
+                    help='JSON; {"architectures": ["Cosmos3ReasonerForConditionalGeneration"]} serves the Reasoner only '
+                         "(the Generator tower is not built)")
+    ap.add_argument("--async-scheduling", action="store_true",
+                    help="accepted for CLI compatibility: the batching engine always steps in its own thread")
     ap.add_argument("--max-image-pixels", type=int, default=12845056,
                     help="ceiling on the pixels per image / video frame after resizing, whatever a request asks for")
     args = ap.parse_args(argv)
@@ -589,8 +596,11 @@ def main(argv=None) -> int:
         torch.cuda.set_device(int(os.environ.get("LOCAL_RANK", "0")))
     dev = f"cuda:{int(os.environ.get('LOCAL_RANK', '0'))}" if torch.cuda.is_available() else None
     dtype = torch.bfloat16 if (dev and args.dtype == "bf16") else torch.float32
+    over = json.loads(args.hf_overrides) if args.hf_overrides else {}
+    reasoner_only = "Cosmos3ReasonerForConditionalGeneration" in (over.get("architectures") or [])
     pipe = Cosmos3OmniPipeline.from_pretrained(args.model, torch_dtype=dtype, device_map=dev,
-                                               enable_safety_checker=not args.no_guardrails)
+                                               enable_safety_checker=not args.no_guardrails,
+                                               towers=("ar",) if reasoner_only else ("ar", "dm"))
     vit = pipe.vision_encoder()
     worker = None
     world = int(os.environ.get("WORLD_SIZE", "1"))

@@ -268,3 +268,20 @@ def test_chat_responses_parse_with_the_vllm_openai_schema(client):
     assert chunks and chunks[0].object == "chat.completion.chunk"
     assert chunks[-1].choices[0].finish_reason in ("stop", "length")
     assert len({c.id for c in chunks}) == 1                              # one id for the whole stream
+
+
+def test_reasoner_only_server_refuses_generator_requests():
+    """`--hf-overrides '{"architectures": ["Cosmos3ReasonerForConditionalGeneration"]}'`: only the AR tower is
+    built; chat works, Generator endpoints answer 400 with the reason."""
+    torch.manual_seed(0)
+    pipe = Cosmos3OmniPipeline.from_pretrained("tiny", torch_dtype=torch.float32, vae_widths=(8, 16, 16, 16), towers=("ar",),
+                                               config_overrides=dict(max_text_len=32, n_layers=1))
+    assert not pipe.transformer.has_dm
+    vit = pipe.vision_encoder()
+    c = TestClient(create_app(Cosmos3Server(pipe, ReasonerEngine(pipe.transformer, vit), vit, "nvidia/Cosmos3-Nano")))
+    r = c.post("/v1/chat/completions", json={"max_tokens": 2, "temperature": 0.0, "messages": [{"role": "user", "content": "hi"}]})
+    assert r.status_code == 200, r.text
+    r = c.post("/v1/images/generations", json={"prompt": "a cat", "size": "64x64", "num_inference_steps": 1})
+    assert r.status_code == 400 and "Reasoner only" in r.text
+    r = c.post("/v1/videos/sync", data={"prompt": "x", "size": "64x64", "num_frames": "5", "num_inference_steps": "1"})
+    assert r.status_code >= 400 and "Reasoner only" in r.text
