@@ -567,7 +567,8 @@ def main(argv=None) -> int:
     ap.add_argument("--cfg-parallel-size", type=int, default=1)
     ap.add_argument("--ulysses-degree", type=int, default=1)
     ap.add_argument("--enable-layerwise-offload", action="store_true")
-    ap.add_argument("--no-guardrails", action="store_true")
+    ap.add_argument("--no-guardrails", "--cosmos3-no-guardrails", dest="no_guardrails", action="store_true",
+                    help="never load the guardrail models (per-request overrides cannot turn them back on)")
     ap.add_argument("--dtype", default="bf16")
     ap.add_argument("--deploy-config", default=None,
                     help="YAML with stages[].model_config.{guardrails, offload_guardrail_models} "
