@@ -433,7 +433,7 @@ class Cosmos3OmniPipeline:
                  num_frames: int = 189, height: int = 720, width: int = 1280, fps: int = 24,
                  num_inference_steps: int = 35, guidance_scale: float = 6.0, enable_sound: bool = False,
                  add_resolution_template: bool = True, add_duration_template: bool = True,
-                 generator: Optional[torch.Generator] = None, output_type: str = "np",
+                 generator: Optional[torch.Generator] = None, output_type: str = "pil",
                  sampling: Optional[SamplingConfig] = None, callback=None, **prep_kw) -> Cosmos3Output:
         from .utils.obs import nvtx_range
         t0 = time.perf_counter()
@@ -461,6 +461,10 @@ class Cosmos3OmniPipeline:
             frames = self.safety_checker.blur_faces(frames)
         t3 = time.perf_counter()
         video_out: Any = frames
+        if output_type not in ("pil", "np", "latent"):
+            raise ValueError("output_type must be 'pil', 'np' or 'latent'")
+        # "pil" (the default, as in the reference's Diffusers surface): a single image comes back as [PIL.Image],
+        # so `out.video[0].save(path)` works; a clip is a uint8 array [T, H, W, 3] either way
         if num_frames == 1 and output_type == "pil":
             from PIL import Image
             video_out = [Image.fromarray(frames[0])]

@@ -135,7 +135,7 @@ def run_generator_sample(pipe, spec: InferenceSpec, out_dir: Path, quality: int,
         out = pipe(prompt=spec.prompt_text(), negative_prompt=negative, image=image,
                    video=video, num_frames=spec.num_frames, height=height, width=width, fps=spec.fps,
                    num_inference_steps=spec.num_steps, guidance_scale=spec.guidance, enable_sound=spec.enable_sound,
-                   sampling=sc, **kw)
+                   sampling=sc, output_type="np", **kw)
     gen_s = time.perf_counter() - t0
     rec = {"name": spec.name, "model_mode": spec.model_mode, "generation_time_s": gen_s, **out.timings}
     if is_writer:

@@ -158,7 +158,7 @@ class Cosmos3Server:
                                  num_inference_steps=steps, guidance_scale=guidance, enable_sound=generate_sound,
                                  add_resolution_template=bool(extra.get("use_resolution_template", True)),
                                  add_duration_template=bool(extra.get("use_duration_template", True)),
-                                 sampling=sc, callback=cb, **kw)
+                                 sampling=sc, callback=cb, output_type="np", **kw)
         finally:
             self.pipe.safety_checker = checker
 

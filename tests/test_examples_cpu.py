@@ -66,6 +66,19 @@ def test_example_runs_on_the_tiny_model(fname, pipe, tmp_path):
         assert act.shape == (spec.action_chunk_size, 10) and np.isfinite(act).all()
 
 
+def test_single_image_output_follows_the_diffusers_convention(pipe, tmp_path):
+    """`pipe(..., num_frames=1).video[0].save(path)` as in the reference's Diffusers notebook; "np" gives the array."""
+    kw = dict(prompt="a cube", num_frames=1, height=32, width=32, num_inference_steps=1, guidance_scale=1.0,
+              generator=torch.Generator().manual_seed(3))
+    out = pipe(**kw)
+    out.video[0].save(tmp_path / "img.png")
+    assert (tmp_path / "img.png").stat().st_size > 100 and out.video[0].size == (32, 32)
+    arr = pipe(output_type="np", **{**kw, "generator": torch.Generator().manual_seed(3)}).video
+    assert arr.shape == (1, 32, 32, 3) and np.array_equal(np.asarray(out.video[0]), arr[0])
+    with pytest.raises(ValueError):
+        pipe(output_type="pt", **kw)
+
+
 def test_generation_is_deterministic_by_seed(pipe):
     """Same spec and seed -> identical frames; another seed -> different frames."""
     import torch

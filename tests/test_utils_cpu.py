@@ -66,3 +66,27 @@ def test_graphed_callable_replays_with_new_inputs():
     for _ in range(3):
         x = torch.randn(8, 64, device="cuda")
         torch.testing.assert_close(g(x), torch.relu(x @ w))
+
+
+def test_media_helpers_follow_the_diffusers_call_shapes(tmp_path):
+    import numpy as np
+    from PIL import Image
+
+    from cosmos_b200.io import media
+    from cosmos_b200.utils.media_helpers import encode_video, export_to_video, load_image
+    frames = (np.random.rand(6, 32, 48, 3) * 255).astype(np.uint8)
+    p = export_to_video(frames, str(tmp_path / "a.mp4"), fps=12, macro_block_size=1)
+    back, fps = media.read_video(p)
+    assert back.shape == frames.shape and abs(fps - 12) < 1e-6
+    pil = [Image.fromarray(f) for f in frames]
+    sound = np.stack([np.sin(np.linspace(0, 40, 24000)), np.zeros(24000)], axis=0).astype(np.float32)      # [2, N]
+    q = encode_video(pil, fps=12, output_path=str(tmp_path / "b.mp4"), audio=sound, audio_sample_rate=48000)
+    assert media.read_video(q)[0].shape == frames.shape and (tmp_path / "b.mp4").stat().st_size > (tmp_path / "a.mp4").stat().st_size
+    floats = export_to_video(frames.astype(np.float32) / 255.0, tmp_path / "c.mp4", fps=8)
+    assert np.abs(media.read_video(floats)[0].astype(int) - back.astype(int)).max() <= 2
+    Image.fromarray(frames[0]).save(tmp_path / "i.png")
+    img = load_image(tmp_path / "i.png")
+    assert img.size == (48, 32) and img.mode == "RGB" and load_image(img).size == (48, 32)
+    import pytest
+    with pytest.raises(ValueError):
+        load_image("https://example.com/x.png")
