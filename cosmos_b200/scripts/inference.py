@@ -159,7 +159,8 @@ def _reasoner_prompt(tokenizer, vit, cfg, spec: InferenceSpec, device):
 
     content, vision_embeds, grids, n_vis, deep = [], None, [], [], None
     if spec.vision_path:
-        frames, src_fps = media.read_video(spec.resolve(spec.vision_path), max_frames=16)
+        # clips are sampled at 2 frames per second (at most 32 frames), as the serving path does by default
+        frames, times, _ = media.sample_video(spec.resolve(spec.vision_path), fps=2.0, limit=32)
         from ..serve.server import smart_resize
         unit = cfg.vit_patch * cfg.vit_spatial_merge
         most = 12845056 if frames.shape[0] == 1 else min(12845056, 25165824 // frames.shape[0])
@@ -172,7 +173,6 @@ def _reasoner_prompt(tokenizer, vit, cfg, spec: InferenceSpec, device):
         is_video = frames.shape[0] > 1
         if is_video:   # one time-stamped vision segment (and rotary grid) per temporal group
             from ..utils.tokenizer import video_layout
-            times = (np.arange(frames.shape[0]) / max(float(src_fps), 1e-6)).tolist()
             grids, n_vis = [(1, grid[1], grid[2])] * grid[0], [video_layout(grid, times, cfg.vit_temporal_patch)]
         else:
             grids, n_vis = [grid], [grid[0] * grid[1] * grid[2]]
@@ -229,7 +229,8 @@ def run_reasoner_sample(engine, tokenizer, vit, spec: InferenceSpec, out_dir: Pa
     messages_content = []
     vision_embeds, grids, n_vis, deep = None, [], [], None
     if spec.vision_path:
-        frames, src_fps = media.read_video(spec.resolve(spec.vision_path), max_frames=16)
+        # clips are sampled at 2 frames per second (at most 32 frames), as the serving path does by default
+        frames, times, _ = media.sample_video(spec.resolve(spec.vision_path), fps=2.0, limit=32)
         unit = engine.cfg.vit_patch * engine.cfg.vit_spatial_merge
         h = max(unit, frames.shape[1] // unit * unit)
         w = max(unit, frames.shape[2] // unit * unit)
