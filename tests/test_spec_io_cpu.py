@@ -313,3 +313,28 @@ def test_sample_video_keeps_only_the_sampled_frames(tmp_path):
     np.save(tmp_path / "arr.npy", frames)                            # arrays go through the in-memory path
     got, times, fps = media.sample_video(tmp_path / "arr.npy", fps=12.0)
     assert fps == 24.0 and got.shape[0] == 15 and times[1] == pytest.approx(2 / 24)
+
+
+@pytest.mark.skipif(not REF.exists(), reason="reference assets not mounted")
+@pytest.mark.parametrize("control", ["edge", "depth"])
+def test_reference_transfer_specs_run_with_their_own_assets(control, tmp_path):
+    """The reference's transfer specs as they are (prompt JSON files, H.264 control clips, chunking keys), shrunk
+    only in size and steps, through the CLI's sample runner on the tiny model."""
+    pytest.importorskip("cv2")
+    import dataclasses
+
+    import torch
+    from cosmos_b200.pipeline import Cosmos3OmniPipeline
+    from cosmos_b200.scripts import inference as cli
+
+    spec = load_specs(REF / "cookbooks/cosmos3/generator/transfer/specs" / f"{control}.json")[0]
+    assert spec.is_transfer and control in spec.controls and spec.prompt_path and spec.negative_prompt_file
+    spec = dataclasses.replace(spec, resolution="256", num_frames=9, num_steps=1, num_video_frames_per_chunk=9)
+    pipe = Cosmos3OmniPipeline.from_pretrained("tiny", torch_dtype=torch.float32, vae_widths=(8, 16, 16, 16),
+                                               config_overrides=dict(max_text_len=32, n_layers=1))
+    with pytest.warns(UserWarning, match="truncated to max_sequence_length"):       # dense JSON prompt, byte tokenizer
+        rec = cli.run_generator_sample(pipe, spec, tmp_path / control, 8, True)
+    assert rec["model_mode"] == "video2video" and (tmp_path / control / "vision.mp4").stat().st_size > 1000
+    from cosmos_b200.io import media
+    frames, fps = media.read_video(tmp_path / control / "vision.mp4")
+    assert frames.shape[0] == 9 and abs(fps - spec.fps) < 1e-6
