@@ -338,3 +338,31 @@ def test_reference_transfer_specs_run_with_their_own_assets(control, tmp_path):
     from cosmos_b200.io import media
     frames, fps = media.read_video(tmp_path / control / "vision.mp4")
     assert frames.shape[0] == 9 and abs(fps - spec.fps) < 1e-6
+
+
+@pytest.mark.skipif(not REF.exists(), reason="reference assets not mounted")
+def test_action_modes_run_on_the_reference_action_assets(tmp_path):
+    """Forward dynamics from the reference's AV trajectory (60 x 9) and start image, inverse dynamics on its UMI
+    clip (H.264): spec files as the notebooks write them, shrunk in size and steps, on the tiny model."""
+    pytest.importorskip("cv2")
+    import torch
+    from cosmos_b200.pipeline import Cosmos3OmniPipeline
+    from cosmos_b200.scripts import inference as cli
+
+    assets = REF / "cookbooks/cosmos3/generator/action/assets"
+    fd = {"model_mode": "forward_dynamics", "name": "av_forward", "prompt": "drive forward", "vision_path": str(assets / "images/av_0.jpg"),
+          "action_path": str(assets / "actions/av_traj_forward.json"), "action_chunk_size": 8, "domain_name": "av",
+          "image_size": 256, "view_point": "ego_view", "num_steps": 1, "guidance": 1.0}
+    idn = {"model_mode": "inverse_dynamics", "name": "umi_id", "prompt": "", "vision_path": str(assets / "videos/umi.mp4"),
+           "action_chunk_size": 8, "domain_name": "umi", "image_size": 256, "num_steps": 1, "guidance": 1.0}
+    (tmp_path / "specs.jsonl").write_text(json.dumps(fd) + "\n" + json.dumps(idn) + "\n")
+    specs = load_specs(tmp_path / "specs.jsonl")
+    assert [s.num_frames for s in specs] == [9, 9] and specs[0].fps == 10 and specs[1].fps == 20      # chunk + 1; domain fps
+    pipe = Cosmos3OmniPipeline.from_pretrained("tiny", torch_dtype=torch.float32, vae_widths=(8, 16, 16, 16),
+                                               config_overrides=dict(max_text_len=16, n_layers=1))
+    rec = cli.run_generator_sample(pipe, specs[0], tmp_path / "fd", 8, True)
+    assert rec["model_mode"] == "forward_dynamics" and (tmp_path / "fd" / "vision.mp4").stat().st_size > 1000
+    rec = cli.run_generator_sample(pipe, specs[1], tmp_path / "id", 8, True)
+    out = json.loads((tmp_path / "id" / "sample_outputs.json").read_text())
+    act = np.asarray(out["outputs"][0]["content"]["action"])
+    assert act.shape == (8, 10) and np.isfinite(act).all()                                              # UMI: 9-D pose + gripper
