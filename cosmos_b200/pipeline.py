@@ -380,6 +380,33 @@ class Cosmos3OmniPipeline:
 
     # ------------------------------------------------------------------ long videos
     @torch.no_grad()
+    def forward_dynamics_rollout(self, image, actions, action_chunk_size: int = 16, domain: int = 0, prompt: str = "",
+                                 height: int = 480, width: int = 832, fps: int = 15, seed: int = 0, callback=None,
+                                 **call_kw) -> Cosmos3Output:
+        """Autoregressive forward dynamics over a long action sequence, in one process: the actions [N, D] are cut
+        into chunks of `action_chunk_size` (N must be a multiple of it), chunk k starts from the last frame that chunk
+        k - 1 produced and uses seed + k, and the clips are joined without repeating the shared frame: 1 + N frames in
+        all. This is the loop the reference's DROID / UMI notebooks run on the client side (reference
+        cookbooks/cosmos3/generator/action/run_fd_with_cosmos_framework.ipynb, the "autoregressive chunks" cells)."""
+        acts = np.asarray(actions, dtype=np.float32)
+        if acts.ndim != 2 or acts.shape[0] == 0 or acts.shape[0] % action_chunk_size:
+            raise ValueError(f"actions must be [N, D] with N a positive multiple of action_chunk_size={action_chunk_size}, "
+                             f"got {acts.shape}")
+        frames, timings, cur = [], {}, image
+        n_chunks = acts.shape[0] // action_chunk_size
+        for k in range(n_chunks):
+            chunk = acts[k * action_chunk_size:(k + 1) * action_chunk_size]
+            out = self(prompt=prompt, image=cur, num_frames=action_chunk_size + 1, height=height, width=width, fps=fps,
+                       action=chunk, domain=domain, action_dim=acts.shape[1], output_type="np",
+                       generator=torch.Generator().manual_seed(seed + k), **call_kw)
+            frames.append(out.video if k == 0 else out.video[1:])
+            cur = out.video[-1]
+            for name, v in out.timings.items():
+                timings[name] = timings.get(name, 0.0) + v
+            if callback is not None:
+                callback(k, n_chunks)
+        return Cosmos3Output(video=np.concatenate(frames), timings=timings)
+
     def generate_chunked(self, prompt: str, negative_prompt: Optional[str] = None, video=None,
                          num_frames: int = 121, height: int = 720, width: int = 1280, fps: int = 24,
                          frames_per_chunk: int = 121, num_conditional_frames: int = 1,

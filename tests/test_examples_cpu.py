@@ -88,3 +88,21 @@ def test_generation_is_deterministic_by_seed(pipe):
     c = pipe(generator=torch.Generator().manual_seed(8), **kw).video
     assert np.array_equal(np.asarray(a), np.asarray(b))
     assert not np.array_equal(np.asarray(a), np.asarray(c))
+
+
+def test_forward_dynamics_rollout_chains_chunks_on_the_last_frame(pipe):
+    """12 actions in chunks of 4 -> three chunks, 13 frames; chunk k starts from chunk k - 1's last frame."""
+    rng = np.random.default_rng(0)
+    acts = rng.normal(0, 0.05, (12, 9)).astype(np.float32)
+    start = (rng.random((32, 32, 3)) * 255).astype(np.uint8)
+    seen = []
+    out = pipe.forward_dynamics_rollout(start, acts, action_chunk_size=4, domain=0, height=32, width=32, fps=10, seed=5,
+                                        num_inference_steps=1, guidance_scale=1.0, callback=lambda k, n: seen.append((k, n)))
+    assert out.video.shape == (13, 32, 32, 3) and seen == [(0, 3), (1, 3), (2, 3)]
+    # the second chunk on its own, started from frame 4 of the rollout with seed 5 + 1, reproduces frames 4..8
+    again = pipe(prompt="", image=out.video[4], num_frames=5, height=32, width=32, fps=10, action=acts[4:8], domain=0,
+                 action_dim=9, num_inference_steps=1, guidance_scale=1.0, output_type="np",
+                 generator=torch.Generator().manual_seed(6))
+    assert np.array_equal(again.video[1:], out.video[5:9])
+    with pytest.raises(ValueError):
+        pipe.forward_dynamics_rollout(start, acts[:10], action_chunk_size=4, height=32, width=32)
