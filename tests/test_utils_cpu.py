@@ -90,3 +90,19 @@ def test_media_helpers_follow_the_diffusers_call_shapes(tmp_path):
     import pytest
     with pytest.raises(ValueError):
         load_image("https://example.com/x.png")
+
+
+def test_top_level_package_exposes_the_public_classes_lazily():
+    import importlib
+    import sys
+
+    import cosmos_b200
+    assert cosmos_b200.__version__ == "0.1.0"
+    from cosmos_b200.pipeline import Cosmos3OmniPipeline
+    assert cosmos_b200.Cosmos3OmniPipeline is Cosmos3OmniPipeline
+    assert cosmos_b200.Cosmos3ReasonerForConditionalGeneration.__name__ == "Cosmos3ReasonerForConditionalGeneration"
+    assert cosmos_b200.SamplingConfig().num_steps == 35 and "UniPCMultistepScheduler" in dir(cosmos_b200)
+    import pytest
+    with pytest.raises(AttributeError):
+        cosmos_b200.NoSuchThing
+    assert importlib.import_module("cosmos_b200.ops") is sys.modules["cosmos_b200.ops"]      # submodules still import
