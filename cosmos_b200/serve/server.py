@@ -133,7 +133,11 @@ class Cosmos3Server:
                 act = extra.get("action")
                 if act is None and extra.get("action_path"):
                     act = json.loads(self._local(extra["action_path"]).read_text())
-                kw["action"] = np.asarray(act, dtype=np.float32)[:chunk]
+                act = np.asarray(act, dtype=np.float32)
+                if act.shape[0] > chunk and act.shape[0] % chunk == 0 and image is not None:
+                    # several chunks of actions: rolled out in this process, each chunk from the last frame of the one before
+                    kw["rollout"] = act
+                kw["action"] = act[:chunk]
             else:  # inverse_dynamics / policy: actions are denoised
                 kw["n_action"], kw["denoise_action"] = chunk, True
                 if mode == "inverse_dynamics":
@@ -153,6 +157,14 @@ class Cosmos3Server:
 
         try:
             with self.gen_lock:
+                if "rollout" in kw:
+                    acts = kw.pop("rollout")
+                    n_chunks = acts.shape[0] // chunk
+                    return self.pipe.forward_dynamics_rollout(
+                        image, acts, chunk, kw["domain"], prompt, height, width, fps, seed,
+                        callback=lambda k, n: cb(k, n_chunks), num_inference_steps=steps, guidance_scale=guidance,
+                        sampling=sc, add_resolution_template=bool(extra.get("use_resolution_template", True)),
+                        add_duration_template=bool(extra.get("use_duration_template", True)))
                 return self.pipe(prompt=prompt, negative_prompt=negative_prompt, image=image, video=video,
                                  num_frames=num_frames, height=height, width=width, fps=fps,
                                  num_inference_steps=steps, guidance_scale=guidance, enable_sound=generate_sound,

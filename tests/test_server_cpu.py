@@ -285,3 +285,26 @@ def test_reasoner_only_server_refuses_generator_requests():
     assert r.status_code == 400 and "Reasoner only" in r.text
     r = c.post("/v1/videos/sync", data={"prompt": "x", "size": "64x64", "num_frames": "5", "num_inference_steps": "1"})
     assert r.status_code >= 400 and "Reasoner only" in r.text
+
+
+def test_forward_dynamics_job_with_several_action_chunks_rolls_out_in_process(client, tmp_path):
+    """12 actions with action_chunk_size 4 in one request: three chunks chained on the last frame, 13 frames back."""
+    img = io.BytesIO()
+    from PIL import Image
+    Image.fromarray((np.random.rand(64, 64, 3) * 255).astype(np.uint8)).save(img, format="PNG")
+    extra = {"action_mode": "forward_dynamics", "domain_name": "av", "raw_action_dim": 9, "action_chunk_size": 4,
+             "action": (np.random.randn(12, 9) * 0.05).tolist(), "guardrails": False}
+    r = client.post("/v1/videos", data={"prompt": "drive", "size": "64x64", "num_inference_steps": "1", "fps": "10",
+                                        "extra_params": json.dumps(extra)},
+                    files={"input_reference": ("frame.png", img.getvalue(), "image/png")})
+    jid = r.json()["id"]
+    for _ in range(300):
+        st = client.get(f"/v1/videos/{jid}").json()
+        if st["status"] in ("completed", "failed"):
+            break
+        time.sleep(0.1)
+    assert st["status"] == "completed" and st["progress"] == 100, st
+    clip = tmp_path / "rollout.mp4"
+    clip.write_bytes(client.get(f"/v1/videos/{jid}/content").content)
+    frames, fps = mp4.read_mp4_mjpeg(clip)
+    assert frames.shape[0] == 13 and abs(fps - 10) < 1e-6
