@@ -90,6 +90,7 @@ class Cosmos3OmniPipeline:
         self.scheduler = scheduler or UniPCMultistepScheduler()
         self.safety_checker = safety_checker if enable_safety_checker else None
         self.engine = engine or GeneratorEngine(model)
+        self.action_normalizer = None   # data/vfm/action/normalization.py::ActionNormalizer, from the checkpoint's action_stats.json
         self.cfg: MoTConfig = model.cfg
         self._step_state: Optional[Tuple[GenState, SamplingConfig, torch.Tensor]] = None
 
@@ -145,6 +146,10 @@ class Cosmos3OmniPipeline:
         eng = GeneratorEngine(model, **(engine_kwargs or {}))
         pipe = cls(model, vae, snd, tok, None, guard, enable_safety_checker, eng)
         pipe._vision_source = ckpt_dir or qwen_dir
+        if ckpt_dir is not None:
+            from .data.vfm.action.normalization import STATS_FILE, ActionNormalizer
+            if (ckpt_dir / STATS_FILE).exists():
+                pipe.action_normalizer = ActionNormalizer.load(ckpt_dir)
         return pipe
 
     def vision_encoder(self):
@@ -178,6 +183,8 @@ class Cosmos3OmniPipeline:
         sio.save_sharded(dict(self.sound_tokenizer.state_dict()), out / "sound_tokenizer")
         if getattr(self, "_vit", None) is not None or getattr(self, "_vision_source", None) is not None:
             sio.save_sharded(dict(self.vision_encoder().state_dict()), out / "vision_encoder")
+        if self.action_normalizer is not None:
+            self.action_normalizer.save(out)
         if hasattr(self.tokenizer, "hf"):  # a checkpoint's own tokenizer travels with it
             self.tokenizer.hf.save_pretrained(str(out / "tokenizer"))
         (out / "scheduler").mkdir(parents=True, exist_ok=True)
@@ -283,6 +290,8 @@ class Cosmos3OmniPipeline:
                 cond[a:b] = True
                 clean[0, a:b, :cfg.patch_dim] = ztok[a:b]
         if action is not None and not denoise_action:
+            if self.action_normalizer is not None:      # per-embodiment standardisation (data/vfm/action/normalization.py)
+                action = self.action_normalizer.normalize(action, cfg.action_domains[domain])
             a = torch.as_tensor(np.asarray(action), dtype=torch.float32, device=self.device)
             off = st.n_video + st.n_sound
             cond[off:off + a.shape[0]] = True
@@ -376,6 +385,8 @@ class Cosmos3OmniPipeline:
         if st.n_action:
             off = st.n_video + st.n_sound
             action = tokens[0, off:off + st.n_action, :st.action_dim].float().cpu().numpy()
+            if self.action_normalizer is not None and getattr(st, "domain", None) is not None:
+                action = self.action_normalizer.denormalize(action, self.cfg.action_domains[int(st.domain)])
         return frames, sound, action
 
     # ------------------------------------------------------------------ long videos

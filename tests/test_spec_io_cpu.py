@@ -366,3 +366,37 @@ def test_action_modes_run_on_the_reference_action_assets(tmp_path):
     out = json.loads((tmp_path / "id" / "sample_outputs.json").read_text())
     act = np.asarray(out["outputs"][0]["content"]["action"])
     assert act.shape == (8, 10) and np.isfinite(act).all()                                              # UMI: 9-D pose + gripper
+
+
+def test_action_normalizer_standardises_free_dims_and_travels_with_the_checkpoint(tmp_path):
+    import torch
+    from cosmos_b200.data.vfm.action.normalization import ActionNormalizer, default_free_dims
+    from cosmos_b200.pipeline import Cosmos3OmniPipeline
+    rng = np.random.default_rng(0)
+    chunks = [np.concatenate([rng.normal(0.02, 0.01, (16, 3)), rng.normal(0, 1, (16, 6)), rng.uniform(0, 1, (16, 1))], -1)
+              for _ in range(20)]
+    assert list(default_free_dims(10)) == [0, 1, 2, 9] and list(default_free_dims(9)) == [0, 1, 2]
+    norm = ActionNormalizer()
+    assert np.array_equal(norm.normalize(chunks[0], "droid_lerobot"), chunks[0].astype(np.float32))      # no statistics: identity
+    norm.fit("droid_lerobot", chunks)
+    z = norm.normalize(np.concatenate(chunks), "droid_lerobot")
+    assert np.abs(z[:, [0, 1, 2, 9]].mean(0)).max() < 1e-3 and np.abs(z[:, [0, 1, 2, 9]].std(0) - 1).max() < 1e-3
+    assert np.allclose(z[:, 3:9], np.concatenate(chunks)[:, 3:9], atol=1e-6)                            # rot6d untouched
+    assert np.allclose(norm.denormalize(z, "droid_lerobot"), np.concatenate(chunks), atol=1e-5)
+    with pytest.raises(ValueError):
+        norm.normalize(np.zeros((4, 9)), "droid_lerobot")
+    pipe = Cosmos3OmniPipeline.from_pretrained("tiny", torch_dtype=torch.float32, vae_widths=(8, 16, 16, 16),
+                                               config_overrides=dict(max_text_len=16, n_layers=1))
+    pipe.action_normalizer = norm
+    pipe.save_pretrained(tmp_path / "ckpt")
+    again = Cosmos3OmniPipeline.from_pretrained(str(tmp_path / "ckpt"), torch_dtype=torch.float32, vae_widths=(8, 16, 16, 16))
+    assert again.action_normalizer.stats == norm.stats
+    # inverse dynamics output comes back in the data's units: the gripper column is mean + std * z
+    dom = list(again.cfg.action_domains).index("droid_lerobot")
+    clip = (rng.random((5, 32, 32, 3)) * 255).astype(np.uint8)
+    kw = dict(prompt="", video=clip, num_frames=5, height=32, width=32, num_inference_steps=1, guidance_scale=1.0, domain=dom,
+              action_dim=10, n_action=4, denoise_action=True, output_type="np")
+    got = again(generator=torch.Generator().manual_seed(1), **kw).action
+    again.action_normalizer = None
+    raw = again(generator=torch.Generator().manual_seed(1), **kw).action
+    assert got.shape == raw.shape == (4, 10) and np.allclose(got, norm.denormalize(raw, "droid_lerobot"), atol=1e-5)
