@@ -37,3 +37,44 @@ def upsample_prompt(reasoner, tokenizer, prompt: str, width: int, height: int, d
     obj.setdefault("duration", duration_s)
     obj.setdefault("fps", fps)
     return json.dumps(obj, separators=(",", ":"), ensure_ascii=False)
+
+
+def main(argv=None) -> int:
+    """`python -m cosmos_b200.utils.prompt_upsampler "a robot stacks blocks" --resolution 720 --num-frames 121 --fps 24`
+    prints the dense caption (compact JSON) for the Generator and, on stderr, what the schema check found."""
+    import argparse
+    import sys
+
+    import torch
+
+    from ..config import resolve_size
+    from ..io.prompt_schema import parse_prompt, validate_prompt
+    from ..models.reasoner import ReasonerEngine
+    from ..pipeline import Cosmos3OmniPipeline
+
+    ap = argparse.ArgumentParser(description=main.__doc__)
+    ap.add_argument("prompt")
+    ap.add_argument("--checkpoint-path", default="Cosmos3-Nano")
+    ap.add_argument("--resolution", default="720")
+    ap.add_argument("--aspect-ratio", default="16,9")
+    ap.add_argument("--num-frames", type=int, default=189)
+    ap.add_argument("--fps", type=int, default=24)
+    ap.add_argument("--max-tokens", type=int, default=UPSAMPLER_DECODING.max_new_tokens)
+    ap.add_argument("--device", default="cuda" if torch.cuda.is_available() else "cpu")
+    a = ap.parse_args(argv)
+    cuda = a.device.startswith("cuda")
+    pipe = Cosmos3OmniPipeline.from_pretrained(a.checkpoint_path, torch_dtype=torch.bfloat16 if cuda else torch.float32,
+                                               device_map=a.device if cuda else None, towers=("ar",),
+                                               enable_safety_checker=False)
+    w, h = resolve_size(a.resolution, a.aspect_ratio)
+    import dataclasses
+    dc = dataclasses.replace(UPSAMPLER_DECODING, max_new_tokens=a.max_tokens)
+    text = upsample_prompt(ReasonerEngine(pipe.transformer, None), pipe.tokenizer, a.prompt, w, h, a.num_frames / a.fps, a.fps, dc)
+    print(text)
+    for problem in validate_prompt(parse_prompt(text) or {}):
+        print(f"schema: {problem}", file=sys.stderr)
+    return 0
+
+
+if __name__ == "__main__":
+    raise SystemExit(main())

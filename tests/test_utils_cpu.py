@@ -106,3 +106,15 @@ def test_top_level_package_exposes_the_public_classes_lazily():
     with pytest.raises(AttributeError):
         cosmos_b200.NoSuchThing
     assert importlib.import_module("cosmos_b200.ops") is sys.modules["cosmos_b200.ops"]      # submodules still import
+
+
+def test_prompt_upsampler_cli_prints_a_compact_json_caption(capsys):
+    import json
+
+    from cosmos_b200.utils import prompt_upsampler as pu
+    assert pu.main(["a robot arm stacks blocks", "--checkpoint-path", "tiny", "--resolution", "256", "--num-frames", "49",
+                    "--fps", "24", "--max-tokens", "4", "--device", "cpu"]) == 0
+    out = capsys.readouterr().out.strip().splitlines()[-1]
+    obj = json.loads(out)
+    assert obj["resolution"] == {"W": 320, "H": 192} and obj["fps"] == 24 and " " not in out.split('"temporal_caption"')[0]
+    assert obj["temporal_caption"] == "a robot arm stacks blocks"          # random weights: the raw prompt is wrapped
