@@ -289,23 +289,57 @@ class Cosmos3Server:
         tok = self.pipe.tokenizer
         ids: List[int] = []
         sent = ""
+        stops, stopped = self._stops(body), False
+        hold = max((len(s) for s in stops), default=1) - 1      # characters that could still become a stop string
         yield chunk({"role": "assistant", "content": ""})
         while True:
             t = q.get()
             if t is None:
                 break
+            if stopped:
+                continue
             ids.append(int(t))
             text = tok.decode(ids)
-            if len(text) > len(sent) and not text.endswith("\ufffd"):  # hold back an incomplete multi-byte character
-                yield chunk({"content": text[len(sent):]})
-                sent = text
+            if text.endswith("\ufffd"):                          # hold back an incomplete multi-byte character
+                continue
+            text, stopped = self._cut_at_stop(text, stops)
+            visible = text if stopped else text[:max(len(sent), len(text) - hold)]
+            if len(visible) > len(sent):
+                yield chunk({"content": visible[len(sent):]})
+                sent = visible
+        if not stopped and "final" in result:                      # what was held back in case it began a stop string
+            rest = result["final"]["choices"][0]["message"]["content"]
+            if len(rest) > len(sent) and rest.startswith(sent):
+                yield chunk({"content": rest[len(sent):]})
         if "error" in result:
             yield "data: " + json.dumps({"error": {"message": result["error"]}}) + "\n\n"
         else:
             yield chunk({}, result["final"]["choices"][0]["finish_reason"])
         yield "data: [DONE]\n\n"
 
+    @staticmethod
+    def _stops(body: dict) -> List[str]:
+        stop = body.get("stop")
+        return [] if not stop else ([stop] if isinstance(stop, str) else [s for s in stop if s])
+
+    @staticmethod
+    def _cut_at_stop(text: str, stops: List[str]):
+        """(text up to the first stop string, whether one was found)."""
+        hits = [i for i in (text.find(s) for s in stops) if i >= 0]
+        return (text[:min(hits)], True) if hits else (text, False)
+
     def chat_completions(self, body: dict, on_token=None) -> dict:
+        """OpenAI chat completion. `stop` (a string or a list) ends the answer before the first stop string."""
+        out = self._chat_completions(body, on_token)
+        stops = self._stops(body)
+        if stops:
+            choice = out["choices"][0]
+            choice["message"]["content"], found = self._cut_at_stop(choice["message"]["content"], stops)
+            if found:
+                choice["finish_reason"] = "stop"
+        return out
+
+    def _chat_completions(self, body: dict, on_token=None) -> dict:
         if self.reasoner is None:
             raise RuntimeError("this server was started without the Reasoner")
         t0 = time.time()

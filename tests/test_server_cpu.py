@@ -308,3 +308,39 @@ def test_forward_dynamics_job_with_several_action_chunks_rolls_out_in_process(cl
     clip.write_bytes(client.get(f"/v1/videos/{jid}/content").content)
     frames, fps = mp4.read_mp4_mjpeg(clip)
     assert frames.shape[0] == 13 and abs(fps - 10) < 1e-6
+
+
+def test_stop_strings_end_the_answer_plain_and_streamed():
+    """`stop`: the answer ends before the first stop string, also when the string arrives split over several streamed
+    tokens; text that only looked like the beginning of a stop string is still delivered."""
+    torch.manual_seed(0)
+    pipe = Cosmos3OmniPipeline.from_pretrained("tiny", torch_dtype=torch.float32, vae_widths=(8, 16, 16, 16), towers=("ar",),
+                                               config_overrides=dict(max_text_len=32, n_layers=1))
+    srv = Cosmos3Server(pipe, ReasonerEngine(pipe.transformer, None), None, "nvidia/Cosmos3-Nano")
+    answer = "The arm lifts the cube. END and more; almost EN done"
+
+    def fake(body, on_token=None):                       # a model that says `answer`, one byte-token at a time
+        for t in pipe.tokenizer.encode(answer):
+            if on_token is not None:
+                on_token(t)
+        return {"id": "x", "object": "chat.completion", "created": 0, "model": "m",
+                "choices": [{"index": 0, "message": {"role": "assistant", "content": answer}, "finish_reason": "length"}],
+                "usage": {"prompt_tokens": 1, "completion_tokens": len(answer), "total_tokens": 1 + len(answer)}}
+
+    srv._chat_completions = fake
+    c = TestClient(create_app(srv))
+    base = {"messages": [{"role": "user", "content": "hi"}]}
+    cut = c.post("/v1/chat/completions", json={**base, "stop": ["END", "never"]}).json()["choices"][0]
+    assert cut["message"]["content"] == "The arm lifts the cube. " and cut["finish_reason"] == "stop"
+    same = c.post("/v1/chat/completions", json={**base, "stop": "never"}).json()["choices"][0]
+    assert same["message"]["content"] == answer and same["finish_reason"] == "length"
+    for stop, want in (("END", "The arm lifts the cube. "), ("ENX", answer), (None, answer)):
+        pieces, finish = [], None
+        with c.stream("POST", "/v1/chat/completions", json={**base, "stream": True, **({"stop": stop} if stop else {})}) as s:
+            for line in s.iter_lines():
+                if line.startswith("data: ") and line != "data: [DONE]":
+                    ch = json.loads(line[6:])["choices"][0]
+                    pieces.append(ch["delta"].get("content") or "")
+                    finish = ch["finish_reason"] or finish
+        assert "".join(pieces) == want, (stop, "".join(pieces))
+        assert finish == ("stop" if stop == "END" else "length")
