@@ -86,6 +86,16 @@ class Metrics:
                     "request_throughput_per_s": self.requests / span}
 
 
+def prometheus_text(snapshot: Dict[str, Any], prefix: str = "cosmos_b200") -> str:
+    """The metrics snapshot in the Prometheus text exposition format (one gauge per figure)."""
+    lines = []
+    for key, value in snapshot.items():
+        name = f"{prefix}_{key}"
+        lines.append(f"# TYPE {name} gauge")
+        lines.append(f"{name} {0.0 if value is None else float(value):.6g}")
+    return "\n".join(lines) + "\n"
+
+
 def parse_size(size: str):
     w, h = size.lower().split("x")
     return int(w), int(h)
@@ -523,8 +533,12 @@ def create_app(server: Cosmos3Server):
         return server.models()
 
     @app.get("/metrics")
-    def metrics():
-        return server.metrics.snapshot()
+    def metrics(request: Request):
+        """JSON by default; `?format=prometheus` (or a scraper's `Accept: text/plain`) gives the text exposition format."""
+        snap = server.metrics.snapshot()
+        if request.query_params.get("format") == "prometheus" or "text/plain" in request.headers.get("accept", ""):
+            return Response(prometheus_text(snap), media_type="text/plain; version=0.0.4")
+        return snap
 
     @app.post("/v1/images/generations")
     async def images(request: Request):

@@ -344,3 +344,16 @@ def test_stop_strings_end_the_answer_plain_and_streamed():
                     finish = ch["finish_reason"] or finish
         assert "".join(pieces) == want, (stop, "".join(pieces))
         assert finish == ("stop" if stop == "END" else "length")
+
+
+def test_metrics_as_json_and_in_the_prometheus_text_format(client):
+    client.post("/v1/chat/completions", json={"max_tokens": 2, "temperature": 0.0, "messages": [{"role": "user", "content": "hi"}]})
+    js = client.get("/metrics").json()
+    assert js["requests"] >= 1
+    txt = client.get("/metrics?format=prometheus")
+    assert txt.status_code == 200 and txt.headers["content-type"].startswith("text/plain")
+    lines = txt.text.splitlines()
+    assert "# TYPE cosmos_b200_requests gauge" in lines
+    val = [ln for ln in lines if ln.startswith("cosmos_b200_requests ")][0].split()[1]
+    assert float(val) >= 1
+    assert client.get("/metrics", headers={"accept": "text/plain"}).text.startswith("# TYPE")
