@@ -257,9 +257,14 @@ class BatchEngine:
     def _accept(self, r: Request, tok: int) -> None:
         """Books a generated token; retires the request when it ends."""
         r.out.append(tok)
+        halt = False
         if r.on_token is not None:
-            r.on_token(tok)
-        if tok in r.eos_ids:
+            # a callback that returns False ends the request here (e.g. a stop string completed); only honoured on a
+            # single rank, because followers of a tensor-parallel engine do not run the callback
+            halt = r.on_token(tok) is False and self.tp == 1
+        if halt:
+            self._retire(r, "stop")
+        elif tok in r.eos_ids:
             self._retire(r, "stop")
         elif len(r.out) >= r.max_new_tokens:
             self._retire(r, "length")

@@ -418,6 +418,17 @@ class Cosmos3Server:
                 x = self.reasoner.embed(ids_t.clamp(max=self.pipe.cfg.vocab_size - 1), ve, vmask)
                 extra_kw = dict(embeds=x[0], positions=self.reasoner.positions(ids_t, vmask, grids),
                                 vision_mask=vmask[0], deepstack=ds)
+            stops = self._stops(body)
+            if stops:
+                # the engine retires the request as soon as a stop string is complete instead of decoding to the limit
+                seen_ids: List[int] = []
+                inner = user_cb
+
+                def user_cb(t, _inner=inner):
+                    if _inner is not None:
+                        _inner(t)
+                    seen_ids.append(int(t))
+                    return not self._cut_at_stop(tok.decode(seen_ids), stops)[1]
             r = self.batch_engine.submit(ids, dc.max_new_tokens, (tok.eos_id, tok.eot_id),
                                          temperature=dc.temperature if dc.do_sample else 0.0, top_k=dc.top_k,
                                          top_p=dc.top_p, presence_penalty=dc.presence_penalty,

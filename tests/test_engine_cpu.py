@@ -256,3 +256,19 @@ def test_tensor_parallel_engine_serves_a_request_with_media():
     out = run_ranks(_tp_engine_media_ranks, 2, timeout=180)
     assert out[0]["outs"] == out[1]["outs"] and [len(o) for o in out[0]["outs"]] == [4, 5]
     assert out[0]["had_media"] == out[1]["had_media"] == [False, True]
+
+
+def test_a_callback_that_returns_false_retires_the_request():
+    """Stop strings are detected by the caller's token callback; returning False ends the request at that token and
+    frees its slot and pages, while its neighbours in the batch carry on."""
+    model = _model()
+    eng = BatchEngine(model, max_batch=2, max_len=48, page_size=4, use_graph=False)
+    free0 = eng.dec.cache.alloc.num_free()
+    got = []
+    a = eng.submit([5, 9, 2, 7, 1], 10, on_token=lambda t: (got.append(t), len(got) < 3)[1])
+    b = eng.submit([3, 3, 8], 6)
+    eng.run_until_done()
+    assert len(a.out) == 3 and a.finish_reason == "stop" and got == a.out
+    assert len(b.out) == 6 and b.finish_reason == "length"
+    assert eng.dec.cache.alloc.num_free() == free0
+    _check_against_reference(model, b)
