@@ -135,4 +135,4 @@ def _symm_alloc_with_a_missing_rank(rank, world):
 def test_symmetric_allocation_names_the_rank_that_dropped_out():
     out = run_ranks(_symm_alloc_with_a_missing_rank, 3, timeout=60)
     for r in (0, 1):
-        assert out[r]["missing"] == [2] and 0.9 < out[r]["waited"] < 2.4
+        assert out[r]["missing"] == [2] and 0.9 < out[r]["waited"] < 8.0
