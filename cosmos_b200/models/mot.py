@@ -160,7 +160,8 @@ class WorkspaceAttn(AttnContext):
         return self._ws[key]
 
     def qkv_project(self, h, w, cos, sin, q_norm, k_norm, cfg: MoTConfig, prefix: Optional[KV] = None):
-        if not (h.is_cuda and h.dtype == torch.bfloat16 and cfg.head_dim == 128) or torch.is_grad_enabled():
+        if (not (h.is_cuda and h.dtype == torch.bfloat16 and cfg.head_dim == 128) or torch.is_grad_enabled()
+                or ops.get_backend() == "library"):
             return super().qkv_project(h, w, cos, sin, q_norm, k_norm, cfg, prefix)
         b, s, _ = h.shape
         n_pre = 0 if prefix is None else prefix[0].shape[1]

@@ -47,6 +47,26 @@ def extension_loaded() -> bool:
     return _loaded
 
 
+# "own" = the hand-written sm_100a kernels for CUDA bf16 tensors (the product); "library" = the same ops on
+# PyTorch's library kernels (ops/library.py), the comparison arm of the benchmarks.
+_backend = os.environ.get("COSMOS_OPS_BACKEND", "own")
+
+
+def set_backend(name: str) -> None:
+    global _backend
+    if name not in ("own", "library"):
+        raise ValueError("backend must be 'own' or 'library'")
+    _backend = name
+
+
+def get_backend() -> str:
+    return _backend
+
+
+def _library(t: torch.Tensor) -> bool:
+    return _backend == "library" and t.is_cuda
+
+
 def _grad_needed(*tensors) -> bool:
     return torch.is_grad_enabled() and any(isinstance(t, torch.Tensor) and t.requires_grad for t in tensors)
 
@@ -55,7 +75,7 @@ def _use_cuda(t: torch.Tensor, *others) -> bool:
     """True when the call should run the forward sm_100a kernel directly: CUDA bf16 input and no autograd
     graph to build. Calls that need gradients go through `_train_cuda` (autograd functions over the forward
     and backward kernels). A CUDA bf16 call without the kernel library raises: there is no silent fallback."""
-    if not (t.is_cuda and t.dtype == torch.bfloat16):
+    if not (t.is_cuda and t.dtype == torch.bfloat16) or _backend == "library":
         return False
     if _grad_needed(t, *others):
         return False
@@ -71,7 +91,7 @@ def _train_cuda(t: torch.Tensor, *others) -> bool:
     kernels (ops/autograd.py): CUDA bf16 input, gradients required, kernel library present.
     COSMOS_TRAIN_LIBRARY_BACKWARD=1 selects the PyTorch / library baseline instead."""
     import os
-    if not (t.is_cuda and t.dtype == torch.bfloat16 and _grad_needed(t, *others)):
+    if not (t.is_cuda and t.dtype == torch.bfloat16 and _grad_needed(t, *others)) or _backend == "library":
         return False
     if os.environ.get("COSMOS_TRAIN_LIBRARY_BACKWARD") == "1":
         return False
@@ -149,6 +169,13 @@ def gemm(a, w, bias=None, epi: int = EPI_PLAIN, resid=None, gate=None, rows_per_
     """a [.., K] @ w[N, K]^T with a fused epilogue (see csrc/gemm_tcgen05.cu)."""
     if _use_cuda(a, w, bias, resid, gate):
         return _k().gemm(a, w, bias, epi, resid, gate, rows_per_batch, out)
+    if _library(a):
+        from . import library as lib
+        r = lib.gemm(a, w, bias, epi, resid, gate, rows_per_batch)
+        if out is not None:
+            out.copy_(r.reshape(out.shape))
+            return out
+        return r
     if a.is_cuda and a.dtype != torch.float32:
         from . import diff
         r = diff.gemm(a, w, bias, epi, resid, gate, rows_per_batch)
@@ -164,7 +191,7 @@ def gemm_grouped2(a0, w0, a1, w1, epi: int = EPI_PLAIN, resid0=None, resid1=None
                   rows_per_batch0: int = 0, rows_per_batch1: int = 0):
     """Two GEMMs with their own weights in ONE persistent launch (MoT per-modality routing: AR
     tokens x AR weights, DM tokens x DM weights). Returns (c0, c1)."""
-    if _use_cuda(a0, w0, a1, w1, resid0, resid1, gate0, gate1) and a1.is_cuda and a1.dtype == torch.bfloat16:
+    if (_use_cuda(a0, w0, a1, w1, resid0, resid1, gate0, gate1) and a1.is_cuda and a1.dtype == torch.bfloat16):
         return _k().gemm_grouped2(a0, w0, a1, w1, epi, resid0, resid1, gate0, gate1, rows_per_batch0, rows_per_batch1)
     return (gemm(a0, w0, None, epi, resid0, gate0, rows_per_batch0),
             gemm(a1, w1, None, epi, resid1, gate1, rows_per_batch1))
@@ -180,7 +207,11 @@ def gemm_qkv_rope(a, w, bias, cos, sin, gamma_q, gamma_k, n_q_heads: int, n_k_he
         return _k().gemm_qkv_rope(a, w, bias, cos, sin, gamma_q, gamma_k, n_q_heads, n_k_heads, eps,
                                   route_ptr, route_ld, out)
     assert route_ptr is None, "routed epilogue is CUDA-only"
-    r = ref.gemm_qkv_rope(a, w, bias, cos, sin, gamma_q, gamma_k, n_q_heads, n_k_heads, eps)
+    if _library(a):
+        from . import library as lib
+        r = lib.gemm_qkv_rope(a, w, bias, cos, sin, gamma_q, gamma_k, n_q_heads, n_k_heads, eps)
+    else:
+        r = ref.gemm_qkv_rope(a, w, bias, cos, sin, gamma_q, gamma_k, n_q_heads, n_k_heads, eps)
     if out is not None:
         out.copy_(r.reshape(out.shape))
         return out
@@ -196,6 +227,13 @@ def attention(q, k, v, scale: Optional[float] = None, mask: int = MASK_FULL, n_a
         o, lse = _k().attn_fwd(q, k, v, scale, mask, n_ar, return_lse, dest_ptr, rows_per_dest, out)
         return o, (lse if return_lse else None)
     assert dest_ptr is None, "routed epilogue is CUDA-only"
+    if _library(q) and not _grad_needed(q, k, v):
+        from . import library as lib
+        o, lse = lib.attention(q, k, v, scale, mask, n_ar, return_lse)
+        if out is not None:
+            out.copy_(o)
+            o = out
+        return o, lse
     if q.is_cuda and q.dtype != torch.float32 and _grad_needed(q, k, v):
         from . import diff
         o, lse = diff.attention(q, k, v, scale, mask, n_ar, return_lse)
@@ -215,6 +253,9 @@ def rmsnorm(x, gamma=None, eps: float = 1e-6, residual=None):
     if residual is None and _train_cuda(x, gamma) and x.shape[-1] % 8 == 0 and x.shape[-1] <= 8192:
         from . import autograd as own
         return own.rmsnorm(x, gamma, eps), None
+    if _library(x):
+        from . import library as lib
+        return lib.rmsnorm(x, gamma, eps, residual)
     return ref.rmsnorm(x, gamma, eps, residual)
 
 
@@ -226,6 +267,9 @@ def adaln_rmsnorm(x, gamma, shift, scale, rows_per_batch: int, eps: float = 1e-6
             and (x.numel() // d) % rows_per_batch == 0 and shift.numel() // d in (1, (x.numel() // d) // rows_per_batch)):
         from . import autograd as own
         return own.adaln_rmsnorm(x, gamma, shift, scale, rows_per_batch, eps)
+    if _library(x):
+        from . import library as lib
+        return lib.adaln_rmsnorm(x, gamma, shift, scale, rows_per_batch, eps)
     return ref.adaln_rmsnorm(x, gamma, shift, scale, rows_per_batch, eps)
 
 
@@ -235,6 +279,9 @@ def mrope(x, cos=None, sin=None, gamma=None, eps: float = 1e-6):
     if _use_cuda(x, gamma) and x.shape[-1] == 128:
         _k().mrope_(x, cos, sin, gamma, eps)
         return x
+    if _library(x):
+        from . import library as lib
+        return lib.mrope(x, cos, sin, gamma, eps)
     return ref.mrope(x, cos, sin, gamma, eps)
 
 
@@ -244,6 +291,9 @@ def gated_residual(x, f, gate=None, rows_per_batch: int = 1):
     if _train_cuda(x, f, gate) and _gate_ok(x, gate, rows_per_batch):
         from . import autograd as own
         return own.gated_residual(x, f, gate, rows_per_batch)
+    if _library(x):
+        from . import library as lib
+        return lib.gated_residual(x, f, gate, rows_per_batch)
     return ref.gated_residual(x, f, gate, rows_per_batch)
 
 
@@ -264,12 +314,16 @@ def swiglu(gate_up):
     if _train_cuda(gate_up) and gate_up.shape[-1] % 16 == 0:
         from . import autograd as own
         return own.swiglu(gate_up)
+    if _library(gate_up):
+        from . import library as lib
+        return lib.swiglu(gate_up)
     return ref.swiglu(gate_up)
 
 
 def cfg_euler_step(x, vc, vu, guidance: float, dt: float, normalize: bool = False):
     """x fp32 latent [rows, d]; CUDA path updates x in place and returns it."""
-    if x.is_cuda and vc.dtype == torch.bfloat16 and load_extension() and x.shape[-1] % 8 == 0 and x.shape[-1] <= 1024:
+    if (_backend != "library" and x.is_cuda and vc.dtype == torch.bfloat16 and load_extension() and x.shape[-1] % 8 == 0
+            and x.shape[-1] <= 1024):
         _k().cfg_euler_step_(x, vc.contiguous(), None if vu is None else vu.contiguous(), guidance, dt, normalize)
         return x
     return ref.cfg_euler_step(x, vc, vu, guidance, dt, normalize)

@@ -48,6 +48,10 @@ class SymmGroup:
         self._meets: Dict[str, int] = {}
         self.pads = self.alloc("__pads__", PAD_WORDS * 4, zero=True)
         self.pads_dev = torch.tensor(self.pads.peer_ptrs, dtype=torch.int64, device=device)
+        # Epochs of the signal slots that kernels advance themselves (CUDA-graph-safe collectives): one int32 per
+        # slot, owned by the group like the pads they are compared with, so every user of a slot (a second
+        # TPContext or decoder on the same ranks, an engine that is rebuilt) continues one epoch stream.
+        self.counters = torch.zeros(N_SLOTS, dtype=torch.int32, device=device)
         self.barrier_host()
 
     # ------------------------------------------------------------------ allocation
@@ -107,6 +111,26 @@ class SymmGroup:
             torch.ops.cosmos_b200.comm_barrier(self.pads_dev, self.rank, self.world, slot, self.next_epoch(slot))
         else:
             dist.barrier(self.group)
+
+    def barrier_counted(self, slot: int) -> None:
+        """Device-side barrier whose epoch lives in `self.counters[slot]` (advanced by the kernel): the launch
+        arguments never change, so the call may be captured in a CUDA graph. A slot is used either this way or
+        through `barrier` (host-side epochs), never both."""
+        if self.world == 1:
+            return
+        if self.on_gpu:
+            torch.ops.cosmos_b200.comm_barrier_counted(self.pads_dev, self.rank, self.world, slot, self.counters)
+        else:
+            dist.barrier(self.group)
+
+    def use_multicast(self, buf: "SymmBuffer") -> int:
+        """NVLink multicast address of `buf` for the multimem kernels, or 0 (no mapping, or COSMOS_NVLS=0:
+        plain peer loads; runs whose ranks may leave mid-job keep it off, a rank that dies while bound to a
+        multicast object can fault its peers)."""
+        import os
+        if os.environ.get("COSMOS_NVLS", "1") == "0":
+            return 0
+        return int(buf.multicast_ptr or 0)
 
     def barrier_host(self) -> None:
         if self.world > 1 and dist.is_initialized():

@@ -48,6 +48,7 @@ class TPContext(AttnContext):
         self._wcache: Dict = {}
         self._ws: Dict = {}
         self._ar_epoch = 0
+        self._arn_parity = 0
 
     @property
     def cp(self) -> int:
@@ -169,8 +170,9 @@ class TPContext(AttnContext):
                 p = (r + i) % tp  # own block first, then staggered so that no peer is hit by all ranks at once
                 partial_fn(slice(p * s_loc, (p + 1) * s_loc), peers[p])
             self.sg.barrier(slot=8)
-            acc = mine.float().sum(0).to(like.dtype)
-            out = ops.gated_residual(resid, acc, gate, rows_per_batch)
+            # one kernel: sum of the tp partial products (fp32) + gate + residual
+            out = torch.ops.cosmos_b200.sum_partials_gated_residual(
+                mine, resid, gate, rows_per_batch if gate is not None else 0).view(resid.shape)
             self.sg.barrier(slot=9)  # partial buffers may be overwritten again
             return out
         part = partial_fn(slice(0, s), None)
@@ -192,15 +194,57 @@ class TPContext(AttnContext):
             mine, ptrs = self._ws[key]
             mine.copy_(x.reshape(-1))
             out = torch.empty_like(x)
-            if not hasattr(self, "_ar_counters"):
-                self._ar_counters = torch.zeros(64, dtype=torch.int32, device=x.device)
-            # epochs of signal slots 16..47 (one row per block) are tracked on the device, so the call is CUDA-graph safe
+            # epochs of signal slots 16..47 (one row per block) are tracked on the device (the group's counters,
+            # shared by every user of these slots), so the call is CUDA-graph safe
             torch.ops.cosmos_b200.allreduce_oneshot(ptrs, self.sg.pads_dev, out.view(-1), self.rank, self.tp, 16, 0,
-                                                    self._ar_counters)
+                                                    self.sg.counters)
             return out
         y = x.contiguous()
         dist.all_reduce(y, group=self.group)
         return y
+
+    def gemm_allreduce_norm(self, a: torch.Tensor, w: torch.Tensor, resid: Optional[torch.Tensor],
+                            gamma: Optional[torch.Tensor], eps: float, want_norm: bool = True):
+        """Row-parallel projection of a decode step in two launches: x_new = resid + sum over ranks of (a w^T) and
+        h = rmsnorm(x_new) * gamma -> (h, x_new). Fused path: the GEMM leaves its split-K partial sums, and ONE
+        kernel reduces them into this rank's symmetric buffer, meets the peers on the device, sums the ranks'
+        buffers (multimem.ld_reduce through the NVLink switch when the buffer has a multicast mapping, else peer
+        loads), adds the residual and applies the norm. Two buffers alternate between consecutive calls, which is
+        what lets the kernel do without a trailing barrier; `begin_step` must open every step / CUDA graph."""
+        m = a.numel() // a.shape[-1]
+        n = w.shape[0]
+        if (self.tp > 1 and self.fused and a.is_cuda and a.dtype == torch.bfloat16 and n % 8 == 0 and n <= 8192
+                and not torch.is_grad_enabled()):
+            key = ("arn", m, n)
+            if key not in self._ws:
+                entries = []
+                for i in range(2):
+                    buf = self.sg.alloc(f"tp_arn_{m}_{n}_{i}", m * n * 2)
+                    entries.append((buf.view(0, (m, n), a.dtype),
+                                    torch.tensor(buf.peer_ptrs, dtype=torch.int64, device=a.device),
+                                    self.sg.use_multicast(buf)))
+                self._ws[key] = entries
+            self._arn_parity ^= 1
+            own, ptrs, mc = self._ws[key][self._arn_parity]
+            h, x_new = torch.ops.cosmos_b200.gemm_allreduce_norm(
+                a, w, resid, gamma, eps, ptrs, mc, own, self.sg.pads_dev, self.rank, self.tp, 16, self.sg.counters,
+                want_norm)
+            shape = tuple(a.shape[:-1]) + (n,)
+            return h.view(shape), x_new.view(shape)
+        y = self._all_reduce(ops.gemm(a, w))
+        if resid is None:
+            return (ops.rmsnorm(y, gamma, eps)[0] if want_norm else y), y
+        if not want_norm:
+            x_new = resid + y
+            return x_new, x_new
+        return ops.rmsnorm(y, gamma, eps, residual=resid)
+
+    def begin_step(self) -> None:
+        """Opens a decode step (or its CUDA graph): one device barrier, after which every peer has finished
+        reading the buffers of the previous step, and the buffer alternation restarts."""
+        self._arn_parity = 0
+        if self.tp > 1 and self.fused:
+            self.sg.barrier_counted(slot=15)
 
     # ------------------------------------------------------------------ AttnContext interface
     def qkv_project(self, h, w, cos, sin, q_norm, k_norm, cfg: MoTConfig, prefix: Optional[KV] = None):

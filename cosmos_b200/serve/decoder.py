@@ -124,6 +124,23 @@ class TPDecoder:
         a = ops.gemm(h, p["w_gate_up"], epi=ops.EPI_SWIGLU)
         return ops.gemm_reduce_rmsnorm(a, p["w_down"], x, next_gamma, cfg.rms_eps)
 
+    def _layer_tp(self, li: int, h: torch.Tensor, x: torch.Tensor, next_gamma: torch.Tensor, cos, sin, slots,
+                  table, lens, max_len: int):
+        """One layer on a tensor-parallel rank with the fused collectives: each row-parallel projection is a GEMM
+        that leaves its split-K partial sums plus ONE kernel that reduces them, meets the peers, sums over the ranks
+        (through the NVLink switch when a multicast mapping exists), adds the residual and applies the next norm."""
+        p = self.layers[li]
+        cfg = self.cfg
+        b = x.shape[0]
+        tpc = self._tpctx
+        qkv = ops.gemm(h, p["wqkv"]).view(b, self.hq + 2 * self.hk, self.hd)
+        q = ops.decode_qkv_post(qkv, self.hq, cos, sin, p["q_norm"], p["k_norm"], cfg.rms_eps, slots,
+                                self.cache.k[li], self.cache.v[li])
+        o = ops.paged_decode(q, self.cache.k[li], self.cache.v[li], table, lens, max_len=max_len)
+        h, x = tpc.gemm_allreduce_norm(o.view(b, -1), p["wo"], x, p["norm2"], cfg.rms_eps)
+        a = ops.gemm(h, p["w_gate_up"], epi=ops.EPI_SWIGLU)
+        return tpc.gemm_allreduce_norm(a, p["w_down"], x, next_gamma, cfg.rms_eps)
+
     def _step_impl(self) -> None:
         """Consumes self.tokens / self.lens (device), writes self.next_tokens and advances lens."""
         b = self.tokens.shape[0]
@@ -146,6 +163,13 @@ class TPDecoder:
             for li in range(n):
                 nxt = self.layers[li + 1]["norm1"] if li + 1 < n else self.final_norm
                 h, x = self._layer_single(li, h, x, nxt, cos, sin, slots, self.table, self.lens, self.max_len)
+        elif self.fused and os.environ.get("COSMOS_DECODE_FUSED_AR", "1") != "0":
+            self._tpctx.begin_step()
+            h, _ = ops.rmsnorm(x, self.layers[0]["norm1"], self.cfg.rms_eps)
+            n = self.cfg.n_layers
+            for li in range(n):
+                nxt = self.layers[li + 1]["norm1"] if li + 1 < n else self.final_norm
+                h, x = self._layer_tp(li, h, x, nxt, cos, sin, slots, self.table, self.lens, self.max_len)
         else:
             delta = None
             for li in range(self.cfg.n_layers):

@@ -77,8 +77,11 @@ class Trainer:
             for n, p in model.named_parameters():
                 if n.startswith("ar.") or n in ("embed", "ar_norm", "lm_head"):
                     p.requires_grad_(False)
+        # replicas (dp_replicate axis) hold the same shards; their gradients are averaged at the optimizer step
+        rep = mesh.size("dp_replicate")
+        rep_group = mesh.group("dp_replicate") if rep > 1 and dist.is_initialized() else None
         self.fsdp = FSDP(model, group, ranks, towers, tc.fused, tc.lr, weight_decay=tc.weight_decay,
-                         max_grad_norm=tc.max_grad_norm)
+                         max_grad_norm=tc.max_grad_norm, replicate_group=rep_group, replicate_size=rep)
         self.ctx = LOCAL_ATTN
         if mesh.size("cp") > 1:
             from .parallel.ulysses import UlyssesAttn

@@ -74,22 +74,33 @@ __device__ __forceinline__ uint64_t add2(uint64_t a, uint64_t b) {
   return r;
 }
 
-// Two exponentials at once on the FMA pipe with packed fp32 instructions (about five issue slots
-// per element, against one slot but eight cycles of the 4-lane-per-scheduler MUFU pipe):
-// round-to-nearest split x = n + f with f in [-0.5, 0.5], degree-3 minimax polynomial for 2^f
-// (max relative error 7.5e-5, far below the bf16 rounding of P), exponent add for 2^n.
-__device__ __forceinline__ void ex2_poly2(uint64_t x2, float& r0, float& r1) {
-  float a, b;
-  unpack2(x2, a, b);
-  a = fmaxf(a, -126.f);
-  b = fmaxf(b, -126.f);
-  const uint64_t xc = pack2(a, b);
-  const uint64_t t2 = add2(xc, pack2(12582912.f, 12582912.f));
-  const uint64_t n2 = add2(t2, pack2(-12582912.f, -12582912.f));
-  const uint64_t f2 = fma2(n2, pack2(-1.f, -1.f), xc);
-  uint64_t p2 = fma2(pack2(0.0551716648f, 0.0551716648f), f2, pack2(0.2426111251f, 0.2426111251f));
-  p2 = fma2(p2, f2, pack2(0.6932609677f, 0.6932609677f));
-  p2 = fma2(p2, f2, pack2(0.9999280572f, 0.9999280572f));
+// Two exponentials at once on the FMA pipe with packed fp32 instructions, for scores already turned into
+// x = s * scale_log2 - m with x >= -126 (the caller clamps the raw score, one FMNMX each):
+// round-to-nearest split x = n + f with f in [-0.5, 0.5] by the magic-number add (the integer n sits in the low
+// mantissa bits of t = x + 1.5 * 2^23), degree-3 minimax polynomial for 2^f (max relative error 7.5e-5, far below
+// the bf16 rounding of P), and 2^n applied by adding n << 23 to the exponent field. Per pair: 2 packed adds,
+// 4 packed FMAs and 2 shift-adds, against 2 x 8 cycles of the 4-lane-per-scheduler MUFU pipe.
+struct Ex2Consts {
+  uint64_t magic, neg_magic, minus1, c3, c2, c1, c0;
+};
+__device__ __forceinline__ Ex2Consts ex2_consts() {
+  Ex2Consts c;
+  c.magic = pack2(12582912.f, 12582912.f);
+  c.neg_magic = pack2(-12582912.f, -12582912.f);
+  c.minus1 = pack2(-1.f, -1.f);
+  c.c3 = pack2(0.0551716648f, 0.0551716648f);
+  c.c2 = pack2(0.2426111251f, 0.2426111251f);
+  c.c1 = pack2(0.6932609677f, 0.6932609677f);
+  c.c0 = pack2(0.9999280572f, 0.9999280572f);
+  return c;
+}
+__device__ __forceinline__ void ex2_poly2(uint64_t x2, const Ex2Consts& c, float& r0, float& r1) {
+  const uint64_t t2 = add2(x2, c.magic);
+  const uint64_t n2 = add2(t2, c.neg_magic);
+  const uint64_t f2 = fma2(n2, c.minus1, x2);
+  uint64_t p2 = fma2(c.c3, f2, c.c2);
+  p2 = fma2(p2, f2, c.c1);
+  p2 = fma2(p2, f2, c.c0);
   float pa, pb, ta, tb;
   unpack2(p2, pa, pb);
   unpack2(t2, ta, tb);
@@ -103,9 +114,13 @@ __device__ __forceinline__ int kv_limit(int qi, const AttnParams& p) {
   return p.Skv;
 }
 
-// EMU: 0 = every exp2 on the MUFU pipe, k = every k-th PAIR of scores on the FMA pipe.
+// EMU: of every 8 pairs of scores, EMU pairs take their exp2 on the FMA pipe (ex2_poly2), the rest on the MUFU pipe.
 // DBG: honour AttnParams::debug (timing experiments); the production instantiation ignores it so
 // that the inner loops carry no tests of it.
+// Measured and not kept: one "P ready" arrival per softmax warp instead of one per thread (slower); packed
+// ex2.approx.f16x2 / bf16x2 (the MUFU pipe retires them at half the instruction rate, so no gain), and P in
+// fp16 with V in bf16 is not possible at all: tcgen05.mma kind::f16 with an fp16 A and a bf16 B operand is an
+// illegal instruction on sm_100a.
 template <int EMU, bool DBG>
 __global__ void __launch_bounds__(ATT_THREADS, 1)
 flash_attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
@@ -212,8 +227,13 @@ flash_attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
         for (int i = first; i < issued; ++i)
           mbar_wait(kv_full(i % NSLOT), (i / NSLOT) & 1, &no_abort, nullptr, 0);
       }
-    } else if (warp == 1 && lane == 0) {
-      // ---------------- MMA issuer
+    } else if (warp == 1) {
+      // ---------------- MMA issuer: the whole warp walks the schedule (barrier phases, descriptors and
+      // addresses are warp-uniform values), one elected lane issues the tcgen05 instructions
+      const bool issuer = elect_one();
+      auto wait_all = [&](uint32_t bar, uint32_t phase) {
+        return __all_sync(0xffffffffu, mbar_wait(bar, phase, abort_flag, p.status, ST_TIMEOUT_MMA)) != 0;
+      };
       constexpr uint32_t idesc_qk = make_idesc_bf16(TQ, TKV, 0, 0);
       constexpr uint32_t idesc_pv = make_idesc_bf16(TQ, HD, 0, 1);
       // Descriptors differ only in their 14-bit start-address field, so they are built as
@@ -225,12 +245,15 @@ flash_attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
         const uint32_t d = tmem_base + t * 128;
         const uint64_t a0 = q_desc0 + uint64_t(t * (TILE_BYTES >> 4));
         const uint64_t b0 = k_desc0 + uint64_t(slot * (TILE_BYTES >> 4));
-        if (dbg & 1) return;
+        if ((dbg & 1) || !issuer) return;
 #pragma unroll
         for (int kk = 0; kk < 8; ++kk) {
           const uint32_t off = (kk >> 2) * (HALF_BYTES >> 4) + 2 * (kk & 3);
           mma_ss(d, a0 + off, b0 + off, idesc_qk, kk > 0 ? 1u : 0u);
         }
+      };
+      auto commit = [&](uint32_t bar) {
+        if (issuer) tc_commit(bar);
       };
       // P is handed over in two halves of 64 keys, so the first four k-steps of PV run while the
       // softmax warps still compute the exponentials of the second half.
@@ -238,51 +261,53 @@ flash_attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
         const uint32_t d = tmem_base + 256 + t * 128;
         const uint32_t a0 = tmem_base + t * 128;
         const uint64_t b0 = v_desc0 + uint64_t(slot * (TILE_BYTES >> 4));
-        if (dbg & 2) return;
+        if ((dbg & 2) || !issuer) return;
 #pragma unroll
         for (int k4 = 0; k4 < 4; ++k4) {
           const int kk = half * 4 + k4;
           mma_ts(d, a0 + kk * 8, b0 + uint64_t(kk * (2048 >> 4)), idesc_pv, (acc || kk > 0) ? 1u : 0u);
         }
       };
-      bool ok = mbar_wait(q_full, 0, abort_flag, p.status, ST_TIMEOUT_MMA);
-      if (ok) ok = mbar_wait(kv_full(0), 0, abort_flag, p.status, ST_TIMEOUT_MMA);
+      bool ok = wait_all(q_full, 0);
+      if (ok) ok = wait_all(kv_full(0), 0);
       if (ok) {
         tc_fence_after();
         issue_qk(0, 0);
-        tc_commit(s_full(0));
+        commit(s_full(0));
         issue_qk(1, 0);
-        tc_commit(s_full(1));
-        tc_commit(kv_empty(0));
+        commit(s_full(1));
+        commit(kv_empty(0));
+        __syncwarp();
       }
       for (int j = 0; j < n_blocks && ok; ++j) {
         const int iv = 2 * j + 1, ik = 2 * j + 2;
         const int sv = iv % NSLOT, sk = ik % NSLOT;
         const bool more = (j + 1 < n_blocks);
-        ok = mbar_wait(kv_full(sv), (iv / NSLOT) & 1, abort_flag, p.status, ST_TIMEOUT_MMA);
-        if (ok && more)
-          ok = mbar_wait(kv_full(sk), (ik / NSLOT) & 1, abort_flag, p.status, ST_TIMEOUT_MMA);
+        ok = wait_all(kv_full(sv), (iv / NSLOT) & 1);
+        if (ok && more) ok = wait_all(kv_full(sk), (ik / NSLOT) & 1);
         if (!ok) break;
 #pragma unroll 1
         for (int t = 0; t < 2; ++t) {
-          ok = mbar_wait(p_full(t, 0), j & 1, abort_flag, p.status, ST_TIMEOUT_MMA);
+          ok = wait_all(p_full(t, 0), j & 1);
           if (!ok) break;
           tc_fence_after();
           issue_pv(t, sv, j > 0, 0);
-          ok = mbar_wait(p_full(t, 1), j & 1, abort_flag, p.status, ST_TIMEOUT_MMA);
+          ok = wait_all(p_full(t, 1), j & 1);
           if (!ok) break;
           tc_fence_after();
           issue_pv(t, sv, j > 0, 1);
           if (more) {
             issue_qk(t, sk);
-            tc_commit(s_full(t));
+            commit(s_full(t));
           } else {
-            tc_commit(o_final(t));
+            commit(o_final(t));
           }
+          __syncwarp();
         }
         if (!ok) break;
-        tc_commit(kv_empty(sv));
-        if (more) tc_commit(kv_empty(sk));
+        commit(kv_empty(sv));
+        if (more) commit(kv_empty(sk));
+        __syncwarp();
       }
     }
   } else {
@@ -297,6 +322,8 @@ flash_attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
     const uint32_t s_addr = lane_addr + t * 128;
     const uint32_t o_addr = lane_addr + 256 + t * 128;
     const float sl2 = p.scale_log2;
+    const float inv_sl2 = 1.f / sl2;
+    const Ex2Consts exc = ex2_consts();
     float m_used = -1e30f, l = 0.f;
     bool ok = true;
     for (int j = 0; j < n_blocks; ++j) {
@@ -351,6 +378,8 @@ flash_attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
       // pipe, packed partial sums
       const uint64_t sl2_2 = pack2(sl2, sl2);
       const uint64_t negm_2 = pack2(-m_used, -m_used);
+      // raw-score floor that keeps x >= -126 on the polynomial path (masked scores, -inf, land there too)
+      const float s_floor = (m_used - 126.f) * inv_sl2;
       uint64_t ls2[4] = {0ull, 0ull, 0ull, 0ull};
 #pragma unroll
       for (int half = 0; half < 2; ++half) {
@@ -358,11 +387,13 @@ flash_attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
 #pragma unroll
         for (int i = 0; i < 32; ++i) {
           const int e = half * 64 + 2 * i;
-          const uint64_t x2 = fma2(pack2(__uint_as_float(s[e]), __uint_as_float(s[e + 1])), sl2_2, negm_2);
           float p0, p1;
-          if (EMU > 0 && (i % (EMU > 0 ? EMU : 1)) == EMU - 1) {
-            ex2_poly2(x2, p0, p1);
+          if (EMU > 0 && (i & 7) < EMU) {
+            const uint64_t x2 = fma2(pack2(fmaxf(__uint_as_float(s[e]), s_floor), fmaxf(__uint_as_float(s[e + 1]), s_floor)),
+                                     sl2_2, negm_2);
+            ex2_poly2(x2, exc, p0, p1);
           } else {
+            const uint64_t x2 = fma2(pack2(__uint_as_float(s[e]), __uint_as_float(s[e + 1])), sl2_2, negm_2);
             unpack2(x2, p0, p1);
             if (!(dbg & 4)) {
               p0 = ex2(p0);
@@ -456,20 +487,23 @@ void flash_attn_fwd(const AttnArgs& a, cudaStream_t stream) {
   if ((a.o_stride_s % 8) || (a.o_stride_h % 8) || (a.o_stride_b % 8))
     throw std::runtime_error("flash_attn_fwd: output strides must be multiples of 8 elements");
   using Kern = void (*)(const CUtensorMap, const CUtensorMap, const CUtensorMap, const cb::AttnParams);
-  // a.exp_emulation: 0 = all exp2 on the MUFU pipe, k = every k-th pair of scores on the FMA pipe
+  // a.exp_emulation: of every 8 pairs of scores, this many take their exp2 on the FMA pipe (0, 2 or 3; measured
+  // slower than 0 whenever the MMAs run); a.debug: timing experiments (wrong results)
   Kern kern = cb::flash_attn_fwd_kernel<0, false>;
   if (a.debug) {
-    kern = a.exp_emulation == 4 ? cb::flash_attn_fwd_kernel<4, true> : cb::flash_attn_fwd_kernel<0, true>;
+    switch (a.exp_emulation) {
+      case 2: kern = cb::flash_attn_fwd_kernel<2, true>; break;
+      case 3: kern = cb::flash_attn_fwd_kernel<3, true>; break;
+      default: kern = cb::flash_attn_fwd_kernel<0, true>; break;
+    }
   } else {
     switch (a.exp_emulation) {
       case 2: kern = cb::flash_attn_fwd_kernel<2, false>; break;
       case 3: kern = cb::flash_attn_fwd_kernel<3, false>; break;
-      case 4: kern = cb::flash_attn_fwd_kernel<4, false>; break;
-      case 6: kern = cb::flash_attn_fwd_kernel<6, false>; break;
       default: break;
     }
   }
-  static thread_local Kern configured[8] = {};
+  static thread_local Kern configured[12] = {};
   bool seen = false;
   for (Kern k : configured) seen |= (k == kern);
   if (!seen) {

@@ -14,6 +14,7 @@
 #include "runtime.h"
 
 namespace {
+constexpr int kDefaultAttnExpEmu = 0;
 
 using at::Tensor;
 using OptT = std::optional<Tensor>;
@@ -326,6 +327,17 @@ Tensor gemm_qkv_rope(const Tensor& A_, const Tensor& W, const OptT& bias, const 
   return C.reshape(shape);
 }
 
+// Forward-attention switches: share of exponentials on the FMA pipe (AttnArgs::exp_emulation, initial value from
+// COSMOS_ATTN_EXP_EMU) and the timing-experiment bits (AttnArgs::debug, COSMOS_ATTN_DEBUG).
+static int& attn_exp_emu() {
+  static int v = [] { const char* e = std::getenv("COSMOS_ATTN_EXP_EMU"); return e ? std::atoi(e) : kDefaultAttnExpEmu; }();
+  return v;
+}
+static int& attn_debug() {
+  static int v = [] { const char* e = std::getenv("COSMOS_ATTN_DEBUG"); return e ? std::atoi(e) : 0; }();
+  return v;
+}
+
 // q [B, Sq, Hq, 128], k/v [B, Skv, Hkv, 128] (any strides with unit inner stride) -> (o, lse)
 std::tuple<Tensor, Tensor> attn_fwd(const Tensor& q, const Tensor& k, const Tensor& v, double scale,
                                     int64_t mask, int64_t n_ar, bool return_lse, const OptT& dest_ptr,
@@ -373,10 +385,8 @@ std::tuple<Tensor, Tensor> attn_fwd(const Tensor& q, const Tensor& k, const Tens
   }
   a.status = status_tensor(q.get_device()).data_ptr<int>();
   {
-    static const int emu = [] { const char* e = std::getenv("COSMOS_ATTN_EXP_EMU"); return e ? std::atoi(e) : 0; }();
-    a.exp_emulation = emu;
-    static const int dbg = [] { const char* e = std::getenv("COSMOS_ATTN_DEBUG"); return e ? std::atoi(e) : 0; }();
-    a.debug = dbg;
+    a.exp_emulation = attn_exp_emu();
+    a.debug = attn_debug();
   }
   cosmos::flash_attn_fwd(a, cur_stream());
   return {o, lse};
@@ -782,6 +792,14 @@ void comm_barrier(const Tensor& pads, int64_t rank, int64_t world, int64_t slot,
                        status_tensor(pads.get_device()).data_ptr<int>(), cur_stream());
 }
 
+void comm_barrier_counted(const Tensor& pads, int64_t rank, int64_t world, int64_t slot, Tensor counters) {
+  c10::cuda::CUDAGuard guard(pads.device());
+  TORCH_CHECK(pads.numel() >= world, "one signal pad address per rank is needed");
+  TORCH_CHECK(counters.is_cuda() && counters.scalar_type() == at::kInt && counters.numel() > slot, "counters: int32 per slot");
+  cosmos::comm_barrier_counted(ptr_table(pads, "pads"), (int)rank, (int)world, (int)slot, counters.data_ptr<int>(),
+                               status_tensor(pads.get_device()).data_ptr<int>(), cur_stream());
+}
+
 void allreduce_oneshot(const Tensor& bufs, const Tensor& pads, Tensor out, int64_t rank, int64_t world,
                        int64_t slot, int64_t epoch, const OptT& counters) {
   check_bf16_cuda(out, "out");
@@ -837,6 +855,11 @@ Tensor decode_qkv_post(const Tensor& qkv, int64_t n_q_heads, const Tensor& cos_t
 
 bool bounds_check_enabled() { return cosmos::bounds_check_enabled(); }
 void gemm_set_grid_limit(int64_t max_ctas) { cosmos::gemm_set_grid_limit((int)max_ctas); }
+// A/B switches for timing and tests: CTA-pair GEMM tiles on/off, attention forward variant bits.
+void gemm_set_cta_pair(bool on) { cosmos::gemm_set_cta_pair(on); }
+void gemm_set_debug(int64_t bits) { cosmos::gemm_set_debug((int)bits); }
+void attn_set_exp_emulation(int64_t v) { attn_exp_emu() = (int)v; }
+void attn_set_debug(int64_t v) { attn_debug() = (int)v; }
 
 // ok[i] = 1 if 0 <= idx[i] < limit[i] (always 1 in a build without the checks); a failed check also
 // records its status code, exactly as inside the kernels. No memory is addressed through idx.
@@ -864,8 +887,13 @@ void rs_adamw(const Tensor& grads, int64_t world, int64_t shard_off, Tensor mast
   float* sqp = nullptr;
   float* redp = nullptr;
   if (mode == 1) {
-    TORCH_CHECK(sq.has_value() && reduced.has_value() && reduced->numel() == n && reduced->scalar_type() == at::kFloat);
-    sqp = sq->data_ptr<float>(); redp = reduced->data_ptr<float>();
+    // sum of squares of the reduced gradient; the reduced values are kept only when `reduced` is given
+    TORCH_CHECK(sq.has_value() && sq->defined(), "mode 1 needs the sum-of-squares accumulator");
+    sqp = sq->data_ptr<float>();
+    if (reduced.has_value() && reduced->defined()) {
+      TORCH_CHECK(reduced->numel() == n && reduced->scalar_type() == at::kFloat);
+      redp = reduced->data_ptr<float>();
+    }
   } else if (mode == 2) {
     TORCH_CHECK(reduced.has_value() && reduced->numel() == n && reduced->scalar_type() == at::kFloat);
     redp = reduced->data_ptr<float>();
@@ -873,6 +901,129 @@ void rs_adamw(const Tensor& grads, int64_t world, int64_t shard_off, Tensor mast
   cosmos::rs_adamw(ptr_table(grads, "grads"), (int)world, shard_off, n, master.data_ptr<float>(),
                    m.data_ptr<float>(), v.data_ptr<float>(), param_shard.data_ptr(), (float)grad_scale, (float)lr,
                    (float)b1, (float)b2, (float)eps, (float)wd, (int)step, sqp, redp, cur_stream());
+}
+
+// ---- fused communication ops (comm.cu) ----
+// grads / bufs: int64 CUDA tensors with one device address per rank; mc_ptr: NVLink multicast address of the same
+// symmetric buffer (0 = none: plain peer loads).
+void reduce_scatter_pull(const Tensor& grads, int64_t mc_ptr, int64_t world, int64_t shard_off, Tensor out,
+                         bool accumulate, double scale, const OptT& sq) {
+  c10::cuda::CUDAGuard guard(out.device());
+  TORCH_CHECK(out.is_cuda() && out.scalar_type() == at::kFloat && out.is_contiguous(), "out must be contiguous fp32");
+  float* sqp = nullptr;
+  if (sq.has_value() && sq->defined()) {
+    TORCH_CHECK(sq->is_cuda() && sq->scalar_type() == at::kFloat && sq->numel() >= 1);
+    sqp = sq->data_ptr<float>();
+  }
+  cosmos::reduce_scatter_pull(ptr_table(grads, "grads"), reinterpret_cast<const void*>(mc_ptr), (int)world, shard_off,
+                              out.numel(), out.data_ptr<float>(), accumulate, (float)scale, sqp, cur_stream());
+}
+
+void adamw_shard(const Tensor& grad, Tensor master, Tensor m, Tensor v, Tensor param, double grad_scale, double lr,
+                 double b1, double b2, double eps, double wd, int64_t step) {
+  c10::cuda::CUDAGuard guard(grad.device());
+  const int64_t n = grad.numel();
+  TORCH_CHECK(grad.scalar_type() == at::kFloat && grad.is_contiguous() && master.numel() == n && m.numel() == n &&
+                  v.numel() == n && param.numel() == n && param.scalar_type() == at::kBFloat16 &&
+                  master.scalar_type() == at::kFloat && m.scalar_type() == at::kFloat && v.scalar_type() == at::kFloat &&
+                  master.is_contiguous() && m.is_contiguous() && v.is_contiguous() && param.is_contiguous(),
+              "adamw_shard: fp32 grad / master / moments and a bf16 parameter shard of one length");
+  cosmos::adamw_shard(grad.data_ptr<float>(), n, master.data_ptr<float>(), m.data_ptr<float>(), v.data_ptr<float>(),
+                      param.data_ptr(), (float)grad_scale, (float)lr, (float)b1, (float)b2, (float)eps, (float)wd,
+                      (int)step, cur_stream());
+}
+
+// x_new = residual + sum over ranks of (a w^T), h = rmsnorm(x_new) * gamma -> (h, x_new). `own` is this rank's
+// symmetric buffer ([M, N] bf16) that the peers read (`bufs` = its addresses on every rank). A skinny problem runs
+// split-K and the all-reduce kernel sums the fp32 partials itself; otherwise the GEMM epilogue writes `own`.
+// With `a` undefined-size-0 semantics are not supported: a is always given.
+std::tuple<Tensor, Tensor> gemm_allreduce_norm(const Tensor& A_, const Tensor& W, const OptT& residual,
+                                               const OptT& gamma, double eps, const Tensor& bufs, int64_t mc_ptr,
+                                               Tensor own, const Tensor& pads, int64_t rank, int64_t world,
+                                               int64_t slot, Tensor counters, bool want_norm) {
+  check_bf16_cuda(A_, "a"); check_bf16_cuda(W, "w"); check_bf16_cuda(own, "own");
+  c10::cuda::CUDAGuard guard(A_.device());
+  Tensor A = as_2d(A_);
+  const int64_t M = A.size(0), K = A.size(1), N = W.size(0);
+  TORCH_CHECK(W.dim() == 2 && W.size(1) == K && A.stride(1) == 1 && W.stride(1) == 1, "a [.., K] and w [N, K] expected");
+  TORCH_CHECK(A.stride(0) % 8 == 0 && W.stride(0) % 8 == 0 && N % 8 == 0 && N <= 8192, "rows must be 16-byte aligned, N <= 8192");
+  TORCH_CHECK(own.is_contiguous() && own.numel() >= M * N, "own buffer too small");
+  TORCH_CHECK(counters.is_cuda() && counters.scalar_type() == at::kInt && counters.numel() >= 64, "counters: int32[64]");
+  const void* Rp = nullptr;
+  Tensor R;
+  if (residual.has_value() && residual->defined()) {
+    check_bf16_cuda(*residual, "residual");
+    R = as_2d(*residual).contiguous();
+    TORCH_CHECK(R.size(0) == M && R.size(1) == N, "bad residual shape");
+    Rp = R.data_ptr();
+  }
+  if (gamma.has_value() && gamma->defined()) { check_bf16_cuda(*gamma, "gamma"); TORCH_CHECK(gamma->numel() == N && gamma->is_contiguous()); }
+  const int ks = cosmos::gemm_pick_k_splits((int)M, (int)N, (int)K, EPI_PLAIN);
+  cosmos::GemmArgs g;
+  g.A = A.data_ptr(); g.B = W.data_ptr(); g.C = own.data_ptr();
+  g.M = (int)M; g.N = (int)N; g.K = (int)K;
+  g.lda = A.stride(0); g.ldb = W.stride(0); g.ldc = N;
+  g.epi = EPI_PLAIN;
+  g.status = status_tensor(A.get_device()).data_ptr<int>();
+  Tensor partial;
+  if (ks > 1) {
+    partial = at::empty({ks, M, N}, A.options().dtype(at::kFloat));
+    g.k_splits = ks; g.partial = partial.data_ptr<float>(); g.partial_only = true;
+  }
+  cosmos::gemm_bf16(g, cur_stream());
+  Tensor x_new = at::empty({M, N}, A.options());
+  Tensor h = want_norm ? at::empty({M, N}, A.options()) : Tensor();
+  cosmos::allreduce_norm(ptr_table(bufs, "bufs"), reinterpret_cast<const void*>(mc_ptr), own.data_ptr(),
+                         ptr_table(pads, "pads"), (int)rank, (int)world, (int)slot, counters.data_ptr<int>(),
+                         ks > 1 ? partial.data_ptr<float>() : nullptr, ks, (int)M, (int)N, Rp, opt_ptr(gamma), (float)eps,
+                         x_new.data_ptr(), want_norm ? h.data_ptr() : nullptr, g.status, cur_stream());
+  return {want_norm ? h : x_new, x_new};
+}
+
+// The all-reduce (+ residual + RMS-norm) kernel on values that are already in `own`.
+std::tuple<Tensor, Tensor> allreduce_norm(const Tensor& bufs, int64_t mc_ptr, Tensor own, const Tensor& pads,
+                                          int64_t rank, int64_t world, int64_t slot, Tensor counters, int64_t M,
+                                          int64_t N, const OptT& residual, const OptT& gamma, double eps, bool want_norm) {
+  check_bf16_cuda(own, "own");
+  c10::cuda::CUDAGuard guard(own.device());
+  TORCH_CHECK(own.is_contiguous() && own.numel() >= M * N && N % 8 == 0 && N <= 8192, "own: [M, N] bf16, N % 8 == 0, N <= 8192");
+  TORCH_CHECK(counters.is_cuda() && counters.scalar_type() == at::kInt && counters.numel() >= 64, "counters: int32[64]");
+  const void* Rp = nullptr;
+  Tensor R;
+  if (residual.has_value() && residual->defined()) {
+    check_bf16_cuda(*residual, "residual");
+    R = residual->reshape({M, N}).contiguous();
+    Rp = R.data_ptr();
+  }
+  if (gamma.has_value() && gamma->defined()) { check_bf16_cuda(*gamma, "gamma"); TORCH_CHECK(gamma->numel() == N && gamma->is_contiguous()); }
+  Tensor x_new = at::empty({M, N}, own.options());
+  Tensor h = want_norm ? at::empty({M, N}, own.options()) : Tensor();
+  cosmos::allreduce_norm(ptr_table(bufs, "bufs"), reinterpret_cast<const void*>(mc_ptr), own.data_ptr(),
+                         ptr_table(pads, "pads"), (int)rank, (int)world, (int)slot, counters.data_ptr<int>(), nullptr, 1,
+                         (int)M, (int)N, Rp, opt_ptr(gamma), (float)eps, x_new.data_ptr(),
+                         want_norm ? h.data_ptr() : nullptr, status_tensor(own.get_device()).data_ptr<int>(), cur_stream());
+  return {want_norm ? h : x_new, x_new};
+}
+
+// out = resid + gate[row / rows_per_batch] * sum_p part[p]; part [P, rows, d] bf16 contiguous.
+Tensor sum_partials_gated_residual(const Tensor& part, const OptT& resid, const OptT& gate, int64_t rows_per_batch) {
+  check_bf16_cuda(part, "part");
+  c10::cuda::CUDAGuard guard(part.device());
+  TORCH_CHECK(part.dim() >= 3 && part.is_contiguous(), "part must be contiguous [P, rows.., d]");
+  const int64_t P = part.size(0), d = part.size(-1), rows = part.numel() / (P * d);
+  const void* Rp = nullptr; const void* Gp = nullptr;
+  Tensor R, G;
+  if (resid.has_value() && resid->defined()) { check_bf16_cuda(*resid, "resid"); R = resid->contiguous(); TORCH_CHECK(R.numel() == rows * d); Rp = R.data_ptr(); }
+  if (gate.has_value() && gate->defined()) {
+    check_bf16_cuda(*gate, "gate"); G = gate->contiguous();
+    TORCH_CHECK(rows_per_batch > 0 && G.numel() == ((rows + rows_per_batch - 1) / rows_per_batch) * d, "gate: [rows / rows_per_batch, d]");
+    Gp = G.data_ptr();
+  }
+  std::vector<int64_t> shp(part.sizes().begin() + 1, part.sizes().end());
+  Tensor out = at::empty(shp, part.options());
+  cosmos::sum_partials_gated_residual(part.data_ptr(), (int)P, rows, (int)d, Rp, Gp, (int)rows_per_batch, out.data_ptr(),
+                                      cur_stream());
+  return out;
 }
 
 void allgather_pull(const Tensor& srcs, int64_t world, Tensor dst, int64_t bytes_per_rank) {
@@ -912,14 +1063,24 @@ TORCH_LIBRARY(cosmos_b200, m) {
   m.def("paged_decode", &paged_decode);
   m.def("paged_decode_pick_splits", &paged_decode_pick_splits);
   m.def("comm_barrier", &comm_barrier);
+  m.def("comm_barrier_counted", &comm_barrier_counted);
   m.def("allreduce_oneshot", &allreduce_oneshot);
   m.def("kv_cache_write", &kv_cache_write);
   m.def("decode_qkv_post", &decode_qkv_post);
   m.def("bounds_check_enabled", &bounds_check_enabled);
   m.def("gemm_set_grid_limit", &gemm_set_grid_limit);
+  m.def("gemm_set_cta_pair", &gemm_set_cta_pair);
+  m.def("gemm_set_debug", &gemm_set_debug);
+  m.def("attn_set_exp_emulation", &attn_set_exp_emulation);
+  m.def("attn_set_debug", &attn_set_debug);
   m.def("bounds_check_selftest", &bounds_check_selftest);
   m.def("rs_adamw", &rs_adamw);
   m.def("allgather_pull", &allgather_pull);
+  m.def("reduce_scatter_pull", &reduce_scatter_pull);
+  m.def("adamw_shard", &adamw_shard);
+  m.def("gemm_allreduce_norm", &gemm_allreduce_norm);
+  m.def("allreduce_norm", &allreduce_norm);
+  m.def("sum_partials_gated_residual", &sum_partials_gated_residual);
   cosmos::register_runtime_ops(m);
   cosmos::register_safetensors(m);
 }

@@ -4,6 +4,10 @@
 //     with plain P2P loads after a barrier and reduces locally in rank order (deterministic)
 //   * fused reduce-scatter + AdamW: the owner of a parameter shard pulls the matching gradient
 //     slices from every peer, reduces in fp32, and applies the optimizer update in one pass
+//   * reduce-scatter by pull (16-byte peer loads, or one multimem.ld_reduce per vector when the buffer
+//     has an NVLink multicast mapping: the switch adds the ranks' values), fp32 shard out + sum of squares
+//   * decode all-reduce fused with what surrounds it: (split-K partial sums ->) symmetric buffer ->
+//     device barrier -> sum over ranks (peer loads or multimem.ld_reduce) -> + residual -> RMS-norm
 // Peers never run on the same GPU as the waiting kernel (one process per GPU).
 #include "common.cuh"
 #include "kernels.h"
@@ -46,6 +50,19 @@ __device__ __forceinline__ bool barrier_device(const long long* pads, int rank, 
 __global__ void barrier_kernel(const long long* pads, int rank, int world, int slot, int epoch,
                                int* status) {
   barrier_device(pads, rank, world, slot, epoch, status);
+}
+
+// The same barrier with the epoch kept on the device (counters[slot], advanced by the kernel), so the
+// launch arguments never change and the call can sit in a CUDA graph.
+__global__ void barrier_counted_kernel(const long long* pads, int rank, int world, int slot, int* counters,
+                                       int* status) {
+  __shared__ int e_s;
+  if (threadIdx.x == 0) e_s = counters[slot] + 1;
+  __syncthreads();
+  const int epoch = e_s;
+  barrier_device(pads, rank, world, slot, epoch, status);
+  __syncthreads();
+  if (threadIdx.x == 0) counters[slot] = epoch;
 }
 
 // out[i] = sum_r peer_r[i] (bf16, fp32 accumulate); bufs[r] = rank r's input buffer.
@@ -111,8 +128,15 @@ rs_adamw_kernel(const long long* grads, int world, long long shard_off, long lon
     if (reduced_out && !sq_out) {
       g = reduced_out[i];
     } else {
-      for (int r = 0; r < world; ++r)
-        g += __bfloat162float(reinterpret_cast<const bf16*>(grads[r])[shard_off + i]);
+      // all peers' values are requested before the first add (one NVLink round trip, not `world`)
+      for (int r0 = 0; r0 < world; r0 += 8) {
+        bf16 pv[8];
+#pragma unroll
+        for (int r = 0; r < 8; ++r)
+          pv[r] = (r0 + r < world) ? reinterpret_cast<const bf16*>(grads[r0 + r])[shard_off + i] : __float2bfloat16(0.f);
+#pragma unroll
+        for (int r = 0; r < 8; ++r) g += __bfloat162float(pv[r]);
+      }
     }
     if (sq_out) {
       if (reduced_out) reduced_out[i] = g;
@@ -148,6 +172,238 @@ allgather_pull_kernel(const long long* srcs, int world, uint4* __restrict__ dst,
   }
 }
 
+// ------------------------------------------------------------------ NVLink multicast (NVLS)
+// `mc` is the multicast address of a symmetric buffer: a load-reduce through it returns the sum over
+// all ranks' copies, added inside the switch (fp32 accumulation, bf16 result); a store through it
+// writes every rank's copy.
+__device__ __forceinline__ uint4 multimem_ld_reduce_bf16x8(const void* mc) {
+  uint4 v;
+  asm volatile("multimem.ld_reduce.relaxed.sys.global.add.acc::f32.v4.bf16x2 {%0, %1, %2, %3}, [%4];"
+               : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
+               : "l"(mc)
+               : "memory");
+  return v;
+}
+__device__ __forceinline__ void multimem_st_bf16x8(void* mc, uint4 v) {
+  asm volatile("multimem.st.relaxed.sys.global.v4.bf16x2 [%0], {%1, %2, %3, %4};" ::"l"(mc), "r"(v.x),
+               "r"(v.y), "r"(v.z), "r"(v.w)
+               : "memory");
+}
+
+// Sum over ranks of one 8-element bf16 vector at element offset `e` of the ranks' buffers, in fp32.
+template <bool MC>
+__device__ __forceinline__ void gather_sum8(const long long* bufs, const bf16* mc, int world, long long e,
+                                            float (&acc)[8]) {
+  if constexpr (MC) {
+    const uint4 v = multimem_ld_reduce_bf16x8(mc + e);
+    acc[0] = bf16lo(v.x); acc[1] = bf16hi(v.x); acc[2] = bf16lo(v.y); acc[3] = bf16hi(v.y);
+    acc[4] = bf16lo(v.z); acc[5] = bf16hi(v.z); acc[6] = bf16lo(v.w); acc[7] = bf16hi(v.w);
+  } else {
+#pragma unroll
+    for (int i = 0; i < 8; ++i) acc[i] = 0.f;
+    for (int r0 = 0; r0 < world; r0 += 8) {
+      uint4 v[8];
+#pragma unroll
+      for (int r = 0; r < 8; ++r)
+        v[r] = (r0 + r < world) ? *reinterpret_cast<const uint4*>(reinterpret_cast<const bf16*>(bufs[r0 + r]) + e)
+                                : make_uint4(0, 0, 0, 0);
+#pragma unroll
+      for (int r = 0; r < 8; ++r) {
+        acc[0] += bf16lo(v[r].x); acc[1] += bf16hi(v[r].x); acc[2] += bf16lo(v[r].y); acc[3] += bf16hi(v[r].y);
+        acc[4] += bf16lo(v[r].z); acc[5] += bf16hi(v[r].z); acc[6] += bf16lo(v[r].w); acc[7] += bf16hi(v[r].w);
+      }
+    }
+  }
+}
+
+// Reduce-scatter by pull: out[i] (+)= sum_r grad_r[shard_off + i] for this rank's shard, plus the sum of
+// squares of the reduced values (global-norm clipping). The caller has run a group barrier on the stream,
+// so every rank's gradients are in place. n and shard_off are multiples of 8.
+template <bool MC>
+__global__ void __launch_bounds__(256)
+reduce_scatter_pull_kernel(const long long* grads, const bf16* mc, int world, long long shard_off, long long n,
+                           float* __restrict__ out, int accumulate, float scale, float* sq_out) {
+  float local_sq = 0.f;
+  const long long n_vec = n >> 3;
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n_vec;
+       i += (long long)gridDim.x * blockDim.x) {
+    float acc[8];
+    gather_sum8<MC>(grads, mc, world, shard_off + i * 8, acc);
+    float4* o = reinterpret_cast<float4*>(out + i * 8);
+    float4 a = make_float4(acc[0] * scale, acc[1] * scale, acc[2] * scale, acc[3] * scale);
+    float4 b = make_float4(acc[4] * scale, acc[5] * scale, acc[6] * scale, acc[7] * scale);
+    if (accumulate) {
+      const float4 pa = o[0], pb = o[1];
+      a.x += pa.x; a.y += pa.y; a.z += pa.z; a.w += pa.w;
+      b.x += pb.x; b.y += pb.y; b.z += pb.z; b.w += pb.w;
+    }
+    o[0] = a;
+    o[1] = b;
+    local_sq += a.x * a.x + a.y * a.y + a.z * a.z + a.w * a.w + b.x * b.x + b.y * b.y + b.z * b.z + b.w * b.w;
+  }
+  if (sq_out) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) local_sq += __shfl_xor_sync(0xffffffffu, local_sq, o);
+    if ((threadIdx.x & 31) == 0) atomicAdd(sq_out, local_sq);
+  }
+}
+
+// AdamW on a local fp32 gradient shard: g = grad[i] * grad_scale; moments, fp32 master and the bf16
+// parameter shard are updated in one pass.
+__global__ void __launch_bounds__(256)
+adamw_shard_kernel(const float* __restrict__ grad, long long n, float* __restrict__ master, float* __restrict__ m,
+                   float* __restrict__ v, bf16* __restrict__ param_shard, float grad_scale, float lr, float b1,
+                   float b2, float eps, float wd, float bc1, float bc2) {
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n;
+       i += (long long)gridDim.x * blockDim.x) {
+    const float g = grad[i] * grad_scale;
+    const float mi = b1 * m[i] + (1.f - b1) * g;
+    const float vi = b2 * v[i] + (1.f - b2) * g * g;
+    m[i] = mi;
+    v[i] = vi;
+    float w = master[i];
+    w -= lr * ((mi / bc1) / (sqrtf(vi / bc2) + eps) + wd * w);
+    master[i] = w;
+    param_shard[i] = __float2bfloat16(w);
+  }
+}
+
+// Decode all-reduce fused with the operations around it. Per block (one signal-slot row each, so
+// blocks never wait for each other) and for the rows m = blockIdx.x, blockIdx.x + gridDim.x, ...:
+//   1. (partial != null) own[m] = sum_ks partial[ks][m]   the split-K pass of the preceding GEMM, written
+//      as bf16 into this rank's symmetric buffer `own`
+//   2. group barrier (leading only: callers alternate two buffers, so a rank that has passed the
+//      barrier of call c knows every peer has finished reading the buffer of call c - 1)
+//   3. x[m] = sum_r buf_r[m] (+ R[m]);  X[m] = x;  H[m] = x * rsqrt(mean(x^2) + eps) * gamma
+// MC: the sum over ranks is one multimem.ld_reduce per vector instead of `world` peer loads.
+// N <= 8192, N % 8 == 0. Epochs come from `counters` (device ints, one per slot), so the launch
+// arguments never change and the call can sit in a CUDA graph.
+template <bool MC>
+__global__ void __launch_bounds__(256)
+allreduce_norm_kernel(const long long* bufs, const bf16* mc, bf16* own, const long long* pads, int rank, int world,
+                      int slot, int* counters, const float* __restrict__ partial, int k_splits, int M, int N,
+                      const bf16* __restrict__ R, const bf16* __restrict__ gamma, float eps, bf16* __restrict__ X,
+                      bf16* __restrict__ H, int* status) {
+  __shared__ float red[8];
+  __shared__ int e_s;
+  const int tid = threadIdx.x;
+  const int nvec = N >> 3;
+  constexpr int MAXJ = 4;  // 256 threads x 4 vectors x 8 = 8192 columns
+  if (partial) {
+    for (int m = blockIdx.x; m < M; m += gridDim.x) {
+      for (int vi = tid; vi < nvec; vi += 256) {
+        float a[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+        for (int ks = 0; ks < k_splits; ++ks) {
+          const float4* src = reinterpret_cast<const float4*>(partial + ((long long)ks * M + m) * N + vi * 8);
+          const float4 x = src[0], y = src[1];
+          a[0] += x.x; a[1] += x.y; a[2] += x.z; a[3] += x.w;
+          a[4] += y.x; a[5] += y.y; a[6] += y.z; a[7] += y.w;
+        }
+        uint4 o;
+        o.x = pack_bf16(a[0], a[1]); o.y = pack_bf16(a[2], a[3]);
+        o.z = pack_bf16(a[4], a[5]); o.w = pack_bf16(a[6], a[7]);
+        *reinterpret_cast<uint4*>(own + (long long)m * N + vi * 8) = o;
+      }
+    }
+  }
+  const int myslot = slot + blockIdx.x;
+  if (tid == 0) e_s = counters[myslot] + 1;
+  __syncthreads();  // also orders this block's writes of `own` before the barrier's release stores
+  const int epoch = e_s;
+  const bool ok = barrier_device(pads, rank, world, myslot, epoch, status);
+  const int all_ok = __syncthreads_and(ok ? 1 : 0);
+  // the epoch advances even when a peer never showed up, so that the ranks stay in step afterwards
+  if (tid == 0) counters[myslot] = epoch;
+  if (!all_ok) return;
+  for (int m = blockIdx.x; m < M; m += gridDim.x) {
+    float x[MAXJ][8];
+    float ss = 0.f;
+#pragma unroll
+    for (int j = 0; j < MAXJ; ++j) {
+      const int vi = tid + j * 256;
+      if (vi < nvec) {
+        const long long e = (long long)m * N + vi * 8;
+        gather_sum8<MC>(bufs, mc, world, e, x[j]);
+        if (R) {
+          const uint4 r = *reinterpret_cast<const uint4*>(R + e);
+          x[j][0] += bf16lo(r.x); x[j][1] += bf16hi(r.x); x[j][2] += bf16lo(r.y); x[j][3] += bf16hi(r.y);
+          x[j][4] += bf16lo(r.z); x[j][5] += bf16hi(r.z); x[j][6] += bf16lo(r.w); x[j][7] += bf16hi(r.w);
+        }
+        uint4 o;
+        o.x = pack_bf16(x[j][0], x[j][1]); o.y = pack_bf16(x[j][2], x[j][3]);
+        o.z = pack_bf16(x[j][4], x[j][5]); o.w = pack_bf16(x[j][6], x[j][7]);
+        if (X) *reinterpret_cast<uint4*>(X + e) = o;
+#pragma unroll
+        for (int i = 0; i < 8; ++i) ss += x[j][i] * x[j][i];
+      }
+    }
+    if (!H) continue;
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+    __syncthreads();  // `red` of the previous row has been read
+    if ((tid & 31) == 0) red[tid >> 5] = ss;
+    __syncthreads();
+    float tot = 0.f;
+#pragma unroll
+    for (int w = 0; w < 8; ++w) tot += red[w];
+    const float rinv = rsqrtf(tot / N + eps);
+#pragma unroll
+    for (int j = 0; j < MAXJ; ++j) {
+      const int vi = tid + j * 256;
+      if (vi < nvec) {
+        float g[8] = {1.f, 1.f, 1.f, 1.f, 1.f, 1.f, 1.f, 1.f};
+        if (gamma) {
+          const uint4 gv = *reinterpret_cast<const uint4*>(gamma + vi * 8);
+          g[0] = bf16lo(gv.x); g[1] = bf16hi(gv.x); g[2] = bf16lo(gv.y); g[3] = bf16hi(gv.y);
+          g[4] = bf16lo(gv.z); g[5] = bf16hi(gv.z); g[6] = bf16lo(gv.w); g[7] = bf16hi(gv.w);
+        }
+        uint4 o;
+        o.x = pack_bf16(x[j][0] * rinv * g[0], x[j][1] * rinv * g[1]);
+        o.y = pack_bf16(x[j][2] * rinv * g[2], x[j][3] * rinv * g[3]);
+        o.z = pack_bf16(x[j][4] * rinv * g[4], x[j][5] * rinv * g[5]);
+        o.w = pack_bf16(x[j][6] * rinv * g[6], x[j][7] * rinv * g[7]);
+        *reinterpret_cast<uint4*>(H + (long long)m * N + vi * 8) = o;
+      }
+    }
+  }
+}
+
+// out = R + gate[m / rows_per_batch] * sum_p part[p]  (tensor-parallel row-parallel GEMMs: the tp partial
+// products of this rank's rows were stored by the peers' GEMM epilogues; gate may be null = 1).
+__global__ void __launch_bounds__(256)
+sum_partials_gated_residual_kernel(const bf16* __restrict__ part, int n_part, long long rows, int d,
+                                   const bf16* __restrict__ R, const bf16* __restrict__ gate, int rows_per_batch,
+                                   bf16* __restrict__ out) {
+  const long long n_vec = rows * (d >> 3);
+  const long long stride = rows * d;
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n_vec;
+       i += (long long)gridDim.x * blockDim.x) {
+    const long long e = i * 8;
+    float a[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+    for (int p = 0; p < n_part; ++p) {
+      const uint4 v = *reinterpret_cast<const uint4*>(part + p * stride + e);
+      a[0] += bf16lo(v.x); a[1] += bf16hi(v.x); a[2] += bf16lo(v.y); a[3] += bf16hi(v.y);
+      a[4] += bf16lo(v.z); a[5] += bf16hi(v.z); a[6] += bf16lo(v.w); a[7] += bf16hi(v.w);
+    }
+    if (gate) {
+      const long long m = e / d;
+      const int n = (int)(e - m * d);
+      const uint4 g = *reinterpret_cast<const uint4*>(gate + (m / rows_per_batch) * d + n);
+      a[0] *= bf16lo(g.x); a[1] *= bf16hi(g.x); a[2] *= bf16lo(g.y); a[3] *= bf16hi(g.y);
+      a[4] *= bf16lo(g.z); a[5] *= bf16hi(g.z); a[6] *= bf16lo(g.w); a[7] *= bf16hi(g.w);
+    }
+    if (R) {
+      const uint4 r = *reinterpret_cast<const uint4*>(R + e);
+      a[0] += bf16lo(r.x); a[1] += bf16hi(r.x); a[2] += bf16lo(r.y); a[3] += bf16hi(r.y);
+      a[4] += bf16lo(r.z); a[5] += bf16hi(r.z); a[6] += bf16lo(r.w); a[7] += bf16hi(r.w);
+    }
+    uint4 o;
+    o.x = pack_bf16(a[0], a[1]); o.y = pack_bf16(a[2], a[3]);
+    o.z = pack_bf16(a[4], a[5]); o.w = pack_bf16(a[6], a[7]);
+    *reinterpret_cast<uint4*>(out + e) = o;
+  }
+}
+
 }  // namespace cb
 
 namespace cosmos {
@@ -156,6 +412,12 @@ void comm_barrier(const long long* pads_dev, int rank, int world, int slot, int 
                   cudaStream_t s) {
   if (world > 64) throw std::runtime_error("comm_barrier: at most 64 ranks per group");
   cb::barrier_kernel<<<1, 64, 0, s>>>(pads_dev, rank, world, slot, epoch, status);
+}
+
+void comm_barrier_counted(const long long* pads_dev, int rank, int world, int slot, int* counters, int* status,
+                          cudaStream_t s) {
+  if (world > 64) throw std::runtime_error("comm_barrier: at most 64 ranks per group");
+  cb::barrier_counted_kernel<<<1, 64, 0, s>>>(pads_dev, rank, world, slot, counters, status);
 }
 
 void allreduce_oneshot(const long long* bufs_dev, const long long* pads_dev, void* out,
@@ -190,6 +452,60 @@ void allgather_pull(const long long* srcs_dev, int world, void* dst, long long b
   if (n_vec == 0) return;
   const int blocks = (int)std::min<long long>((n_vec * world + 255) / 256, 148 * 16);
   cb::allgather_pull_kernel<<<blocks, 256, 0, s>>>(srcs_dev, world, (uint4*)dst, n_vec);
+}
+
+void reduce_scatter_pull(const long long* grads_dev, const void* mc, int world, long long shard_off, long long n,
+                         float* out, bool accumulate, float scale, float* sq_out, cudaStream_t s) {
+  if (n == 0) return;
+  if (n % 8 != 0 || shard_off % 8 != 0)
+    throw std::runtime_error("reduce_scatter_pull: shard length and offset must be multiples of 8");
+  const int blocks = (int)std::min<long long>((n / 8 + 255) / 256, 148 * 8);
+  if (mc)
+    cb::reduce_scatter_pull_kernel<true><<<blocks, 256, 0, s>>>(grads_dev, (const bf16*)mc, world, shard_off, n, out,
+                                                                accumulate ? 1 : 0, scale, sq_out);
+  else
+    cb::reduce_scatter_pull_kernel<false><<<blocks, 256, 0, s>>>(grads_dev, nullptr, world, shard_off, n, out,
+                                                                 accumulate ? 1 : 0, scale, sq_out);
+}
+
+void adamw_shard(const float* grad, long long n, float* master, float* m, float* v, void* param_shard,
+                 float grad_scale, float lr, float b1, float b2, float eps, float wd, int step, cudaStream_t s) {
+  if (n == 0) return;
+  const float bc1 = 1.f - powf(b1, (float)step), bc2 = 1.f - powf(b2, (float)step);
+  const int blocks = (int)std::min<long long>((n + 255) / 256, 148 * 8);
+  cb::adamw_shard_kernel<<<blocks, 256, 0, s>>>(grad, n, master, m, v, (bf16*)param_shard, grad_scale, lr, b1, b2,
+                                                eps, wd, bc1, bc2);
+}
+
+int allreduce_norm_blocks(int M) { return M < 32 ? (M < 1 ? 1 : M) : 32; }
+
+void allreduce_norm(const long long* bufs_dev, const void* mc, void* own, const long long* pads_dev, int rank,
+                    int world, int slot, int* counters, const float* partial, int k_splits, int M, int N,
+                    const void* R, const void* gamma, float eps, void* X, void* H, int* status, cudaStream_t s) {
+  if (N % 8 != 0 || N > 8192) throw std::runtime_error("allreduce_norm: N must be a multiple of 8 and <= 8192");
+  if (world > 64) throw std::runtime_error("allreduce_norm: at most 64 ranks per group");
+  if (!counters) throw std::runtime_error("allreduce_norm: needs the group's epoch counters");
+  const int blocks = allreduce_norm_blocks(M);
+  if (slot + blocks > 64) throw std::runtime_error("allreduce_norm: signal slots out of range");
+  if (mc)
+    cb::allreduce_norm_kernel<true><<<blocks, 256, 0, s>>>(bufs_dev, (const bf16*)mc, (bf16*)own, pads_dev, rank, world,
+                                                           slot, counters, partial, k_splits, M, N, (const bf16*)R,
+                                                           (const bf16*)gamma, eps, (bf16*)X, (bf16*)H, status);
+  else
+    cb::allreduce_norm_kernel<false><<<blocks, 256, 0, s>>>(bufs_dev, nullptr, (bf16*)own, pads_dev, rank, world, slot,
+                                                            counters, partial, k_splits, M, N, (const bf16*)R,
+                                                            (const bf16*)gamma, eps, (bf16*)X, (bf16*)H, status);
+}
+
+void sum_partials_gated_residual(const void* part, int n_part, long long rows, int d, const void* R, const void* gate,
+                                 int rows_per_batch, void* out, cudaStream_t s) {
+  if (rows == 0) return;
+  if (d % 8 != 0) throw std::runtime_error("sum_partials_gated_residual: d must be a multiple of 8");
+  const long long n_vec = rows * (d / 8);
+  const int blocks = (int)std::min<long long>((n_vec + 255) / 256, 148 * 16);
+  cb::sum_partials_gated_residual_kernel<<<blocks, 256, 0, s>>>((const bf16*)part, n_part, rows, d, (const bf16*)R,
+                                                                (const bf16*)gate, rows_per_batch > 0 ? rows_per_batch : 1,
+                                                                (bf16*)out);
 }
 
 }  // namespace cosmos

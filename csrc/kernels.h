@@ -57,6 +57,7 @@ struct GemmArgs {
   bool a_mn = false, b_mn = false;
   int k_splits = 1;       // > 1: split-K with fp32 partials in `partial` ([k_splits, M, N] floats)
   float* partial = nullptr;
+  bool partial_only = false;  // split-K: stop after the partial sums (the caller's next kernel reduces them)
   // split-K only (EPI_PLAIN): the reduction pass also adds the residual R (ldr) and applies an RMS-norm, writing
   // x_new = R + A B^T to `C` and rmsnorm(x_new) * norm_gamma to `norm_out` (both [M, N] bf16, row stride ldc)
   const void* norm_gamma = nullptr;
@@ -72,6 +73,12 @@ struct GemmArgs {
 int gemm_pick_k_splits(int M, int N, int K, int epi);
 // Debug knob for race hunting: at most `max_ctas` persistent CTAs per GEMM launch (0 = one per SM).
 void gemm_set_grid_limit(int max_ctas);
+// A/B switch: problems taller than one 128-row tile run on CTA pairs (256-row tiles, tcgen05 cta_group::2)
+// when on (the default; COSMOS_GEMM_CTA_PAIR=0 starts with it off).
+void gemm_set_cta_pair(bool on);
+// Timing experiments (results are wrong): bit 0 = every tile loads the operand tiles at (0, 0) (all loads hit L2),
+// bit 1 = no operand loads at all (the MMA issue rate alone).
+void gemm_set_debug(int bits);
 void gemm_bf16(const GemmArgs& a, cudaStream_t stream);
 // K12: one persistent launch over one or two problems with the same epilogue kind (per-modality
 // weight routing: tokens are already grouped into an AR segment and a DM segment).
@@ -98,8 +105,8 @@ struct AttnArgs {
   const long long* dest_ptr = nullptr;
   int rows_per_dest = 0;
   int* status = nullptr;
-  // Every k-th softmax element computes exp2 with a polynomial on the FMA pipe (2, 3, 4; 0 = none).
-  // Measured on B200 the softmax warps are latency/issue bound rather than MUFU bound, so 0 is fastest.
+  // Of every 8 pairs of scores, this many compute exp2 with a polynomial on the FMA pipe (2, 3; 0 = none).
+  // Measured on B200: faster than 0 with the MMAs switched off, slower with them on, so 0 is the default.
   int exp_emulation = 0;
   int debug = 0;  // timing experiments (results are wrong): 1 = no QK MMAs, 2 = no PV MMAs, 4 = no exponentials
 };
@@ -227,6 +234,9 @@ void qkv_post_bwd(const void* qkv, const void* dq, const void* dk, const void* d
 // Signal pads are int32 arrays laid out as [slot][64]; epochs must grow monotonically per slot.
 void comm_barrier(const long long* pads_dev, int rank, int world, int slot, int epoch, int* status,
                   cudaStream_t s);
+// Epoch read from and advanced in counters[slot] on the device (CUDA-graph friendly).
+void comm_barrier_counted(const long long* pads_dev, int rank, int world, int slot, int* counters, int* status,
+                          cudaStream_t s);
 // Uses slots [slot, slot + 8) and epochs (epoch, epoch + 1); with `counters` (device ints, one per
 // slot) the kernel tracks the epochs itself and `epoch` is ignored (CUDA-graph friendly).
 void allreduce_oneshot(const long long* bufs_dev, const long long* pads_dev, void* out,
@@ -235,6 +245,25 @@ void allreduce_oneshot(const long long* bufs_dev, const long long* pads_dev, voi
 void rs_adamw(const long long* grads_dev, int world, long long shard_off, long long n, float* master,
               float* m, float* v, void* param_shard, float grad_scale, float lr, float b1, float b2,
               float eps, float wd, int step, float* sq_out, float* reduced_out, cudaStream_t s);
+// Reduce-scatter by pull into an fp32 shard (out[i] (+)= scale * sum_r grad_r[shard_off + i]) with the sum of squares
+// of the results added to *sq_out (may be null). `mc` != null: the buffers' NVLink multicast address; the sum over
+// ranks is then one multimem.ld_reduce per 16-byte vector (added inside the switch) instead of `world` peer loads.
+void reduce_scatter_pull(const long long* grads_dev, const void* mc, int world, long long shard_off, long long n,
+                         float* out, bool accumulate, float scale, float* sq_out, cudaStream_t s);
+// AdamW on a local fp32 gradient shard (fp32 master + moments, bf16 parameter shard rewritten).
+void adamw_shard(const float* grad, long long n, float* master, float* m, float* v, void* param_shard,
+                 float grad_scale, float lr, float b1, float b2, float eps, float wd, int step, cudaStream_t s);
+// Decode all-reduce fused with its neighbours: (sum of the GEMM's split-K partials -> `own`, this rank's symmetric
+// buffer) -> group barrier -> sum over ranks (+ residual R) -> X, and H = rmsnorm(X) * gamma. One launch; epochs in
+// `counters` (one device int per signal slot; slots [slot, slot + allreduce_norm_blocks(M)) belong to the call).
+// Callers alternate two symmetric buffers between consecutive calls (there is no trailing barrier).
+int allreduce_norm_blocks(int M);
+void allreduce_norm(const long long* bufs_dev, const void* mc, void* own, const long long* pads_dev, int rank,
+                    int world, int slot, int* counters, const float* partial, int k_splits, int M, int N,
+                    const void* R, const void* gamma, float eps, void* X, void* H, int* status, cudaStream_t s);
+// out = R + gate[m / rows_per_batch] * sum_p part[p] over n_part stacked [rows, d] bf16 partial products.
+void sum_partials_gated_residual(const void* part, int n_part, long long rows, int d, const void* R, const void* gate,
+                                 int rows_per_batch, void* out, cudaStream_t s);
 void allgather_pull(const long long* srcs_dev, int world, void* dst, long long bytes_per_rank,
                     cudaStream_t s);
 
