@@ -1,8 +1,9 @@
 """Worker for the multi-GPU training test (torch.distributed.run, one rank per GPU): two FSDP
-steps of a small head_dim-128 model with the fused paths (pull all-gather kernel, reduce-scatter
-folded into the AdamW kernel) against the NCCL-collective baseline, plus the one-shot all-reduce
-kernel against NCCL all_reduce. Training math on CUDA uses fp32 parameters here so that both
-paths run the same (PyTorch autograd) forward/backward and differ only in the collectives."""
+steps of a small head_dim-128 bf16 model with the fused paths (parameter gathers prefetched on a side
+stream by the pull kernel, per-layer reduce-scatter by pull during backward, AdamW kernel on the fp32
+gradient shards) against the NCCL-collective baseline, plus the one-shot all-reduce kernel against NCCL
+all_reduce. Both paths run the forward and backward on this package's kernels (bf16 parameters) and
+differ only in the collectives and the optimizer kernel."""
 import os
 import sys
 

@@ -32,6 +32,14 @@ def test_fused_fsdp_and_allreduce_two_gpus():
     assert r.stdout.count("OK") == 2, r.stdout
 
 
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs 2 GPUs")
+def test_fused_comm_kernels_two_gpus():
+    """Reduce-scatter pull, all-reduce + residual + RMS-norm (peer loads and multimem), two decoders in turn."""
+    r = _torchrun(2, "mp_comm_worker.py")
+    assert r.returncode == 0, r.stdout[-3000:] + r.stderr[-3000:]
+    assert r.stdout.count("OK") == 3, r.stdout
+
+
 @pytest.mark.skipif(torch.cuda.device_count() < 4, reason="needs 4 GPUs")
 def test_fused_cfgp_x_ulysses_four_gpus():
     r = _torchrun(4, "mp_fused_worker.py", json.dumps([{"cfgp": 2, "cp": 2}, {"cp": 4}]))
