@@ -36,7 +36,12 @@ class GenState:
     fps: Optional[int] = None
     cond_mask: Optional[torch.Tensor] = None   # [S_dm] True = clean conditioning token (never updated)
     clean_tokens: Optional[torch.Tensor] = None  # [1, S_dm, F] values for the cond_mask positions
+    # video transfer: clean latent tokens of the control clip (edge / blur / depth / seg / wsm map), [1, n_video, F] on
+    # this rank's token shard. They run as a second vision stream that shares the target's 3-D rotary positions
+    # (reference cookbooks/cosmos3/generator/transfer/README.md:35,98) and are flagged clean; `control_weight`
+    # scales the control guidance term.
     control_tokens: Optional[torch.Tensor] = None
+    control_weight: float = 1.0
     # context parallelism: this rank holds DM tokens [shard_start, shard_start + S_dm) of total_tokens
     shard_start: int = 0
     total_tokens: int = 0
@@ -62,10 +67,13 @@ class GeneratorEngine:
 
     # ------------------------------------------------------------------ one DM evaluation
     @torch.no_grad()
-    def velocity(self, tokens: torch.Tensor, sigma: torch.Tensor, st: GenState, ar_kv: List[KV]
-                 ) -> torch.Tensor:
+    def velocity(self, tokens: torch.Tensor, sigma: torch.Tensor, st: GenState, ar_kv: List[KV],
+                 with_control: bool = False) -> torch.Tensor:
         """tokens [B, S_dm, F] (noisy video/sound/action features, padded to a common width)
-        -> velocity prediction of the same shape, bf16/fp32 as the model computes."""
+        -> velocity prediction of the same shape, bf16/fp32 as the model computes. `with_control` appends the
+        state's control stream (clean tokens at the target's positions) to the sequence; its outputs are dropped."""
+        if with_control:
+            return self._velocity_with_control(tokens, sigma, st, ar_kv)
         m = self.model
         nv, ns, na = st.n_video, st.n_sound, st.n_action
         pd = self.cfg.patch_dim
@@ -89,6 +97,35 @@ class GeneratorEngine:
         return out
 
     @torch.no_grad()
+    def _velocity_with_control(self, tokens, sigma, st: GenState, ar_kv: List[KV]) -> torch.Tensor:
+        if st.n_sound or st.n_action:
+            raise ValueError("a control stream needs a video-only token sequence")
+        m, nv, pd = self.model, st.n_video, self.cfg.patch_dim
+        dt = m.patch_in.dtype
+        b = tokens.shape[0]
+        ctrl = st.control_tokens[:, :, :pd].to(dt).expand(b, -1, -1)
+        video = torch.cat([tokens[:, :nv, :pd].to(dt), ctrl], dim=1)
+        cm = torch.zeros(b, 2 * nv, dtype=torch.bool, device=tokens.device)
+        if st.cond_mask is not None:
+            cm[:, :nv] = st.cond_mask[None, :nv]
+        cm[:, nv:] = True
+        x = m.dm_embed(video, None, None, st.domain, st.fps, cm)
+        if not hasattr(st, "_ctrl_tables"):
+            pos2 = torch.cat([st.pos[:, :nv], st.pos[:, :nv]], dim=1)
+            st._ctrl_tables = (pos2, tuple(torch.cat([t[:nv], t[:nv]], dim=0) for t in st.cos_sin))
+        pos2, cs2 = st._ctrl_tables
+        h = m.dm_forward(x, sigma, pos2, ar_kv, self.ctx, cos_sin=cs2)
+        return m.dm_heads(h[:, :nv], nv, 0, 0, st.domain, st.action_dim)["video"]
+
+    def _control_scale(self, st: GenState, sc: SamplingConfig) -> float:
+        """Weight of the control term v += w (v_ctrl - v_cond): the sampling's `control_guidance` (1 when a control
+        clip is given without it) times the hint's `control_weight`; 0 without a control stream."""
+        if st.control_tokens is None:
+            return 0.0
+        g = 1.0 if sc.control_guidance is None else float(sc.control_guidance)
+        return g * float(st.control_weight)
+
+    @torch.no_grad()
     def denoise_step(self, x: torch.Tensor, sigma: float, sigma_next: float, st: GenState,
                      sc: SamplingConfig, smp=None) -> torch.Tensor:
         """One guided step on the fp32 latent tokens x [1, S_dm, F]; returns the updated tokens."""
@@ -99,8 +136,11 @@ class GeneratorEngine:
         if st.cond_mask is not None and st.clean_tokens is not None:
             xin = torch.where(st.cond_mask[None, :, None], st.clean_tokens.to(x.dtype), x)
         mdt = self.model.patch_in.dtype
+        gc = self._control_scale(st, sc)
         if self.cfg_group is not None and use_cfg:
-            vc, vu = self.cfg_group.branch_velocities(self, xin, sigma, st)
+            vc, vu = self.cfg_group.branch_velocities(self, xin, sigma, st, control_scale=gc,
+                                                      guidance=sc.guidance)
+            gc = 0.0   # already folded into the cond branch
         elif use_cfg:
             kv2 = [(torch.cat([kc, ku]), torch.cat([vc_, vu_]))
                    for (kc, vc_), (ku, vu_) in zip(st.ar_kv_cond, st.ar_kv_uncond)] \
@@ -112,6 +152,14 @@ class GeneratorEngine:
         else:
             sig = torch.full((1,), float(sigma), device=dev)
             vc, vu = self.velocity(xin.to(mdt), sig, st, st.ar_kv_cond), None
+        if gc != 0.0:
+            # third branch: the same prompt with the control stream. v = v_u + g (v_c - v_u) + g_c (v_ctrl - v_c)
+            # equals the two-branch formula with v_c replaced by v_c + (g_c / g) (v_ctrl - v_c), so the fused
+            # CFG + sampler kernel serves it unchanged.
+            sig1 = torch.full((1,), float(sigma), device=dev)
+            v_ctrl = self.velocity(xin.to(mdt), sig1, st, st.ar_kv_cond, with_control=True)
+            w = gc / float(sc.guidance) if vu is not None else gc
+            vc = torch.lerp(vc.float(), v_ctrl.float(), w).to(vc.dtype)
         if smp is None or isinstance(smp, samplers.EulerSampler):
             dt = float(sigma_next - sigma)
             if smp is not None:

@@ -53,6 +53,25 @@ def _round_up(n: int, m: int) -> int:
     return (n + m - 1) // m * m
 
 
+class _FlatSplit(torch.autograd.Function):
+    """flat [n] -> the named views of a `FlatLayer`; backward gathers the views' gradients into one flat tensor."""
+
+    @staticmethod
+    def forward(ctx, flat: torch.Tensor, layer: "FlatLayer"):
+        ctx.layer = layer
+        ctx.meta = (flat.shape, flat.dtype, flat.device)
+        return tuple(flat[off:off + n].view(layer.spec[name]) for name, (off, n) in layer.offsets.items())
+
+    @staticmethod
+    def backward(ctx, *grads):
+        shape, dtype, device = ctx.meta
+        g = torch.zeros(shape, dtype=dtype, device=device)
+        for (name, (off, n)), gv in zip(ctx.layer.offsets.items(), grads):
+            if gv is not None:
+                g[off:off + n].copy_(gv.reshape(-1))
+        return g, None
+
+
 class FlatLayer(nn.Module):
     """One transformer layer's parameters as a single flat tensor with named views.
 
@@ -75,6 +94,11 @@ class FlatLayer(nn.Module):
 
     def views(self, flat: Optional[torch.Tensor] = None) -> Dict[str, torch.Tensor]:
         flat = self.flat if flat is None else flat
+        if torch.is_grad_enabled() and flat.requires_grad:
+            # one autograd node for all views: its backward writes every view's gradient into ONE flat gradient
+            # (plain slicing would build a full-size zero tensor per view and add them up pairwise)
+            outs = _FlatSplit.apply(flat, self)
+            return dict(zip(self.offsets.keys(), outs))
         return {name: flat[off:off + n].view(self.spec[name]) for name, (off, n) in self.offsets.items()}
 
     @torch.no_grad()

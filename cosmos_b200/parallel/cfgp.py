@@ -46,12 +46,18 @@ class CFGParallel:
             self._buf = (views, tuple(like.shape))
         return self._buf[0]
 
-    def branch_velocities(self, engine, xin: torch.Tensor, sigma: float, st) -> Tuple[torch.Tensor, torch.Tensor]:
-        """Returns (v_cond, v_uncond) for this rank's token shard; one of the two lives on the peer."""
+    def branch_velocities(self, engine, xin: torch.Tensor, sigma: float, st, control_scale: float = 0.0,
+                          guidance: float = 1.0) -> Tuple[torch.Tensor, torch.Tensor]:
+        """Returns (v_cond, v_uncond) for this rank's token shard; one of the two lives on the peer. With a control
+        stream (`control_scale` != 0) the cond branch also evaluates the prompt with the control tokens and
+        publishes v_c + (g_c / g) (v_ctrl - v_c), which turns the two-branch combine into the three-branch one."""
         kv = st.ar_kv_cond if self.branch == 0 else st.ar_kv_uncond
         mdt = engine.model.patch_in.dtype
         sig = torch.full((1,), float(sigma), device=xin.device)
         v = engine.velocity(xin.to(mdt), sig, st, kv)
+        if control_scale != 0.0 and self.branch == 0:
+            v_ctrl = engine.velocity(xin.to(mdt), sig, st, kv, with_control=True)
+            v = torch.lerp(v.float(), v_ctrl.float(), control_scale / float(guidance)).to(v.dtype)
         if self.fused and v.is_cuda:
             views = self._buffers(v)
             mine, peer = views[self._step & 1]

@@ -32,10 +32,74 @@ from ..models.mot import KV, AttnContext
 from .symm import symm_group
 
 
+def tp_local_config(cfg: MoTConfig, tp: int) -> MoTConfig:
+    """The configuration of ONE tensor-parallel rank's model shard: 1/tp of the heads and of the FFN units, everything
+    else (width, layers, vocabulary, embeddings, modulation tables) as in `cfg`. A `MoTModel` built from it holds
+    only that rank's slice of every block weight (Cosmos3-Super on 8 ranks: 16 GB of block weights per GPU instead
+    of 128 GB), and `TPContext(cfg, ..., presliced=True)` runs it."""
+    import dataclasses
+    if cfg.n_heads % tp or cfg.n_kv_heads % tp or cfg.ffn_dim % tp:
+        raise ValueError("tp must divide the head counts and the FFN width")
+    return dataclasses.replace(cfg, n_heads=cfg.n_heads // tp, n_kv_heads=cfg.n_kv_heads // tp,
+                               ffn_dim=cfg.ffn_dim // tp)
+
+
+def tp_slice_rows(name: str, cfg: MoTConfig, tp: int, rank: int):
+    """Which part of a full block weight `name` belongs to `rank`: ("rows", [(start, stop), ...]) for weights split by
+    output rows (wqkv: the rank's q, k and v head blocks; w_gate_up: its gate and up blocks), ("cols", (start, stop))
+    for weights split by input columns (wo, w_down), None for replicated tensors. Used to read a rank's shard straight
+    from a checkpoint (`ckpt/safetensors_io.py::read_range` for row blocks)."""
+    hd = cfg.head_dim
+    if name == "wqkv":
+        hq, hk = cfg.n_heads // tp, cfg.n_kv_heads // tp
+        q0, k0, v0 = 0, cfg.q_dim, cfg.q_dim + cfg.kv_dim
+        return "rows", [(q0 + rank * hq * hd, q0 + (rank + 1) * hq * hd), (k0 + rank * hk * hd, k0 + (rank + 1) * hk * hd),
+                        (v0 + rank * hk * hd, v0 + (rank + 1) * hk * hd)]
+    if name == "w_gate_up":
+        f = cfg.ffn_dim // tp
+        return "rows", [(rank * f, (rank + 1) * f), (cfg.ffn_dim + rank * f, cfg.ffn_dim + (rank + 1) * f)]
+    if name == "wo":
+        c = cfg.q_dim // tp
+        return "cols", (rank * c, (rank + 1) * c)
+    if name == "w_down":
+        f = cfg.ffn_dim // tp
+        return "cols", (rank * f, (rank + 1) * f)
+    return None
+
+
+def shard_full_model(full, local, cfg: MoTConfig, tp: int, rank: int) -> None:
+    """Copies `rank`'s slices of a full `MoTModel` into a model built from `tp_local_config` (tests, and loading a
+    checkpoint that was read in full); replicated tensors are copied whole."""
+    with torch.no_grad():
+        for tname in ("ar", "dm"):
+            ft, lt = getattr(full, tname, None), getattr(local, tname, None)
+            if ft is None or lt is None:
+                continue
+            for fl, ll in zip(ft.layers, lt.layers):
+                fv, lv = fl.views(), ll.views()
+                for name, dst in lv.items():
+                    how = tp_slice_rows(name, cfg, tp, rank)
+                    if how is None:
+                        dst.copy_(fv[name])
+                    elif how[0] == "rows":
+                        dst.copy_(torch.cat([fv[name][a:b] for a, b in how[1]]))
+                    else:
+                        dst.copy_(fv[name][:, how[1][0]:how[1][1]])
+        skip = {n for n, _ in local.named_parameters() if ".layers." in n}
+        fp = dict(full.named_parameters())
+        for n, p in local.named_parameters():
+            if n not in skip and n in fp and fp[n].shape == p.shape:
+                p.copy_(fp[n])
+
+
 class TPContext(AttnContext):
     def __init__(self, cfg: MoTConfig, group, ranks: List[int], device, fused: bool = True,
-                 sequence_parallel: bool = True):
+                 sequence_parallel: bool = True, presliced: bool = False):
+        """`cfg` is always the FULL model's configuration. `presliced`: the model that runs under this context was
+        built from `tp_local_config(cfg, tp)`, so its weights (and the K/V it caches) are this rank's slices already."""
         self.cfg, self.group = cfg, group
+        self.presliced = bool(presliced)
+        self._ranks = list(ranks)
         self.tp = len(ranks)
         self.rank = ranks.index(dist.get_rank()) if dist.is_initialized() else 0
         if cfg.n_kv_heads % self.tp or cfg.n_heads % self.tp or cfg.ffn_dim % self.tp:
@@ -58,6 +122,8 @@ class TPContext(AttnContext):
     # ------------------------------------------------------------------ weight slices
     def _slice(self, w: torch.Tensor, kind: str) -> torch.Tensor:
         """Local part of a full weight. Cached per storage so inference slices once."""
+        if self.presliced:
+            return w
         key = (w.data_ptr(), kind, tuple(w.shape))
         if key in self._wcache and not torch.is_grad_enabled():
             return self._wcache[key]
@@ -247,30 +313,68 @@ class TPContext(AttnContext):
             self.sg.barrier_counted(slot=15)
 
     # ------------------------------------------------------------------ AttnContext interface
+    def prefill_context(self) -> "TPContext":
+        """The same ranks and buffers without sequence parallelism (every rank holds the whole, short sequence and the
+        row-parallel outputs are all-reduced): how the prompt runs through a pre-sliced AR tower."""
+        if not self.sp:
+            return self
+        if getattr(self, "_prefill", None) is None:
+            c = TPContext(self.cfg, self.group, self._ranks, self.device, fused=self.fused, sequence_parallel=False,
+                          presliced=self.presliced)
+            self._prefill = c
+        return self._prefill
+
     def qkv_project(self, h, w, cos, sin, q_norm, k_norm, cfg: MoTConfig, prefix: Optional[KV] = None):
+        cfg = self.cfg   # head counts come from the full configuration (the caller's may be the rank-local one)
         wl = self._slice(w, "qkv")
         x = self._all_gather_seq(h)
         b, s, _ = x.shape
         hq, hk, hd = cfg.n_heads // self.tp, cfg.n_kv_heads // self.tp, cfg.head_dim
-        qkv = self._gemm_rowblocks(x, wl).view(b, s, hq + 2 * hk, hd)
-        self._ag_done()
-        q, k, v = qkv[:, :, :hq], qkv[:, :, hq:hq + hk], qkv[:, :, hq + hk:]
         gq = q_norm if cfg.qk_norm else None
         gk = k_norm if cfg.qk_norm else None
         # cos/sin are given for the local sequence shard; attention needs the full sequence
         cos_f, sin_f = self._full_rope(cos, sin)
-        if q.is_cuda and q.dtype == torch.bfloat16 and hd == 128:
-            q_ = ops.mrope(q.contiguous(), cos_f, sin_f, gq, cfg.rms_eps)
-            k_ = ops.mrope(k.contiguous(), cos_f, sin_f, gk, cfg.rms_eps)
-            q, k = q_, k_
+        if x.is_cuda and x.dtype == torch.bfloat16 and hd == 128 and b == 1 and not torch.is_grad_enabled() \
+                and ops.get_backend() == "own":
+            # q/k RMS-norm and the rotary rotation run in the GEMM's epilogue, row block by row block as the
+            # peers' sequence shards arrive
+            qkv = self._gemm_rowblocks_qkv(x, wl, cos_f, sin_f, gq, gk, hq, hk).view(b, s, hq + 2 * hk, hd)
+            self._ag_done()
+            q, k, v = qkv[:, :, :hq], qkv[:, :, hq:hq + hk], qkv[:, :, hq + hk:]
         else:
-            q = ops.ref.mrope(q, cos_f, sin_f, gq, cfg.rms_eps)
-            k = ops.ref.mrope(k, cos_f, sin_f, gk, cfg.rms_eps)
+            qkv = self._gemm_rowblocks(x, wl).view(b, s, hq + 2 * hk, hd)
+            self._ag_done()
+            q, k, v = qkv[:, :, :hq], qkv[:, :, hq:hq + hk], qkv[:, :, hq + hk:]
+            if q.is_cuda and q.dtype == torch.bfloat16 and hd == 128:
+                q = ops.mrope(q.contiguous(), cos_f, sin_f, gq, cfg.rms_eps)
+                k = ops.mrope(k.contiguous(), cos_f, sin_f, gk, cfg.rms_eps)
+            else:
+                q = ops.ref.mrope(q, cos_f, sin_f, gq, cfg.rms_eps)
+                k = ops.ref.mrope(k, cos_f, sin_f, gk, cfg.rms_eps)
         if prefix is not None:
-            sl = slice(self.rank * hk, (self.rank + 1) * hk)
+            sl = slice(None) if (self.presliced or prefix[0].shape[2] == hk) else slice(self.rank * hk, (self.rank + 1) * hk)
             k = torch.cat([prefix[0][:, :, sl], k], dim=1)
             v = torch.cat([prefix[1][:, :, sl], v], dim=1)
         return q, k, v
+
+    def _gemm_rowblocks_qkv(self, x_full, w, cos, sin, gq, gk, hq, hk) -> torch.Tensor:
+        """QKV projection with the fused norm + rotary epilogue on a gathered input [1, S, d] -> [1, S, (hq + 2 hk) * 128];
+        with a fused gather in flight it runs block by block in arrival order, each block with its rows of the
+        rotary tables."""
+        eps = self.cfg.rms_eps
+        ev = getattr(self, "_ag_events", None)
+        if not ev:
+            return ops.gemm_qkv_rope(x_full[0], w, None, cos, sin, gq, gk, hq, hk, eps)[None]
+        s_loc = self._ag_s_loc
+        out = torch.empty(1, x_full.shape[1], w.shape[0], dtype=x_full.dtype, device=x_full.device)
+        main = torch.cuda.current_stream()
+        for r in self._ag_order:
+            if r in ev:
+                main.wait_event(ev[r])
+            rows = slice(r * s_loc, (r + 1) * s_loc)
+            ops.gemm_qkv_rope(x_full[0, rows], w, None, cos[rows].contiguous(), sin[rows].contiguous(), gq, gk, hq, hk, eps,
+                              out=out[0, rows])
+        return out
 
     def _full_rope(self, cos, sin):
         if self.tp == 1 or not self.sp:

@@ -229,8 +229,14 @@ class Cosmos3OmniPipeline:
                 seed: int = 0, sampling: Optional[SamplingConfig] = None,
                 max_sequence_length: Optional[int] = None, sound_duration: Optional[float] = None,
                 condition_video_keep: Optional[str] = None,
-                negative_metadata_same: bool = False) -> Tuple[GenState, SamplingConfig]:
-        """`sound_duration` (seconds) overrides the sound track length, which otherwise equals the clip's
+                negative_metadata_same: bool = False, control_video=None, control_weight: float = 1.0
+                ) -> Tuple[GenState, SamplingConfig]:
+        """`control_video` (a path, frames [T, H, W, 3] or a list of images: an edge / blur / depth / segmentation /
+        world-scenario map of the clip to generate) makes this a video-transfer generation: the control clip is
+        encoded by the tokenizer into clean latent tokens that run as a second vision stream at the target's own
+        3-D rotary positions, in a third guidance branch weighted by `sampling.control_guidance * control_weight`
+        (reference cookbooks/cosmos3/generator/transfer/README.md:35,98, specs/edge.json:11-22).
+        `sound_duration` (seconds) overrides the sound track length, which otherwise equals the clip's
         `num_frames / fps` (reference cookbooks/cosmos3/generator/audiovisual/run_with_vllm_omni.ipynb:429).
         `condition_video_keep` says which end of an input video supplies the conditioning frames:
         "first" (default) or "last" (continue a clip from its final frames).
@@ -296,6 +302,20 @@ class Cosmos3OmniPipeline:
             off = st.n_video + st.n_sound
             cond[off:off + a.shape[0]] = True
             clean[0, off:off + a.shape[0], :a.shape[1]] = a
+        if control_video is not None:
+            if n_sound or n_act:
+                raise ValueError("video transfer (a control clip) generates vision only")
+            n_pix = 1 + (grid[0] - 1) * cfg.vae_t_compress
+            cf = _to_frames(control_video, width, height)[:n_pix]
+            if cf.shape[0] < n_pix:
+                cf = np.concatenate([cf, np.repeat(cf[-1:], n_pix - cf.shape[0], 0)])
+            cx = CausalVideoVAE.from_uint8(torch.from_numpy(np.array(cf))[None].to(self.device)).to(vdt)
+            with torch.no_grad():
+                cz = self.vae.encode(cx, chunk_frames=4 if n_pix > 1 else None).float()
+            ctok = patchify(cz, cfg)                       # [1, all video tokens, patch_dim]
+            a = st.shard_start
+            st.control_tokens = ctok[:, a:a + st.n_video].contiguous()   # this rank's context-parallel shard
+            st.control_weight = float(control_weight)
         if cond.any():
             st.cond_mask, st.clean_tokens = cond, clean
         return st, sc
@@ -435,6 +455,9 @@ class Cosmos3OmniPipeline:
         n_first = num_first_chunk_conditional_frames if video is not None else 0
         plan = _chunk_plan(num_frames, frames_per_chunk, n_first, num_conditional_frames, tc)
         src = _to_frames(video, width, height) if video is not None else None
+        ctrl_src = call_kw.pop("control_video", None)
+        ctrl_all = _to_frames(ctrl_src, width, height) if ctrl_src is not None else None
+        done = 0   # output frames produced so far = position of the next chunk's first new frame in the clip
         frames_out: List[np.ndarray] = []
         sounds, timings = [], {}
         tail = None
@@ -448,6 +471,13 @@ class Cosmos3OmniPipeline:
             kw = dict(call_kw)
             if cond is not None:
                 kw["condition_frame_indexes"] = list(range(1 + (c - 1) // tc))
+            if ctrl_all is not None:
+                # the chunk covers clip frames [done - c, done - c + total): its control frames are the same range
+                lo = max(0, done - c)
+                seg = ctrl_all[lo:lo + total]
+                if seg.shape[0] == 0:
+                    seg = ctrl_all[-1:]
+                kw["control_video"] = seg
             sc = dataclasses.replace(sampling, seed=sampling.seed + k) if sampling is not None else None
             if sc is None and "generator" not in kw:
                 kw["generator"] = torch.Generator().manual_seed(k)
@@ -455,6 +485,7 @@ class Cosmos3OmniPipeline:
                         sampling=sc, callback=callback, **kw)
             fr = np.asarray(last.video)
             frames_out.append(fr[c:c + new])
+            done += new
             tail = fr[:c + new]
             if last.sound is not None:
                 sounds.append(np.asarray(last.sound))

@@ -85,6 +85,35 @@ def _size_for(spec: InferenceSpec):
     return resolve_size(spec.resolution, spec.aspect_ratio)
 
 
+EDGE_PRESETS = {"very_low": (20, 50), "low": (50, 100), "medium": (100, 200), "high": (200, 300), "very_high": (300, 400)}
+BLUR_PRESETS = {"very_low": 5, "low": 11, "medium": 21, "high": 31, "very_high": 41}
+
+
+def _control_frames(spec: InferenceSpec, kind: str, ctrl: Dict, width: int, height: int) -> np.ndarray:
+    """Frames [T, H, W, 3] of the control clip. `control_path` names a ready-made map; when that file is absent and the
+    spec has an input video, edge and blur maps are computed from it (Canny thresholds / Gaussian kernel chosen by
+    `preset_edge_threshold` / `preset_blur_strength`); depth, seg and wsm maps need their file."""
+    path = spec.resolve(ctrl["control_path"]) if ctrl.get("control_path") else None
+    if path is not None and Path(path).exists():
+        frames, _ = media.read_video(path) if str(path).lower().endswith((".mp4", ".mov", ".mkv", ".webm", ".avi")) \
+            else (media.read_image(path)[None], None)
+        return np.asarray(frames)
+    if kind not in ("edge", "blur") or not spec.vision_path:
+        raise FileNotFoundError(f"control clip {path} not found (only edge and blur maps can be derived from the input video)")
+    import cv2
+    src, _ = media.read_video(spec.resolve(spec.vision_path))
+    out = []
+    for f in np.asarray(src):
+        if kind == "edge":
+            lo, hi = EDGE_PRESETS.get(str(ctrl.get("preset_edge_threshold", "medium")), EDGE_PRESETS["medium"])
+            e = cv2.Canny(cv2.cvtColor(f, cv2.COLOR_RGB2GRAY), lo, hi)
+            out.append(np.repeat(e[..., None], 3, axis=-1))
+        else:
+            k = BLUR_PRESETS.get(str(ctrl.get("preset_blur_strength", "medium")), BLUR_PRESETS["medium"])
+            out.append(cv2.GaussianBlur(f, (k, k), 0))
+    return np.stack(out)
+
+
 def run_generator_sample(pipe, spec: InferenceSpec, out_dir: Path, quality: int, is_writer: bool) -> Dict:
     from ..data.vfm.action.av_dataset import DOMAIN_ACTION_DIM
 
@@ -101,10 +130,17 @@ def run_generator_sample(pipe, spec: InferenceSpec, out_dir: Path, quality: int,
         elif spec.model_mode == "inverse_dynamics":
             kw["condition_frame_indexes"] = list(range((spec.num_frames - 1) // 4 + 1))
     if spec.is_transfer:
-        # the control video conditions generation as clean tokens of a second vision stream
-        ctrl = next(iter(spec.controls.values()))
-        video = spec.resolve(ctrl["control_path"]) if video is None else video
-        kw.setdefault("condition_frame_indexes", [0])
+        # the control clip (edge / blur / depth / seg / wsm map) runs as a second, clean vision stream at the target's
+        # positions; `control_guidance` and the hint's `control_weight` weigh its guidance branch
+        kind, ctrl = next(iter(spec.controls.items()))
+        kw["control_video"] = _control_frames(spec, kind, ctrl, width, height)
+        kw["control_weight"] = float(ctrl.get("control_weight", 1.0))
+        if video is not None and not spec.condition_frame_indexes_vision:
+            n_first = spec.num_first_chunk_conditional_frames or 0
+            if n_first:
+                kw["condition_frame_indexes"] = list(range(1 + (n_first - 1) // pipe.cfg.vae_t_compress))
+            else:
+                video = None   # the input clip only served to derive the control map
     if spec.model_mode in ("forward_dynamics", "inverse_dynamics", "policy"):
         dom = spec.domain_name
         adim = spec.raw_action_dim or DOMAIN_ACTION_DIM.get(dom, 9)

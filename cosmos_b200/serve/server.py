@@ -105,13 +105,14 @@ class Cosmos3Server:
     """Holds the pipeline/reasoner and implements the endpoint logic independent of FastAPI."""
 
     def __init__(self, pipe, reasoner=None, vit=None, model_name: str = "nvidia/Cosmos3-Nano",
-                 guardrails_default: bool = True, allowed_local_media_path: str = "/", batch_engine=None):
+                 guardrails_default: bool = True, allowed_local_media_path: str = "", batch_engine=None):
         self.pipe, self.reasoner, self.vit = pipe, reasoner, vit
         # serve/engine.py::EngineWorker: chat requests share decode steps (continuous batching)
         self.batch_engine = batch_engine
         self.model_name = model_name
         self.guardrails_default = guardrails_default
-        self.allowed_root = Path(allowed_local_media_path)
+        # empty = requests may not name files of this machine at all (media comes as data: URLs or uploads)
+        self.allowed_root = Path(allowed_local_media_path).resolve() if allowed_local_media_path else None
         self.max_image_pixels = 12845056     # server-side ceiling per frame, whatever a request asks for (--max-image-pixels)
         self.max_video_frames = 32           # frames kept per clip unless the request names `max_frames`
         self.jobs: Dict[str, Job] = {}
@@ -185,6 +186,8 @@ class Cosmos3Server:
             self.pipe.safety_checker = checker
 
     def _local(self, p: str) -> Path:
+        if self.allowed_root is None:
+            raise PermissionError("local media paths are disabled (start the server with --allowed-local-media-path DIR)")
         path = Path(p).resolve()
         if self.allowed_root not in path.parents and path != self.allowed_root:
             raise PermissionError(f"{p} is outside --allowed-local-media-path")
@@ -215,8 +218,9 @@ class Cosmos3Server:
             if isinstance(extra, str):
                 extra = json.loads(extra) if extra else {}
             image = video = None
+            ref_tmp = None
             if ref_bytes:
-                p = self.tmp / f"{uuid.uuid4().hex}_{Path(ref_name or 'ref.bin').name}"
+                p = ref_tmp = self.tmp / f"{uuid.uuid4().hex}_{Path(ref_name or 'ref.bin').name}"
                 p.write_bytes(ref_bytes)
                 if p.suffix.lower() in (".png", ".jpg", ".jpeg", ".webp", ".bmp"):
                     image = str(p)
@@ -240,6 +244,9 @@ class Cosmos3Server:
             job.status, job.progress = "completed", 100
         except Exception as e:  # noqa: BLE001 - reported through the job status
             job.status, job.error = "failed", f"{type(e).__name__}: {e}"
+        finally:
+            if ref_tmp is not None:
+                ref_tmp.unlink(missing_ok=True)   # the uploaded reference is only needed while the job runs
         return job
 
     def videos_sync(self, form: dict, ref_bytes=None, ref_name="") -> bytes:
@@ -248,7 +255,9 @@ class Cosmos3Server:
         if job.status != "completed":
             raise RuntimeError(job.error or "generation failed")
         self.metrics.record(None, (time.time() - t0) * 1e3)
-        return Path(job.video_path).read_bytes()
+        data = Path(job.video_path).read_bytes()
+        Path(job.video_path).unlink(missing_ok=True)   # a synchronous result is returned once and not kept
+        return data
 
     def videos_submit(self, form: dict, ref_bytes=None, ref_name="") -> dict:
         job = Job(id=f"video_{uuid.uuid4().hex[:16]}")
@@ -455,15 +464,28 @@ class Cosmos3Server:
                 "usage": {**usage, "total_tokens": usage["prompt_tokens"] + usage["completion_tokens"]}}
 
     def _load_media(self, url: str, is_video: bool, extra: dict):
-        if url.startswith("data:"):
-            raw = base64.b64decode(url.split(",", 1)[1])
-            suffix = ".mp4" if is_video else ".png"
-            p = self.tmp / f"{uuid.uuid4().hex}{suffix}"
-            p.write_bytes(raw)
-        elif url.startswith("file://"):
-            p = self._local(url[7:])
-        else:
-            p = self._local(url)
+        """Frames (and their times) of one media item of a chat request. `data:` URLs are decoded into a temporary file
+        that is removed again before returning; `file://` URLs and bare paths are served only below
+        --allowed-local-media-path (off by default); remote URLs are refused (this server fetches nothing)."""
+        tmp = None
+        try:
+            if url.startswith("data:"):
+                raw = base64.b64decode(url.split(",", 1)[1])
+                suffix = ".mp4" if is_video else ".png"
+                p = tmp = self.tmp / f"{uuid.uuid4().hex}{suffix}"
+                p.write_bytes(raw)
+            elif url.startswith(("http://", "https://")):
+                raise ValueError("remote media URLs are not fetched by this server: send the media as a data: URL")
+            elif url.startswith("file://"):
+                p = self._local(url[7:])
+            else:
+                p = self._local(url)
+            return self._read_media(p, is_video, extra)
+        finally:
+            if tmp is not None:
+                tmp.unlink(missing_ok=True)
+
+    def _read_media(self, p, is_video: bool, extra: dict):
         if not is_video:
             frames, _ = media.read_video(p, max_frames=1)
             return frames, [0.0]
@@ -632,7 +654,9 @@ def main(argv=None) -> int:
     ap.add_argument("--host", default="127.0.0.1")
     ap.add_argument("--omni", action="store_true", help="accepted for CLI compatibility")
     ap.add_argument("--model-class-name", default="Cosmos3OmniDiffusersPipeline")
-    ap.add_argument("--allowed-local-media-path", default="/")
+    ap.add_argument("--allowed-local-media-path", default="",
+                    help="directory below which chat requests may name local files (file:// URLs or paths); "
+                         "empty (default) = no local file access")
     ap.add_argument("--init-timeout", type=int, default=1800)
     ap.add_argument("--tensor-parallel-size", type=int, default=1)
     ap.add_argument("--cfg-parallel-size", type=int, default=1)

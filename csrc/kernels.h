@@ -190,6 +190,8 @@ bool paged_decode_tc_supported(const PagedDecodeArgs& a);
 void paged_decode_tc_launch(const PagedDecodeArgs& a, float* pa, float* pm, cudaStream_t s);
 size_t paged_decode_scratch_bytes(int B, int Hq, int n_splits);
 void paged_decode(const PagedDecodeArgs& a, cudaStream_t s);
+// Loads every CUDA-core decode kernel variant and the merge kernel into the current context (no launch).
+void paged_decode_preload();
 // Scatters new K/V rows [N, Hkv, 128] into the paged caches at flat slots (page * page_size + offset).
 // `n_slots` (token rows of the cache) and `status` serve the bounds-checked build, which reports a slot
 // outside the cache instead of writing there.

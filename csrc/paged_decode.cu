@@ -262,6 +262,17 @@ static void launch_pd(const PagedDecodeArgs& a, float* pa, float* pm, cudaStream
       (bf16*)a.out COSMOS_BC_ARGS(a.num_pages, a.status));
 }
 
+// Loads the CUDA-core decode kernels (every GQA group size) and the split merge kernel into the current context:
+// cudaFuncGetAttributes forces the load that lazy module loading would otherwise do at a kernel's first launch.
+void paged_decode_preload() {
+  cudaFuncAttributes fa;
+  cudaFuncGetAttributes(&fa, cb::paged_decode_kernel<1>);
+  cudaFuncGetAttributes(&fa, cb::paged_decode_kernel<2>);
+  cudaFuncGetAttributes(&fa, cb::paged_decode_kernel<4>);
+  cudaFuncGetAttributes(&fa, cb::paged_decode_kernel<8>);
+  cudaFuncGetAttributes(&fa, cb::paged_decode_merge_kernel);
+}
+
 void paged_decode(const PagedDecodeArgs& a, cudaStream_t s) {
   if (a.B <= 0) return;
   if (a.Hkv <= 0 || a.Hq % a.Hkv != 0) throw std::runtime_error("paged_decode: Hq % Hkv != 0");
@@ -472,6 +483,9 @@ int noalloc_scratch(float** out, char* errbuf, int errbuf_len) {
       std::snprintf(msg, sizeof(msg), "cudaGetSymbolAddress failed: %s", cudaGetErrorString(e));
       return fail(COSMOS_NOALLOC_CUDA_ERROR, errbuf, errbuf_len, msg);
     }
+    // Load every kernel this entry point can launch now (lazy module loading would otherwise do it,
+    // and possibly allocate, at a variant's first launch).
+    cosmos::paged_decode_preload();
     g_noalloc_ptr[dev] = p;
   }
   *out = g_noalloc_ptr[dev];
@@ -500,6 +514,13 @@ extern "C" int cosmos_paged_decode_noalloc(const void* q, const void* k_cache, c
                   "problem too large for the built-in scratch: B*Hq*n_splits = %lld > %d rows; lower n_splits "
                   "or use the allocating entry point", rows, COSMOS_PAGED_DECODE_NOALLOC_MAX_ROWS);
     return fail(COSMOS_NOALLOC_TOO_LARGE, errbuf, errbuf_len, msg);
+  }
+  // an error left pending by somebody else's earlier call is theirs: report it, do not consume it
+  const cudaError_t pending = cudaPeekAtLastError();
+  if (pending != cudaSuccess) {
+    char msg[200];
+    std::snprintf(msg, sizeof(msg), "pending CUDA error from an earlier call: %s", cudaGetErrorString(pending));
+    return fail(COSMOS_NOALLOC_CUDA_ERROR, errbuf, errbuf_len, msg);
   }
   float* scratch = nullptr;
   const int rc = noalloc_scratch(&scratch, errbuf, errbuf_len);

@@ -32,13 +32,20 @@ extern "C" {
 //   `n_splits` in [1, 64] splits every sequence along kv across CTAs.
 // The split partials live in a fixed device array inside the library, so the call performs no
 // cudaMalloc/cudaFree and calls no allocating library routine.
-//   * The first call on a device looks up that array's device address (cudaGetSymbolAddress);
-//     make that first call outside of any stream capture.
+//   * The first call on a device looks up that array's device address (cudaGetSymbolAddress)
+//     and loads every kernel variant this entry point can launch (one per GQA group size 1, 2,
+//     4, 8, plus the kernel that merges the splits), so that no later call has to load code
+//     (with lazy module loading the first launch of a kernel may allocate). Make that first
+//     call during start-up: outside of any stream capture and before the real-time phase.
 //   * All calls on a device share the one array. Each call overwrites every slot it reads, so
 //     nothing has to be cleared in between, but two calls that overlap on the GPU (different
 //     streams) race on it: order them on one stream or with events.
 //   * Problems with B * Hq * n_splits > COSMOS_PAGED_DECODE_NOALLOC_MAX_ROWS are rejected with
 //     COSMOS_NOALLOC_TOO_LARGE; lower n_splits or use the allocating entry point.
+//   * COSMOS_NOALLOC_CUDA_ERROR reports an error raised by this call's own launches. An error
+//     that an earlier, unrelated call left pending on the thread is reported as such ("pending
+//     CUDA error from an earlier call") before anything is launched, and is left for its owner
+//     to clear.
 // When `errbuf` is not NULL a human-readable message is written there on failure.
 int cosmos_paged_decode_noalloc(const void* q, const void* k_cache, const void* v_cache,
                                 const int* block_table, const int* seq_lens, void* out, int B, int Hq,

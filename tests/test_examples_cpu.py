@@ -106,3 +106,45 @@ def test_forward_dynamics_rollout_chains_chunks_on_the_last_frame(pipe):
     assert np.array_equal(again.video[1:], out.video[5:9])
     with pytest.raises(ValueError):
         pipe.forward_dynamics_rollout(start, acts[:10], action_chunk_size=4, height=32, width=32)
+
+
+def test_video_transfer_control_stream_steers_the_generation(pipe):
+    """The control clip runs as a second clean vision stream in a third guidance branch: another control clip or
+    another `control_guidance` changes the result, weight 0 reproduces the generation without a control clip, and
+    chunked generation hands every chunk its own stretch of the control clip."""
+    from cosmos_b200.config import SamplingConfig
+    rng = np.random.default_rng(3)
+    ctrl_a = (rng.random((5, 32, 32, 3)) * 255).astype(np.uint8)
+    ctrl_b = (rng.random((5, 32, 32, 3)) * 255).astype(np.uint8)
+    kw = dict(prompt="a robot arm", num_frames=5, height=32, width=32, fps=8, output_type="latent")
+
+    def run(control, cg, weight=1.0):
+        sc = SamplingConfig(num_steps=2, guidance=3.0, shift=3.0, scheduler="euler", seed=11, control_guidance=cg)
+        extra = {} if control is None else {"control_video": control, "control_weight": weight}
+        return pipe(sampling=sc, **kw, **extra).latents
+
+    base = run(None, None)
+    a15 = run(ctrl_a, 1.5)
+    assert not torch.allclose(a15, base)
+    assert not torch.allclose(run(ctrl_b, 1.5), a15)            # the control clip matters
+    assert not torch.allclose(run(ctrl_a, 0.5), a15)            # and so does its guidance scale
+    assert torch.allclose(run(ctrl_a, 0.0), base, atol=1e-6)    # scale 0 = no control
+    assert torch.allclose(run(ctrl_a, 1.5, weight=0.0), base, atol=1e-6)
+    # chunked: 9 frames in chunks of 5 with 1 conditioning frame -> chunk 1 sees control frames 4..8
+    seen = []
+    orig = pipe.prepare
+
+    def spy(*a, **k):
+        seen.append(None if k.get("control_video") is None else np.asarray(k["control_video"]).copy())
+        return orig(*a, **k)
+
+    long_ctrl = (rng.random((9, 32, 32, 3)) * 255).astype(np.uint8)
+    pipe.prepare = spy
+    try:
+        sc = SamplingConfig(num_steps=1, guidance=2.0, shift=3.0, scheduler="euler", seed=1, control_guidance=1.0)
+        out = pipe.generate_chunked("a robot arm", num_frames=9, height=32, width=32, fps=8, frames_per_chunk=5,
+                                    num_conditional_frames=1, sampling=sc, control_video=long_ctrl, output_type="np")
+    finally:
+        pipe.prepare = orig
+    assert out.video.shape[0] == 9 and len(seen) == 2
+    assert np.array_equal(seen[0], long_ctrl[0:5]) and np.array_equal(seen[1], long_ctrl[4:9])

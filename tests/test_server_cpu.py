@@ -25,8 +25,47 @@ def client():
     pipe = Cosmos3OmniPipeline.from_pretrained("tiny", torch_dtype=torch.float32, vae_widths=(8, 16, 16, 16),
                                                config_overrides=dict(max_text_len=32, n_layers=2))
     vit = VisionEncoder(pipe.cfg).eval()
-    srv = Cosmos3Server(pipe, ReasonerEngine(pipe.transformer, vit), vit, "nvidia/Cosmos3-Nano")
+    srv = Cosmos3Server(pipe, ReasonerEngine(pipe.transformer, vit), vit, "nvidia/Cosmos3-Nano",
+                        allowed_local_media_path="/")
     return TestClient(create_app(srv))
+
+
+def test_local_and_remote_media_are_refused_by_default_and_temp_files_do_not_pile_up(tmp_path):
+    """Without --allowed-local-media-path a request cannot make the server open files of its machine; remote URLs are
+    never fetched; media sent as data: URLs leaves nothing behind in the server's scratch directory."""
+    import base64
+    import io
+    import os
+
+    from PIL import Image
+    torch.manual_seed(0)
+    pipe = Cosmos3OmniPipeline.from_pretrained("tiny", torch_dtype=torch.float32, vae_widths=(8, 16, 16, 16),
+                                               config_overrides=dict(max_text_len=32, n_layers=1))
+    vit = VisionEncoder(pipe.cfg).eval()
+    srv = Cosmos3Server(pipe, ReasonerEngine(pipe.transformer, vit), vit, "nvidia/Cosmos3-Nano")
+    c = TestClient(create_app(srv), raise_server_exceptions=False)
+    img = tmp_path / "a.png"
+    Image.new("RGB", (32, 32), (200, 10, 10)).save(img)
+
+    def ask(url):
+        body = {"max_tokens": 2, "temperature": 0.0,
+                "messages": [{"role": "user", "content": [{"type": "image_url", "image_url": {"url": url}},
+                                                          {"type": "text", "text": "what is this?"}]}]}
+        return c.post("/v1/chat/completions", json=body)
+
+    for url in (f"file://{img}", str(img), "https://example.com/a.png"):
+        assert ask(url).status_code >= 400, url
+    buf = io.BytesIO()
+    Image.open(img).save(buf, format="PNG")
+    ok = ask("data:image/png;base64," + base64.b64encode(buf.getvalue()).decode())
+    assert ok.status_code == 200, ok.text
+    assert os.listdir(srv.tmp) == []
+    # opting in to a directory serves files below it and nothing else
+    srv2 = Cosmos3Server(pipe, ReasonerEngine(pipe.transformer, vit), vit, "nvidia/Cosmos3-Nano",
+                         allowed_local_media_path=str(tmp_path))
+    assert srv2._local(str(img)) == img.resolve()
+    with pytest.raises(PermissionError):
+        srv2._local("/etc/hostname")
 
 
 def test_health_and_models(client):

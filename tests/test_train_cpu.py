@@ -34,7 +34,9 @@ def _worker(rank, world, pc_kw, steps, save_dir=None, resume=False, extra_steps=
     tr = Trainer(model, mesh, TrainConfig(lr=1e-3, max_grad_norm=0.5, fused=False))
     n_dp = pc.dp_shard * pc.dp_replicate
     lat, ids, t, eps = _data(2)
-    d = mesh.index("dp_shard") if n_dp > 1 else slice(None)
+    # one clip per data-parallel rank (replica-major, as train.py shards the data)
+    d = (mesh.index("dp_replicate") * pc.dp_shard + mesh.index("dp_shard")) if n_dp > 1 else slice(None)
+    lat, ids, t, eps = _data(max(2, n_dp))
     sel = slice(d, d + 1) if isinstance(d, int) else d
     start = 0
     if resume:
@@ -66,6 +68,30 @@ def test_fsdp_x_cp_matches_single_process():
     for got, _ in outs:
         for k in want:
             assert torch.allclose(got[k], want[k], atol=3e-5), (k, (got[k] - want[k]).abs().max())
+
+
+def test_replicas_average_their_gradients_and_stay_identical():
+    """dp_replicate 2 x dp_shard 2: four ranks, four clips. Each replica pair holds the same shards; their gradients
+    are averaged over the replicate axis at the optimizer step, so after two steps the replicas are bit-equal and
+    equal the single-process step on the four-clip batch."""
+    outs = run_ranks(_worker, 4, dict(dp_replicate=2, dp_shard=2), 2)
+    (a0, l0), (a1, _), (b0, _), (b1, _) = outs        # ranks 0, 1 = replica 0; ranks 2, 3 = replica 1
+    for k in a0:
+        assert torch.equal(a0[k], b0[k]) and torch.equal(a1[k], b1[k]), k
+    from cosmos_b200.config import ParallelConfig
+    from cosmos_b200.models.mot import MoTModel
+    from cosmos_b200.parallel.mesh import Mesh
+    from cosmos_b200.train import TrainConfig, Trainer
+    model = MoTModel(_cfg(), pad_to=128)
+    model.init_weights(seed=3)
+    tr = Trainer(model, Mesh(ParallelConfig(), 1, 0), TrainConfig(lr=1e-3, max_grad_norm=0.5, fused=False))
+    lat, ids, t, eps = _data(4)
+    for _ in range(2):
+        log = tr.train_step(lat, ids, t=t, eps=eps)
+    want = tr.fsdp.full_state()
+    for k in want:
+        assert torch.allclose(a0[k], want[k], atol=3e-5), (k, (a0[k] - want[k]).abs().max())
+    assert abs(l0[-1]["grad_norm"] - log["grad_norm"]) < 1e-4
 
 
 def test_checkpoint_resume_continues_identically(tmp_path):

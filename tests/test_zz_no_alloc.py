@@ -21,7 +21,7 @@ MAX_ROWS = 8192
 
 def _lib():
     assert ops.load_extension()
-    lib = ctypes.CDLL(str(Path(ops.__file__).resolve().parents[1] / "_C.so"))
+    lib = ctypes.CDLL(str(ops._SO))   # the library file that `ops` loaded (regular or bounds-checked build)
     fn = lib.cosmos_paged_decode_noalloc
     fn.restype = ctypes.c_int
     fn.argtypes = [ctypes.c_void_p] * 6 + [ctypes.c_int] * 5 + [ctypes.c_float, ctypes.c_int, ctypes.c_void_p,
@@ -58,15 +58,31 @@ def test_noalloc_matches_allocating_entry_point_twice():
                                                               (2, 4, 1, 32, [1500, 1200], 8)]):
         q, kc, vc, table, sl = _case(100 + seed, b, hq, hkv, page, lens)
         want = ops.paged_decode(q, kc, vc, table, sl, n_splits=splits, impl=1)  # the same CUDA-core kernel
-        before = torch.cuda.memory_allocated()
-        rc, got, msg = _call(fn, q, kc, vc, table, sl, splits)
+        ref = ops.paged_decode_ref(q, kc, vc, table, sl)                         # and the fp32 definition
+        rc, got, msg = _call(fn, q, kc, vc, table, sl, splits)                   # first call: set-up happens here
         torch.cuda.synchronize()
         assert rc == 0, msg
-        grown = torch.cuda.memory_allocated() - before
-        assert grown <= (got.numel() * 2 + 511) // 512 * 512, grown  # only the output tensor this test made
-        err = (got.float() - want.float()).abs()
-        tol = 2e-2 + 2e-2 * want.float().abs()
-        assert (err <= tol).all(), f"call {seed}: max err {err.max().item()}"
+        # The second call must not take device memory from anybody: neither from PyTorch's caching allocator
+        # (memory_allocated) nor from the driver behind its back (free device memory, which a raw cudaMalloc
+        # would lower). Its output tensor is made before the measurement.
+        out2 = torch.empty_like(q)
+        err2 = ctypes.create_string_buffer(256)
+        torch.cuda.synchronize()
+        free0, _ = torch.cuda.mem_get_info()
+        alloc0 = torch.cuda.memory_allocated()
+        rc2 = fn(q.data_ptr(), kc.data_ptr(), vc.data_ptr(), table.data_ptr(), sl.data_ptr(), out2.data_ptr(),
+                 q.shape[0], q.shape[1], kc.shape[1], kc.shape[2], table.shape[1], 1.0 / 128 ** 0.5, splits,
+                 ctypes.c_void_p(torch.cuda.current_stream().cuda_stream), err2, 256)
+        torch.cuda.synchronize()
+        free1, _ = torch.cuda.mem_get_info()
+        assert rc2 == 0, err2.value.decode()
+        assert torch.cuda.memory_allocated() == alloc0
+        assert free1 >= free0, f"free device memory fell by {free0 - free1} bytes during the call"
+        assert torch.equal(out2, got)
+        for name, target in (("allocating entry point", want), ("fp32 definition", ref)):
+            err = (got.float() - target.float()).abs()
+            tol = 2e-2 + 2e-2 * target.float().abs()
+            assert (err <= tol).all(), f"call {seed} vs {name}: max err {err.max().item()}"
     ops.check_status()
 
 
