@@ -168,11 +168,21 @@ def phase_dit(c: Ctx, rec: dict):
     overrides = {"max_text_len": args.text_len}
     if args.layers:
         overrides["n_layers"] = args.layers
+    full_cfg = None
+    if mesh.size("tp") > 1:
+        # every rank builds only its slice of the block weights (1 / tp of the heads and FFN units)
+        from cosmos_b200.config import get_model_config
+        from cosmos_b200.parallel.tp import tp_local_config
+        full_cfg = get_model_config(args.model, **overrides)
+        loc = tp_local_config(full_cfg, mesh.size("tp"))
+        overrides.update(n_heads=loc.n_heads, n_kv_heads=loc.n_kv_heads, ffn_dim=loc.ffn_dim)
     pipe = Cosmos3OmniPipeline.from_pretrained(args.model, torch_dtype=torch.bfloat16,
                                                device_map=f"cuda:{c.local_rank}", enable_safety_checker=False,
-                                               config_overrides=overrides, engine_kwargs=None)
-    pipe.engine = build_engine_for_mesh(pipe.transformer, mesh, fused=not c.library)
+                                               config_overrides=overrides, engine_kwargs=None,
+                                               layer_seed=(1 + mesh.index("tp")) if full_cfg is not None else None)
+    pipe.engine = build_engine_for_mesh(pipe.transformer, mesh, fused=not c.library, full_cfg=full_cfg)
     cfg = pipe.cfg
+    weight_gb = sum(p.numel() * p.element_size() for p in pipe.transformer.parameters()) / 2 ** 30
     width, height = resolve_size(args.resolution)
     grid = latent_shape(cfg, args.frames, width, height)
     n_tokens = (grid[0] // cfg.patch_t) * (grid[1] // cfg.patch_hw) * (grid[2] // cfg.patch_hw)
@@ -235,6 +245,8 @@ def phase_dit(c: Ctx, rec: dict):
     ms, e2e_ms, prefill_ms = c.max_over_ranks(ms, e2e_ms, prefill_ms)
 
     pub = PUBLISHED_S_PER_VIDEO.get(c.world) if args.model == "Cosmos3-Nano" else None   # the table is Nano's
+    if args.model == "Cosmos3-Super" and c.world == 8:
+        pub = 65.91   # Super I2V 720p on 8 GPUs, PyTorch engine (inference_benchmarks.md:193)
     base_ms = None if pub is None else pub * 1e3 / PUBLISHED_STEPS
     rec.update({
         "metric": f"dit_step_ms ({args.model} T2V {args.resolution}p, one guided denoise step: cond+uncond forward, CFG, Euler)",
@@ -247,6 +259,7 @@ def phase_dit(c: Ctx, rec: dict):
                    "global_batch": 1, "seq_len": n_tokens + args.text_len, "video_tokens": n_tokens,
                    "text_tokens": args.text_len, "frames": args.frames, "resolution": f"{width}x{height}",
                    "layers": cfg.n_layers, "cfg_scale": args.guidance, "parallelism": mesh.describe(),
+                   "transformer_weights_gib_per_gpu": round(weight_gb, 2),
                    "l2": "inputs larger than L2 (16 GB weights + GBs of activations per step)",
                    "baseline_note": "published number is for the reference's own 189-frame model, whose "
                                     "compute per token is far below these dense stand-in shapes"},

@@ -62,7 +62,13 @@ class GeneratorEngine:
     def encode_prompt(self, ids: torch.Tensor) -> List[KV]:
         """ids [B, n] (already padded/truncated to the conditioning length) -> per-layer (K, V)."""
         pos = rope.text_positions(ids.shape[1], 0, ids.device)
-        _, kvs = self.model.ar_forward(self.model.embed_tokens(ids), pos)
+        # a tensor-parallel model whose AR tower holds only this rank's heads runs the prompt through the same
+        # rank group (all-reduced projections); every other layout runs the full AR tower locally
+        pre = getattr(self.ctx, "prefill_context", None)
+        if pre is not None and getattr(self.ctx, "presliced", False):
+            _, kvs = self.model.ar_forward(self.model.embed_tokens(ids), pos, None, pre())
+        else:
+            _, kvs = self.model.ar_forward(self.model.embed_tokens(ids), pos)
         return kvs
 
     # ------------------------------------------------------------------ one DM evaluation

@@ -332,16 +332,22 @@ class MoTModel(nn.Module):
         self.init_weights()
 
     @torch.no_grad()
-    def init_weights(self, seed: Optional[int] = None) -> None:
+    def init_weights(self, seed: Optional[int] = None, layer_seed: Optional[int] = None) -> None:
+        """Random initialisation. `layer_seed` (tensor-parallel shards): the block weights are drawn from it, while the
+        replicated tensors (embeddings, projections, heads) still come from `seed` and so agree on every rank."""
         std = self.cfg.init_std
         gen = None
+        dev = next(self.parameters()).device
         if seed is not None:
-            dev = next(self.parameters()).device
             gen = torch.Generator(device=dev)
             gen.manual_seed(seed)
+        lgen = gen
+        if layer_seed is not None:
+            lgen = torch.Generator(device=dev)
+            lgen.manual_seed(layer_seed)
         for tower in ([self.ar] if self.has_ar else []) + ([self.dm] if self.has_dm else []):
             for layer in tower.layers:
-                layer.init_weights(std, gen)
+                layer.init_weights(std, lgen)
         for name, p in self.named_parameters():
             if ".layers." in name:
                 continue

@@ -67,8 +67,9 @@ def finish(hard: bool = True, grace_s: float = 0.0) -> None:
         os._exit(0)
 
 
-def build_engine_for_mesh(model, mesh: Mesh, fused: bool = True):
-    """GeneratorEngine whose attention context and CFG handling match the mesh."""
+def build_engine_for_mesh(model, mesh: Mesh, fused: bool = True, full_cfg=None):
+    """GeneratorEngine whose attention context and CFG handling match the mesh. `full_cfg`: the full model's
+    configuration when `model` was built from `parallel.tp.tp_local_config` (it holds this rank's weight slices)."""
     from ..models.generator import GeneratorEngine
 
     ctx = None
@@ -81,7 +82,8 @@ def build_engine_for_mesh(model, mesh: Mesh, fused: bool = True):
     if mesh.size("tp") > 1:
         from .tp import TPContext
         dev = next(model.parameters()).device
-        ctx = TPContext(model.cfg, mesh.group("tp"), mesh.group_ranks["tp"], dev, fused=fused)
+        ctx = TPContext(full_cfg or model.cfg, mesh.group("tp"), mesh.group_ranks["tp"], dev, fused=fused,
+                        presliced=full_cfg is not None)
     if mesh.size("cfgp") > 1:
         from .cfgp import CFGParallel
         cfg_group = CFGParallel(mesh, fused=fused)

@@ -99,7 +99,8 @@ class Cosmos3OmniPipeline:
     def from_pretrained(cls, name_or_path: str, torch_dtype=torch.bfloat16, device_map: Optional[str] = None,
                         safety_checker=None, enable_safety_checker: bool = True, seed: int = 0,
                         config_overrides: Optional[dict] = None, towers: Sequence[str] = ("ar", "dm"),
-                        vae_widths: Sequence[int] = (64, 128, 256, 256), engine_kwargs: Optional[dict] = None):
+                        vae_widths: Sequence[int] = (64, 128, 256, 256), engine_kwargs: Optional[dict] = None,
+                        layer_seed: Optional[int] = None):
         device = "cpu"
         if device_map in ("cuda", "auto") and torch.cuda.is_available():
             device = f"cuda:{torch.cuda.current_device()}"
@@ -128,7 +129,7 @@ class Cosmos3OmniPipeline:
         else:
             cfg = get_model_config(name_or_path, **(config_overrides or {}))
         model = MoTModel(cfg, dtype=torch_dtype, device=device, towers=towers)
-        model.init_weights(seed)
+        model.init_weights(seed, layer_seed)
         vae = CausalVideoVAE(cfg.latent_channels, vae_widths).to(device=device, dtype=torch_dtype)
         snd = SoundTokenizer(cfg.sound_latent_dim).to(device=device, dtype=torch_dtype)
         if ckpt_dir is not None:

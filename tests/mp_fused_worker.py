@@ -28,16 +28,26 @@ def run(pc_kw, steps=2):
     cfg = tiny128_config(max_text_len=64, n_heads=8, n_kv_heads=4)
     model = MoTModel(cfg, dtype=torch.bfloat16, device=dev)
     model.init_weights(seed=5)
+    presliced = bool(pc_kw.pop("presliced", False))
     mesh = Mesh(ParallelConfig(**pc_kw), world, rank)
+    local = None
+    if presliced:
+        # the same weights as rank-local slices: a model built from the tensor-parallel local configuration
+        from cosmos_b200.parallel.tp import shard_full_model, tp_local_config
+        local = MoTModel(tp_local_config(cfg, mesh.size("tp")), dtype=torch.bfloat16, device=dev)
+        shard_full_model(model, local, cfg, mesh.size("tp"), mesh.index("tp"))
     outs = {}
     for fused in (False, True):
-        eng = build_engine_for_mesh(model, mesh, fused=fused)
+        if presliced and fused:
+            eng = build_engine_for_mesh(local, mesh, fused=True, full_cfg=cfg)
+        else:
+            eng = build_engine_for_mesh(model, mesh, fused=fused)
         g = torch.Generator(device=dev).manual_seed(1)
         ids_c = torch.randint(0, cfg.vocab_size, (1, 64), generator=g, device=dev)
         ids_u = torch.randint(0, cfg.vocab_size, (1, 64), generator=g, device=dev)
         st = eng.make_state(ids_c, ids_u, (5, 32, 32))
         sc = SamplingConfig(num_steps=steps, guidance=5.0, shift=3.0, seed=2)
-        pipe = Cosmos3OmniPipeline(model, None, None, None, engine=eng)
+        pipe = Cosmos3OmniPipeline(eng.model, None, None, None, engine=eng)
         x = pipe.begin(st, sc)
         for i in range(steps):
             x = pipe.step(x, i)

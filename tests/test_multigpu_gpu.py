@@ -20,9 +20,10 @@ def _torchrun(nproc, script, *args, timeout=420):
 
 @pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs 2 GPUs")
 def test_fused_ulysses_and_cfgp_two_gpus():
-    r = _torchrun(2, "mp_fused_worker.py", json.dumps([{"cp": 2}, {"cfgp": 2}, {"cp": 2, "cp_mode": "ring"}, {"tp": 2}]))
+    r = _torchrun(2, "mp_fused_worker.py", json.dumps([{"cp": 2}, {"cfgp": 2}, {"cp": 2, "cp_mode": "ring"}, {"tp": 2},
+                                                      {"tp": 2, "presliced": True}]))
     assert r.returncode == 0, r.stdout[-3000:] + r.stderr[-3000:]
-    assert r.stdout.count("OK") == 4, r.stdout
+    assert r.stdout.count("OK") == 5, r.stdout
 
 
 @pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs 2 GPUs")
