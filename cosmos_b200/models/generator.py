@@ -178,6 +178,11 @@ class GeneratorEngine:
             else:
                 x_new = ops.ref.cfg_euler_step(x2, vc.reshape(s, f), None if vu is None else vu.reshape(s, f),
                                                sc.guidance, dt, sc.normalize_cfg).reshape(x.shape).to(x.dtype)
+        elif isinstance(smp, samplers.UniPCSampler) and x.is_cuda and vc.dtype == torch.bfloat16 and x.shape[0] == 1:
+            s, f = x.shape[1], x.shape[2]
+            x_new = ops.cfg_unipc_step(x.reshape(s, f).contiguous(), vc.reshape(s, f),
+                                       None if vu is None else vu.reshape(s, f), sc.guidance, smp,
+                                       sc.normalize_cfg).reshape(x.shape)
         else:
             v = samplers.cfg_velocity(vc, vu, sc.guidance, sc.normalize_cfg)
             x_new = smp.step(x, v.to(x.dtype))

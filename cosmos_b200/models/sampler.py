@@ -127,25 +127,100 @@ class UniPCSampler:
         D1_t = x0_new - m0
         return x_t - a_next * B_h * (corr + rho_c * D1_t)
 
-    def step(self, x: torch.Tensor, v: torch.Tensor) -> torch.Tensor:
+    # ------------------------------------------------------------------ the step as linear combinations
+    def _coeffs(self, n_hist: int, lams: List[float], s_cur: float, s_next: float, corrector: bool):
+        """Scalar weights of one `_update`: the result is cx * x + c0 * m0 + c1 * m_prev (+ cn * x0_new for the
+        corrector), with m0 / m_prev the latest / second-latest stored predictions (`n_hist` of them exist)."""
+        a_next = 1 - s_next
+        lam_c, lam_n = self._lam(s_cur), self._lam(s_next)
+        h = lam_n - lam_c
+        hh = -h
+        h_phi_1 = math.expm1(hh)
+        B_h = math.expm1(hh)
+        cx = s_next / max(s_cur, 1e-12)
+        c0 = -a_next * h_phi_1
+        c1 = cn = 0.0
+        rk = (lams[-2] - lam_c) / h if n_hist > 1 else None
+        if not corrector:
+            if rk is not None:
+                c1 = -a_next * B_h * 0.5 / rk
+                c0 += a_next * B_h * 0.5 / rk
+            return cx, c0, c1, cn
+        h_phi_k = h_phi_1 / hh - 1.0
+        if rk is not None:
+            b1 = h_phi_k / B_h
+            h_phi_k2 = h_phi_k / hh - 0.5
+            b2 = h_phi_k2 * 2.0 / B_h
+            det = 1.0 - rk
+            rho_p = (b1 - b2) / det if abs(det) > 1e-12 else 0.0
+            rho_c = b1 - rho_p
+            c1 = -a_next * B_h * rho_p / rk
+            c0 += a_next * B_h * rho_p / rk
+        else:
+            rho_c = 0.5
+        cn = -a_next * B_h * rho_c
+        c0 += a_next * B_h * rho_c
+        return cx, c0, c1, cn
+
+    def plan(self) -> dict:
+        """Weights of the current step (index self.i), for the eager path and for the fused CFG + UniPC kernel:
+            x0  = x - s_cur * v
+            xf  = cL * L + cP * P + cP2 * P2 + cX0 * x0     (corrector; only when `correct`)   else xf = x
+            x0  = xf - s_cur * v                                                     (again, after the corrector)
+            out = dX * xf + dX0 * x0 + dP * P               (predictor)              or out = x0 when `final`
+        with L the latent that entered the previous step (after its corrector), P / P2 the previous / second-previous
+        stored predictions. Afterwards L <- xf, P2 <- P, P <- x0."""
         s_cur = float(self.sigmas[self.i])
         s_next = float(self.sigmas[self.i + 1])
-        xf = x.float()
-        x0 = xf - s_cur * v.float()
-        if self.last_x is not None and s_cur > 0:
-            # corrector: redo the previous step with the now-known prediction at s_cur
+        n = len(self.lam_hist)
+        out = {"s_cur": s_cur, "correct": False, "final": s_next <= 0.0, "cL": 0.0, "cP": 0.0, "cP2": 0.0, "cX0": 0.0,
+               "dX": 0.0, "dX0": 0.0, "dP": 0.0}
+        if n >= 1 and s_cur > 0:
             s_prev = float(self.sigmas[self.i - 1])
-            xf = self._update(self.last_x, self.x0_hist[-self.order:], self.lam_hist[-self.order:], s_prev, s_cur,
-                              x0_new=x0)
-            x0 = xf - s_cur * v.float()
+            k = min(self.order, n)
+            cx, c0, c1, cn = self._coeffs(k, self.lam_hist[-k:], s_prev, s_cur, corrector=True)
+            out.update(correct=True, cL=cx, cP=c0, cP2=c1, cX0=cn)
+        if not out["final"]:
+            lams = (self.lam_hist + [self._lam(s_cur)])[-self.order:]
+            cx, c0, c1, _ = self._coeffs(len(lams), lams, s_cur, s_next, corrector=False)
+            out.update(dX=cx, dX0=c0, dP=c1)
+        return out
+
+    def device_state(self, like: torch.Tensor) -> dict:
+        """Buffers of the fused kernel path: L (latent of the previous step), P / P2 (latest / second-latest stored
+        predictions), n = how many predictions are stored. Allocated once per generation."""
+        if getattr(self, "_dev", None) is None or self._dev["L"].shape != like.shape:
+            self._dev = {"L": torch.zeros_like(like), "P": torch.zeros_like(like), "P2": torch.zeros_like(like), "n": 0}
+        return self._dev
+
+    def advance(self) -> None:
+        """Book-keeping after a step whose tensors were updated elsewhere (the fused kernel)."""
+        self.lam_hist.append(self._lam(float(self.sigmas[self.i])))
+        self.i += 1
+
+    def step(self, x: torch.Tensor, v: torch.Tensor) -> torch.Tensor:
+        pl = self.plan()
+        s_cur = pl["s_cur"]
+        xf = x.float()
+        vf = v.float()
+        x0 = xf - s_cur * vf
+        P = self.x0_hist[-1] if self.x0_hist else None
+        P2 = self.x0_hist[-2] if len(self.x0_hist) > 1 else None
+        if pl["correct"]:
+            xf = pl["cL"] * self.last_x + pl["cP"] * P + pl["cX0"] * x0
+            if P2 is not None and pl["cP2"] != 0.0:
+                xf = xf + pl["cP2"] * P2
+            x0 = xf - s_cur * vf
         self.x0_hist.append(x0)
-        self.lam_hist.append(self._lam(s_cur))
+        self.x0_hist = self.x0_hist[-2:]
         self.last_x = xf
-        if s_next <= 0.0:
+        if pl["final"]:
             out = x0
         else:
-            out = self._update(xf, self.x0_hist[-self.order:], self.lam_hist[-self.order:], s_cur, s_next)
-        self.i += 1
+            out = pl["dX"] * xf + pl["dX0"] * x0
+            if P is not None and pl["dP"] != 0.0:
+                out = out + pl["dP"] * P
+        self.advance()
         return out.to(x.dtype)
 
 

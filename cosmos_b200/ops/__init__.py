@@ -329,6 +329,25 @@ def cfg_euler_step(x, vc, vu, guidance: float, dt: float, normalize: bool = Fals
     return ref.cfg_euler_step(x, vc, vu, guidance, dt, normalize)
 
 
+def cfg_unipc_step(x, vc, vu, guidance: float, smp, normalize: bool = False):
+    """CFG combine + one UniPC step of `smp` (models/sampler.py::UniPCSampler) on the fp32 latent x [rows, d]. On CUDA
+    one kernel reads x, both velocities and the sampler's stored tensors and writes the new latent and the sampler
+    state (x is updated in place and returned); elsewhere the sampler's own `step` runs on the combined velocity."""
+    if (_backend != "library" and x.is_cuda and vc.dtype == torch.bfloat16 and load_extension()
+            and x.shape[-1] % 8 == 0 and x.shape[-1] <= 1024 and x.dtype == torch.float32):
+        pl = smp.plan()
+        st = smp.device_state(x)
+        coef = [pl["s_cur"], pl["cL"], pl["cP"], pl["cP2"], pl["cX0"], pl["dX"], pl["dX0"], pl["dP"]]
+        _k().cfg_unipc_step_(x, vc.contiguous(), None if vu is None else vu.contiguous(), st["L"], st["P"], st["P2"],
+                             guidance, normalize, coef, pl["correct"], pl["final"], st["n"] >= 1, st["n"] >= 2)
+        st["P"], st["P2"] = st["P2"], st["P"]      # the kernel wrote the new prediction into P2's buffer
+        st["n"] += 1
+        smp.advance()
+        return x
+    v = ref.cfg_combine(vc.reshape(x.shape), None if vu is None else vu.reshape(x.shape), guidance, normalize)
+    return smp.step(x, v.to(x.dtype))
+
+
 def l2_flush(buf: torch.Tensor) -> None:
     """Overwrites `buf` (larger than L2) so that the next kernel starts with a cold cache."""
     if buf.is_cuda and load_extension():

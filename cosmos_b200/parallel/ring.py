@@ -4,11 +4,15 @@ all ranks one hop at a time, merging the per-hop partial attention with its log-
 the head counts do not divide, e.g. cp > 8 KV heads, or when heads are already split by TP.)
 
 NVSwitch gives every pair of GPUs the same bandwidth, so "ring" is only a schedule: at hop i
-rank r reads the shard of rank (r + i) mod cp. On CUDA the peers' K/V shards live in symmetric
-memory and hop i+1's shard is pulled into a local double buffer by a copy kernel on a side
-stream (plain peer loads, each byte crosses NVLink once) while the flash-attention kernel works
-on hop i; the attention kernel then reads the local copy. On CPU (gloo) the shards are exchanged
-with all_gather and visited in the same order, which is the oracle for the schedule.
+rank r reads the shard of rank (r + i) mod cp. On CUDA the ranks' K/V shards live in symmetric
+memory and ONE flash-attention launch per layer walks them: the kernel gets one tensor map per
+source (the prompt prefix, this rank's shard, then the peers' shards in rank-staggered order) and its
+TMA producer pulls the peers' K/V tiles over NVLink straight into shared memory (plain loads, no
+multicast), while the running max, the row sums and the output accumulator stay in registers and
+tensor memory across hops. No partial outputs, no log-sum-exp merge, no staging copy. The earlier
+schedule (a copy kernel on a side stream per hop + one attention launch per hop + an fp32 merge)
+is kept as `COSMOS_RING_STAGED=1` for comparison. On CPU (gloo) the shards are exchanged with
+all_gather and visited in the same order, which is the oracle for the schedule.
 """
 from __future__ import annotations
 
@@ -84,7 +88,35 @@ class RingAttn(AttnContext):
             self._ws[key] = (k_sym, v_sym, [ptr1(p) for p in k_ptrs], [ptr1(p) for p in v_ptrs], stage, nbytes)
         return self._ws[key]
 
+    def _attend_in_kernel(self, q, k, v):
+        """One attention launch over the prefix, the own shard and the peers' shards (K/V tiles of the peers are read
+        from their symmetric buffers by the kernel's TMA loads)."""
+        k_sym, v_sym, k_ptrs, v_ptrs, _, _ = self._buffers(k)
+        key = ("addr", tuple(k.shape))
+        if key not in self._ws:
+            buf = self.sg._bufs[f"ring_kv_{tuple(k.shape)}"]
+            nb = (k.numel() * k.element_size() + 255) // 256 * 256
+            self._ws[key] = ([buf.peer_addr(r, 0) for r in range(self.cp)], [buf.peer_addr(r, nb) for r in range(self.cp)])
+        ka, va = self._ws[key]
+        k_sym.copy_(k)
+        v_sym.copy_(v)
+        self.sg.barrier(slot=5)  # every rank's shard is published
+        order = [(self.rank + i) % self.cp for i in range(self.cp)]
+        kp = [ka[r] for r in order]
+        vp = [va[r] for r in order]
+        lens = [k.shape[1]] * self.cp
+        if self._prefix is not None:
+            pk, pv = self._prefix[0].contiguous(), self._prefix[1].contiguous()
+            self._keep = (pk, pv)
+            kp, vp, lens = [pk.data_ptr()] + kp, [pv.data_ptr()] + vp, [pk.shape[1]] + lens
+        o = torch.ops.cosmos_b200.attn_fwd_sources(q, kp, vp, lens, k.shape[2], 1.0 / (q.shape[-1] ** 0.5), None)
+        self.sg.barrier(slot=6)  # peers are done reading this layer's shards
+        return o
+
     def _attend_fused(self, q, k, v, mask):
+        import os
+        if os.environ.get("COSMOS_RING_STAGED") != "1" and self.cp + 1 <= 9:
+            return self._attend_in_kernel(q, k, v)
         k_sym, v_sym, k_ptrs, v_ptrs, stage, nbytes = self._buffers(k)
         k_sym.copy_(k)
         v_sym.copy_(v)

@@ -29,8 +29,22 @@ constexpr int TILE_BYTES = TQ * HD * 2;        // 32 KB
 constexpr int HALF_BYTES = TILE_BYTES / 2;     // one 64-column half, 16 KB
 constexpr int ATT_SMEM = 2 * TILE_BYTES + NSLOT * TILE_BYTES + 1024 + 256;
 
+constexpr int MAX_KV_SRC = 9;  // K/V sources of one launch: e.g. a local prompt prefix + 8 ranks' sequence shards
+
+// Tensor maps of the K/V sources. Source s covers src_len[s] keys; the kernel walks the sources in the given
+// order, so the keys of the whole sequence never have to sit in one buffer. A source may be another GPU's
+// symmetric buffer: the TMA loads then pull its tiles over NVLink straight into this SM's shared memory
+// (plain loads of one CTA each, no multicast), which is the ring-KV schedule of context parallelism inside
+// the attention main loop.
+struct KVMaps {
+  CUtensorMap k[MAX_KV_SRC];
+  CUtensorMap v[MAX_KV_SRC];
+};
+
 struct AttnParams {
-  int Sq, Skv, Hq, Hkv, group;  // group = Hq / Hkv
+  int n_src;                    // number of K/V sources (1 = the ordinary single-buffer call)
+  int src_len[MAX_KV_SRC];      // keys per source (MASK_FULL only when n_src > 1)
+  int Sq, Skv, Hq, Hkv, group;  // group = Hq / Hkv; Skv = total number of keys
   int mask, n_ar;
   float scale_log2;  // softmax scale * log2(e)
   bf16* O;
@@ -123,8 +137,8 @@ __device__ __forceinline__ int kv_limit(int qi, const AttnParams& p) {
 // illegal instruction on sm_100a.
 template <int EMU, bool DBG>
 __global__ void __launch_bounds__(ATT_THREADS, 1)
-flash_attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
-                      const __grid_constant__ CUtensorMap tmV, const AttnParams p) {
+flash_attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ KVMaps kv,
+                      const AttnParams p) {
   extern __shared__ uint8_t smem_raw[];
   const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
   uint8_t* gen_base = smem_raw + (smem_base - smem_u32(smem_raw));
@@ -154,7 +168,11 @@ flash_attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
 
   // Number of K/V blocks this CTA visits.
   int n_blocks;
-  {
+  const bool multi = p.n_src > 1;
+  if (multi) {
+    n_blocks = 0;
+    for (int s = 0; s < p.n_src; ++s) n_blocks += (p.src_len[s] + TKV - 1) / TKV;
+  } else {
     const int last_row = min(p.Sq - 1, q0 + 2 * TQ - 1);
     int lim = p.Skv;
     if (p.mask == MASK_CAUSAL) lim = kv_limit(last_row, p);
@@ -177,8 +195,10 @@ flash_attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
     *abort_flag = 0;
     fence_barrier_init();
     prefetch_tmap(&tmQ);
-    prefetch_tmap(&tmK);
-    prefetch_tmap(&tmV);
+    for (int s = 0; s < p.n_src; ++s) {
+      prefetch_tmap(&kv.k[s]);
+      prefetch_tmap(&kv.v[s]);
+    }
   }
   if (warp == 1) {
     tmem_alloc(tmem_slot, 512);
@@ -205,6 +225,7 @@ flash_attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
                       q0 + t * TQ, batch);
       int issued = 0;
       bool ok = true;
+      int src = 0, jb = 0;  // current K/V source and block within it
       for (int i = 0; i < 2 * n_blocks; ++i) {
         const int s = i % NSLOT;
         const uint32_t ph = (i / NSLOT) & 1;
@@ -212,13 +233,19 @@ flash_attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
           ok = false;
           break;
         }
-        const int j = i >> 1;
-        const CUtensorMap* tm = (i & 1) ? &tmV : &tmK;
+        const CUtensorMap* tm = (i & 1) ? &kv.v[src] : &kv.k[src];
         const uint32_t dst = kv_smem + s * TILE_BYTES;
         mbar_arrive_expect_tx(kv_full(s), TILE_BYTES);
-        tma_load_4d(dst, tm, kv_full(s), 0, kv_head, j * TKV, batch);
-        tma_load_4d(dst + HALF_BYTES, tm, kv_full(s), 64, kv_head, j * TKV, batch);
+        tma_load_4d(dst, tm, kv_full(s), 0, kv_head, jb * TKV, batch);
+        tma_load_4d(dst + HALF_BYTES, tm, kv_full(s), 64, kv_head, jb * TKV, batch);
         issued = i + 1;
+        if (i & 1) {  // K and V of this block are on their way: next block, possibly of the next source
+          ++jb;
+          if (multi && jb * TKV >= p.src_len[src]) {
+            jb = 0;
+            ++src;
+          }
+        }
       }
       if (!ok) {
         volatile int no_abort = 0;
@@ -326,6 +353,7 @@ flash_attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
     const Ex2Consts exc = ex2_consts();
     float m_used = -1e30f, l = 0.f;
     bool ok = true;
+    int src = 0, jb = 0;  // K/V source and block within it (multi-source launches)
     for (int j = 0; j < n_blocks; ++j) {
       if (!mbar_wait(s_full(t), j & 1, abort_flag, p.status, ST_TIMEOUT_SOFTMAX)) {
         ok = false;
@@ -338,11 +366,26 @@ flash_attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
       tmem_ld32(s_addr + 64, *reinterpret_cast<uint32_t(*)[32]>(&s[64]));
       tmem_ld32(s_addr + 96, *reinterpret_cast<uint32_t(*)[32]>(&s[96]));
       tmem_wait_ld();
-      const int kv0 = j * TKV;
-      if (kv0 + TKV > limit) {
+      if (multi) {
+        // the last block of a source may be ragged: rows beyond the source's end were zero-filled by the copy
+        const int valid = p.src_len[src] - jb * TKV;
+        if (valid < TKV) {
 #pragma unroll
-        for (int i = 0; i < 128; ++i)
-          if (kv0 + i >= limit) s[i] = 0xff800000u;  // -inf
+          for (int i = 0; i < 128; ++i)
+            if (i >= valid) s[i] = 0xff800000u;  // -inf
+        }
+        ++jb;
+        if (jb * TKV >= p.src_len[src]) {
+          jb = 0;
+          ++src;
+        }
+      } else {
+        const int kv0 = j * TKV;
+        if (kv0 + TKV > limit) {
+#pragma unroll
+          for (int i = 0; i < 128; ++i)
+            if (kv0 + i >= limit) s[i] = 0xff800000u;  // -inf
+        }
       }
       // eight independent chains of three-input max (60 instructions for 128 values)
       float mx8[8];
@@ -486,7 +529,10 @@ void flash_attn_fwd(const AttnArgs& a, cudaStream_t stream) {
     throw std::runtime_error("flash_attn_fwd: MoT mask needs Skv == Sq");
   if ((a.o_stride_s % 8) || (a.o_stride_h % 8) || (a.o_stride_b % 8))
     throw std::runtime_error("flash_attn_fwd: output strides must be multiples of 8 elements");
-  using Kern = void (*)(const CUtensorMap, const CUtensorMap, const CUtensorMap, const cb::AttnParams);
+  using Kern = void (*)(const CUtensorMap, const cb::KVMaps, const cb::AttnParams);
+  const int n_src = a.n_src > 0 ? a.n_src : 1;
+  if (n_src > cb::MAX_KV_SRC) throw std::runtime_error("flash_attn_fwd: too many K/V sources");
+  if (n_src > 1 && a.mask != MASK_FULL) throw std::runtime_error("flash_attn_fwd: several K/V sources need the full mask");
   // a.exp_emulation: of every 8 pairs of scores, this many take their exp2 on the FMA pipe (0, 2 or 3; measured
   // slower than 0 whenever the MMAs run); a.debug: timing experiments (wrong results)
   Kern kern = cb::flash_attn_fwd_kernel<0, false>;
@@ -515,11 +561,24 @@ void flash_attn_fwd(const AttnArgs& a, cudaStream_t stream) {
   auto fix = [](long long sb, long long ss, int S) { return sb > 0 ? sb : ss * S; };
   CUtensorMap tq = make_qkv_map(a.Q, a.B, a.Sq, a.Hq, fix(a.q_stride_b, a.q_stride_s, a.Sq),
                                 a.q_stride_s, a.q_stride_h);
-  CUtensorMap tk = make_qkv_map(a.K, a.B, a.Skv, a.Hkv, fix(a.k_stride_b, a.k_stride_s, a.Skv),
-                                a.k_stride_s, a.k_stride_h);
-  CUtensorMap tv = make_qkv_map(a.V, a.B, a.Skv, a.Hkv, fix(a.v_stride_b, a.v_stride_s, a.Skv),
-                                a.v_stride_s, a.v_stride_h);
+  cb::KVMaps kv{};
   cb::AttnParams p{};
+  p.n_src = n_src;
+  if (n_src == 1) {
+    kv.k[0] = make_qkv_map(a.K, a.B, a.Skv, a.Hkv, fix(a.k_stride_b, a.k_stride_s, a.Skv), a.k_stride_s, a.k_stride_h);
+    kv.v[0] = make_qkv_map(a.V, a.B, a.Skv, a.Hkv, fix(a.v_stride_b, a.v_stride_s, a.Skv), a.v_stride_s, a.v_stride_h);
+    p.src_len[0] = a.Skv;
+  } else {
+    // every source is a contiguous [B, len, Hkv, 128] buffer (possibly on a peer GPU)
+    for (int s = 0; s < n_src; ++s) {
+      const int len = a.src_len[s];
+      if (len <= 0) throw std::runtime_error("flash_attn_fwd: empty K/V source");
+      const long long ss = (long long)a.Hkv * 128, sb = ss * len;
+      kv.k[s] = make_qkv_map(a.src_k[s], a.B, len, a.Hkv, sb, ss, 128);
+      kv.v[s] = make_qkv_map(a.src_v[s], a.B, len, a.Hkv, sb, ss, 128);
+      p.src_len[s] = len;
+    }
+  }
   p.Sq = a.Sq; p.Skv = a.Skv; p.Hq = a.Hq; p.Hkv = a.Hkv; p.group = a.Hq / a.Hkv;
   p.mask = a.mask; p.n_ar = a.n_ar;
   p.scale_log2 = a.scale * 1.4426950408889634f;
@@ -530,7 +589,7 @@ void flash_attn_fwd(const AttnArgs& a, cudaStream_t stream) {
   p.status = a.status;
   p.debug = a.debug;
   dim3 grid((a.Sq + 2 * cb::TQ - 1) / (2 * cb::TQ), a.Hq, a.B);
-  kern<<<grid, cb::ATT_THREADS, cb::ATT_SMEM, stream>>>(tq, tk, tv, p);
+  kern<<<grid, cb::ATT_THREADS, cb::ATT_SMEM, stream>>>(tq, kv, p);
 }
 
 }  // namespace cosmos

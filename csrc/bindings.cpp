@@ -392,6 +392,47 @@ std::tuple<Tensor, Tensor> attn_fwd(const Tensor& q, const Tensor& k, const Tens
   return {o, lse};
 }
 
+// Attention of q [B, Sq, Hq, 128] over several K/V sources in ONE launch (full mask): source s is a contiguous
+// [B, lens[s], Hkv, 128] bf16 buffer at device address k_ptrs[s] / v_ptrs[s] (own memory or a peer GPU's symmetric
+// buffer), visited in the given order. This is ring-KV context parallelism with the peers' K/V tiles pulled over
+// NVLink by the attention kernel's own TMA loads.
+Tensor attn_fwd_sources(const Tensor& q, std::vector<int64_t> k_ptrs, std::vector<int64_t> v_ptrs,
+                        std::vector<int64_t> lens, int64_t Hkv, double scale, const OptT& out) {
+  check_bf16_cuda(q, "q");
+  c10::cuda::CUDAGuard guard(q.device());
+  TORCH_CHECK(q.dim() == 4 && q.size(3) == 128 && q.stride(3) == 1, "q must be [B, Sq, Hq, 128]");
+  const size_t n = k_ptrs.size();
+  TORCH_CHECK(n >= 1 && n <= 9 && v_ptrs.size() == n && lens.size() == n, "1 to 9 K/V sources with one length each");
+  const int64_t B = q.size(0), Sq = q.size(1), Hq = q.size(2);
+  Tensor o = (out.has_value() && out->defined()) ? *out : at::empty({B, Sq, Hq, 128}, q.options());
+  TORCH_CHECK(o.dim() == 4 && o.stride(3) == 1 && o.size(1) == Sq && o.size(2) == Hq, "bad out");
+  cosmos::AttnArgs a;
+  a.Q = q.data_ptr(); a.O = o.data_ptr();
+  a.B = (int)B; a.Sq = (int)Sq; a.Hq = (int)Hq; a.Hkv = (int)Hkv;
+  a.q_stride_b = q.stride(0); a.q_stride_s = q.stride(1); a.q_stride_h = q.stride(2);
+  a.o_stride_b = o.stride(0); a.o_stride_s = o.stride(1); a.o_stride_h = o.stride(2);
+  a.scale = (float)scale; a.mask = MASK_FULL;
+  int64_t total = 0;
+  a.n_src = (int)n;
+  for (size_t s = 0; s < n; ++s) {
+    TORCH_CHECK(lens[s] > 0 && k_ptrs[s] % 16 == 0 && v_ptrs[s] % 16 == 0, "sources need a positive length and 16-byte aligned addresses");
+    a.src_k[s] = reinterpret_cast<const void*>(k_ptrs[s]);
+    a.src_v[s] = reinterpret_cast<const void*>(v_ptrs[s]);
+    a.src_len[s] = (int)lens[s];
+    total += lens[s];
+  }
+  a.Skv = (int)total;
+  if (n == 1) {   // the ordinary single-buffer call
+    a.n_src = 0;
+    a.K = a.src_k[0]; a.V = a.src_v[0];
+    a.k_stride_h = a.v_stride_h = 128; a.k_stride_s = a.v_stride_s = Hkv * 128;
+    a.k_stride_b = a.v_stride_b = Hkv * 128 * lens[0];
+  }
+  a.status = status_tensor(q.get_device()).data_ptr<int>();
+  cosmos::flash_attn_fwd(a, cur_stream());
+  return o;
+}
+
 // Flash attention backward: q/k/v/do [B, S, H, 128] (unit inner stride), lse/delta [B, Hq, Sq] fp32
 // -> (dq, dk, dv) contiguous bf16.
 std::tuple<Tensor, Tensor, Tensor> attn_bwd(const Tensor& q, const Tensor& k, const Tensor& v, const Tensor& dout,
@@ -650,6 +691,24 @@ std::tuple<Tensor, Tensor> qkv_post_bwd(const Tensor& qkv, const Tensor& dq, con
 }
 
 // x fp32 [rows, d] updated in place: x += dt * cfg(vc, vu)
+void cfg_unipc_step_(Tensor x, const Tensor& vc, const OptT& vu, Tensor L, const Tensor& P, Tensor P2, double guidance,
+                     bool normalize, std::vector<double> coef, bool correct, bool final_step, bool has_p, bool has_p2) {
+  c10::cuda::CUDAGuard guard(x.device());
+  TORCH_CHECK(x.is_cuda() && x.scalar_type() == at::kFloat && x.is_contiguous() && x.dim() == 2, "x must be fp32 [rows, d]");
+  check_bf16_cuda(vc, "vc");
+  TORCH_CHECK(vc.is_contiguous() && vc.numel() == x.numel(), "vc must match x");
+  if (vu.has_value() && vu->defined()) TORCH_CHECK(vu->is_contiguous() && vu->numel() == x.numel(), "vu must match x");
+  for (const Tensor* t : {static_cast<const Tensor*>(&L), &P, static_cast<const Tensor*>(&P2)})
+    TORCH_CHECK(t->is_cuda() && t->scalar_type() == at::kFloat && t->is_contiguous() && t->numel() == x.numel(),
+                "L, P, P2 must be fp32 tensors of x's size");
+  TORCH_CHECK(coef.size() == 8, "eight coefficients expected");
+  float c8[8];
+  for (int i = 0; i < 8; ++i) c8[i] = (float)coef[i];
+  cosmos::cfg_unipc_step(x.data_ptr<float>(), vc.data_ptr(), opt_ptr(vu), L.data_ptr<float>(), P.data_ptr<float>(),
+                         P2.data_ptr<float>(), (float)guidance, normalize ? 1 : 0, c8, correct, final_step, has_p, has_p2,
+                         x.size(0), (int)x.size(1), cur_stream());
+}
+
 void cfg_euler_step_(Tensor x, const Tensor& vc, const OptT& vu, double guidance, double dt, bool normalize) {
   c10::cuda::CUDAGuard guard(x.device());
   TORCH_CHECK(x.is_cuda() && x.scalar_type() == at::kFloat && x.is_contiguous(), "x must be fp32 contiguous");
@@ -1044,6 +1103,7 @@ TORCH_LIBRARY(cosmos_b200, m) {
   m.def("attn_bwd_scores", &attn_bwd_scores);
   m.def("attn_fwd", &attn_fwd);
   m.def("attn_bwd", &attn_bwd);
+  m.def("attn_fwd_sources", &attn_fwd_sources);
   m.def("rmsnorm_bwd", &rmsnorm_bwd);
   m.def("gated_residual_bwd", &gated_residual_bwd);
   m.def("swiglu_bwd", &swiglu_bwd);
@@ -1055,6 +1115,7 @@ TORCH_LIBRARY(cosmos_b200, m) {
   m.def("gated_residual", &gated_residual);
   m.def("swiglu", &swiglu);
   m.def("cfg_euler_step_", &cfg_euler_step_);
+  m.def("cfg_unipc_step_", &cfg_unipc_step_);
   m.def("l2_flush_", &l2_flush_);
   m.def("conv3d_cl", &conv3d_cl);
   m.def("rmsnorm_silu", &rmsnorm_silu);

@@ -282,6 +282,102 @@ cfg_euler_kernel(float* __restrict__ x, const bf16* __restrict__ vc, const bf16*
   }
 }
 
+// CFG combine + one UniPC step (predictor and, from the second step on, the corrector of the previous step) in one
+// pass over the latent. One warp per row; d % 8 == 0, d <= 1024. With v = cfg(vc, vu):
+//   x0 = x - s_cur v;   if correct: xf = cL L + cP P + cP2 P2 + cX0 x0, x0 = xf - s_cur v   else xf = x
+//   out = final ? x0 : dX xf + dX0 x0 + dP P
+// and then  x <- out,  L <- xf,  P2's buffer <- x0  (the caller swaps the roles of P and P2 afterwards).
+// vu may be a peer GPU's buffer (CFG-parallel): it is only read.
+struct UniPCCoef {
+  float s_cur, cL, cP, cP2, cX0, dX, dX0, dP;
+  int correct, final_step, has_p, has_p2;
+};
+__global__ void __launch_bounds__(256)
+cfg_unipc_kernel(float* __restrict__ x, const bf16* __restrict__ vc, const bf16* __restrict__ vu,
+                 float* __restrict__ L, const float* __restrict__ P, float* __restrict__ P2, float guidance,
+                 int normalize, UniPCCoef k, long long rows, int d) {
+  const int lane = threadIdx.x & 31;
+  const long long row = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  if (row >= rows) return;
+  const int nvec = d >> 3;
+  float v[4][8];
+  float nc = 0.f, nv = 0.f;
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const int vi = lane + i * 32;
+    if (vi < nvec) {
+      float c[8];
+      unpack8(reinterpret_cast<const uint4*>(vc + row * d)[vi], c);
+      if (vu) {
+        float u[8];
+        unpack8(reinterpret_cast<const uint4*>(vu + row * d)[vi], u);
+#pragma unroll
+        for (int e = 0; e < 8; ++e) v[i][e] = u[e] + guidance * (c[e] - u[e]);
+      } else {
+#pragma unroll
+        for (int e = 0; e < 8; ++e) v[i][e] = c[e];
+      }
+#pragma unroll
+      for (int e = 0; e < 8; ++e) {
+        nc += c[e] * c[e];
+        nv += v[i][e] * v[i][e];
+      }
+    }
+  }
+  float rs = 1.f;
+  if (normalize) {
+    nc = warp_sum(nc);
+    nv = warp_sum(nv);
+    rs = nv > 0.f ? fminf(1.f, sqrtf(nc / nv)) : 1.f;
+  }
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const int vi = lane + i * 32;
+    if (vi < nvec) {
+      const long long off = row * d + vi * 8;
+      float xv[8], lv[8], pv[8], p2v[8];
+      const float4* xp = reinterpret_cast<const float4*>(x + off);
+      *reinterpret_cast<float4*>(&xv[0]) = xp[0];
+      *reinterpret_cast<float4*>(&xv[4]) = xp[1];
+#pragma unroll
+      for (int e = 0; e < 8; ++e) lv[e] = pv[e] = p2v[e] = 0.f;
+      if (k.correct) {
+        *reinterpret_cast<float4*>(&lv[0]) = reinterpret_cast<const float4*>(L + off)[0];
+        *reinterpret_cast<float4*>(&lv[4]) = reinterpret_cast<const float4*>(L + off)[1];
+      }
+      if (k.has_p) {
+        *reinterpret_cast<float4*>(&pv[0]) = reinterpret_cast<const float4*>(P + off)[0];
+        *reinterpret_cast<float4*>(&pv[4]) = reinterpret_cast<const float4*>(P + off)[1];
+      }
+      if (k.has_p2 && k.correct) {
+        *reinterpret_cast<float4*>(&p2v[0]) = reinterpret_cast<const float4*>(P2 + off)[0];
+        *reinterpret_cast<float4*>(&p2v[4]) = reinterpret_cast<const float4*>(P2 + off)[1];
+      }
+      float xf[8], x0[8], out[8];
+#pragma unroll
+      for (int e = 0; e < 8; ++e) {
+        const float ve = rs * v[i][e];
+        x0[e] = xv[e] - k.s_cur * ve;
+        xf[e] = xv[e];
+        if (k.correct) {
+          xf[e] = k.cL * lv[e] + k.cP * pv[e] + k.cP2 * p2v[e] + k.cX0 * x0[e];
+          x0[e] = xf[e] - k.s_cur * ve;
+        }
+        out[e] = k.final_step ? x0[e] : k.dX * xf[e] + k.dX0 * x0[e] + k.dP * pv[e];
+      }
+      float4* xo = reinterpret_cast<float4*>(x + off);
+      xo[0] = *reinterpret_cast<float4*>(&out[0]);
+      xo[1] = *reinterpret_cast<float4*>(&out[4]);
+      float4* lo = reinterpret_cast<float4*>(L + off);
+      lo[0] = *reinterpret_cast<float4*>(&xf[0]);
+      lo[1] = *reinterpret_cast<float4*>(&xf[4]);
+      float4* po = reinterpret_cast<float4*>(P2 + off);
+      po[0] = *reinterpret_cast<float4*>(&x0[0]);
+      po[1] = *reinterpret_cast<float4*>(&x0[4]);
+    }
+  }
+}
+
 __global__ void l2_flush_kernel(uint4* buf, size_t n) {
   for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n;
        i += (size_t)gridDim.x * blockDim.x)
@@ -387,6 +483,19 @@ void cfg_euler_step(float* x, const void* vc, const void* vu, float guidance, fl
   const unsigned grid = (unsigned)((rows + 7) / 8);
   cb::cfg_euler_kernel<<<grid, 256, 0, s>>>(x, (const bf16*)vc, (const bf16*)vu, guidance, dt,
                                             normalize, rows, d);
+}
+
+void cfg_unipc_step(float* x, const void* vc, const void* vu, float* L, const float* P, float* P2, float guidance,
+                    int normalize, const float* coef8, int correct, int final_step, int has_p, int has_p2,
+                    long long rows, int d, cudaStream_t s) {
+  check_d(d, "cfg_unipc_step");
+  if (d > 1024) throw std::runtime_error("cfg_unipc_step: row length above 1024 is not supported");
+  if (rows == 0) return;
+  cb::UniPCCoef k{coef8[0], coef8[1], coef8[2], coef8[3], coef8[4], coef8[5], coef8[6], coef8[7],
+                  correct, final_step, has_p, has_p2};
+  const unsigned grid = (unsigned)((rows + 7) / 8);
+  cb::cfg_unipc_kernel<<<grid, 256, 0, s>>>(x, (const bf16*)vc, (const bf16*)vu, L, P, P2, guidance, normalize, k,
+                                            rows, d);
 }
 
 void l2_flush(void* buf, size_t bytes, cudaStream_t s) {

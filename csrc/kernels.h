@@ -105,6 +105,14 @@ struct AttnArgs {
   const long long* dest_ptr = nullptr;
   int rows_per_dest = 0;
   int* status = nullptr;
+  // Several K/V sources in one launch (ring-KV context parallelism: this rank's shard, the peers' shards in their
+  // symmetric buffers, a local prompt prefix): n_src > 1, src_k / src_v [n_src] device addresses of contiguous
+  // [B, src_len[s], Hkv, 128] bf16 buffers, walked in this order; K, V and Skv (= sum of src_len) then only describe
+  // the total. Full mask only.
+  int n_src = 0;
+  const void* src_k[9] = {};
+  const void* src_v[9] = {};
+  int src_len[9] = {};
   // Of every 8 pairs of scores, this many compute exp2 with a polynomial on the FMA pipe (2, 3; 0 = none).
   // Measured on B200: faster than 0 with the MMAs switched off, slower with them on, so 0 is the default.
   int exp_emulation = 0;
@@ -156,6 +164,13 @@ void swiglu(const void* gate_up, void* y, long long rows, int dff, cudaStream_t 
 // vc/vu may point into another GPU's memory (CFG-parallel exchange by peer loads).
 void cfg_euler_step(float* x, const void* vc, const void* vu, float guidance, float dt,
                     int normalize, long long rows, int d, cudaStream_t s);
+// CFG combine + one UniPC step (order 2, with the previous step's corrector) on the fp32 latent x [rows, d]:
+// coef8 = {s_cur, cL, cP, cP2, cX0, dX, dX0, dP} (models/sampler.py::UniPCSampler.plan). L (latent of the previous
+// step), P (latest stored prediction) are read; on return x holds the new latent, L the corrected latent of this
+// step and P2's buffer the new prediction (the caller then swaps P and P2).
+void cfg_unipc_step(float* x, const void* vc, const void* vu, float* L, const float* P, float* P2, float guidance,
+                    int normalize, const float* coef8, int correct, int final_step, int has_p, int has_p2,
+                    long long rows, int d, cudaStream_t s);
 void l2_flush(void* buf, size_t bytes, cudaStream_t s);
 // y = silu(rmsnorm(x) * gamma) over rows of d channels (channels-last tokenizer activations)
 void rmsnorm_silu(const void* x, const void* gamma, void* y, long long rows, int d, float eps, cudaStream_t s);

@@ -662,3 +662,43 @@ def test_gemm_result_does_not_depend_on_the_tile_to_cta_assignment():
             _close(outs[0], want, 3e-2, 2e-2, "gemm")
     finally:
         k.gemm_set_grid_limit(0)
+
+
+def test_attention_over_several_kv_sources_in_one_launch():
+    """Ring-KV in the kernel: K/V given as separate buffers of different (ragged) lengths, visited in order by one
+    launch, equals attention over their concatenation."""
+    torch.manual_seed(5)
+    b, sq, hq, hkv = 1, 700, 8, 2
+    lens = [512, 300, 129, 77]
+    q = torch.randn(b, sq, hq, 128, device="cuda").bfloat16()
+    ks = [torch.randn(b, n, hkv, 128, device="cuda").bfloat16() for n in lens]
+    vs = [torch.randn(b, n, hkv, 128, device="cuda").bfloat16() for n in lens]
+    o = torch.ops.cosmos_b200.attn_fwd_sources(q, [t.data_ptr() for t in ks], [t.data_ptr() for t in vs], lens, hkv,
+                                               128 ** -0.5, None)
+    ref, _ = ops.ref.attention(q.float(), torch.cat(ks, 1).float(), torch.cat(vs, 1).float())
+    assert (o.float() - ref).abs().max().item() < 2e-2
+    one, _ = ops.attention(q, torch.cat(ks, 1), torch.cat(vs, 1))
+    assert (o.float() - one.float()).abs().max().item() < 1e-2
+    single = torch.ops.cosmos_b200.attn_fwd_sources(q, [ks[0].data_ptr()], [vs[0].data_ptr()], lens[:1], hkv, 128 ** -0.5, None)
+    ref1, _ = ops.ref.attention(q.float(), ks[0].float(), vs[0].float())
+    assert (single.float() - ref1).abs().max().item() < 2e-2
+
+
+@pytest.mark.parametrize("normalize", [False, True])
+def test_cfg_unipc_step_matches_the_sampler(normalize):
+    """The fused CFG + UniPC kernel against the sampler's own fp32 step, over a whole schedule (first step without a
+    corrector, later ones with it, the last one returning the prediction)."""
+    from cosmos_b200.models import sampler as samplers
+    torch.manual_seed(2)
+    rows, d, steps = 300, 64, 6
+    sig = samplers.shifted_sigmas(steps, 3.0, None, device="cpu")
+    a, b = samplers.UniPCSampler(sig), samplers.UniPCSampler(sig)
+    x = torch.randn(rows, d, device="cuda")
+    xa, xb = x.clone(), x.clone()
+    for i in range(steps):
+        vc = torch.randn(rows, d, device="cuda").bfloat16()
+        vu = torch.randn(rows, d, device="cuda").bfloat16()
+        v = ops.ref.cfg_combine(vc, vu, 4.0, normalize)
+        xa = a.step(xa, v)
+        xb = ops.cfg_unipc_step(xb, vc, vu, 4.0, b, normalize)
+        assert (xa - xb).abs().max().item() < 2e-4 * (1 + xa.abs().max().item()), i
