@@ -56,6 +56,12 @@ class GeneratorEngine:
         dev = next(model.parameters()).device
         self.ctx = ctx if ctx is not None else (WorkspaceAttn() if dev.type == "cuda" else LOCAL_ATTN)
         self.cfg_group = cfg_group
+        # Launch-bound tiers (images, 256p clips): the model evaluation of a denoise step is captured in a CUDA graph
+        # once per generation and replayed for the other steps (the reference's PyTorch engine also runs "with CUDA
+        # Graphs enabled where supported", inference_benchmarks.md:39). Sequences longer than this many DM tokens are
+        # compute bound and run eagerly; 0 switches graphs off. Single-GPU layouts only (COSMOS_CUDA_GRAPH_TOKENS).
+        import os
+        self.graph_max_tokens = int(os.environ.get("COSMOS_CUDA_GRAPH_TOKENS", "8192"))
 
     # ------------------------------------------------------------------ prompt
     @torch.no_grad()
@@ -101,6 +107,23 @@ class GeneratorEngine:
         if na:
             out[:, nv + ns:, :st.action_dim] = heads["action"]
         return out
+
+    def _graphed_velocity(self, tokens: torch.Tensor, sigma: torch.Tensor, st: GenState, ar_kv: List[KV],
+                          with_control: bool = False) -> torch.Tensor:
+        """`velocity` through a CUDA graph when the call is small enough to be launch bound and runs on this GPU alone.
+        The graph (inputs: tokens and sigma; everything else belongs to the generation state) is captured at the first
+        call of a generation and kept on the state object; the result lives in the graph's static output buffer."""
+        eligible = (tokens.is_cuda and self.graph_max_tokens > 0 and tokens.shape[1] <= self.graph_max_tokens
+                    and self.cfg_group is None and type(self.ctx) in (AttnContext, WorkspaceAttn)
+                    and tokens.dtype == torch.bfloat16 and ops.get_backend() == "own" and not torch.is_grad_enabled())
+        if not eligible:
+            return self.velocity(tokens, sigma, st, ar_kv, with_control)
+        from ..utils.graphs import GraphedCallable
+        graphs = st.__dict__.setdefault("_graphs", {})
+        key = (tuple(tokens.shape), bool(with_control), id(ar_kv))
+        if key not in graphs:
+            graphs[key] = GraphedCallable(lambda t, s: self.velocity(t, s, st, ar_kv, with_control), [tokens, sigma])
+        return graphs[key](tokens, sigma)
 
     @torch.no_grad()
     def _velocity_with_control(self, tokens, sigma, st: GenState, ar_kv: List[KV]) -> torch.Tensor:
@@ -153,17 +176,17 @@ class GeneratorEngine:
                 if not hasattr(st, "_kv2") else st._kv2
             st._kv2 = kv2
             sig = torch.full((2,), float(sigma), device=dev)
-            v2 = self.velocity(xin.to(mdt).expand(2, -1, -1), sig, st, kv2)
+            v2 = self._graphed_velocity(xin.to(mdt).expand(2, -1, -1).contiguous(), sig, st, kv2)
             vc, vu = v2[:1], v2[1:]
         else:
             sig = torch.full((1,), float(sigma), device=dev)
-            vc, vu = self.velocity(xin.to(mdt), sig, st, st.ar_kv_cond), None
+            vc, vu = self._graphed_velocity(xin.to(mdt), sig, st, st.ar_kv_cond), None
         if gc != 0.0:
             # third branch: the same prompt with the control stream. v = v_u + g (v_c - v_u) + g_c (v_ctrl - v_c)
             # equals the two-branch formula with v_c replaced by v_c + (g_c / g) (v_ctrl - v_c), so the fused
             # CFG + sampler kernel serves it unchanged.
             sig1 = torch.full((1,), float(sigma), device=dev)
-            v_ctrl = self.velocity(xin.to(mdt), sig1, st, st.ar_kv_cond, with_control=True)
+            v_ctrl = self._graphed_velocity(xin.to(mdt), sig1, st, st.ar_kv_cond, with_control=True)
             w = gc / float(sc.guidance) if vu is not None else gc
             vc = torch.lerp(vc.float(), v_ctrl.float(), w).to(vc.dtype)
         if smp is None or isinstance(smp, samplers.EulerSampler):
