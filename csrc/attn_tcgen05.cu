@@ -19,15 +19,24 @@
 // (peer GPUs) to fuse the head->sequence all-to-all of Ulysses context parallelism.
 #include "common.cuh"
 #include "kernels.h"
+#include <cstdlib>
 
 namespace cb {
 
 constexpr int ATT_THREADS = 384;
 constexpr int TQ = 128, TKV = 128, HD = 128;
-constexpr int NSLOT = 5;
 constexpr int TILE_BYTES = TQ * HD * 2;        // 32 KB
 constexpr int HALF_BYTES = TILE_BYTES / 2;     // one 64-column half, 16 KB
-constexpr int ATT_SMEM = 2 * TILE_BYTES + NSLOT * TILE_BYTES + 1024 + 256;
+// NC = 1: one CTA streams whole 128-key K and V tiles (32 KB ring slots, 5 of them).
+// NC = 2: a CTA pair (cluster of 2, tcgen05 cta_group::2, M = 256 = tile t of both CTAs) shares every K/V block:
+// for S = Q K^T each CTA stages 64 of the block's 128 keys (the B operand's N rows are split over the pair), for
+// O += P V each CTA stages all 128 keys of 64 of the 128 head-dim columns. A ring slot is 16 KB (8 of them), the
+// K/V bytes copied into and read from each CTA's shared memory are halved, and so is the L2 -> SM traffic.
+template <int NC> struct AttCfg {
+  static constexpr int NSLOT = NC == 2 ? 8 : 5;
+  static constexpr int SLOT_BYTES = TILE_BYTES / NC;
+  static constexpr int SMEM = 2 * TILE_BYTES + NSLOT * SLOT_BYTES + 1024 + 256;
+};
 
 constexpr int MAX_KV_SRC = 9;  // K/V sources of one launch: e.g. a local prompt prefix + 8 ranks' sequence shards
 
@@ -135,16 +144,22 @@ __device__ __forceinline__ int kv_limit(int qi, const AttnParams& p) {
 // ex2.approx.f16x2 / bf16x2 (the MUFU pipe retires them at half the instruction rate, so no gain), and P in
 // fp16 with V in bf16 is not possible at all: tcgen05.mma kind::f16 with an fp16 A and a bf16 B operand is an
 // illegal instruction on sm_100a.
-template <int EMU, bool DBG>
+template <int EMU, bool DBG, int NC>
 __global__ void __launch_bounds__(ATT_THREADS, 1)
 flash_attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ KVMaps kv,
                       const AttnParams p) {
+  constexpr int NSLOT = AttCfg<NC>::NSLOT;
+  constexpr int SLOT_BYTES = AttCfg<NC>::SLOT_BYTES;
+  constexpr int K_HALF = SLOT_BYTES / 2;   // one 64-column half of a K slot
   extern __shared__ uint8_t smem_raw[];
   const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
   uint8_t* gen_base = smem_raw + (smem_base - smem_u32(smem_raw));
   const uint32_t q_smem = smem_base;
   const uint32_t kv_smem = smem_base + 2 * TILE_BYTES;
-  const uint32_t bar_base = kv_smem + NSLOT * TILE_BYTES;
+  const uint32_t bar_base = kv_smem + NSLOT * SLOT_BYTES;
+  // CTA pair: rank 0 (the leader) issues the MMAs and owns the barriers that both CTAs signal (q_full, kv_full,
+  // p_full); s_full, kv_empty and o_final exist in both CTAs and the leader's commits reach both.
+  const uint32_t cta_rank = NC == 2 ? cluster_ctarank() : 0u;
   const uint32_t q_full = bar_base;
   auto kv_full = [&](int s) { return bar_base + 8u * (1 + s); };
   auto kv_empty = [&](int s) { return bar_base + 8u * (1 + NSLOT + s); };
@@ -153,18 +168,21 @@ flash_attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
   auto o_final = [&](int t) { return bar_base + 8u * (7 + 2 * NSLOT + t); };
   constexpr int NBAR = 9 + 2 * NSLOT;
   const uint32_t tmem_slot = bar_base + 8u * NBAR;
-  volatile uint32_t* tmem_slot_ptr =
-      reinterpret_cast<volatile uint32_t*>(gen_base + 7 * TILE_BYTES + 8 * NBAR);
-  volatile int* abort_flag = reinterpret_cast<volatile int*>(gen_base + 7 * TILE_BYTES + 8 * NBAR + 8);
+  constexpr int BAR_OFF = 2 * TILE_BYTES + NSLOT * SLOT_BYTES;
+  volatile uint32_t* tmem_slot_ptr = reinterpret_cast<volatile uint32_t*>(gen_base + BAR_OFF + 8 * NBAR);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(gen_base + BAR_OFF + 8 * NBAR + 8);
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
   const int dbg = DBG ? p.debug : 0;
   const int qt = (p.mask == MASK_FULL) ? blockIdx.x : (gridDim.x - 1 - blockIdx.x);
+  // the other CTA of a pair holds the neighbouring query tile; both walk the K/V blocks that the later tile needs
+  const int qt_peer = NC == 2 ? ((p.mask == MASK_FULL) ? int(blockIdx.x ^ 1u) : int(gridDim.x - 1 - (blockIdx.x ^ 1u))) : qt;
   const int head = blockIdx.y;
   const int batch = blockIdx.z;
   const int kv_head = head / p.group;
   const int q0 = qt * 2 * TQ;
+  const int q0_hi = max(qt, qt_peer) * 2 * TQ;
 
   // Number of K/V blocks this CTA visits.
   int n_blocks;
@@ -173,7 +191,7 @@ flash_attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
     n_blocks = 0;
     for (int s = 0; s < p.n_src; ++s) n_blocks += (p.src_len[s] + TKV - 1) / TKV;
   } else {
-    const int last_row = min(p.Sq - 1, q0 + 2 * TQ - 1);
+    const int last_row = min(p.Sq - 1, q0_hi + 2 * TQ - 1);
     int lim = p.Skv;
     if (p.mask == MASK_CAUSAL) lim = kv_limit(last_row, p);
     if (p.mask == MASK_MOT) lim = (last_row >= p.n_ar) ? p.Skv : last_row + 1;
@@ -188,8 +206,8 @@ flash_attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
     }
     for (int t = 0; t < 2; ++t) {
       mbar_init(s_full(t), 1);
-      mbar_init(p_full(t, 0), 128);
-      mbar_init(p_full(t, 1), 128);
+      mbar_init(p_full(t, 0), NC == 2 ? 8 : 128);   // pair: one arrival per softmax warp of both CTAs
+      mbar_init(p_full(t, 1), NC == 2 ? 8 : 128);
       mbar_init(o_final(t), 1);
     }
     *abort_flag = 0;
@@ -201,11 +219,17 @@ flash_attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
     }
   }
   if (warp == 1) {
-    tmem_alloc(tmem_slot, 512);
-    tmem_relinquish();
+    if constexpr (NC == 2) {
+      tmem_alloc_pair(tmem_slot, 512);
+      tmem_relinquish_pair();
+    } else {
+      tmem_alloc(tmem_slot, 512);
+      tmem_relinquish();
+    }
   }
   tc_fence_before();
   __syncthreads();
+  if constexpr (NC == 2) cluster_sync_all();  // the peer's barriers are initialised before anything signals them
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot_ptr;
 
@@ -216,13 +240,17 @@ flash_attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
     asm volatile("setmaxnreg.dec.sync.aligned.u32 56;");
     if (warp == 0 && lane == 0) {
       // ---------------- TMA producer
-      mbar_arrive_expect_tx(q_full, 2 * TILE_BYTES);
+      const uint32_t qf = NC == 2 ? mapa(q_full, 0) : q_full;
+      if (cta_rank == 0) mbar_arrive_expect_tx(q_full, NC * 2 * TILE_BYTES);
 #pragma unroll
       for (int t = 0; t < 2; ++t)
 #pragma unroll
-        for (int h = 0; h < 2; ++h)
-          tma_load_4d(q_smem + t * TILE_BYTES + h * HALF_BYTES, &tmQ, q_full, h * 64, head,
-                      q0 + t * TQ, batch);
+        for (int h = 0; h < 2; ++h) {
+          if constexpr (NC == 2)
+            tma_load_4d_pair(q_smem + t * TILE_BYTES + h * HALF_BYTES, &tmQ, qf, h * 64, head, q0 + t * TQ, batch);
+          else
+            tma_load_4d(q_smem + t * TILE_BYTES + h * HALF_BYTES, &tmQ, qf, h * 64, head, q0 + t * TQ, batch);
+        }
       int issued = 0;
       bool ok = true;
       int src = 0, jb = 0;  // current K/V source and block within it
@@ -234,10 +262,24 @@ flash_attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
           break;
         }
         const CUtensorMap* tm = (i & 1) ? &kv.v[src] : &kv.k[src];
-        const uint32_t dst = kv_smem + s * TILE_BYTES;
-        mbar_arrive_expect_tx(kv_full(s), TILE_BYTES);
-        tma_load_4d(dst, tm, kv_full(s), 0, kv_head, jb * TKV, batch);
-        tma_load_4d(dst + HALF_BYTES, tm, kv_full(s), 64, kv_head, jb * TKV, batch);
+        const uint32_t dst = kv_smem + s * SLOT_BYTES;
+        if constexpr (NC == 2) {
+          // both CTAs' bytes are counted on the leader's barrier, which expects the pair's total
+          const uint32_t fb = mapa(kv_full(s), 0);
+          if (cta_rank == 0) mbar_arrive_expect_tx(kv_full(s), 2 * SLOT_BYTES);
+          if (i & 1) {
+            // V: all 128 keys of this CTA's 64 head-dim columns
+            tma_load_4d_pair(dst, tm, fb, int(cta_rank) * 64, kv_head, jb * TKV, batch);
+          } else {
+            // K: this CTA's 64 keys of the block, both 64-column halves
+            tma_load_4d_pair(dst, tm, fb, 0, kv_head, jb * TKV + int(cta_rank) * 64, batch);
+            tma_load_4d_pair(dst + K_HALF, tm, fb, 64, kv_head, jb * TKV + int(cta_rank) * 64, batch);
+          }
+        } else {
+          mbar_arrive_expect_tx(kv_full(s), SLOT_BYTES);
+          tma_load_4d(dst, tm, kv_full(s), 0, kv_head, jb * TKV, batch);
+          tma_load_4d(dst + HALF_BYTES, tm, kv_full(s), 64, kv_head, jb * TKV, batch);
+        }
         issued = i + 1;
         if (i & 1) {  // K and V of this block are on their way: next block, possibly of the next source
           ++jb;
@@ -248,21 +290,28 @@ flash_attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
         }
       }
       if (!ok) {
-        volatile int no_abort = 0;
-        mbar_wait(q_full, 0, &no_abort, nullptr, 0);
-        const int first = issued > NSLOT ? issued - NSLOT : 0;
-        for (int i = first; i < issued; ++i)
-          mbar_wait(kv_full(i % NSLOT), (i / NSLOT) & 1, &no_abort, nullptr, 0);
+        if (NC == 2 && cta_rank != 0) {
+          // this CTA's copies are counted on the leader's barriers, which only the leader can wait on: give
+          // them a fixed time (far beyond a copy's latency) to land instead
+          const long long t0 = clock64();
+          while (clock64() - t0 < 2000000ll) {}
+        } else {
+          volatile int no_abort = 0;
+          mbar_wait(q_full, 0, &no_abort, nullptr, 0);
+          const int first = issued > NSLOT ? issued - NSLOT : 0;
+          for (int i = first; i < issued; ++i)
+            mbar_wait(kv_full(i % NSLOT), (i / NSLOT) & 1, &no_abort, nullptr, 0);
+        }
       }
-    } else if (warp == 1) {
+    } else if (warp == 1 && cta_rank == 0) {
       // ---------------- MMA issuer: the whole warp walks the schedule (barrier phases, descriptors and
       // addresses are warp-uniform values), one elected lane issues the tcgen05 instructions
       const bool issuer = elect_one();
       auto wait_all = [&](uint32_t bar, uint32_t phase) {
         return __all_sync(0xffffffffu, mbar_wait(bar, phase, abort_flag, p.status, ST_TIMEOUT_MMA)) != 0;
       };
-      constexpr uint32_t idesc_qk = make_idesc_bf16(TQ, TKV, 0, 0);
-      constexpr uint32_t idesc_pv = make_idesc_bf16(TQ, HD, 0, 1);
+      constexpr uint32_t idesc_qk = make_idesc_bf16(TQ * NC, TKV, 0, 0);
+      constexpr uint32_t idesc_pv = make_idesc_bf16(TQ * NC, HD, 0, 1);
       // Descriptors differ only in their 14-bit start-address field, so they are built as
       // one 64-bit constant plus a small address offset (in 16-byte units).
       const uint64_t q_desc0 = make_smem_desc_sw128(q_smem, 16, 1024);
@@ -271,28 +320,42 @@ flash_attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
       auto issue_qk = [&](int t, int slot) {
         const uint32_t d = tmem_base + t * 128;
         const uint64_t a0 = q_desc0 + uint64_t(t * (TILE_BYTES >> 4));
-        const uint64_t b0 = k_desc0 + uint64_t(slot * (TILE_BYTES >> 4));
+        const uint64_t b0 = k_desc0 + uint64_t(slot * (SLOT_BYTES >> 4));
         if ((dbg & 1) || !issuer) return;
 #pragma unroll
         for (int kk = 0; kk < 8; ++kk) {
-          const uint32_t off = (kk >> 2) * (HALF_BYTES >> 4) + 2 * (kk & 3);
-          mma_ss(d, a0 + off, b0 + off, idesc_qk, kk > 0 ? 1u : 0u);
+          const uint32_t off_a = (kk >> 2) * (HALF_BYTES >> 4) + 2 * (kk & 3);
+          const uint32_t off_b = (kk >> 2) * (K_HALF >> 4) + 2 * (kk & 3);
+          if constexpr (NC == 2)
+            mma_ss_pair(d, a0 + off_a, b0 + off_b, idesc_qk, kk > 0 ? 1u : 0u);
+          else
+            mma_ss(d, a0 + off_a, b0 + off_b, idesc_qk, kk > 0 ? 1u : 0u);
         }
       };
+      // a commit releases / signals in this CTA and, for a pair, in the peer as well
       auto commit = [&](uint32_t bar) {
-        if (issuer) tc_commit(bar);
+        if (!issuer) return;
+        if constexpr (NC == 2) {
+          tc_commit_pair(bar);
+          tc_commit_pair(mapa(bar, 1));
+        } else {
+          tc_commit(bar);
+        }
       };
       // P is handed over in two halves of 64 keys, so the first four k-steps of PV run while the
       // softmax warps still compute the exponentials of the second half.
       auto issue_pv = [&](int t, int slot, bool acc, int half) {
         const uint32_t d = tmem_base + 256 + t * 128;
         const uint32_t a0 = tmem_base + t * 128;
-        const uint64_t b0 = v_desc0 + uint64_t(slot * (TILE_BYTES >> 4));
+        const uint64_t b0 = v_desc0 + uint64_t(slot * (SLOT_BYTES >> 4));
         if ((dbg & 2) || !issuer) return;
 #pragma unroll
         for (int k4 = 0; k4 < 4; ++k4) {
           const int kk = half * 4 + k4;
-          mma_ts(d, a0 + kk * 8, b0 + uint64_t(kk * (2048 >> 4)), idesc_pv, (acc || kk > 0) ? 1u : 0u);
+          if constexpr (NC == 2)
+            mma_ts_pair(d, a0 + kk * 8, b0 + uint64_t(kk * (2048 >> 4)), idesc_pv, (acc || kk > 0) ? 1u : 0u);
+          else
+            mma_ts(d, a0 + kk * 8, b0 + uint64_t(kk * (2048 >> 4)), idesc_pv, (acc || kk > 0) ? 1u : 0u);
         }
       };
       bool ok = wait_all(q_full, 0);
@@ -391,10 +454,12 @@ flash_attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
       float mx8[8];
 #pragma unroll
       for (int e = 0; e < 8; ++e) mx8[e] = __uint_as_float(s[e]);
+      if (!((dbg & 8) && j > 0)) {   // timing experiment: no row maximum after the first block
 #pragma unroll
-      for (int i = 8; i < 128; i += 16)
+        for (int i = 8; i < 128; i += 16)
 #pragma unroll
-        for (int e = 0; e < 8; ++e) mx8[e] = max3(mx8[e], __uint_as_float(s[i + e]), __uint_as_float(s[i + 8 + e]));
+          for (int e = 0; e < 8; ++e) mx8[e] = max3(mx8[e], __uint_as_float(s[i + e]), __uint_as_float(s[i + 8 + e]));
+      }
       const float mx = max3(max3(mx8[0], mx8[1], mx8[2]), max3(mx8[3], mx8[4], mx8[5]), fmaxf(mx8[6], mx8[7]));
       const float m_new = fmaxf(m_used, mx * sl2);
       if (j == 0) {
@@ -449,7 +514,18 @@ flash_attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
         tmem_st32(s_addr + half * 32, pk);
         tmem_wait_st();
         tc_fence_before();
-        mbar_arrive(p_full(t, half));
+        if constexpr (NC == 2) {
+          // one arrival per warp on the leader's barrier (a cluster-scope arrive from the peer CTA)
+          __syncwarp();
+          if (lane == 0) {
+            if (cta_rank == 0)
+              mbar_arrive(p_full(t, half));
+            else
+              mbar_arrive_cluster(mapa(p_full(t, half), 0));
+          }
+        } else {
+          mbar_arrive(p_full(t, half));
+        }
       }
       {
         float a0, a1, b0, b1;
@@ -501,10 +577,16 @@ flash_attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
   // ---------------- common tail
   tc_fence_before();
   __syncthreads();
+  // neither CTA of a pair leaves (or frees tensor memory) while the other may still signal its barriers or have
+  // MMAs in flight that read its shared memory
+  if constexpr (NC == 2) cluster_sync_all();
   if (warp == 1) {
     __syncwarp();
     tc_fence_after();
-    tmem_dealloc(tmem_base, 512);
+    if constexpr (NC == 2)
+      tmem_dealloc_pair(tmem_base, 512);
+    else
+      tmem_dealloc(tmem_base, 512);
   }
 }
 
@@ -513,11 +595,60 @@ flash_attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
 namespace cosmos {
 
 static CUtensorMap make_qkv_map(const void* base, int B, int S, int H, long long sb, long long ss,
-                                long long sh) {
+                                long long sh, int box_rows = 128) {
   const uint64_t dims[4] = {128, (uint64_t)H, (uint64_t)S, (uint64_t)B};
   const uint64_t strides[3] = {(uint64_t)sh * 2, (uint64_t)ss * 2, (uint64_t)sb * 2};
-  const uint32_t box[4] = {64, 1, 128, 1};
+  const uint32_t box[4] = {64, 1, (uint32_t)box_rows, 1};
   return cbh::make_tmap_bf16(base, 4, dims, strides, box, true);
+}
+
+// A/B switch: query blocks of more than one 256-row tile run on CTA pairs when on (COSMOS_ATTN_CTA_PAIR=1 or
+// attn_set_cta_pair). Off by default: the pair halves the K/V bytes through each CTA's shared memory, but every
+// hand-over of the per-tile chain (scores ready -> softmax -> P ready -> MMA issue) then crosses to the other CTA,
+// and the chain, not the operand traffic, bounds this kernel: measured 4.68 ms against 3.56 ms for single CTAs at
+// 32768 x 32768, 8 / 2 heads, in seconds-long loops on a B200.
+static int g_attn_pair = -1;
+static bool attn_pair_enabled() {
+  if (g_attn_pair < 0) {
+    const char* e = std::getenv("COSMOS_ATTN_CTA_PAIR");
+    g_attn_pair = (e && e[0] == '1') ? 1 : 0;
+  }
+  return g_attn_pair == 1;
+}
+void attn_set_cta_pair(bool on) { g_attn_pair = on ? 1 : 0; }
+
+template <int EMU, bool DBG>
+static void launch_attn(int nc, dim3 grid, const CUtensorMap& tq, const cb::KVMaps& kv, const cb::AttnParams& p,
+                        cudaStream_t stream) {
+  cudaLaunchConfig_t cfg{};
+  cfg.blockDim = dim3(cb::ATT_THREADS, 1, 1);
+  cfg.stream = stream;
+  cudaLaunchAttribute at[1];
+  at[0].id = cudaLaunchAttributeClusterDimension;
+  at[0].val.clusterDim.x = nc; at[0].val.clusterDim.y = 1; at[0].val.clusterDim.z = 1;
+  cfg.attrs = at; cfg.numAttrs = 1;
+  if (nc == 2) {
+    static bool configured = false;
+    if (!configured) {
+      cudaFuncSetAttribute(cb::flash_attn_fwd_kernel<EMU, DBG, 2>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                           cb::AttCfg<2>::SMEM);
+      configured = true;
+    }
+    grid.x = (grid.x + 1) & ~1u;   // whole pairs; a CTA beyond the last query row computes and stores nothing
+    cfg.gridDim = grid;
+    cfg.dynamicSmemBytes = cb::AttCfg<2>::SMEM;
+    cudaLaunchKernelEx(&cfg, cb::flash_attn_fwd_kernel<EMU, DBG, 2>, tq, kv, p);
+  } else {
+    static bool configured = false;
+    if (!configured) {
+      cudaFuncSetAttribute(cb::flash_attn_fwd_kernel<EMU, DBG, 1>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                           cb::AttCfg<1>::SMEM);
+      configured = true;
+    }
+    cfg.gridDim = grid;
+    cfg.dynamicSmemBytes = cb::AttCfg<1>::SMEM;
+    cudaLaunchKernelEx(&cfg, cb::flash_attn_fwd_kernel<EMU, DBG, 1>, tq, kv, p);
+  }
 }
 
 void flash_attn_fwd(const AttnArgs& a, cudaStream_t stream) {
@@ -529,34 +660,13 @@ void flash_attn_fwd(const AttnArgs& a, cudaStream_t stream) {
     throw std::runtime_error("flash_attn_fwd: MoT mask needs Skv == Sq");
   if ((a.o_stride_s % 8) || (a.o_stride_h % 8) || (a.o_stride_b % 8))
     throw std::runtime_error("flash_attn_fwd: output strides must be multiples of 8 elements");
-  using Kern = void (*)(const CUtensorMap, const cb::KVMaps, const cb::AttnParams);
   const int n_src = a.n_src > 0 ? a.n_src : 1;
   if (n_src > cb::MAX_KV_SRC) throw std::runtime_error("flash_attn_fwd: too many K/V sources");
   if (n_src > 1 && a.mask != MASK_FULL) throw std::runtime_error("flash_attn_fwd: several K/V sources need the full mask");
-  // a.exp_emulation: of every 8 pairs of scores, this many take their exp2 on the FMA pipe (0, 2 or 3; measured
-  // slower than 0 whenever the MMAs run); a.debug: timing experiments (wrong results)
-  Kern kern = cb::flash_attn_fwd_kernel<0, false>;
-  if (a.debug) {
-    switch (a.exp_emulation) {
-      case 2: kern = cb::flash_attn_fwd_kernel<2, true>; break;
-      case 3: kern = cb::flash_attn_fwd_kernel<3, true>; break;
-      default: kern = cb::flash_attn_fwd_kernel<0, true>; break;
-    }
-  } else {
-    switch (a.exp_emulation) {
-      case 2: kern = cb::flash_attn_fwd_kernel<2, false>; break;
-      case 3: kern = cb::flash_attn_fwd_kernel<3, false>; break;
-      default: break;
-    }
-  }
-  static thread_local Kern configured[12] = {};
-  bool seen = false;
-  for (Kern k : configured) seen |= (k == kern);
-  if (!seen) {
-    cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, cb::ATT_SMEM);
-    for (Kern& k : configured)
-      if (!k) { k = kern; break; }
-  }
+  dim3 grid((a.Sq + 2 * cb::TQ - 1) / (2 * cb::TQ), a.Hq, a.B);
+  // CTA pairs as soon as there is more than one 256-row query block
+  const int nc = (attn_pair_enabled() && grid.x >= 2) ? 2 : 1;
+  const int k_rows = nc == 2 ? 64 : 128;   // a pair's CTA copies 64 of a block's 128 keys for QK^T
   // B == 1 tensors may carry a zero batch stride; TMA needs a non-zero multiple of 16 bytes.
   auto fix = [](long long sb, long long ss, int S) { return sb > 0 ? sb : ss * S; };
   CUtensorMap tq = make_qkv_map(a.Q, a.B, a.Sq, a.Hq, fix(a.q_stride_b, a.q_stride_s, a.Sq),
@@ -565,7 +675,8 @@ void flash_attn_fwd(const AttnArgs& a, cudaStream_t stream) {
   cb::AttnParams p{};
   p.n_src = n_src;
   if (n_src == 1) {
-    kv.k[0] = make_qkv_map(a.K, a.B, a.Skv, a.Hkv, fix(a.k_stride_b, a.k_stride_s, a.Skv), a.k_stride_s, a.k_stride_h);
+    kv.k[0] = make_qkv_map(a.K, a.B, a.Skv, a.Hkv, fix(a.k_stride_b, a.k_stride_s, a.Skv), a.k_stride_s, a.k_stride_h,
+                           k_rows);
     kv.v[0] = make_qkv_map(a.V, a.B, a.Skv, a.Hkv, fix(a.v_stride_b, a.v_stride_s, a.Skv), a.v_stride_s, a.v_stride_h);
     p.src_len[0] = a.Skv;
   } else {
@@ -574,7 +685,7 @@ void flash_attn_fwd(const AttnArgs& a, cudaStream_t stream) {
       const int len = a.src_len[s];
       if (len <= 0) throw std::runtime_error("flash_attn_fwd: empty K/V source");
       const long long ss = (long long)a.Hkv * 128, sb = ss * len;
-      kv.k[s] = make_qkv_map(a.src_k[s], a.B, len, a.Hkv, sb, ss, 128);
+      kv.k[s] = make_qkv_map(a.src_k[s], a.B, len, a.Hkv, sb, ss, 128, k_rows);
       kv.v[s] = make_qkv_map(a.src_v[s], a.B, len, a.Hkv, sb, ss, 128);
       p.src_len[s] = len;
     }
@@ -588,8 +699,21 @@ void flash_attn_fwd(const AttnArgs& a, cudaStream_t stream) {
   p.dest_ptr = a.dest_ptr; p.rows_per_dest = a.rows_per_dest > 0 ? a.rows_per_dest : 1;
   p.status = a.status;
   p.debug = a.debug;
-  dim3 grid((a.Sq + 2 * cb::TQ - 1) / (2 * cb::TQ), a.Hq, a.B);
-  kern<<<grid, cb::ATT_THREADS, cb::ATT_SMEM, stream>>>(tq, kv, p);
+  // a.exp_emulation: of every 8 pairs of scores, this many take their exp2 on the FMA pipe (0, 2 or 3; measured
+  // slower than 0 whenever the MMAs run); a.debug: timing experiments (wrong results)
+  if (a.debug) {
+    switch (a.exp_emulation) {
+      case 2: launch_attn<2, true>(nc, grid, tq, kv, p, stream); break;
+      case 3: launch_attn<3, true>(nc, grid, tq, kv, p, stream); break;
+      default: launch_attn<0, true>(nc, grid, tq, kv, p, stream); break;
+    }
+  } else {
+    switch (a.exp_emulation) {
+      case 2: launch_attn<2, false>(nc, grid, tq, kv, p, stream); break;
+      case 3: launch_attn<3, false>(nc, grid, tq, kv, p, stream); break;
+      default: launch_attn<0, false>(nc, grid, tq, kv, p, stream); break;
+    }
+  }
 }
 
 }  // namespace cosmos

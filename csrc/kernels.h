@@ -119,6 +119,8 @@ struct AttnArgs {
   int debug = 0;  // timing experiments (results are wrong): 1 = no QK MMAs, 2 = no PV MMAs, 4 = no exponentials
 };
 void flash_attn_fwd(const AttnArgs& a, cudaStream_t stream);
+// A/B switch: CTA-pair (cta_group::2) attention tiles on / off (off by default: measured slower, see attn_tcgen05.cu).
+void attn_set_cta_pair(bool on);
 
 // Flash attention backward (attn_bwd_tcgen05.cu): dQ, dK, dV from Q, K, V, dO, the forward's
 // log-sum-exp and delta = rowsum(dO * O). Inputs [B, S, H, 128] bf16 with element strides; outputs

@@ -730,3 +730,23 @@ def test_denoise_steps_through_a_cuda_graph_equal_the_eager_steps(scheduler):
         assert (limit > 0) == bool(st.__dict__.get("_graphs"))
     assert torch.isfinite(outs[0]).all()
     assert (outs[0] - outs[8192]).abs().max().item() <= 1e-5 * (1 + outs[0].abs().max().item())
+
+
+def test_attention_on_cta_pairs_matches_the_reference():
+    """The CTA-pair variant of the forward kernel (cta_group::2 tiles; off by default) on shapes with an odd number of
+    query blocks, causal and MoT masks, GQA and a batch."""
+    k = torch.ops.cosmos_b200
+    k.attn_set_cta_pair(True)
+    try:
+        torch.manual_seed(1)
+        for (b, sq, skv, hq, hkv, mask, n_ar) in ((1, 777, 777, 4, 4, ops.MASK_CAUSAL, 0), (2, 600, 900, 2, 1, ops.MASK_FULL, 0),
+                                                 (1, 1300, 1300, 4, 2, ops.MASK_MOT, 333)):
+            q = torch.randn(b, sq, hq, 128, device=DEV).bfloat16()
+            kk = torch.randn(b, skv, hkv, 128, device=DEV).bfloat16()
+            v = torch.randn(b, skv, hkv, 128, device=DEV).bfloat16()
+            o, lse = ops.attention(q, kk, v, mask=mask, n_ar=n_ar, return_lse=True)
+            ro, rlse = ops.ref.attention(q.float(), kk.float(), v.float(), 128 ** -0.5, mask, n_ar, True)
+            assert (o.float() - ro).abs().max().item() < 2e-2
+            assert (lse - rlse).abs().max().item() < 1e-3
+    finally:
+        k.attn_set_cta_pair(False)
