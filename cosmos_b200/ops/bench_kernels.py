@@ -2,6 +2,12 @@
 iterations, achieved TFLOP/s (or GB/s) and fraction of the measured peaks.
 
     python -m cosmos_b200.ops.bench_kernels [--what gemm,qkvroute,attn,attnbwd,norm,paged,vae] [--iters 5] [--small]
+
+`--sustained SECONDS` times every GEMM / attention case in a back-to-back loop of that length instead (no L2 flush;
+the inputs are larger than L2) and reports the median SM clock and power sampled with nvidia-smi during the loop:
+on a power-capped part this, not the burst figure, is what a long-running step sees. A/B switches:
+`--gemm-pair 0|1` (CTA-pair tiles), `--attn-pair 0|1`, `--gemm-debug BITS` and COSMOS_ATTN_DEBUG=BITS (timing
+experiments that switch parts of a kernel off; results are wrong with them).
 """
 from __future__ import annotations
 
@@ -40,6 +46,62 @@ def timeit(fn, iters, flush):
     return times[len(times) // 2]
 
 
+class _Smi:
+    """Samples SM clock and power every 100 ms while a loop runs."""
+
+    def __init__(self):
+        import subprocess
+        import threading
+        self.rows = []
+        try:
+            self.p = subprocess.Popen(["nvidia-smi", "--query-gpu=clocks.sm,power.draw", "--format=csv,noheader,nounits",
+                                       "-lms", "100", "-i", str(torch.cuda.current_device())], stdout=subprocess.PIPE,
+                                      text=True)
+            threading.Thread(target=self._read, daemon=True).start()
+        except Exception:  # noqa: BLE001 - no nvidia-smi: no clocks
+            self.p = None
+
+    def _read(self):
+        import time
+        for line in self.p.stdout:
+            self.rows.append((time.time(), [c.strip() for c in line.split(",")]))
+
+    def window(self, t0, t1):
+        import statistics
+        r = [x for t, x in self.rows if t0 + 0.5 <= t <= t1]
+        if not r:
+            return {}
+        return {"sm_mhz": statistics.median(float(x[0]) for x in r), "power_w": statistics.median(float(x[1]) for x in r)}
+
+
+_SMI = None
+
+
+def sustained(fn, secs):
+    """Back-to-back calls for `secs` seconds -> (ms per call, clocks during the loop)."""
+    import time
+    global _SMI
+    if _SMI is None:
+        _SMI = _Smi()
+        time.sleep(1.0)
+    fn()
+    torch.cuda.synchronize()
+    t0 = time.time()
+    n = 0
+    s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    s.record()
+    while time.time() - t0 < secs:
+        for _ in range(20):
+            fn()
+        n += 20
+        torch.cuda.synchronize()
+    e.record()
+    torch.cuda.synchronize()
+    t1 = time.time()
+    time.sleep(0.5)
+    return s.elapsed_time(e) / n, _SMI.window(t0, t1)
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--what", default="gemm,attn,norm")
@@ -47,8 +109,26 @@ def main():
     ap.add_argument("--small", action="store_true", help="sizes for a profiler capture")
     ap.add_argument("--cublas", action="store_true", help="also time torch.matmul / SDPA for comparison")
     ap.add_argument("--attn-shape", default=None, help="sq,skv,hq,hkv for a single attention case")
+    ap.add_argument("--sustained", type=float, default=0.0, help="seconds of back-to-back calls per case (0 = burst timing)")
+    ap.add_argument("--gemm-pair", type=int, default=None, help="0 / 1: single-CTA or CTA-pair GEMM tiles")
+    ap.add_argument("--attn-pair", type=int, default=None, help="0 / 1: single-CTA or CTA-pair attention tiles")
+    ap.add_argument("--gemm-debug", type=int, default=0, help="timing experiment bits of the GEMM (1: all tiles load tile (0,0); 2: no loads)")
     args = ap.parse_args()
     ops.load_extension()
+    if args.gemm_pair is not None:
+        torch.ops.cosmos_b200.gemm_set_cta_pair(bool(args.gemm_pair))
+    if args.attn_pair is not None:
+        torch.ops.cosmos_b200.attn_set_cta_pair(bool(args.attn_pair))
+    if args.gemm_debug:
+        torch.ops.cosmos_b200.gemm_set_debug(args.gemm_debug)
+
+    def measure(fn):
+        """(ms, extra record fields) by the selected method."""
+        if args.sustained > 0:
+            ms, clk = sustained(fn, args.sustained)
+            return ms, {"method": f"sustained {args.sustained:g} s", **clk}
+        return timeit(fn, args.iters, flush), {"method": "burst, L2 flushed"}
+
     tf_peak, bw_peak, src = _peaks()
     dev = "cuda"
     flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
@@ -61,13 +141,14 @@ def main():
             a = torch.randn(m, k, device=dev).bfloat16()
             w = torch.randn(n, k, device=dev).bfloat16()
             epi = ops.EPI_SWIGLU if n == 24576 else ops.EPI_PLAIN
-            ms = timeit(lambda: ops.gemm(a, w, epi=epi), args.iters, flush)
+            ms, how = measure(lambda: ops.gemm(a, w, epi=epi))
             tf = 2.0 * m * n * k / ms / 1e9
             rec = {"kernel": "gemm_bf16_tcgen05", "shape": [m, n, k], "epi": epi, "ms": round(ms, 4),
-                   "tflops": round(tf, 1), f"frac_of_{src}_bf16": round(tf / tf_peak, 3)}
+                   "tflops": round(tf, 1), f"frac_of_{src}_bf16": round(tf / tf_peak, 3), **how}
             if args.cublas:
-                ms2 = timeit(lambda: torch.matmul(a, w.t()), args.iters, flush)
+                ms2, how2 = measure(lambda: torch.matmul(a, w.t()))
                 rec["cublas_ms"] = round(ms2, 4)
+                rec["cublas_clocks"] = {k_: v_ for k_, v_ in how2.items() if k_ != "method"}
             out.append(rec)
             print(json.dumps(rec), flush=True)
     if "qkvroute" in what:
@@ -102,15 +183,15 @@ def main():
             q = torch.randn(1, sq, hq, 128, device=dev).bfloat16()
             k = torch.randn(1, skv, hkv, 128, device=dev).bfloat16()
             v = torch.randn(1, skv, hkv, 128, device=dev).bfloat16()
-            ms = timeit(lambda: ops.attention(q, k, v), args.iters, flush)
+            ms, how = measure(lambda: ops.attention(q, k, v))
             tf = 4.0 * sq * skv * hq * 128 / ms / 1e9
             rec = {"kernel": "flash_attn_fwd_tcgen05", "shape": [sq, skv, hq, hkv], "ms": round(ms, 4),
-                   "tflops": round(tf, 1), f"frac_of_{src}_bf16": round(tf / tf_peak, 3)}
+                   "tflops": round(tf, 1), f"frac_of_{src}_bf16": round(tf / tf_peak, 3), **how}
             if args.cublas:
                 qt, kt, vt = (t.permute(0, 2, 1, 3) for t in (q, k, v))
-                ms2 = timeit(lambda: torch.nn.functional.scaled_dot_product_attention(qt, kt, vt, enable_gqa=True),
-                             args.iters, flush)
+                ms2, how2 = measure(lambda: torch.nn.functional.scaled_dot_product_attention(qt, kt, vt, enable_gqa=True))
                 rec["sdpa_ms"] = round(ms2, 4)
+                rec["sdpa_clocks"] = {k_: v_ for k_, v_ in how2.items() if k_ != "method"}
             out.append(rec)
             print(json.dumps(rec), flush=True)
     if "norm" in what:

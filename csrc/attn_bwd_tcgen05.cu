@@ -215,48 +215,60 @@ flash_attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid
       issued = it + 1;
     }
     if (!ok) bwd_drain(sm, fixed_issued, issued);
-  } else if (warp == 1 && lane == 0) {
-    // ---------------- MMA issuer
+  } else if (warp == 1) {
+    // ---------------- MMA issuer: the whole warp walks the loop (barrier phases and descriptors are warp-uniform
+    // values), one elected lane issues the tcgen05 instructions
+    const bool issuer = elect_one();
+    auto wait_all = [&](uint32_t bar, uint32_t phase) {
+      return __all_sync(0xffffffffu, mbar_wait(bar, phase, abort_flag, p.status, ST_TIMEOUT_MMA)) != 0;
+    };
     constexpr uint32_t idesc_ss = make_idesc_bf16(BT, BT, 0, 0);
     constexpr uint32_t idesc_ts = make_idesc_bf16(BT, 128, 0, 1);
     const uint64_t k_desc = make_smem_desc_sw128(sm.fixed(0), 16, 1024);
     const uint64_t v_desc = make_smem_desc_sw128(sm.fixed(1), 16, 1024);
-    bool ok = n_it == 0 || mbar_wait(sm.bar + 8u * BB_FIXED, 0, abort_flag, p.status, ST_TIMEOUT_MMA);
+    bool ok = n_it == 0 || wait_all(sm.bar + 8u * BB_FIXED, 0);
     for (int it = 0; it < n_it && ok; ++it) {
       const int s = it % BWD_NST;
-      ok = mbar_wait(sm.bar + 8u * (BB_FULL + s), (it / BWD_NST) & 1, abort_flag, p.status, ST_TIMEOUT_MMA);
+      ok = wait_all(sm.bar + 8u * (BB_FULL + s), (it / BWD_NST) & 1);
       if (!ok) break;
       tc_fence_after();
       const uint64_t q_k = make_smem_desc_sw128(sm.stream(s, 0), 16, 1024);
       const uint64_t do_k = make_smem_desc_sw128(sm.stream(s, 1), 16, 1024);
       const uint64_t q_mn = make_smem_desc_sw128(sm.stream(s, 0), BHALF_BYTES, 1024);
       const uint64_t do_mn = make_smem_desc_sw128(sm.stream(s, 1), BHALF_BYTES, 1024);
+      if (issuer) {
 #pragma unroll
-      for (int kk = 0; kk < 8; ++kk) {
-        const uint32_t off = (kk >> 2) * (BHALF_BYTES >> 4) + 2 * (kk & 3);
-        mma_ss(T_ST, k_desc + off, q_k + off, idesc_ss, kk > 0 ? 1u : 0u);
-      }
+        for (int kk = 0; kk < 8; ++kk) {
+          const uint32_t off = (kk >> 2) * (BHALF_BYTES >> 4) + 2 * (kk & 3);
+          mma_ss(T_ST, k_desc + off, q_k + off, idesc_ss, kk > 0 ? 1u : 0u);
+        }
 #pragma unroll
-      for (int kk = 0; kk < 8; ++kk) {
-        const uint32_t off = (kk >> 2) * (BHALF_BYTES >> 4) + 2 * (kk & 3);
-        mma_ss(T_DPT, v_desc + off, do_k + off, idesc_ss, kk > 0 ? 1u : 0u);
+        for (int kk = 0; kk < 8; ++kk) {
+          const uint32_t off = (kk >> 2) * (BHALF_BYTES >> 4) + 2 * (kk & 3);
+          mma_ss(T_DPT, v_desc + off, do_k + off, idesc_ss, kk > 0 ? 1u : 0u);
+        }
+        tc_commit(sm.bar + 8u * BB_S);
       }
-      tc_commit(sm.bar + 8u * BB_S);
-      ok = mbar_wait(sm.bar + 8u * BB_P, it & 1, abort_flag, p.status, ST_TIMEOUT_MMA);
+      __syncwarp();
+      ok = wait_all(sm.bar + 8u * BB_P, it & 1);
       if (!ok) break;
       tc_fence_after();
-      // bf16 P^T / dS^T of query columns [64 w, 64 w + 64) sit at 32-bit columns [64 w, 64 w + 32)
+      if (issuer) {
+        // bf16 P^T / dS^T of query columns [64 w, 64 w + 64) sit at 32-bit columns [64 w, 64 w + 32)
 #pragma unroll
-      for (int kk = 0; kk < 8; ++kk)
-        mma_ts(T_DV, T_ST + (kk >> 2) * 64 + (kk & 3) * 8, do_mn + uint64_t(kk * (2048 >> 4)), idesc_ts,
-               (it > 0 || kk > 0) ? 1u : 0u);
+        for (int kk = 0; kk < 8; ++kk)
+          mma_ts(T_DV, T_ST + (kk >> 2) * 64 + (kk & 3) * 8, do_mn + uint64_t(kk * (2048 >> 4)), idesc_ts,
+                 (it > 0 || kk > 0) ? 1u : 0u);
 #pragma unroll
-      for (int kk = 0; kk < 8; ++kk)
-        mma_ts(T_DK, T_DPT + (kk >> 2) * 64 + (kk & 3) * 8, q_mn + uint64_t(kk * (2048 >> 4)), idesc_ts,
-               (it > 0 || kk > 0) ? 1u : 0u);
-      tc_commit(sm.bar + 8u * (BB_EMPTY + s));
+        for (int kk = 0; kk < 8; ++kk)
+          mma_ts(T_DK, T_DPT + (kk >> 2) * 64 + (kk & 3) * 8, q_mn + uint64_t(kk * (2048 >> 4)), idesc_ts,
+                 (it > 0 || kk > 0) ? 1u : 0u);
+        tc_commit(sm.bar + 8u * (BB_EMPTY + s));
+      }
+      __syncwarp();
     }
-    if (ok && n_it > 0) tc_commit(sm.bar + 8u * BB_DONE);
+    if (ok && n_it > 0 && issuer) tc_commit(sm.bar + 8u * BB_DONE);
+    __syncwarp();
   } else if (warp >= 4) {
     // ---------------- element-wise math: this thread owns K/V row kv0 + r (TMEM lane r)
     const int quad = warp & 3;
@@ -408,42 +420,53 @@ flash_attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_c
       issued = j + 1;
     }
     if (!ok) bwd_drain(sm, true, issued);
-  } else if (warp == 1 && lane == 0) {
-    // ---------------- MMA issuer
+  } else if (warp == 1) {
+    // ---------------- MMA issuer (whole warp walks the loop, one elected lane issues)
+    const bool issuer = elect_one();
+    auto wait_all = [&](uint32_t bar, uint32_t phase) {
+      return __all_sync(0xffffffffu, mbar_wait(bar, phase, abort_flag, p.status, ST_TIMEOUT_MMA)) != 0;
+    };
     constexpr uint32_t idesc_ss = make_idesc_bf16(BT, BT, 0, 0);
     constexpr uint32_t idesc_ts = make_idesc_bf16(BT, 128, 0, 1);
     const uint64_t q_desc = make_smem_desc_sw128(sm.fixed(0), 16, 1024);
     const uint64_t do_desc = make_smem_desc_sw128(sm.fixed(1), 16, 1024);
-    bool ok = mbar_wait(sm.bar + 8u * BB_FIXED, 0, abort_flag, p.status, ST_TIMEOUT_MMA);
+    bool ok = wait_all(sm.bar + 8u * BB_FIXED, 0);
     for (int j = 0; j < n_blocks && ok; ++j) {
       const int s = j % BWD_NST;
-      ok = mbar_wait(sm.bar + 8u * (BB_FULL + s), (j / BWD_NST) & 1, abort_flag, p.status, ST_TIMEOUT_MMA);
+      ok = wait_all(sm.bar + 8u * (BB_FULL + s), (j / BWD_NST) & 1);
       if (!ok) break;
       tc_fence_after();
       const uint64_t k_k = make_smem_desc_sw128(sm.stream(s, 0), 16, 1024);
       const uint64_t v_k = make_smem_desc_sw128(sm.stream(s, 1), 16, 1024);
       const uint64_t k_mn = make_smem_desc_sw128(sm.stream(s, 0), BHALF_BYTES, 1024);
+      if (issuer) {
 #pragma unroll
-      for (int kk = 0; kk < 8; ++kk) {
-        const uint32_t off = (kk >> 2) * (BHALF_BYTES >> 4) + 2 * (kk & 3);
-        mma_ss(T_S, q_desc + off, k_k + off, idesc_ss, kk > 0 ? 1u : 0u);
-      }
+        for (int kk = 0; kk < 8; ++kk) {
+          const uint32_t off = (kk >> 2) * (BHALF_BYTES >> 4) + 2 * (kk & 3);
+          mma_ss(T_S, q_desc + off, k_k + off, idesc_ss, kk > 0 ? 1u : 0u);
+        }
 #pragma unroll
-      for (int kk = 0; kk < 8; ++kk) {
-        const uint32_t off = (kk >> 2) * (BHALF_BYTES >> 4) + 2 * (kk & 3);
-        mma_ss(T_DP, do_desc + off, v_k + off, idesc_ss, kk > 0 ? 1u : 0u);
+        for (int kk = 0; kk < 8; ++kk) {
+          const uint32_t off = (kk >> 2) * (BHALF_BYTES >> 4) + 2 * (kk & 3);
+          mma_ss(T_DP, do_desc + off, v_k + off, idesc_ss, kk > 0 ? 1u : 0u);
+        }
+        tc_commit(sm.bar + 8u * BB_S);
       }
-      tc_commit(sm.bar + 8u * BB_S);
-      ok = mbar_wait(sm.bar + 8u * BB_P, j & 1, abort_flag, p.status, ST_TIMEOUT_MMA);
+      __syncwarp();
+      ok = wait_all(sm.bar + 8u * BB_P, j & 1);
       if (!ok) break;
       tc_fence_after();
+      if (issuer) {
 #pragma unroll
-      for (int kk = 0; kk < 8; ++kk)
-        mma_ts(T_DQ, T_S + (kk >> 2) * 64 + (kk & 3) * 8, k_mn + uint64_t(kk * (2048 >> 4)), idesc_ts,
-               (j > 0 || kk > 0) ? 1u : 0u);
-      tc_commit(sm.bar + 8u * (BB_EMPTY + s));
+        for (int kk = 0; kk < 8; ++kk)
+          mma_ts(T_DQ, T_S + (kk >> 2) * 64 + (kk & 3) * 8, k_mn + uint64_t(kk * (2048 >> 4)), idesc_ts,
+                 (j > 0 || kk > 0) ? 1u : 0u);
+        tc_commit(sm.bar + 8u * (BB_EMPTY + s));
+      }
+      __syncwarp();
     }
-    if (ok) tc_commit(sm.bar + 8u * BB_DONE);
+    if (ok && issuer) tc_commit(sm.bar + 8u * BB_DONE);
+    __syncwarp();
   } else if (warp >= 4) {
     // ---------------- element-wise math: this thread owns query row q0 + r (TMEM lane r)
     const int quad = warp & 3;

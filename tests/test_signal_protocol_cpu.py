@@ -120,3 +120,53 @@ def test_device_kept_epochs_stay_in_step_across_ranks():
         for r in range(world):
             assert (results[r][c] == want).all(), (r, c)
     assert all(cnt[16] == 2 * calls for cnt in counters)
+
+
+def test_alternating_buffers_need_only_a_leading_barrier_and_a_new_user_continues_the_epochs():
+    """Protocol of the fused all-reduce + residual + RMS-norm kernel (`allreduce_norm_kernel`): every call writes this
+    rank's values into one of TWO buffers (alternating), meets the peers on a barrier whose epoch comes from a counter
+    that belongs to the group, then reads all ranks' buffers; there is no trailing barrier. A rank that has passed the
+    barrier of call c knows that every peer has finished reading the buffer of call c - 1, which is the one call c + 1
+    overwrites. One counted barrier opens every step (graph replay) and resets the alternation. A second "decoder" that
+    starts later on the same group keeps using the group's counters, so its first barrier is not satisfied by stale pads."""
+    world, steps, calls = 4, 12, 7          # an odd number of calls per step: the step-opening barrier covers the wrap
+    p = Pads(world)
+    counters = [np.zeros(64, dtype=np.int64) for _ in range(world)]      # owned by the group, not by a decoder
+    bufs = [[np.zeros(8), np.zeros(8)] for _ in range(world)]
+    rnd = [random.Random(10 + r) for r in range(world)]
+    results = [[] for _ in range(world)]
+
+    def counted_barrier(r, slot):
+        e = counters[r][slot] + 1
+        ok = barrier(p, r, slot, e)
+        counters[r][slot] = e                 # advanced even after a timeout, so ranks stay in step
+        return ok
+
+    def decoder_step(r, tag):
+        assert counted_barrier(r, 15)         # begin_step: peers are done with the previous step's buffers
+        parity = 0
+        for c in range(calls):
+            parity ^= 1
+            if rnd[r].random() < 0.3:
+                time.sleep(rnd[r].random() * 5e-4)
+            bufs[r][parity][:] = (r + 1) * (tag * 100 + c + 1)           # split-K partials reduced into the own buffer
+            assert counted_barrier(r, 16)
+            results[r].append(sum(bufs[q][parity] for q in range(world)).copy())   # no barrier after the reads
+
+    def body(r):
+        for s in range(steps):
+            decoder_step(r, s)
+        # a second decoder on the same ranks (engine rebuilt): same counters, epochs continue
+        for s in range(steps, steps + 3):
+            decoder_step(r, s)
+
+    _run(world, body)
+    k = 0
+    for s in range(steps + 3):
+        for c in range(calls):
+            want = sum((q + 1) * (s * 100 + c + 1) for q in range(world))
+            for r in range(world):
+                assert (results[r][k] == want).all(), (r, s, c, results[r][k][0], want)
+            k += 1
+    assert all(cnt[16] == (steps + 3) * calls and cnt[15] == steps + 3 for cnt in counters)
+    assert all(s == ST_OK for s in p.status)
