@@ -240,6 +240,8 @@ class FSDP:
         gradient norm before clipping."""
         self.step_count += 1
         self._last_key = None
+        for u in self.units.values():
+            u._prefetched = None   # a gather that nobody consumed would hold the parameters from before this update
         b1, b2 = self.betas
         ws = self.ws
         # replicated parameters: all-reduce (mean) their gradients over the shard group and the replicas
