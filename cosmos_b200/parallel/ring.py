@@ -5,14 +5,23 @@ the head counts do not divide, e.g. cp > 8 KV heads, or when heads are already s
 
 NVSwitch gives every pair of GPUs the same bandwidth, so "ring" is only a schedule: at hop i
 rank r reads the shard of rank (r + i) mod cp. On CUDA the ranks' K/V shards live in symmetric
-memory and ONE flash-attention launch per layer walks them: the kernel gets one tensor map per
-source (the prompt prefix, this rank's shard, then the peers' shards in rank-staggered order) and its
-TMA producer pulls the peers' K/V tiles over NVLink straight into shared memory (plain loads, no
-multicast), while the running max, the row sums and the output accumulator stay in registers and
-tensor memory across hops. No partial outputs, no log-sum-exp merge, no staging copy. The earlier
-schedule (a copy kernel on a side stream per hop + one attention launch per hop + an fp32 merge)
-is kept as `COSMOS_RING_STAGED=1` for comparison. On CPU (gloo) the shards are exchanged with
-all_gather and visited in the same order, which is the oracle for the schedule.
+memory and ONE flash-attention launch per layer walks all of them: the kernel gets one tensor map per
+source (the prompt prefix, this rank's shard, then the peers' shards in rank-staggered order) and keeps
+the running max, the row sums and the output accumulator in registers and tensor memory across sources:
+no partial outputs, no log-sum-exp merge, no concatenation copy. Where the peers' K/V come from is a
+choice (`COSMOS_RING_MODE`):
+  * `gather` (default): a pull kernel first copies every peer's shard into local staging buffers (each
+    byte crosses NVLink once; rank-staggered, so no peer is read by everybody at once), then the attention
+    kernel reads local memory only. Every (query block, head) CTA re-reads its K/V head, which the local
+    L2 serves; data read straight from a peer is not cached locally.
+  * `remote`: the attention kernel's TMA loads pull the peers' tiles over NVLink straight into shared
+    memory. One launch and no staging, but every CTA's tile then crosses NVLink: measured 5 x slower than
+    `gather` at 111,600 tokens on 4 GPUs (20.1 s against 3.8 s per guided step), so it is meant for short
+    query shards only.
+  * `staged`: the earlier schedule (a copy kernel on a side stream per hop + one attention launch per hop +
+    an fp32 merge of the partial outputs).
+On CPU (gloo) the shards are exchanged with all_gather and visited in the same order, which is the oracle
+for the schedule.
 """
 from __future__ import annotations
 
@@ -88,10 +97,10 @@ class RingAttn(AttnContext):
             self._ws[key] = (k_sym, v_sym, [ptr1(p) for p in k_ptrs], [ptr1(p) for p in v_ptrs], stage, nbytes)
         return self._ws[key]
 
-    def _attend_in_kernel(self, q, k, v):
-        """One attention launch over the prefix, the own shard and the peers' shards (K/V tiles of the peers are read
-        from their symmetric buffers by the kernel's TMA loads)."""
-        k_sym, v_sym, k_ptrs, v_ptrs, _, _ = self._buffers(k)
+    def _attend_in_kernel(self, q, k, v, remote: bool):
+        """One attention launch over the prefix, the own shard and the peers' shards. `remote`: the kernel's TMA loads
+        read the peers' symmetric buffers directly; otherwise a pull kernel copies them into local staging first."""
+        k_sym, v_sym, k_ptrs, v_ptrs, _, nbytes = self._buffers(k)
         key = ("addr", tuple(k.shape))
         if key not in self._ws:
             buf = self.sg._bufs[f"ring_kv_{tuple(k.shape)}"]
@@ -102,8 +111,20 @@ class RingAttn(AttnContext):
         v_sym.copy_(v)
         self.sg.barrier(slot=5)  # every rank's shard is published
         order = [(self.rank + i) % self.cp for i in range(self.cp)]
-        kp = [ka[r] for r in order]
-        vp = [va[r] for r in order]
+        if remote:
+            kp = [ka[r] for r in order]
+            vp = [va[r] for r in order]
+        else:
+            skey = ("stage", tuple(k.shape))
+            if skey not in self._ws:
+                self._ws[skey] = [(torch.empty_like(k), torch.empty_like(k)) for _ in range(self.cp - 1)]
+            stage = self._ws[skey]
+            kp, vp = [k_sym.data_ptr()], [v_sym.data_ptr()]
+            for i, r in enumerate(order[1:]):
+                torch.ops.cosmos_b200.allgather_pull(k_ptrs[r], 1, stage[i][0], nbytes)
+                torch.ops.cosmos_b200.allgather_pull(v_ptrs[r], 1, stage[i][1], nbytes)
+                kp.append(stage[i][0].data_ptr())
+                vp.append(stage[i][1].data_ptr())
         lens = [k.shape[1]] * self.cp
         if self._prefix is not None:
             pk, pv = self._prefix[0].contiguous(), self._prefix[1].contiguous()
@@ -115,8 +136,9 @@ class RingAttn(AttnContext):
 
     def _attend_fused(self, q, k, v, mask):
         import os
-        if os.environ.get("COSMOS_RING_STAGED") != "1" and self.cp + 1 <= 9:
-            return self._attend_in_kernel(q, k, v)
+        mode = os.environ.get("COSMOS_RING_MODE", "staged" if os.environ.get("COSMOS_RING_STAGED") == "1" else "gather")
+        if mode in ("gather", "remote") and self.cp + 1 <= 9:
+            return self._attend_in_kernel(q, k, v, remote=(mode == "remote"))
         k_sym, v_sym, k_ptrs, v_ptrs, stage, nbytes = self._buffers(k)
         k_sym.copy_(k)
         v_sym.copy_(v)

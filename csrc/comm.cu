@@ -162,13 +162,27 @@ rs_adamw_kernel(const long long* grads, int world, long long shard_off, long lon
 
 // All-gather by pull: dst[r * n_vec + i] = peer_r[i]; used to materialise FSDP parameters
 // from the peers' shards (one kernel, all peers in flight at once over NVSwitch).
+// Each thread keeps four 16-byte peer loads in flight per trip (NVLink latency is microseconds, so the copy rate
+// is bytes in flight / latency).
 __global__ void __launch_bounds__(256)
 allgather_pull_kernel(const long long* srcs, int world, uint4* __restrict__ dst, long long n_vec) {
   const long long total = n_vec * world;
-  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total;
-       i += (long long)gridDim.x * blockDim.x) {
-    const int r = (int)(i / n_vec);
-    dst[i] = reinterpret_cast<const uint4*>(srcs[r])[i - (long long)r * n_vec];
+  const long long stride = (long long)gridDim.x * blockDim.x;
+  for (long long i0 = (long long)blockIdx.x * blockDim.x + threadIdx.x; i0 < total; i0 += 4 * stride) {
+    uint4 v[4];
+#pragma unroll
+    for (int u = 0; u < 4; ++u) {
+      const long long i = i0 + u * stride;
+      if (i < total) {
+        const int r = (int)(i / n_vec);
+        v[u] = reinterpret_cast<const uint4*>(srcs[r])[i - (long long)r * n_vec];
+      }
+    }
+#pragma unroll
+    for (int u = 0; u < 4; ++u) {
+      const long long i = i0 + u * stride;
+      if (i < total) dst[i] = v[u];
+    }
   }
 }
 
@@ -450,7 +464,7 @@ void allgather_pull(const long long* srcs_dev, int world, void* dst, long long b
   if (bytes_per_rank % 16 != 0) throw std::runtime_error("allgather_pull: shard bytes must be % 16");
   const long long n_vec = bytes_per_rank / 16;
   if (n_vec == 0) return;
-  const int blocks = (int)std::min<long long>((n_vec * world + 255) / 256, 148 * 16);
+  const int blocks = (int)std::min<long long>((n_vec * world + 1023) / 1024, 148 * 8);
   cb::allgather_pull_kernel<<<blocks, 256, 0, s>>>(srcs_dev, world, (uint4*)dst, n_vec);
 }
 
