@@ -154,7 +154,11 @@ def check_status(reset: bool = True) -> None:
         if reset:
             w.zero_()
         what = STATUS_MESSAGES.get(code & 0xFF, "?")
-        if code >> 8:
+        if 1 <= (code & 0xFF) <= 4 and code >> 8:
+            d = code >> 8   # the wait that gave up (csrc/common.cuh, mbar_wait)
+            what += (f" (barrier slot {d & 0x7F}, parity {(d >> 7) & 1}, grid size {(d >> 8) & 0xFF} mod 256, "
+                     f"{2 * ((d >> 16) & 0x7F)} KB of dynamic shared memory)")
+        elif code >> 8:
             what += f" at {STATUS_SITES.get(code >> 8, f'site {code >> 8}')}"
         raise RuntimeError(f"cosmos_b200 kernel reported status {code}: {what}")
 

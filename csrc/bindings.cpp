@@ -917,6 +917,7 @@ void gemm_set_grid_limit(int64_t max_ctas) { cosmos::gemm_set_grid_limit((int)ma
 // A/B switches for timing and tests: CTA-pair GEMM tiles on/off, attention forward variant bits.
 void gemm_set_cta_pair(bool on) { cosmos::gemm_set_cta_pair(on); }
 void gemm_set_debug(int64_t bits) { cosmos::gemm_set_debug((int)bits); }
+void set_pdl(bool on) { cosmos::set_pdl(on); }
 void attn_set_cta_pair(bool on) { cosmos::attn_set_cta_pair(on); }
 void attn_set_exp_emulation(int64_t v) { attn_exp_emu() = (int)v; }
 void attn_set_debug(int64_t v) { attn_debug() = (int)v; }
@@ -1133,6 +1134,7 @@ TORCH_LIBRARY(cosmos_b200, m) {
   m.def("gemm_set_grid_limit", &gemm_set_grid_limit);
   m.def("gemm_set_cta_pair", &gemm_set_cta_pair);
   m.def("gemm_set_debug", &gemm_set_debug);
+  m.def("set_pdl", &set_pdl);
   m.def("attn_set_cta_pair", &attn_set_cta_pair);
   m.def("attn_set_exp_emulation", &attn_set_exp_emulation);
   m.def("attn_set_debug", &attn_set_debug);

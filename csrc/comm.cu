@@ -11,6 +11,7 @@
 // Peers never run on the same GPU as the waiting kernel (one process per GPU).
 #include "common.cuh"
 #include "kernels.h"
+#include "launch.cuh"
 
 namespace cb {
 
@@ -303,6 +304,8 @@ allreduce_norm_kernel(const long long* bufs, const bf16* mc, bf16* own, const lo
   const int tid = threadIdx.x;
   const int nvec = N >> 3;
   constexpr int MAXJ = 4;  // 256 threads x 4 vectors x 8 = 8192 columns
+  pdl_launch_dependents();
+  pdl_wait();
   if (partial) {
     for (int m = blockIdx.x; m < M; m += gridDim.x) {
       for (int vi = tid; vi < nvec; vi += 256) {
@@ -502,13 +505,13 @@ void allreduce_norm(const long long* bufs_dev, const void* mc, void* own, const 
   const int blocks = allreduce_norm_blocks(M);
   if (slot + blocks > 64) throw std::runtime_error("allreduce_norm: signal slots out of range");
   if (mc)
-    cb::allreduce_norm_kernel<true><<<blocks, 256, 0, s>>>(bufs_dev, (const bf16*)mc, (bf16*)own, pads_dev, rank, world,
-                                                           slot, counters, partial, k_splits, M, N, (const bf16*)R,
-                                                           (const bf16*)gamma, eps, (bf16*)X, (bf16*)H, status);
+    launch_pdl(cb::allreduce_norm_kernel<true>, dim3(blocks), dim3(256), 0, s, bufs_dev, (const bf16*)mc, (bf16*)own,
+               pads_dev, rank, world, slot, counters, partial, k_splits, M, N, (const bf16*)R, (const bf16*)gamma, eps,
+               (bf16*)X, (bf16*)H, status);
   else
-    cb::allreduce_norm_kernel<false><<<blocks, 256, 0, s>>>(bufs_dev, nullptr, (bf16*)own, pads_dev, rank, world, slot,
-                                                            counters, partial, k_splits, M, N, (const bf16*)R,
-                                                            (const bf16*)gamma, eps, (bf16*)X, (bf16*)H, status);
+    launch_pdl(cb::allreduce_norm_kernel<false>, dim3(blocks), dim3(256), 0, s, bufs_dev, (const bf16*)nullptr,
+               (bf16*)own, pads_dev, rank, world, slot, counters, partial, k_splits, M, N, (const bf16*)R,
+               (const bf16*)gamma, eps, (bf16*)X, (bf16*)H, status);
 }
 
 void sum_partials_gated_residual(const void* part, int n_part, long long rows, int d, const void* R, const void* gate,

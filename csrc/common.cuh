@@ -133,7 +133,16 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
       if (*abort_flag) return false;
       if (clock64() - t0 > COSMOS_WAIT_LIMIT_CYCLES) {
         *abort_flag = 1;
-        if (status) atomicCAS(status, 0, tag);
+        if (status) {
+          // which wait gave up: barrier slot (its offset in the 1 KB-aligned barrier block / 8), the parity waited
+          // for, the low byte of the grid size and the kernel's dynamic shared memory in 2 KB units (these two tell
+          // the kernels and their launches apart)
+          uint32_t dyn_smem;
+          asm volatile("mov.u32 %0, %%dynamic_smem_size;" : "=r"(dyn_smem));
+          const uint32_t detail = (((bar & 1023u) >> 3) & 0x7fu) | ((parity & 1u) << 7) | ((gridDim.x & 0xffu) << 8) |
+                                  (((dyn_smem >> 11) & 0x7fu) << 16);
+          atomicCAS(status, 0, tag | int(detail << 8));
+        }
         return false;
       }
     }
@@ -198,6 +207,15 @@ __device__ __forceinline__ void tmem_relinquish() {
 __device__ __forceinline__ void tmem_dealloc(uint32_t addr, uint32_t ncols) {
   asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(addr), "r"(ncols)
                : "memory");
+}
+// Programmatic dependent launch. A kernel launched with the programmatic-serialization attribute may start while
+// its predecessor in the stream still runs: everything before `pdl_wait()` (barrier set-up, TMEM allocation,
+// loads of data that no kernel of the stream writes, such as weights) overlaps the predecessor's tail; after
+// `pdl_wait()` the predecessor has completed and its writes are visible. `pdl_launch_dependents()` lets the
+// successor start that early part. Without the launch attribute both instructions do nothing.
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void pdl_launch_dependents() {
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
 }
 __device__ __forceinline__ void tc_fence_before() {
   asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");

@@ -388,6 +388,10 @@ __global__ void l2_flush_kernel(uint4* buf, size_t n) {
 
 namespace cosmos {
 
+static bool g_pdl = false;
+void set_pdl(bool on) { g_pdl = on; }
+bool pdl_on() { return g_pdl; }
+
 static void check_d(int d, const char* who) {
   if (d % 8 != 0 || d <= 0)
     throw std::runtime_error(std::string(who) + ": feature size must be a positive multiple of 8");

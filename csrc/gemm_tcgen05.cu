@@ -20,6 +20,7 @@
 // through the common tail (TMEM is freed).
 #include "common.cuh"
 #include "kernels.h"
+#include "launch.cuh"
 #include <cstdlib>
 
 namespace cb {
@@ -163,12 +164,39 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
   if constexpr (NC == 2) cluster_sync_all();  // the peer's barriers are initialised before anything signals them
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot_ptr;
+  // The set-up above overlapped the previous kernel's tail when this one was launched as its programmatic
+  // dependent; the successor may begin its own set-up now. Every thread but the producer waits here for the
+  // previous kernel's results; the producer first starts the weight tiles of its first stages (below).
+  pdl_launch_dependents();
+  const bool is_producer = warp == 0 && lane == 0;
+  if (!is_producer) pdl_wait();
 
   if (warp == 0) {
     if (lane == 0) {
       // ---------------- TMA producer
       int it = 0;
       bool ok = true;
+      // Weight prefetch ahead of the dependency wait (single-CTA tiles, B in its [N, K] layout): the B halves of
+      // the first tile's first stages are requested before `pdl_wait()`, their A halves after it. The full
+      // barrier of a stage completes only when both have landed.
+      int prefetched = 0;
+      if (NC == 1 && EPI != EPI_CONV && first_tile < total_tiles && first_tile < g.tiles0 && !g.p[0].b_mn &&
+          !g.p[0].debug) {
+        const GemmParams& p = g.p[0];
+        const int k_blocks = (p.K + BK - 1) / BK;
+        const int ks = first_tile % p.k_splits;
+        const int kb0 = ks * k_blocks / p.k_splits, kb1 = (ks + 1) * k_blocks / p.k_splits;
+        int tm, tn;
+        tile_coords(first_tile / p.k_splits, p.m_tiles, p.n_tiles, tm, tn);
+        const int n0 = (EPI == EPI_SWIGLU) ? tn * 128 : tn * BN;
+        for (int kb = kb0; kb < kb1 && prefetched < STAGES; ++kb, ++prefetched) {
+          const uint32_t sa = smem_base + prefetched * STAGE_BYTES;
+          mbar_arrive_expect_tx(full_bar(prefetched), STAGE_BYTES);
+          tma_load_2d(sa + A_BYTES, &tmB, full_bar(prefetched), kb * BK, n0);
+          tma_load_2d(sa + A_BYTES + B_BYTES / 2, &tmB, full_bar(prefetched), kb * BK, n0 + p.b_row1);
+        }
+      }
+      pdl_wait();
       for (int t = first_tile; t < total_tiles && ok; t += tile_step) {
         const int second = t >= g.tiles0;
         const GemmParams& p = g.p[second];
@@ -186,11 +214,21 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
         for (int kb = kb0; kb < kb1; ++kb, ++it) {
           const int s = it % STAGES;
           const uint32_t ph = (it / STAGES) & 1;
+          const uint32_t sa = smem_base + s * STAGE_BYTES;
+          if (it < prefetched) {
+            // stage already armed and its B half in flight: only the A half is left
+            if (p.a_mn) {
+              tma_load_2d(sa, mA, full_bar(s), m0, kb * BK);
+              tma_load_2d(sa + A_BYTES / 2, mA, full_bar(s), m0 + 64, kb * BK);
+            } else {
+              tma_load_2d(sa, mA, full_bar(s), kb * BK, m0);
+            }
+            continue;
+          }
           if (!mbar_wait(empty_bar(s), ph ^ 1, abort_flag, p.status, ST_TIMEOUT_TMA)) {
             ok = false;
             break;
           }
-          const uint32_t sa = smem_base + s * STAGE_BYTES;
           if constexpr (NC == 2) {
             // both CTAs' bytes are counted on the leader's barrier, which expects the pair's total
             const uint32_t fb = mapa(full_bar(s), 0);
@@ -670,6 +708,8 @@ splitk_reduce_rmsnorm_kernel(const float* __restrict__ partial, int k_splits, in
                              long long ldr, const bf16* __restrict__ gamma, float eps, bf16* __restrict__ X,
                              bf16* __restrict__ H, long long ldc) {
   __shared__ float red[8];
+  pdl_launch_dependents();
+  pdl_wait();
   const int m = blockIdx.x, tid = threadIdx.x;
   const int nvec = N >> 2;
   constexpr int MAXJ = 8;  // N <= 8192
@@ -725,6 +765,8 @@ __global__ void __launch_bounds__(256)
 splitk_reduce_kernel(const float* __restrict__ partial, int k_splits, int M, int N, int epi, bf16* __restrict__ C,
                      long long ldc, const bf16* __restrict__ bias, const bf16* __restrict__ R, long long ldr,
                      const bf16* __restrict__ gate, int rows_per_batch) {
+  pdl_launch_dependents();
+  pdl_wait();
   const int n_out = epi == EPI_SWIGLU ? N / 2 : N;
   const int vec_per_row = n_out / 4;
   const long long total = (long long)M * vec_per_row;
@@ -825,7 +867,7 @@ CUtensorMap make_tmap_bf16(const void* base, int rank, const uint64_t* dims,
   return m;
 }
 const char* status_str(int st) {
-  switch (st) {
+  switch (st & 0xff) {  // the upper bits say which wait gave up
     case cb::ST_OK: return "ok";
     case cb::ST_TIMEOUT_TMA: return "timeout: TMA producer waiting for a free stage";
     case cb::ST_TIMEOUT_MMA: return "timeout: MMA issuer waiting for data";
@@ -912,10 +954,12 @@ static void launch(const CUtensorMap* maps, const cb::GemmGroup& g, int units, i
   cfg.blockDim = dim3(cb::GEMM_THREADS, 1, 1);
   cfg.dynamicSmemBytes = cb::GemmCfg<NC>::SMEM;
   cfg.stream = stream;
-  cudaLaunchAttribute at[1];
+  cudaLaunchAttribute at[2];
   at[0].id = cudaLaunchAttributeClusterDimension;
   at[0].val.clusterDim.x = NC; at[0].val.clusterDim.y = 1; at[0].val.clusterDim.z = 1;
-  cfg.attrs = at; cfg.numAttrs = 1;
+  at[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  at[1].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = at; cfg.numAttrs = (NC == 1 && pdl_on()) ? 2 : 1;
   cudaLaunchKernelEx(&cfg, cb::gemm_bf16_kernel<EPI, NC>, maps[0], maps[1], maps[2], maps[3], g);
 }
 
@@ -1091,7 +1135,7 @@ void gemm_bf16(const GemmArgs& a, cudaStream_t stream) {
   if (a.norm_out) {
     if (a.epi != EPI_PLAIN || a.N > 8192 || a.N % 4 != 0 || a.ldc % 4 != 0 || (a.R && a.ldr % 4 != 0))
       throw std::runtime_error("gemm_bf16: the fused reduce + RMS-norm pass needs a plain epilogue and N <= 8192");
-    cb::splitk_reduce_rmsnorm_kernel<<<a.M, 256, 0, stream>>>(
+    launch_pdl(cb::splitk_reduce_rmsnorm_kernel, dim3(a.M), dim3(256), 0, stream,
         a.partial, ks, a.M, a.N, reinterpret_cast<const bf16*>(a.R), a.ldr, reinterpret_cast<const bf16*>(a.norm_gamma),
         a.norm_eps, reinterpret_cast<bf16*>(a.C), reinterpret_cast<bf16*>(a.norm_out), a.ldc);
     return;
@@ -1099,7 +1143,7 @@ void gemm_bf16(const GemmArgs& a, cudaStream_t stream) {
   const int n_out = a.epi == EPI_SWIGLU ? a.N / 2 : a.N;
   const long long vecs = (long long)a.M * (n_out / 4);
   const int blocks = (int)std::min<long long>((vecs + 255) / 256, 148 * 8);
-  cb::splitk_reduce_kernel<<<blocks, 256, 0, stream>>>(
+  launch_pdl(cb::splitk_reduce_kernel, dim3(blocks), dim3(256), 0, stream,
       a.partial, ks, a.M, a.N, a.epi, reinterpret_cast<bf16*>(a.C), a.ldc,
       reinterpret_cast<const bf16*>(a.bias), reinterpret_cast<const bf16*>(a.R), a.ldr,
       reinterpret_cast<const bf16*>(a.gate), a.rows_per_batch > 0 ? a.rows_per_batch : (a.M > 0 ? a.M : 1));

@@ -24,6 +24,14 @@ enum AttnMask : int {
 
 namespace cosmos {
 
+// Programmatic dependent launch for the decode-step kernels (GEMM, split-K reductions, QKV post-processing, paged
+// attention and its merge, all-reduce + norm): while on, those kernels are launched so that their set-up and their
+// weight prefetch overlap the tail of the kernel before them. Only kernels whose early part reads nothing that
+// another kernel of the stream writes honour it; the caller turns it on around a decode step (where the GEMMs'
+// B operands are weights) and off afterwards.
+void set_pdl(bool on);
+bool pdl_on();
+
 struct GemmArgs {
   const void* A = nullptr;  // [M, K] bf16, row stride lda
   const void* B = nullptr;  // [N, K] bf16, row stride ldb  (nn.Linear weight layout)

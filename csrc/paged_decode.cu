@@ -15,6 +15,7 @@
 // (acc, running max, running sum) to a scratch buffer and a second kernel merges the splits.
 #include "common.cuh"
 #include "kernels.h"
+#include "launch.cuh"
 
 namespace cb {
 
@@ -221,6 +222,8 @@ paged_decode_kernel(const bf16* __restrict__ q, const bf16* __restrict__ kc, con
 __global__ void __launch_bounds__(128)
 paged_decode_merge_kernel(const float* __restrict__ part_acc, const float* __restrict__ part_ml,
                           int n_splits, bf16* __restrict__ out) {
+  pdl_launch_dependents();
+  pdl_wait();
   const long long bh = blockIdx.x;
   const int d = threadIdx.x;
   float m = -1e30f;
@@ -298,7 +301,7 @@ void paged_decode(const PagedDecodeArgs& a, cudaStream_t s) {
     }
   }
   if (a.n_splits > 1)
-    cb::paged_decode_merge_kernel<<<a.B * a.Hq, 128, 0, s>>>(pa, pm, a.n_splits, (bf16*)a.out);
+    launch_pdl(cb::paged_decode_merge_kernel, dim3(a.B * a.Hq), dim3(128), 0, s, pa, pm, a.n_splits, (bf16*)a.out);
 }
 
 }  // namespace cosmos
@@ -359,6 +362,8 @@ decode_qkv_post_kernel(const bf16* __restrict__ qkv, int B, int Hq, int Hkv, con
                        const bf16* __restrict__ gamma_k, float eps, const long long* __restrict__ slots,
                        bf16* __restrict__ q_out, bf16* __restrict__ kc, bf16* __restrict__ vc, int page_size
                        COSMOS_BC_PARAMS) {
+  pdl_launch_dependents();
+  pdl_wait();
   const int lane = threadIdx.x & 31;
   const int heads = Hq + 2 * Hkv;
   const long long w = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
@@ -405,7 +410,7 @@ void decode_qkv_post(const void* qkv, int B, int Hq, int Hkv, const float* cos_t
   (void)n_slots; (void)status;  // used by the bounds-checked build
   const long long warps = (long long)B * (Hq + 2 * Hkv);
   if (warps <= 0) return;
-  cb::decode_qkv_post_kernel<<<(unsigned)((warps + 7) / 8), 256, 0, s>>>(
+  launch_pdl(cb::decode_qkv_post_kernel, dim3((unsigned)((warps + 7) / 8)), dim3(256), 0, s,
       (const bf16*)qkv, B, Hq, Hkv, cos_t, sin_t, (const bf16*)gamma_q, (const bf16*)gamma_k, eps, slots,
       (bf16*)q_out, (bf16*)k_cache, (bf16*)v_cache, page_size COSMOS_BC_ARGS(n_slots, status));
 }

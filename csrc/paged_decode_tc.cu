@@ -20,6 +20,7 @@
 //   k_cache / v_cache [num_pages, Hkv, page_size, 128] bf16, page_size in {8, 16, 32, 64, 128}
 #include "common.cuh"
 #include "kernels.h"
+#include "launch.cuh"
 
 namespace cb {
 
@@ -37,9 +38,13 @@ constexpr int PT_SMEM = PT_NST * 2 * PT_TILE_BYTES + PT_NOPB * PT_OPB + 2048 + 1
 constexpr int PB_FULL = 0;                 // + stage
 constexpr int PB_EMPTY = PT_NST;           // + stage
 constexpr int PB_S = 2 * PT_NST;           // + (tile & 1): scores ready
-constexpr int PB_P = 2 * PT_NST + 2;       // P written (128 arrivals)
-constexpr int PB_PV = 2 * PT_NST + 3;      // + (tile & 1): second product of that tile done
-constexpr int PB_COUNT = 2 * PT_NST + 5;
+// One P barrier per P buffer. With a single barrier the 128 softmax threads could complete the phases of tiles t
+// and t + 1 back to back (the scores of t + 1 are issued before the issuer waits for P of t) and an issuer that
+// looked late would see the parity of t "not completed" again and wait for good. A buffer's barrier completes a
+// second time only after the product that read the buffer, which the issuer starts after it has seen the first.
+constexpr int PB_P = 2 * PT_NST + 2;       // + (tile & 1): P of that tile written (128 arrivals)
+constexpr int PB_PV = 2 * PT_NST + 4;      // + (tile & 1): second product of that tile done
+constexpr int PB_COUNT = 2 * PT_NST + 6;
 
 __device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t (&v)[16]) {
   asm volatile(
@@ -131,6 +136,7 @@ paged_decode_tc_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_con
     mbar_init(B(PB_S), 1);
     mbar_init(B(PB_S + 1), 1);
     mbar_init(B(PB_P), 128);
+    mbar_init(B(PB_P + 1), 128);
     mbar_init(B(PB_PV), 1);
     mbar_init(B(PB_PV + 1), 1);
     *abort_flag = 0;
@@ -148,6 +154,10 @@ paged_decode_tc_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_con
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
+  // set-up done: the next kernel may start its own, and this one waits for the kernel that wrote q and the
+  // newest cache row (no-ops unless launched as a programmatic dependent)
+  pdl_launch_dependents();
+  pdl_wait();
   const uint32_t tmem_base = *tmem_slot_ptr;
   const uint32_t T_S0 = tmem_base, T_O = tmem_base + 32;  // scores of global tile g at T_S0 + 16 * (g & 1)
 
@@ -265,7 +275,7 @@ paged_decode_tc_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_con
           issue_s(gt + 1);
           tc_commit(B(PB_S + ((gt + 1) & 1)));
         }
-        ok = mbar_wait(B(PB_P), gt & 1, abort_flag, status, ST_TIMEOUT_MMA);
+        ok = mbar_wait(B(PB_P + (gt & 1)), (gt >> 1) & 1, abort_flag, status, ST_TIMEOUT_MMA);
         if (!ok) break;
         tc_fence_after();
         const uint64_t v_desc = make_smem_desc_sw128(v_smem(s), PT_HALF, 1024);
@@ -359,7 +369,7 @@ paged_decode_tc_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_con
           *reinterpret_cast<bf16*>(pbuf + opb_offset(g, t)) = __float2bfloat16(p);
         }
         fence_proxy_async();
-        mbar_arrive(B(PB_P));
+        mbar_arrive(B(PB_P + (gt & 1)));
       }
       if (!ok) break;
       // ---- item epilogue: row sums over the 128 threads, then this thread's output dim for every head
@@ -473,7 +483,7 @@ static void launch_tc(const PagedDecodeArgs& a, float* pa, float* pm, cudaStream
   }
   const long long items = (long long)a.n_splits * a.Hkv * a.B;
   const int grid = (int)std::min<long long>(items, sms);
-  cb::paged_decode_tc_kernel<GROUP><<<grid, cb::PT_THREADS, cb::PT_SMEM, s>>>(
+  launch_pdl(cb::paged_decode_tc_kernel<GROUP>, dim3(grid), dim3(cb::PT_THREADS), cb::PT_SMEM, s,
       tk, tv, (const bf16*)a.q, a.block_table, a.seq_lens, a.max_pages, a.page_size, a.num_pages, a.B, a.Hq, a.Hkv,
       a.n_splits, a.scale * 1.4426950408889634f, pa, pm, (bf16*)a.out, a.status);
 }
