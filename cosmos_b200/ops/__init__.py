@@ -411,6 +411,71 @@ def decode_qkv_post(qkv, n_q_heads: int, cos, sin, q_gamma, k_gamma, eps: float,
     return q
 
 
+SAMPLE_K = 64  # candidates kept per sequence and vocabulary shard by the sampling ops
+
+
+def sample_topk(logits, seen_any, seen_out, tokens, presence, repetition, vocab_offset: int = 0):
+    """First half of the decode-step sampler. `logits` [B, V]: this rank's vocabulary shard. Marks tokens[b] (the
+    token consumed by this step) in the [B, V] flag tensors `seen_any` / `seen_out` when it lies in the shard, applies
+    the repetition penalty (CTRL style, on tokens seen in prompt or output) and the presence penalty (on generated
+    tokens), and returns cand [B, 64, 2] float: the 64 largest penalised logits, best first, each with its global
+    token id stored as int32 bits. Flags may be None (no penalties). One kernel on CUDA (bf16 logits): radix select
+    over the row, no [B, V] intermediate."""
+    b, v = logits.shape
+    if _use_cuda(logits) and logits.dtype == torch.bfloat16:
+        return _k().sample_topk(logits, seen_any, seen_out, tokens, presence, repetition, int(vocab_offset))
+    l = logits.float()
+    if seen_any is not None:
+        loc = tokens - vocab_offset
+        mine = ((loc >= 0) & (loc < v))[:, None]
+        idx = loc.clamp(0, v - 1)[:, None]
+        # tokens of other shards write back what was there
+        seen_out.scatter_(1, idx, seen_out.gather(1, idx) | mine)
+        seen_any.scatter_(1, idx, seen_any.gather(1, idx) | mine)
+        rep = repetition[:, None]
+        l = torch.where(seen_any.bool(), torch.where(l > 0, l / rep, l * rep), l)
+        l = l - presence[:, None] * seen_out.float()
+    k = min(SAMPLE_K, v)
+    vals, idx = torch.topk(l, k, dim=-1)
+    if k < SAMPLE_K:
+        vals = torch.cat([vals, vals.new_full((b, SAMPLE_K - k), float("-inf"))], dim=1)
+        idx = torch.cat([idx, idx.new_zeros((b, SAMPLE_K - k))], dim=1)
+    ids = (idx + vocab_offset).to(torch.int32).view(torch.float32)
+    return torch.stack([vals, ids], dim=-1).contiguous()
+
+
+def sample_pick(cand, n_src: int, temperature, top_k, top_p, noise, vocab_size: int, out):
+    """Second half: cand [n_src * B, 64, 2] (the candidates of every vocabulary shard, shard-major) -> out [B]
+    (int64 token ids). Merges the shards' candidates, keeps the top_k[b] best, softmax at temperature[b], nucleus
+    cut at top_p[b] (the most likely token always stays) and the Gumbel-max draw with noise[b, :64] (uniform in
+    (0, 1)); temperature 0 takes the best candidate. Ids are clamped to vocab_size - 1 (padded LM-head rows)."""
+    if cand.is_cuda and _backend != "library" and load_extension():
+        _k().sample_pick_(cand.contiguous(), int(n_src), temperature, top_k, top_p, noise, int(vocab_size), out)
+        return out
+    b = cand.shape[0] // n_src
+    c = cand.view(n_src, b, SAMPLE_K, 2).permute(1, 0, 2, 3).reshape(b, n_src * SAMPLE_K, 2)
+    vals, ids = c[..., 0], c[..., 1].contiguous().view(torch.int32).long()
+    if n_src > 1:
+        # best value first; equal values: the smaller token id first
+        o = torch.argsort(ids, dim=1, stable=True)
+        vals, ids = vals.gather(1, o), ids.gather(1, o)
+        o = torch.argsort(vals, dim=1, descending=True, stable=True)[:, :SAMPLE_K]
+        vals, ids = vals.gather(1, o), ids.gather(1, o)
+    k = SAMPLE_K
+    t = temperature[:, None]
+    z = vals / torch.where(t > 0, t, torch.ones_like(t))
+    rank = torch.arange(k, device=cand.device)[None]
+    z = torch.where(rank < top_k[:, None].clamp(1, k), z, torch.full_like(z, float("-inf")))
+    p = torch.softmax(z, dim=-1)
+    keep = (torch.cumsum(p, dim=-1) - p) < top_p[:, None]
+    z = torch.where(keep, z, torch.full_like(z, float("-inf")))
+    g = -torch.log(-torch.log(noise[:, :k]))
+    pick = torch.argmax(z + g, dim=-1)
+    sampled = ids.gather(1, pick[:, None])[:, 0]
+    out.copy_(torch.where(temperature > 0, sampled, ids[:, 0]).clamp(0, vocab_size - 1))
+    return out
+
+
 def paged_decode(q, k_cache, v_cache, block_table, seq_lens, scale: Optional[float] = None,
                  n_splits: Optional[int] = None, scratch=None, max_len: Optional[int] = None, impl: int = 0):
     """q [B, Hq, 128] against a paged cache [pages, Hkv, page_size, 128] -> [B, Hq, 128].

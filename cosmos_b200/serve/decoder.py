@@ -191,26 +191,26 @@ class TPDecoder:
             for li in range(self.cfg.n_layers):
                 x, delta = self._layer(li, x, delta, cos, sin, slots, self.table, self.lens, self.max_len)
             h, _ = ops.rmsnorm(delta, self.final_norm, self.cfg.rms_eps, residual=x)
-        return ops.gemm(h, self.lm_head).float()     # [B, V/tp]
+        return ops.gemm(h, self.lm_head)             # [B, V/tp]
 
     def _finish_step(self, logits: torch.Tensor, b: int) -> None:
         self.last_logits = logits                    # this rank's vocab shard, kept for inspection
         if self.sampling is not None:
-            idx = self._sample(self._penalise(logits), distributed=True)   # global ids across the vocab shards
-        else:
-            val, idx = logits.max(dim=-1)
-            idx = idx + self.rank * self.v_loc
-            if self.tp > 1:
-                packed = torch.stack([val, idx.float()], dim=-1)      # [B, 2]
-                allp = torch.empty(self.tp * b, 2, device=self.device)            # rank-major concatenation
-                dist.all_gather_into_tensor(allp, packed, group=self.group)
-                allp = allp.view(self.tp, b, 2)
-                best = allp[..., 0].argmax(dim=0)
-                idx = allp[best, torch.arange(b, device=self.device), 1].long()
+            self._sample(logits)                     # global ids across the vocab shards, into self.next_tokens
+            return
+        val, idx = logits.float().max(dim=-1)
+        idx = idx + self.rank * self.v_loc
+        if self.tp > 1:
+            packed = torch.stack([val, idx.float()], dim=-1)      # [B, 2]
+            allp = torch.empty(self.tp * b, 2, device=self.device)            # rank-major concatenation
+            dist.all_gather_into_tensor(allp, packed, group=self.group)
+            allp = allp.view(self.tp, b, 2)
+            best = allp[..., 0].argmax(dim=0)
+            idx = allp[best, torch.arange(b, device=self.device), 1].long()
         self.next_tokens.copy_(idx.clamp(max=self.cfg.vocab_size - 1))
 
     # ------------------------------------------------------------------ sampling (tp = 1)
-    SAMPLE_K = 64  # candidates kept per slot; a request's top_k is clamped to it
+    SAMPLE_K = ops.SAMPLE_K  # candidates kept per slot; a request's top_k is clamped to it
 
     def enable_sampling(self, batch: int) -> None:
         """Per-slot sampling state, all on the device so that the step stays one CUDA graph:
@@ -231,51 +231,20 @@ class TPDecoder:
         if self.sampling is not None:
             self.sampling["noise"].uniform_(1e-7, 1.0, generator=generator)
 
-    def _penalise(self, logits: torch.Tensor) -> torch.Tensor:
-        """Repetition penalty (CTRL style) on tokens seen in prompt or output, presence penalty on generated
-        tokens; the token consumed by this step (self.tokens) counts as generated."""
+    def _sample(self, logits: torch.Tensor) -> torch.Tensor:
+        """Penalties, top-k / top-p and the Gumbel-max draw for every slot (`ops.sample_topk`, `ops.sample_pick`):
+        the 64 best penalised logits of this rank's vocabulary shard, the candidates of all shards gathered, then
+        the draw. Every rank ends up with the same choice (same candidates, same noise). The token consumed by
+        this step (self.tokens) counts as generated. Writes self.next_tokens."""
         sp = self.sampling
-        loc = self.tokens - self.rank * self.v_loc            # position in this rank's vocabulary shard
-        mine = ((loc >= 0) & (loc < self.v_loc))[:, None]
-        idx = loc.clamp(0, self.v_loc - 1)[:, None]
-        # device-side scatter (no host tensor involved, so it can sit in the graph); tokens of other shards write
-        # back what was there
-        sp["seen_out"].scatter_(1, idx, sp["seen_out"].gather(1, idx) | mine)
-        sp["seen_any"].scatter_(1, idx, sp["seen_any"].gather(1, idx) | mine)
-        rep = sp["repetition"][:, None]
-        pen = torch.where(logits > 0, logits / rep, logits * rep)
-        logits = torch.where(sp["seen_any"], pen, logits)
-        return logits - sp["presence"][:, None] * sp["seen_out"].float()
-
-    def _sample(self, logits: torch.Tensor, distributed: bool) -> torch.Tensor:
-        """Top-k / top-p sampling among the SAMPLE_K best logits of every slot with the Gumbel-max trick; returns
-        token ids in the full vocabulary. `distributed`: `logits` is this rank's vocabulary shard and the
-        candidates of all ranks are merged (every rank ends up with the same choice: same candidates, same noise)."""
-        sp = self.sampling
-        k = min(self.SAMPLE_K, logits.shape[-1])
-        vals, cand = torch.topk(logits, k, dim=-1)                    # sorted, best first
-        if distributed:
-            cand = cand + self.rank * self.v_loc
-            if self.tp > 1:
-                b = logits.shape[0]
-                packed = torch.stack([vals, cand.float()], dim=-1).contiguous()          # [B, k, 2]
-                allp = torch.empty(self.tp * b, k, 2, device=logits.device)   # rank-major concatenation
-                dist.all_gather_into_tensor(allp, packed, group=self.group)
-                allp = allp.view(self.tp, b, k, 2).permute(1, 0, 2, 3).reshape(b, self.tp * k, 2)
-                vals, pos = torch.topk(allp[..., 0], k, dim=-1)
-                cand = allp[..., 1].gather(1, pos).long()
-        greedy_idx = cand[:, 0]
-        t = sp["temperature"][:, None]
-        z = vals / torch.where(t > 0, t, torch.ones_like(t))
-        rank = torch.arange(k, device=logits.device)[None]
-        z = torch.where(rank < sp["top_k"][:, None].clamp(1, k), z, torch.full_like(z, float("-inf")))
-        p = torch.softmax(z, dim=-1)
-        keep = (torch.cumsum(p, dim=-1) - p) < sp["top_p"][:, None]   # always keeps the most likely token
-        z = torch.where(keep, z, torch.full_like(z, float("-inf")))
-        g = -torch.log(-torch.log(sp["noise"][:, :k]))
-        pick = torch.argmax(z + g, dim=-1)
-        sampled = cand.gather(1, pick[:, None])[:, 0]
-        return torch.where(sp["temperature"] > 0, sampled, greedy_idx)
+        cand = ops.sample_topk(logits, sp["seen_any"], sp["seen_out"], self.tokens, sp["presence"], sp["repetition"],
+                               self.rank * self.v_loc)
+        if self.tp > 1:
+            allc = torch.empty(self.tp * cand.shape[0], ops.SAMPLE_K, 2, device=cand.device)  # rank-major
+            dist.all_gather_into_tensor(allc, cand, group=self.group)
+            cand = allc
+        return ops.sample_pick(cand, self.tp, sp["temperature"], sp["top_k"], sp["top_p"], sp["noise"],
+                               self.cfg.vocab_size, self.next_tokens)
 
     # ------------------------------------------------------------------ public
     @torch.no_grad()

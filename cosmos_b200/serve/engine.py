@@ -27,6 +27,7 @@ from typing import Deque, Dict, List, Optional, Sequence
 
 import torch
 
+from .. import ops
 from ..config import MoTConfig
 from ..models import rope
 from .decoder import TPDecoder
@@ -119,7 +120,7 @@ class BatchEngine:
             raise ValueError(f"prompt ({len(ids)}) + max_new_tokens ({max_new_tokens}) exceeds max_len {self.max_len}")
         params = dict(ids=[min(int(t), self.cfg.vocab_size - 1) for t in ids], max_new_tokens=int(max_new_tokens),
                       eos_ids=tuple(eos_ids), temperature=float(temperature),
-                      top_k=int(top_k) if top_k and top_k > 0 else TPDecoder.SAMPLE_K, top_p=float(top_p),
+                      top_k=int(top_k) if top_k and top_k > 0 else ops.SAMPLE_K, top_p=float(top_p),
                       presence_penalty=float(presence_penalty), repetition_penalty=float(repetition_penalty))
         r = self._enqueue(params, embeds, positions, vision_mask, deepstack, on_token)
         if embeds is not None and (positions is None or embeds.shape[0] != len(r.ids)):
@@ -246,13 +247,11 @@ class BatchEngine:
         rep = sp["repetition"][slot_idx][:, None]
         pen = torch.where(logits > 0, logits / rep, logits * rep)
         logits = torch.where(seen, pen, logits)
-        sub = {k: (v[slot_idx] if v.shape[0] == self.max_batch else v) for k, v in sp.items()}
-        sub["noise"] = torch.rand(len(slot_idx), dec.SAMPLE_K, device=logits.device, generator=self.noise_gen).clamp_min(1e-7)
-        keep, dec.sampling = dec.sampling, sub
-        try:
-            return dec._sample(logits, distributed=False)
-        finally:
-            dec.sampling = keep
+        noise = torch.rand(len(slot_idx), ops.SAMPLE_K, device=logits.device, generator=self.noise_gen).clamp_min(1e-7)
+        cand = ops.sample_topk(logits, None, None, None, None, None, 0)
+        out = torch.empty(len(slot_idx), dtype=torch.long, device=logits.device)
+        return ops.sample_pick(cand, 1, sp["temperature"][slot_idx].contiguous(), sp["top_k"][slot_idx].contiguous(),
+                               sp["top_p"][slot_idx].contiguous(), noise, dec.cfg.vocab_size, out)
 
     def _accept(self, r: Request, tok: int) -> None:
         """Books a generated token; retires the request when it ends."""

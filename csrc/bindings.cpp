@@ -916,6 +916,59 @@ bool bounds_check_enabled() { return cosmos::bounds_check_enabled(); }
 void gemm_set_grid_limit(int64_t max_ctas) { cosmos::gemm_set_grid_limit((int)max_ctas); }
 // A/B switches for timing and tests: CTA-pair GEMM tiles on/off, attention forward variant bits.
 void gemm_set_cta_pair(bool on) { cosmos::gemm_set_cta_pair(on); }
+// Decode-step sampling: the 64 best penalised logits of this rank's vocabulary shard per sequence ...
+Tensor sample_topk(const Tensor& logits, const OptT& seen_any, const OptT& seen_out, const OptT& tokens,
+                   const OptT& presence, const OptT& repetition, int64_t vocab_offset) {
+  check_bf16_cuda(logits, "logits");
+  TORCH_CHECK(logits.dim() == 2 && logits.stride(1) == 1, "logits must be [B, V] with unit column stride");
+  c10::cuda::CUDAGuard guard(logits.device());
+  const int64_t B = logits.size(0), V = logits.size(1);
+  auto flags = [&](const OptT& t, const char* name) -> void* {
+    if (!t.has_value() || !t->defined()) return nullptr;
+    TORCH_CHECK(t->is_cuda() && t->is_contiguous() && t->element_size() == 1 && t->numel() == B * V, name,
+                " must be a contiguous [B, V] tensor of 1-byte flags");
+    return t->data_ptr();
+  };
+  auto vecf = [&](const OptT& t, const char* name) -> const float* {
+    if (!t.has_value() || !t->defined()) return nullptr;
+    TORCH_CHECK(t->is_cuda() && t->scalar_type() == at::kFloat && t->is_contiguous() && t->numel() == B, name,
+                " must be a float tensor [B]");
+    return t->data_ptr<float>();
+  };
+  const long long* tok = nullptr;
+  if (tokens.has_value() && tokens->defined()) {
+    TORCH_CHECK(tokens->is_cuda() && tokens->scalar_type() == at::kLong && tokens->is_contiguous() && tokens->numel() == B,
+                "tokens must be an int64 tensor [B]");
+    tok = reinterpret_cast<const long long*>(tokens->data_ptr<int64_t>());
+  }
+  Tensor cand = at::empty({B, 64, 2}, logits.options().dtype(at::kFloat));
+  cosmos::sample_topk(logits.data_ptr(), logits.stride(0), (int)B, (int)V, flags(seen_any, "seen_any"),
+                      flags(seen_out, "seen_out"), tok, vecf(presence, "presence"), vecf(repetition, "repetition"),
+                      (int)vocab_offset, cand.data_ptr(), cur_stream());
+  return cand;
+}
+
+// ... and the draw among the candidates of all shards (cand [n_src * B, 64, 2], source-major) into tokens_out.
+void sample_pick_(const Tensor& cand, int64_t n_src, const Tensor& temperature, const Tensor& top_k, const Tensor& top_p,
+                  const Tensor& noise, int64_t vocab_size, Tensor tokens_out) {
+  TORCH_CHECK(cand.is_cuda() && cand.scalar_type() == at::kFloat && cand.is_contiguous() && cand.dim() == 3 &&
+              cand.size(1) == 64 && cand.size(2) == 2 && cand.size(0) % n_src == 0, "cand must be [n_src * B, 64, 2] float");
+  c10::cuda::CUDAGuard guard(cand.device());
+  const int64_t B = cand.size(0) / n_src;
+  TORCH_CHECK(temperature.scalar_type() == at::kFloat && temperature.numel() == B && temperature.is_contiguous() &&
+              top_p.scalar_type() == at::kFloat && top_p.numel() == B && top_p.is_contiguous() &&
+              top_k.scalar_type() == at::kLong && top_k.numel() == B && top_k.is_contiguous(),
+              "temperature / top_p float [B], top_k int64 [B]");
+  TORCH_CHECK(noise.scalar_type() == at::kFloat && noise.dim() == 2 && noise.size(0) == B && noise.size(1) >= 64 &&
+              noise.stride(1) == 1, "noise must be float [B, >= 64]");
+  TORCH_CHECK(tokens_out.scalar_type() == at::kLong && tokens_out.numel() == B && tokens_out.is_contiguous(),
+              "tokens_out must be int64 [B]");
+  cosmos::sample_pick(cand.data_ptr(), (int)n_src, (int)B, temperature.data_ptr<float>(),
+                      reinterpret_cast<const long long*>(top_k.data_ptr<int64_t>()), top_p.data_ptr<float>(),
+                      noise.data_ptr<float>(), noise.stride(0), (int)vocab_size,
+                      reinterpret_cast<long long*>(tokens_out.data_ptr<int64_t>()), cur_stream());
+}
+
 void gemm_set_debug(int64_t bits) { cosmos::gemm_set_debug((int)bits); }
 void set_pdl(bool on) { cosmos::set_pdl(on); }
 void attn_set_cta_pair(bool on) { cosmos::attn_set_cta_pair(on); }
@@ -1135,6 +1188,8 @@ TORCH_LIBRARY(cosmos_b200, m) {
   m.def("gemm_set_cta_pair", &gemm_set_cta_pair);
   m.def("gemm_set_debug", &gemm_set_debug);
   m.def("set_pdl", &set_pdl);
+  m.def("sample_topk", &sample_topk);
+  m.def("sample_pick_", &sample_pick_);
   m.def("attn_set_cta_pair", &attn_set_cta_pair);
   m.def("attn_set_exp_emulation", &attn_set_exp_emulation);
   m.def("attn_set_debug", &attn_set_debug);

@@ -92,6 +92,16 @@ void gemm_bf16(const GemmArgs& a, cudaStream_t stream);
 // weight routing: tokens are already grouped into an AR segment and a DM segment).
 void gemm_bf16_grouped(const GemmArgs* args, int n, cudaStream_t stream);
 
+// Decode-step sampling (csrc/sampling.cu). sample_topk: bf16 logits [B, V] (row stride ld) of one vocabulary shard
+// -> cand [B, 64] (penalised logit, global token id as int bits), best first; seen_any / seen_out are [B, V] byte
+// flags (null = no penalties), updated for tokens[b]. sample_pick: cand [n_src, B, 64] -> tokens_out [B] (int64).
+void sample_topk(const void* logits, long long ld, int B, int V, void* seen_any, void* seen_out,
+                 const long long* tokens, const float* presence, const float* repetition, int vocab_offset,
+                 void* cand, cudaStream_t s);
+void sample_pick(const void* cand, int n_src, int B, const float* temperature, const long long* top_k,
+                 const float* top_p, const float* noise, long long noise_ld, int vocab_size, long long* tokens_out,
+                 cudaStream_t s);
+
 struct AttnArgs {
   // Q [B, Sq, Hq, 128], K/V [B, Skv, Hkv, 128], O [B, Sq, Hq, 128]; element strides given.
   const void* Q = nullptr;

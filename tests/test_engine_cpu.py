@@ -3,6 +3,7 @@ times; every token the engine emits must be the (near-)arg-max of the reference 
 that engine is fed the same prefix (teacher forcing keeps near-ties from cascading)."""
 import torch
 
+from cosmos_b200 import ops
 from cosmos_b200.config import tiny_config
 from cosmos_b200.models import rope
 from cosmos_b200.models.mot import MoTModel
@@ -107,9 +108,11 @@ def test_device_side_sampling_follows_the_truncated_softmax():
     g = torch.Generator().manual_seed(0)
     n = 4000
     counts = torch.zeros(4, 300)
+    dec.tokens = torch.zeros(4, dtype=torch.long)             # no penalties set: the seen flags change nothing
+    dec.next_tokens = torch.zeros(4, dtype=torch.long)
     for _ in range(n):
         dec.refill_noise(g)
-        tok = dec._sample(logits, distributed=True)
+        tok = dec._sample(logits)
         counts[torch.arange(4), tok] += 1
     f = counts / n
     want0 = torch.softmax(base[:3], -1)                       # slot 0: top_k = 3
@@ -124,9 +127,18 @@ def test_device_side_sampling_follows_the_truncated_softmax():
     dec.tokens = torch.tensor([10, 11, 12, 13])
     sp["presence"][:] = torch.tensor([1.5, 0.0, 0.0, 0.0])
     sp["repetition"][:] = torch.tensor([1.0, 2.0, 1.0, 1.0])
-    out = dec._penalise(logits.clone())
-    assert torch.isclose(out[0, 10], torch.tensor(0.5)) and torch.isclose(out[1, 11], torch.tensor(0.75))
-    assert torch.equal(out[2], logits[2]) and torch.isclose(out[1, 10], torch.tensor(2.0))
+    sp["seen_any"].zero_()
+    sp["seen_out"].zero_()
+    cand = ops.sample_topk(logits.clone(), sp["seen_any"], sp["seen_out"], dec.tokens, sp["presence"], sp["repetition"], 0)
+    vals, ids = cand[..., 0], cand[..., 1].contiguous().view(torch.int32)
+
+    def val(b, tok):
+        return vals[b][ids[b] == tok]
+
+    assert torch.isclose(val(0, 10), torch.tensor(0.5)) and torch.isclose(val(1, 11), torch.tensor(0.75))
+    assert torch.isclose(val(2, 12), torch.tensor(1.0)) and torch.isclose(val(1, 10), torch.tensor(2.0))
+    assert sp["seen_out"][0, 10] and sp["seen_any"][3, 13] and sp["seen_out"].sum() == 4
+    assert torch.equal(ids[2, :6].long(), torch.arange(10, 16))   # best first
 
 
 def test_sampled_requests_run_through_the_engine():

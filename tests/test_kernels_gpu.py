@@ -750,3 +750,65 @@ def test_attention_on_cta_pairs_matches_the_reference():
             assert (lse - rlse).abs().max().item() < 1e-3
     finally:
         k.attn_set_cta_pair(False)
+
+
+@pytest.mark.parametrize("b,v,flags", [(5, 151936, True), (3, 4097, True), (4, 1000, False), (2, 50, True)])
+def test_sample_topk_selects_the_64_largest_penalised_logits(b, v, flags):
+    """Radix-select kernel against torch.topk over the fp32 definition of the penalties. bf16 logits tie often, so the
+    values are compared in order and every id is checked against the penalised row."""
+    g = torch.Generator(device=DEV).manual_seed(v)
+    logits = (torch.randn(b, v, device=DEV, generator=g) * 3).bfloat16()
+    tokens = torch.randint(0, v, (b,), device=DEV, generator=g)
+    any_ = (torch.rand(b, v, device=DEV, generator=g) < 0.3) if flags else None
+    out_ = (any_ & (torch.rand(b, v, device=DEV, generator=g) < 0.5)) if flags else None
+    pres = torch.rand(b, device=DEV, generator=g) * 2 if flags else None
+    rep = 1 + torch.rand(b, device=DEV, generator=g) if flags else None
+    off = 1000
+    ref_any, ref_out = (any_.clone(), out_.clone()) if flags else (None, None)
+    want = ops.sample_topk(logits.float(), ref_any, ref_out, tokens + off, pres, rep, off)      # PyTorch definition
+    got = ops.sample_topk(logits, any_, out_, tokens + off, pres, rep, off)
+    torch.cuda.synchronize()
+    if flags:
+        assert torch.equal(any_, ref_any) and torch.equal(out_, ref_out)
+        assert out_[torch.arange(b), tokens].all()
+    assert torch.equal(got[..., 0], want[..., 0])
+    ids = got[..., 1].contiguous().view(torch.int32).long() - off
+    k = min(64, v)
+    pen = logits.float()
+    if flags:
+        pen = torch.where(ref_any, torch.where(pen > 0, pen / rep[:, None], pen * rep[:, None]), pen)
+        pen = pen - pres[:, None] * ref_out.float()
+    assert ((ids[:, :k] >= 0) & (ids[:, :k] < v)).all()
+    assert torch.equal(pen.gather(1, ids[:, :k]), got[:, :k, 0])
+    for r in range(b):
+        assert ids[r, :k].unique().numel() == k
+
+
+def test_sample_topk_with_all_logits_equal():
+    logits = torch.full((2, 5000), 1.25, device=DEV, dtype=torch.bfloat16)
+    got = ops.sample_topk(logits, None, None, None, None, None, 0)
+    assert (got[..., 0] == 1.25).all()
+    ids = got[..., 1].contiguous().view(torch.int32)
+    assert all(ids[r].unique().numel() == 64 and ids[r].min() >= 0 and ids[r].max() < 5000 for r in range(2))
+
+
+@pytest.mark.parametrize("n_src", [1, 2, 8])
+def test_sample_pick_matches_the_definition(n_src):
+    """Merge of the shards' candidates and the draw against the PyTorch definition on the same noise."""
+    g = torch.Generator(device=DEV).manual_seed(n_src)
+    b = 300
+    vals = torch.randn(n_src, b, 64, device=DEV, generator=g).sort(dim=-1, descending=True).values * 2
+    ids = torch.stack([torch.randperm(100000, device=DEV, generator=g)[:n_src * 64].view(n_src, 64) for _ in range(b)], 1)
+    cand = torch.stack([vals, ids.to(torch.int32).view(torch.float32)], -1).view(n_src * b, 64, 2).contiguous()
+    temp = torch.where(torch.rand(b, device=DEV, generator=g) < 0.2, torch.zeros(b, device=DEV),
+                       0.3 + torch.rand(b, device=DEV, generator=g))
+    top_k = torch.randint(1, 80, (b,), device=DEV, generator=g)
+    top_p = 0.2 + 0.8 * torch.rand(b, device=DEV, generator=g)
+    noise = torch.rand(b, 64, device=DEV, generator=g).clamp_min(1e-7)
+    got = ops.sample_pick(cand, n_src, temp, top_k, top_p, noise, 90000, torch.empty(b, dtype=torch.long, device=DEV))
+    want = ops.sample_pick(cand.cpu(), n_src, temp.cpu(), top_k.cpu(), top_p.cpu(), noise.cpu(), 90000,
+                           torch.empty(b, dtype=torch.long))
+    same = (got.cpu() == want).float().mean().item()
+    assert same >= 0.99, f"only {same:.3f} of the draws agree"      # a nucleus boundary within rounding may differ
+    greedy = temp.cpu() == 0
+    assert torch.equal(got.cpu()[greedy], want[greedy]) and (got < 90000).all()
