@@ -56,12 +56,16 @@ class GeneratorEngine:
         dev = next(model.parameters()).device
         self.ctx = ctx if ctx is not None else (WorkspaceAttn() if dev.type == "cuda" else LOCAL_ATTN)
         self.cfg_group = cfg_group
-        # Launch-bound tiers (images, 256p clips): the model evaluation of a denoise step is captured in a CUDA graph
-        # once per generation and replayed for the other steps (the reference's PyTorch engine also runs "with CUDA
-        # Graphs enabled where supported", inference_benchmarks.md:39). Sequences longer than this many DM tokens are
-        # compute bound and run eagerly; 0 switches graphs off. Single-GPU layouts only (COSMOS_CUDA_GRAPH_TOKENS).
+        # Launch-bound steps (thumbnails, short low-resolution clips): the model evaluation of a denoise step is
+        # captured in a CUDA graph once per generation and replayed for the other steps (the reference's PyTorch
+        # engine also runs "with CUDA Graphs enabled where supported", inference_benchmarks.md:39). Sequences longer
+        # than this many DM tokens run eagerly; 0 switches graphs off. Single-GPU layouts only
+        # (COSMOS_CUDA_GRAPH_TOKENS). With this dense 8 B-parameter stand-in a 720p image (3600 tokens) and a
+        # 61-frame 256p clip (7168 tokens) are already compute-bound at ~0.12 s per guided step: measured 4.29 s and
+        # 4.41 s of sampling without a graph against 4.54 s and 4.68 s with one (the capture costs more than 35
+        # replays save), hence the low default.
         import os
-        self.graph_max_tokens = int(os.environ.get("COSMOS_CUDA_GRAPH_TOKENS", "8192"))
+        self.graph_max_tokens = int(os.environ.get("COSMOS_CUDA_GRAPH_TOKENS", "1024"))
 
     # ------------------------------------------------------------------ prompt
     @torch.no_grad()
