@@ -411,6 +411,17 @@ def decode_qkv_post(qkv, n_q_heads: int, cos, sin, q_gamma, k_gamma, eps: float,
     return q
 
 
+def gemm_decode_qkv_post(h, w, n_q_heads: int, cos, sin, q_gamma, k_gamma, eps: float, slots, k_cache, v_cache):
+    """QKV projection of a decode step followed by `decode_qkv_post`. h [B, d]; w [(Hq + 2 Hkv) * 128, d]. On CUDA the
+    skinny GEMM leaves its split-K partial sums and the post-processing kernel reduces them as it reads: one launch
+    and one bf16 round trip fewer per layer."""
+    if _use_cuda(h, w) and w.shape[0] % 128 == 0:
+        return _k().gemm_decode_qkv_post(h, w, n_q_heads, cos.contiguous(), sin.contiguous(), q_gamma, k_gamma, eps,
+                                         slots.contiguous(), k_cache, v_cache)
+    qkv = gemm(h, w).view(h.shape[0], -1, k_cache.shape[-1])
+    return decode_qkv_post(qkv, n_q_heads, cos, sin, q_gamma, k_gamma, eps, slots, k_cache, v_cache)
+
+
 SAMPLE_K = 64  # candidates kept per sequence and vocabulary shard by the sampling ops
 
 

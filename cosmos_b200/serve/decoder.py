@@ -98,8 +98,7 @@ class TPDecoder:
             h, _ = ops.rmsnorm(x, p["norm1"], cfg.rms_eps)
         else:
             h, x = ops.rmsnorm(resid_delta, p["norm1"], cfg.rms_eps, residual=x)
-        qkv = ops.gemm(h, p["wqkv"]).view(b, self.hq + 2 * self.hk, self.hd)
-        q = ops.decode_qkv_post(qkv, self.hq, cos, sin, p["q_norm"], p["k_norm"], cfg.rms_eps, slots,
+        q = ops.gemm_decode_qkv_post(h, p["wqkv"], self.hq, cos, sin, p["q_norm"], p["k_norm"], cfg.rms_eps, slots,
                                 self.cache.k[li], self.cache.v[li])
         o = ops.paged_decode(q, self.cache.k[li], self.cache.v[li], table, lens, max_len=max_len)
         y = self._allreduce(ops.gemm(o.view(b, -1), p["wo"]))
@@ -116,8 +115,7 @@ class TPDecoder:
         p = self.layers[li]
         cfg = self.cfg
         b = x.shape[0]
-        qkv = ops.gemm(h, p["wqkv"]).view(b, self.hq + 2 * self.hk, self.hd)
-        q = ops.decode_qkv_post(qkv, self.hq, cos, sin, p["q_norm"], p["k_norm"], cfg.rms_eps, slots,
+        q = ops.gemm_decode_qkv_post(h, p["wqkv"], self.hq, cos, sin, p["q_norm"], p["k_norm"], cfg.rms_eps, slots,
                                 self.cache.k[li], self.cache.v[li])
         o = ops.paged_decode(q, self.cache.k[li], self.cache.v[li], table, lens, max_len=max_len)
         h, x = ops.gemm_reduce_rmsnorm(o.view(b, -1), p["wo"], x, p["norm2"], cfg.rms_eps)
@@ -133,8 +131,7 @@ class TPDecoder:
         cfg = self.cfg
         b = x.shape[0]
         tpc = self._tpctx
-        qkv = ops.gemm(h, p["wqkv"]).view(b, self.hq + 2 * self.hk, self.hd)
-        q = ops.decode_qkv_post(qkv, self.hq, cos, sin, p["q_norm"], p["k_norm"], cfg.rms_eps, slots,
+        q = ops.gemm_decode_qkv_post(h, p["wqkv"], self.hq, cos, sin, p["q_norm"], p["k_norm"], cfg.rms_eps, slots,
                                 self.cache.k[li], self.cache.v[li])
         o = ops.paged_decode(q, self.cache.k[li], self.cache.v[li], table, lens, max_len=max_len)
         h, x = tpc.gemm_allreduce_norm(o.view(b, -1), p["wo"], x, p["norm2"], cfg.rms_eps)
@@ -157,12 +154,13 @@ class TPDecoder:
         else:
             self.lens.add_(self.step_inc)
         x = self.embed[self.tokens]
-        # Programmatic dependent launch for the layer kernels: each one's set-up (and the GEMMs' first weight tiles)
-        # overlaps the tail of the kernel before it. On by default under tensor parallelism, where the step is
-        # latency-bound (8.96 -> 8.77 ms at TP 2); off on one GPU, where the step is bandwidth-bound and the early
-        # CTAs cost more than they hide (12.45 -> 12.6 ms). COSMOS_DECODE_PDL=0 / 1 overrides.
+        # Programmatic dependent launch for the layer kernels (COSMOS_DECODE_PDL=1): each one's set-up, and the GEMMs'
+        # first weight tiles, may overlap the tail of the kernel before it. Off by default: measured 8.96 -> 8.77 ms
+        # per step at TP 2, but 12.45 -> 12.6 ms on one GPU at batch 32 and 5.30 -> 5.50 ms at batch 1. A GEMM CTA
+        # needs most of an SM's shared memory, so the next GEMM cannot become resident before the current one
+        # leaves, and the programmatic edges cost about 0.5 us per launch in the replayed graph.
         pdl = self.device.type == "cuda" and ops.get_backend() != "library" and \
-            os.environ.get("COSMOS_DECODE_PDL", "1" if self.tp > 1 else "0") != "0"
+            os.environ.get("COSMOS_DECODE_PDL", "0") == "1"
         if pdl:
             torch.ops.cosmos_b200.set_pdl(True)
         try:

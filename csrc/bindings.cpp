@@ -912,6 +912,51 @@ Tensor decode_qkv_post(const Tensor& qkv, int64_t n_q_heads, const Tensor& cos_t
   return q;
 }
 
+// QKV projection of a decode step and its post-processing without the bf16 round trip: the skinny GEMM leaves its
+// split-K partial sums, and the q/k norm + rotary + cache-write kernel reduces them while it reads (one launch fewer
+// per layer than gemm + decode_qkv_post). h [B, K]; w [(Hq + 2 Hkv) * 128, K]. Returns q [B, Hq, 128].
+Tensor gemm_decode_qkv_post(const Tensor& h, const Tensor& w, int64_t n_q_heads, const Tensor& cos_t, const Tensor& sin_t,
+                            const Tensor& gamma_q, const Tensor& gamma_k, double eps, const Tensor& slots,
+                            Tensor k_cache, Tensor v_cache) {
+  check_bf16_cuda(h, "h"); check_bf16_cuda(w, "w");
+  c10::cuda::CUDAGuard guard(h.device());
+  Tensor A = as_2d(h);
+  const int64_t M = A.size(0), K = A.size(1), N = w.size(0);
+  TORCH_CHECK(w.dim() == 2 && w.size(1) == K && A.stride(1) == 1 && w.stride(1) == 1 && N % 128 == 0, "h [B, K], w [heads * 128, K]");
+  const int ks = cosmos::gemm_pick_k_splits((int)M, (int)N, (int)K, EPI_PLAIN);
+  const int64_t heads = N / 128, Hq = n_q_heads, Hkv = (heads - Hq) / 2;
+  if (ks <= 1 || A.stride(0) % 8 != 0 || w.stride(0) % 8 != 0) {
+    Tensor qkv = gemm(A, w, {}, EPI_PLAIN, {}, {}, 0, {});
+    return decode_qkv_post(qkv.view({M, heads, 128}), n_q_heads, cos_t, sin_t, gamma_q, gamma_k, eps, slots, k_cache, v_cache);
+  }
+  check_bf16_cuda(gamma_q, "gamma_q"); check_bf16_cuda(gamma_k, "gamma_k");
+  check_bf16_cuda(k_cache, "k_cache"); check_bf16_cuda(v_cache, "v_cache");
+  TORCH_CHECK(Hq > 0 && Hkv > 0 && Hq + 2 * Hkv == heads, "bad head split");
+  TORCH_CHECK(k_cache.dim() == 4 && k_cache.is_contiguous() && v_cache.is_contiguous() && k_cache.size(1) == Hkv &&
+              k_cache.size(3) == 128 && v_cache.sizes() == k_cache.sizes(), "caches must be contiguous [pages, Hkv, page_size, 128]");
+  TORCH_CHECK(cos_t.is_cuda() && cos_t.scalar_type() == at::kFloat && cos_t.is_contiguous() && cos_t.numel() == M * 64 &&
+              sin_t.is_cuda() && sin_t.scalar_type() == at::kFloat && sin_t.is_contiguous() && sin_t.numel() == M * 64,
+              "cos/sin must be contiguous fp32 [B, 64]");
+  TORCH_CHECK(gamma_q.numel() == 128 && gamma_k.numel() == 128 && gamma_q.is_contiguous() && gamma_k.is_contiguous());
+  TORCH_CHECK(slots.is_cuda() && slots.scalar_type() == at::kLong && slots.is_contiguous() && slots.numel() == M);
+  Tensor partial = at::empty({ks, M, N}, A.options().dtype(at::kFloat));
+  cosmos::GemmArgs g;
+  g.A = A.data_ptr(); g.B = w.data_ptr(); g.C = nullptr;
+  g.M = (int)M; g.N = (int)N; g.K = (int)K;
+  g.lda = A.stride(0); g.ldb = w.stride(0); g.ldc = N;
+  g.epi = EPI_PLAIN;
+  g.k_splits = ks; g.partial = partial.data_ptr<float>(); g.partial_only = true;
+  g.status = status_tensor(A.get_device()).data_ptr<int>();
+  cosmos::gemm_bf16(g, cur_stream());
+  Tensor q = at::empty({M, Hq, 128}, A.options());
+  cosmos::decode_qkv_post(nullptr, (int)M, (int)Hq, (int)Hkv, cos_t.data_ptr<float>(), sin_t.data_ptr<float>(),
+                          gamma_q.data_ptr(), gamma_k.data_ptr(), (float)eps,
+                          reinterpret_cast<const long long*>(slots.data_ptr<int64_t>()), q.data_ptr(),
+                          k_cache.data_ptr(), v_cache.data_ptr(), (int)k_cache.size(2), k_cache.size(0) * k_cache.size(2),
+                          status_tensor(A.get_device()).data_ptr<int>(), cur_stream(), partial.data_ptr<float>(), ks);
+  return q;
+}
+
 bool bounds_check_enabled() { return cosmos::bounds_check_enabled(); }
 void gemm_set_grid_limit(int64_t max_ctas) { cosmos::gemm_set_grid_limit((int)max_ctas); }
 // A/B switches for timing and tests: CTA-pair GEMM tiles on/off, attention forward variant bits.
@@ -1183,6 +1228,7 @@ TORCH_LIBRARY(cosmos_b200, m) {
   m.def("allreduce_oneshot", &allreduce_oneshot);
   m.def("kv_cache_write", &kv_cache_write);
   m.def("decode_qkv_post", &decode_qkv_post);
+  m.def("gemm_decode_qkv_post", &gemm_decode_qkv_post);
   m.def("bounds_check_enabled", &bounds_check_enabled);
   m.def("gemm_set_grid_limit", &gemm_set_grid_limit);
   m.def("gemm_set_cta_pair", &gemm_set_cta_pair);

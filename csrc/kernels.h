@@ -237,7 +237,8 @@ void kv_cache_write(const void* k, const void* v, const long long* slots, void* 
 // their paged-cache rows (slot = page * page_size + offset, one per sequence). cos/sin [B, 64] fp32.
 void decode_qkv_post(const void* qkv, int B, int Hq, int Hkv, const float* cos_t, const float* sin_t,
                      const void* gamma_q, const void* gamma_k, float eps, const long long* slots, void* q_out,
-                     void* k_cache, void* v_cache, int page_size, long long n_slots, int* status, cudaStream_t s);
+                     void* k_cache, void* v_cache, int page_size, long long n_slots, int* status, cudaStream_t s,
+                     const float* partial = nullptr, int k_splits = 0);  // partial: split-K sums [k_splits, B, heads * 128] instead of qkv
 
 // True in a build with -DCOSMOS_BOUNDS_CHECK. The self-test runs the index check on (idx[i], limit[i])
 // pairs and writes 1 / 0 to ok[i]; it touches no memory through the tested indices.

@@ -360,8 +360,8 @@ __global__ void __launch_bounds__(256)
 decode_qkv_post_kernel(const bf16* __restrict__ qkv, int B, int Hq, int Hkv, const float* __restrict__ cos_t,
                        const float* __restrict__ sin_t, const bf16* __restrict__ gamma_q,
                        const bf16* __restrict__ gamma_k, float eps, const long long* __restrict__ slots,
-                       bf16* __restrict__ q_out, bf16* __restrict__ kc, bf16* __restrict__ vc, int page_size
-                       COSMOS_BC_PARAMS) {
+                       bf16* __restrict__ q_out, bf16* __restrict__ kc, bf16* __restrict__ vc, int page_size,
+                       const float* __restrict__ partial, int k_splits COSMOS_BC_PARAMS) {
   pdl_launch_dependents();
   pdl_wait();
   const int lane = threadIdx.x & 31;
@@ -369,9 +369,24 @@ decode_qkv_post_kernel(const bf16* __restrict__ qkv, int B, int Hq, int Hkv, con
   const long long w = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
   if (w >= (long long)B * heads) return;
   const int b = (int)(w / heads), h = (int)(w % heads);
-  const bf16* p = qkv + ((long long)b * heads + h) * 128;
-  const uint32_t lo = reinterpret_cast<const uint32_t*>(p)[lane];
-  const uint32_t hi = reinterpret_cast<const uint32_t*>(p + 64)[lane];
+  uint32_t lo, hi;
+  if (partial) {
+    // the projection's split-K partial sums [k_splits, B, heads * 128] (fp32) are reduced here
+    float2 a = make_float2(0.f, 0.f), c = make_float2(0.f, 0.f);
+    const long long split_stride = (long long)B * heads * 128;
+    const float* pp = partial + ((long long)b * heads + h) * 128;
+    for (int ks = 0; ks < k_splits; ++ks, pp += split_stride) {
+      const float2 x = reinterpret_cast<const float2*>(pp)[lane];
+      const float2 y = reinterpret_cast<const float2*>(pp + 64)[lane];
+      a.x += x.x; a.y += x.y; c.x += y.x; c.y += y.y;
+    }
+    lo = pack_bf16(a.x, a.y);
+    hi = pack_bf16(c.x, c.y);
+  } else {
+    const bf16* p = qkv + ((long long)b * heads + h) * 128;
+    lo = reinterpret_cast<const uint32_t*>(p)[lane];
+    hi = reinterpret_cast<const uint32_t*>(p + 64)[lane];
+  }
   bf16* dst;
   if (h < Hq) {
     dst = q_out + ((long long)b * Hq + h) * 128;
@@ -406,13 +421,14 @@ decode_qkv_post_kernel(const bf16* __restrict__ qkv, int B, int Hq, int Hkv, con
 namespace cosmos {
 void decode_qkv_post(const void* qkv, int B, int Hq, int Hkv, const float* cos_t, const float* sin_t,
                      const void* gamma_q, const void* gamma_k, float eps, const long long* slots, void* q_out,
-                     void* k_cache, void* v_cache, int page_size, long long n_slots, int* status, cudaStream_t s) {
+                     void* k_cache, void* v_cache, int page_size, long long n_slots, int* status, cudaStream_t s,
+                     const float* partial, int k_splits) {
   (void)n_slots; (void)status;  // used by the bounds-checked build
   const long long warps = (long long)B * (Hq + 2 * Hkv);
   if (warps <= 0) return;
   launch_pdl(cb::decode_qkv_post_kernel, dim3((unsigned)((warps + 7) / 8)), dim3(256), 0, s,
       (const bf16*)qkv, B, Hq, Hkv, cos_t, sin_t, (const bf16*)gamma_q, (const bf16*)gamma_k, eps, slots,
-      (bf16*)q_out, (bf16*)k_cache, (bf16*)v_cache, page_size COSMOS_BC_ARGS(n_slots, status));
+      (bf16*)q_out, (bf16*)k_cache, (bf16*)v_cache, page_size, partial, k_splits COSMOS_BC_ARGS(n_slots, status));
 }
 }  // namespace cosmos
 

@@ -812,3 +812,28 @@ def test_sample_pick_matches_the_definition(n_src):
     assert same >= 0.99, f"only {same:.3f} of the draws agree"      # a nucleus boundary within rounding may differ
     greedy = temp.cpu() == 0
     assert torch.equal(got.cpu()[greedy], want[greedy]) and (got < 90000).all()
+
+
+@pytest.mark.parametrize("b,hq,hkv,d", [(32, 32, 8, 4096), (1, 32, 8, 4096), (8, 8, 2, 1024), (300, 4, 4, 512)])
+def test_gemm_decode_qkv_post_reduces_the_split_k_partials_in_the_glue_kernel(b, hq, hkv, d):
+    """QKV projection + decode glue in two launches (partials reduced by the glue kernel) against the three-launch
+    form (GEMM, split-K reduction, glue) and, through it, the fp32 definition."""
+    torch.manual_seed(b)
+    page, n_pages = 16, 2 * ((b + 15) // 16) + 1
+    h = _rand(b, d)
+    w = _rand((hq + 2 * hkv) * 128, d, scale=d ** -0.5)
+    ang = torch.rand(b, 64, device=DEV) * 6.0
+    cos, sin = ang.cos().contiguous(), ang.sin().contiguous()
+    gq, gk = (1 + 0.1 * torch.randn(128, device=DEV)).bfloat16(), (1 + 0.1 * torch.randn(128, device=DEV)).bfloat16()
+    slots = (torch.randperm(n_pages * page, device=DEV)[:b]).long()
+    kc, vc = _rand(n_pages, hkv, page, 128), _rand(n_pages, hkv, page, 128)
+    kc2, vc2 = kc.clone(), vc.clone()
+    q = ops.gemm_decode_qkv_post(h, w, hq, cos, sin, gq, gk, 1e-6, slots, kc, vc)
+    qkv = ops.gemm(h, w).view(b, hq + 2 * hkv, 128)
+    q2 = ops.decode_qkv_post(qkv, hq, cos, sin, gq, gk, 1e-6, slots, kc2, vc2)
+    torch.cuda.synchronize()
+    _close(q, q2, 1e-2, 1e-2, "q")
+    _close(kc, kc2, 1e-2, 1e-2, "k cache")
+    _close(vc, vc2, 1e-2, 1e-2, "v cache")
+    f = (h.float() @ w.float().t()).view(b, hq + 2 * hkv, 128)
+    _close(q, ref.mrope(f[:, :hq], cos, sin, gq.float(), 1e-6), 4e-2, 4e-2, "q vs fp32")
