@@ -260,6 +260,25 @@ def main():
                "ms": round(ms, 2)}
         out.append(rec)
         print(json.dumps(rec), flush=True)
+        # tokenizer encode of the same clip: implicit-GEMM encoder, and the PyTorch modules (cuDNN) with --cublas
+        from cosmos_b200.models.vae_cuda import CLEncoder
+        enc = CLEncoder(vae)
+        video = torch.rand(1, 3, 1 + 4 * (t_lat - 1), 8 * h_lat, 8 * w_lat, device=dev).bfloat16() * 2 - 1
+        lat = None
+
+        def run_enc():
+            nonlocal lat
+            lat = enc.encode(video)
+
+        ms = timeit(run_enc, max(1, min(args.iters, 3)), flush)
+        rec = {"kernel": "vae_encode_cl", "frames": list(video.shape[2:]), "latent": list(lat.shape[2:]), "ms": round(ms, 2)}
+        if args.cublas:
+            def run_ref():
+                with torch.no_grad():
+                    vae.encode(video, chunk_frames=4)
+            rec["pytorch_cudnn_ms"] = round(timeit(run_ref, 1, flush), 2)
+        out.append(rec)
+        print(json.dumps(rec), flush=True)
     torch.cuda.synchronize()
     ops.check_status()
     return out

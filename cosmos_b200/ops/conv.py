@@ -1,8 +1,8 @@
 """PyTorch definitions of the video tokenizer's ops: temporally-causal 3D convolution and the channel
-RMS-norm + SiLU. They run the encoder (strided convolutions, on cuDNN when the tensors are on a GPU), every
-tokenizer whose channel widths are not multiples of 64, and the CPU path, and they are the oracle of the
-channels-last decoder. The decoder's hot path does not go through this module: `models/vae_cuda.py` runs it on the
-implicit-GEMM tcgen05 kernel (`torch.ops.cosmos_b200.conv3d_cl`, `rmsnorm_silu`, `upsample_cl`, `conv_out_rgb`)."""
+RMS-norm + SiLU. They run training through the tokenizer, every tokenizer whose channel widths are not multiples
+of 64, and the CPU path, and they are the oracle of the channels-last encoder and decoder. The inference hot path
+does not go through this module: `models/vae_cuda.py` runs encoder and decoder on the implicit-GEMM tcgen05 kernel
+(`torch.ops.cosmos_b200.conv3d_cl`, `rmsnorm_silu`, `upsample_cl`, `conv_out_rgb`)."""
 from __future__ import annotations
 
 from typing import Sequence, Tuple

@@ -289,8 +289,7 @@ class Cosmos3OmniPipeline:
             if fr.shape[0] < n_pix:
                 fr = np.concatenate([fr, np.repeat(fr[-1:], n_pix - fr.shape[0], 0)])
             x = CausalVideoVAE.from_uint8(torch.from_numpy(np.array(fr))[None].to(self.device)).to(vdt)
-            with torch.no_grad():
-                z = self.vae.encode(x, chunk_frames=4 if n_pix > 1 else None).float()
+            z = self._encode_video(x)
             ztok = patchify(z, cfg)[0]
             for li in condition_frame_indexes:
                 a, b = li * tokens_per_frame, (li + 1) * tokens_per_frame
@@ -311,8 +310,7 @@ class Cosmos3OmniPipeline:
             if cf.shape[0] < n_pix:
                 cf = np.concatenate([cf, np.repeat(cf[-1:], n_pix - cf.shape[0], 0)])
             cx = CausalVideoVAE.from_uint8(torch.from_numpy(np.array(cf))[None].to(self.device)).to(vdt)
-            with torch.no_grad():
-                cz = self.vae.encode(cx, chunk_frames=4 if n_pix > 1 else None).float()
+            cz = self._encode_video(cx)
             ctok = patchify(cz, cfg)                       # [1, all video tokens, patch_dim]
             a = st.shard_start
             st.control_tokens = ctok[:, a:a + st.n_video].contiguous()   # this rank's context-parallel shard
@@ -372,6 +370,26 @@ class Cosmos3OmniPipeline:
             self._cl = CLDecoder(self.vae)
             return self._cl
         return None
+
+    def _encode_video(self, x: torch.Tensor) -> torch.Tensor:
+        """[1, 3, T, H, W] in [-1, 1] -> latent mean [1, C, 1 + (T - 1) / 4, H / 8, W / 8] (fp32). On CUDA in bf16 with
+        64-multiple widths the implicit-GEMM encoder (`models/vae_cuda.py::CLEncoder`), else the PyTorch modules."""
+        n_pix = x.shape[2]
+        enc = getattr(self, "_cl_enc", None)
+        if enc is None:
+            p0 = next(self.vae.parameters())
+            convs = [self.vae.enc_in] + [d.conv for d in self.vae.enc_down]
+            ok = (p0.is_cuda and p0.dtype == torch.bfloat16 and ops.get_backend() != "library" and
+                  all(m.weight.shape[0] % 64 == 0 for m in convs) and ops.load_extension())
+            if ok:
+                from .models.vae_cuda import CLEncoder
+                enc = self._cl_enc = CLEncoder(self.vae)
+            else:
+                self._cl_enc = enc = False
+        if enc and x.shape[3] % 8 == 0 and x.shape[4] % 8 == 0:
+            return enc.encode(x, chunk_frames=8)
+        with torch.no_grad():
+            return self.vae.encode(x, chunk_frames=4 if n_pix > 1 else None).float()
 
     def gather_tokens(self, tokens: torch.Tensor, st: GenState) -> torch.Tensor:
         """All-gathers context-parallel token shards into the full sequence (no-op without cp)."""

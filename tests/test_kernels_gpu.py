@@ -837,3 +837,24 @@ def test_gemm_decode_qkv_post_reduces_the_split_k_partials_in_the_glue_kernel(b,
     _close(vc, vc2, 1e-2, 1e-2, "v cache")
     f = (h.float() @ w.float().t()).view(b, hq + 2 * hkv, 128)
     _close(q, ref.mrope(f[:, :hq], cos, sin, gq.float(), 1e-6), 4e-2, 4e-2, "q vs fp32")
+
+
+def test_vae_channels_last_encoder_matches_pytorch():
+    """Implicit-GEMM encoder (strided convolutions as stride-1 + even positions, 1x1 skips as GEMMs, chunked in time)
+    against the fp32 PyTorch modules in one pass."""
+    from cosmos_b200.models.vae import CausalVideoVAE
+    from cosmos_b200.models.vae_cuda import CLEncoder
+    torch.manual_seed(21)
+    vae = CausalVideoVAE(16, (64, 128, 256, 256)).to(DEV).float().eval()
+    video = torch.rand(1, 3, 17, 48, 64, device=DEV) * 2 - 1
+    with torch.no_grad():
+        want = vae.encode(video)
+    enc = CLEncoder(vae)
+    got = enc.encode(video, chunk_frames=8)
+    assert got.shape == want.shape == (1, 16, 5, 6, 8)
+    err = (got - want).abs()
+    scale = want.abs().mean().item()
+    assert err.mean().item() < 0.03 * scale and err.max().item() < 0.25 * want.abs().max().item(), \
+        (err.mean().item(), err.max().item(), scale)
+    other = enc.encode(video, chunk_frames=4)
+    assert (other - got).abs().max().item() <= 0.02 * want.abs().max().item()   # chunking does not change the result
