@@ -82,10 +82,14 @@ constexpr int BWD_TILES = 2 + 2 * BWD_NST;
 constexpr int BB_FIXED = 0;                 // stationary tiles landed
 constexpr int BB_FULL = 1;                  // + s
 constexpr int BB_EMPTY = 1 + BWD_NST;       // + s
-constexpr int BB_S = 1 + 2 * BWD_NST;       // scores ready (tcgen05.commit)
-constexpr int BB_P = 2 + 2 * BWD_NST;       // P / dS written (128 arrivals)
-constexpr int BB_DONE = 3 + 2 * BWD_NST;    // accumulators final
-constexpr int BB_COUNT = 4 + 2 * BWD_NST;
+// The score tile is handled as two 64-column halves, one per element-wise warpgroup, each with its own pair of
+// barriers: while a warpgroup turns its half into P / dS the tensor pipe runs the other half's products, and a
+// half's next scores are issued as soon as the gradient products that read its P / dS have been issued.
+constexpr int BB_S = 1 + 2 * BWD_NST;       // + half: scores of that half ready (tcgen05.commit)
+constexpr int BB_P = 3 + 2 * BWD_NST;       // + half: P / dS of that half written (128 arrivals)
+constexpr int BB_DONE = 5 + 2 * BWD_NST;    // accumulators final
+constexpr int BB_COUNT = 6 + 2 * BWD_NST;
+constexpr uint32_t HALF_ROWS_DESC = (64 * 128) >> 4;  // descriptor offset of rows 64.. of a K-major tile
 
 __device__ __forceinline__ BwdSmem bwd_smem_setup(uint8_t* raw) {
   BwdSmem s;
@@ -102,7 +106,9 @@ __device__ __forceinline__ void bwd_init_barriers(const BwdSmem& sm, volatile in
     mbar_init(sm.bar + 8u * (BB_EMPTY + s), 1);
   }
   mbar_init(sm.bar + 8u * BB_S, 1);
-  mbar_init(sm.bar + 8u * BB_P, 256);
+  mbar_init(sm.bar + 8u * (BB_S + 1), 1);
+  mbar_init(sm.bar + 8u * BB_P, 128);
+  mbar_init(sm.bar + 8u * (BB_P + 1), 128);
   mbar_init(sm.bar + 8u * BB_DONE, 1);
   *abort_flag = 0;
   fence_barrier_init();
@@ -222,48 +228,77 @@ flash_attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid
     auto wait_all = [&](uint32_t bar, uint32_t phase) {
       return __all_sync(0xffffffffu, mbar_wait(bar, phase, abort_flag, p.status, ST_TIMEOUT_MMA)) != 0;
     };
-    constexpr uint32_t idesc_ss = make_idesc_bf16(BT, BT, 0, 0);
+    constexpr uint32_t idesc_ss = make_idesc_bf16(BT, 64, 0, 0);   // one 64-column half of the score tile
     constexpr uint32_t idesc_ts = make_idesc_bf16(BT, 128, 0, 1);
     const uint64_t k_desc = make_smem_desc_sw128(sm.fixed(0), 16, 1024);
     const uint64_t v_desc = make_smem_desc_sw128(sm.fixed(1), 16, 1024);
+    // S^T and dP^T of query columns [64 h, 64 h + 64) of the tile pair in stage st
+    auto scores = [&](int st, int h) {
+      const uint64_t q_k = make_smem_desc_sw128(sm.stream(st, 0), 16, 1024) + uint64_t(h * HALF_ROWS_DESC);
+      const uint64_t do_k = make_smem_desc_sw128(sm.stream(st, 1), 16, 1024) + uint64_t(h * HALF_ROWS_DESC);
+#pragma unroll
+      for (int kk = 0; kk < 8; ++kk) {
+        const uint32_t off = (kk >> 2) * (BHALF_BYTES >> 4) + 2 * (kk & 3);
+        mma_ss(T_ST + 64 * h, k_desc + off, q_k + off, idesc_ss, kk > 0 ? 1u : 0u);
+      }
+#pragma unroll
+      for (int kk = 0; kk < 8; ++kk) {
+        const uint32_t off = (kk >> 2) * (BHALF_BYTES >> 4) + 2 * (kk & 3);
+        mma_ss(T_DPT + 64 * h, v_desc + off, do_k + off, idesc_ss, kk > 0 ? 1u : 0u);
+      }
+      tc_commit(sm.bar + 8u * (BB_S + h));
+    };
+    // dV += P^T dO and dK += dS^T Q over the 64 queries of half h (bf16 P^T / dS^T of those columns sit at
+    // 32-bit columns [64 h, 64 h + 32) of the score buffers)
+    auto grads = [&](int st, int h, bool first) {
+      const uint64_t q_mn = make_smem_desc_sw128(sm.stream(st, 0), BHALF_BYTES, 1024);
+      const uint64_t do_mn = make_smem_desc_sw128(sm.stream(st, 1), BHALF_BYTES, 1024);
+#pragma unroll
+      for (int k4 = 0; k4 < 4; ++k4) {
+        const int kk = 4 * h + k4;
+        mma_ts(T_DV, T_ST + h * 64 + k4 * 8, do_mn + uint64_t(kk * (2048 >> 4)), idesc_ts, (first && k4 == 0) ? 0u : 1u);
+      }
+#pragma unroll
+      for (int k4 = 0; k4 < 4; ++k4) {
+        const int kk = 4 * h + k4;
+        mma_ts(T_DK, T_DPT + h * 64 + k4 * 8, q_mn + uint64_t(kk * (2048 >> 4)), idesc_ts, (first && k4 == 0) ? 0u : 1u);
+      }
+    };
     bool ok = n_it == 0 || wait_all(sm.bar + 8u * BB_FIXED, 0);
+    if (ok && n_it > 0) {
+      ok = wait_all(sm.bar + 8u * BB_FULL, 0);
+      if (ok) {
+        tc_fence_after();
+        if (issuer) {
+          scores(0, 0);
+          scores(0, 1);
+        }
+        __syncwarp();
+      }
+    }
     for (int it = 0; it < n_it && ok; ++it) {
       const int s = it % BWD_NST;
-      ok = wait_all(sm.bar + 8u * (BB_FULL + s), (it / BWD_NST) & 1);
-      if (!ok) break;
-      tc_fence_after();
-      const uint64_t q_k = make_smem_desc_sw128(sm.stream(s, 0), 16, 1024);
-      const uint64_t do_k = make_smem_desc_sw128(sm.stream(s, 1), 16, 1024);
-      const uint64_t q_mn = make_smem_desc_sw128(sm.stream(s, 0), BHALF_BYTES, 1024);
-      const uint64_t do_mn = make_smem_desc_sw128(sm.stream(s, 1), BHALF_BYTES, 1024);
-      if (issuer) {
-#pragma unroll
-        for (int kk = 0; kk < 8; ++kk) {
-          const uint32_t off = (kk >> 2) * (BHALF_BYTES >> 4) + 2 * (kk & 3);
-          mma_ss(T_ST, k_desc + off, q_k + off, idesc_ss, kk > 0 ? 1u : 0u);
-        }
-#pragma unroll
-        for (int kk = 0; kk < 8; ++kk) {
-          const uint32_t off = (kk >> 2) * (BHALF_BYTES >> 4) + 2 * (kk & 3);
-          mma_ss(T_DPT, v_desc + off, do_k + off, idesc_ss, kk > 0 ? 1u : 0u);
-        }
-        tc_commit(sm.bar + 8u * BB_S);
+      const bool more = it + 1 < n_it;
+      const int sn = (it + 1) % BWD_NST;
+      if (more) {
+        ok = wait_all(sm.bar + 8u * (BB_FULL + sn), ((it + 1) / BWD_NST) & 1);
+        if (!ok) break;
       }
-      __syncwarp();
       ok = wait_all(sm.bar + 8u * BB_P, it & 1);
       if (!ok) break;
       tc_fence_after();
       if (issuer) {
-        // bf16 P^T / dS^T of query columns [64 w, 64 w + 64) sit at 32-bit columns [64 w, 64 w + 32)
-#pragma unroll
-        for (int kk = 0; kk < 8; ++kk)
-          mma_ts(T_DV, T_ST + (kk >> 2) * 64 + (kk & 3) * 8, do_mn + uint64_t(kk * (2048 >> 4)), idesc_ts,
-                 (it > 0 || kk > 0) ? 1u : 0u);
-#pragma unroll
-        for (int kk = 0; kk < 8; ++kk)
-          mma_ts(T_DK, T_DPT + (kk >> 2) * 64 + (kk & 3) * 8, q_mn + uint64_t(kk * (2048 >> 4)), idesc_ts,
-                 (it > 0 || kk > 0) ? 1u : 0u);
+        grads(s, 0, it == 0);
+        if (more) scores(sn, 0);   // in issue order behind the products that read this half's P^T / dS^T
+      }
+      __syncwarp();
+      ok = wait_all(sm.bar + 8u * (BB_P + 1), it & 1);
+      if (!ok) break;
+      tc_fence_after();
+      if (issuer) {
+        grads(s, 1, false);
         tc_commit(sm.bar + 8u * (BB_EMPTY + s));
+        if (more) scores(sn, 1);
       }
       __syncwarp();
     }
@@ -281,14 +316,17 @@ flash_attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid
       const int head = kvh * p.group + it / n_qt;
       const int q0 = (i0 + it % n_qt) * BT;
       const int buf = it & 1;
-      if (wg == 0) {
-        const int qi = q0 + r;
+      if (r < 64) {
+        // log-sum-exp and D of this warpgroup's 64 query columns (double-buffered; the warpgroup's own barrier
+        // of the next iteration separates the reads of this buffer from its rewrite two iterations later)
+        const int qc = 64 * wg + r;
+        const int qi = q0 + qc;
         const long long off = ((long long)batch * p.Hq + head) * p.Sq + qi;
-        lse_s[buf * BT + r] = qi < p.Sq ? p.lse[off] * 1.4426950408889634f : INFINITY;
-        dlt_s[buf * BT + r] = qi < p.Sq ? p.delta[off] : 0.f;
+        lse_s[buf * BT + qc] = qi < p.Sq ? p.lse[off] * 1.4426950408889634f : INFINITY;
+        dlt_s[buf * BT + qc] = qi < p.Sq ? p.delta[off] : 0.f;
       }
-      named_bar_sync(1, 256);
-      if (!mbar_wait(sm.bar + 8u * BB_S, it & 1, abort_flag, p.status, ST_TIMEOUT_SOFTMAX)) {
+      named_bar_sync(1 + wg, 128);
+      if (!mbar_wait(sm.bar + 8u * (BB_S + wg), it & 1, abort_flag, p.status, ST_TIMEOUT_SOFTMAX)) {
         ok = false;
         break;
       }
@@ -330,7 +368,7 @@ flash_attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid
       }
       tmem_wait_st();
       tc_fence_before();
-      mbar_arrive(sm.bar + 8u * BB_P);
+      mbar_arrive(sm.bar + 8u * (BB_P + wg));
     }
     const bool row_ok = kv < p.Skv;
     bf16* dk_row = p.dK + (((long long)batch * p.Skv + kv) * p.Hkv + kvh) * 128;
@@ -426,42 +464,70 @@ flash_attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_c
     auto wait_all = [&](uint32_t bar, uint32_t phase) {
       return __all_sync(0xffffffffu, mbar_wait(bar, phase, abort_flag, p.status, ST_TIMEOUT_MMA)) != 0;
     };
-    constexpr uint32_t idesc_ss = make_idesc_bf16(BT, BT, 0, 0);
+    constexpr uint32_t idesc_ss = make_idesc_bf16(BT, 64, 0, 0);   // one 64-key half of the score tile
     constexpr uint32_t idesc_ts = make_idesc_bf16(BT, 128, 0, 1);
     const uint64_t q_desc = make_smem_desc_sw128(sm.fixed(0), 16, 1024);
     const uint64_t do_desc = make_smem_desc_sw128(sm.fixed(1), 16, 1024);
+    // S and dP against keys [64 h, 64 h + 64) of the K/V tiles in stage st
+    auto scores = [&](int st, int h) {
+      const uint64_t k_k = make_smem_desc_sw128(sm.stream(st, 0), 16, 1024) + uint64_t(h * HALF_ROWS_DESC);
+      const uint64_t v_k = make_smem_desc_sw128(sm.stream(st, 1), 16, 1024) + uint64_t(h * HALF_ROWS_DESC);
+#pragma unroll
+      for (int kk = 0; kk < 8; ++kk) {
+        const uint32_t off = (kk >> 2) * (BHALF_BYTES >> 4) + 2 * (kk & 3);
+        mma_ss(T_S + 64 * h, q_desc + off, k_k + off, idesc_ss, kk > 0 ? 1u : 0u);
+      }
+#pragma unroll
+      for (int kk = 0; kk < 8; ++kk) {
+        const uint32_t off = (kk >> 2) * (BHALF_BYTES >> 4) + 2 * (kk & 3);
+        mma_ss(T_DP + 64 * h, do_desc + off, v_k + off, idesc_ss, kk > 0 ? 1u : 0u);
+      }
+      tc_commit(sm.bar + 8u * (BB_S + h));
+    };
+    // dQ += dS K over the 64 keys of half h
+    auto grads = [&](int st, int h, bool first) {
+      const uint64_t k_mn = make_smem_desc_sw128(sm.stream(st, 0), BHALF_BYTES, 1024);
+#pragma unroll
+      for (int k4 = 0; k4 < 4; ++k4) {
+        const int kk = 4 * h + k4;
+        mma_ts(T_DQ, T_S + h * 64 + k4 * 8, k_mn + uint64_t(kk * (2048 >> 4)), idesc_ts, (first && k4 == 0) ? 0u : 1u);
+      }
+    };
     bool ok = wait_all(sm.bar + 8u * BB_FIXED, 0);
+    if (ok) {
+      ok = wait_all(sm.bar + 8u * BB_FULL, 0);
+      if (ok) {
+        tc_fence_after();
+        if (issuer) {
+          scores(0, 0);
+          scores(0, 1);
+        }
+        __syncwarp();
+      }
+    }
     for (int j = 0; j < n_blocks && ok; ++j) {
       const int s = j % BWD_NST;
-      ok = wait_all(sm.bar + 8u * (BB_FULL + s), (j / BWD_NST) & 1);
-      if (!ok) break;
-      tc_fence_after();
-      const uint64_t k_k = make_smem_desc_sw128(sm.stream(s, 0), 16, 1024);
-      const uint64_t v_k = make_smem_desc_sw128(sm.stream(s, 1), 16, 1024);
-      const uint64_t k_mn = make_smem_desc_sw128(sm.stream(s, 0), BHALF_BYTES, 1024);
-      if (issuer) {
-#pragma unroll
-        for (int kk = 0; kk < 8; ++kk) {
-          const uint32_t off = (kk >> 2) * (BHALF_BYTES >> 4) + 2 * (kk & 3);
-          mma_ss(T_S, q_desc + off, k_k + off, idesc_ss, kk > 0 ? 1u : 0u);
-        }
-#pragma unroll
-        for (int kk = 0; kk < 8; ++kk) {
-          const uint32_t off = (kk >> 2) * (BHALF_BYTES >> 4) + 2 * (kk & 3);
-          mma_ss(T_DP, do_desc + off, v_k + off, idesc_ss, kk > 0 ? 1u : 0u);
-        }
-        tc_commit(sm.bar + 8u * BB_S);
+      const bool more = j + 1 < n_blocks;
+      const int sn = (j + 1) % BWD_NST;
+      if (more) {
+        ok = wait_all(sm.bar + 8u * (BB_FULL + sn), ((j + 1) / BWD_NST) & 1);
+        if (!ok) break;
       }
-      __syncwarp();
       ok = wait_all(sm.bar + 8u * BB_P, j & 1);
       if (!ok) break;
       tc_fence_after();
       if (issuer) {
-#pragma unroll
-        for (int kk = 0; kk < 8; ++kk)
-          mma_ts(T_DQ, T_S + (kk >> 2) * 64 + (kk & 3) * 8, k_mn + uint64_t(kk * (2048 >> 4)), idesc_ts,
-                 (j > 0 || kk > 0) ? 1u : 0u);
+        grads(s, 0, j == 0);
+        if (more) scores(sn, 0);
+      }
+      __syncwarp();
+      ok = wait_all(sm.bar + 8u * (BB_P + 1), j & 1);
+      if (!ok) break;
+      tc_fence_after();
+      if (issuer) {
+        grads(s, 1, false);
         tc_commit(sm.bar + 8u * (BB_EMPTY + s));
+        if (more) scores(sn, 1);
       }
       __syncwarp();
     }
@@ -480,7 +546,7 @@ flash_attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_c
     const float dlt = row_ok ? p.delta[off] : 0.f;
     bool ok = true;
     for (int j = 0; j < n_blocks; ++j) {
-      if (!mbar_wait(sm.bar + 8u * BB_S, j & 1, abort_flag, p.status, ST_TIMEOUT_SOFTMAX)) {
+      if (!mbar_wait(sm.bar + 8u * (BB_S + wg), j & 1, abort_flag, p.status, ST_TIMEOUT_SOFTMAX)) {
         ok = false;
         break;
       }
@@ -515,7 +581,7 @@ flash_attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_c
       }
       tmem_wait_st();
       tc_fence_before();
-      mbar_arrive(sm.bar + 8u * BB_P);
+      mbar_arrive(sm.bar + 8u * (BB_P + wg));
     }
     if (ok) ok = mbar_wait(sm.bar + 8u * BB_DONE, 0, abort_flag, p.status, ST_TIMEOUT_SOFTMAX);
     if (ok) {
