@@ -310,6 +310,7 @@ allreduce_norm_kernel(const long long* bufs, const bf16* mc, bf16* own, const lo
     for (int m = blockIdx.x; m < M; m += gridDim.x) {
       for (int vi = tid; vi < nvec; vi += 256) {
         float a[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+#pragma unroll 4
         for (int ks = 0; ks < k_splits; ++ks) {
           const float4* src = reinterpret_cast<const float4*>(partial + ((long long)ks * M + m) * N + vi * 8);
           const float4 x = src[0], y = src[1];

@@ -703,25 +703,39 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
 
 // Second pass of split-K fused with the residual add and the RMS-norm that follow an output projection in a
 // decode step: x = R + sum_ks partial[ks]; X[m] = x; H[m] = x * rsqrt(mean(x^2) + eps) * gamma. One CTA per row.
-__global__ void __launch_bounds__(256)
+constexpr int RN_THREADS = 1024;
+// One CTA of 1024 threads per row: a row of 4096 columns is one float4 per thread and split, and the loads of four
+// splits are in flight together (with 256 threads and one split at a time the kernel took 13 us for 147 KB).
+__global__ void __launch_bounds__(RN_THREADS)
 splitk_reduce_rmsnorm_kernel(const float* __restrict__ partial, int k_splits, int M, int N, const bf16* __restrict__ R,
                              long long ldr, const bf16* __restrict__ gamma, float eps, bf16* __restrict__ X,
                              bf16* __restrict__ H, long long ldc) {
-  __shared__ float red[8];
+  __shared__ float red[RN_THREADS / 32];
   pdl_launch_dependents();
   pdl_wait();
   const int m = blockIdx.x, tid = threadIdx.x;
   const int nvec = N >> 2;
-  constexpr int MAXJ = 8;  // N <= 8192
+  constexpr int MAXJ = 2;  // N <= 8192
   float4 v[MAXJ];
   float ss = 0.f;
+  const long long split_stride = (long long)M * N;
 #pragma unroll
   for (int j = 0; j < MAXJ; ++j) {
-    const int vi = tid + j * 256;
+    const int vi = tid + j * RN_THREADS;
     if (vi < nvec) {
       float4 a = make_float4(0, 0, 0, 0);
-      for (int ks = 0; ks < k_splits; ++ks) {
-        const float4 x = *reinterpret_cast<const float4*>(partial + ((long long)ks * M + m) * N + vi * 4);
+      const float* src = partial + (long long)m * N + vi * 4;
+      int ks = 0;
+      for (; ks + 4 <= k_splits; ks += 4) {
+        const float4 x0 = *reinterpret_cast<const float4*>(src + (ks + 0) * split_stride);
+        const float4 x1 = *reinterpret_cast<const float4*>(src + (ks + 1) * split_stride);
+        const float4 x2 = *reinterpret_cast<const float4*>(src + (ks + 2) * split_stride);
+        const float4 x3 = *reinterpret_cast<const float4*>(src + (ks + 3) * split_stride);
+        a.x += (x0.x + x1.x) + (x2.x + x3.x); a.y += (x0.y + x1.y) + (x2.y + x3.y);
+        a.z += (x0.z + x1.z) + (x2.z + x3.z); a.w += (x0.w + x1.w) + (x2.w + x3.w);
+      }
+      for (; ks < k_splits; ++ks) {
+        const float4 x = *reinterpret_cast<const float4*>(src + ks * split_stride);
         a.x += x.x; a.y += x.y; a.z += x.z; a.w += x.w;
       }
       if (R) {
@@ -738,11 +752,11 @@ splitk_reduce_rmsnorm_kernel(const float* __restrict__ partial, int k_splits, in
   __syncthreads();
   float tot = 0.f;
 #pragma unroll
-  for (int w = 0; w < 8; ++w) tot += red[w];
+  for (int w = 0; w < RN_THREADS / 32; ++w) tot += red[w];
   const float rinv = rsqrtf(tot / N + eps);
 #pragma unroll
   for (int j = 0; j < MAXJ; ++j) {
-    const int vi = tid + j * 256;
+    const int vi = tid + j * RN_THREADS;
     if (vi < nvec) {
       const float4 a = v[j];
       uint2 xo, ho;
@@ -775,6 +789,7 @@ splitk_reduce_kernel(const float* __restrict__ partial, int k_splits, int M, int
     const int m = (int)(i / vec_per_row);
     const int n = (int)(i - (long long)m * vec_per_row) * 4;
     float4 a = make_float4(0, 0, 0, 0), u = make_float4(0, 0, 0, 0);
+#pragma unroll 4
     for (int ks = 0; ks < k_splits; ++ks) {
       const float* row = partial + ((long long)ks * M + m) * N;
       const float4 x = *reinterpret_cast<const float4*>(row + n);
@@ -1068,11 +1083,27 @@ int gemm_pick_k_splits(int M, int N, int K, int epi) {
   const int tiles = m_tiles * n_tiles;
   const int k_blocks = (K + cb::BK - 1) / cb::BK;
   const int sms = sm_count();
-  if (tiles * 2 > sms || k_blocks < 8 || N % 8 != 0) return 1;
-  int ks = sms / tiles;                      // one wave: tiles * ks <= number of SMs
-  if (ks > k_blocks / 4) ks = k_blocks / 4;  // at least 4 k-blocks (256 columns of K) per split
-  if (ks > 32) ks = 32;
-  return ks < 2 ? 1 : ks;
+  if (tiles >= sms || k_blocks < 8 || N % 8 != 0) return 1;
+  if (tiles * 2 <= sms) {
+    int ks = sms / tiles;                      // one wave: tiles * ks <= number of SMs
+    if (ks > k_blocks / 4) ks = k_blocks / 4;  // at least 4 k-blocks (256 columns of K) per split
+    if (ks > 32) ks = 32;
+    return ks < 2 ? 1 : ks;
+  }
+  // Between half a wave and a full one (the 96 tiles of a 24576-wide SwiGLU projection leave 52 SMs idle and took
+  // 59 us for 201 MB of weights): split so that the work items fill whole rounds of the persistent CTAs. Cost of a
+  // choice = rounds x k-blocks per item; the smallest split count within 3 % of the best wins.
+  int best = 1;
+  double best_cost = (double)k_blocks;
+  for (int ks = 2; ks <= 8 && ks <= k_blocks / 4; ++ks) {
+    const int rounds = (tiles * ks + sms - 1) / sms;
+    const double cost = rounds * (double)((k_blocks + ks - 1) / ks);
+    if (cost < 0.97 * best_cost) {
+      best = ks;
+      best_cost = cost;
+    }
+  }
+  return best;
 }
 
 // One launch for one or two problems that share the epilogue kind.
@@ -1135,7 +1166,7 @@ void gemm_bf16(const GemmArgs& a, cudaStream_t stream) {
   if (a.norm_out) {
     if (a.epi != EPI_PLAIN || a.N > 8192 || a.N % 4 != 0 || a.ldc % 4 != 0 || (a.R && a.ldr % 4 != 0))
       throw std::runtime_error("gemm_bf16: the fused reduce + RMS-norm pass needs a plain epilogue and N <= 8192");
-    launch_pdl(cb::splitk_reduce_rmsnorm_kernel, dim3(a.M), dim3(256), 0, stream,
+    launch_pdl(cb::splitk_reduce_rmsnorm_kernel, dim3(a.M), dim3(cb::RN_THREADS), 0, stream,
         a.partial, ks, a.M, a.N, reinterpret_cast<const bf16*>(a.R), a.ldr, reinterpret_cast<const bf16*>(a.norm_gamma),
         a.norm_eps, reinterpret_cast<bf16*>(a.C), reinterpret_cast<bf16*>(a.norm_out), a.ldc);
     return;
