@@ -112,6 +112,7 @@ def main():
     ap.add_argument("--sustained", type=float, default=0.0, help="seconds of back-to-back calls per case (0 = burst timing)")
     ap.add_argument("--gemm-pair", type=int, default=None, help="0 / 1: single-CTA or CTA-pair GEMM tiles")
     ap.add_argument("--attn-pair", type=int, default=None, help="0 / 1: single-CTA or CTA-pair attention tiles")
+    ap.add_argument("--page", type=int, default=16, help="tokens per KV-cache page in the paged decode case")
     ap.add_argument("--gemm-debug", type=int, default=0, help="timing experiment bits of the GEMM (1: all tiles load tile (0,0); 2: no loads)")
     args = ap.parse_args()
     ops.load_extension()
@@ -224,7 +225,7 @@ def main():
         print(json.dumps(rec), flush=True)
     if "paged" in what:
         # decode attention over a paged cache: batch 32, 32 q heads / 8 kv heads, 8448 cached tokens
-        b, hq, hkv, ctx, page = (8, 32, 8, 2048, 16) if args.small else (32, 32, 8, 8448, 16)
+        b, hq, hkv, ctx, page = (8, 32, 8, 2048, args.page) if args.small else (32, 32, 8, 8448, args.page)
         n_pages = b * ((ctx + page - 1) // page)
         kc = torch.randn(n_pages, hkv, page, 128, device=dev).bfloat16()
         vc = torch.randn(n_pages, hkv, page, 128, device=dev).bfloat16()
@@ -235,7 +236,7 @@ def main():
             ms = timeit(lambda: ops.paged_decode(q, kc, vc, table, lens, 128 ** -0.5, max_len=ctx, impl=impl),
                         args.iters, flush)
             gbs = 2.0 * b * ctx * hkv * 128 * 2 / ms / 1e6
-            rec = {"kernel": name, "shape": [b, hq, hkv, ctx], "ms": round(ms, 4), "gbs": round(gbs, 1),
+            rec = {"kernel": name, "shape": [b, hq, hkv, ctx], "page": page, "ms": round(ms, 4), "gbs": round(gbs, 1),
                    f"frac_of_{src}_hbm": round(gbs / bw_peak, 3)}
             out.append(rec)
             print(json.dumps(rec), flush=True)

@@ -33,9 +33,11 @@ from .paged import PagedKVCache
 
 
 class TPDecoder:
-    def __init__(self, cfg: MoTConfig, tp: int, rank: int, group, device, page_size: int = 16,
+    def __init__(self, cfg: MoTConfig, tp: int, rank: int, group, device, page_size: int = 32,
                  max_batch: int = 32, max_len: int = 9000, seed: int = 0, fused: bool = True, dtype=torch.bfloat16):
         assert cfg.n_heads % tp == 0 and cfg.n_kv_heads % tp == 0 and cfg.ffn_dim % tp == 0
+        # page_size 32: the decode-attention kernel fetches one TMA box per page, tensor and 64-column half; measured
+        # 0.73 of the copy bandwidth with 16-token pages (2 KB boxes), 0.86 with 32, 0.89 with 128
         self.cfg, self.tp, self.rank, self.group = cfg, tp, rank, group
         self.device = torch.device(device)
         self.hq, self.hk, self.hd = cfg.n_heads // tp, cfg.n_kv_heads // tp, cfg.head_dim

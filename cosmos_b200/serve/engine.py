@@ -62,7 +62,7 @@ class Request:
 
 
 class BatchEngine:
-    def __init__(self, model, max_batch: int = 8, max_len: int = 4096, page_size: int = 16, device=None,
+    def __init__(self, model, max_batch: int = 8, max_len: int = 4096, page_size: int = 32, device=None,
                  dtype=None, use_graph: Optional[bool] = None, group=None):
         """`group`: tensor-parallel process group (None = one rank). Every rank of the group builds the engine on
         the same model weights; rank 0 of the group takes the requests (`submit`), the others call `follow()`."""
