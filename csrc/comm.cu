@@ -117,40 +117,79 @@ allreduce_oneshot_kernel(const long long* bufs, const long long* pads, bf16* out
 // and the bf16 parameter shard is rewritten from the fp32 master. grads[r] are peer pointers
 // (plain P2P loads). With sq_out != null the kernel only accumulates sum(g^2) (pre-pass for
 // global-norm clipping) and performs no update.
+struct AdamW {
+  float grad_scale, lr, b1, b2, eps, wd, bc1, bc2;
+  __device__ __forceinline__ void step(float g, float& m, float& v, float& w) const {
+    g *= grad_scale;
+    m = b1 * m + (1.f - b1) * g;
+    v = b2 * v + (1.f - b2) * g * g;
+    w -= lr * ((m / bc1) / (sqrtf(v / bc2) + eps) + wd * w);
+  }
+};
+
+// Four elements per thread and trip (8-byte gradient loads from every peer, 16-byte loads and stores of the fp32
+// state) when the shard allows it; `vec` says so (offset, length and base addresses checked by the host).
 __global__ void __launch_bounds__(256)
 rs_adamw_kernel(const long long* grads, int world, long long shard_off, long long n,
                 float* __restrict__ master, float* __restrict__ m, float* __restrict__ v,
-                bf16* __restrict__ param_shard, float grad_scale, float lr, float b1, float b2,
-                float eps, float wd, float bc1, float bc2, float* sq_out, float* reduced_out) {
+                bf16* __restrict__ param_shard, AdamW opt, float* sq_out, float* reduced_out, int vec) {
   float local_sq = 0.f;
-  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n;
-       i += (long long)gridDim.x * blockDim.x) {
+  const long long stride = (long long)gridDim.x * blockDim.x;
+  // the gradient sources are only known here: 8-byte loads need every source 8-byte aligned at the shard's offset
+  bool g_aligned = true;
+  if (!(reduced_out && !sq_out))
+    for (int r = 0; r < world; ++r) g_aligned = g_aligned && ((grads[r] + 2 * shard_off) & 7ll) == 0;
+  const long long n4 = (vec && g_aligned) ? n >> 2 : 0;
+  for (long long i4 = (long long)blockIdx.x * blockDim.x + threadIdx.x; i4 < n4; i4 += stride) {
+    const long long i = i4 << 2;
+    float g[4] = {0.f, 0.f, 0.f, 0.f};
+    if (reduced_out && !sq_out) {
+      const float4 r = *reinterpret_cast<const float4*>(reduced_out + i);
+      g[0] = r.x; g[1] = r.y; g[2] = r.z; g[3] = r.w;
+    } else {
+      // all peers' values are requested before the first add (one NVLink round trip, not `world`)
+      for (int r0 = 0; r0 < world; r0 += 8) {
+        uint2 pv[8];
+#pragma unroll
+        for (int r = 0; r < 8; ++r)
+          pv[r] = (r0 + r < world) ? *reinterpret_cast<const uint2*>(reinterpret_cast<const bf16*>(grads[r0 + r]) + shard_off + i)
+                                   : make_uint2(0u, 0u);
+#pragma unroll
+        for (int r = 0; r < 8; ++r) {
+          g[0] += bf16lo(pv[r].x); g[1] += bf16hi(pv[r].x); g[2] += bf16lo(pv[r].y); g[3] += bf16hi(pv[r].y);
+        }
+      }
+    }
+    if (sq_out) {
+      if (reduced_out) *reinterpret_cast<float4*>(reduced_out + i) = make_float4(g[0], g[1], g[2], g[3]);
+      local_sq += g[0] * g[0] + g[1] * g[1] + g[2] * g[2] + g[3] * g[3];
+      continue;
+    }
+    float4 mm = *reinterpret_cast<const float4*>(m + i), vv = *reinterpret_cast<const float4*>(v + i);
+    float4 ww = *reinterpret_cast<const float4*>(master + i);
+    opt.step(g[0], mm.x, vv.x, ww.x); opt.step(g[1], mm.y, vv.y, ww.y);
+    opt.step(g[2], mm.z, vv.z, ww.z); opt.step(g[3], mm.w, vv.w, ww.w);
+    *reinterpret_cast<float4*>(m + i) = mm;
+    *reinterpret_cast<float4*>(v + i) = vv;
+    *reinterpret_cast<float4*>(master + i) = ww;
+    *reinterpret_cast<uint2*>(param_shard + i) = make_uint2(pack_bf16(ww.x, ww.y), pack_bf16(ww.z, ww.w));
+  }
+  for (long long i = (n4 << 2) + (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += stride) {
     float g = 0.f;
     if (reduced_out && !sq_out) {
       g = reduced_out[i];
     } else {
-      // all peers' values are requested before the first add (one NVLink round trip, not `world`)
-      for (int r0 = 0; r0 < world; r0 += 8) {
-        bf16 pv[8];
-#pragma unroll
-        for (int r = 0; r < 8; ++r)
-          pv[r] = (r0 + r < world) ? reinterpret_cast<const bf16*>(grads[r0 + r])[shard_off + i] : __float2bfloat16(0.f);
-#pragma unroll
-        for (int r = 0; r < 8; ++r) g += __bfloat162float(pv[r]);
-      }
+      for (int r = 0; r < world; ++r) g += __bfloat162float(reinterpret_cast<const bf16*>(grads[r])[shard_off + i]);
     }
     if (sq_out) {
       if (reduced_out) reduced_out[i] = g;
       local_sq += g * g;
       continue;
     }
-    g *= grad_scale;
-    const float mi = b1 * m[i] + (1.f - b1) * g;
-    const float vi = b2 * v[i] + (1.f - b2) * g * g;
+    float mi = m[i], vi = v[i], w = master[i];
+    opt.step(g, mi, vi, w);
     m[i] = mi;
     v[i] = vi;
-    float w = master[i];
-    w -= lr * ((mi / bc1) / (sqrtf(vi / bc2) + eps) + wd * w);
     master[i] = w;
     param_shard[i] = __float2bfloat16(w);
   }
@@ -267,17 +306,26 @@ reduce_scatter_pull_kernel(const long long* grads, const bf16* mc, int world, lo
 // parameter shard are updated in one pass.
 __global__ void __launch_bounds__(256)
 adamw_shard_kernel(const float* __restrict__ grad, long long n, float* __restrict__ master, float* __restrict__ m,
-                   float* __restrict__ v, bf16* __restrict__ param_shard, float grad_scale, float lr, float b1,
-                   float b2, float eps, float wd, float bc1, float bc2) {
-  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n;
-       i += (long long)gridDim.x * blockDim.x) {
-    const float g = grad[i] * grad_scale;
-    const float mi = b1 * m[i] + (1.f - b1) * g;
-    const float vi = b2 * v[i] + (1.f - b2) * g * g;
+                   float* __restrict__ v, bf16* __restrict__ param_shard, AdamW opt, int vec) {
+  const long long stride = (long long)gridDim.x * blockDim.x;
+  const long long n4 = vec ? n >> 2 : 0;
+  for (long long i4 = (long long)blockIdx.x * blockDim.x + threadIdx.x; i4 < n4; i4 += stride) {
+    const long long i = i4 << 2;
+    const float4 g = *reinterpret_cast<const float4*>(grad + i);
+    float4 mm = *reinterpret_cast<const float4*>(m + i), vv = *reinterpret_cast<const float4*>(v + i);
+    float4 ww = *reinterpret_cast<const float4*>(master + i);
+    opt.step(g.x, mm.x, vv.x, ww.x); opt.step(g.y, mm.y, vv.y, ww.y);
+    opt.step(g.z, mm.z, vv.z, ww.z); opt.step(g.w, mm.w, vv.w, ww.w);
+    *reinterpret_cast<float4*>(m + i) = mm;
+    *reinterpret_cast<float4*>(v + i) = vv;
+    *reinterpret_cast<float4*>(master + i) = ww;
+    *reinterpret_cast<uint2*>(param_shard + i) = make_uint2(pack_bf16(ww.x, ww.y), pack_bf16(ww.z, ww.w));
+  }
+  for (long long i = (n4 << 2) + (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += stride) {
+    float mi = m[i], vi = v[i], w = master[i];
+    opt.step(grad[i], mi, vi, w);
     m[i] = mi;
     v[i] = vi;
-    float w = master[i];
-    w -= lr * ((mi / bc1) / (sqrtf(vi / bc2) + eps) + wd * w);
     master[i] = w;
     param_shard[i] = __float2bfloat16(w);
   }
@@ -457,10 +505,14 @@ void rs_adamw(const long long* grads_dev, int world, long long shard_off, long l
               float eps, float wd, int step, float* sq_out, float* reduced_out, cudaStream_t s) {
   if (n == 0) return;
   const float bc1 = 1.f - powf(b1, (float)step), bc2 = 1.f - powf(b2, (float)step);
-  const int blocks = (int)std::min<long long>((n + 255) / 256, 148 * 8);
-  cb::rs_adamw_kernel<<<blocks, 256, 0, s>>>(grads_dev, world, shard_off, n, master, m, v,
-                                             (bf16*)param_shard, grad_scale, lr, b1, b2, eps, wd, bc1,
-                                             bc2, sq_out, reduced_out);
+  auto al = [](const void* p, size_t a) { return reinterpret_cast<uintptr_t>(p) % a == 0; };
+  // peers' gradient buffers are symmetric allocations (page aligned), so the offset decides their alignment
+  const int vec = (shard_off % 4 == 0) && al(master, 16) && al(m, 16) && al(v, 16) && al(param_shard, 8) &&
+                  (!reduced_out || al(reduced_out, 16));
+  const int blocks = (int)std::min<long long>(((vec ? n / 4 : n) + 255) / 256 + 1, 148 * 8);
+  const cb::AdamW opt{grad_scale, lr, b1, b2, eps, wd, bc1, bc2};
+  cb::rs_adamw_kernel<<<blocks, 256, 0, s>>>(grads_dev, world, shard_off, n, master, m, v, (bf16*)param_shard, opt,
+                                             sq_out, reduced_out, vec);
 }
 
 void allgather_pull(const long long* srcs_dev, int world, void* dst, long long bytes_per_rank,
@@ -490,9 +542,11 @@ void adamw_shard(const float* grad, long long n, float* master, float* m, float*
                  float grad_scale, float lr, float b1, float b2, float eps, float wd, int step, cudaStream_t s) {
   if (n == 0) return;
   const float bc1 = 1.f - powf(b1, (float)step), bc2 = 1.f - powf(b2, (float)step);
-  const int blocks = (int)std::min<long long>((n + 255) / 256, 148 * 8);
-  cb::adamw_shard_kernel<<<blocks, 256, 0, s>>>(grad, n, master, m, v, (bf16*)param_shard, grad_scale, lr, b1, b2,
-                                                eps, wd, bc1, bc2);
+  auto al = [](const void* p, size_t a) { return reinterpret_cast<uintptr_t>(p) % a == 0; };
+  const int vec = al(grad, 16) && al(master, 16) && al(m, 16) && al(v, 16) && al(param_shard, 8);
+  const int blocks = (int)std::min<long long>(((vec ? n / 4 : n) + 255) / 256 + 1, 148 * 8);
+  const cb::AdamW opt{grad_scale, lr, b1, b2, eps, wd, bc1, bc2};
+  cb::adamw_shard_kernel<<<blocks, 256, 0, s>>>(grad, n, master, m, v, (bf16*)param_shard, opt, vec);
 }
 
 int allreduce_norm_blocks(int M) { return M < 32 ? (M < 1 ? 1 : M) : 32; }

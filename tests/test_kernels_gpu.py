@@ -858,3 +858,42 @@ def test_vae_channels_last_encoder_matches_pytorch():
         (err.mean().item(), err.max().item(), scale)
     other = enc.encode(video, chunk_frames=4)
     assert (other - got).abs().max().item() <= 0.02 * want.abs().max().item()   # chunking does not change the result
+
+
+@pytest.mark.parametrize("n,off", [(4096, 0), (1003, 0), (2048, 3), (777, 8)])
+def test_adamw_kernels_match_the_fp32_definition(n, off):
+    """`rs_adamw` (gradients read from bf16 buffers, here one local source) and `adamw_shard` (fp32 reduced
+    gradient): vector path, scalar tail and a source offset that rules the vector loads out."""
+    k = torch.ops.cosmos_b200
+    g = torch.Generator(device=DEV).manual_seed(n + off)
+    full = torch.randn(off + n + 5, device=DEV, generator=g).bfloat16()
+    lr, b1, b2, eps, wd, scale, step = 1e-2, 0.9, 0.95, 1e-8, 0.1, 0.5, 3
+
+    def fresh():
+        w = torch.randn(n, device=DEV, generator=torch.Generator(device=DEV).manual_seed(1))
+        m = torch.randn(n, device=DEV, generator=torch.Generator(device=DEV).manual_seed(2)) * 0.1
+        v = torch.rand(n, device=DEV, generator=torch.Generator(device=DEV).manual_seed(3)) * 0.1
+        return w, m, v, torch.empty(n, device=DEV, dtype=torch.bfloat16)
+
+    gr = full[off:off + n].float()
+    w0, m0, v0, _ = fresh()
+    gs = gr * scale
+    m_ref = b1 * m0 + (1 - b1) * gs
+    v_ref = b2 * v0 + (1 - b2) * gs * gs
+    w_ref = w0 - lr * ((m_ref / (1 - b1 ** step)) / ((v_ref / (1 - b2 ** step)).sqrt() + eps) + wd * w0)
+    ptrs = torch.tensor([full.data_ptr()], dtype=torch.int64, device=DEV)
+    # pass 1: sum of squares (and the reduced gradient), pass 2: the update from the sources
+    sq = torch.zeros(1, device=DEV)
+    red = torch.empty(n, device=DEV)
+    w, m, v, p = fresh()
+    k.rs_adamw(ptrs, 1, off, w, m, v, p, 1.0, 0.0, b1, b2, eps, 0.0, step, 1, sq, red)
+    assert torch.allclose(sq, (gr * gr).sum()[None], rtol=1e-4) and torch.equal(red, gr)
+    k.rs_adamw(ptrs, 1, off, w, m, v, p, scale, lr, b1, b2, eps, wd, step, 0, None, None)
+    for got, want in ((m, m_ref), (v, v_ref), (w, w_ref)):
+        assert torch.allclose(got, want, rtol=1e-5, atol=1e-6)
+    assert torch.equal(p, w.bfloat16())
+    w, m, v, p = fresh()
+    k.adamw_shard(gr.contiguous(), w, m, v, p, scale, lr, b1, b2, eps, wd, step)
+    for got, want in ((m, m_ref), (v, v_ref), (w, w_ref)):
+        assert torch.allclose(got, want, rtol=1e-5, atol=1e-6)
+    assert torch.equal(p, w.bfloat16())
