@@ -464,7 +464,7 @@ def main():
     def watchdog():
         # A phase that blocks (a rank that failed alone leaves the others inside a collective) must not cost the
         # headline: past the deadline rank 0 prints what it has and every rank leaves.
-        deadline = args.extras_budget_s + 300.0
+        deadline = args.extras_budget_s + 150.0
         while time.perf_counter() - t_extra < deadline:
             time.sleep(1.0)
             if running["phase"] == "done":
