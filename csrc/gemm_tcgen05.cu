@@ -132,6 +132,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
   const int lane = threadIdx.x & 31;
   const int total_tiles = g.total;
 
+  int prefetched = 0;  // stages whose B half thread 0 has requested ahead of the producer loop
   if (threadIdx.x == 0) {
     for (int s = 0; s < STAGES; ++s) {
       mbar_init(full_bar(s), 1);
@@ -148,6 +149,25 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     if (g.total > g.tiles0) {
       prefetch_tmap(&tmA1);
       prefetch_tmap(&tmB1);
+    }
+    // Weight prefetch (single-CTA tiles, B in its [N, K] layout): the B halves of the first tile's first stages are
+    // requested here, while warp 1 still allocates tensor memory and before the dependency wait of a programmatic
+    // launch; their A halves follow in the producer loop. A stage's full barrier completes when both have landed.
+    if (NC == 1 && EPI != EPI_CONV && first_tile < total_tiles && first_tile < g.tiles0 && !g.p[0].b_mn &&
+        !g.p[0].debug) {
+      const GemmParams& p = g.p[0];
+      const int k_blocks = (p.K + BK - 1) / BK;
+      const int ks = first_tile % p.k_splits;
+      const int kb0 = ks * k_blocks / p.k_splits, kb1 = (ks + 1) * k_blocks / p.k_splits;
+      int tm, tn;
+      tile_coords(first_tile / p.k_splits, p.m_tiles, p.n_tiles, tm, tn);
+      const int n0 = (EPI == EPI_SWIGLU) ? tn * 128 : tn * BN;
+      for (int kb = kb0; kb < kb1 && prefetched < STAGES; ++kb, ++prefetched) {
+        const uint32_t sa = smem_base + prefetched * STAGE_BYTES;
+        mbar_arrive_expect_tx(full_bar(prefetched), STAGE_BYTES);
+        tma_load_2d(sa + A_BYTES, &tmB, full_bar(prefetched), kb * BK, n0);
+        tma_load_2d(sa + A_BYTES + B_BYTES / 2, &tmB, full_bar(prefetched), kb * BK, n0 + p.b_row1);
+      }
     }
   }
   if (warp == 1) {
@@ -176,26 +196,6 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       // ---------------- TMA producer
       int it = 0;
       bool ok = true;
-      // Weight prefetch ahead of the dependency wait (single-CTA tiles, B in its [N, K] layout): the B halves of
-      // the first tile's first stages are requested before `pdl_wait()`, their A halves after it. The full
-      // barrier of a stage completes only when both have landed.
-      int prefetched = 0;
-      if (NC == 1 && EPI != EPI_CONV && first_tile < total_tiles && first_tile < g.tiles0 && !g.p[0].b_mn &&
-          !g.p[0].debug) {
-        const GemmParams& p = g.p[0];
-        const int k_blocks = (p.K + BK - 1) / BK;
-        const int ks = first_tile % p.k_splits;
-        const int kb0 = ks * k_blocks / p.k_splits, kb1 = (ks + 1) * k_blocks / p.k_splits;
-        int tm, tn;
-        tile_coords(first_tile / p.k_splits, p.m_tiles, p.n_tiles, tm, tn);
-        const int n0 = (EPI == EPI_SWIGLU) ? tn * 128 : tn * BN;
-        for (int kb = kb0; kb < kb1 && prefetched < STAGES; ++kb, ++prefetched) {
-          const uint32_t sa = smem_base + prefetched * STAGE_BYTES;
-          mbar_arrive_expect_tx(full_bar(prefetched), STAGE_BYTES);
-          tma_load_2d(sa + A_BYTES, &tmB, full_bar(prefetched), kb * BK, n0);
-          tma_load_2d(sa + A_BYTES + B_BYTES / 2, &tmB, full_bar(prefetched), kb * BK, n0 + p.b_row1);
-        }
-      }
       pdl_wait();
       for (int t = first_tile; t < total_tiles && ok; t += tile_step) {
         const int second = t >= g.tiles0;
