@@ -156,13 +156,14 @@ class TPDecoder:
         else:
             self.lens.add_(self.step_inc)
         x = self.embed[self.tokens]
-        # Programmatic dependent launch for the layer kernels (COSMOS_DECODE_PDL=1): each one's set-up, and the GEMMs'
-        # first weight tiles, may overlap the tail of the kernel before it. Off by default: measured 8.96 -> 8.77 ms
-        # per step at TP 2, but 12.45 -> 12.6 ms on one GPU at batch 32 and 5.30 -> 5.50 ms at batch 1. A GEMM CTA
-        # needs most of an SM's shared memory, so the next GEMM cannot become resident before the current one
-        # leaves, and the programmatic edges cost about 0.5 us per launch in the replayed graph.
+        # Programmatic dependent launch for the layer kernels: each one's set-up, and the GEMMs' first weight tiles,
+        # may overlap the tail of the kernel before it. Measured per step: 5.80 -> 5.45 ms at TP 4 and 8.96 -> 8.77 ms
+        # at TP 2, but 12.45 -> 12.6 ms on one GPU at batch 32 and 5.30 -> 5.50 ms at batch 1 (a GEMM CTA needs most
+        # of an SM's shared memory, so the next GEMM cannot become resident before the current one leaves, and the
+        # programmatic edges cost about 0.5 us per launch in the replayed graph). Hence on from TP 4, where the step
+        # is latency-bound; COSMOS_DECODE_PDL=0 / 1 overrides.
         pdl = self.device.type == "cuda" and ops.get_backend() != "library" and \
-            os.environ.get("COSMOS_DECODE_PDL", "0") == "1"
+            os.environ.get("COSMOS_DECODE_PDL", "1" if self.tp >= 4 else "0") == "1"
         if pdl:
             torch.ops.cosmos_b200.set_pdl(True)
         try:

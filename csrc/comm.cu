@@ -206,23 +206,33 @@ rs_adamw_kernel(const long long* grads, int world, long long shard_off, long lon
 // is bytes in flight / latency).
 __global__ void __launch_bounds__(256)
 allgather_pull_kernel(const long long* srcs, int world, uint4* __restrict__ dst, long long n_vec) {
-  const long long total = n_vec * world;
+  // The sources are visited round-robin in chunks of 64 vectors (1 KB), so at any moment a GPU reads from all of
+  // its peers at once. Walking through the sources one after the other made every rank read the same source at the
+  // same time: 366 GB/s per rank on 4 GPUs against 574 on 2.
+  constexpr int CH = 64;
+  const long long nch = (n_vec + CH - 1) / CH;  // chunks per source
+  const long long total = nch * world * CH;
   const long long stride = (long long)gridDim.x * blockDim.x;
   for (long long i0 = (long long)blockIdx.x * blockDim.x + threadIdx.x; i0 < total; i0 += 4 * stride) {
     uint4 v[4];
+    long long at[4];
 #pragma unroll
     for (int u = 0; u < 4; ++u) {
       const long long i = i0 + u * stride;
+      at[u] = -1;
       if (i < total) {
-        const int r = (int)(i / n_vec);
-        v[u] = reinterpret_cast<const uint4*>(srcs[r])[i - (long long)r * n_vec];
+        const long long c = i / CH;
+        const int r = (int)(c % world);
+        const long long pos = (c / world) * CH + (i % CH);
+        if (pos < n_vec) {
+          v[u] = reinterpret_cast<const uint4*>(srcs[r])[pos];
+          at[u] = (long long)r * n_vec + pos;
+        }
       }
     }
 #pragma unroll
-    for (int u = 0; u < 4; ++u) {
-      const long long i = i0 + u * stride;
-      if (i < total) dst[i] = v[u];
-    }
+    for (int u = 0; u < 4; ++u)
+      if (at[u] >= 0) dst[at[u]] = v[u];
   }
 }
 
@@ -520,7 +530,7 @@ void allgather_pull(const long long* srcs_dev, int world, void* dst, long long b
   if (bytes_per_rank % 16 != 0) throw std::runtime_error("allgather_pull: shard bytes must be % 16");
   const long long n_vec = bytes_per_rank / 16;
   if (n_vec == 0) return;
-  const int blocks = (int)std::min<long long>((n_vec * world + 1023) / 1024, 148 * 8);
+  const int blocks = (int)std::min<long long>((n_vec * world + 1023) / 1024 + 1, 148 * 8);
   cb::allgather_pull_kernel<<<blocks, 256, 0, s>>>(srcs_dev, world, (uint4*)dst, n_vec);
 }
 
