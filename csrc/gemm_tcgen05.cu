@@ -1148,7 +1148,10 @@ void gemm_bf16(const GemmArgs& a, cudaStream_t stream) {
   if (!a.partial || a.N % 8 != 0) throw std::runtime_error("gemm_bf16: split-K needs a partial buffer and N % 8 == 0");
   cb::GemmGroup g{};
   CUtensorMap maps[4];
-  fill_problem(a, g.p[0], maps[0], maps[1]);
+  // more than one 128-row tile (a serving batch of 256): CTA pairs, so that each CTA stages half of the weight tile
+  // (the skinny GEMMs of such a batch are bound by operand delivery into shared memory, not by HBM)
+  const int nc = (pair_enabled() && a.epi != EPI_SWIGLU && a.M > cb::BM) ? 2 : 1;
+  fill_problem(a, g.p[0], maps[0], maps[1], nc);
   const int k_blocks = (a.K + cb::BK - 1) / cb::BK;
   const int ks = a.k_splits < k_blocks ? a.k_splits : k_blocks;
   g.p[0].k_splits = ks;
@@ -1156,11 +1159,19 @@ void gemm_bf16(const GemmArgs& a, cudaStream_t stream) {
   g.tiles0 = g.total = g.p[0].m_tiles * g.p[0].n_tiles * ks;
   maps[2] = maps[0];
   maps[3] = maps[1];
-  switch (a.epi) {
-    case EPI_PLAIN: launch<EPI_PLAIN, 1>(maps, g, g.total, 0, stream); break;
-    case EPI_SWIGLU: launch<EPI_SWIGLU, 1>(maps, g, g.total, 0, stream); break;
-    case EPI_GATED_RESID: launch<EPI_GATED_RESID, 1>(maps, g, g.total, 0, stream); break;
-    default: throw std::runtime_error("gemm_bf16: unknown epilogue");
+  if (nc == 2) {
+    switch (a.epi) {
+      case EPI_PLAIN: launch<EPI_PLAIN, 2>(maps, g, g.total, 0, stream); break;
+      case EPI_GATED_RESID: launch<EPI_GATED_RESID, 2>(maps, g, g.total, 0, stream); break;
+      default: throw std::runtime_error("gemm_bf16: unknown epilogue");
+    }
+  } else {
+    switch (a.epi) {
+      case EPI_PLAIN: launch<EPI_PLAIN, 1>(maps, g, g.total, 0, stream); break;
+      case EPI_SWIGLU: launch<EPI_SWIGLU, 1>(maps, g, g.total, 0, stream); break;
+      case EPI_GATED_RESID: launch<EPI_GATED_RESID, 1>(maps, g, g.total, 0, stream); break;
+      default: throw std::runtime_error("gemm_bf16: unknown epilogue");
+    }
   }
   if (a.partial_only) return;
   if (a.norm_out) {

@@ -325,7 +325,10 @@ def test_gemm_grouped_two_segments(epi):
 
 @pytest.mark.parametrize("m,n,k,epi", [(32, 768, 4096, ops.EPI_PLAIN), (32, 3072, 4096, ops.EPI_SWIGLU),
                                         (32, 4096, 1536, ops.EPI_GATED_RESID), (7, 512, 1024, ops.EPI_PLAIN),
-                                        (64, 1000, 2048, ops.EPI_PLAIN)])
+                                        (64, 1000, 2048, ops.EPI_PLAIN),
+                                        # more than one 128-row tile: split-K on CTA pairs
+                                        (256, 6144, 4096, ops.EPI_PLAIN), (200, 4096, 12288, ops.EPI_GATED_RESID),
+                                        (384, 1024, 4096, ops.EPI_PLAIN), (256, 24576, 4096, ops.EPI_SWIGLU)])
 def test_gemm_skinny_split_k(m, n, k, epi):
     """Decode-sized problems take the split-K path (fp32 partials + reduce/epilogue kernel)."""
     torch.manual_seed(18)
@@ -556,7 +559,8 @@ def test_training_step_own_kernels_match_library_baseline(monkeypatch):
     assert worst < 2e-2, f"parameters differ by {worst}"
 
 
-@pytest.mark.parametrize("m,n,k", [(32, 4096, 4096), (1, 4096, 12288), (7, 1024, 2048), (300, 512, 256)])
+@pytest.mark.parametrize("m,n,k", [(32, 4096, 4096), (1, 4096, 12288), (7, 1024, 2048), (300, 512, 256),
+                                   (256, 4096, 12288), (130, 4096, 4096)])
 def test_gemm_reduce_rmsnorm(m, n, k):
     """Output projection + residual + RMS-norm (the split-K reduction pass does all three for skinny problems;
     the last shape takes the unfused fallback) against the fp32 definition."""
