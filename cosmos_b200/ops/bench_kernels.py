@@ -240,6 +240,37 @@ def main():
                    f"frac_of_{src}_hbm": round(gbs / bw_peak, 3)}
             out.append(rec)
             print(json.dumps(rec), flush=True)
+    if "sample" in what:
+        # decode-step sampler over one vocabulary shard: penalties + top-64 selection, then the draw
+        b, v = (32, 151936) if args.small else (256, 151936)
+        g = torch.Generator(device=dev).manual_seed(0)
+        logits = (torch.randn(b, v, device=dev, generator=g) * 3).bfloat16()
+        seen_any = torch.rand(b, v, device=dev, generator=g) < 0.01
+        seen_out = seen_any & (torch.rand(b, v, device=dev, generator=g) < 0.5)
+        tokens = torch.randint(0, v, (b,), device=dev, generator=g)
+        pres, rep = torch.full((b,), 1.5, device=dev), torch.full((b,), 1.1, device=dev)
+        temp, top_p = torch.full((b,), 0.7, device=dev), torch.full((b,), 0.8, device=dev)
+        top_k = torch.full((b,), 20, device=dev, dtype=torch.long)
+        noise = torch.rand(b, 64, device=dev, generator=g).clamp_min(1e-7)
+        out_tok = torch.empty(b, dtype=torch.long, device=dev)
+
+        def run_sample():
+            cand = ops.sample_topk(logits, seen_any, seen_out, tokens, pres, rep, 0)
+            ops.sample_pick(cand, 1, temp, top_k, top_p, noise, v, out_tok)
+
+        ms = timeit(run_sample, args.iters, flush)
+        traffic = b * v * (2 + 1 + 1)
+        rec = {"kernel": "sample_topk + sample_pick", "shape": [b, v], "ms": round(ms, 4),
+               "one_pass_gbs": round(traffic / ms / 1e6, 1)}
+        if args.cublas:
+            lf = logits.float()
+
+            def run_ref():
+                cand = ops.sample_topk(lf, seen_any, seen_out, tokens, pres, rep, 0)   # fp32 logits: PyTorch definition
+                ops.sample_pick(cand, 1, temp, top_k, top_p, noise, v, out_tok)
+            rec["pytorch_ms"] = round(timeit(run_ref, args.iters, flush), 4)
+        out.append(rec)
+        print(json.dumps(rec), flush=True)
     if "vae" in what:
         # tokenizer decode of one clip through the channels-last implicit-GEMM decoder
         from cosmos_b200.models.vae import CausalVideoVAE
