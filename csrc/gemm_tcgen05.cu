@@ -1092,7 +1092,10 @@ int gemm_pick_k_splits(int M, int N, int K, int epi) {
   }
   // Between half a wave and a full one (the 96 tiles of a 24576-wide SwiGLU projection leave 52 SMs idle and took
   // 59 us for 201 MB of weights): split so that the work items fill whole rounds of the persistent CTAs. Cost of a
-  // choice = rounds x k-blocks per item; the smallest split count within 3 % of the best wins.
+  // choice = rounds x k-blocks per item; the smallest split count within 3 % of the best wins. Only for skinny
+  // problems (at most two 128-row tiles), where the weights dominate the traffic; taller ones would pay more for
+  // the fp32 partial sums than they gain.
+  if (m_tiles > 2) return 1;
   int best = 1;
   double best_cost = (double)k_blocks;
   for (int ks = 2; ks <= 8 && ks <= k_blocks / 4; ++ks) {
