@@ -284,3 +284,30 @@ def test_a_callback_that_returns_false_retires_the_request():
     assert len(b.out) == 6 and b.finish_reason == "length"
     assert eng.dec.cache.alloc.num_free() == free0
     _check_against_reference(model, b)
+
+
+def test_sampling_over_vocabulary_shards_equals_sampling_over_the_whole_vocabulary():
+    """`ops.sample_topk` per shard + `ops.sample_pick` over the gathered candidates (what tensor-parallel ranks do)
+    draws the same tokens as one shard holding the whole vocabulary: same candidates after the merge, same noise."""
+    g = torch.Generator().manual_seed(5)
+    b, v, shards = 6, 1000, 4
+    logits = torch.randn(b, v, generator=g) * 3
+    seen_any = torch.rand(b, v, generator=g) < 0.2
+    seen_out = seen_any & (torch.rand(b, v, generator=g) < 0.5)
+    tokens = torch.randint(0, v, (b,), generator=g)
+    pres, rep = torch.rand(b, generator=g), 1 + torch.rand(b, generator=g)
+    temp = torch.tensor([0.0, 0.5, 1.0, 0.8, 1.3, 0.0])
+    top_k = torch.tensor([5, 64, 10, 3, 40, 1])
+    top_p = torch.tensor([1.0, 0.9, 0.5, 1.0, 0.7, 1.0])
+    noise = torch.rand(b, 64, generator=g).clamp_min(1e-7)
+    whole = ops.sample_topk(logits, seen_any.clone(), seen_out.clone(), tokens, pres, rep, 0)
+    want = ops.sample_pick(whole, 1, temp, top_k, top_p, noise, v, torch.empty(b, dtype=torch.long))
+    vl = v // shards
+    parts = []
+    for r in range(shards):
+        sl = slice(r * vl, (r + 1) * vl)
+        parts.append(ops.sample_topk(logits[:, sl].contiguous(), seen_any[:, sl].contiguous(), seen_out[:, sl].contiguous(),
+                                     tokens, pres, rep, r * vl))
+    got = ops.sample_pick(torch.cat(parts, 0), shards, temp, top_k, top_p, noise, v, torch.empty(b, dtype=torch.long))
+    assert torch.equal(got, want)
+    assert got[0] == whole[0, 0, 1].view(torch.int32) and got[5] == whole[5, 0, 1].view(torch.int32)   # greedy rows
