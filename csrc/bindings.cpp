@@ -1015,6 +1015,10 @@ void sample_pick_(const Tensor& cand, int64_t n_src, const Tensor& temperature, 
 }
 
 void gemm_set_debug(int64_t bits) { cosmos::gemm_set_debug((int)bits); }
+// Split count that the skinny-GEMM path would use for this problem (1 = no split); host-side, needs no device.
+int64_t gemm_pick_k_splits(int64_t M, int64_t N, int64_t K, int64_t epi) {
+  return cosmos::gemm_pick_k_splits((int)M, (int)N, (int)K, (int)epi);
+}
 void set_pdl(bool on) { cosmos::set_pdl(on); }
 void attn_set_cta_pair(bool on) { cosmos::attn_set_cta_pair(on); }
 void attn_set_exp_emulation(int64_t v) { attn_exp_emu() = (int)v; }
@@ -1233,6 +1237,7 @@ TORCH_LIBRARY(cosmos_b200, m) {
   m.def("gemm_set_grid_limit", &gemm_set_grid_limit);
   m.def("gemm_set_cta_pair", &gemm_set_cta_pair);
   m.def("gemm_set_debug", &gemm_set_debug);
+  m.def("gemm_pick_k_splits", &gemm_pick_k_splits);
   m.def("set_pdl", &set_pdl);
   m.def("sample_topk", &sample_topk);
   m.def("sample_pick_", &sample_pick_);
