@@ -311,3 +311,15 @@ def test_sampling_over_vocabulary_shards_equals_sampling_over_the_whole_vocabula
     got = ops.sample_pick(torch.cat(parts, 0), shards, temp, top_k, top_p, noise, v, torch.empty(b, dtype=torch.long))
     assert torch.equal(got, want)
     assert got[0] == whole[0, 0, 1].view(torch.int32) and got[5] == whole[5, 0, 1].view(torch.int32)   # greedy rows
+
+
+def test_sample_topk_definition_pads_small_shards_and_takes_no_flags():
+    logits = torch.tensor([[0.5, 3.0, -1.0, 2.0]])
+    cand = ops.sample_topk(logits, None, None, None, None, None, 100)
+    vals, ids = cand[0, :, 0], cand[0, :, 1].contiguous().view(torch.int32)
+    assert cand.shape == (1, 64, 2)
+    assert vals[:4].tolist() == [3.0, 2.0, 0.5, -1.0] and ids[:4].tolist() == [101, 103, 100, 102]
+    assert torch.isinf(vals[4:]).all() and (vals[4:] < 0).all()
+    out = ops.sample_pick(cand, 1, torch.tensor([1.0]), torch.tensor([64]), torch.tensor([1.0]),
+                          torch.full((1, 64), 0.5), 1000, torch.empty(1, dtype=torch.long))
+    assert out.item() == 101      # equal noise: the most likely candidate wins; padded entries never do
