@@ -42,6 +42,7 @@ template <int NC> struct GemmCfg {
 struct GemmParams {
   int M, N, K;
   int b_row1;            // row offset in B of the second 128-row half of the tile
+  int mma_n;             // N of the MMA instruction: BN, or 64 / 128 for a convolution with that few output channels
   int n_tiles, m_tiles;  // tile counts (n_tiles counts 256-wide (or 128-wide for SWIGLU) tiles)
   bf16* C;
   long long ldc;
@@ -306,7 +307,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
         tc_fence_after();
         const uint32_t d_tmem = tmem_base + b * BN;
         const uint32_t a_step = p.a_mn ? 128u : 2u, b_step = p.b_mn ? 128u : 2u;
-        const uint32_t idesc = make_idesc_bf16(TILE_M, BN, p.a_mn, p.b_mn);
+        const uint32_t idesc = make_idesc_bf16(TILE_M, p.mma_n, p.a_mn, p.b_mn);
         for (int kb = kb0; kb < kb1; ++kb, ++it) {
           const int s = it % STAGES;
           const uint32_t ph = (it / STAGES) & 1;
@@ -1049,6 +1050,14 @@ static void fill_problem(const GemmArgs& a, cb::GemmParams& p, CUtensorMap& ta, 
   } else {
     p.n_tiles = (a.N + cb::BN - 1) / cb::BN;
     p.b_row1 = 128;
+  }
+  p.mma_n = cb::BN;
+  if (a.epi == EPI_CONV && a.N <= 128) {
+    // a tokenizer layer with 64 or 128 output channels: a 256-column MMA would spend 3/4 or 1/2 of its cycles on
+    // zero rows of B. The tile keeps its layout (one n tile, accumulator columns 0 .. N - 1); a CTA pair splits
+    // the narrower B between its two CTAs.
+    p.mma_n = a.N <= 64 ? 64 : 128;
+    if (nc == 2) p.b_row1 = p.mma_n / 2;
   }
   p.C = reinterpret_cast<bf16*>(a.C); p.ldc = a.ldc;
   p.bias = reinterpret_cast<const bf16*>(a.bias);

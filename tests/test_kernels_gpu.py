@@ -340,11 +340,13 @@ def test_gemm_skinny_split_k(m, n, k, epi):
     _close(got, want, 3e-2, 2e-2, f"skinny gemm {m}x{n}x{k} epi {epi}")
 
 
-def test_conv3d_implicit_gemm_matches_conv3d():
-    """One causal 3x3x3 convolution on a padded channels-last volume vs F.conv3d."""
+@pytest.mark.parametrize("cin,cout", [(64, 128), (64, 64), (128, 32), (64, 256), (128, 384)])
+def test_conv3d_implicit_gemm_matches_conv3d(cin, cout):
+    """One causal 3x3x3 convolution on a padded channels-last volume vs F.conv3d (64 / 128 output channels and fewer
+    run narrower MMAs; 384 takes two n tiles)."""
     import torch.nn.functional as F
     torch.manual_seed(19)
-    t, h, w, cin, cout = 5, 12, 20, 64, 128
+    t, h, w = 5, 12, 20
     x = _rand(1, cin, t, h, w)
     wt = _rand(cout, cin, 3, 3, 3, scale=1 / math.sqrt(27 * cin))
     b = _rand(cout)
