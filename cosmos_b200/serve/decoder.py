@@ -368,6 +368,7 @@ def main(argv=None) -> int:
     ap.add_argument("--no-graph", action="store_true")
     ap.add_argument("--no-fused", action="store_true", help="NCCL all-reduce instead of the one-shot kernel")
     ap.add_argument("--layers", type=int, default=0)
+    ap.add_argument("--page-size", type=int, default=32, help="tokens per KV-cache page (8, 16, 32, 64 or 128)")
     args = ap.parse_args(argv)
     world = int(os.environ.get("WORLD_SIZE", "1"))
     rank = int(os.environ.get("RANK", "0"))
@@ -379,7 +380,8 @@ def main(argv=None) -> int:
     cfg = get_model_config(args.model, **({"n_layers": args.layers} if args.layers else {}))
     prompt = args.prompt_vision + args.prompt_text
     dec = TPDecoder(cfg, world, rank, dist.group.WORLD if world > 1 else None, dev, max_batch=args.batch,
-                    max_len=prompt + args.new_tokens + args.warmup + 8, fused=not args.no_fused)
+                    max_len=prompt + args.new_tokens + args.warmup + 8, fused=not args.no_fused,
+                    page_size=args.page_size)
     dec.prefill_synthetic(args.batch, prompt, args.new_tokens + args.warmup + 8)
     if args.no_graph:
         for _ in range(args.warmup):

@@ -414,6 +414,7 @@ def main(argv=None) -> int:
     ap.add_argument("--prompt-len", type=int, default=306, help="50 text tokens + a short clip's vision tokens")
     ap.add_argument("--new-tokens", type=int, default=100)
     ap.add_argument("--layers", type=int, default=0)
+    ap.add_argument("--page-size", type=int, default=32, help="tokens per KV-cache page (8, 16, 32, 64 or 128)")
     ap.add_argument("--temperature", type=float, default=0.0, help="0 = greedy; else top-k 20 / top-p 0.8 sampling")
     args = ap.parse_args(argv)
     cuda = torch.cuda.is_available()
@@ -422,7 +423,8 @@ def main(argv=None) -> int:
     cfg = get_model_config(args.model, **({"n_layers": args.layers} if args.layers else {}))
     model = MoTModel(cfg, dtype=dtype, device=dev, towers=("ar",))  # the Reasoner needs the AR tower only
     model.init_weights(seed=0)
-    eng = BatchEngine(model, max_batch=args.max_num_seqs, max_len=args.prompt_len + args.new_tokens + 16)
+    eng = BatchEngine(model, max_batch=args.max_num_seqs, max_len=args.prompt_len + args.new_tokens + 16,
+                      page_size=args.page_size)
     g = torch.Generator().manual_seed(0)
     warm = eng.submit(torch.randint(0, cfg.vocab_size, (args.prompt_len,), generator=g).tolist(), 4)
     eng.run_until_done()  # graph capture and workspace set-up happen here
