@@ -28,7 +28,7 @@ namespace cosmos {
 // attention and its merge, all-reduce + norm): while on, those kernels are launched so that their set-up and their
 // weight prefetch overlap the tail of the kernel before them. Only kernels whose early part reads nothing that
 // another kernel of the stream writes honour it; the caller turns it on around a decode step (where the GEMMs'
-// B operands are weights) and off afterwards.
+// B operands are weights) and off afterwards. The switch is process-wide: launches from other host threads see it.
 void set_pdl(bool on);
 bool pdl_on();
 

@@ -44,9 +44,9 @@ __device__ __forceinline__ float penalised(float l, uint32_t any, uint32_t out, 
 
 // Calls f(index, key) for every element of the row; 8 elements per 16-byte load when the row allows it.
 template <typename F>
-__device__ __forceinline__ void for_each_key(const bf16* __restrict__ row, const uint8_t* __restrict__ any,
-                                             const uint8_t* __restrict__ out, int V, bool vec, float rep,
-                                             float presence, F f) {
+// (the flag rows are written by this kernel before they are read, so they are not declared read-only)
+__device__ __forceinline__ void for_each_key(const bf16* __restrict__ row, const uint8_t* any, const uint8_t* out,
+                                             int V, bool vec, float rep, float presence, F f) {
   if (vec) {
     const int nv = V >> 3;
     for (int v = threadIdx.x; v < nv; v += S_THREADS) {
