@@ -415,7 +415,7 @@ def gemm_decode_qkv_post(h, w, n_q_heads: int, cos, sin, q_gamma, k_gamma, eps: 
     """QKV projection of a decode step followed by `decode_qkv_post`. h [B, d]; w [(Hq + 2 Hkv) * 128, d]. On CUDA the
     skinny GEMM leaves its split-K partial sums and the post-processing kernel reduces them as it reads: one launch
     and one bf16 round trip fewer per layer."""
-    if _use_cuda(h, w) and w.shape[0] % 128 == 0:
+    if _use_cuda(h, w) and k_cache.shape[-1] == 128 and w.shape[0] % 128 == 0:
         return _k().gemm_decode_qkv_post(h, w, n_q_heads, cos.contiguous(), sin.contiguous(), q_gamma, k_gamma, eps,
                                          slots.contiguous(), k_cache, v_cache)
     qkv = gemm(h, w).view(h.shape[0], -1, k_cache.shape[-1])
