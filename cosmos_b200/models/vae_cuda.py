@@ -123,6 +123,14 @@ class CLDecoder:
         return torch.cat(outs, dim=0)[None]
 
 
+def even_frames(t0: int, n: int):
+    """Temporal stride 2 over a chunk of `n` frames whose first frame has index `t0` in its level's timeline: the
+    causal strided convolution keeps the frames with an even index. Returns (offset of the first kept frame inside
+    the chunk, number of kept frames, index of the first kept frame in the next level's timeline)."""
+    first = t0 % 2
+    return first, max(0, (n - first + 1) // 2), (t0 + 1) // 2
+
+
 class CLEncoder:
     """Tokenizer encoder on the same kernels as `CLDecoder`: padded channels-last volumes, every 3x3x3 causal
     convolution an implicit GEMM on the tensor cores, channel RMS-norm + SiLU as a bandwidth kernel.
@@ -204,9 +212,8 @@ class CLEncoder:
         y = self._conv(cache, name, x)
         body = y[TPAD:]
         if temporal:
-            first = t0 % 2          # offset of the first even-index frame inside the chunk
+            first, _, t0 = even_frames(t0, body.shape[0])
             body = body[first::2]
-            t0 = (t0 + 1) // 2
         hs, ws = (x.shape[1] - 2) // 2, (x.shape[2] - 2) // 2
         dst = torch.zeros(body.shape[0] + TPAD, hs + 2, ws + 2, y.shape[3], dtype=torch.bfloat16, device=self.device)
         dst[TPAD:, 1:-1, 1:-1] = body[:, 1:-1:2, 1:-1:2]
